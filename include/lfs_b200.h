@@ -1,0 +1,272 @@
+/*
+ * lfs_b200 — C ABI of the B200 (sm_100a) Gaussian-splatting training-step library.
+ *
+ * Drop-in boundary for the gsplat / 3DGUT path of LichtFeld Studio: every entry point replaces
+ * one operator (or one fused group of operators) that the reference reaches through
+ * gsplat/Ops.h, src/training/kernels/ssim.cu, src/training/fastgs/optimizer and
+ * src/training/strategies/mcmc.cpp. The citation above each declaration names the reference
+ * interface it replaces (paths relative to the reference project root).
+ *
+ * Conventions
+ *  - All data pointers are DEVICE pointers to contiguous float32 / int32 / int64 arrays in the
+ *    reference's layouts unless a parameter is documented as a host value.
+ *  - Nothing here allocates: outputs and scratch ("workspace") are supplied by the caller; the
+ *    *_workspace_bytes functions give the scratch size. Workspace pointers must be 256-byte aligned.
+ *  - Every call is asynchronous on `stream` (a cudaStream_t passed as void*) and returns
+ *    LFS_OK or a negative lfs_status. lfs_last_error() returns the message of the last failure on
+ *    the calling thread. No call synchronises the device except where stated.
+ *  - One camera per rasterize call, like the reference kernels (the camera index only selects the
+ *    output plane); batches are loops over cameras.
+ */
+#ifndef LFS_B200_H
+#define LFS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum lfs_status {
+    LFS_OK = 0,
+    LFS_EINVAL = -1,    /* bad argument (null pointer, unsupported size / mode) */
+    LFS_ECAPACITY = -2, /* a caller-provided buffer or workspace is too small */
+    LFS_ECUDA = -3,     /* a CUDA runtime call or kernel launch failed */
+    LFS_EUNSUPPORTED = -4
+} lfs_status;
+
+/* gsplat/Common.h:46-51 */
+typedef enum lfs_camera_model { LFS_PINHOLE = 0, LFS_ORTHO = 1, LFS_FISHEYE = 2, LFS_EQUIRECTANGULAR = 3 } lfs_camera_model;
+
+/* gsplat/Cameras.h:27-45 (UnscentedTransformParameters, passed by value in the reference) */
+typedef struct lfs_ut_params {
+    float alpha;                        /* 0.1 */
+    float beta;                         /* 2.0 */
+    float kappa;                        /* 0.0 */
+    float in_image_margin_factor;       /* 0.1 */
+    int require_all_sigma_points_valid; /* 1 */
+} lfs_ut_params;
+
+const char* lfs_last_error(void);
+/* Library version and the SM architecture the kernels were compiled for ("sm_100a"). */
+const char* lfs_build_info(void);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Operator level (same inputs / outputs as the reference operators)                           */
+/* ------------------------------------------------------------------------------------------ */
+
+/* gsplat/Ops.h:67-95 projection_ut_3dgs_fused -> gsplat/ProjectionUT3DGSFused.cu:17.
+ * Global shutter; camera_model PINHOLE (no distortion) or FISHEYE (radial_coeffs [C,4] or NULL).
+ * opacities and compensations may be NULL. Outputs of culled Gaussians other than radii = 0 are
+ * left untouched, like the reference. */
+int lfs_projection_ut_3dgs_fused(
+    int C, int N, const float* means, const float* quats, const float* scales, const float* opacities,
+    const float* viewmats0, const float* Ks, int image_width, int image_height,
+    float eps2d, float near_plane, float far_plane, float radius_clip,
+    int camera_model, lfs_ut_params ut_params, const float* radial_coeffs,
+    int32_t* radii, float* means2d, float* depths, float* conics, float* compensations, void* stream);
+
+/* gsplat/Ops.h:12-17 spherical_harmonics_fwd -> gsplat/SphericalHarmonicsCUDA.cu:374.
+ * n elements, coeffs [n,K,3], masks (uint8, NULL = all), colors [n,3]. */
+int lfs_spherical_harmonics_fwd(int n, int K, int degrees_to_use, const float* dirs, const float* coeffs,
+                                const uint8_t* masks, float* colors, void* stream);
+
+/* gsplat/Ops.h:18-25 spherical_harmonics_bwd (compute_v_dirs = false) -> SphericalHarmonicsCUDA.cu:445.
+ * Writes the FULL v_coeffs [n,K,3] (zeros where masked or above the active degree). */
+int lfs_spherical_harmonics_bwd(int n, int K, int degrees_to_use, const float* dirs, const uint8_t* masks,
+                                const float* v_colors, float* v_coeffs, void* stream);
+
+/* gsplat/Ops.h:28-38 intersect_tile, first pass (gsplat/Intersect.cpp:55-77): tiles_per_gauss [C,N]
+ * and the total number of intersections written to *n_isects_dev (device int64). The caller reads
+ * it back to size the outputs of lfs_intersect_tile_emit, exactly like the reference's .item(). */
+int lfs_intersect_tile_count(int C, int N, const float* means2d, const int32_t* radii,
+                             int tile_size, int tile_width, int tile_height,
+                             int32_t* tiles_per_gauss, int64_t* n_isects_dev, void* stream);
+
+size_t lfs_intersect_tile_workspace_bytes(int C, int N, int64_t n_isects);
+
+/* gsplat/Ops.h:28-38 intersect_tile, second pass + sort (gsplat/Intersect.cpp:79-121,
+ * gsplat/IntersectTile.cu:290-328). isect_ids [n_isects] int64 and flatten_ids [n_isects] int32 come
+ * out in the order a stable ascending radix sort of the (camera | tile | depth-bits) key gives.
+ * With sort == 0 they are written in emission order. */
+int lfs_intersect_tile_emit(int C, int N, const float* means2d, const int32_t* radii, const float* depths,
+                            const int32_t* tiles_per_gauss, int tile_size, int tile_width, int tile_height,
+                            int sort, int64_t n_isects, int64_t* isect_ids, int32_t* flatten_ids,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* gsplat/Ops.h:39-43 intersect_offset -> gsplat/IntersectTile.cu:206. offsets [C,tile_h,tile_w]. */
+int lfs_intersect_offset(int64_t n_isects, const int64_t* isect_ids, int C, int tile_width, int tile_height,
+                         int32_t* offsets, void* stream);
+
+size_t lfs_rasterize_workspace_bytes(int N);
+
+/* gsplat/Ops.h:97-125 rasterize_to_pixels_from_world_3dgs_fwd ->
+ * gsplat/RasterizeToPixelsFromWorld3DGSFwd.cu:20 (CDIM = 3, one camera). backgrounds [3] or NULL.
+ * renders [H,W,3], alphas [H,W,1], last_ids [H,W]. */
+int lfs_rasterize_to_pixels_from_world_3dgs_fwd(
+    int N, int64_t n_isects, const float* means, const float* quats, const float* scales, const float* colors,
+    const float* opacities, const float* backgrounds, int image_width, int image_height, int tile_size,
+    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs,
+    const int32_t* tile_offsets, const int32_t* flatten_ids,
+    float* renders, float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes, void* stream);
+
+/* gsplat/Ops.h:127-160 rasterize_to_pixels_from_world_3dgs_bwd ->
+ * gsplat/RasterizeToPixelsFromWorld3DGSBwd.cu:17. Writes (not accumulates) v_means [N,3],
+ * v_quats [N,4], v_scales [N,3], v_colors [N,3], v_opacities [N]. */
+int lfs_rasterize_to_pixels_from_world_3dgs_bwd(
+    int N, int64_t n_isects, const float* means, const float* quats, const float* scales, const float* colors,
+    const float* opacities, const float* backgrounds, int image_width, int image_height, int tile_size,
+    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs,
+    const int32_t* tile_offsets, const int32_t* flatten_ids,
+    const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
+    float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+/* src/training/kernels/ssim.cu:431 fusedssim (train = true). Images [CH,H,W]. */
+int lfs_fusedssim(int CH, int H, int W, float C1, float C2, const float* img1, const float* img2,
+                  float* ssim_map, float* dm_dmu1, float* dm_dsigma1_sq, float* dm_dsigma12, void* stream);
+
+/* src/training/kernels/ssim.cu:476 fusedssim_backward. */
+int lfs_fusedssim_backward(int CH, int H, int W, float C1, float C2, const float* img1, const float* img2,
+                           const float* dL_dmap, const float* dm_dmu1, const float* dm_dsigma1_sq,
+                           const float* dm_dsigma12, float* dL_dimg1, void* stream);
+
+/* src/training/fastgs/optimizer/include/adam_api.h (adam_step_wrapper) ->
+ * fastgs/optimizer/include/adam_kernels.cuh:13. */
+int lfs_adam_step(float* param, float* exp_avg, float* exp_avg_sq, const float* grad, int64_t n_elements,
+                  float lr, float beta1, float beta2, float eps, float bias_correction1_rcp,
+                  float bias_correction2_sqrt_rcp, void* stream);
+
+/* gsplat/Ops.h:50-57 relocation -> gsplat/RelocationCUDA.cu:12. */
+int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms,
+                   int n_max, float* new_opacities, float* new_scales, void* stream);
+
+/* gsplat/Ops.h:59-65 add_noise -> gsplat/RelocationCUDA.cu:113 (in place on means). */
+int lfs_add_noise(int n, const float* raw_opacities, const float* raw_scales, const float* raw_quats,
+                  const float* noise, float* means, float current_lr, void* stream);
+
+/* gsplat/Ops.h:45-48 quats_to_rotmats -> gsplat/QuatToRotmatCUDA.cu:13. rotmats [n,3,3] row-major. */
+int lfs_quats_to_rotmats(int n, const float* quats, float* rotmats, void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Fused training path (replaces the torch glue between the operators as well)                 */
+/* ------------------------------------------------------------------------------------------ */
+
+/* The six parameter tensors of SplatData (src/core/splat_data.hpp:104-109), or tensors of the same
+ * shapes (gradients, Adam moments). */
+typedef struct lfs_splats {
+    float* means;        /* [N,3]      */
+    float* sh0;          /* [N,1,3]    */
+    float* shN;          /* [N,K-1,3]  */
+    float* scaling_raw;  /* [N,3] log  */
+    float* rotation_raw; /* [N,4] wxyz */
+    float* opacity_raw;  /* [N,1] logit */
+} lfs_splats;
+
+/* Constants of src/training/rasterization/rasterizer.cpp:90-94 plus the per-call inputs. */
+typedef struct lfs_render_config {
+    int N;                 /* Gaussians */
+    int sh_coeffs;         /* K = total SH bases stored per Gaussian (1 + shN rows) */
+    int sh_degree;         /* active degree */
+    int image_width, image_height;
+    int tile_size;         /* 16 */
+    int camera_model;      /* lfs_camera_model */
+    float eps2d, near_plane, far_plane, radius_clip;
+    lfs_ut_params ut;
+    int64_t isect_capacity; /* room for intersections in the workspace; overflow -> LFS_ECAPACITY flag */
+} lfs_render_config;
+
+size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);
+
+/* Forward of FusedRasterizationWithSHFunction (src/training/rasterization/rasterizer_autograd.cpp:11)
+ * = gsplat::rasterize_from_world_with_sh_fwd (gsplat/Rasterization.cpp:279) including the SplatData
+ * activations (src/core/splat_data.cpp:267-286), for one camera. viewmat [4,4], K [3,3],
+ * radial_coeffs [4] or NULL, background [3] or NULL are device pointers.
+ * Outputs: render [H,W,3] (unclamped), alpha [H,W,1]. Everything the backward needs stays in the
+ * workspace. status_dev (device int32[4]): [0] overflow flag, [1] n_isects, [2] n_visible. */
+int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat,
+                       const float* K, const float* radial_coeffs, const float* background,
+                       float* render, float* alpha, int32_t* status_dev,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward of the same node (rasterizer_autograd.cpp:105 -> gsplat/Rasterization.cpp:470) followed by
+ * the activation backward, for the camera whose forward state is in the workspace. alpha is the
+ * forward's alpha output, v_render [H,W,3] and v_alpha [H,W,1] (may be NULL = zeros) the output gradients.
+ * grads: the six raw-parameter gradients; accumulate != 0 adds to them, else they are overwritten
+ * (all N rows, zeros for Gaussians that were not visible). */
+int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
+                        const float* alpha, const float* v_render, const float* v_alpha, const lfs_splats* grads,
+                        int accumulate, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device pointers of the forward state kept in the workspace, valid after lfs_render_forward on the
+ * same stream: the per-Gaussian outputs gsplat::rasterize_from_world_with_sh_fwd returns
+ * (gsplat/Ops.h:171-185) — radii [N,2], means2d [N,2], depths [N] (meaningful where radii > 0) — plus
+ * tiles_per_gauss [N], tile_offsets [tile_h*tile_w + 1] (last entry = n_isects), flatten_ids
+ * [n_isects], last_ids [H,W] and the packed 16-float rasterizer records [N,16] whose floats 12..14
+ * are the clamped colours. */
+typedef struct lfs_render_view {
+    const int32_t* radii;
+    const float* means2d;
+    const float* depths;
+    const int32_t* tiles_per_gauss;
+    const int32_t* tile_offsets;
+    const int32_t* flatten_ids;
+    const int32_t* last_ids;
+    const float* records;
+} lfs_render_view;
+int lfs_render_workspace_view(const lfs_render_config* cfg, void* workspace, size_t workspace_bytes,
+                              lfs_render_view* view);
+
+size_t lfs_photometric_loss_workspace_bytes(int H, int W);
+
+/* Trainer::compute_photometric_loss (src/training/trainer.cpp:107-134) on the clamped, permuted render
+ * (rasterizer.cpp:205) with fused_ssim "valid" padding (include/kernels/fused_ssim.cuh:59-67, :117-122),
+ * and its gradient w.r.t. the unclamped HWC render. target is CHW [3,H,W]. loss_dev (device float[4]):
+ * [0] loss, [1] L1 mean, [2] SSIM mean. grad_scale multiplies the gradient (1/batch for batches). */
+int lfs_photometric_loss(int H, int W, float lambda_dssim, float grad_scale, const float* render_hwc,
+                         const float* target_chw, float* v_render_hwc, float* loss_dev,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* FusedAdam::step over all six groups in one launch (src/training/optimizers/fused_adam.cpp:22-95,
+ * group order and learning rates of src/training/strategies/mcmc.cpp:487-492). lr[6] host values in
+ * group order means, sh0, shN, scaling, rotation, opacity; step_count >= 1 is the optimizer step
+ * index (bias corrections in double on the host); skip_shN != 0 reproduces the `iteration <= 1000`
+ * skip. first_row/n_rows select a contiguous Gaussian range (optimizer-state sharding).
+ * grad_scale multiplies the gradient on read. */
+int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const lfs_splats* exp_avg,
+                         const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr,
+                         float beta1, float beta2, float eps, int64_t step_count, int skip_shN,
+                         int64_t first_row, int64_t n_rows, float grad_scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* MCMC densification index work (src/training/strategies/mcmc.cpp:112-347)                    */
+/* ------------------------------------------------------------------------------------------ */
+
+/* mcmc.cpp:121-131: dead = sigmoid(opacity_raw) <= min_opacity | |rotation_raw|^2 < 1e-8.
+ * Writes ascending dead_indices / alive_indices (int64, capacity N each), alive_opacities (the
+ * probabilities handed to multinomial) and counts_dev (device int32[2]: n_dead, n_alive). */
+size_t lfs_mcmc_workspace_bytes(int N);
+int lfs_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity,
+                      int64_t* dead_indices, int64_t* alive_indices, float* alive_opacities,
+                      int32_t* counts_dev, void* workspace, size_t workspace_bytes, void* stream);
+
+/* mcmc.cpp:139-150 / :221-228: ratios[i] = clamp(1 + #occurrences of sampled[i] in sampled, 1, n_max),
+ * plus the gathered activated opacity / scale of each sampled Gaussian. counts is an int32[N] scratch. */
+int lfs_mcmc_gather_ratios(int N, int n_sampled, const int64_t* sampled, const float* opacity_raw,
+                           const float* scaling_raw, int n_max, int32_t* counts, int32_t* ratios,
+                           float* sampled_opacities, float* sampled_scales, void* stream);
+
+/* mcmc.cpp:160-187 (relocate, dst = dead indices) and :238-344 (add, dst = N..N+n-1 when dst_indices is
+ * NULL): clamp new opacity to [min_opacity, 1-1e-7], write logit / log back at the sampled rows, copy
+ * all six parameter rows sampled -> dst, zero the Adam moments at `sampled` (relocate) or at the
+ * appended rows (add). The parameter / moment buffers must have capacity for N + n rows when adding. */
+int lfs_mcmc_apply(int N, int sh_coeffs, int n_sampled, const int64_t* sampled, const int64_t* dst_indices,
+                   const float* new_opacities, const float* new_scales, float min_opacity,
+                   const lfs_splats* params, const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LFS_B200_H */

@@ -1,0 +1,495 @@
+// extern "C" entry points declared in include/lfs_b200.h: argument checks, workspace carving and
+// the launch sequences. No allocation happens here; every call is asynchronous on the caller's stream.
+#include <cmath>
+#include <cstring>
+
+#include "elementwise.cuh"
+#include "loss.cuh"
+#include "projection.cuh"
+#include "raster.cuh"
+#include "sort.cuh"
+
+#define LFS_STR2(x) #x
+#define LFS_STR(x) LFS_STR2(x)
+
+namespace lfs {
+const char* last_error();
+
+namespace {
+
+inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+struct Carver {
+    char* base;
+    size_t off = 0;
+    explicit Carver(void* b) : base(reinterpret_cast<char*>(b)) {}
+    template <typename T>
+    T* take(size_t count) {
+        off = (off + 255) & ~(size_t)255;
+        T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += count * sizeof(T);
+        return p;
+    }
+    size_t total() const { return (off + 255) & ~(size_t)255; }
+};
+
+uint32_t bit_width_u32(uint32_t v) {
+    uint32_t b = 0;
+    while (v) { ++b; v >>= 1; }
+    return b;
+}
+
+// which buffer of a ping-pong pair holds the result after sorting key_bits bits
+int sorted_sel(int key_bits) { return ((key_bits + 7) / 8) & 1; }
+
+SortScratch carve_scratch(Carver& c) {
+    SortScratch s;
+    s.hist = c.take<uint32_t>((size_t)kRadixBlocks * 256);
+    s.block_sums = c.take<uint32_t>(kScanBlocks + 64);
+    return s;
+}
+
+// ---- fused render workspace -------------------------------------------------------------------
+struct RenderWs {
+    CamDev* cam;
+    int32_t* counters;  // [0] overflow, [1] n_isects, [2] n_visible
+    int32_t *radii, *tiles, *offs, *tile_offsets, *last_ids;
+    float *means2d, *depths, *accum;
+    float4* records;
+    uint32_t *gkeys[2], *gvals[2], *tkeys[2], *tvals[2];
+    SortScratch scratch;
+    size_t bytes;
+};
+
+RenderWs carve_render(const lfs_render_config& cfg, void* base) {
+    Carver c(base);
+    RenderWs w;
+    const size_t N = (size_t)cfg.N;
+    const size_t cap = (size_t)cfg.isect_capacity;
+    const int tw = (cfg.image_width + cfg.tile_size - 1) / cfg.tile_size;
+    const int th = (cfg.image_height + cfg.tile_size - 1) / cfg.tile_size;
+    w.cam = c.take<CamDev>(1);
+    w.counters = c.take<int32_t>(16);
+    w.radii = c.take<int32_t>(N * 2);
+    w.means2d = c.take<float>(N * 2);
+    w.depths = c.take<float>(N);
+    w.tiles = c.take<int32_t>(N);
+    w.offs = c.take<int32_t>(N);
+    for (int k = 0; k < 2; ++k) { w.gkeys[k] = c.take<uint32_t>(N); w.gvals[k] = c.take<uint32_t>(N); }
+    w.records = c.take<float4>(N * 4);
+    w.accum = c.take<float>(N * 16);
+    for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
+    w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
+    w.last_ids = c.take<int32_t>((size_t)cfg.image_width * cfg.image_height);
+    w.scratch = carve_scratch(c);
+    w.bytes = c.total();
+    return w;
+}
+
+int check_cfg(const lfs_render_config* cfg) {
+    LFS_REQUIRE(cfg != nullptr, "null config");
+    LFS_REQUIRE(cfg->N >= 0 && cfg->image_width > 0 && cfg->image_height > 0, "bad sizes");
+    LFS_REQUIRE(cfg->tile_size == 16, "tile_size must be 16");
+    LFS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 4, "sh_degree must be in [0,4]");
+    LFS_REQUIRE(cfg->sh_coeffs >= (cfg->sh_degree + 1) * (cfg->sh_degree + 1), "not enough SH coefficients for the degree");
+    LFS_REQUIRE(cfg->camera_model == LFS_PINHOLE || cfg->camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
+    LFS_REQUIRE(cfg->isect_capacity >= 0 && cfg->isect_capacity < ((int64_t)1 << 31), "isect_capacity out of range");
+    return LFS_OK;
+}
+
+}  // namespace
+}  // namespace lfs
+
+using namespace lfs;
+
+extern "C" {
+
+const char* lfs_last_error(void) { return lfs::last_error(); }
+const char* lfs_build_info(void) { return "lfs_b200 0.1 (sm_100a, CUDA " LFS_STR(CUDART_VERSION) ")"; }
+
+// ---------------------------------------------------------------------------------------------
+int lfs_projection_ut_3dgs_fused(int C, int N, const float* means, const float* quats, const float* scales,
+                                 const float* opacities, const float* viewmats0, const float* Ks, int W, int H, float eps2d,
+                                 float near_plane, float far_plane, float radius_clip, int camera_model, lfs_ut_params ut,
+                                 const float* radial_coeffs, int32_t* radii, float* means2d, float* depths, float* conics,
+                                 float* compensations, void* stream) {
+    LFS_REQUIRE(C >= 0 && N >= 0 && W > 0 && H > 0, "bad sizes");
+    LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
+    if ((int64_t)C * N == 0) return LFS_OK;
+    LFS_REQUIRE(means && quats && scales && viewmats0 && Ks && radii && means2d && depths && conics, "null pointer");
+    return launch_projection_ut(C, N, means, quats, scales, opacities, viewmats0, Ks, radial_coeffs, W, H,
+                                make_proj_params(eps2d, near_plane, far_plane, radius_clip, ut), camera_model, radii,
+                                means2d, depths, conics, compensations, S(stream));
+}
+
+int lfs_spherical_harmonics_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks,
+                                float* colors, void* stream) {
+    LFS_REQUIRE(n >= 0 && degree >= 0 && degree <= 4 && K >= (degree + 1) * (degree + 1), "bad sizes");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(dirs && coeffs && colors, "null pointer");
+    return launch_sh_fwd(n, K, degree, dirs, coeffs, masks, colors, S(stream));
+}
+
+int lfs_spherical_harmonics_bwd(int n, int K, int degree, const float* dirs, const uint8_t* masks, const float* v_colors,
+                                float* v_coeffs, void* stream) {
+    LFS_REQUIRE(n >= 0 && degree >= 0 && degree <= 4 && K >= (degree + 1) * (degree + 1), "bad sizes");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(dirs && v_colors && v_coeffs, "null pointer");
+    return launch_sh_bwd(n, K, degree, dirs, masks, v_colors, v_coeffs, S(stream));
+}
+
+int lfs_intersect_tile_count(int C, int N, const float* means2d, const int32_t* radii, int tile_size, int tw, int th,
+                             int32_t* tiles_per_gauss, int64_t* n_isects_dev, void* stream) {
+    LFS_REQUIRE(C >= 0 && N >= 0 && tile_size > 0 && tw >= 0 && th >= 0, "bad sizes");
+    LFS_REQUIRE(n_isects_dev != nullptr, "null pointer");
+    const int64_t total = (int64_t)C * N;
+    if (total > 0) LFS_REQUIRE(means2d && radii && tiles_per_gauss, "null pointer");
+    int rc = launch_tile_count(total, means2d, radii, tile_size, tw, th, tiles_per_gauss, S(stream));
+    if (rc != LFS_OK) return rc;
+    return launch_sum_i32(total, tiles_per_gauss, n_isects_dev, S(stream));
+}
+
+static size_t isect_ws(int C, int N, int64_t n_isects, void* base, uint32_t** gk, uint32_t** gv, int32_t** offs,
+                       int32_t** n_dev, uint32_t** tk, uint32_t** tv, SortScratch* s) {
+    Carver c(base);
+    const size_t total = (size_t)C * N, cap = (size_t)(n_isects > 0 ? n_isects : 1);
+    for (int k = 0; k < 2; ++k) { gk[k] = c.take<uint32_t>(total); gv[k] = c.take<uint32_t>(total); }
+    *offs = c.take<int32_t>(total);
+    *n_dev = c.take<int32_t>(16);
+    for (int k = 0; k < 2; ++k) { tk[k] = c.take<uint32_t>(cap); tv[k] = c.take<uint32_t>(cap); }
+    *s = carve_scratch(c);
+    return c.total();
+}
+
+size_t lfs_intersect_tile_workspace_bytes(int C, int N, int64_t n_isects) {
+    uint32_t *gk[2], *gv[2], *tk[2], *tv[2];
+    int32_t *offs, *n_dev;
+    SortScratch s;
+    return isect_ws(C, N, n_isects, nullptr, gk, gv, &offs, &n_dev, tk, tv, &s);
+}
+
+int lfs_intersect_tile_emit(int C, int N, const float* means2d, const int32_t* radii, const float* depths,
+                            const int32_t* tiles_per_gauss, int tile_size, int tw, int th, int sort, int64_t n_isects,
+                            int64_t* isect_ids, int32_t* flatten_ids, void* workspace, size_t workspace_bytes, void* stream) {
+    LFS_REQUIRE(C >= 0 && N >= 0 && tile_size > 0 && n_isects >= 0 && n_isects < ((int64_t)1 << 31), "bad sizes");
+    if (n_isects == 0 || (int64_t)C * N == 0) return LFS_OK;
+    LFS_REQUIRE(means2d && radii && depths && tiles_per_gauss && isect_ids && flatten_ids && workspace, "null pointer");
+    TileListArgs a{};
+    const size_t need = isect_ws(C, N, n_isects, workspace, a.gkeys, a.gvals, &a.offs, &a.n_isects_dev, a.tkeys, a.tvals, &a.scratch);
+    if (workspace_bytes < need) { set_error("lfs_intersect_tile_emit: workspace too small (%zu < %zu)", workspace_bytes, need); return LFS_ECAPACITY; }
+    a.C = C; a.N = N; a.tw = tw; a.th = th; a.tile_size = tile_size; a.sort = sort ? 1 : 0; a.keys_ready = 0;
+    a.means2d = means2d; a.radii = radii; a.depths = depths; a.tiles = tiles_per_gauss;
+    a.capacity = n_isects; a.overflow = nullptr; a.tile_offsets = nullptr;
+    int sel = 0;
+    a.sel_out = &sel;
+    int rc = build_tile_lists(a, S(stream));
+    if (rc != LFS_OK) return rc;
+    return launch_compose_isect_ids(n_isects, a.tkeys[sel], a.tvals[sel], depths, isect_ids, flatten_ids, S(stream));
+}
+
+int lfs_intersect_offset(int64_t n_isects, const int64_t* isect_ids, int C, int tw, int th, int32_t* offsets, void* stream) {
+    LFS_REQUIRE(n_isects >= 0 && C >= 0 && tw >= 0 && th >= 0, "bad sizes");
+    if ((int64_t)C * tw * th == 0) return LFS_OK;
+    LFS_REQUIRE(offsets && (n_isects == 0 || isect_ids), "null pointer");
+    return launch_isect_offset(n_isects, isect_ids, C, tw, th, offsets, S(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+size_t lfs_rasterize_workspace_bytes(int N) {
+    Carver c(nullptr);
+    c.take<CamDev>(1);
+    c.take<float4>((size_t)N * 4);
+    c.take<float>((size_t)N * 16);
+    return c.total();
+}
+
+static int raster_common(int N, int64_t n_isects, int W, int H, int tile_size, int camera_model, const void* workspace,
+                         size_t workspace_bytes) {
+    LFS_REQUIRE(N >= 0 && n_isects >= 0 && n_isects < ((int64_t)1 << 31) && W > 0 && H > 0, "bad sizes");
+    LFS_REQUIRE(tile_size == 16, "tile_size must be 16");
+    LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
+    LFS_REQUIRE(workspace != nullptr, "null workspace");
+    if (workspace_bytes < lfs_rasterize_workspace_bytes(N)) { set_error("rasterize: workspace too small"); return LFS_ECAPACITY; }
+    return LFS_OK;
+}
+
+int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, const float* means, const float* quats,
+                                                const float* scales, const float* colors, const float* opacities,
+                                                const float* backgrounds, int W, int H, int tile_size, const float* viewmat0,
+                                                const float* K, int camera_model, const float* radial_coeffs,
+                                                const int32_t* tile_offsets, const int32_t* flatten_ids, float* renders,
+                                                float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes,
+                                                void* stream) {
+    int rc = raster_common(N, n_isects, W, H, tile_size, camera_model, workspace, workspace_bytes);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(viewmat0 && K && tile_offsets && renders && alphas && last_ids, "null pointer");
+    Carver c(workspace);
+    CamDev* cam = c.take<CamDev>(1);
+    float4* records = c.take<float4>((size_t)N * 4);
+    rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
+    if (rc != LFS_OK) return rc;
+    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, nullptr, S(stream));
+    if (rc != LFS_OK) return rc;
+    RasterArgs a{cam, records, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
+                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model};
+    return launch_raster_fwd(a, renders, alphas, last_ids, S(stream));
+}
+
+int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, const float* means, const float* quats,
+                                                const float* scales, const float* colors, const float* opacities,
+                                                const float* backgrounds, int W, int H, int tile_size, const float* viewmat0,
+                                                const float* K, int camera_model, const float* radial_coeffs,
+                                                const int32_t* tile_offsets, const int32_t* flatten_ids,
+                                                const float* render_alphas, const int32_t* last_ids,
+                                                const float* v_render_colors, const float* v_render_alphas, float* v_means,
+                                                float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
+                                                void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = raster_common(N, n_isects, W, H, tile_size, camera_model, workspace, workspace_bytes);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(viewmat0 && K && tile_offsets && render_alphas && last_ids && v_render_colors, "null pointer");
+    LFS_REQUIRE(v_means && v_quats && v_scales && v_colors && v_opacities, "null output pointer");
+    Carver c(workspace);
+    CamDev* cam = c.take<CamDev>(1);
+    float4* records = c.take<float4>((size_t)N * 4);
+    float* accum = c.take<float>((size_t)N * 16);
+    rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
+    if (rc != LFS_OK) return rc;
+    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, reinterpret_cast<float4*>(accum), S(stream));
+    if (rc != LFS_OK) return rc;
+    RasterArgs a{cam, records, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
+                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model};
+    rc = launch_raster_bwd(a, render_alphas, last_ids, v_render_colors, v_render_alphas, accum, S(stream));
+    if (rc != LFS_OK) return rc;
+    return launch_grad_epilogue_op(N, cam, accum, means, quats, scales, v_means, v_quats, v_scales, v_colors, v_opacities, S(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+int lfs_fusedssim(int CH, int H, int W, float C1, float C2, const float* img1, const float* img2, float* ssim_map,
+                  float* dm_dmu1, float* dm_dsigma1_sq, float* dm_dsigma12, void* stream) {
+    LFS_REQUIRE(CH >= 0 && H >= 0 && W >= 0, "bad sizes");
+    if ((int64_t)CH * H * W == 0) return LFS_OK;
+    LFS_REQUIRE(img1 && img2 && ssim_map, "null pointer");
+    LFS_REQUIRE((dm_dmu1 == nullptr) == (dm_dsigma1_sq == nullptr) && (dm_dmu1 == nullptr) == (dm_dsigma12 == nullptr),
+                "derivative maps must be all given or all null");
+    return launch_fusedssim(CH, H, W, C1, C2, img1, img2, ssim_map, dm_dmu1, dm_dsigma1_sq, dm_dsigma12, S(stream));
+}
+
+int lfs_fusedssim_backward(int CH, int H, int W, float C1, float C2, const float* img1, const float* img2,
+                           const float* dL_dmap, const float* dm_dmu1, const float* dm_dsigma1_sq, const float* dm_dsigma12,
+                           float* dL_dimg1, void* stream) {
+    (void)C1; (void)C2;
+    LFS_REQUIRE(CH >= 0 && H >= 0 && W >= 0, "bad sizes");
+    if ((int64_t)CH * H * W == 0) return LFS_OK;
+    LFS_REQUIRE(img1 && img2 && dL_dmap && dm_dmu1 && dm_dsigma1_sq && dm_dsigma12 && dL_dimg1, "null pointer");
+    return launch_fusedssim_backward(CH, H, W, img1, img2, dL_dmap, dm_dmu1, dm_dsigma1_sq, dm_dsigma12, dL_dimg1, S(stream));
+}
+
+size_t lfs_photometric_loss_workspace_bytes(int H, int W) { return photometric_workspace_bytes(H, W); }
+
+int lfs_photometric_loss(int H, int W, float lambda_dssim, float grad_scale, const float* render_hwc, const float* target_chw,
+                         float* v_render_hwc, float* loss_dev, void* workspace, size_t workspace_bytes, void* stream) {
+    LFS_REQUIRE(H > 0 && W > 0, "bad sizes");
+    LFS_REQUIRE(render_hwc && target_chw && loss_dev && workspace, "null pointer");
+    if (workspace_bytes < photometric_workspace_bytes(H, W)) { set_error("lfs_photometric_loss: workspace too small"); return LFS_ECAPACITY; }
+    return launch_photometric_loss(H, W, lambda_dssim, grad_scale, render_hwc, target_chw, v_render_hwc, loss_dev, workspace, S(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int lfs_adam_step(float* param, float* exp_avg, float* exp_avg_sq, const float* grad, int64_t n, float lr, float beta1,
+                  float beta2, float eps, float bc1_rcp, float bc2_sqrt_rcp, void* stream) {
+    LFS_REQUIRE(n >= 0, "bad size");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(param && exp_avg && exp_avg_sq && grad, "null pointer");
+    AdamGroups G{};
+    G.n_groups = 1;
+    G.g[0] = AdamGroup{param, exp_avg, exp_avg_sq, grad, n, lr * bc1_rcp,
+                       aligned16(param) && aligned16(exp_avg) && aligned16(exp_avg_sq) && aligned16(grad)};
+    G.prefix4[0] = 0;
+    G.prefix4[1] = (n + 3) / 4;
+    G.beta1 = beta1; G.beta2 = beta2; G.eps = eps; G.bc2_sqrt_rcp = bc2_sqrt_rcp; G.grad_scale = 1.0f;
+    return launch_adam_groups(G, S(stream));
+}
+
+int lfs_adam_step_splats(int N, int K, const lfs_splats* params, const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq,
+                         const lfs_splats* grads, const float* lr, float beta1, float beta2, float eps, int64_t step_count,
+                         int skip_shN, int64_t first_row, int64_t n_rows, float grad_scale, void* stream) {
+    LFS_REQUIRE(params && exp_avg && exp_avg_sq && grads && lr, "null pointer");
+    LFS_REQUIRE(N >= 0 && K >= 1 && step_count >= 1, "bad sizes");
+    LFS_REQUIRE(first_row >= 0 && n_rows >= 0 && first_row + n_rows <= N, "row range outside [0, N)");
+    if (n_rows == 0) return LFS_OK;
+    const double bc1 = 1.0 / (1.0 - std::pow((double)beta1, (double)step_count));
+    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow((double)beta2, (double)step_count));
+    float* P[6] = {params->means, params->sh0, params->shN, params->scaling_raw, params->rotation_raw, params->opacity_raw};
+    float* M[6] = {exp_avg->means, exp_avg->sh0, exp_avg->shN, exp_avg->scaling_raw, exp_avg->rotation_raw, exp_avg->opacity_raw};
+    float* V[6] = {exp_avg_sq->means, exp_avg_sq->sh0, exp_avg_sq->shN, exp_avg_sq->scaling_raw, exp_avg_sq->rotation_raw, exp_avg_sq->opacity_raw};
+    float* Gd[6] = {grads->means, grads->sh0, grads->shN, grads->scaling_raw, grads->rotation_raw, grads->opacity_raw};
+    const int width[6] = {3, 3, (K - 1) * 3, 3, 4, 1};
+    AdamGroups G{};
+    int ng = 0;
+    G.prefix4[0] = 0;
+    for (int k = 0; k < 6; ++k) {
+        if (width[k] == 0) continue;
+        if (k == 2 && skip_shN) continue;
+        LFS_REQUIRE(P[k] && M[k] && V[k] && Gd[k], "null tensor in a parameter group");
+        const int64_t off = first_row * width[k], n = n_rows * width[k];
+        AdamGroup g{P[k] + off, M[k] + off, V[k] + off, Gd[k] + off, n, (float)((double)lr[k]) * (float)bc1, 0};
+        g.aligned = aligned16(g.p) && aligned16(g.m) && aligned16(g.v) && aligned16(g.g);
+        G.g[ng] = g;
+        G.prefix4[ng + 1] = G.prefix4[ng] + (n + 3) / 4;
+        ++ng;
+    }
+    G.n_groups = ng;
+    G.beta1 = beta1; G.beta2 = beta2; G.eps = eps; G.bc2_sqrt_rcp = (float)bc2; G.grad_scale = grad_scale;
+    return launch_adam_groups(G, S(stream));
+}
+
+int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,
+                   float* new_opacities, float* new_scales, void* stream) {
+    LFS_REQUIRE(n >= 0 && n_max > 0, "bad sizes");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(opacities && scales && ratios && binoms && new_opacities && new_scales, "null pointer");
+    return launch_relocation(n, opacities, scales, ratios, binoms, n_max, new_opacities, new_scales, S(stream));
+}
+
+int lfs_add_noise(int n, const float* raw_opacities, const float* raw_scales, const float* raw_quats, const float* noise,
+                  float* means, float current_lr, void* stream) {
+    LFS_REQUIRE(n >= 0, "bad size");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(raw_opacities && raw_scales && raw_quats && noise && means, "null pointer");
+    return launch_add_noise(n, raw_opacities, raw_scales, raw_quats, noise, means, current_lr, S(stream));
+}
+
+int lfs_quats_to_rotmats(int n, const float* quats, float* rotmats, void* stream) {
+    LFS_REQUIRE(n >= 0, "bad size");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(quats && rotmats, "null pointer");
+    return launch_quats_to_rotmats(n, quats, rotmats, S(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+size_t lfs_render_workspace_bytes(const lfs_render_config* cfg) {
+    if (check_cfg(cfg) != LFS_OK) return 0;
+    return carve_render(*cfg, nullptr).bytes;
+}
+
+int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
+                       const float* radial_coeffs, const float* background, float* render, float* alpha,
+                       int32_t* status_dev, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && viewmat && K && render && alpha && workspace, "null pointer");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_render_forward: workspace too small (%zu < %zu)", workspace_bytes, w.bytes); return LFS_ECAPACITY; }
+    cudaStream_t st = S(stream);
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    rc = launch_camera_setup(1, viewmat, K, radial_coeffs, cfg->image_width, cfg->image_height, cfg->camera_model, w.cam, st);
+    if (rc != LFS_OK) return rc;
+    cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
+    const ProjParams pp = make_proj_params(cfg->eps2d, cfg->near_plane, cfg->far_plane, cfg->radius_clip, cfg->ut);
+    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, cfg->camera_model, cfg->tile_size, tw,
+                             th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records,
+                             reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
+    if (rc != LFS_OK) return rc;
+    TileListArgs a{};
+    a.C = 1; a.N = cfg->N; a.tw = tw; a.th = th; a.tile_size = cfg->tile_size; a.sort = 1; a.keys_ready = 1;
+    a.means2d = w.means2d; a.radii = w.radii; a.depths = w.depths; a.tiles = w.tiles;
+    for (int k = 0; k < 2; ++k) { a.gkeys[k] = w.gkeys[k]; a.gvals[k] = w.gvals[k]; a.tkeys[k] = w.tkeys[k]; a.tvals[k] = w.tvals[k]; }
+    a.offs = w.offs; a.n_isects_dev = w.counters + 1; a.capacity = cfg->isect_capacity; a.overflow = w.counters + 0;
+    int sel = 0;
+    a.sel_out = &sel;
+    a.tile_offsets = w.tile_offsets; a.scratch = w.scratch;
+    rc = build_tile_lists(a, st);
+    if (rc != LFS_OK) return rc;
+    RasterArgs ra{w.cam, w.records, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
+                  cfg->image_width, cfg->image_height, tw, th, cfg->camera_model};
+    rc = launch_raster_fwd(ra, render, alpha, w.last_ids, st);
+    if (rc != LFS_OK) return rc;
+    if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    return check_launch("lfs_render_forward");
+}
+
+int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, const float* background, const float* alpha,
+                        const float* v_render, const float* v_alpha, const lfs_splats* grads, int accumulate, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && alpha && v_render && grads && workspace, "null pointer");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_render_backward: workspace too small"); return LFS_ECAPACITY; }
+    cudaStream_t st = S(stream);
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
+    RasterArgs ra{w.cam, w.records, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
+                  cfg->image_width, cfg->image_height, tw, th, cfg->camera_model};
+    rc = launch_raster_bwd(ra, alpha, w.last_ids, v_render, v_alpha, w.accum, st);
+    if (rc != LFS_OK) return rc;
+    return launch_grad_epilogue_fused(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, w.accum, w.records, w.radii, *params,
+                                      *grads, accumulate, st);
+}
+
+int lfs_render_workspace_view(const lfs_render_config* cfg, void* workspace, size_t workspace_bytes, lfs_render_view* view) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(workspace && view, "null pointer");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_render_workspace_view: workspace too small"); return LFS_ECAPACITY; }
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
+    view->radii = w.radii; view->means2d = w.means2d; view->depths = w.depths; view->tiles_per_gauss = w.tiles;
+    view->tile_offsets = w.tile_offsets; view->flatten_ids = reinterpret_cast<const int32_t*>(w.tvals[sel]);
+    view->last_ids = w.last_ids; view->records = reinterpret_cast<const float*>(w.records);
+    return LFS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+static size_t mcmc_ws(int N, void* base, int32_t** flags, int32_t** offs, int32_t** total, SortScratch* s) {
+    Carver c(base);
+    *flags = c.take<int32_t>((size_t)N);
+    *offs = c.take<int32_t>((size_t)N);
+    *total = c.take<int32_t>(16);
+    *s = carve_scratch(c);
+    return c.total();
+}
+
+size_t lfs_mcmc_workspace_bytes(int N) {
+    int32_t *a, *b, *t;
+    SortScratch s;
+    return mcmc_ws(N, nullptr, &a, &b, &t, &s);
+}
+
+int lfs_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity, int64_t* dead_indices,
+                      int64_t* alive_indices, float* alive_opacities, int32_t* counts_dev, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+    LFS_REQUIRE(N >= 0, "bad size");
+    LFS_REQUIRE(counts_dev && workspace, "null pointer");
+    if (N > 0) LFS_REQUIRE(opacity_raw && rotation_raw && dead_indices && alive_indices && alive_opacities, "null pointer");
+    int32_t *flags, *offs, *total;
+    SortScratch s;
+    if (workspace_bytes < mcmc_ws(N, workspace, &flags, &offs, &total, &s)) { set_error("lfs_mcmc_classify: workspace too small"); return LFS_ECAPACITY; }
+    return launch_mcmc_classify(N, opacity_raw, rotation_raw, min_opacity, dead_indices, alive_indices, alive_opacities,
+                                counts_dev, flags, offs, total, s, S(stream));
+}
+
+int lfs_mcmc_gather_ratios(int N, int n_sampled, const int64_t* sampled, const float* opacity_raw, const float* scaling_raw,
+                           int n_max, int32_t* counts, int32_t* ratios, float* sampled_opacities, float* sampled_scales,
+                           void* stream) {
+    LFS_REQUIRE(N >= 0 && n_sampled >= 0 && n_max > 0, "bad sizes");
+    LFS_REQUIRE(counts != nullptr || N == 0, "null pointer");
+    if (n_sampled > 0) LFS_REQUIRE(sampled && opacity_raw && scaling_raw && ratios && sampled_opacities && sampled_scales, "null pointer");
+    return launch_mcmc_gather_ratios(N, n_sampled, sampled, opacity_raw, scaling_raw, n_max, counts, ratios, sampled_opacities,
+                                     sampled_scales, S(stream));
+}
+
+int lfs_mcmc_apply(int N, int K, int n_sampled, const int64_t* sampled, const int64_t* dst_indices, const float* new_opacities,
+                   const float* new_scales, float min_opacity, const lfs_splats* params, const lfs_splats* exp_avg,
+                   const lfs_splats* exp_avg_sq, void* stream) {
+    LFS_REQUIRE(N >= 0 && K >= 1 && n_sampled >= 0, "bad sizes");
+    if (n_sampled == 0) return LFS_OK;
+    LFS_REQUIRE(sampled && new_opacities && new_scales && params, "null pointer");
+    return launch_mcmc_apply(N, K, n_sampled, sampled, dst_indices, new_opacities, new_scales, min_opacity, *params, exp_avg,
+                             exp_avg_sq, S(stream));
+}
+
+}  // extern "C"

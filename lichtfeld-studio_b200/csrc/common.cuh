@@ -1,0 +1,84 @@
+// Shared declarations of the lfs_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lfs_b200.h"
+
+namespace lfs {
+
+// ---------------------------------------------------------------------------------------------
+// Error reporting: every entry point returns a status and leaves a message for lfs_last_error().
+// ---------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+
+#define LFS_REQUIRE(cond, msg)                         \
+    do {                                               \
+        if (!(cond)) {                                 \
+            ::lfs::set_error("%s: %s", __func__, msg); \
+            return LFS_EINVAL;                         \
+        }                                              \
+    } while (0)
+
+// The B200 has 148 SMs; persistent / grid-stride kernels are sized in multiples of it.
+constexpr int kNumSMs = 148;
+
+inline int grid_for(int64_t n, int block, int max_blocks_per_sm = 8) {
+    int64_t g = (n + block - 1) / block;
+    const int64_t cap = (int64_t)kNumSMs * max_blocks_per_sm;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-camera constants derived once per call by camera_setup_kernel from the row-major
+// world-to-camera matrix and the intrinsics (global shutter).
+// ---------------------------------------------------------------------------------------------
+struct CamDev {
+    float qw, qx, qy, qz;  // quat_cast of the rotation block
+    float tx, ty, tz;      // translation column
+    float Rinv[9];         // mat3_cast(inverse(q)), row-major
+    float ro[3];           // world ray origin = -Rinv * t
+    float campos[3];       // -R^T t (what inverse(viewmat)[:3,3] gives), used for SH directions
+    float fx, fy, cx, cy;
+    float k[4];            // fisheye radial coefficients
+    float max_angle;       // fisheye
+    float approx_b1;       // fisheye: linear term of the crude backward polynomial
+    int W, H, model;
+    int pad;
+};
+
+// One packed 64-byte record per Gaussian for the rasterizer:
+//   r0 = (M00, M01, M02, gro.x)   M = diag(1/scale) * R^T
+//   r1 = (M10, M11, M12, gro.y)   gro = M * (ray_origin - mean)
+//   r2 = (M20, M21, M22, gro.z)
+//   r3 = (red, green, blue, opacity)
+constexpr int kRecordFloats = 16;
+
+// Host-side launchers shared between translation units (all asynchronous on `st`).
+int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, int W, int H,
+                        int model, CamDev* cams, cudaStream_t st);
+
+// ---- sort.cu -------------------------------------------------------------------------------
+struct SortScratch {
+    uint32_t* hist;       // [kRadixBlocks * 256]
+    uint32_t* block_sums; // [kScanBlocks + 1]
+};
+constexpr int kRadixBlocks = kNumSMs * 4;
+constexpr int kScanBlocks = kNumSMs * 4;
+size_t sort_scratch_bytes();
+
+// Stable LSD radix sort of (key, value) uint32 pairs over key bits [0, key_bits). n is read from
+// *n_dev when n_dev != nullptr (device-side count, bounded by n_max), else n_max is the count.
+// Returns the index (0 or 1) of the buffer pair holding the result.
+int radix_sort_pairs(uint32_t* keys[2], uint32_t* vals[2], const int32_t* n_dev, int64_t n_max, int key_bits,
+                     const SortScratch& scratch, cudaStream_t st);
+
+// out[i] = exclusive prefix sum of gather(i) = src[idx ? idx[i] : i]; total written to *total_dev.
+int exclusive_scan_gather(const int32_t* src, const uint32_t* idx, int64_t n, int32_t* out, int32_t* total_dev,
+                          const SortScratch& scratch, cudaStream_t st);
+
+}  // namespace lfs

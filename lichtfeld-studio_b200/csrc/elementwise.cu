@@ -1,0 +1,321 @@
+// Streaming per-element / per-Gaussian kernels: fused Adam, operator-level SH, MCMC relocation,
+// noise injection, quaternion -> matrix, and the index work of the MCMC densification step.
+//
+// Replaces src/training/fastgs/optimizer/include/adam_kernels.cuh:13 (K11, one launch for all six
+// groups instead of six), gsplat/SphericalHarmonicsCUDA.cu:374 / :445 (K2 / K3), gsplat/RelocationCUDA.cu:12
+// (K12) and :113 (K13), gsplat/QuatToRotmatCUDA.cu:13 (K14) and the ATen index glue of
+// src/training/strategies/mcmc.cpp:112-347. All of it is HBM-bound.
+#include "elementwise.cuh"
+#include "gsmath.cuh"
+
+namespace lfs {
+
+namespace {
+
+// ---- Adam -----------------------------------------------------------------------------------
+__device__ __forceinline__ void adam_update(float& p, float& m, float& v, float g, float beta1, float beta2, float eps,
+                                            float step_size, float bc2_sqrt_rcp) {
+    const float m1 = beta1 * m + (1.0f - beta1) * g;
+    const float m2 = beta2 * v + (1.0f - beta2) * g * g;
+    const float denom = sqrtf(m2) * bc2_sqrt_rcp + eps;
+    p -= step_size * m1 / denom;
+    m = m1;
+    v = m2;
+}
+
+__global__ void __launch_bounds__(256) adam_groups_kernel(AdamGroups G) {
+    const int64_t total4 = G.prefix4[G.n_groups];
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < total4; q += (int64_t)gridDim.x * blockDim.x) {
+        int gi = 0;
+#pragma unroll
+        for (int k = 1; k < 6; ++k)
+            if (k < G.n_groups && q >= G.prefix4[k]) gi = k;
+        const AdamGroup& grp = G.g[gi];
+        const int64_t e = (q - G.prefix4[gi]) * 4;
+        if (grp.aligned && e + 4 <= grp.n) {
+            float4 p = *reinterpret_cast<float4*>(grp.p + e);
+            float4 m = *reinterpret_cast<float4*>(grp.m + e);
+            float4 v = *reinterpret_cast<float4*>(grp.v + e);
+            const float4 g = *reinterpret_cast<const float4*>(grp.g + e);
+            adam_update(p.x, m.x, v.x, g.x * G.grad_scale, G.beta1, G.beta2, G.eps, grp.step_size, G.bc2_sqrt_rcp);
+            adam_update(p.y, m.y, v.y, g.y * G.grad_scale, G.beta1, G.beta2, G.eps, grp.step_size, G.bc2_sqrt_rcp);
+            adam_update(p.z, m.z, v.z, g.z * G.grad_scale, G.beta1, G.beta2, G.eps, grp.step_size, G.bc2_sqrt_rcp);
+            adam_update(p.w, m.w, v.w, g.w * G.grad_scale, G.beta1, G.beta2, G.eps, grp.step_size, G.bc2_sqrt_rcp);
+            *reinterpret_cast<float4*>(grp.p + e) = p;
+            *reinterpret_cast<float4*>(grp.m + e) = m;
+            *reinterpret_cast<float4*>(grp.v + e) = v;
+        } else {
+            for (int64_t i = e; i < e + 4 && i < grp.n; ++i) {
+                float p = grp.p[i], m = grp.m[i], v = grp.v[i];
+                adam_update(p, m, v, grp.g[i] * G.grad_scale, G.beta1, G.beta2, G.eps, grp.step_size, G.bc2_sqrt_rcp);
+                grp.p[i] = p; grp.m[i] = m; grp.v[i] = v;
+            }
+        }
+    }
+}
+
+// ---- spherical harmonics, operator level ------------------------------------------------------
+__global__ void __launch_bounds__(256) sh_fwd_kernel(int n, int K, int degree, const float* __restrict__ dirs,
+                                                     const float* __restrict__ coeffs, const uint8_t* __restrict__ masks,
+                                                     float* __restrict__ colors) {
+    const int nb = (degree + 1) * (degree + 1);
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < n; e += gridDim.x * blockDim.x) {
+        if (masks && !masks[e]) continue;
+        float B[25];
+        sh_basis(degree, dirs[e * 3], dirs[e * 3 + 1], dirs[e * 3 + 2], B);
+        const float* cf = coeffs + (size_t)e * K * 3;
+        float r = 0.f, g = 0.f, b = 0.f;
+        for (int k = 0; k < nb; ++k) { r += B[k] * cf[k * 3]; g += B[k] * cf[k * 3 + 1]; b += B[k] * cf[k * 3 + 2]; }
+        colors[e * 3] = r; colors[e * 3 + 1] = g; colors[e * 3 + 2] = b;
+    }
+}
+
+__global__ void __launch_bounds__(256) sh_bwd_kernel(int n, int K, int degree, const float* __restrict__ dirs,
+                                                     const uint8_t* __restrict__ masks, const float* __restrict__ v_colors,
+                                                     float* __restrict__ v_coeffs) {
+    const int nb = (degree + 1) * (degree + 1);
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < n; e += gridDim.x * blockDim.x) {
+        float* vc = v_coeffs + (size_t)e * K * 3;
+        if (masks && !masks[e]) {
+            for (int k = 0; k < K * 3; ++k) vc[k] = 0.f;
+            continue;
+        }
+        float B[25];
+        sh_basis(degree, dirs[e * 3], dirs[e * 3 + 1], dirs[e * 3 + 2], B);
+        const float r = v_colors[e * 3], g = v_colors[e * 3 + 1], b = v_colors[e * 3 + 2];
+        for (int k = 0; k < K; ++k) {
+            const float w = k < nb ? B[k] : 0.f;
+            vc[k * 3] = w * r; vc[k * 3 + 1] = w * g; vc[k * 3 + 2] = w * b;
+        }
+    }
+}
+
+// ---- MCMC ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) relocation_kernel(int n, const float* __restrict__ opacities, const float* __restrict__ scales,
+                                                         const int32_t* __restrict__ ratios, const float* __restrict__ binoms,
+                                                         int n_max, float* __restrict__ new_opacities, float* __restrict__ new_scales) {
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+        const int n_idx = ratios[idx];
+        const float op = opacities[idx];
+        const float no = 1.0f - powf(1.0f - op, 1.0f / (float)n_idx);
+        new_opacities[idx] = no;
+        // denom = sum_{i=1..n} sum_{k<i} C(i-1,k) (-1)^k no^(k+1) / sqrt(k+1), same summation order
+        float denom_sum = 0.0f;
+        for (int i = 1; i <= n_idx; ++i) {
+            float pw = no;  // no^(k+1)
+            for (int k = 0; k <= i - 1; ++k) {
+                const float sign = (k & 1) ? -1.0f : 1.0f;
+                const float term = (sign / sqrtf((float)(k + 1))) * pw;
+                denom_sum += binoms[(i - 1) * n_max + k] * term;
+                pw *= no;
+            }
+        }
+        const float coeff = op / denom_sum;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) new_scales[idx * 3 + k] = coeff * scales[idx * 3 + k];
+    }
+}
+
+__global__ void __launch_bounds__(256) add_noise_kernel(int n, const float* __restrict__ raw_opacities, const float* __restrict__ raw_scales,
+                                                        const float* __restrict__ raw_quats, const float* __restrict__ noise,
+                                                        float* __restrict__ means, float current_lr) {
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+        const float s2[3] = {__expf(2.f * raw_scales[idx * 3]), __expf(2.f * raw_scales[idx * 3 + 1]), __expf(2.f * raw_scales[idx * 3 + 2])};
+        const float4 q = reinterpret_cast<const float4*>(raw_quats)[idx];
+        float w = q.x, x = q.y, y = q.z, z = q.w;
+        const float inv_norm = fminf(rsqrtf(x * x + y * y + z * z + w * w), 1e+12f);
+        x *= inv_norm; y *= inv_norm; z *= inv_norm; w *= inv_norm;
+        const float x2 = x * x, y2 = y * y, z2 = z * z, xy = x * y, xz = x * z, yz = y * z, wx = w * x, wy = w * y, wz = w * z;
+        const float R[9] = {1.f - 2.f * (y2 + z2), 2.f * (xy - wz), 2.f * (xz + wy),
+                            2.f * (xy + wz), 1.f - 2.f * (x2 + z2), 2.f * (yz - wx),
+                            2.f * (xz - wy), 2.f * (yz + wx), 1.f - 2.f * (x2 + y2)};
+        const float nz[3] = {noise[idx * 3], noise[idx * 3 + 1], noise[idx * 3 + 2]};
+        // (R S^2 R^T) noise = R (S^2 (R^T noise))
+        float tmp[3];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) tmp[k] = s2[k] * (R[0 * 3 + k] * nz[0] + R[1 * 3 + k] * nz[1] + R[2 * 3 + k] * nz[2]);
+        const float opacity = 1.0f / (1.f + __expf(-raw_opacities[idx]));
+        const float op_sigmoid = 1.0f / (1.f + __expf(100.f * opacity - 0.5f));
+        const float nf = current_lr * op_sigmoid;
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+            means[idx * 3 + a] += nf * (R[a * 3 + 0] * tmp[0] + R[a * 3 + 1] * tmp[1] + R[a * 3 + 2] * tmp[2]);
+    }
+}
+
+__global__ void __launch_bounds__(256) quats_to_rotmats_kernel(int n, const float* __restrict__ quats, float* __restrict__ rotmats) {
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+        const float4 q = reinterpret_cast<const float4*>(quats)[idx];
+        float R[9], inv_norm, qn[4];
+        quat_to_rotmat_renorm(q.x, q.y, q.z, q.w, R, inv_norm, qn);
+#pragma unroll
+        for (int k = 0; k < 9; ++k) rotmats[(size_t)idx * 9 + k] = R[k];
+    }
+}
+
+__device__ __forceinline__ float sigmoid_d(float x) { return (float)(1.0 / (1.0 + exp(-(double)x))); }
+
+__global__ void __launch_bounds__(256) mcmc_flags_kernel(int N, const float* __restrict__ opacity_raw, const float* __restrict__ rotation_raw,
+                                                         float min_opacity, int32_t* __restrict__ flags) {
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
+        const float4 q = reinterpret_cast<const float4*>(rotation_raw)[g];
+        const float n2 = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+        flags[g] = (sigmoid_d(opacity_raw[g]) <= min_opacity || n2 < 1e-8f) ? 1 : 0;
+    }
+}
+
+__global__ void __launch_bounds__(256) mcmc_compact_kernel(int N, const int32_t* __restrict__ flags, const int32_t* __restrict__ dead_offs,
+                                                           const int32_t* __restrict__ n_dead_dev, const float* __restrict__ opacity_raw,
+                                                           int64_t* __restrict__ dead_indices, int64_t* __restrict__ alive_indices,
+                                                           float* __restrict__ alive_opacities, int32_t* __restrict__ counts) {
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
+        const int d = dead_offs[g];
+        if (flags[g]) {
+            dead_indices[d] = g;
+        } else {
+            const int a = g - d;
+            alive_indices[a] = g;
+            alive_opacities[a] = sigmoid_d(opacity_raw[g]);
+        }
+        if (g == 0) { counts[0] = *n_dead_dev; counts[1] = N - *n_dead_dev; }
+    }
+}
+
+__global__ void __launch_bounds__(256) mcmc_count_kernel(int n, const int64_t* __restrict__ sampled, int32_t* __restrict__ counts) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) atomicAdd(&counts[sampled[i]], 1);
+}
+
+__global__ void __launch_bounds__(256) mcmc_gather_kernel(int n, const int64_t* __restrict__ sampled, const int32_t* __restrict__ counts,
+                                                          const float* __restrict__ opacity_raw, const float* __restrict__ scaling_raw,
+                                                          int n_max, int32_t* __restrict__ ratios, float* __restrict__ s_opac,
+                                                          float* __restrict__ s_scales) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int64_t g = sampled[i];
+        ratios[i] = max(1, min(1 + counts[g], n_max));
+        s_opac[i] = sigmoid_d(opacity_raw[g]);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) s_scales[i * 3 + k] = (float)exp((double)scaling_raw[g * 3 + k]);
+    }
+}
+
+__global__ void __launch_bounds__(256) mcmc_writeback_kernel(int n, const int64_t* __restrict__ sampled, const float* __restrict__ new_opac,
+                                                             const float* __restrict__ new_scales, float min_opacity,
+                                                             float* __restrict__ opacity_raw, float* __restrict__ scaling_raw) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int64_t g = sampled[i];
+        const float o = fminf(fmaxf(new_opac[i], min_opacity), 1.0f - 1e-7f);
+        opacity_raw[g] = logf(o / (1.0f - o));
+#pragma unroll
+        for (int k = 0; k < 3; ++k) scaling_raw[g * 3 + k] = logf(new_scales[i * 3 + k]);
+    }
+}
+
+struct RowTable {
+    float* p[6]; float* m[6]; float* v[6];
+    int width[6];
+    int prefix[7];
+};
+
+// Copies the 6 parameter rows src -> dst and zeroes the moments: at the source rows when relocating
+// (zero_at_dst == 0), at the destination rows when appending.
+__global__ void __launch_bounds__(256) mcmc_copy_rows_kernel(int n, int64_t N, const int64_t* __restrict__ sampled,
+                                                             const int64_t* __restrict__ dst_indices, RowTable T, int zero_at_dst) {
+    const int row_w = T.prefix[6];
+    const int64_t total = (int64_t)n * row_w;
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (int64_t)gridDim.x * blockDim.x) {
+        const int i = (int)(q / row_w), j = (int)(q % row_w);
+        int gi = 0;
+#pragma unroll
+        for (int k = 1; k < 6; ++k)
+            if (j >= T.prefix[k]) gi = k;
+        const int col = j - T.prefix[gi], w = T.width[gi];
+        const int64_t src = sampled[i];
+        const int64_t dst = dst_indices ? dst_indices[i] : (N + i);
+        T.p[gi][dst * w + col] = T.p[gi][src * w + col];
+        const int64_t z = zero_at_dst ? dst : src;
+        if (T.m[gi]) T.m[gi][z * w + col] = 0.f;
+        if (T.v[gi]) T.v[gi][z * w + col] = 0.f;
+    }
+}
+
+}  // namespace
+
+int launch_adam_groups(const AdamGroups& G, cudaStream_t st) {
+    const int64_t total4 = G.prefix4[G.n_groups];
+    if (total4 == 0) return LFS_OK;
+    adam_groups_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(G);
+    return check_launch("adam_groups");
+}
+
+int launch_sh_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks, float* colors, cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    sh_fwd_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, K, degree, dirs, coeffs, masks, colors);
+    return check_launch("sh_fwd");
+}
+int launch_sh_bwd(int n, int K, int degree, const float* dirs, const uint8_t* masks, const float* v_colors, float* v_coeffs, cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    sh_bwd_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, K, degree, dirs, masks, v_colors, v_coeffs);
+    return check_launch("sh_bwd");
+}
+int launch_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,
+                      float* new_opacities, float* new_scales, cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    relocation_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, opacities, scales, ratios, binoms, n_max, new_opacities, new_scales);
+    return check_launch("relocation");
+}
+int launch_add_noise(int n, const float* raw_opacities, const float* raw_scales, const float* raw_quats, const float* noise,
+                     float* means, float lr, cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    add_noise_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, raw_opacities, raw_scales, raw_quats, noise, means, lr);
+    return check_launch("add_noise");
+}
+int launch_quats_to_rotmats(int n, const float* quats, float* rotmats, cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    quats_to_rotmats_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, quats, rotmats);
+    return check_launch("quats_to_rotmats");
+}
+
+int launch_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity, int64_t* dead_indices,
+                         int64_t* alive_indices, float* alive_opacities, int32_t* counts_dev, int32_t* flags, int32_t* offs,
+                         int32_t* total_dev, const SortScratch& s, cudaStream_t st) {
+    if (N == 0) { cudaMemsetAsync(counts_dev, 0, 2 * sizeof(int32_t), st); return LFS_OK; }
+    mcmc_flags_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, opacity_raw, rotation_raw, min_opacity, flags);
+    const int rc = exclusive_scan_gather(flags, nullptr, N, offs, total_dev, s, st);
+    if (rc != LFS_OK) return rc;
+    mcmc_compact_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, flags, offs, total_dev, opacity_raw, dead_indices, alive_indices,
+                                                          alive_opacities, counts_dev);
+    return check_launch("mcmc_classify");
+}
+
+int launch_mcmc_gather_ratios(int N, int n, const int64_t* sampled, const float* opacity_raw, const float* scaling_raw, int n_max,
+                              int32_t* counts, int32_t* ratios, float* s_opac, float* s_scales, cudaStream_t st) {
+    cudaMemsetAsync(counts, 0, (size_t)N * sizeof(int32_t), st);
+    if (n == 0) return LFS_OK;
+    mcmc_count_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, sampled, counts);
+    mcmc_gather_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, sampled, counts, opacity_raw, scaling_raw, n_max, ratios, s_opac, s_scales);
+    return check_launch("mcmc_gather_ratios");
+}
+
+int launch_mcmc_apply(int N, int K, int n, const int64_t* sampled, const int64_t* dst_indices, const float* new_opac,
+                      const float* new_scales, float min_opacity, const lfs_splats& p, const lfs_splats* m, const lfs_splats* v,
+                      cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    mcmc_writeback_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, sampled, new_opac, new_scales, min_opacity, p.opacity_raw, p.scaling_raw);
+    RowTable T;
+    float* pp[6] = {p.means, p.sh0, p.shN, p.scaling_raw, p.rotation_raw, p.opacity_raw};
+    const int w[6] = {3, 3, (K - 1) * 3, 3, 4, 1};
+    T.prefix[0] = 0;
+    for (int k = 0; k < 6; ++k) {
+        T.p[k] = pp[k];
+        T.width[k] = w[k];
+        T.prefix[k + 1] = T.prefix[k] + w[k];
+        T.m[k] = nullptr; T.v[k] = nullptr;
+    }
+    if (m) { float* a[6] = {m->means, m->sh0, m->shN, m->scaling_raw, m->rotation_raw, m->opacity_raw}; for (int k = 0; k < 6; ++k) T.m[k] = a[k]; }
+    if (v) { float* a[6] = {v->means, v->sh0, v->shN, v->scaling_raw, v->rotation_raw, v->opacity_raw}; for (int k = 0; k < 6; ++k) T.v[k] = a[k]; }
+    const int64_t total = (int64_t)n * T.prefix[6];
+    mcmc_copy_rows_kernel<<<grid_for(total, 256), 256, 0, st>>>(n, (int64_t)N, sampled, dst_indices, T, dst_indices ? 0 : 1);
+    return check_launch("mcmc_apply");
+}
+
+}  // namespace lfs

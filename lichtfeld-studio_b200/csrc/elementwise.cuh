@@ -1,0 +1,38 @@
+// Launchers of the streaming kernels (elementwise.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace lfs {
+
+struct AdamGroup {
+    float* p; float* m; float* v; const float* g;
+    int64_t n;        // elements in this group (already restricted to the row range)
+    float step_size;  // lr * bias_correction1_rcp
+    int aligned;      // all four pointers 16-byte aligned
+};
+struct AdamGroups {
+    AdamGroup g[6];
+    int64_t prefix4[7];  // prefix sums of ceil(n / 4)
+    int n_groups;
+    float beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
+};
+
+int launch_adam_groups(const AdamGroups& G, cudaStream_t st);
+int launch_sh_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks, float* colors, cudaStream_t st);
+int launch_sh_bwd(int n, int K, int degree, const float* dirs, const uint8_t* masks, const float* v_colors, float* v_coeffs, cudaStream_t st);
+int launch_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,
+                      float* new_opacities, float* new_scales, cudaStream_t st);
+int launch_add_noise(int n, const float* raw_opacities, const float* raw_scales, const float* raw_quats, const float* noise,
+                     float* means, float lr, cudaStream_t st);
+int launch_quats_to_rotmats(int n, const float* quats, float* rotmats, cudaStream_t st);
+int launch_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity, int64_t* dead_indices,
+                         int64_t* alive_indices, float* alive_opacities, int32_t* counts_dev, int32_t* flags, int32_t* offs,
+                         int32_t* total_dev, const SortScratch& s, cudaStream_t st);
+int launch_mcmc_gather_ratios(int N, int n, const int64_t* sampled, const float* opacity_raw, const float* scaling_raw, int n_max,
+                              int32_t* counts, int32_t* ratios, float* s_opac, float* s_scales, cudaStream_t st);
+int launch_mcmc_apply(int N, int K, int n, const int64_t* sampled, const int64_t* dst_indices, const float* new_opac,
+                      const float* new_scales, float min_opacity, const lfs_splats& p, const lfs_splats* m, const lfs_splats* v,
+                      cudaStream_t st);
+
+}  // namespace lfs

@@ -1,0 +1,237 @@
+// Device math shared by the kernels: quaternion / pose helpers, camera models, SH basis.
+// The projection translation unit is compiled with --fmad=false so that these functions give
+// bit-identical results to a plain IEEE float32 evaluation in the same operation order; the
+// rasterizer units use the default contraction.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <float.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace lfs {
+
+struct f3 { float x, y, z; };
+
+__device__ __forceinline__ f3 operator+(f3 a, f3 b) { return {a.x + b.x, a.y + b.y, a.z + b.z}; }
+__device__ __forceinline__ f3 operator-(f3 a, f3 b) { return {a.x - b.x, a.y - b.y, a.z - b.z}; }
+__device__ __forceinline__ f3 operator*(f3 a, float s) { return {a.x * s, a.y * s, a.z * s}; }
+__device__ __forceinline__ f3 operator*(float s, f3 a) { return {a.x * s, a.y * s, a.z * s}; }
+__device__ __forceinline__ float dot3(f3 a, f3 b) { return a.x * b.x + a.y * b.y + a.z * b.z; }
+__device__ __forceinline__ f3 cross3(f3 a, f3 b) {
+    return {a.y * b.z - b.y * a.z, a.z * b.x - b.z * a.x, a.x * b.y - b.x * a.y};
+}
+
+// Rotation of v by the quaternion (w; x,y,z): v + 2 (w (q x v) + q x (q x v)).
+__device__ __forceinline__ f3 quat_rotate(float qw, float qx, float qy, float qz, f3 v) {
+    const f3 qv{qx, qy, qz};
+    const f3 uv = cross3(qv, v);
+    const f3 uuv = cross3(qv, uv);
+    return v + ((uv * qw) + uuv) * 2.0f;
+}
+
+// Rotation matrix (row-major m[r*3+c]) of a quaternion assumed to be unit length.
+__device__ __forceinline__ void quat_to_mat_unit(float w, float x, float y, float z, float* m) {
+    const float qxx = x * x, qyy = y * y, qzz = z * z;
+    const float qxz = x * z, qxy = x * y, qyz = y * z;
+    const float qwx = w * x, qwy = w * y, qwz = w * z;
+    m[0] = 1.0f - 2.0f * (qyy + qzz);
+    m[3] = 2.0f * (qxy + qwz);
+    m[6] = 2.0f * (qxz - qwy);
+    m[1] = 2.0f * (qxy - qwz);
+    m[4] = 1.0f - 2.0f * (qxx + qzz);
+    m[7] = 2.0f * (qyz + qwx);
+    m[2] = 2.0f * (qxz + qwy);
+    m[5] = 2.0f * (qyz - qwx);
+    m[8] = 1.0f - 2.0f * (qxx + qyy);
+}
+
+// Rotation matrix of a quaternion that is re-normalised first with an approximate reciprocal
+// square root (the rasterizer's convention). Also returns the normalised components.
+__device__ __forceinline__ void quat_to_rotmat_renorm(float w, float x, float y, float z, float* m,
+                                                      float& inv_norm, float* qn) {
+    inv_norm = rsqrtf(x * x + y * y + z * z + w * w);
+    x *= inv_norm; y *= inv_norm; z *= inv_norm; w *= inv_norm;
+    qn[0] = w; qn[1] = x; qn[2] = y; qn[3] = z;
+    const float x2 = x * x, y2 = y * y, z2 = z * z;
+    const float xy = x * y, xz = x * z, yz = y * z;
+    const float wx = w * x, wy = w * y, wz = w * z;
+    m[0] = 1.f - 2.f * (y2 + z2); m[1] = 2.f * (xy - wz);       m[2] = 2.f * (xz + wy);
+    m[3] = 2.f * (xy + wz);       m[4] = 1.f - 2.f * (x2 + z2); m[5] = 2.f * (yz - wx);
+    m[6] = 2.f * (xz - wy);       m[7] = 2.f * (yz + wx);       m[8] = 1.f - 2.f * (x2 + y2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Camera models (global shutter). Pinhole without distortion and the OpenCV fisheye model.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool in_bounds_margin(float px, float py, const CamDev& c, float margin) {
+    const float mx = (float)c.W * margin, my = (float)c.H * margin;
+    bool valid = true;
+    valid &= (-mx) <= px && px < ((float)c.W + mx);
+    valid &= (-my) <= py && py < ((float)c.H + my);
+    return valid;
+}
+
+__device__ __forceinline__ float stable_norm2(float x, float y) {
+    const float ax = fabsf(x), ay = fabsf(y);
+    const float mn = fminf(ax, ay), mx = fmaxf(ax, ay);
+    if (mx <= 0.f) return 0.f;
+    const float r = mn / mx;
+    return mx * sqrtf(1.f + r * r);
+}
+
+__device__ __forceinline__ float fisheye_poly_odd(const float* k, float x) {
+    const float x2 = x * x;
+    float y = 0.f;
+    y = x2 * y + k[3];
+    y = x2 * y + k[2];
+    y = x2 * y + k[1];
+    y = x2 * y + k[0];
+    y = x2 * y + 1.f;
+    return x * y;
+}
+__device__ __forceinline__ float fisheye_dpoly_even(const float* k, float x) {
+    const float x2 = x * x;
+    float y = 0.f;
+    y = x2 * y + 9 * k[3];
+    y = x2 * y + 7 * k[2];
+    y = x2 * y + 5 * k[1];
+    y = x2 * y + 3 * k[0];
+    y = x2 * y + 1.f;
+    return y;
+}
+
+// Camera-space point -> image point. Returns validity (inside the image with margin, in front
+// of the camera, inside the fisheye cone). atan2 is evaluated in double and rounded so that a
+// host evaluation of the same expression gives the same float.
+template <int MODEL>
+__device__ __forceinline__ bool cam_point_to_image(const CamDev& c, f3 p, float margin, float& ox, float& oy) {
+    ox = 0.f; oy = 0.f;
+    if (p.z <= 0.f) return false;
+    if (MODEL == LFS_PINHOLE) {
+        ox = (p.x / p.z) * c.fx + c.cx;
+        oy = (p.y / p.z) * c.fy + c.cy;
+        return in_bounds_margin(ox, oy, c, margin);
+    } else {
+        float n = stable_norm2(p.x, p.y);
+        if (n <= 0.f) n = FLT_EPSILON;
+        const float theta_full = (float)atan2((double)n, (double)p.z);
+        const float theta = theta_full < c.max_angle ? theta_full : c.max_angle;
+        const float delta = fisheye_poly_odd(c.k, theta) / n;
+        if (delta <= 0.f) return false;
+        ox = c.fx * delta * p.x + c.cx;
+        oy = c.fy * delta * p.y + c.cy;
+        bool valid = in_bounds_margin(ox, oy, c, margin);
+        valid &= theta <= c.max_angle;
+        return valid;
+    }
+}
+
+// Pixel centre -> unit camera ray. Fisheye inverts the forward polynomial with up to 20 Newton steps.
+template <int MODEL>
+__device__ __forceinline__ bool image_to_cam_ray(const CamDev& c, float px, float py, f3& ray) {
+    const float ux = (px - c.cx) / c.fx;
+    const float uy = (py - c.cy) / c.fy;
+    if (MODEL == LFS_PINHOLE) {
+        const float len = sqrtf(ux * ux + uy * uy + 1.f);
+        ray = {ux / len, uy / len, 1.f / len};
+        return true;
+    } else {
+        const float delta = sqrtf(ux * ux + uy * uy);
+        bool converged = false;
+        float x = delta * c.approx_b1 + 0.f;
+        for (int j = 0; j < 20; ++j) {
+            const float dfdx = fisheye_dpoly_even(c.k, x);
+            const float residual = fisheye_poly_odd(c.k, x) - delta;
+            const float dx = residual / dfdx;
+            x -= dx;
+            if (fabsf(dx) < 1e-6f) { converged = true; break; }
+        }
+        const float theta = x;
+        if (theta < 0.f || theta >= c.max_angle || !converged) { ray = {0.f, 0.f, 1.f}; return false; }
+        if (delta >= 1e-6f) {
+            const float sf = (float)sin((double)theta) / delta;
+            ray = {sf * ux, sf * uy, (float)cos((double)theta)};
+            return true;
+        }
+        ray = {0.f, 0.f, 1.f};
+        return true;
+    }
+}
+
+// World-space ray direction of a pixel centre.
+template <int MODEL>
+__device__ __forceinline__ bool pixel_world_dir(const CamDev& c, float px, float py, f3& d) {
+    f3 cr;
+    const bool valid = image_to_cam_ray<MODEL>(c, px, py, cr);
+    d.x = c.Rinv[0] * cr.x + c.Rinv[1] * cr.y + c.Rinv[2] * cr.z;
+    d.y = c.Rinv[3] * cr.x + c.Rinv[4] * cr.y + c.Rinv[5] * cr.z;
+    d.z = c.Rinv[6] * cr.x + c.Rinv[7] * cr.y + c.Rinv[8] * cr.z;
+    return valid;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Real SH basis up to degree 4 at a direction that is normalised here (Sloan's recurrences).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void sh_basis(int degree, float dx, float dy, float dz, float* B) {
+    B[0] = 0.2820947917738781f;
+    if (degree < 1) return;
+    const float inorm = rsqrtf(dx * dx + dy * dy + dz * dz);
+    const float x = dx * inorm, y = dy * inorm, z = dz * inorm;
+    B[1] = -0.48860251190292f * y;
+    B[2] = 0.48860251190292f * z;
+    B[3] = -0.48860251190292f * x;
+    if (degree < 2) return;
+    const float z2 = z * z;
+    const float fTmp0B = -1.092548430592079f * z;
+    const float fC1 = x * x - y * y;
+    const float fS1 = 2.f * x * y;
+    B[6] = (0.9461746957575601f * z2 - 0.3153915652525201f);
+    B[7] = fTmp0B * x;
+    B[5] = fTmp0B * y;
+    B[8] = 0.5462742152960395f * fC1;
+    B[4] = 0.5462742152960395f * fS1;
+    if (degree < 3) return;
+    const float fTmp0C = -2.285228997322329f * z2 + 0.4570457994644658f;
+    const float fTmp1B = 1.445305721320277f * z;
+    const float fC2 = x * fC1 - y * fS1;
+    const float fS2 = x * fS1 + y * fC1;
+    B[12] = z * (1.865881662950577f * z2 - 1.119528997770346f);
+    B[13] = fTmp0C * x;
+    B[11] = fTmp0C * y;
+    B[14] = fTmp1B * fC1;
+    B[10] = fTmp1B * fS1;
+    B[15] = -0.5900435899266435f * fC2;
+    B[9] = -0.5900435899266435f * fS2;
+    if (degree < 4) return;
+    const float fTmp0D = z * (-4.683325804901025f * z2 + 2.007139630671868f);
+    const float fTmp1C = 3.31161143515146f * z2 - 0.47308734787878f;
+    const float fTmp2B = -1.770130769779931f * z;
+    const float fC3 = x * fC2 - y * fS2;
+    const float fS3 = x * fS2 + y * fC2;
+    B[20] = (1.984313483298443f * z * B[12] - 1.006230589874905f * B[6]);
+    B[21] = fTmp0D * x;
+    B[19] = fTmp0D * y;
+    B[22] = fTmp1C * fC1;
+    B[18] = fTmp1C * fS1;
+    B[23] = fTmp2B * fC2;
+    B[17] = fTmp2B * fS2;
+    B[24] = 0.6258357354491763f * fC3;
+    B[16] = 0.6258357354491763f * fS3;
+}
+
+// Tile rectangle covered by a projected Gaussian: [x0,x1) x [y0,y1) in tile units. The float ->
+// unsigned conversion saturates (negative -> 0), which is what clips boxes that start left of /
+// above the image.
+__device__ __forceinline__ void tile_rect(float mx, float my, int rx, int ry, float tile_size, uint32_t tw,
+                                          uint32_t th, uint32_t& x0, uint32_t& y0, uint32_t& x1, uint32_t& y1) {
+    const float trx = (float)rx / tile_size, try_ = (float)ry / tile_size;
+    const float tx = mx / tile_size, ty = my / tile_size;
+    x0 = min((uint32_t)floorf(tx - trx), tw);
+    y0 = min((uint32_t)floorf(ty - try_), th);
+    x1 = min((uint32_t)ceilf(tx + trx), tw);
+    y1 = min((uint32_t)ceilf(ty + try_), th);
+}
+
+}  // namespace lfs

@@ -1,0 +1,250 @@
+// Separable 11x11 Gaussian-window SSIM (forward with derivative maps, backward) and the fused
+// photometric loss 0.8 L1 + 0.2 (1 - SSIM_valid) with its gradient w.r.t. the unclamped HWC render.
+//
+// Replaces src/training/kernels/ssim.cu:64 (K9) and :284 (K10), the crop / pad / mean glue of
+// include/kernels/fused_ssim.cuh:59-67, :85-96, :117-122, torch::l1_loss of
+// src/training/trainer.cpp:126 and the clamp + permute of src/training/rasterization/rasterizer.cpp:205.
+// HBM-bound stencil work: each CTA stages a 26x26 halo tile in shared memory and runs the 11-tap
+// horizontal and vertical passes from there.
+#include "common.cuh"
+#include "loss.cuh"
+
+namespace lfs {
+
+namespace {
+
+constexpr int kB = 16;           // tile edge
+constexpr int kHalo = 5;
+constexpr int kS = kB + 2 * kHalo;  // 26
+
+__constant__ float cTaps[11] = {
+    0.001028380123898387f, 0.0075987582094967365f, 0.036000773310661316f, 0.10936068743467331f,
+    0.21300552785396576f,  0.26601171493530273f,   0.21300552785396576f,  0.10936068743467331f,
+    0.036000773310661316f, 0.0075987582094967365f, 0.001028380123898387f};
+
+// FUSED: img1 is the unclamped HWC render (clamped to [0,1] on load); otherwise plain CHW.
+template <bool FUSED>
+__device__ __forceinline__ float load_img1(const float* img1, int c, int y, int x, int H, int W) {
+    if (x < 0 || x >= W || y < 0 || y >= H) return 0.f;
+    if (FUSED) return fminf(1.f, fmaxf(0.f, img1[((size_t)y * W + x) * 3 + c]));
+    return img1[(size_t)c * H * W + (size_t)y * W + x];
+}
+__device__ __forceinline__ float load_chw(const float* img, int c, int y, int x, int H, int W) {
+    if (x < 0 || x >= W || y < 0 || y >= H) return 0.f;
+    return img[(size_t)c * H * W + (size_t)y * W + x];
+}
+
+// Forward. Plain mode writes ssim_map and the three derivative maps. Fused mode writes the
+// derivative maps already multiplied by dL/dmap (map_grad inside the valid crop, 0 outside) and
+// accumulates sum(ssim over the crop) and sum(|img1 - img2|) into sums[0], sums[1].
+template <bool FUSED>
+__global__ void __launch_bounds__(kB* kB) ssim_fwd_kernel(int CH, int H, int W, float C1, float C2,
+                                                          const float* __restrict__ img1, const float* __restrict__ img2,
+                                                          float* __restrict__ ssim_map, float* __restrict__ dm_dmu1,
+                                                          float* __restrict__ dm_dsigma1_sq, float* __restrict__ dm_dsigma12,
+                                                          float map_grad, int crop, double* __restrict__ sums) {
+    __shared__ float sX[kS][kS + 1], sY[kS][kS + 1];
+    __shared__ float sH[kS][kB][5];
+    __shared__ float red[2][kB * kB / 32];
+    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kB + tx;
+    const int x = blockIdx.x * kB + tx, y = blockIdx.y * kB + ty;
+    float ssim_acc = 0.f, l1_acc = 0.f;
+    for (int c = 0; c < CH; ++c) {
+        for (int q = tid; q < kS * kS; q += kB * kB) {
+            const int ly = q / kS, lx = q % kS;
+            const int gy = blockIdx.y * kB + ly - kHalo, gx = blockIdx.x * kB + lx - kHalo;
+            sX[ly][lx] = load_img1<FUSED>(img1, c, gy, gx, H, W);
+            sY[ly][lx] = load_chw(img2, c, gy, gx, H, W);
+        }
+        __syncthreads();
+        for (int ly = ty; ly < kS; ly += kB) {
+            const int lx = tx + kHalo;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, a4 = 0.f;
+#pragma unroll
+            for (int d = 1; d <= kHalo; ++d) {
+                const float w = cTaps[kHalo - d];
+                const float Xl = sX[ly][lx - d], Yl = sY[ly][lx - d], Xr = sX[ly][lx + d], Yr = sY[ly][lx + d];
+                a0 += (Xl + Xr) * w;
+                a1 += ((Xl * Xl) + (Xr * Xr)) * w;
+                a2 += (Yl + Yr) * w;
+                a3 += ((Yl * Yl) + (Yr * Yr)) * w;
+                a4 += ((Xl * Yl) + (Xr * Yr)) * w;
+            }
+            const float cX = sX[ly][lx], cY = sY[ly][lx], wc = cTaps[kHalo];
+            a0 += cX * wc; a1 += (cX * cX) * wc; a2 += cY * wc; a3 += (cY * cY) * wc; a4 += (cX * cY) * wc;
+            sH[ly][tx][0] = a0; sH[ly][tx][1] = a1; sH[ly][tx][2] = a2; sH[ly][tx][3] = a3; sH[ly][tx][4] = a4;
+        }
+        __syncthreads();
+        {
+            const int ly = ty + kHalo;
+            float o[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int d = 1; d <= kHalo; ++d) {
+                const float w = cTaps[kHalo - d];
+#pragma unroll
+                for (int k = 0; k < 5; ++k) o[k] += (sH[ly - d][tx][k] + sH[ly + d][tx][k]) * w;
+            }
+#pragma unroll
+            for (int k = 0; k < 5; ++k) o[k] += sH[ly][tx][k] * cTaps[kHalo];
+            if (x < W && y < H) {
+                const float mu1 = o[0], mu2 = o[2];
+                const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
+                const float sigma1_sq = o[1] - mu1_sq, sigma2_sq = o[3] - mu2_sq, sigma12 = o[4] - mu1 * mu2;
+                const float A = mu1_sq + mu2_sq + C1, B = sigma1_sq + sigma2_sq + C2;
+                const float C_ = 2.f * mu1 * mu2 + C1, D_ = 2.f * sigma12 + C2;
+                const float val = (C_ * D_) / (A * B);
+                const float g_mu1 = ((mu2 * 2.f * D_) / (A * B) - (mu2 * 2.f * C_) / (A * B) -
+                                     (mu1 * 2.f * C_ * D_) / (A * A * B) + (mu1 * 2.f * C_ * D_) / (A * B * B));
+                const float g_s1 = (-C_ * D_) / (A * B * B);
+                const float g_s12 = (2.f * C_) / (A * B);
+                const size_t gi = (size_t)c * H * W + (size_t)y * W + x;
+                if (FUSED) {
+                    const bool in_crop = !crop || (x >= kHalo && x < W - kHalo && y >= kHalo && y < H - kHalo);
+                    const float chain = in_crop ? map_grad : 0.f;
+                    dm_dmu1[gi] = g_mu1 * chain;
+                    dm_dsigma1_sq[gi] = g_s1 * chain;
+                    dm_dsigma12[gi] = g_s12 * chain;
+                    if (in_crop) ssim_acc += val;
+                    l1_acc += fabsf(sX[ty + kHalo][tx + kHalo] - sY[ty + kHalo][tx + kHalo]);
+                } else {
+                    ssim_map[gi] = val;
+                    if (dm_dmu1) { dm_dmu1[gi] = g_mu1; dm_dsigma1_sq[gi] = g_s1; dm_dsigma12[gi] = g_s12; }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (FUSED) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ssim_acc += __shfl_xor_sync(0xffffffffu, ssim_acc, o);
+            l1_acc += __shfl_xor_sync(0xffffffffu, l1_acc, o);
+        }
+        if ((tid & 31) == 0) { red[0][tid >> 5] = ssim_acc; red[1][tid >> 5] = l1_acc; }
+        __syncthreads();
+        if (tid == 0) {
+            double s = 0.0, l = 0.0;
+            for (int k = 0; k < kB * kB / 32; ++k) { s += red[0][k]; l += red[1][k]; }
+            atomicAdd(&sums[0], s);
+            atomicAdd(&sums[1], l);
+        }
+    }
+}
+
+// Backward. Plain mode: maps are multiplied by dL_dmap on load and dL_dimg1 is CHW. Fused mode: the maps
+// are pre-multiplied, the L1 sign term and the clamp mask are applied and the output is the HWC
+// gradient of the unclamped render, scaled by grad_scale.
+template <bool FUSED>
+__global__ void __launch_bounds__(kB* kB) ssim_bwd_kernel(int CH, int H, int W, const float* __restrict__ img1,
+                                                          const float* __restrict__ img2, const float* __restrict__ dL_dmap,
+                                                          const float* __restrict__ dm_dmu1, const float* __restrict__ dm_dsigma1_sq,
+                                                          const float* __restrict__ dm_dsigma12, float* __restrict__ dL_dimg1,
+                                                          float l1_grad, float grad_scale) {
+    __shared__ float sD[3][kS][kS + 1];
+    __shared__ float sH[kS][kB][3];
+    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kB + tx;
+    const int x = blockIdx.x * kB + tx, y = blockIdx.y * kB + ty;
+    for (int c = 0; c < CH; ++c) {
+        for (int q = tid; q < kS * kS; q += kB * kB) {
+            const int ly = q / kS, lx = q % kS;
+            const int gy = blockIdx.y * kB + ly - kHalo, gx = blockIdx.x * kB + lx - kHalo;
+            const float chain = FUSED ? 1.f : load_chw(dL_dmap, c, gy, gx, H, W);
+            sD[0][ly][lx] = load_chw(dm_dmu1, c, gy, gx, H, W) * chain;
+            sD[1][ly][lx] = load_chw(dm_dsigma1_sq, c, gy, gx, H, W) * chain;
+            sD[2][ly][lx] = load_chw(dm_dsigma12, c, gy, gx, H, W) * chain;
+        }
+        __syncthreads();
+        for (int ly = ty; ly < kS; ly += kB) {
+            const int lx = tx + kHalo;
+            float a[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+            for (int d = 1; d <= kHalo; ++d) {
+                const float w = cTaps[kHalo - d];
+#pragma unroll
+                for (int k = 0; k < 3; ++k) a[k] += (sD[k][ly][lx - d] + sD[k][ly][lx + d]) * w;
+            }
+#pragma unroll
+            for (int k = 0; k < 3; ++k) { a[k] += sD[k][ly][lx] * cTaps[kHalo]; sH[ly][tx][k] = a[k]; }
+        }
+        __syncthreads();
+        if (x < W && y < H) {
+            const int ly = ty + kHalo;
+            float s[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+            for (int d = 1; d <= kHalo; ++d) {
+                const float w = cTaps[kHalo - d];
+#pragma unroll
+                for (int k = 0; k < 3; ++k) s[k] += (sH[ly - d][tx][k] + sH[ly + d][tx][k]) * w;
+            }
+#pragma unroll
+            for (int k = 0; k < 3; ++k) s[k] += sH[ly][tx][k] * cTaps[kHalo];
+            if (FUSED) {
+                const float raw = img1[((size_t)y * W + x) * 3 + c];
+                const float p1 = fminf(1.f, fmaxf(0.f, raw));
+                const float p2 = img2[(size_t)c * H * W + (size_t)y * W + x];
+                float g = s[0] + (2.f * p1) * s[1] + (p2)*s[2];
+                const float diff = p1 - p2;
+                g += l1_grad * (diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f));
+                if (!(raw >= 0.f && raw <= 1.f)) g = 0.f;
+                dL_dimg1[((size_t)y * W + x) * 3 + c] = g * grad_scale;
+            } else {
+                const size_t gi = (size_t)c * H * W + (size_t)y * W + x;
+                const float p1 = img1[gi], p2 = img2[gi];
+                dL_dimg1[gi] = s[0] + (2.f * p1) * s[1] + (p2)*s[2];
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void loss_finalize_kernel(const double* sums, double n_all, double n_valid, float lambda, float* loss) {
+    const float l1 = (float)(sums[1] / n_all);
+    const float ssim = (float)(sums[0] / n_valid);
+    loss[0] = (1.f - lambda) * l1 + lambda * (1.f - ssim);
+    loss[1] = l1;
+    loss[2] = ssim;
+}
+
+}  // namespace
+
+int launch_fusedssim(int CH, int H, int W, float C1, float C2, const float* img1, const float* img2, float* ssim_map,
+                     float* dm1, float* ds1, float* ds12, cudaStream_t st) {
+    if (CH * H * W == 0) return LFS_OK;
+    dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    ssim_fwd_kernel<false><<<grid, block, 0, st>>>(CH, H, W, C1, C2, img1, img2, ssim_map, dm1, ds1, ds12, 0.f, 0, nullptr);
+    return check_launch("fusedssim");
+}
+
+int launch_fusedssim_backward(int CH, int H, int W, const float* img1, const float* img2, const float* dL_dmap,
+                              const float* dm1, const float* ds1, const float* ds12, float* dL_dimg1, cudaStream_t st) {
+    if (CH * H * W == 0) return LFS_OK;
+    dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    ssim_bwd_kernel<false><<<grid, block, 0, st>>>(CH, H, W, img1, img2, dL_dmap, dm1, ds1, ds12, dL_dimg1, 0.f, 1.f);
+    return check_launch("fusedssim_backward");
+}
+
+size_t photometric_workspace_bytes(int H, int W) { return 256 + (size_t)3 * 3 * H * W * sizeof(float); }
+
+int launch_photometric_loss(int H, int W, float lambda, float grad_scale, const float* render_hwc, const float* target_chw,
+                            float* v_render_hwc, float* loss_dev, void* workspace, cudaStream_t st) {
+    double* sums = reinterpret_cast<double*>(workspace);
+    float* maps = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+    const size_t plane = (size_t)3 * H * W;
+    float *d1 = maps, *d2 = maps + plane, *d3 = maps + 2 * plane;
+    const int crop = (H > 10 && W > 10) ? 1 : 0;
+    const double n_all = 3.0 * H * W;
+    const double n_valid = crop ? 3.0 * (H - 10) * (W - 10) : n_all;
+    const float map_grad = (float)(-(double)lambda / n_valid);
+    const float l1_grad = (float)((1.0 - (double)lambda) / n_all);
+    cudaMemsetAsync(sums, 0, 2 * sizeof(double), st);
+    dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    ssim_fwd_kernel<true><<<grid, block, 0, st>>>(3, H, W, (float)(0.01 * 0.01), (float)(0.03 * 0.03), render_hwc,
+                                                  target_chw, nullptr, d1, d2, d3, map_grad, crop, sums);
+    if (v_render_hwc)
+        ssim_bwd_kernel<true><<<grid, block, 0, st>>>(3, H, W, render_hwc, target_chw, nullptr, d1, d2, d3, v_render_hwc,
+                                                      l1_grad, grad_scale);
+    loss_finalize_kernel<<<1, 1, 0, st>>>(sums, n_all, n_valid, lambda, loss_dev);
+    return check_launch("photometric_loss");
+}
+
+}  // namespace lfs

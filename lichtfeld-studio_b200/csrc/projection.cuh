@@ -1,0 +1,39 @@
+// Launchers of the per-Gaussian stage (projection.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace lfs {
+
+struct ProjParams {
+    float eps2d, near_plane, far_plane, radius_clip;
+    float alpha, beta, kappa, margin;
+    bool require_all;
+};
+
+inline ProjParams make_proj_params(float eps2d, float near_plane, float far_plane, float radius_clip,
+                                   const lfs_ut_params& ut) {
+    ProjParams p;
+    p.eps2d = eps2d; p.near_plane = near_plane; p.far_plane = far_plane; p.radius_clip = radius_clip;
+    p.alpha = ut.alpha; p.beta = ut.beta; p.kappa = ut.kappa; p.margin = ut.in_image_margin_factor;
+    p.require_all = ut.require_all_sigma_points_valid != 0;
+    return p;
+}
+
+int launch_projection_ut(int C, int N, const float* means, const float* quats, const float* scales,
+                         const float* opacities, const float* viewmats, const float* Ks, const float* radial, int W, int H,
+                         const ProjParams& pp, int model, int32_t* radii,
+                         float* means2d, float* depths, float* conics, float* compensations, cudaStream_t st);
+
+int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
+                        const float* opacities, const CamDev* cam, float4* records, float4* accum, cudaStream_t st);
+
+int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
+                        int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
+                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, float4* accum,
+                        int32_t* n_visible, cudaStream_t st);
+
+int launch_tile_count(int64_t total, const float* means2d, const int32_t* radii, int tile_size, int tw, int th,
+                      int32_t* tiles, cudaStream_t st);
+
+}  // namespace lfs

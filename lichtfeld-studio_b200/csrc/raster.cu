@@ -1,0 +1,503 @@
+// Alpha-blend rasterizer by ray / Gaussian distance: forward, backward and the per-Gaussian
+// gradient epilogues.
+//
+// Replaces gsplat/RasterizeToPixelsFromWorld3DGSFwd.cu:20 (K7), gsplat/RasterizeToPixelsFromWorld3DGSBwd.cu:17
+// (K8) with the VJPs of gsplat/Utils.cuh:104-194, gsplat/SphericalHarmonicsCUDA.cu:445 (K3) and the
+// activation backward that autograd performs for src/core/splat_data.cpp:267-286.
+//
+// Design (FP32-pipe bound, no tensor cores: the largest contraction is 3x3):
+//  * one CTA per 16x16 tile, one thread per pixel, warps cover 8x4 pixel patches;
+//  * the tile's depth-sorted Gaussians are staged in shared memory in batches of 256 packed
+//    64-byte records (M = S^-1 R^T, gro = M (o - mu), colour, opacity) built once per Gaussian,
+//    so no quaternion -> matrix work is repeated per tile or per pixel;
+//  * per pair the response is -0.5 |u x gro|^2 / |u|^2 with u = M d (same value as the normalised
+//    cross-product form), preceded by an exp-free conservative rejection test;
+//  * backward: every (warp, Gaussian) contribution is 16 numbers that are LINEAR in the per-pixel
+//    terms (sum v_u (x) d, sum v_gro, v_rgb, v_opacity). They are summed with a 16-shuffle halving
+//    butterfly, combined across the 8 warps in shared memory, and leave the CTA as four float4
+//    reductions per (tile, Gaussian). The nonlinear quaternion / scale VJP runs once per Gaussian in
+//    the epilogue instead of once per pixel pair.
+#include "gsmath.cuh"
+#include "raster.cuh"
+
+namespace lfs {
+
+namespace {
+
+constexpr int kBlock = 256;
+constexpr float kAlphaMin = 1.f / 255.f;
+constexpr float kRejectMargin = 0.02f;  // slack (in units of the exponent) of the exp-free rejection test
+
+__device__ __forceinline__ void pixel_of_thread(int tile, int tw, int& i, int& j) {
+    // warps tile the 16x16 block as 2 x 4 patches of 8 x 4 pixels
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lx = (warp & 1) * 8 + (lane & 7);
+    const int ly = (warp >> 1) * 4 + (lane >> 3);
+    i = (tile / tw) * 16 + ly;
+    j = (tile % tw) * 16 + lx;
+}
+
+__device__ __forceinline__ int32_t load_count(const int32_t* n_dev, int64_t n_host) {
+    return n_dev ? *n_dev : (int32_t)n_host;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int MODEL>
+__global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
+    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint32_t* __restrict__ flatten_ids,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
+    const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
+    float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids) {
+    __shared__ float4 srec[kBlock * 4];
+    __shared__ float sthr[kBlock];
+
+    if (overflow && *overflow) return;
+    const int tile = blockIdx.x;
+    int i, j;
+    pixel_of_thread(tile, tw, i, j);
+    const bool inside = (i < H && j < W);
+    const CamDev& cam = cams[0];
+    f3 d;
+    const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
+    bool done = !inside || !ray_ok;
+
+    const int32_t n_isects = load_count(n_isects_dev, n_isects_host);
+    const int32_t range_start = tile_offsets[tile];
+    const int32_t range_end = (tile == n_tiles - 1) ? n_isects : tile_offsets[tile + 1];
+
+    float T = 1.0f;
+    uint32_t cur_idx = 0;
+    float pr = 0.f, pg = 0.f, pb = 0.f;
+
+    for (int32_t batch_start = range_start; batch_start < range_end; batch_start += kBlock) {
+        if (__syncthreads_count(done) >= kBlock) break;
+        const int32_t batch_size = min(kBlock, range_end - batch_start);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int q = k * kBlock + threadIdx.x;
+            const int e = q >> 2, part = q & 3;
+            if (e < batch_size) {
+                const uint32_t g = flatten_ids[batch_start + e];
+                const float4 v = records[(size_t)g * 4 + part];
+                srec[q] = v;
+                // exponent below which opacity * exp(p) < 1/255 for certain
+                if (part == 3) sthr[e] = -__logf(255.0f * v.w) - kRejectMargin;
+            }
+        }
+        __syncthreads();
+        if (!__all_sync(0xffffffffu, done)) {
+            for (int t = 0; t < batch_size && !done; ++t) {
+                const float4 r0 = srec[t * 4 + 0], r1 = srec[t * 4 + 1], r2 = srec[t * 4 + 2];
+                const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
+                const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
+                const float uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
+                const float cx = uy * r2.w - r1.w * uz;
+                const float cy = uz * r0.w - r2.w * ux;
+                const float cz = ux * r1.w - r0.w * uy;
+                const float cc = cx * cx + cy * cy + cz * cz;
+                const float uu = ux * ux + uy * uy + uz * uz;
+                // power = -0.5 cc / uu ; reject when power < thr  <=>  cc > -2 thr uu
+                if (cc > -2.0f * sthr[t] * uu) continue;
+                const float4 r3 = srec[t * 4 + 3];
+                const float power = -0.5f * __fdividef(cc, fmaxf(uu, 1e-37f));
+                const float alpha = fminf(0.999f, r3.w * __expf(power));
+                if (alpha < kAlphaMin) continue;
+                const float next_T = T * (1.0f - alpha);
+                if (next_T <= 1e-4f) { done = true; break; }
+                const float vis = alpha * T;
+                pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
+                cur_idx = (uint32_t)(batch_start + t);
+                T = next_T;
+            }
+        }
+    }
+    if (inside) {
+        const int pid = i * W + j;
+        alphas[pid] = 1.0f - T;
+        if (background) { pr += T * background[0]; pg += T * background[1]; pb += T * background[2]; }
+        render[pid * 3 + 0] = pr;
+        render[pid * 3 + 1] = pg;
+        render[pid * 3 + 2] = pb;
+        last_ids[pid] = (int32_t)cur_idx;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 16 values per lane -> per-value sums over the warp, value k left in lanes 2k and 2k+1.
+__device__ __forceinline__ float warp_reduce16(float (&v)[16]) {
+    const int lane = threadIdx.x & 31;
+    {
+        const bool hi = lane & 16;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float send = hi ? v[k] : v[k + 8];
+            const float keep = hi ? v[k + 8] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+    }
+    {
+        const bool hi = lane & 8;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float send = hi ? v[k] : v[k + 4];
+            const float keep = hi ? v[k + 4] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+    }
+    {
+        const bool hi = lane & 4;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float send = hi ? v[k] : v[k + 2];
+            const float keep = hi ? v[k + 2] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+        }
+    }
+    {
+        const bool hi = lane & 2;
+        const float send = hi ? v[0] : v[1];
+        const float keep = hi ? v[1] : v[0];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+template <int MODEL>
+__global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
+    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint32_t* __restrict__ flatten_ids,
+    const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
+    const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
+    const float* __restrict__ render_alphas, const int32_t* __restrict__ last_ids,
+    const float* __restrict__ v_render, const float* __restrict__ v_alphas, float* __restrict__ accum) {
+    __shared__ float4 srec[kBlock * 4];
+    __shared__ float sthr[kBlock];
+    __shared__ uint32_t sid[kBlock];
+    __shared__ __align__(16) float sacc[kBlock * 16];
+    __shared__ int stouched[kBlock];
+
+    if (overflow && *overflow) return;
+    const int tile = blockIdx.x;
+    int i, j;
+    pixel_of_thread(tile, tw, i, j);
+    const bool inside = (i < H && j < W);
+    const CamDev& cam = cams[0];
+    f3 d;
+    const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
+    const bool active = inside && ray_ok;
+    const int pid = min(i * W + j, W * H - 1);
+
+    const int32_t n_isects = load_count(n_isects_dev, n_isects_host);
+    const int32_t range_start = tile_offsets[tile];
+    const int32_t range_end = (tile == n_tiles - 1) ? n_isects : tile_offsets[tile + 1];
+
+    const float T_final = 1.0f - render_alphas[pid];
+    float T = T_final;
+    float bufr = 0.f, bufg = 0.f, bufb = 0.f;
+    const int32_t bin_final = active ? last_ids[pid] : 0;
+    const float vcr = v_render[pid * 3 + 0], vcg = v_render[pid * 3 + 1], vcb = v_render[pid * 3 + 2];
+    const float v_a = v_alphas ? v_alphas[pid] : 0.f;
+    float bg_dot = 0.f;
+    if (background) bg_dot = background[0] * vcr + background[1] * vcg + background[2] * vcb;
+    const int32_t warp_bin_final = __reduce_max_sync(0xffffffffu, bin_final);
+    const int lane = threadIdx.x & 31;
+
+#pragma unroll
+    for (int k = 0; k < 16; ++k) sacc[threadIdx.x * 16 + k] = 0.f;
+    stouched[threadIdx.x] = 0;
+
+    for (int32_t batch_end = range_end - 1; batch_end >= range_start; batch_end -= kBlock) {
+        __syncthreads();
+        const int32_t batch_size = min(kBlock, batch_end + 1 - range_start);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int q = k * kBlock + threadIdx.x;
+            const int e = q >> 2, part = q & 3;
+            if (e < batch_size) {
+                const uint32_t g = flatten_ids[batch_end - e];
+                const float4 v = records[(size_t)g * 4 + part];
+                srec[q] = v;
+                if (part == 3) { sthr[e] = -__logf(255.0f * v.w) - kRejectMargin; sid[e] = g; }
+            }
+        }
+        __syncthreads();
+        for (int t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
+            bool valid = active && (batch_end - t <= bin_final);
+            float ux, uy, uz, cx, cy, cz, uu;
+            float4 r0, r1, r2;
+            if (valid) {
+                r0 = srec[t * 4 + 0]; r1 = srec[t * 4 + 1]; r2 = srec[t * 4 + 2];
+                ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
+                uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
+                uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
+                cx = uy * r2.w - r1.w * uz;
+                cy = uz * r0.w - r2.w * ux;
+                cz = ux * r1.w - r0.w * uy;
+                const float cc = cx * cx + cy * cy + cz * cz;
+                uu = ux * ux + uy * uy + uz * uz;
+                if (cc > -2.0f * sthr[t] * uu) valid = false;
+            }
+            float alpha = 0.f, vis = 0.f, inv = 0.f;
+            float4 r3 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) {
+                r3 = srec[t * 4 + 3];
+                inv = rsqrtf(fmaxf(uu, 1e-37f));
+                cx *= inv; cy *= inv; cz *= inv;  // cross(normalised u, gro)
+                const float power = -0.5f * (cx * cx + cy * cy + cz * cz);
+                vis = __expf(power);
+                alpha = fminf(0.999f, r3.w * vis);
+                if (alpha < kAlphaMin) valid = false;
+            }
+            if (!__any_sync(0xffffffffu, valid)) continue;
+            float v[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) v[k] = 0.f;
+            if (valid) {
+                const float ra = 1.0f / (1.0f - alpha);
+                T *= ra;
+                const float fac = alpha * T;
+                v[12] = fac * vcr; v[13] = fac * vcg; v[14] = fac * vcb;
+                float v_alpha = (r3.x * T - bufr * ra) * vcr + (r3.y * T - bufg * ra) * vcg + (r3.z * T - bufb * ra) * vcb;
+                v_alpha += T_final * ra * v_a;
+                v_alpha += -T_final * ra * bg_dot;
+                if (r3.w * vis <= 0.999f) {
+                    const float v_vis = r3.w * v_alpha;
+                    const float s = -vis * v_vis;  // v_c = s * c
+                    const float vcx = s * cx, vcy = s * cy, vcz = s * cz;
+                    const float nx = ux * inv, ny = uy * inv, nz = uz * inv;
+                    const float gx = r0.w, gy = r1.w, gz = r2.w;
+                    // v_n = -(v_c x g) = g x v_c ; v_g = v_c x n
+                    const float vnx = gy * vcz - vcy * gz, vny = gz * vcx - vcz * gx, vnz = gx * vcy - vcx * gy;
+                    const float vgx = vcy * nz - ny * vcz, vgy = vcz * nx - nz * vcx, vgz = vcx * ny - nx * vcy;
+                    // v_u = inv * v_n - inv^3 (v_n . u) u
+                    const float il3 = inv * inv * inv;
+                    const float dd = (vnx * ux + vny * uy + vnz * uz) * il3;
+                    const float vux = inv * vnx - dd * ux, vuy = inv * vny - dd * uy, vuz = inv * vnz - dd * uz;
+                    v[0] = vux * d.x; v[1] = vux * d.y; v[2] = vux * d.z;
+                    v[3] = vuy * d.x; v[4] = vuy * d.y; v[5] = vuy * d.z;
+                    v[6] = vuz * d.x; v[7] = vuz * d.y; v[8] = vuz * d.z;
+                    v[9] = vgx; v[10] = vgy; v[11] = vgz;
+                    v[15] = vis * v_alpha;
+                }
+                bufr += r3.x * fac; bufg += r3.y * fac; bufb += r3.z * fac;
+            }
+            const float total = warp_reduce16(v);
+            if ((lane & 1) == 0) atomicAdd(&sacc[t * 16 + (lane >> 1)], total);
+            if (lane == 0) stouched[t] = 1;
+        }
+        __syncthreads();
+        // flush this batch's sums: four 16-byte reductions per touched Gaussian
+        if (threadIdx.x < batch_size && stouched[threadIdx.x]) {
+            const uint32_t g = sid[threadIdx.x];
+            float4* dst = reinterpret_cast<float4*>(accum) + (size_t)g * 4;
+            float4* src = reinterpret_cast<float4*>(sacc) + threadIdx.x * 4;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                atomicAdd(dst + k, src[k]);
+                src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            stouched[threadIdx.x] = 0;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-Gaussian gradient from the 16 accumulated numbers. Outputs gradients w.r.t. the ACTIVATED
+// mean / quaternion / scale / opacity and the colour.
+// ---------------------------------------------------------------------------------------------
+struct GaussGrad {
+    float v_mean[3], v_quat[4], v_scale[3], v_opac, v_rgb[3];
+};
+
+__device__ __forceinline__ void gaussian_vjp(const CamDev& cam, const float* acc /*16*/, f3 mean, float qw, float qx,
+                                             float qy, float qz, f3 scale, GaussGrad& o) {
+    float R[9], inv_norm, qn[4];
+    quat_to_rotmat_renorm(qw, qx, qy, qz, R, inv_norm, qn);
+    const float is[3] = {1.0f / scale.x, 1.0f / scale.y, 1.0f / scale.z};
+    const float omu[3] = {cam.ro[0] - mean.x, cam.ro[1] - mean.y, cam.ro[2] - mean.z};
+    const float G[3] = {acc[9], acc[10], acc[11]};
+    // v_Mt = A + G (x) (o - mu)
+    float vMt[9];
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+#pragma unroll
+        for (int b = 0; b < 3; ++b) vMt[a * 3 + b] = acc[a * 3 + b] + G[a] * omu[b];
+    // v_(o-mu) = Mt^T G with Mt[a][b] = is[a] R[b][a]  ->  sum_a is[a] R[b][a] G[a]
+#pragma unroll
+    for (int b = 0; b < 3; ++b)
+        o.v_mean[b] = -(is[0] * R[b * 3 + 0] * G[0] + is[1] * R[b * 3 + 1] * G[1] + is[2] * R[b * 3 + 2] * G[2]);
+    // v_R[a][b] = v_M[a][b] is[b] with v_M = v_Mt^T
+    float vR[9];
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+#pragma unroll
+        for (int b = 0; b < 3; ++b) vR[a * 3 + b] = vMt[b * 3 + a] * is[b];
+    const float w = qn[0], x = qn[1], y = qn[2], z = qn[3];
+    const float vqn[4] = {
+        2.f * (x * (vR[7] - vR[5]) + y * (vR[2] - vR[6]) + z * (vR[3] - vR[1])),
+        2.f * (-2.f * x * (vR[4] + vR[8]) + y * (vR[3] + vR[1]) + z * (vR[6] + vR[2]) + w * (vR[7] - vR[5])),
+        2.f * (x * (vR[3] + vR[1]) - 2.f * y * (vR[0] + vR[8]) + z * (vR[7] + vR[5]) + w * (vR[2] - vR[6])),
+        2.f * (x * (vR[6] + vR[2]) + y * (vR[7] + vR[5]) - 2.f * z * (vR[0] + vR[4]) + w * (vR[3] - vR[1]))};
+    const float dq = vqn[0] * qn[0] + vqn[1] * qn[1] + vqn[2] * qn[2] + vqn[3] * qn[3];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.v_quat[k] = (vqn[k] - dq * qn[k]) * inv_norm;
+    // v_scale[j] = -is[j]^2 sum_a R[a][j] v_M[a][j] = -is[j]^2 sum_a R[a][j] vMt[j][a]
+#pragma unroll
+    for (int jx = 0; jx < 3; ++jx)
+        o.v_scale[jx] = -is[jx] * is[jx] * (R[0 * 3 + jx] * vMt[jx * 3 + 0] + R[1 * 3 + jx] * vMt[jx * 3 + 1] + R[2 * 3 + jx] * vMt[jx * 3 + 2]);
+    o.v_rgb[0] = acc[12]; o.v_rgb[1] = acc[13]; o.v_rgb[2] = acc[14];
+    o.v_opac = acc[15];
+}
+
+__global__ void __launch_bounds__(256) grad_epilogue_op_kernel(
+    int N, const CamDev* __restrict__ cams, const float* __restrict__ accum, const float* __restrict__ means,
+    const float* __restrict__ quats, const float* __restrict__ scales, float* __restrict__ v_means,
+    float* __restrict__ v_quats, float* __restrict__ v_scales, float* __restrict__ v_colors, float* __restrict__ v_opacities) {
+    const CamDev& cam = cams[0];
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
+        float acc[16];
+        const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const float4 t = a4[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
+        const float4 q = reinterpret_cast<const float4*>(quats)[g];
+        GaussGrad o;
+        gaussian_vjp(cam, acc, f3{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]}, q.x, q.y, q.z, q.w,
+                     f3{scales[g * 3], scales[g * 3 + 1], scales[g * 3 + 2]}, o);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { v_means[g * 3 + k] = o.v_mean[k]; v_scales[g * 3 + k] = o.v_scale[k]; v_colors[g * 3 + k] = o.v_rgb[k]; }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v_quats[g * 4 + k] = o.v_quat[k];
+        v_opacities[g] = o.v_opac;
+    }
+}
+
+// Fused-path epilogue: raw-parameter gradients (activation backward folded in) and the SH backward.
+__global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
+    int N, int K, int sh_degree, const CamDev* __restrict__ cams, const float* __restrict__ accum,
+    const float4* __restrict__ records, const int32_t* __restrict__ radii,
+    const float* __restrict__ means, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
+    const float* __restrict__ opacity_raw,
+    float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN, float* __restrict__ g_scaling,
+    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate) {
+    const CamDev& cam = cams[0];
+    const int rest = (K - 1) * 3;
+    const int nb = (sh_degree + 1) * (sh_degree + 1);
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
+        const bool visible = radii[g * 2] > 0 && radii[g * 2 + 1] > 0;
+        if (!visible) {
+            if (!accumulate) {
+#pragma unroll
+                for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] = 0.f; g_sh0[g * 3 + k] = 0.f; g_scaling[g * 3 + k] = 0.f; }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] = 0.f;
+                g_opacity[g] = 0.f;
+                float* dst = g_shN + (size_t)g * rest;
+                for (int k = 0; k < rest; ++k) dst[k] = 0.f;
+            }
+            continue;
+        }
+        float acc[16];
+        const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const float4 t = a4[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
+        const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
+        const float opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
+        const f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
+                       (float)exp((double)scaling_raw[g * 3 + 2])};
+        const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
+        const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
+        const float nrm = fmaxf(sqrtf(n2), 1e-12f);
+        const float q[4] = {qr.x / nrm, qr.y / nrm, qr.z / nrm, qr.w / nrm};
+        GaussGrad o;
+        gaussian_vjp(cam, acc, mean, q[0], q[1], q[2], q[3], scale, o);
+        // activation backward: sigmoid, exp, x / max(|x|, eps)
+        const float go = o.v_opac * (opacity * (1.0f - opacity));
+        const float gs[3] = {o.v_scale[0] * scale.x, o.v_scale[1] * scale.y, o.v_scale[2] * scale.z};
+        const float dq = o.v_quat[0] * q[0] + o.v_quat[1] * q[1] + o.v_quat[2] * q[2] + o.v_quat[3] * q[3];
+        float gq[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) gq[k] = (o.v_quat[k] - q[k] * dq) / nrm;
+        // colour clamp mask, then SH backward
+        const float4 r3 = records[(size_t)g * 4 + 3];
+        float vc[3] = {o.v_rgb[0], o.v_rgb[1], o.v_rgb[2]};
+        if (r3.x <= 0.f) vc[0] = 0.f;
+        if (r3.y <= 0.f) vc[1] = 0.f;
+        if (r3.z <= 0.f) vc[2] = 0.f;
+        float B[25];
+        sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
+        float* dst = g_shN + (size_t)g * rest;
+        if (accumulate) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] += o.v_mean[k]; g_sh0[g * 3 + k] += B[0] * vc[k]; g_scaling[g * 3 + k] += gs[k]; }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] += gq[k];
+            g_opacity[g] += go;
+            for (int k = 1; k < nb; ++k)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) dst[(k - 1) * 3 + c] += B[k] * vc[c];
+        } else {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] = o.v_mean[k]; g_sh0[g * 3 + k] = B[0] * vc[k]; g_scaling[g * 3 + k] = gs[k]; }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] = gq[k];
+            g_opacity[g] = go;
+            for (int k = 1; k < K; ++k)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) dst[(k - 1) * 3 + c] = k < nb ? B[k] * vc[c] : 0.f;
+        }
+    }
+}
+
+}  // namespace
+
+int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, cudaStream_t st) {
+    const int n_tiles = a.tw * a.th;
+    if (n_tiles == 0) return LFS_OK;
+    if (a.model == LFS_PINHOLE)
+        raster_fwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
+                                                                   a.H, a.tw, n_tiles, render, alphas, last_ids);
+    else
+        raster_fwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
+                                                                   a.H, a.tw, n_tiles, render, alphas, last_ids);
+    return check_launch("raster_fwd");
+}
+
+int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int32_t* last_ids, const float* v_render,
+                      const float* v_alphas, float* accum, cudaStream_t st) {
+    const int n_tiles = a.tw * a.th;
+    if (n_tiles == 0) return LFS_OK;
+    if (a.model == LFS_PINHOLE)
+        raster_bwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
+                                                                   a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
+                                                                   v_alphas, accum);
+    else
+        raster_bwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
+                                                                   a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
+                                                                   v_alphas, accum);
+    return check_launch("raster_bwd");
+}
+
+int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const float* means, const float* quats,
+                            const float* scales, float* v_means, float* v_quats, float* v_scales, float* v_colors,
+                            float* v_opacities, cudaStream_t st) {
+    if (N == 0) return LFS_OK;
+    grad_epilogue_op_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, cam, accum, means, quats, scales, v_means, v_quats,
+                                                              v_scales, v_colors, v_opacities);
+    return check_launch("grad_epilogue_op");
+}
+
+int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
+                               const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
+                               int accumulate, cudaStream_t st) {
+    if (N == 0) return LFS_OK;
+    grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
+                                                                 p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
+                                                                 g.sh0, g.shN, g.scaling_raw, g.rotation_raw,
+                                                                 g.opacity_raw, accumulate);
+    return check_launch("grad_epilogue_fused");
+}
+
+}  // namespace lfs

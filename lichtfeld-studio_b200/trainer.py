@@ -1,0 +1,192 @@
+"""Fused training-step path over the C ABI: the call sequence of Trainer::train_step
+(src/training/trainer.cpp:599-875) for the gsplat / 3DGUT rasterizer — rasterize()
+(src/training/rasterization/rasterizer.cpp:15), compute_photometric_loss (trainer.cpp:107-134),
+backward (rasterizer_autograd.cpp:105) and strategy->step — without autograd or ATen glue.
+
+All buffers (parameters, gradients, forward state, loss scratch) are allocated once and reused;
+every step is a fixed sequence of asynchronous launches on the current stream with no host
+synchronisation. torch provides device memory and streams only."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _capi as capi
+from ._capi import RenderConfig, UTParams, call, ptr, splats_struct
+
+PARAM_NAMES = ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")
+
+
+def _stream():
+    return capi.vp(torch.cuda.current_stream().cuda_stream)
+
+
+def row_widths(K: int):
+    return dict(means=3, sh0=3, shN=(K - 1) * 3, scaling_raw=3, rotation_raw=4, opacity_raw=1)
+
+
+class SplatData:
+    """The six raw parameter tensors of src/core/splat_data.hpp:104-109 as views into ONE flat
+    buffer, group-major ([means | sh0 | shN | scaling | rotation | opacity], each with room for
+    `capacity` rows) so that gradients / moments of all groups can be reduced or updated as one
+    range. `size` rows are live; densification appends rows in place instead of torch.cat."""
+
+    def __init__(self, n: int, sh_coeffs: int, device, capacity: int | None = None):
+        self.K = int(sh_coeffs)
+        self.capacity = int(capacity or n)
+        self.size = int(n)
+        self.device = device
+        w = row_widths(self.K)
+        self.row_floats = sum(w.values())
+        self.flat = torch.zeros(self.capacity * self.row_floats, dtype=torch.float32, device=device)
+        self._full = {}
+        off = 0
+        for name in PARAM_NAMES:
+            cnt = self.capacity * w[name]
+            self._full[name] = self.flat[off:off + cnt]
+            off += cnt
+        self._w = w
+
+    def tensor(self, name: str) -> torch.Tensor:
+        """Live rows of one group in the reference's shape."""
+        w = self._w[name]
+        t = self._full[name][: self.size * w]
+        if name == "sh0":
+            return t.view(self.size, 1, 3)
+        if name == "shN":
+            return t.view(self.size, self.K - 1, 3)
+        return t.view(self.size, w)
+
+    def tensors(self) -> dict:
+        return {n: self.tensor(n) for n in PARAM_NAMES}
+
+    def load(self, params: dict):
+        for n in PARAM_NAMES:
+            self.tensor(n).copy_(torch.as_tensor(params[n]).to(self.device).reshape(self.tensor(n).shape))
+        return self
+
+    def struct(self) -> capi.Splats:
+        return capi.Splats(*(self._full[n].data_ptr() for n in PARAM_NAMES))
+
+    def like(self) -> "SplatData":
+        return SplatData(self.size, self.K, self.device, self.capacity)
+
+
+@dataclass
+class Camera:
+    """What the step needs of gs::Camera: world-to-camera [R|t] (world_view_transform), K, size, model."""
+    viewmat: torch.Tensor  # [4,4] float32 on device
+    K: torch.Tensor        # [3,3]
+    width: int
+    height: int
+    camera_model: int = capi.PINHOLE
+    radial: torch.Tensor | None = None  # [4] fisheye coefficients
+
+
+@dataclass
+class RenderOutput:
+    """src/training/rasterization/rasterizer.hpp RenderOutput (fields the trainer uses)."""
+    image: torch.Tensor   # [H,W,3] unclamped render; the clamp / permute is folded into the loss kernel
+    alpha: torch.Tensor   # [H,W,1]
+    width: int
+    height: int
+    status: torch.Tensor  # int32[4] on device: overflow flag, n_isects, n_visible
+
+
+class Rasterizer:
+    """rasterize() + FusedRasterizationWithSHFunction for a fixed (N capacity, image size): owns the
+    workspace that carries the forward state to the backward."""
+
+    def __init__(self, model: SplatData, width: int, height: int, sh_degree: int, camera_model=capi.PINHOLE,
+                 isect_capacity: int | None = None, eps2d=0.3, near_plane=0.01, far_plane=10000.0, radius_clip=0.0):
+        self.model = model
+        self.W, self.H = int(width), int(height)
+        cap = int(isect_capacity) if isect_capacity is not None else max(8 * model.capacity, 1 << 20)
+        self.cfg = RenderConfig(model.size, model.K, int(sh_degree), self.W, self.H, 16, int(camera_model),
+                                eps2d, near_plane, far_plane, radius_clip, UTParams(), cap)
+        self._alloc()
+        dev = model.device
+        self.render = torch.empty((self.H, self.W, 3), dtype=torch.float32, device=dev)
+        self.alpha = torch.empty((self.H, self.W, 1), dtype=torch.float32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def _alloc(self):
+        cfg = RenderConfig.from_buffer_copy(self.cfg)
+        cfg.N = self.model.capacity
+        nbytes = capi.lib().lfs_render_workspace_bytes(C.byref(cfg))
+        if nbytes == 0:
+            raise capi.LfsError("lfs_render_workspace_bytes: " + capi.lib().lfs_last_error().decode())
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.model.device)
+
+    def set_sh_degree(self, d: int):
+        self.cfg.sh_degree = int(d)
+
+    def forward(self, cam: Camera, background: torch.Tensor | None) -> RenderOutput:
+        if cam.width != self.W or cam.height != self.H:
+            raise RuntimeError("camera size does not match the rasterizer")
+        self.cfg.N = self.model.size
+        self.cfg.camera_model = int(cam.camera_model)
+        p = self.model.struct()
+        call("lfs_render_forward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), ptr(cam.radial),
+             ptr(background), ptr(self.render), ptr(self.alpha), ptr(self.status), ptr(self.ws), self.ws.numel(), _stream())
+        return RenderOutput(self.render, self.alpha, self.W, self.H, self.status)
+
+    def backward(self, v_render: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
+                 v_alpha: torch.Tensor | None = None, accumulate: bool = False):
+        p, g = self.model.struct(), grads.struct()
+        call("lfs_render_backward", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.alpha), ptr(v_render), ptr(v_alpha),
+             C.byref(g), 1 if accumulate else 0, ptr(self.ws), self.ws.numel(), _stream())
+
+
+    def state(self) -> dict:
+        """Copies of the forward state in the workspace (per-Gaussian projection outputs and tile lists);
+        synchronises. For inspection, tests and strategies that need radii / means2d."""
+        view = capi.RenderView()
+        cfg = RenderConfig.from_buffer_copy(self.cfg)
+        cfg.N = self.model.capacity
+        call("lfs_render_workspace_view", C.byref(cfg), ptr(self.ws), self.ws.numel(), C.byref(view))
+        torch.cuda.synchronize()
+        n_isects = int(self.status[1].item())
+        n, tiles = self.model.size, ((self.W + 15) // 16) * ((self.H + 15) // 16)
+        base = self.ws.data_ptr()
+
+        def grab(p, count, dtype):
+            nbytes = count * torch.empty(0, dtype=dtype).element_size()
+            off = p - base
+            return self.ws[off:off + nbytes].view(dtype).clone()
+
+        return dict(radii=grab(view.radii, n * 2, torch.int32).view(n, 2),
+                    means2d=grab(view.means2d, n * 2, torch.float32).view(n, 2),
+                    depths=grab(view.depths, n, torch.float32),
+                    tiles_per_gauss=grab(view.tiles_per_gauss, n, torch.int32),
+                    tile_offsets=grab(view.tile_offsets, tiles + 1, torch.int32),
+                    flatten_ids=grab(view.flatten_ids, n_isects, torch.int32),
+                    last_ids=grab(view.last_ids, self.W * self.H, torch.int32).view(self.H, self.W),
+                    records=grab(view.records, n * 16, torch.float32).view(n, 16), n_isects=n_isects)
+
+
+class PhotometricLoss:
+    """Trainer::compute_photometric_loss and its backward in two kernels."""
+
+    def __init__(self, width: int, height: int, device, lambda_dssim: float = 0.2):
+        self.W, self.H, self.lam = int(width), int(height), float(lambda_dssim)
+        self.ws = torch.empty(capi.lib().lfs_photometric_loss_workspace_bytes(self.H, self.W), dtype=torch.uint8, device=device)
+        self.v_render = torch.empty((self.H, self.W, 3), dtype=torch.float32, device=device)
+        self.loss = torch.zeros(4, dtype=torch.float32, device=device)
+
+    def __call__(self, render_hwc: torch.Tensor, target_chw: torch.Tensor, grad_scale: float = 1.0, want_grad: bool = True):
+        call("lfs_photometric_loss", self.H, self.W, self.lam, float(grad_scale), ptr(render_hwc), ptr(target_chw),
+             ptr(self.v_render) if want_grad else None, ptr(self.loss), ptr(self.ws), self.ws.numel(), _stream())
+        return self.loss, self.v_render
+
+
+def adam_step_splats(model: SplatData, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
+                     beta1=0.9, beta2=0.999, eps=1e-15, skip_shN=False, first_row=0, n_rows=None, grad_scale=1.0):
+    """One launch of the fused Adam over all six groups (FusedAdam::step)."""
+    n_rows = model.size - first_row if n_rows is None else n_rows
+    lr = (C.c_float * 6)(*[float(x) for x in lrs])
+    p, m, v, g = model.struct(), exp_avg.struct(), exp_avg_sq.struct(), grads.struct()
+    call("lfs_adam_step_splats", model.size, model.K, C.byref(p), C.byref(m), C.byref(v), C.byref(g), lr, float(beta1),
+         float(beta2), float(eps), int(step_count), 1 if skip_shN else 0, int(first_row), int(n_rows), float(grad_scale), _stream())

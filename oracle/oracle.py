@@ -1,0 +1,327 @@
+"""TEST INFRASTRUCTURE — ctypes front end of the scalar CPU oracle (oracle/lfs_oracle.cpp).
+
+Only tests, the smoke check and the benchmark's CPU-baseline / reference arm may import this
+module. The product (the CUDA library and its host mirror) never does.
+
+Parity status: PARITY UNPINNED by the reference's own tests — the reference ships no golden
+vectors or known-answer tests for this path and has no CPU implementation. See the header of
+lfs_oracle.cpp.
+
+The orchestration functions below restate the reference's torch glue:
+  * activations: src/core/splat_data.cpp:267-286 (sigmoid / exp / F.normalize / cat(sh0, shN))
+  * forward:     gsplat/Rasterization.cpp:326-466
+  * backward:    gsplat/Rasterization.cpp:527-641
+  * image:       src/training/rasterization/rasterizer.cpp:205 (clamp + permute)
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SO = _HERE / "_build" / "liblfs_oracle.so"
+_SRC = _HERE / "lfs_oracle.cpp"
+
+
+def build(force: bool = False) -> Path:
+    """Compile the oracle with gcc (IEEE float32, no contraction, OpenMP)."""
+    if force or not _SO.exists() or _SO.stat().st_mtime < _SRC.stat().st_mtime:
+        _SO.parent.mkdir(exist_ok=True)
+        subprocess.check_call(
+            ["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC",
+             "-o", str(_SO), str(_SRC)])
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(str(build()))
+        _lib.orc_intersect_count.restype = C.c_int64
+        _lib.orc_rasterize_fwd.restype = C.c_int64
+        _lib.orc_rasterize_bwd.restype = C.c_int64
+        _lib.orc_photometric_loss.restype = C.c_float
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+f = C.c_float
+i32 = C.c_int
+u32 = C.c_uint32
+i64 = C.c_int64
+
+UT_DEFAULT = np.array([0.1, 2.0, 0.0, 0.1, 1.0], dtype=np.float32)
+PINHOLE, ORTHO, FISHEYE, EQUIRECTANGULAR = 0, 1, 2, 3
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+# ------------------------------------------------------------------ operators
+def projection_ut_3dgs_fused(means, quats, scales, opacities, viewmats, Ks, W, H, eps2d=0.3,
+                             near=0.01, far=1e4, radius_clip=0.0, calc_compensations=False,
+                             camera_model=PINHOLE, ut=UT_DEFAULT, radial_coeffs=None):
+    means, quats, scales = _f32(means), _f32(quats), _f32(scales)
+    opacities, viewmats, Ks = _f32(opacities), _f32(viewmats), _f32(Ks)
+    radial_coeffs = _f32(radial_coeffs)
+    N, Cn = means.shape[0], viewmats.shape[0]
+    radii = np.zeros((Cn, N, 2), np.int32)
+    means2d = np.zeros((Cn, N, 2), np.float32)
+    depths = np.zeros((Cn, N), np.float32)
+    conics = np.zeros((Cn, N, 3), np.float32)
+    comps = np.zeros((Cn, N), np.float32) if calc_compensations else None
+    lib().orc_projection_ut_3dgs_fused(
+        i32(Cn), i32(N), _p(means), _p(quats), _p(scales), _p(opacities), _p(viewmats), _p(Ks),
+        i32(W), i32(H), f(eps2d), f(near), f(far), f(radius_clip), i32(camera_model),
+        _p(_f32(ut)), _p(radial_coeffs), _p(radii), _p(means2d), _p(depths), _p(conics), _p(comps))
+    return radii, means2d, depths, conics, comps
+
+
+def spherical_harmonics_fwd(degree, dirs, coeffs, masks=None):
+    dirs, coeffs = _f32(dirs), _f32(coeffs)
+    n, K = dirs.reshape(-1, 3).shape[0], coeffs.shape[-2]
+    colors = np.zeros((n, 3), np.float32)
+    m = None if masks is None else np.ascontiguousarray(masks.reshape(-1), np.uint8)
+    lib().orc_spherical_harmonics_fwd(i32(n), i32(K), i32(degree), _p(dirs), _p(coeffs), _p(m), _p(colors))
+    return colors.reshape(dirs.shape)
+
+
+def spherical_harmonics_bwd(K, degree, dirs, masks, v_colors):
+    dirs, v_colors = _f32(dirs), _f32(v_colors)
+    n = dirs.reshape(-1, 3).shape[0]
+    v_coeffs = np.zeros((n, K, 3), np.float32)
+    m = None if masks is None else np.ascontiguousarray(masks.reshape(-1), np.uint8)
+    lib().orc_spherical_harmonics_bwd(i32(n), i32(K), i32(degree), _p(dirs), _p(m), _p(v_colors), _p(v_coeffs))
+    return v_coeffs
+
+
+def intersect_tile(means2d, radii, depths, Cn, tile_size, tw, th, sort=True):
+    means2d, depths = _f32(means2d), _f32(depths)
+    radii = np.ascontiguousarray(radii, np.int32)
+    N = means2d.size // 2 // Cn
+    tpg = np.zeros((Cn, N), np.int32)
+    n = int(lib().orc_intersect_count(i32(Cn), i32(N), _p(means2d), _p(radii), u32(tile_size), u32(tw), u32(th), _p(tpg)))
+    ids = np.zeros(n, np.int64)
+    flat = np.zeros(n, np.int32)
+    lib().orc_intersect_emit_sort(i32(Cn), i32(N), _p(means2d), _p(radii), _p(depths), u32(tile_size), u32(tw), u32(th),
+                                  i32(1 if sort else 0), i64(n), _p(ids), _p(flat))
+    return tpg, ids, flat
+
+
+def intersect_offset(isect_ids, Cn, tw, th):
+    isect_ids = np.ascontiguousarray(isect_ids, np.int64)
+    off = np.zeros((Cn, th, tw), np.int32)
+    lib().orc_intersect_offset(i64(isect_ids.size), _p(isect_ids), i32(Cn), u32(tw), u32(th), _p(off))
+    return off
+
+
+def rasterize_fwd(means, quats, scales, colors, opacities, background, W, H, tile_size, viewmat, K,
+                  tile_offsets, flatten_ids, camera_model=PINHOLE, radial=None):
+    """One camera (the reference kernel supports C = 1 only). Returns render [H,W,3], alpha [H,W,1],
+    last_ids [H,W] and the number of (pixel, entry) pairs visited."""
+    a = [_f32(x) for x in (means, quats, scales, colors, opacities)]
+    bg = _f32(background)
+    render = np.zeros((H, W, 3), np.float32)
+    alpha = np.zeros((H, W, 1), np.float32)
+    last = np.zeros((H, W), np.int32)
+    to = np.ascontiguousarray(tile_offsets, np.int32)
+    fl = np.ascontiguousarray(flatten_ids, np.int32)
+    npairs = lib().orc_rasterize_fwd(
+        i32(a[0].shape[0]), i64(fl.size), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg),
+        i32(W), i32(H), i32(tile_size), _p(_f32(viewmat)), _p(_f32(K)), i32(camera_model), _p(_f32(radial)),
+        _p(to), _p(fl), _p(render), _p(alpha), _p(last))
+    return render, alpha, last, int(npairs)
+
+
+def rasterize_bwd(means, quats, scales, colors, opacities, background, W, H, tile_size, viewmat, K,
+                  tile_offsets, flatten_ids, render_alphas, last_ids, v_render_colors, v_render_alphas,
+                  camera_model=PINHOLE, radial=None):
+    a = [_f32(x) for x in (means, quats, scales, colors, opacities)]
+    N = a[0].shape[0]
+    bg = _f32(background)
+    to = np.ascontiguousarray(tile_offsets, np.int32)
+    fl = np.ascontiguousarray(flatten_ids, np.int32)
+    v_means = np.zeros((N, 3), np.float32)
+    v_quats = np.zeros((N, 4), np.float32)
+    v_scales = np.zeros((N, 3), np.float32)
+    v_colors = np.zeros((N, 3), np.float32)
+    v_opac = np.zeros((N,), np.float32)
+    npairs = lib().orc_rasterize_bwd(
+        i32(N), i64(fl.size), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg),
+        i32(W), i32(H), i32(tile_size), _p(_f32(viewmat)), _p(_f32(K)), i32(camera_model), _p(_f32(radial)),
+        _p(to), _p(fl), _p(_f32(render_alphas)), _p(np.ascontiguousarray(last_ids, np.int32)),
+        _p(_f32(v_render_colors)), _p(_f32(v_render_alphas)),
+        _p(v_means), _p(v_quats), _p(v_scales), _p(v_colors), _p(v_opac))
+    return v_means, v_quats, v_scales, v_colors, v_opac, int(npairs)
+
+
+def fusedssim(img1, img2, C1=0.01 ** 2, C2=0.03 ** 2):
+    img1, img2 = _f32(img1), _f32(img2)
+    CH, H, W = img1.shape
+    outs = [np.zeros_like(img1) for _ in range(4)]
+    lib().orc_fusedssim_fwd(i32(CH), i32(H), i32(W), f(C1), f(C2), _p(img1), _p(img2), *[_p(o) for o in outs])
+    return outs
+
+
+def fusedssim_backward(img1, img2, dL_dmap, dm1, ds1, ds12):
+    img1 = _f32(img1)
+    CH, H, W = img1.shape
+    out = np.zeros_like(img1)
+    lib().orc_fusedssim_bwd(i32(CH), i32(H), i32(W), _p(img1), _p(_f32(img2)), _p(_f32(dL_dmap)),
+                            _p(_f32(dm1)), _p(_f32(ds1)), _p(_f32(ds12)), _p(out))
+    return out
+
+
+def photometric_loss(render_hwc, target_chw, lambda_dssim=0.2, want_grad=True):
+    render_hwc, target_chw = _f32(render_hwc), _f32(target_chw)
+    H, W, _ = render_hwc.shape
+    g = np.zeros_like(render_hwc) if want_grad else None
+    l1, ss = C.c_float(), C.c_float()
+    loss = lib().orc_photometric_loss(i32(H), i32(W), f(lambda_dssim), _p(render_hwc), _p(target_chw), _p(g),
+                                      C.byref(l1), C.byref(ss))
+    return float(loss), g, float(l1.value), float(ss.value)
+
+
+def adam_step(param, exp_avg, exp_avg_sq, grad, lr, beta1, beta2, eps, step_count):
+    """In place. Bias terms in double on the host as src/training/optimizers/fused_adam.cpp:78-79."""
+    bc1 = 1.0 / (1.0 - beta1 ** step_count)
+    bc2 = 1.0 / np.sqrt(1.0 - beta2 ** step_count)
+    for a in (param, exp_avg, exp_avg_sq):
+        assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    lib().orc_adam_step(i64(param.size), _p(param), _p(exp_avg), _p(exp_avg_sq), _p(_f32(grad)),
+                        f(lr), f(beta1), f(beta2), f(eps), f(bc1), f(bc2))
+
+
+def binoms_table(n_max=51):
+    """src/training/strategies/mcmc.cpp:459-472: running float product."""
+    b = np.zeros((n_max, n_max), np.float32)
+    for n in range(n_max):
+        for k in range(n + 1):
+            v = np.float32(1.0)
+            for i in range(k):
+                v = np.float32(v * (np.float32(n - i) / np.float32(i + 1)))
+            b[n, k] = v
+    return b
+
+
+def relocation(opacities, scales, ratios, binoms, n_max):
+    opacities, scales, binoms = _f32(opacities), _f32(scales), _f32(binoms)
+    ratios = np.ascontiguousarray(ratios, np.int32)
+    n = opacities.shape[0]
+    no = np.zeros(n, np.float32)
+    ns = np.zeros((n, 3), np.float32)
+    lib().orc_relocation(i32(n), _p(opacities), _p(scales), _p(ratios), _p(binoms), i32(n_max), _p(no), _p(ns))
+    return no, ns
+
+
+def add_noise(raw_opacities, raw_scales, raw_quats, noise, means, current_lr):
+    """In place on means."""
+    assert means.dtype == np.float32 and means.flags["C_CONTIGUOUS"]
+    lib().orc_add_noise(i32(means.shape[0]), _p(_f32(raw_opacities)), _p(_f32(raw_scales)), _p(_f32(raw_quats)),
+                        _p(_f32(noise)), _p(means), f(current_lr))
+
+
+def quats_to_rotmats(quats):
+    quats = _f32(quats)
+    out = np.zeros((quats.shape[0], 3, 3), np.float32)
+    lib().orc_quats_to_rotmats(i32(quats.shape[0]), _p(quats), _p(out))
+    return out
+
+
+def campos(viewmat):
+    out = np.zeros(3, np.float32)
+    lib().orc_campos(_p(_f32(viewmat)), _p(out))
+    return out
+
+
+# ------------------------------------------------------------------ activations
+def act_opacity(raw):
+    return (1.0 / (1.0 + np.exp(-raw.astype(np.float64)))).astype(np.float32).reshape(-1)
+
+
+def act_scale(raw):
+    return np.exp(raw.astype(np.float64)).astype(np.float32)
+
+
+def act_quat(raw):
+    raw = raw.astype(np.float32)
+    n2 = ((raw[:, 0] * raw[:, 0] + raw[:, 1] * raw[:, 1]) + raw[:, 2] * raw[:, 2]) + raw[:, 3] * raw[:, 3]
+    nrm = np.maximum(np.sqrt(n2), np.float32(1e-12)).astype(np.float32)
+    return (raw / nrm[:, None]).astype(np.float32), nrm
+
+
+# ------------------------------------------------------------------ orchestration
+def render_fwd(params, viewmat, K, W, H, sh_degree, background=None, camera_model=PINHOLE, radial=None,
+               tile_size=16, eps2d=0.3, near=0.01, far=1e4):
+    """gsplat::rasterize_from_world_with_sh_fwd for one camera on raw SplatData parameters.
+    params: dict(means, sh0, shN, scaling_raw, rotation_raw, opacity_raw)."""
+    means = _f32(params["means"])
+    opac = act_opacity(params["opacity_raw"])
+    scales = act_scale(params["scaling_raw"])
+    quats, qnorm = act_quat(params["rotation_raw"])
+    sh = np.concatenate([params["sh0"], params["shN"]], axis=1).astype(np.float32)
+    vm = _f32(viewmat).reshape(1, 4, 4)
+    Kc = _f32(K).reshape(1, 3, 3)
+    rc = None if radial is None else _f32(radial).reshape(1, 4)
+    radii, means2d, depths, conics, _ = projection_ut_3dgs_fused(
+        means, quats, scales, opac, vm, Kc, W, H, eps2d, near, far, 0.0, False, camera_model, UT_DEFAULT, rc)
+    cp = campos(vm[0])
+    dirs = (means - cp[None, :]).astype(np.float32)
+    masks = (radii[0] > 0).all(-1)
+    rgb = spherical_harmonics_fwd(sh_degree, dirs, sh, masks)
+    colors = np.maximum(rgb + np.float32(0.5), np.float32(0.0)).astype(np.float32)
+    colors[~masks] = 0.0
+    tw, th = (W + tile_size - 1) // tile_size, (H + tile_size - 1) // tile_size
+    tpg, ids, flat = intersect_tile(means2d, radii, depths, 1, tile_size, tw, th, True)
+    offs = intersect_offset(ids, 1, tw, th)
+    render, alpha, last, npairs = rasterize_fwd(means, quats, scales, colors, opac, background, W, H, tile_size,
+                                                vm[0], Kc[0], offs[0], flat, camera_model, rc)
+    return dict(render=render, alpha=alpha, last_ids=last, radii=radii[0], means2d=means2d[0], depths=depths[0],
+                colors=colors, tile_offsets=offs[0], flatten_ids=flat, isect_ids=ids, tiles_per_gauss=tpg[0],
+                masks=masks, dirs=dirs, opac=opac, scales=scales, quats=quats, qnorm=qnorm, sh=sh,
+                n_pairs_fwd=npairs, conics=conics[0])
+
+
+def render_bwd(params, fwd, viewmat, K, W, H, sh_degree, v_render, v_alpha=None, background=None,
+               camera_model=PINHOLE, radial=None, tile_size=16):
+    """gsplat::rasterize_from_world_with_sh_bwd followed by the activation backward; returns
+    gradients w.r.t. the six raw parameter tensors."""
+    means = _f32(params["means"])
+    if v_alpha is None:
+        v_alpha = np.zeros((H, W, 1), np.float32)
+    rc = None if radial is None else _f32(radial).reshape(1, 4)
+    v_means, v_quats, v_scales, v_colors, v_opac, npairs = rasterize_bwd(
+        means, fwd["quats"], fwd["scales"], fwd["colors"], fwd["opac"], background, W, H, tile_size,
+        viewmat, K, fwd["tile_offsets"], fwd["flatten_ids"], fwd["alpha"], fwd["last_ids"], v_render, v_alpha,
+        camera_model, rc)
+    v_pre = v_colors.copy()
+    v_pre[fwd["colors"] <= 0.0] = 0.0
+    K_sh = fwd["sh"].shape[1]
+    v_sh = spherical_harmonics_bwd(K_sh, sh_degree, fwd["dirs"], fwd["masks"], v_pre)
+    o, s, q, nrm = fwd["opac"], fwd["scales"], fwd["quats"], fwd["qnorm"]
+    g_opacity = (v_opac * (o * (np.float32(1.0) - o))).astype(np.float32).reshape(-1, 1)
+    g_scaling = (v_scales * s).astype(np.float32)
+    dq = (v_quats * q).sum(-1, keepdims=True).astype(np.float32)
+    g_rotation = ((v_quats - q * dq) / nrm[:, None]).astype(np.float32)
+    return dict(means=v_means, sh0=np.ascontiguousarray(v_sh[:, :1]), shN=np.ascontiguousarray(v_sh[:, 1:]),
+                scaling_raw=g_scaling, rotation_raw=g_rotation, opacity_raw=g_opacity,
+                v_colors=v_colors, v_opacities=v_opac, v_quats=v_quats, v_scales=v_scales, n_pairs_bwd=npairs)

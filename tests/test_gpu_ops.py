@@ -1,0 +1,272 @@
+"""GPU parity tests proper: every operator of the C ABI against the CPU oracle on the same seeded
+inputs. Integer / index outputs must be bit-exact; float outputs within the stated tolerance
+(images 1e-4 max-abs, gradients 1e-3 relative L2)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_scene, rel_l2
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def activated(orc, P):
+    q, _ = orc.act_quat(P["rotation_raw"])
+    return P["means"], q, orc.act_scale(P["scaling_raw"]), orc.act_opacity(P["opacity_raw"])
+
+
+@pytest.fixture(scope="module")
+def scene(synth, orc):
+    cfg, P, vm, K = make_scene(synth, 16384, 256, 256, 0)
+    fwd = orc.render_fwd(P, vm, K, 256, 256, 0, background=np.zeros(3, np.float32))
+    return cfg, P, vm, K, fwd
+
+
+@pytest.fixture(scope="module")
+def scene_sh3(synth, orc):
+    # ragged image (not a multiple of 16), SH degree 3, non-zero background
+    cfg, P, vm, K = make_scene(synth, 20000, 250, 170, 3, seed=3, fx=260.0)
+    bg = np.array([0.2, 0.5, 0.1], np.float32)
+    fwd = orc.render_fwd(P, vm, K, 250, 170, 3, background=bg)
+    return cfg, P, vm, K, fwd, bg
+
+
+def test_projection_bit_exact(pkg, orc, scene):
+    cfg, P, vm, K, fwd = scene
+    means, q, s, o = activated(orc, P)
+    radii, means2d, depths, conics, comps = pkg.ops.projection_ut_3dgs_fused(
+        T(means), T(q), T(s), T(o), T(vm[None]), None, T(K[None]), 256, 256, 0.3, 0.01, 1e4, 0.0, True, 0)
+    r_ref, m_ref, d_ref, c_ref, comp_ref = orc.projection_ut_3dgs_fused(means, q, s, o, vm[None], K[None], 256, 256, calc_compensations=True)
+    radii = radii.cpu().numpy()
+    assert np.array_equal(radii, r_ref)
+    vis = (r_ref[0] > 0).all(-1)
+    assert vis.sum() > 1000
+    # bit-exact floats where defined (culled entries are left uninitialised by both sides)
+    assert np.array_equal(means2d.cpu().numpy()[0][vis].view(np.uint32), m_ref[0][vis].view(np.uint32))
+    assert np.array_equal(depths.cpu().numpy()[0][vis].view(np.uint32), d_ref[0][vis].view(np.uint32))
+    assert np.array_equal(conics.cpu().numpy()[0][vis].view(np.uint32), c_ref[0][vis].view(np.uint32))
+    assert np.array_equal(comps.cpu().numpy()[0][vis].view(np.uint32), comp_ref[0][vis].view(np.uint32))
+
+
+def test_projection_multi_camera_and_culling(pkg, orc, synth):
+    # two cameras, Gaussians spread wider than the frustum, some behind the camera
+    P = synth.make_gaussians(5000, 7, "wide", 0)
+    means, q, s, o = activated(orc, P)
+    poses = synth.hemisphere_poses(2, 6.0)
+    K = synth.intrinsics(200, 200, 100, 75)[None].repeat(2, 0)
+    out = pkg.ops.projection_ut_3dgs_fused(T(means), T(q), T(s * 30), T(o), T(poses), None, T(K), 200, 150, 0.3, 0.01, 1e4, 0.0, False, 0)
+    ref = orc.projection_ut_3dgs_fused(means, q, s * 30, o, poses, K, 200, 150)
+    assert np.array_equal(out[0].cpu().numpy(), ref[0])
+    vis = (ref[0] > 0).all(-1)
+    assert 0 < vis.sum() < vis.size
+    assert np.array_equal(out[1].cpu().numpy()[vis].view(np.uint32), ref[1][vis].view(np.uint32))
+
+
+def test_projection_fisheye(pkg, orc, synth):
+    P = synth.make_gaussians(8000, 11, "cube", 0)
+    means, q, s, o = activated(orc, P)
+    vm = synth.look_at_origin([0.5, -2.5, 0.7])[None]
+    K = synth.intrinsics(120.0, 120.0, 160, 160)[None]
+    for radial in (None, np.array([[0.05, -0.01, 0.0, 0.0]], np.float32)):
+        out = pkg.ops.projection_ut_3dgs_fused(T(means), T(q), T(s * 4), T(o), T(vm), None, T(K), 320, 320, 0.3, 0.01, 1e4, 0.0, False, 2,
+                                               radial_coeffs=None if radial is None else T(radial))
+        ref = orc.projection_ut_3dgs_fused(means, q, s * 4, o, vm, K, 320, 320, camera_model=2, radial_coeffs=radial)
+        # atan2 goes through double on both sides; allow a vanishing number of last-bit disagreements
+        mism = (out[0].cpu().numpy() != ref[0]).any(-1).sum()
+        assert mism <= 2, mism
+        vis = (ref[0] > 0).all(-1) & (out[0].cpu().numpy() > 0).all(-1)
+        assert vis.sum() > 500
+        assert np.abs(out[1].cpu().numpy()[vis] - ref[1][vis]).max() < 1e-3
+
+
+def test_sh_fwd_bwd(pkg, orc, synth):
+    rng = np.random.default_rng(0)
+    n = 5000
+    dirs = rng.normal(size=(n, 3)).astype(np.float32)
+    masks = rng.random(n) > 0.2
+    for deg in range(5):
+        K = 25
+        coeffs = rng.normal(size=(n, K, 3)).astype(np.float32)
+        col = pkg.ops.spherical_harmonics_fwd(deg, T(dirs), T(coeffs), T(masks)).cpu().numpy()
+        ref = orc.spherical_harmonics_fwd(deg, dirs, coeffs, masks)
+        assert np.abs(col[masks] - ref[masks]).max() < 2e-5
+        v = rng.normal(size=(n, 3)).astype(np.float32)
+        g, _ = pkg.ops.spherical_harmonics_bwd(K, deg, T(dirs), None, T(masks), T(v))
+        gref = orc.spherical_harmonics_bwd(K, deg, dirs, masks, v)
+        assert np.abs(g.cpu().numpy() - gref).max() < 2e-5
+        assert (g.cpu().numpy()[~masks] == 0).all()
+
+
+def test_intersect_bit_exact(pkg, orc, scene, scene_sh3):
+    for sc, (W, H) in ((scene, (256, 256)), (scene_sh3, (250, 170))):
+        fwd = sc[4]
+        tw, th = (W + 15) // 16, (H + 15) // 16
+        m2, r, d = fwd["means2d"][None], fwd["radii"][None], fwd["depths"][None]
+        for sort in (True, False):
+            tpg, ids, flat = pkg.ops.intersect_tile(T(m2), T(r), T(d), None, None, 1, 16, tw, th, sort)
+            tpg_r, ids_r, flat_r = orc.intersect_tile(m2, r, d, 1, 16, tw, th, sort)
+            assert np.array_equal(tpg.cpu().numpy(), tpg_r)
+            assert np.array_equal(ids.cpu().numpy(), ids_r)
+            assert np.array_equal(flat.cpu().numpy(), flat_r)
+        off = pkg.ops.intersect_offset(ids if sort else ids, 1, tw, th)
+        tpg, ids, flat = pkg.ops.intersect_tile(T(m2), T(r), T(d), None, None, 1, 16, tw, th, True)
+        off = pkg.ops.intersect_offset(ids, 1, tw, th).cpu().numpy()
+        assert np.array_equal(off[0], fwd["tile_offsets"])
+
+
+def test_intersect_multi_camera_ties_and_empty(pkg, orc):
+    # hand-made case: 2 cameras, duplicate depths (ties broken by index), negative / huge boxes, zero radii
+    rng = np.random.default_rng(5)
+    C, N, tw, th = 2, 3000, 9, 7
+    m2 = (rng.random((C, N, 2)) * [tw * 16 + 60, th * 16 + 60] - 30).astype(np.float32)
+    r = rng.integers(0, 40, size=(C, N, 2)).astype(np.int32)
+    r[:, ::7] = 0
+    d = rng.integers(1, 20, size=(C, N)).astype(np.float32) * 0.25  # many exact ties
+    tpg, ids, flat = pkg.ops.intersect_tile(T(m2), T(r), T(d), None, None, C, 16, tw, th, True)
+    tpg_r, ids_r, flat_r = orc.intersect_tile(m2, r, d, C, 16, tw, th, True)
+    assert np.array_equal(tpg.cpu().numpy(), tpg_r) and np.array_equal(ids.cpu().numpy(), ids_r)
+    assert np.array_equal(flat.cpu().numpy(), flat_r)
+    off = pkg.ops.intersect_offset(ids, C, tw, th).cpu().numpy()
+    assert np.array_equal(off, orc.intersect_offset(ids_r, C, tw, th))
+    # nothing visible at all
+    r0 = np.zeros_like(r)
+    tpg, ids, flat = pkg.ops.intersect_tile(T(m2), T(r0), T(d), None, None, C, 16, tw, th, True)
+    assert ids.numel() == 0 and flat.numel() == 0 and int(tpg.sum()) == 0
+    assert (pkg.ops.intersect_offset(ids, C, tw, th).cpu().numpy() == 0).all()
+
+
+def _raster_inputs(orc, P, fwd):
+    means, q, s, o = activated(orc, P)
+    return means, q, s, fwd["colors"], o
+
+
+def _check_image(img, ref, tol=1e-4, max_outliers=2):
+    diff = np.abs(img - ref)
+    # a pixel can differ by up to alpha*T ~ 4e-3 when an alpha sits within rounding of the 1/255
+    # threshold on one side only; allow a vanishing number of those
+    assert (diff.max(-1) > tol).sum() <= max_outliers, ((diff.max(-1) > tol).sum(), diff.max())
+    assert np.quantile(diff, 0.9999) < tol
+
+
+def test_rasterize_fwd_bwd_against_oracle(pkg, orc, scene, scene_sh3):
+    for sc, (W, H), bg in ((scene, (256, 256), np.zeros(3, np.float32)), (scene_sh3, (250, 170), scene_sh3[5])):
+        cfg, P, vm, K, fwd = sc[:5]
+        means, q, s, col, o = _raster_inputs(orc, P, fwd)
+        args = [T(means), T(q), T(s), T(col[None]), T(o[None]), T(bg[None]), None, W, H, 16, T(vm[None]), None, T(K[None]), 0]
+        kw = dict(tile_offsets=T(fwd["tile_offsets"][None]), flatten_ids=T(fwd["flatten_ids"]))
+        ren, alp, last = pkg.ops.rasterize_to_pixels_from_world_3dgs_fwd(*args, **kw)
+        _check_image(ren.cpu().numpy()[0], fwd["render"])
+        _check_image(alp.cpu().numpy()[0], fwd["alpha"])
+        assert (last.cpu().numpy()[0] != fwd["last_ids"]).sum() <= 2
+        rng = np.random.default_rng(1)
+        v_r = rng.normal(size=(H, W, 3)).astype(np.float32) * 1e-3
+        v_a = rng.normal(size=(H, W, 1)).astype(np.float32) * 1e-3
+        ref = orc.rasterize_bwd(means, q, s, col, o, bg, W, H, 16, vm, K, fwd["tile_offsets"], fwd["flatten_ids"],
+                                fwd["alpha"], fwd["last_ids"], v_r, v_a)
+        out = pkg.ops.rasterize_to_pixels_from_world_3dgs_bwd(*args, **kw, render_alphas=T(fwd["alpha"][None]),
+                                                              last_ids=T(fwd["last_ids"][None]), v_render_colors=T(v_r[None]),
+                                                              v_render_alphas=T(v_a[None]))
+        for name, a, b in zip(("v_means", "v_quats", "v_scales", "v_colors", "v_opacities"), out, ref[:5]):
+            assert rel_l2(a.cpu().numpy(), b) < 1e-3, name
+
+
+def test_rasterize_empty_lists(pkg, orc, scene):
+    cfg, P, vm, K, fwd = scene
+    means, q, s, col, o = _raster_inputs(orc, P, fwd)
+    bg = np.array([0.3, 0.6, 0.9], np.float32)
+    offs = np.zeros((1, 16, 16), np.int32)
+    flat = np.zeros(0, np.int32)
+    ren, alp, last = pkg.ops.rasterize_to_pixels_from_world_3dgs_fwd(
+        T(means), T(q), T(s), T(col[None]), T(o[None]), T(bg[None]), None, 256, 256, 16, T(vm[None]), None, T(K[None]), 0,
+        tile_offsets=T(offs), flatten_ids=T(flat))
+    assert np.allclose(ren.cpu().numpy()[0], bg) and (alp.cpu().numpy() == 0).all() and (last.cpu().numpy() == 0).all()
+
+
+def test_fusedssim_fwd_bwd(pkg, orc):
+    rng = np.random.default_rng(2)
+    for (H, W) in ((64, 80), (37, 53), (9, 12)):
+        a = rng.random((3, H, W)).astype(np.float32)
+        b = np.clip(a + rng.normal(size=a.shape).astype(np.float32) * 0.1, 0, 1)
+        outs = pkg.ops.fusedssim(1e-4, 9e-4, T(a[None]), T(b[None]), True)
+        ref = orc.fusedssim(a, b)
+        for x, y in zip(outs, ref):
+            assert np.abs(x.cpu().numpy()[0] - y).max() < 2e-4 * max(1.0, np.abs(y).max())
+        dmap = rng.normal(size=a.shape).astype(np.float32)
+        g = pkg.ops.fusedssim_backward(1e-4, 9e-4, T(a[None]), T(b[None]), T(dmap[None]), *[T(r[None]) for r in ref[1:]])
+        gref = orc.fusedssim_backward(a, b, dmap, *ref[1:])
+        assert rel_l2(g.cpu().numpy()[0], gref) < 1e-4
+
+
+def test_photometric_loss(pkg, orc):
+    rng = np.random.default_rng(3)
+    tr = pkg.trainer
+    for (H, W) in ((96, 130), (8, 9)):
+        render = (rng.random((H, W, 3)).astype(np.float32) * 1.4 - 0.2)  # some values outside [0,1]
+        target = rng.random((3, H, W)).astype(np.float32)
+        lossfn = tr.PhotometricLoss(W, H, DEV, 0.2)
+        loss, g = lossfn(T(render), T(target))
+        lref, gref, l1, ss = orc.photometric_loss(render, target, 0.2)
+        l = loss.cpu().numpy()
+        assert abs(l[0] - lref) < 2e-6 and abs(l[1] - l1) < 2e-6 and abs(l[2] - ss) < 2e-6
+        assert rel_l2(g.cpu().numpy(), gref) < 1e-4
+        assert (g.cpu().numpy()[(render < 0) | (render > 1)] == 0).all()
+
+
+def test_adam(pkg, orc):
+    rng = np.random.default_rng(4)
+    for n in (1, 7, 4096, 100003):
+        p = rng.normal(size=n).astype(np.float32)
+        m = rng.normal(size=n).astype(np.float32) * 0.01
+        v = (rng.random(n).astype(np.float32) * 1e-4)
+        g = rng.normal(size=n).astype(np.float32) * 0.01
+        tp, tm, tv = T(p), T(m), T(v)
+        step = 17
+        bc1 = 1.0 / (1.0 - 0.9 ** step)
+        bc2 = 1.0 / np.sqrt(1.0 - 0.999 ** step)
+        pkg.ops.adam_step_wrapper(tp, tm, tv, T(g), 1e-3, 0.9, 0.999, 1e-15, bc1, bc2)
+        orc.adam_step(p, m, v, g, 1e-3, 0.9, 0.999, 1e-15, step)
+        assert np.allclose(tp.cpu().numpy(), p, rtol=1e-6, atol=1e-9)
+        assert np.allclose(tm.cpu().numpy(), m, rtol=1e-6, atol=1e-12)
+        assert np.allclose(tv.cpu().numpy(), v, rtol=1e-6, atol=1e-15)
+
+
+def test_relocation_noise_rotmats(pkg, orc):
+    rng = np.random.default_rng(6)
+    n = 4000
+    op = (rng.random(n) * 0.98 + 0.01).astype(np.float32)
+    sc = np.exp(rng.normal(size=(n, 3)) - 4).astype(np.float32)
+    ratios = rng.integers(1, 52, size=n).astype(np.int32)
+    binoms = orc.binoms_table(51)
+    no, ns = pkg.ops.relocation(T(op), T(sc), T(ratios), T(binoms), 51)
+    no_r, ns_r = orc.relocation(op, sc, ratios, binoms, 51)
+    assert np.allclose(no.cpu().numpy(), no_r, rtol=2e-5, atol=1e-7)
+    ok = np.isfinite(ns_r).all(-1)
+    assert np.allclose(ns.cpu().numpy()[ok], ns_r[ok], rtol=2e-3)
+    raw_o = rng.normal(size=n).astype(np.float32) * 3
+    raw_s = (rng.normal(size=(n, 3)) * 0.5 - 4).astype(np.float32)
+    raw_q = rng.normal(size=(n, 4)).astype(np.float32)
+    noise = rng.normal(size=(n, 3)).astype(np.float32)
+    means = rng.normal(size=(n, 3)).astype(np.float32)
+    tm = T(means)
+    pkg.ops.add_noise(T(raw_o), T(raw_s), T(raw_q), T(noise), tm, 80.0)
+    ref = means.copy()
+    orc.add_noise(raw_o, raw_s, raw_q, noise, ref, 80.0)
+    assert np.abs(tm.cpu().numpy() - ref).max() < 1e-5 and np.abs(ref - means).max() > 1e-4
+    assert np.abs(pkg.ops.quats_to_rotmats(T(raw_q)).cpu().numpy() - orc.quats_to_rotmats(raw_q)).max() < 1e-5
+
+
+def test_error_behaviour(pkg):
+    ops = pkg.ops
+    a = torch.zeros(4, 3)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        ops.quats_to_rotmats(torch.zeros(4, 4))
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        ops.quats_to_rotmats(torch.zeros(4, 8, device=DEV)[:, ::2])
+    with pytest.raises(pkg.LfsError):
+        pkg._capi.call("lfs_adam_step", None, None, None, None, 10, 0.1, 0.9, 0.999, 1e-8, 1.0, 1.0, None)
+    assert b"null pointer" in pkg._capi.lib().lfs_last_error()

@@ -1,0 +1,114 @@
+"""End-to-end parity of the fused training path (raw SplatData parameters -> image -> loss ->
+raw-parameter gradients -> Adam) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_scene, rel_l2
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _run(pkg, orc, synth, n, W, H, deg, seed, bg, fx=300.0, n_cams=1):
+    tr = pkg.trainer
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=seed, fx=fx)
+    _, P2, _, _ = make_scene(synth, n, W, H, deg, seed=seed + 1000, fx=fx)
+    fwd = orc.render_fwd(P, vm, K, W, H, deg, background=bg)
+    target = np.ascontiguousarray(np.clip(orc.render_fwd(P2, vm, K, W, H, deg, background=bg)["render"], 0, 1).transpose(2, 0, 1))
+    loss_ref, g_ref, _, _ = orc.photometric_loss(fwd["render"], target, 0.2)
+    bwd = orc.render_bwd(P, fwd, vm, K, W, H, deg, g_ref, background=bg)
+
+    model = tr.SplatData(n, (deg + 1) ** 2, DEV).load(P)
+    grads, m, v = model.like(), model.like(), model.like()
+    rast = tr.Rasterizer(model, W, H, deg)
+    lossfn = tr.PhotometricLoss(W, H, DEV)
+    cam = tr.Camera(T(vm), T(K), W, H)
+    tbg = None if bg is None else T(bg)
+    out = rast.forward(cam, tbg)
+    loss, v_render = lossfn(out.image, T(target))
+    rast.backward(v_render, grads, tbg)
+    st = rast.state()
+    return dict(P=P, fwd=fwd, bwd=bwd, loss_ref=loss_ref, g_ref=g_ref, model=model, grads=grads, m=m, v=v, rast=rast, out=out,
+                loss=loss, v_render=v_render, state=st, target=target, cam=cam, tbg=tbg, lossfn=lossfn)
+
+
+@pytest.mark.parametrize("n,W,H,deg,seed,bg", [
+    (16384, 256, 256, 0, 0, np.zeros(3, np.float32)),      # the tiny benchmark configuration
+    (20000, 250, 170, 3, 3, np.array([0.2, 0.5, 0.1], np.float32)),  # ragged image, SH degree 3, background
+    (3000, 64, 48, 2, 9, None),                            # no background
+])
+def test_fused_step_matches_oracle(pkg, orc, synth, n, W, H, deg, seed, bg):
+    r = _run(pkg, orc, synth, n, W, H, deg, seed, bg)
+    fwd, st = r["fwd"], r["state"]
+    # tile lists from raw parameters: bit-exact
+    assert np.array_equal(st["radii"].cpu().numpy(), fwd["radii"])
+    assert np.array_equal(st["tiles_per_gauss"].cpu().numpy(), fwd["tiles_per_gauss"])
+    assert st["n_isects"] == fwd["flatten_ids"].size
+    assert np.array_equal(st["flatten_ids"].cpu().numpy(), fwd["flatten_ids"])
+    assert np.array_equal(st["tile_offsets"].cpu().numpy()[:-1], fwd["tile_offsets"].reshape(-1))
+    vis = fwd["masks"]
+    assert np.array_equal(st["means2d"].cpu().numpy()[vis].view(np.uint32), fwd["means2d"][vis].view(np.uint32))
+    assert np.array_equal(st["depths"].cpu().numpy()[vis].view(np.uint32), fwd["depths"][vis].view(np.uint32))
+    status = r["out"].status.cpu().numpy()
+    assert status[0] == 0 and status[2] == vis.sum()
+    # colours (clamped SH) and image
+    assert np.abs(st["records"].cpu().numpy()[vis][:, 12:15] - fwd["colors"][vis]).max() < 2e-5
+    diff = np.abs(r["out"].image.cpu().numpy() - fwd["render"]).max(-1)
+    assert (diff > 1e-4).sum() <= 2 and np.quantile(diff, 0.9999) < 1e-4, diff.max()
+    assert np.abs(r["out"].alpha.cpu().numpy() - fwd["alpha"]).max() < 5e-3
+    assert (st["last_ids"].cpu().numpy() != fwd["last_ids"]).sum() <= 2
+    # loss and gradients
+    assert abs(float(r["loss"][0].item()) - r["loss_ref"]) < 1e-5
+    for name in ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw"):
+        a = r["grads"].tensor(name).cpu().numpy()
+        if a.size:
+            assert rel_l2(a, r["bwd"][name]) < 1e-3, name
+    # Adam on the oracle side with the oracle's gradients
+    tr = pkg.trainer
+    tr.adam_step_splats(r["model"], r["m"], r["v"], r["grads"], LRS, 1)
+    for gi, name in enumerate(("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")):
+        p = r["P"][name].copy().reshape(-1)
+        if p.size == 0:
+            continue
+        mm, vv = np.zeros_like(p), np.zeros_like(p)
+        orc.adam_step(p, mm, vv, r["grads"].tensor(name).cpu().numpy().reshape(-1), LRS[gi], 0.9, 0.999, 1e-15, 1)
+        assert np.allclose(r["model"].tensor(name).cpu().numpy().reshape(-1), p, rtol=1e-5, atol=1e-8), name
+
+
+def test_accumulate_and_row_range(pkg, orc, synth):
+    r = _run(pkg, orc, synth, 3000, 64, 48, 1, 21, np.zeros(3, np.float32))
+    tr = pkg.trainer
+    g1 = {k: t.clone() for k, t in r["grads"].tensors().items()}
+    r["rast"].backward(r["v_render"], r["grads"], r["tbg"], accumulate=True)
+    for k, t in r["grads"].tensors().items():
+        assert torch.allclose(t, 2 * g1[k], rtol=1e-6, atol=0)
+    # sharded Adam: two half ranges == one full range
+    a, b = r["model"], r["model"].like()
+    b.flat.copy_(a.flat)
+    ma, va, mb, vb = a.like(), a.like(), a.like(), a.like()
+    tr.adam_step_splats(a, ma, va, r["grads"], LRS, 3, grad_scale=0.5)
+    half = a.size // 2 + 1
+    tr.adam_step_splats(b, mb, vb, r["grads"], LRS, 3, first_row=0, n_rows=half, grad_scale=0.5)
+    tr.adam_step_splats(b, mb, vb, r["grads"], LRS, 3, first_row=half, n_rows=a.size - half, grad_scale=0.5)
+    assert torch.equal(a.flat, b.flat) and torch.equal(ma.flat, mb.flat) and torch.equal(va.flat, vb.flat)
+    # skip_shN leaves the shN group untouched
+    c = a.like(); c.flat.copy_(a.flat)
+    tr.adam_step_splats(c, ma, va, r["grads"], LRS, 4, skip_shN=True)
+    assert torch.equal(c.tensor("shN"), a.tensor("shN")) and not torch.equal(c.tensor("means"), a.tensor("means"))
+
+
+def test_isect_overflow_is_reported(pkg, orc, synth):
+    tr = pkg.trainer
+    cfg, P, vm, K = make_scene(synth, 4000, 96, 96, 0, seed=2)
+    model = tr.SplatData(4000, 1, DEV).load(P)
+    rast = tr.Rasterizer(model, 96, 96, 0, isect_capacity=100)
+    out = rast.forward(tr.Camera(T(vm), T(K), 96, 96), None)
+    torch.cuda.synchronize()
+    st = out.status.cpu().numpy()
+    assert st[0] == 1 and st[1] > 100
