@@ -1,0 +1,376 @@
+"""Benchmark of the Gaussian-splatting training step (forward + L1/SSIM loss + backward + fused Adam).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload `train_1m` (default, N = 1): 1,000,000 Gaussians, SH degree 3, one 1296x840 pinhole camera
+per step out of 200 hemisphere poses, loss 0.8 L1 + 0.2 (1 - SSIM), Adam with the per-group rates of
+the reference's MCMC strategy. N > 1: workload `dp_3m` (3,000,000 Gaussians, 1600x1064), one camera
+per GPU per step (weak scaling), gradients reduce-scattered over NCCL, Adam on each rank's shard,
+parameters all-gathered. Synthetic seeded inputs stand in for the Mip-NeRF-360 shapes.
+
+Rank 0 prints ONE JSON line. `value` is steps/s with every input resident in HBM; `e2e` is the same
+step driven from pinned host memory (target image + camera copied in, loss read back each step).
+`--impl reference` times the CPU oracle (the reference has no CPU implementation of this path and its
+CUDA sources need the glm library, which is not on the machine) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]  # means, sh0, shN, scaling, rotation, opacity
+METRIC = "train steps/s (fwd+loss+bwd+Adam)"
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------- CPU arm
+_SCENE_CACHE = {}
+
+
+def cpu_step_sample(workload: str, n_rows: int = 6, step: int = 0):
+    """One training step of the CPU oracle on a bounded sample: projection, SH, tile lists, loss, SH
+    backward and Adam in full; rasterizer forward / backward on `n_rows` full rows of tiles spread evenly
+    over the image height, their time scaled to the whole image. Returns (seconds for a full step,
+    description, threads)."""
+    from oracle import oracle as orc
+    synth = importlib.import_module("lichtfeld-studio_b200").synth
+    cfg = synth.CONFIGS[workload]
+    W, H, deg, n = cfg["W"], cfg["H"], cfg["sh_degree"], cfg["n"]
+    if workload not in _SCENE_CACHE:
+        _SCENE_CACHE[workload] = synth.make_gaussians(n, 0, cfg["layout"], deg)
+    P = {k: v.copy() for k, v in _SCENE_CACHE[workload].items()}
+    poses, K = synth.make_cameras(cfg)
+    vm = poses[synth.pose_index(step, cfg["n_poses"])]
+    bg = np.zeros(3, np.float32)
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    rows = sorted({int((k + 1) * th / (n_rows + 1)) for k in range(n_rows)})
+    t_start = time.perf_counter()
+    fwd = orc.render_fwd(P, vm, K, W, H, deg, background=bg, tile_range=(0, 0))  # everything but the rasterizer
+    t_front = time.perf_counter() - t_start
+    a = [P["means"], fwd["quats"], fwd["scales"], fwd["colors"], fwd["opac"]]
+    t_rf = 0.0
+    for r in rows:
+        t0 = time.perf_counter()
+        ren, alp, last, _ = orc.rasterize_fwd(*a, bg, W, H, 16, vm, K, fwd["tile_offsets"], fwd["flatten_ids"],
+                                              tile_range=(r * tw, (r + 1) * tw))
+        t_rf += time.perf_counter() - t0
+        y0, y1 = r * 16, min(H, (r + 1) * 16)
+        fwd["render"][y0:y1], fwd["alpha"][y0:y1], fwd["last_ids"][y0:y1] = ren[y0:y1], alp[y0:y1], last[y0:y1]
+    target = np.ascontiguousarray(np.clip(fwd["render"], 0, 1).transpose(2, 0, 1)) * np.float32(0.9)
+    t0 = time.perf_counter()
+    loss, g, _, _ = orc.photometric_loss(fwd["render"], target, 0.2)
+    t_loss = time.perf_counter() - t0
+    t_rb = 0.0
+    for r in rows:
+        t0 = time.perf_counter()
+        orc.rasterize_bwd(*a, bg, W, H, 16, vm, K, fwd["tile_offsets"], fwd["flatten_ids"], fwd["alpha"], fwd["last_ids"], g,
+                          np.zeros((H, W, 1), np.float32), tile_range=(r * tw, (r + 1) * tw))
+        t_rb += time.perf_counter() - t0
+    t0 = time.perf_counter()
+    bwd = orc.render_bwd(P, fwd, vm, K, W, H, deg, g, background=bg, tile_range=(0, 0))  # SH + activation backward
+    for gi, name in enumerate(("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")):
+        p = P[name].reshape(-1)
+        orc.adam_step(p, np.zeros_like(p), np.zeros_like(p), bwd[name].reshape(-1), LRS[gi], 0.9, 0.999, 1e-15, 1)
+    t_back = time.perf_counter() - t0
+    scale = th / len(rows)
+    full = t_front + t_loss + t_back + (t_rf + t_rb) * scale
+    desc = (f"{workload}: projection+SH+tile lists {t_front:.2f}s, loss {t_loss:.2f}s, SH/activation bwd+Adam {t_back:.2f}s in full; "
+            f"rasterizer fwd {t_rf:.2f}s + bwd {t_rb:.2f}s on tile rows {rows} of {th}, scaled by {scale:.1f}; "
+            f"sample wall time {time.perf_counter() - t_start:.1f}s")
+    return full, desc, orc.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = args.workload or ("train_1m" if args.gpus == 1 else "dp_3m")
+    times = []
+    for s in range(args.warmup + args.steps):
+        full, desc, threads = cpu_step_sample(workload, step=s)
+        if s >= args.warmup:
+            times.append(full)
+    sec = float(np.mean(times))
+    val = args.gpus / sec if args.gpus > 1 else 1.0 / sec
+    out = {"impl": "reference", "metric": METRIC, "value": val, "unit": "steps/s", "n_gpus": args.gpus, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "f32", "data": "synthetic", "config": {"workload": workload},
+           "cpu_baseline": {"value": val, "unit": "steps/s", "cores": threads, "kind": "port", "sample": desc},
+           "e2e": {"value": val, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "note": "CPU oracle (scalar C++ restatement, OpenMP over tiles / Gaussians): the reference has no CPU path and "
+                   "its CUDA sources need glm, which is not installed"}
+    print(json.dumps(out), flush=True)
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = importlib.import_module("lichtfeld-studio_b200")
+    synth, tr, capi = pkg.synth, pkg.trainer, pkg._capi
+    capi.lib()  # fails loudly if the CUDA library is missing
+
+    workload = args.workload or ("train_1m" if world == 1 else "dp_3m")
+    cfg = synth.CONFIGS[workload]
+    W, H, deg, n = cfg["W"], cfg["H"], cfg["sh_degree"], cfg["n"]
+    K_sh = (deg + 1) ** 2
+    P = synth.make_gaussians(n, 0, cfg["layout"], deg)
+    P_target = synth.make_gaussians(n, 1000, cfg["layout"], deg)
+    poses, Kmat = synth.make_cameras(cfg)
+    total_steps = args.warmup + args.steps
+
+    model = tr.SplatData(n, K_sh, dev).load(P)
+    held_out = tr.SplatData(n, K_sh, dev).load(P_target)
+    grads, m, v = model.like(), model.like(), model.like()
+    rast = tr.Rasterizer(model, W, H, deg, isect_capacity=max(12 * n, 1 << 22))
+    rast_t = tr.Rasterizer(held_out, W, H, deg, isect_capacity=max(12 * n, 1 << 22))
+    lossfn = tr.PhotometricLoss(W, H, dev)
+    bg = torch.zeros(3, device=dev)
+    Kt = torch.from_numpy(Kmat).to(dev)
+
+    # the camera of (step, rank) and its target, rendered from the held-out Gaussians with this library
+    def pose_of(step):
+        return poses[synth.pose_index(step * world + rank, cfg["n_poses"])]
+
+    n_e2e = min(args.steps, 10)
+    targets_dev, targets_host, vms_dev, vms_host = [], [], [], []
+    for s in range(max(total_steps, n_e2e)):
+        vm = torch.from_numpy(pose_of(s)).to(dev)
+        out = rast_t.forward(tr.Camera(vm, Kt, W, H), bg)
+        tgt = out.image.clamp(0, 1).permute(2, 0, 1).contiguous()
+        targets_dev.append(tgt)
+        vms_dev.append(vm)
+        if s < n_e2e:
+            targets_host.append(tgt.cpu().pin_memory())
+            vms_host.append(torch.from_numpy(pose_of(s)).pin_memory())
+    del rast_t, held_out
+    torch.cuda.synchronize()
+
+    flat_len = model.flat.numel()
+    shard = (flat_len + world - 1) // world
+    pad = shard * world - flat_len
+
+    def exchange_and_adam(step_count):
+        if world == 1:
+            tr.adam_step_splats(model, m, v, grads, LRS, step_count)
+            return
+        # gradients summed over cameras, mean over the batch folded into Adam's gradient read
+        dist.all_reduce(grads.flat)
+        tr.adam_step_splats(model, m, v, grads, LRS, step_count, grad_scale=1.0 / world)
+
+    def step(s, target, vm):
+        out = rast.forward(tr.Camera(vm, Kt, W, H), bg)
+        loss, v_render = lossfn(out.image, target)
+        rast.backward(v_render, grads, bg)
+        exchange_and_adam(s + 1)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------------------------
+    for s in range(args.warmup):
+        step(s, targets_dev[s], vms_dev[s])
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(args.warmup, total_steps):
+        step(s, targets_dev[s], vms_dev[s])
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    status = rast.status.cpu().numpy()
+
+    # ---- end to end from pinned host memory ---------------------------------------------------
+    tgt_buf = torch.empty_like(targets_dev[0])
+    vm_buf = torch.empty((4, 4), device=dev)
+    barrier()
+    e0.record()
+    for s in range(n_e2e):
+        tgt_buf.copy_(targets_host[s], non_blocking=True)
+        vm_buf.copy_(vms_host[s], non_blocking=True)
+        loss = step(total_steps + s, tgt_buf, vm_buf)
+        loss_host = loss.cpu()  # device -> host read of the step's result
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    ms_e2e /= n_e2e
+    h2d = targets_host[0].numel() * 4 + 64
+    d2h = loss_host.numel() * 4
+
+    # ---- per-kernel times (CUDA events inside the library), pair counts, rooflines --------------------
+    kernels, roofline, extra = {}, None, {}
+    if rank == 0:
+        capi.profile_enable(True)
+        n_prof = 3
+        for s in range(n_prof):
+            step(s, targets_dev[s], vms_dev[s])
+        torch.cuda.synchronize()
+        recs = capi.profile_collect()
+        capi.profile_enable(False)
+        for name, msv in recs:
+            kernels.setdefault(name, []).append(msv)
+        launches_per_step = len(recs) / n_prof
+        # launches inside one call that are not individually bracketed: scan = 3 kernels, sort = 3 per pass
+        per_step_kernels = {"exclusive_scan": 3, "radix_sort_depth": 12, "radix_sort_tile": 6}
+        gpu_launches_step = sum(per_step_kernels.get(k, 1) * len(vs) / n_prof for k, vs in kernels.items()) + 4
+        st = rast.state()
+        last, offs = st["last_ids"].long(), st["tile_offsets"].long()
+        tw = (W + 15) // 16
+        ys, xs = torch.meshgrid(torch.arange(H, device=dev), torch.arange(W, device=dev), indexing="ij")
+        tile = (ys // 16) * tw + xs // 16
+        start, end = offs[tile], offs[tile + 1]
+        q_b = int(torch.clamp(torch.minimum(last, end - 1) - start + 1, min=0).sum().item())
+        q_list = int((end - start).sum().item())
+        sm_clock = (clocks or {}).get("sm_mhz") or 1965.0
+        fp32_peak = 148 * 128 * 2 * sm_clock * 1e6 / 1e12
+        t_bwd = float(np.mean(kernels.get("raster_bwd", [float("nan")])))
+        t_fwd = float(np.mean(kernels.get("raster_fwd", [float("nan")])))
+        t_adam = float(np.mean(kernels.get("adam", [float("nan")])))
+        hbm_peak, peak_kind = load_peaks()
+        ach = 370.0 * q_b / (t_bwd * 1e-3) / 1e12
+        roofline = {"kernel": "raster_bwd_kernel", "bound": "fp32", "achieved": ach, "peak": fp32_peak, "unit": "TFLOP/s",
+                    "frac": ach / fp32_peak, "traffic": None,
+                    "note": f"370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms; peak = 148 SM x 128 lanes x 2 x "
+                            f"{sm_clock:.0f} MHz sampled under load (no tensor cores on this path)"}
+        adam_bytes = 28.0 * 59 * n if K_sh == 16 else 28.0 * model.row_floats * n
+        extra = {"roofline_adam": {"kernel": "adam_groups_kernel", "bound": "hbm", "achieved": adam_bytes / (t_adam * 1e-3) / 1e9,
+                                   "peak": hbm_peak, "unit": "GB/s", "frac": adam_bytes / (t_adam * 1e-3) / 1e9 / hbm_peak,
+                                   "traffic": None, "note": f"28 B x {model.row_floats} floats x {n} Gaussians, of {peak_kind}"},
+                 "roofline_raster_fwd": {"kernel": "raster_fwd_kernel", "bound": "fp32",
+                                         "achieved": 70.0 * q_list / (t_fwd * 1e-3) / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
+                                         "frac": 70.0 * q_list / (t_fwd * 1e-3) / 1e12 / fp32_peak,
+                                         "note": f"70 flop x {q_list} list entries x pixels (upper bound of pairs visited)"},
+                 "kernel_ms": {k: float(np.mean(vs)) for k, vs in kernels.items()},
+                 "n_isects": int(status[1]), "n_visible": int(status[2]), "pairs_bwd": q_b, "pairs_list": q_list,
+                 "gpix_per_s_fwd": W * H / (sum(float(np.mean(kernels[k])) for k in kernels if k in (
+                     "project_pack", "radix_sort_depth", "exclusive_scan", "emit_instances", "radix_sort_tile", "tile_offsets",
+                     "raster_fwd")) * 1e-3) / 1e9}
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            full, desc, threads = cpu_step_sample(workload)
+            cpu = {"value": 1.0 / full, "unit": "steps/s", "cores": threads, "kind": "port", "sample": desc}
+        out = {"metric": METRIC, "value": world * 1e3 / ms_per_step, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+               "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+               "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": world,
+                          "parallelism": f"dp{world}" if world > 1 else "single", "l2": "inputs larger than L2 "
+                          f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
+               "clocks": clocks, "e2e": {"value": world * 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
+                                         "d2h_bytes_per_step": d2h, "steps": n_e2e},
+               "gpu_launches": int(round(gpu_launches_step * args.steps)), "roofline": roofline, "cpu_baseline": cpu,
+               "gpix_per_s_step": world * W * H / (ms_per_step * 1e-3) / 1e9}
+        out.update(extra)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

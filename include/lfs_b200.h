@@ -52,6 +52,14 @@ const char* lfs_last_error(void);
 /* Library version and the SM architecture the kernels were compiled for ("sm_100a"). */
 const char* lfs_build_info(void);
 
+/* Opt-in per-kernel timing (the reference only has wall-clock ScopedTimer logging,
+ * include/core/logger.hpp:382-401). While enabled, every kernel launch of this library is bracketed by
+ * two CUDA events on its stream. lfs_profile_collect waits for the recorded events and returns up to
+ * max_records (name, milliseconds) pairs in launch order; lfs_profile_enable(0 or 1) clears the list.
+ * Not thread-safe; creates CUDA events, so leave it off in production and during graph capture. */
+int lfs_profile_enable(int on);
+int lfs_profile_collect(int max_records, const char** names, float* ms);
+
 /* ------------------------------------------------------------------------------------------ */
 /* Operator level (same inputs / outputs as the reference operators)                           */
 /* ------------------------------------------------------------------------------------------ */

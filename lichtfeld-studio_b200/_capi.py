@@ -80,7 +80,8 @@ _SIZE_FUNCS = {
     "lfs_photometric_loss_workspace_bytes": [i32, i32],
     "lfs_mcmc_workspace_bytes": [i32],
 }
-EXPORTED = sorted(list(_SIGNATURES) + list(_SIZE_FUNCS) + ["lfs_last_error", "lfs_build_info"])
+EXPORTED = sorted(list(_SIGNATURES) + list(_SIZE_FUNCS) + ["lfs_last_error", "lfs_build_info", "lfs_profile_enable",
+                                                          "lfs_profile_collect"])
 
 
 def lib():
@@ -107,6 +108,18 @@ def call(name: str, *args):
     rc = getattr(lib(), name)(*args)
     if rc != LFS_OK:
         raise LfsError(f"{name} failed ({rc}): {lib().lfs_last_error().decode()}")
+
+
+def profile_enable(on: bool):
+    lib().lfs_profile_enable(1 if on else 0)
+
+
+def profile_collect(max_records: int = 4096):
+    """[(kernel name, milliseconds)] in launch order since profile_enable(True)."""
+    names = (C.c_char_p * max_records)()
+    ms = (C.c_float * max_records)()
+    n = lib().lfs_profile_collect(max_records, names, ms)
+    return [(names[i].decode(), float(ms[i])) for i in range(n)]
 
 
 def ptr(t):

@@ -14,6 +14,19 @@ namespace lfs {
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 
+// Opt-in per-kernel timing (lfs_profile_enable): when on, a KernelTimer brackets a launch with two
+// CUDA events on the launching stream; lfs_profile_collect returns the elapsed times. Off by default
+// and free when off.
+struct KernelTimer {
+    KernelTimer(const char* name, cudaStream_t st);
+    ~KernelTimer();
+    const char* name_;
+    cudaStream_t st_;
+    void* a_;
+    void* b_;
+};
+#define LFS_TIMED(name, st) ::lfs::KernelTimer lfs_kernel_timer_(name, st)
+
 #define LFS_REQUIRE(cond, msg)                         \
     do {                                               \
         if (!(cond)) {                                 \

@@ -243,6 +243,7 @@ __global__ void __launch_bounds__(256) mcmc_copy_rows_kernel(int n, int64_t N, c
 int launch_adam_groups(const AdamGroups& G, cudaStream_t st) {
     const int64_t total4 = G.prefix4[G.n_groups];
     if (total4 == 0) return LFS_OK;
+    LFS_TIMED("adam", st);
     adam_groups_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(G);
     return check_launch("adam_groups");
 }

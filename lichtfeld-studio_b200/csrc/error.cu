@@ -1,6 +1,7 @@
 // Error bookkeeping for the C ABI.
 #include <cstdarg>
 #include <cstdio>
+#include <vector>
 
 #include "common.cuh"
 
@@ -25,5 +26,43 @@ int check_launch(const char* what) {
 }
 
 const char* last_error() { return g_err; }
+
+namespace {
+struct ProfRec { const char* name; cudaEvent_t a, b; };
+bool g_prof = false;
+std::vector<ProfRec> g_recs;
+}  // namespace
+
+KernelTimer::KernelTimer(const char* name, cudaStream_t st) : name_(name), st_(st), a_(nullptr), b_(nullptr) {
+    if (!g_prof) return;
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    cudaEventRecord(a, st);
+    a_ = a; b_ = b;
+}
+KernelTimer::~KernelTimer() {
+    if (!a_) return;
+    cudaEventRecord(reinterpret_cast<cudaEvent_t>(b_), st_);
+    g_recs.push_back(ProfRec{name_, reinterpret_cast<cudaEvent_t>(a_), reinterpret_cast<cudaEvent_t>(b_)});
+}
+
+void profile_enable(bool on) {
+    for (auto& r : g_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    g_recs.clear();
+    g_prof = on;
+}
+int profile_collect(int max_records, const char** names, float* ms) {
+    int n = 0;
+    for (auto& r : g_recs) {
+        if (n >= max_records) break;
+        if (cudaEventSynchronize(r.b) != cudaSuccess) break;
+        float t = 0.f;
+        cudaEventElapsedTime(&t, r.a, r.b);
+        names[n] = r.name;
+        ms[n] = t;
+        ++n;
+    }
+    return n;
+}
 
 }  // namespace lfs

@@ -238,11 +238,16 @@ int launch_photometric_loss(int H, int W, float lambda, float grad_scale, const 
     const float l1_grad = (float)((1.0 - (double)lambda) / n_all);
     cudaMemsetAsync(sums, 0, 2 * sizeof(double), st);
     dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    {
+    LFS_TIMED("loss_fwd", st);
     ssim_fwd_kernel<true><<<grid, block, 0, st>>>(3, H, W, (float)(0.01 * 0.01), (float)(0.03 * 0.03), render_hwc,
                                                   target_chw, nullptr, d1, d2, d3, map_grad, crop, sums);
-    if (v_render_hwc)
+    }
+    if (v_render_hwc) {
+        LFS_TIMED("loss_bwd", st);
         ssim_bwd_kernel<true><<<grid, block, 0, st>>>(3, H, W, render_hwc, target_chw, nullptr, d1, d2, d3, v_render_hwc,
                                                       l1_grad, grad_scale);
+    }
     loss_finalize_kernel<<<1, 1, 0, st>>>(sums, n_all, n_valid, lambda, loss_dev);
     return check_launch("photometric_loss");
 }

@@ -255,6 +255,7 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
     const int64_t total = (int64_t)C * N;
     if (total == 0) return LFS_OK;
     const int grid = grid_for(total, 256);
+    LFS_TIMED("projection_ut", st);
     if (model == LFS_PINHOLE)
         projection_ut_kernel<LFS_PINHOLE><<<grid, 256, 0, st>>>(C, N, means, quats, scales, opacities, viewmats, Ks, radial,
                                                                 W, H, pp, radii, means2d, depths, conics, compensations);
@@ -312,6 +313,7 @@ __global__ void __launch_bounds__(256) pack_records_kernel(
 int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
                         const float* opacities, const CamDev* cam, float4* records, float4* accum, cudaStream_t st) {
     if (N == 0) return LFS_OK;
+    LFS_TIMED("pack_records", st);
     pack_records_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, means, quats, scales, colors, opacities, cam, records, accum);
     return check_launch("pack_records");
 }
@@ -395,6 +397,7 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
                         int32_t* n_visible, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     const int grid = grid_for(N, 256);
+    LFS_TIMED("project_pack", st);
     if (model == LFS_PINHOLE)
         project_pack_kernel<LFS_PINHOLE><<<grid, 256, 0, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
                                                                p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,

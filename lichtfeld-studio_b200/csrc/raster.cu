@@ -452,6 +452,7 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
 int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, cudaStream_t st) {
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
+    LFS_TIMED("raster_fwd", st);
     if (a.model == LFS_PINHOLE)
         raster_fwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
@@ -467,6 +468,7 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
                       const float* v_alphas, float* accum, cudaStream_t st) {
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
+    LFS_TIMED("raster_bwd", st);
     if (a.model == LFS_PINHOLE)
         raster_bwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
@@ -484,6 +486,7 @@ int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const 
                             const float* scales, float* v_means, float* v_quats, float* v_scales, float* v_colors,
                             float* v_opacities, cudaStream_t st) {
     if (N == 0) return LFS_OK;
+    LFS_TIMED("grad_epilogue", st);
     grad_epilogue_op_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, cam, accum, means, quats, scales, v_means, v_quats,
                                                               v_scales, v_colors, v_opacities);
     return check_launch("grad_epilogue_op");
@@ -493,6 +496,7 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
                                int accumulate, cudaStream_t st) {
     if (N == 0) return LFS_OK;
+    LFS_TIMED("grad_epilogue", st);
     grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
                                                                  p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
                                                                  g.sh0, g.shN, g.scaling_raw, g.rotation_raw,

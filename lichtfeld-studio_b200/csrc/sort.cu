@@ -331,6 +331,7 @@ int exclusive_scan_gather(const int32_t* src, const uint32_t* idx, int64_t n, in
     int nb = (int)((n + kTile - 1) / kTile);
     if (nb > kScanBlocks) nb = kScanBlocks;
     const int64_t chunk = (n + nb - 1) / nb;
+    LFS_TIMED("exclusive_scan", st);
     scan_reduce_kernel<<<nb, kThreads, 0, st>>>(src, idx, n, chunk, s.block_sums);
     scan_block_sums_kernel<<<1, 1024, 0, st>>>(s.block_sums, nb, total_dev);
     scan_apply_kernel<<<nb, kThreads, 0, st>>>(src, idx, n, chunk, s.block_sums, out);
@@ -345,6 +346,7 @@ int radix_sort_pairs(uint32_t* keys[2], uint32_t* vals[2], const int32_t* n_dev,
     int nb = (int)((n_max + kTile - 1) / kTile);
     if (nb > kRadixBlocks) nb = kRadixBlocks;
     int cur = 0;
+    LFS_TIMED(key_bits == 32 ? "radix_sort_depth" : "radix_sort_tile", st);
     for (int p = 0; p < passes; ++p) {
         const int shift = p * bits;
         const int nbits = (shift + bits > key_bits) ? (key_bits - shift) : bits;
@@ -388,11 +390,13 @@ int build_tile_lists(const TileListArgs& a, cudaStream_t st) {
     }
     int rc = exclusive_scan_gather(a.tiles, order, total, a.offs, a.n_isects_dev, s, st);
     if (rc != LFS_OK) return rc;
-    if (total > 0)
+    if (total > 0) {
+        LFS_TIMED("emit_instances", st);
         emit_instances_kernel<<<grid_for(total, 256), 256, 0, st>>>(total, a.N, order, a.tiles, a.offs, a.means2d, a.radii,
                                                                     (float)a.tile_size, (uint32_t)a.tw, (uint32_t)a.th,
                                                                     tile_n_bits, a.capacity, a.tkeys[0], a.tvals[0],
                                                                     a.overflow);
+    }
     int sel = 0;
     if (a.sort && a.capacity > 0) {
         uint32_t* k[2] = {a.tkeys[0], a.tkeys[1]};
@@ -403,6 +407,7 @@ int build_tile_lists(const TileListArgs& a, cudaStream_t st) {
     if (a.sel_out) *a.sel_out = sel;
     if (a.tile_offsets) {
         const int64_t n_ids = (int64_t)a.C * n_tiles;
+        LFS_TIMED("tile_offsets", st);
         tile_offsets_kernel<<<grid_for(a.capacity > 0 ? a.capacity : 1, 256), 256, 0, st>>>(
             a.tkeys[sel], a.n_isects_dev, a.capacity, n_tiles, tile_n_bits, n_ids, a.tile_offsets);
     }

@@ -683,13 +683,15 @@ int64_t orc_rasterize_fwd(
     const float* background /*nullable [3]*/,
     int W, int H, int tile_size, const float* viewmat, const float* K, int camera_model, const float* radial,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
-    float* render_colors /*[H,W,3]*/, float* render_alphas /*[H,W]*/, int32_t* last_ids /*[H,W]*/) {
+    float* render_colors /*[H,W,3]*/, float* render_alphas /*[H,W]*/, int32_t* last_ids /*[H,W]*/,
+    int tile_lo, int tile_hi /* only tiles in [tile_lo, tile_hi) are rendered; pass 0, -1 for all */) {
     const int tw = (W + tile_size - 1) / tile_size, th = (H + tile_size - 1) / tile_size;
     const Pose pose = pose_from_viewmat(viewmat);
     const Camera cam = make_camera(camera_model, K, W, H, radial);
     int64_t n_pairs = 0;
+    if (tile_hi < 0) tile_hi = tw * th;
 #pragma omp parallel for schedule(dynamic, 1) reduction(+ : n_pairs)
-    for (int tile = 0; tile < tw * th; ++tile) {
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
         const int ty = tile / tw, tx = tile % tw;
         const int32_t range_start = tile_offsets[tile];
         const int32_t range_end = (tile == tw * th - 1) ? (int32_t)n_isects : tile_offsets[tile + 1];
@@ -754,7 +756,8 @@ int64_t orc_rasterize_bwd(
     int W, int H, int tile_size, const float* viewmat, const float* K, int camera_model, const float* radial,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
-    float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities) {
+    float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
+    int tile_lo, int tile_hi /* only tiles in [tile_lo, tile_hi) contribute; pass 0, -1 for all */) {
     const int tw = (W + tile_size - 1) / tile_size, th = (H + tile_size - 1) / tile_size;
     const Pose pose = pose_from_viewmat(viewmat);
     const Camera cam = make_camera(camera_model, K, W, H, radial);
@@ -764,8 +767,9 @@ int64_t orc_rasterize_bwd(
     // into per-thread buffers would reorder sums, so parallelism is over tiles with a merge in tile order.
     const int n_tiles = tw * th;
     std::vector<std::vector<std::pair<int, std::array<double, 14>>>> tile_out(n_tiles);
+    if (tile_hi < 0) tile_hi = n_tiles;
 #pragma omp parallel for schedule(dynamic, 1) reduction(+ : n_pairs)
-    for (int tile = 0; tile < n_tiles; ++tile) {
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
         const int ty = tile / tw, tx = tile % tw;
         const int32_t range_start = tile_offsets[tile];
         const int32_t range_end = (tile == n_tiles - 1) ? (int32_t)n_isects : tile_offsets[tile + 1];

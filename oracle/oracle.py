@@ -135,7 +135,7 @@ def intersect_offset(isect_ids, Cn, tw, th):
 
 
 def rasterize_fwd(means, quats, scales, colors, opacities, background, W, H, tile_size, viewmat, K,
-                  tile_offsets, flatten_ids, camera_model=PINHOLE, radial=None):
+                  tile_offsets, flatten_ids, camera_model=PINHOLE, radial=None, tile_range=(0, -1)):
     """One camera (the reference kernel supports C = 1 only). Returns render [H,W,3], alpha [H,W,1],
     last_ids [H,W] and the number of (pixel, entry) pairs visited."""
     a = [_f32(x) for x in (means, quats, scales, colors, opacities)]
@@ -148,13 +148,13 @@ def rasterize_fwd(means, quats, scales, colors, opacities, background, W, H, til
     npairs = lib().orc_rasterize_fwd(
         i32(a[0].shape[0]), i64(fl.size), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg),
         i32(W), i32(H), i32(tile_size), _p(_f32(viewmat)), _p(_f32(K)), i32(camera_model), _p(_f32(radial)),
-        _p(to), _p(fl), _p(render), _p(alpha), _p(last))
+        _p(to), _p(fl), _p(render), _p(alpha), _p(last), i32(tile_range[0]), i32(tile_range[1]))
     return render, alpha, last, int(npairs)
 
 
 def rasterize_bwd(means, quats, scales, colors, opacities, background, W, H, tile_size, viewmat, K,
                   tile_offsets, flatten_ids, render_alphas, last_ids, v_render_colors, v_render_alphas,
-                  camera_model=PINHOLE, radial=None):
+                  camera_model=PINHOLE, radial=None, tile_range=(0, -1)):
     a = [_f32(x) for x in (means, quats, scales, colors, opacities)]
     N = a[0].shape[0]
     bg = _f32(background)
@@ -170,7 +170,7 @@ def rasterize_bwd(means, quats, scales, colors, opacities, background, W, H, til
         i32(W), i32(H), i32(tile_size), _p(_f32(viewmat)), _p(_f32(K)), i32(camera_model), _p(_f32(radial)),
         _p(to), _p(fl), _p(_f32(render_alphas)), _p(np.ascontiguousarray(last_ids, np.int32)),
         _p(_f32(v_render_colors)), _p(_f32(v_render_alphas)),
-        _p(v_means), _p(v_quats), _p(v_scales), _p(v_colors), _p(v_opac))
+        _p(v_means), _p(v_quats), _p(v_scales), _p(v_colors), _p(v_opac), i32(tile_range[0]), i32(tile_range[1]))
     return v_means, v_quats, v_scales, v_colors, v_opac, int(npairs)
 
 
@@ -271,7 +271,7 @@ def act_quat(raw):
 
 # ------------------------------------------------------------------ orchestration
 def render_fwd(params, viewmat, K, W, H, sh_degree, background=None, camera_model=PINHOLE, radial=None,
-               tile_size=16, eps2d=0.3, near=0.01, far=1e4):
+               tile_size=16, eps2d=0.3, near=0.01, far=1e4, tile_range=(0, -1)):
     """gsplat::rasterize_from_world_with_sh_fwd for one camera on raw SplatData parameters.
     params: dict(means, sh0, shN, scaling_raw, rotation_raw, opacity_raw)."""
     means = _f32(params["means"])
@@ -294,7 +294,7 @@ def render_fwd(params, viewmat, K, W, H, sh_degree, background=None, camera_mode
     tpg, ids, flat = intersect_tile(means2d, radii, depths, 1, tile_size, tw, th, True)
     offs = intersect_offset(ids, 1, tw, th)
     render, alpha, last, npairs = rasterize_fwd(means, quats, scales, colors, opac, background, W, H, tile_size,
-                                                vm[0], Kc[0], offs[0], flat, camera_model, rc)
+                                                vm[0], Kc[0], offs[0], flat, camera_model, rc, tile_range)
     return dict(render=render, alpha=alpha, last_ids=last, radii=radii[0], means2d=means2d[0], depths=depths[0],
                 colors=colors, tile_offsets=offs[0], flatten_ids=flat, isect_ids=ids, tiles_per_gauss=tpg[0],
                 masks=masks, dirs=dirs, opac=opac, scales=scales, quats=quats, qnorm=qnorm, sh=sh,
@@ -302,7 +302,7 @@ def render_fwd(params, viewmat, K, W, H, sh_degree, background=None, camera_mode
 
 
 def render_bwd(params, fwd, viewmat, K, W, H, sh_degree, v_render, v_alpha=None, background=None,
-               camera_model=PINHOLE, radial=None, tile_size=16):
+               camera_model=PINHOLE, radial=None, tile_size=16, tile_range=(0, -1)):
     """gsplat::rasterize_from_world_with_sh_bwd followed by the activation backward; returns
     gradients w.r.t. the six raw parameter tensors."""
     means = _f32(params["means"])
@@ -312,7 +312,7 @@ def render_bwd(params, fwd, viewmat, K, W, H, sh_degree, v_render, v_alpha=None,
     v_means, v_quats, v_scales, v_colors, v_opac, npairs = rasterize_bwd(
         means, fwd["quats"], fwd["scales"], fwd["colors"], fwd["opac"], background, W, H, tile_size,
         viewmat, K, fwd["tile_offsets"], fwd["flatten_ids"], fwd["alpha"], fwd["last_ids"], v_render, v_alpha,
-        camera_model, rc)
+        camera_model, rc, tile_range)
     v_pre = v_colors.copy()
     v_pre[fwd["colors"] <= 0.0] = 0.0
     K_sh = fwd["sh"].shape[1]
