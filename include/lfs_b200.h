@@ -239,12 +239,13 @@ int lfs_photometric_loss(int H, int W, float lambda_dssim, float grad_scale, con
 /* FusedAdam::step over all six groups in one launch (src/training/optimizers/fused_adam.cpp:22-95,
  * group order and learning rates of src/training/strategies/mcmc.cpp:487-492). lr[6] host values in
  * group order means, sh0, shN, scaling, rotation, opacity; step_count >= 1 is the optimizer step
- * index (bias corrections in double on the host); skip_shN != 0 reproduces the `iteration <= 1000`
+ * index (beta1 / beta2 are doubles because the reference computes the bias corrections from the double
+ * option values before narrowing, fused_adam.cpp:78-79); skip_shN != 0 reproduces the `iteration <= 1000`
  * skip. first_row/n_rows select a contiguous Gaussian range (optimizer-state sharding).
  * grad_scale multiplies the gradient on read. */
 int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const lfs_splats* exp_avg,
                          const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr,
-                         float beta1, float beta2, float eps, int64_t step_count, int skip_shN,
+                         double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
                          int64_t first_row, int64_t n_rows, float grad_scale, void* stream);
 
 /* ------------------------------------------------------------------------------------------ */

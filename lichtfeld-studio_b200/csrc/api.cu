@@ -317,14 +317,14 @@ int lfs_adam_step(float* param, float* exp_avg, float* exp_avg_sq, const float* 
 }
 
 int lfs_adam_step_splats(int N, int K, const lfs_splats* params, const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq,
-                         const lfs_splats* grads, const float* lr, float beta1, float beta2, float eps, int64_t step_count,
+                         const lfs_splats* grads, const float* lr, double beta1, double beta2, double eps, int64_t step_count,
                          int skip_shN, int64_t first_row, int64_t n_rows, float grad_scale, void* stream) {
     LFS_REQUIRE(params && exp_avg && exp_avg_sq && grads && lr, "null pointer");
     LFS_REQUIRE(N >= 0 && K >= 1 && step_count >= 1, "bad sizes");
     LFS_REQUIRE(first_row >= 0 && n_rows >= 0 && first_row + n_rows <= N, "row range outside [0, N)");
     if (n_rows == 0) return LFS_OK;
-    const double bc1 = 1.0 / (1.0 - std::pow((double)beta1, (double)step_count));
-    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow((double)beta2, (double)step_count));
+    const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
     float* P[6] = {params->means, params->sh0, params->shN, params->scaling_raw, params->rotation_raw, params->opacity_raw};
     float* M[6] = {exp_avg->means, exp_avg->sh0, exp_avg->shN, exp_avg->scaling_raw, exp_avg->rotation_raw, exp_avg->opacity_raw};
     float* V[6] = {exp_avg_sq->means, exp_avg_sq->sh0, exp_avg_sq->shN, exp_avg_sq->scaling_raw, exp_avg_sq->rotation_raw, exp_avg_sq->opacity_raw};
@@ -345,7 +345,7 @@ int lfs_adam_step_splats(int N, int K, const lfs_splats* params, const lfs_splat
         ++ng;
     }
     G.n_groups = ng;
-    G.beta1 = beta1; G.beta2 = beta2; G.eps = eps; G.bc2_sqrt_rcp = (float)bc2; G.grad_scale = grad_scale;
+    G.beta1 = (float)beta1; G.beta2 = (float)beta2; G.eps = (float)eps; G.bc2_sqrt_rcp = (float)bc2; G.grad_scale = grad_scale;
     return launch_adam_groups(G, S(stream));
 }
 
