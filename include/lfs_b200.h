@@ -254,11 +254,14 @@ int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const l
 
 /* mcmc.cpp:121-131: dead = sigmoid(opacity_raw) <= min_opacity | |rotation_raw|^2 < 1e-8.
  * Writes ascending dead_indices / alive_indices (int64, capacity N each), alive_opacities (the
- * probabilities handed to multinomial) and counts_dev (device int32[2]: n_dead, n_alive). */
+ * probabilities handed to multinomial, float32 1/(1+exp(-x)) like torch::sigmoid) and counts_dev (device int32[2]: n_dead, n_alive). */
 size_t lfs_mcmc_workspace_bytes(int N);
 int lfs_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity,
                       int64_t* dead_indices, int64_t* alive_indices, float* alive_opacities,
                       int32_t* counts_dev, void* workspace, size_t workspace_bytes, void* stream);
+
+/* mcmc.cpp:137: sampled = alive_indices.index_select(0, sampled_local): out[i] = index_map[local_indices[i]]. */
+int lfs_mcmc_map_indices(int n, const int64_t* local_indices, const int64_t* index_map, int64_t* out, void* stream);
 
 /* mcmc.cpp:139-150 / :221-228: ratios[i] = clamp(1 + #occurrences of sampled[i] in sampled, 1, n_max),
  * plus the gathered activated opacity / scale of each sampled Gaussian. counts is an int32[N] scratch. */

@@ -19,6 +19,8 @@ int profile_collect(int max_records, const char** names, float* ms);
 
 namespace {
 
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 struct Carver {
@@ -47,7 +49,7 @@ int sorted_sel(int key_bits) { return ((key_bits + 7) / 8) & 1; }
 SortScratch carve_scratch(Carver& c) {
     SortScratch s;
     s.hist = c.take<uint32_t>((size_t)kRadixBlocks * 256);
-    s.block_sums = c.take<uint32_t>(kScanBlocks + 64);
+    s.block_sums = c.take<uint32_t>(kScanBlocks + 320);  // also holds the 256 digit totals of a radix pass
     return s;
 }
 
@@ -121,6 +123,7 @@ int lfs_projection_ut_3dgs_fused(int C, int N, const float* means, const float* 
     LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
     if ((int64_t)C * N == 0) return LFS_OK;
     LFS_REQUIRE(means && quats && scales && viewmats0 && Ks && radii && means2d && depths && conics, "null pointer");
+    LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
     return launch_projection_ut(C, N, means, quats, scales, opacities, viewmats0, Ks, radial_coeffs, W, H,
                                 make_proj_params(eps2d, near_plane, far_plane, radius_clip, ut), camera_model, radii,
                                 means2d, depths, conics, compensations, S(stream));
@@ -227,6 +230,7 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, const f
     int rc = raster_common(N, n_isects, W, H, tile_size, camera_model, workspace, workspace_bytes);
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(viewmat0 && K && tile_offsets && renders && alphas && last_ids, "null pointer");
+    LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
     Carver c(workspace);
     CamDev* cam = c.take<CamDev>(1);
     float4* records = c.take<float4>((size_t)N * 4);
@@ -252,6 +256,7 @@ int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, const f
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(viewmat0 && K && tile_offsets && render_alphas && last_ids && v_render_colors, "null pointer");
     LFS_REQUIRE(v_means && v_quats && v_scales && v_colors && v_opacities, "null output pointer");
+    LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
     Carver c(workspace);
     CamDev* cam = c.take<CamDev>(1);
     float4* records = c.take<float4>((size_t)N * 4);
@@ -299,7 +304,6 @@ int lfs_photometric_loss(int H, int W, float lambda_dssim, float grad_scale, con
 }
 
 // ---------------------------------------------------------------------------------------------
-static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int lfs_adam_step(float* param, float* exp_avg, float* exp_avg_sq, const float* grad, int64_t n, float lr, float beta1,
                   float beta2, float eps, float bc1_rcp, float bc2_sqrt_rcp, void* stream) {
@@ -362,6 +366,7 @@ int lfs_add_noise(int n, const float* raw_opacities, const float* raw_scales, co
     LFS_REQUIRE(n >= 0, "bad size");
     if (n == 0) return LFS_OK;
     LFS_REQUIRE(raw_opacities && raw_scales && raw_quats && noise && means, "null pointer");
+    LFS_REQUIRE(aligned16(raw_quats), "raw_quats must be 16-byte aligned");
     return launch_add_noise(n, raw_opacities, raw_scales, raw_quats, noise, means, current_lr, S(stream));
 }
 
@@ -369,6 +374,7 @@ int lfs_quats_to_rotmats(int n, const float* quats, float* rotmats, void* stream
     LFS_REQUIRE(n >= 0, "bad size");
     if (n == 0) return LFS_OK;
     LFS_REQUIRE(quats && rotmats, "null pointer");
+    LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
     return launch_quats_to_rotmats(n, quats, rotmats, S(stream));
 }
 
@@ -384,6 +390,7 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     int rc = check_cfg(cfg);
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(params && viewmat && K && render && alpha && workspace, "null pointer");
+    LFS_REQUIRE(aligned16(params->rotation_raw), "rotation_raw must be 16-byte aligned");
     RenderWs w = carve_render(*cfg, workspace);
     if (workspace_bytes < w.bytes) { set_error("lfs_render_forward: workspace too small (%zu < %zu)", workspace_bytes, w.bytes); return LFS_ECAPACITY; }
     cudaStream_t st = S(stream);
@@ -420,6 +427,7 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
     int rc = check_cfg(cfg);
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(params && alpha && v_render && grads && workspace, "null pointer");
+    LFS_REQUIRE(aligned16(params->rotation_raw) && aligned16(grads->rotation_raw), "rotation_raw tensors must be 16-byte aligned");
     RenderWs w = carve_render(*cfg, workspace);
     if (workspace_bytes < w.bytes) { set_error("lfs_render_backward: workspace too small"); return LFS_ECAPACITY; }
     cudaStream_t st = S(stream);
@@ -469,11 +477,19 @@ int lfs_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw
     LFS_REQUIRE(N >= 0, "bad size");
     LFS_REQUIRE(counts_dev && workspace, "null pointer");
     if (N > 0) LFS_REQUIRE(opacity_raw && rotation_raw && dead_indices && alive_indices && alive_opacities, "null pointer");
+    LFS_REQUIRE(aligned16(rotation_raw), "rotation_raw must be 16-byte aligned");
     int32_t *flags, *offs, *total;
     SortScratch s;
     if (workspace_bytes < mcmc_ws(N, workspace, &flags, &offs, &total, &s)) { set_error("lfs_mcmc_classify: workspace too small"); return LFS_ECAPACITY; }
     return launch_mcmc_classify(N, opacity_raw, rotation_raw, min_opacity, dead_indices, alive_indices, alive_opacities,
                                 counts_dev, flags, offs, total, s, S(stream));
+}
+
+int lfs_mcmc_map_indices(int n, const int64_t* local_indices, const int64_t* index_map, int64_t* out, void* stream) {
+    LFS_REQUIRE(n >= 0, "bad size");
+    if (n == 0) return LFS_OK;
+    LFS_REQUIRE(local_indices && index_map && out, "null pointer");
+    return launch_mcmc_map_indices(n, local_indices, index_map, out, S(stream));
 }
 
 int lfs_mcmc_gather_ratios(int N, int n_sampled, const int64_t* sampled, const float* opacity_raw, const float* scaling_raw,

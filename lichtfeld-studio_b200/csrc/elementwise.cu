@@ -153,7 +153,9 @@ __global__ void __launch_bounds__(256) quats_to_rotmats_kernel(int n, const floa
     }
 }
 
-__device__ __forceinline__ float sigmoid_d(float x) { return (float)(1.0 / (1.0 + exp(-(double)x))); }
+// float32 sigmoid / exp exactly as ATen evaluates them (1 / (1 + exp(-x)) in float): the MCMC sampling
+// probabilities and the dead mask must be the values torch::sigmoid gives, or multinomial draws differ.
+__device__ __forceinline__ float sigmoid_d(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 __global__ void __launch_bounds__(256) mcmc_flags_kernel(int N, const float* __restrict__ opacity_raw, const float* __restrict__ rotation_raw,
                                                          float min_opacity, int32_t* __restrict__ flags) {
@@ -181,6 +183,11 @@ __global__ void __launch_bounds__(256) mcmc_compact_kernel(int N, const int32_t*
     }
 }
 
+__global__ void __launch_bounds__(256) mcmc_map_indices_kernel(int n, const int64_t* __restrict__ local, const int64_t* __restrict__ map,
+                                                               int64_t* __restrict__ out) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = map[local[i]];
+}
+
 __global__ void __launch_bounds__(256) mcmc_count_kernel(int n, const int64_t* __restrict__ sampled, int32_t* __restrict__ counts) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) atomicAdd(&counts[sampled[i]], 1);
 }
@@ -194,7 +201,7 @@ __global__ void __launch_bounds__(256) mcmc_gather_kernel(int n, const int64_t* 
         ratios[i] = max(1, min(1 + counts[g], n_max));
         s_opac[i] = sigmoid_d(opacity_raw[g]);
 #pragma unroll
-        for (int k = 0; k < 3; ++k) s_scales[i * 3 + k] = (float)exp((double)scaling_raw[g * 3 + k]);
+        for (int k = 0; k < 3; ++k) s_scales[i * 3 + k] = expf(scaling_raw[g * 3 + k]);
     }
 }
 
@@ -286,6 +293,12 @@ int launch_mcmc_classify(int N, const float* opacity_raw, const float* rotation_
     mcmc_compact_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, flags, offs, total_dev, opacity_raw, dead_indices, alive_indices,
                                                           alive_opacities, counts_dev);
     return check_launch("mcmc_classify");
+}
+
+int launch_mcmc_map_indices(int n, const int64_t* local, const int64_t* map, int64_t* out, cudaStream_t st) {
+    if (n == 0) return LFS_OK;
+    mcmc_map_indices_kernel<<<grid_for(n, 256), 256, 0, st>>>(n, local, map, out);
+    return check_launch("mcmc_map_indices");
 }
 
 int launch_mcmc_gather_ratios(int N, int n, const int64_t* sampled, const float* opacity_raw, const float* scaling_raw, int n_max,

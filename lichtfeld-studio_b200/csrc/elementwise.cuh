@@ -29,6 +29,7 @@ int launch_quats_to_rotmats(int n, const float* quats, float* rotmats, cudaStrea
 int launch_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity, int64_t* dead_indices,
                          int64_t* alive_indices, float* alive_opacities, int32_t* counts_dev, int32_t* flags, int32_t* offs,
                          int32_t* total_dev, const SortScratch& s, cudaStream_t st);
+int launch_mcmc_map_indices(int n, const int64_t* local, const int64_t* map, int64_t* out, cudaStream_t st);
 int launch_mcmc_gather_ratios(int N, int n, const int64_t* sampled, const float* opacity_raw, const float* scaling_raw, int n_max,
                               int32_t* counts, int32_t* ratios, float* s_opac, float* s_scales, cudaStream_t st);
 int launch_mcmc_apply(int N, int K, int n, const int64_t* sampled, const int64_t* dst_indices, const float* new_opac,

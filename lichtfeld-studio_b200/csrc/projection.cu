@@ -332,63 +332,88 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
     int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths,
     int32_t* __restrict__ tiles, uint32_t* __restrict__ sort_keys, uint32_t* __restrict__ sort_vals,
     float4* __restrict__ records, float4* __restrict__ accum, int32_t* __restrict__ n_visible) {
+    // Each warp handles 32 consecutive Gaussians per iteration. Their higher-order SH rows ((K-1)*3 floats
+    // each, contiguous in memory) are fetched as one coalesced run into shared memory when any of the 32
+    // is visible, and every visible lane then reads its own row from there.
+    extern __shared__ float s_rows[];
     const CamDev cam = cams[0];
+    const int rest = (K - 1) * 3;
+    const int nb = (sh_degree + 1) * (sh_degree + 1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my = s_rows + (size_t)warp * 32 * rest;
+    const int n_chunks = (N + 31) / 32;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
     int local_visible = 0;
-    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
-        const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
-        // activations: sigmoid / exp through double, rounded once; F.normalize-style quaternion
-        const float opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
-        const f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
-                       (float)exp((double)scaling_raw[g * 3 + 2])};
-        const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
-        const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
-        const float nrm = fmaxf(sqrtf(n2), 1e-12f);
-        const float qw = qr.x / nrm, qx = qr.y / nrm, qy = qr.z / nrm, qz = qr.w / nrm;
-
+    for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
+        const int g = chunk * 32 + lane;
+        const bool in_range = g < N;
+        bool vis = false;
         ProjOut o;
-        const bool vis = project_gaussian<MODEL>(cam, pp, mean, qw, qx, qy, qz, scale, true, opacity, o);
-        sort_vals[g] = (uint32_t)g;
-        if (!vis) {
-            radii[g * 2] = 0; radii[g * 2 + 1] = 0;
-            tiles[g] = 0;
-            sort_keys[g] = 0xFFFFFFFFu;
-            continue;
+        f3 mean{0.f, 0.f, 0.f}, scale{1.f, 1.f, 1.f};
+        float opacity = 0.f, qw = 1.f, qx = 0.f, qy = 0.f, qz = 0.f;
+        if (in_range) {
+            mean = f3{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
+            // activations: sigmoid / exp through double, rounded once; F.normalize-style quaternion
+            opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
+            scale = f3{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
+                       (float)exp((double)scaling_raw[g * 3 + 2])};
+            const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
+            const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
+            const float nrm = fmaxf(sqrtf(n2), 1e-12f);
+            qw = qr.x / nrm; qx = qr.y / nrm; qy = qr.z / nrm; qz = qr.w / nrm;
+            vis = project_gaussian<MODEL>(cam, pp, mean, qw, qx, qy, qz, scale, true, opacity, o);
+            sort_vals[g] = (uint32_t)g;
+            if (!vis) {
+                radii[g * 2] = 0; radii[g * 2 + 1] = 0;
+                tiles[g] = 0;
+                sort_keys[g] = 0xFFFFFFFFu;
+            }
         }
-        radii[g * 2] = o.rx; radii[g * 2 + 1] = o.ry;
-        means2d[g * 2] = o.mx; means2d[g * 2 + 1] = o.my;
-        depths[g] = o.depth;
-        uint32_t x0, y0, x1, y1;
-        tile_rect(o.mx, o.my, o.rx, o.ry, tile_size, tw, th, x0, y0, x1, y1);
-        const int nt = (int)((y1 - y0) * (x1 - x0));
-        tiles[g] = nt;
-        sort_keys[g] = nt > 0 ? __float_as_uint(o.depth) : 0xFFFFFFFFu;
-        ++local_visible;
-
-        // colour from SH along (mean - camera position)
-        float B[25];
-        sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
-        float rgb[3];
-        const int nb = (sh_degree + 1) * (sh_degree + 1);
-#pragma unroll
-        for (int c = 0; c < 3; ++c) rgb[c] = B[0] * sh0[g * 3 + c];
-        const float* rest = shN + (size_t)g * (K - 1) * 3;
-        for (int k = 1; k < nb; ++k) {
-#pragma unroll
-            for (int c = 0; c < 3; ++c) rgb[c] += B[k] * rest[(k - 1) * 3 + c];
+        const bool any_vis = __any_sync(0xffffffffu, vis);
+        if (any_vis && nb > 1) {
+            const int n_rows = min(32, N - chunk * 32);
+            const int total = n_rows * rest;
+            const float* src = shN + (size_t)chunk * 32 * rest;
+            for (int i = lane; i < total; i += 32) my[i] = src[i];
         }
-#pragma unroll
-        for (int c = 0; c < 3; ++c) rgb[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
+        __syncwarp();
+        if (vis) {
+            radii[g * 2] = o.rx; radii[g * 2 + 1] = o.ry;
+            means2d[g * 2] = o.mx; means2d[g * 2 + 1] = o.my;
+            depths[g] = o.depth;
+            uint32_t x0, y0, x1, y1;
+            tile_rect(o.mx, o.my, o.rx, o.ry, tile_size, tw, th, x0, y0, x1, y1);
+            const int nt = (int)((y1 - y0) * (x1 - x0));
+            tiles[g] = nt;
+            sort_keys[g] = nt > 0 ? __float_as_uint(o.depth) : 0xFFFFFFFFu;
+            ++local_visible;
 
-        float4 rec[4];
-        make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, rec);
+            // colour from SH along (mean - camera position)
+            float B[25];
+            sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
+            float rgb[3];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
+            for (int c = 0; c < 3; ++c) rgb[c] = B[0] * sh0[g * 3 + c];
+            const float* row = my + lane * rest;
+            for (int k = 1; k < nb; ++k) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) accum[(size_t)g * 4 + k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int c = 0; c < 3; ++c) rgb[c] += B[k] * row[(k - 1) * 3 + c];
+            }
+#pragma unroll
+            for (int c = 0; c < 3; ++c) rgb[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
+
+            float4 rec[4];
+            make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, rec);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) accum[(size_t)g * 4 + k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncwarp();
     }
     // visible count (statistics only)
     local_visible = __reduce_add_sync(0xffffffffu, local_visible);
-    if ((threadIdx.x & 31) == 0 && local_visible) atomicAdd(n_visible, local_visible);
+    if (lane == 0 && local_visible) atomicAdd(n_visible, local_visible);
 }
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
@@ -397,14 +422,20 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
                         int32_t* n_visible, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     const int grid = grid_for(N, 256);
+    const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
+    if (smem > 200 * 1024) { set_error("project_pack: too many SH coefficients"); return LFS_EINVAL; }
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(project_pack_kernel<LFS_PINHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(project_pack_kernel<LFS_FISHEYE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     LFS_TIMED("project_pack", st);
     if (model == LFS_PINHOLE)
-        project_pack_kernel<LFS_PINHOLE><<<grid, 256, 0, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
+        project_pack_kernel<LFS_PINHOLE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
                                                                p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,
                                                                tw, th, radii, means2d, depths, tiles, sort_keys,
                                                                sort_vals, records, accum, n_visible);
     else
-        project_pack_kernel<LFS_FISHEYE><<<grid, 256, 0, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
+        project_pack_kernel<LFS_FISHEYE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
                                                                p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,
                                                                tw, th, radii, means2d, depths, tiles, sort_keys,
                                                                sort_vals, records, accum, n_visible);

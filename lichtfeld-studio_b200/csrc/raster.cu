@@ -371,6 +371,8 @@ __global__ void __launch_bounds__(256) grad_epilogue_op_kernel(
 }
 
 // Fused-path epilogue: raw-parameter gradients (activation backward folded in) and the SH backward.
+// Each warp handles 32 consecutive Gaussians per iteration; their shN gradient rows (the bulk of the
+// output, (K-1)*3 floats each) are staged in shared memory and written as one contiguous run.
 __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
     int N, int K, int sh_degree, const CamDev* __restrict__ cams, const float* __restrict__ accum,
     const float4* __restrict__ records, const int32_t* __restrict__ radii,
@@ -378,71 +380,86 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
     const float* __restrict__ opacity_raw,
     float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN, float* __restrict__ g_scaling,
     float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate) {
+    extern __shared__ float s_rows[];
     const CamDev& cam = cams[0];
     const int rest = (K - 1) * 3;
     const int nb = (sh_degree + 1) * (sh_degree + 1);
-    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
-        const bool visible = radii[g * 2] > 0 && radii[g * 2 + 1] > 0;
-        if (!visible) {
-            if (!accumulate) {
-#pragma unroll
-                for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] = 0.f; g_sh0[g * 3 + k] = 0.f; g_scaling[g * 3 + k] = 0.f; }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] = 0.f;
-                g_opacity[g] = 0.f;
-                float* dst = g_shN + (size_t)g * rest;
-                for (int k = 0; k < rest; ++k) dst[k] = 0.f;
-            }
-            continue;
-        }
-        float acc[16];
-        const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { const float4 t = a4[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
-        const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
-        const float opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
-        const f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
-                       (float)exp((double)scaling_raw[g * 3 + 2])};
-        const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
-        const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
-        const float nrm = fmaxf(sqrtf(n2), 1e-12f);
-        const float q[4] = {qr.x / nrm, qr.y / nrm, qr.z / nrm, qr.w / nrm};
-        GaussGrad o;
-        gaussian_vjp(cam, acc, mean, q[0], q[1], q[2], q[3], scale, o);
-        // activation backward: sigmoid, exp, x / max(|x|, eps)
-        const float go = o.v_opac * (opacity * (1.0f - opacity));
-        const float gs[3] = {o.v_scale[0] * scale.x, o.v_scale[1] * scale.y, o.v_scale[2] * scale.z};
-        const float dq = o.v_quat[0] * q[0] + o.v_quat[1] * q[1] + o.v_quat[2] * q[2] + o.v_quat[3] * q[3];
-        float gq[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) gq[k] = (o.v_quat[k] - q[k] * dq) / nrm;
-        // colour clamp mask, then SH backward
-        const float4 r3 = records[(size_t)g * 4 + 3];
-        float vc[3] = {o.v_rgb[0], o.v_rgb[1], o.v_rgb[2]};
-        if (r3.x <= 0.f) vc[0] = 0.f;
-        if (r3.y <= 0.f) vc[1] = 0.f;
-        if (r3.z <= 0.f) vc[2] = 0.f;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my = s_rows + (size_t)warp * 32 * rest;
+    const int n_chunks = (N + 31) / 32;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
+        const int g = chunk * 32 + lane;
+        const bool in_range = g < N;
+        const bool visible = in_range && radii[g * 2] > 0 && radii[g * 2 + 1] > 0;
+        float gm[3] = {0.f, 0.f, 0.f}, g0[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, go = 0.f;
+        float vc[3] = {0.f, 0.f, 0.f};
         float B[25];
-        sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
-        float* dst = g_shN + (size_t)g * rest;
-        if (accumulate) {
 #pragma unroll
-            for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] += o.v_mean[k]; g_sh0[g * 3 + k] += B[0] * vc[k]; g_scaling[g * 3 + k] += gs[k]; }
+        for (int k = 0; k < 25; ++k) B[k] = 0.f;
+        if (visible) {
+            float acc[16];
+            const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] += gq[k];
-            g_opacity[g] += go;
-            for (int k = 1; k < nb; ++k)
+            for (int k = 0; k < 4; ++k) { const float4 t = a4[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
+            const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
+            const float opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
+            const f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
+                           (float)exp((double)scaling_raw[g * 3 + 2])};
+            const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
+            const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
+            const float nrm = fmaxf(sqrtf(n2), 1e-12f);
+            const float q[4] = {qr.x / nrm, qr.y / nrm, qr.z / nrm, qr.w / nrm};
+            GaussGrad o;
+            gaussian_vjp(cam, acc, mean, q[0], q[1], q[2], q[3], scale, o);
+            // activation backward: sigmoid, exp, x / max(|x|, eps)
+            go = o.v_opac * (opacity * (1.0f - opacity));
+            gs[0] = o.v_scale[0] * scale.x; gs[1] = o.v_scale[1] * scale.y; gs[2] = o.v_scale[2] * scale.z;
+            const float dq = o.v_quat[0] * q[0] + o.v_quat[1] * q[1] + o.v_quat[2] * q[2] + o.v_quat[3] * q[3];
 #pragma unroll
-                for (int c = 0; c < 3; ++c) dst[(k - 1) * 3 + c] += B[k] * vc[c];
-        } else {
+            for (int k = 0; k < 4; ++k) gq[k] = (o.v_quat[k] - q[k] * dq) / nrm;
 #pragma unroll
-            for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] = o.v_mean[k]; g_sh0[g * 3 + k] = B[0] * vc[k]; g_scaling[g * 3 + k] = gs[k]; }
+            for (int k = 0; k < 3; ++k) gm[k] = o.v_mean[k];
+            // colour clamp mask, then SH backward
+            const float4 r3 = records[(size_t)g * 4 + 3];
+            vc[0] = r3.x <= 0.f ? 0.f : o.v_rgb[0];
+            vc[1] = r3.y <= 0.f ? 0.f : o.v_rgb[1];
+            vc[2] = r3.z <= 0.f ? 0.f : o.v_rgb[2];
+            sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] = gq[k];
-            g_opacity[g] = go;
-            for (int k = 1; k < K; ++k)
+            for (int k = 0; k < 3; ++k) g0[k] = B[0] * vc[k];
+        }
+        for (int k = 1; k < K; ++k) {
+            const float w = k < nb ? B[k] : 0.f;
 #pragma unroll
-                for (int c = 0; c < 3; ++c) dst[(k - 1) * 3 + c] = k < nb ? B[k] * vc[c] : 0.f;
+            for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] = w * vc[c];
+        }
+        __syncwarp();
+        {
+            const int n_rows = min(32, N - chunk * 32);
+            const int total = n_rows * rest;
+            float* dst = g_shN + (size_t)chunk * 32 * rest;
+            if (accumulate) {
+                if (__any_sync(0xffffffffu, visible))
+                    for (int i = lane; i < total; i += 32) dst[i] += my[i];
+            } else {
+                for (int i = lane; i < total; i += 32) dst[i] = my[i];
+            }
+        }
+        __syncwarp();
+        if (in_range && (visible || !accumulate)) {
+            if (accumulate) {
+#pragma unroll
+                for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] += gm[k]; g_sh0[g * 3 + k] += g0[k]; g_scaling[g * 3 + k] += gs[k]; }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) g_rotation[g * 4 + k] += gq[k];
+                g_opacity[g] += go;
+            } else {
+#pragma unroll
+                for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] = gm[k]; g_sh0[g * 3 + k] = g0[k]; g_scaling[g * 3 + k] = gs[k]; }
+                reinterpret_cast<float4*>(g_rotation)[g] = make_float4(gq[0], gq[1], gq[2], gq[3]);
+                g_opacity[g] = go;
+            }
         }
     }
 }
@@ -497,7 +514,11 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
                                int accumulate, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("grad_epilogue", st);
-    grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
+    const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
+    if (smem > 200 * 1024) { set_error("grad_epilogue_fused: too many SH coefficients"); return LFS_EINVAL; }
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(grad_epilogue_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
                                                                  p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
                                                                  g.sh0, g.shN, g.scaling_raw, g.rotation_raw,
                                                                  g.opacity_raw, accumulate);

@@ -118,34 +118,42 @@ __global__ void __launch_bounds__(kThreads) radix_hist_kernel(const uint32_t* __
     hist[(size_t)threadIdx.x * nb + blockIdx.x] = h[threadIdx.x];
 }
 
-// Exclusive scan of the digit-major histogram table (radix * nb entries) by one block.
-__global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t* __restrict__ hist, int n) {
+// One CTA per digit: exclusive scan of that digit's per-block counts (row d of the digit-major table)
+// and the digit total. The prefix over digits is taken by every scatter CTA from the 256 totals.
+__global__ void __launch_bounds__(kThreads) radix_scan_kernel(uint32_t* __restrict__ hist, int nb,
+                                                              uint32_t* __restrict__ digit_totals) {
     __shared__ int sm[33];
-    const int per = (n + 1023) / 1024;
-    const int lo = threadIdx.x * per, hi = min(n, lo + per);
-    int s = 0;
-    for (int i = lo; i < hi; ++i) s += (int)hist[i];
-    int total;
-    int run = block_excl_scan(s, total, sm);
-    for (int i = lo; i < hi; ++i) {
-        const int v = (int)hist[i];
-        hist[i] = (uint32_t)run;
-        run += v;
+    uint32_t* row = hist + (size_t)blockIdx.x * nb;
+    int carry = 0;
+    for (int base = 0; base < nb; base += kThreads) {
+        const int i = base + threadIdx.x;
+        const int v = i < nb ? (int)row[i] : 0;
+        int total;
+        const int ex = block_excl_scan(v, total, sm);
+        if (i < nb) row[i] = (uint32_t)(carry + ex);
+        carry += total;
     }
+    if (threadIdx.x == 0) digit_totals[blockIdx.x] = (uint32_t)carry;
 }
 
 __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out,
     uint32_t* __restrict__ vals_out, const int32_t* n_dev, int64_t n_max, int shift, uint32_t mask, int nb,
-    const uint32_t* __restrict__ hist) {
+    const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_totals) {
     __shared__ uint32_t cnt[kWarps][256];
     __shared__ uint32_t gbase[256];
+    __shared__ int sm[33];
     const int64_t n = device_count(n_dev, n_max);
     const int64_t chunk = (n + nb - 1) / nb;
     const int64_t lo = (int64_t)blockIdx.x * chunk, hi = min(n, lo + chunk);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t lt_mask = (1u << lane) - 1u;
-    gbase[threadIdx.x] = hist[(size_t)threadIdx.x * nb + blockIdx.x];
+    {
+        // start of digit d = totals of the smaller digits + this digit's counts in the earlier blocks
+        int total;
+        const int digit_base = block_excl_scan((int)digit_totals[threadIdx.x], total, sm);
+        gbase[threadIdx.x] = (uint32_t)digit_base + hist[(size_t)threadIdx.x * nb + blockIdx.x];
+    }
     for (int64_t tile_lo = lo; tile_lo < hi; tile_lo += kTile) {
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] = 0;
@@ -320,7 +328,7 @@ __global__ void __launch_bounds__(kThreads) sum_i32_kernel(int64_t n, const int3
 
 }  // namespace
 
-size_t sort_scratch_bytes() { return ((size_t)kRadixBlocks * 256 + kScanBlocks + 64) * sizeof(uint32_t); }
+size_t sort_scratch_bytes() { return ((size_t)kRadixBlocks * 256 + kScanBlocks + 320) * sizeof(uint32_t); }
 
 int exclusive_scan_gather(const int32_t* src, const uint32_t* idx, int64_t n, int32_t* out, int32_t* total_dev,
                           const SortScratch& s, cudaStream_t st) {
@@ -352,9 +360,9 @@ int radix_sort_pairs(uint32_t* keys[2], uint32_t* vals[2], const int32_t* n_dev,
         const int nbits = (shift + bits > key_bits) ? (key_bits - shift) : bits;
         const uint32_t mask = (1u << nbits) - 1u;
         radix_hist_kernel<<<nb, kThreads, 0, st>>>(keys[cur], n_dev, n_max, shift, mask, nb, s.hist);
-        radix_scan_kernel<<<1, 1024, 0, st>>>(s.hist, 256 * nb);
+        radix_scan_kernel<<<256, kThreads, 0, st>>>(s.hist, nb, s.block_sums);
         radix_scatter_kernel<<<nb, kThreads, 0, st>>>(keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n_dev, n_max,
-                                                      shift, mask, nb, s.hist);
+                                                      shift, mask, nb, s.hist, s.block_sums);
         cur ^= 1;
     }
     if (check_launch("radix_sort") != LFS_OK) return -1;

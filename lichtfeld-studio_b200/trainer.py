@@ -35,7 +35,8 @@ class SplatData:
 
     def __init__(self, n: int, sh_coeffs: int, device, capacity: int | None = None):
         self.K = int(sh_coeffs)
-        self.capacity = int(capacity or n)
+        # a multiple of 4 rows keeps every group's start (and each quaternion row) 16-byte aligned
+        self.capacity = (int(capacity or n) + 3) // 4 * 4
         self.size = int(n)
         self.device = device
         w = row_widths(self.K)

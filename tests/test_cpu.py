@@ -1,0 +1,193 @@
+"""CPU-only checks: the oracle against analytic cases and finite differences (its only pins: the reference
+ships no golden vectors for this path), the seeded generator, the host-side logic and the C ABI surface."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from conftest import make_scene, rel_l2
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_abi_exports_every_declared_symbol(pkg):
+    header = (ROOT / "include" / "lfs_b200.h").read_text()
+    declared = set(re.findall(r"\b(lfs_[a-z0-9_]+)\s*\(", header))
+    declared -= {"lfs_status", "lfs_camera_model"}
+    lib = ctypes.CDLL(str(pkg._capi.LIB_PATH))
+    missing = [n for n in sorted(declared) if not hasattr(lib, n)]
+    assert not missing, missing
+    assert set(pkg._capi.EXPORTED) == declared
+    assert b"sm_100a" in pkg._capi.lib().lfs_build_info()
+
+
+def test_synth_is_deterministic_and_distributed(synth):
+    a = synth.make_gaussians(5000, 0, "clusters", 3)
+    b = synth.make_gaussians(5000, 0, "clusters", 3)
+    c = synth.make_gaussians(5000, 1, "clusters", 3)
+    for k in a:
+        assert np.array_equal(a[k], b[k]) and not np.array_equal(a[k], c[k])
+    assert a["shN"].shape == (5000, 15, 3) and a["opacity_raw"].shape == (5000, 1)
+    assert abs(a["scaling_raw"].mean() + 4.5) < 0.05 and abs(a["scaling_raw"].std() - 0.6) < 0.05
+    assert abs(np.linalg.norm(a["rotation_raw"], axis=1) - 1).max() < 1e-5
+    assert np.abs(a["means"]).max() <= 3.0
+    n = synth.normal(3, 9, 200001)
+    assert abs(n.mean()) < 0.01 and abs(n.std() - 1) < 0.01
+    poses = synth.hemisphere_poses(200, 5.0)
+    R = poses[:, :3, :3]
+    assert np.abs(R @ R.transpose(0, 2, 1) - np.eye(3)).max() < 1e-6
+    campos = -np.einsum("nji,nj->ni", R, poses[:, :3, 3])
+    assert np.abs(np.linalg.norm(campos, axis=1) - 5).max() < 1e-5 and (campos[:, 2] > 0).all()
+
+
+def test_oracle_projection_analytic(orc):
+    """A small isotropic Gaussian on the optical axis projects to the principal point with covariance
+    (f s / z)^2 + eps2d and radius ceil(min(3.33, sqrt(2 ln(255 o))) * sigma)."""
+    vm = np.eye(4, dtype=np.float32); vm[2, 3] = 4.0
+    K = np.array([[300, 0, 128], [0, 300, 128], [0, 0, 1]], np.float32)
+    s, o = 0.01, 0.8
+    radii, m2, d, conics, comp = orc.projection_ut_3dgs_fused(
+        np.zeros((1, 3), np.float32), np.array([[1, 0, 0, 0]], np.float32), np.full((1, 3), s, np.float32),
+        np.array([o], np.float32), vm[None], K[None], 256, 256, calc_compensations=True)
+    var = (300 * s / 4.0) ** 2
+    assert np.allclose(m2[0, 0], [128, 128], atol=1e-3) and abs(d[0, 0] - 4.0) < 1e-6
+    assert abs(1 / conics[0, 0, 0] - (var + 0.3)) < 2e-3 and abs(conics[0, 0, 1]) < 1e-3
+    assert abs(comp[0, 0] - var / (var + 0.3)) < 2e-3
+    ext = min(3.33, np.sqrt(2 * np.log(o * comp[0, 0] * 255)))
+    assert radii[0, 0, 0] == int(np.ceil(ext * np.sqrt(var + 0.3)))
+    # behind the camera / beyond the far plane / almost transparent -> culled
+    for mean, op in (([0, 0, -5], 0.8), ([0, 0, 2e4], 0.8), ([0, 0, 0], 0.001)):
+        r = orc.projection_ut_3dgs_fused(np.array([mean], np.float32), np.array([[1, 0, 0, 0]], np.float32),
+                                         np.full((1, 3), s, np.float32), np.array([op], np.float32), vm[None], K[None], 256, 256)[0]
+        assert (r == 0).all()
+
+
+def test_oracle_intersect_hand_case(orc):
+    """One Gaussian covering tiles (1..2, 0..1) of a 4x3 grid, one culled, one clipped at the top-left corner."""
+    m2 = np.array([[[30.0, 10.0], [5.0, 5.0], [-3.0, -2.0]]], np.float32)
+    r = np.array([[[10, 8], [0, 4], [6, 6]]], np.int32)
+    d = np.array([[2.0, 1.0, 0.5]], np.float32)
+    tpg, ids, flat = orc.intersect_tile(m2, r, d, 1, 16, 4, 3, True)
+    assert tpg.tolist() == [[4, 0, 1]]
+    tile_of = (ids >> 32).tolist()
+    assert tile_of == [0, 1, 2, 5, 6] and flat.tolist() == [2, 0, 0, 0, 0]
+    assert (ids & 0xFFFFFFFF).tolist()[0] == int(np.float32(0.5).view(np.uint32))
+    off = orc.intersect_offset(ids, 1, 4, 3)
+    assert off.reshape(-1).tolist() == [0, 1, 2, 3, 3, 3, 4, 5, 5, 5, 5, 5]
+    # ties in depth keep ascending index; unsorted emission is row-major per Gaussian
+    d2 = np.array([[1.0, 1.0, 1.0]], np.float32)
+    _, ids2, flat2 = orc.intersect_tile(m2, np.array([[[10, 8], [3, 3], [6, 6]]], np.int32), d2, 1, 16, 4, 3, True)
+    assert flat2.tolist()[:2] == [1, 2]
+
+
+def test_oracle_rasterizer_single_gaussian(orc):
+    """One Gaussian on the axis: centre pixel alpha = opacity * exp(-0.5 dist^2) with dist the ray offset in
+    units of sigma; alpha-compositing against a background."""
+    vm = np.eye(4, dtype=np.float32); vm[2, 3] = 4.0
+    K = np.array([[64, 0, 16], [0, 64, 16], [0, 0, 1]], np.float32)
+    s, o = 0.05, 0.6
+    P = dict(means=np.zeros((1, 3), np.float32), sh0=np.full((1, 1, 3), 0.5 / 0.2820947917738781, np.float32),
+             shN=np.zeros((1, 0, 3), np.float32), scaling_raw=np.full((1, 3), np.log(s), np.float32),
+             rotation_raw=np.array([[1, 0, 0, 0]], np.float32), opacity_raw=np.full((1, 1), np.log(o / (1 - o)), np.float32))
+    bg = np.array([0.1, 0.2, 0.3], np.float32)
+    f = orc.render_fwd(P, vm, K, 32, 32, 0, background=bg)
+    # pixel (16,16) has its centre at (16.5,16.5): ray offset 0.5/64 * 4 = 0.03125 in x and y at depth 4
+    dist2 = 2 * (0.03125 / s) ** 2 / (1 + 2 * (0.5 / 64) ** 2)
+    a = o * np.exp(-0.5 * dist2)
+    assert abs(f["alpha"][16, 16, 0] - a) < 2e-4
+    assert np.allclose(f["render"][16, 16], a * 1.0 + (1 - a) * bg, atol=3e-4)
+    assert np.allclose(f["render"][0, 0], bg) and f["alpha"][0, 0, 0] == 0
+
+
+def _loss_of(orc, P, vm, K, W, H, deg, target, bg):
+    f = orc.render_fwd(P, vm, K, W, H, deg, background=bg)
+    return orc.photometric_loss(f["render"], target, 0.2, want_grad=False)[0], f
+
+
+def test_oracle_gradients_finite_difference(orc, synth):
+    """Backward of the whole chain (rasterizer VJPs, SH, activations, L1+SSIM) against central differences of
+    the oracle's own forward. Float32 forward => loose tolerance, but any wrong term is off by O(1)."""
+    cfg, P, vm, K = make_scene(synth, 60, 48, 40, 2, seed=4, fx=60.0)
+    P["scaling_raw"] += 1.6  # big enough to overlap many pixels
+    bg = np.array([0.3, 0.1, 0.2], np.float32)
+    _, P2, _, _ = make_scene(synth, 60, 48, 40, 2, seed=77, fx=60.0)
+    P2["scaling_raw"] += 1.6
+    target = np.ascontiguousarray(np.clip(orc.render_fwd(P2, vm, K, 48, 40, 2, background=bg)["render"], 0, 1).transpose(2, 0, 1))
+    loss, f = _loss_of(orc, P, vm, K, 48, 40, 2, target, bg)
+    _, g, _, _ = orc.photometric_loss(f["render"], target, 0.2)
+    bwd = orc.render_bwd(P, f, vm, K, 48, 40, 2, g, background=bg)
+    rng = np.random.default_rng(0)
+    checked = 0
+    for name, eps in (("means", 2e-3), ("scaling_raw", 5e-3), ("rotation_raw", 5e-3), ("opacity_raw", 1e-2), ("sh0", 1e-2), ("shN", 2e-2)):
+        gflat = bwd[name].reshape(-1)
+        order = np.argsort(-np.abs(gflat))[:6]
+        for idx in order:
+            if abs(gflat[idx]) < 1e-6:
+                continue
+            vals = []
+            for sgn in (+1, -1):
+                Q = {k: v.copy() for k, v in P.items()}
+                Q[name].reshape(-1)[idx] += sgn * eps
+                vals.append(_loss_of(orc, Q, vm, K, 48, 40, 2, target, bg)[0])
+            fd = (vals[0] - vals[1]) / (2 * eps)
+            assert abs(fd - gflat[idx]) < 0.15 * abs(gflat[idx]) + 2e-5, (name, idx, fd, gflat[idx])
+            checked += 1
+    assert checked >= 20
+
+
+def test_oracle_ssim_properties(orc):
+    rng = np.random.default_rng(1)
+    a = rng.random((3, 40, 50)).astype(np.float32)
+    m, d1, d2, d3 = orc.fusedssim(a, a)
+    assert np.abs(m - 1).max() < 1e-5  # identical images
+    b = rng.random((3, 40, 50)).astype(np.float32)
+    loss, g, l1, ss = orc.photometric_loss(np.ascontiguousarray(a.transpose(1, 2, 0)), b, 0.2)
+    assert abs(l1 - np.abs(a - b).mean()) < 1e-6 and abs(loss - (0.8 * l1 + 0.2 * (1 - ss))) < 1e-6
+    # gradient of the loss w.r.t. the render by central differences on a few pixels
+    r = np.ascontiguousarray(a.transpose(1, 2, 0))
+    for (y, x, c) in ((20, 25, 0), (7, 44, 2), (0, 0, 1)):
+        vals = []
+        for sgn in (1, -1):
+            q = r.copy(); q[y, x, c] += sgn * 1e-2
+            vals.append(orc.photometric_loss(q, b, 0.2, want_grad=False)[0])
+        assert abs((vals[0] - vals[1]) / 2e-2 - g[y, x, c]) < 0.05 * abs(g[y, x, c]) + 1e-6
+
+
+def test_oracle_adam_and_relocation(orc):
+    p = np.array([1.0, -2.0], np.float32); m = np.zeros(2, np.float32); v = np.zeros(2, np.float32)
+    orc.adam_step(p, m, v, np.array([0.5, -0.25], np.float32), 0.1, 0.9, 0.999, 1e-15, 1)
+    assert np.allclose(p, [0.9, -1.9], atol=1e-6) and np.allclose(m, [0.05, -0.025]) and np.allclose(v, [2.5e-4, 6.25e-5], rtol=1e-4)
+    b = orc.binoms_table(51)
+    assert b[4, 2] == 6 and b[10, 3] == 120 and b[0, 0] == 1 and b[3, 5] == 0
+    # ratio 1 keeps the Gaussian unchanged; ratio n keeps total opacity: 1 - (1 - o')^n = o
+    no, ns = orc.relocation(np.array([0.7, 0.7], np.float32), np.ones((2, 3), np.float32), np.array([1, 4], np.int32), b, 51)
+    assert abs(no[0] - 0.7) < 1e-6 and np.allclose(ns[0], 1, atol=1e-5)
+    assert abs(1 - (1 - no[1]) ** 4 - 0.7) < 1e-5 and (ns[1] < 1).all()
+
+
+def test_splat_data_layout_and_strategy_schedule(pkg):
+    import torch
+    tr, st = pkg.trainer, pkg.strategy
+    sd = tr.SplatData(10, 16, "cpu", capacity=13)
+    assert sd.capacity == 16 and sd.row_floats == 59 and sd.flat.numel() == 16 * 59
+    assert sd.tensor("shN").shape == (10, 15, 3) and sd.tensor("sh0").shape == (10, 1, 3) and sd.tensor("opacity_raw").shape == (10, 1)
+    sd.tensor("means").fill_(1.0)
+    assert sd.flat[:30].eq(1).all() and sd.flat[30:].eq(0).all()
+    for name in tr.PARAM_NAMES:  # every group starts 16-byte aligned
+        assert (sd._full[name].data_ptr() - sd.flat.data_ptr()) % 16 == 0
+    assert np.array_equal(st.binoms_table(51), __import__("oracle.oracle", fromlist=["x"]).binoms_table(51))
+    p = st.OptimizationParameters()
+    assert (p.iterations, p.min_opacity, p.refine_every, p.start_refine, p.stop_refine, p.max_cap) == (30000, 0.005, 100, 500, 25000, 1000000)
+
+
+def test_library_fails_loudly_without_gpu(pkg):
+    """No CPU fallback: on a machine without a GPU the calls must raise, not silently compute elsewhere."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        pkg.ops.quats_to_rotmats(torch.zeros(4, 4))
+    with pytest.raises(pkg.LfsError):
+        pkg._capi.call("lfs_quats_to_rotmats", 4, ctypes.c_void_p(256), ctypes.c_void_p(512), None)

