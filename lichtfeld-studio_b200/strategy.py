@@ -159,15 +159,20 @@ class MCMC(IStrategy):
 
     def remove_gaussians(self, mask: torch.Tensor):
         """mcmc.cpp:406-444: keep rows where mask is False (parameters and Adam moments)."""
+        old_n = self._splat_data.size
+        if mask.numel() != old_n:
+            raise RuntimeError(f"mask must have {old_n} elements, got {mask.numel()}")
         keep = (~mask.bool()).nonzero().squeeze(-1)
-        if keep.numel() == self._splat_data.size:
+        new_n = int(keep.numel())
+        if new_n == old_n:
             return
         for sd in (self._splat_data, self._optimizer.exp_avg, self._optimizer.exp_avg_sq):
-            sd.size = self._splat_data.size if sd is not self._splat_data else sd.size
+            sd.size = old_n  # every buffer is gathered with indices into the OLD row range
             kept = {n: sd.tensor(n).index_select(0, keep) for n in ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")}
-            sd.size = keep.numel()
+            sd.size = new_n
             for n, t in kept.items():
                 sd.tensor(n).copy_(t)
+        self.grads.size = new_n
 
     # ------------------------------------------------------------------ pieces
     @staticmethod

@@ -182,6 +182,31 @@ def test_splat_data_layout_and_strategy_schedule(pkg):
     assert (p.iterations, p.min_opacity, p.refine_every, p.start_refine, p.stop_refine, p.max_cap) == (30000, 0.005, 100, 500, 25000, 1000000)
 
 
+def test_remove_gaussians_compacts_all_buffers(pkg):
+    """Host-side row surgery of MCMC::remove_gaussians (mcmc.cpp:406-444) on CPU tensors."""
+    import torch
+    tr, st = pkg.trainer, pkg.strategy
+    sd = tr.SplatData(12, 4, "cpu", capacity=20)
+    sd.flat.copy_(torch.arange(sd.flat.numel(), dtype=torch.float32))
+    s = st.MCMC(sd)
+    s.initialize(st.OptimizationParameters(max_cap=20, sh_degree=1))
+    s._optimizer.exp_avg.flat.copy_(sd.flat + 1000)
+    s._optimizer.exp_avg_sq.flat.copy_(sd.flat + 2000)
+    before = {n: sd.tensor(n).clone() for n in tr.PARAM_NAMES}
+    mask = torch.zeros(12, dtype=torch.bool)
+    mask[[0, 5, 11]] = True
+    s.remove_gaussians(mask)
+    assert sd.size == 9 and s._optimizer.exp_avg.size == 9 and s._optimizer.exp_avg_sq.size == 9 and s.grads.size == 9
+    for n in tr.PARAM_NAMES:
+        assert torch.equal(sd.tensor(n), before[n][~mask])
+        assert torch.equal(s._optimizer.exp_avg.tensor(n), before[n][~mask] + 1000)
+        assert torch.equal(s._optimizer.exp_avg_sq.tensor(n), before[n][~mask] + 2000)
+    with pytest.raises(RuntimeError, match="mask must have"):
+        s.remove_gaussians(torch.zeros(12, dtype=torch.bool))
+    s.remove_gaussians(torch.zeros(9, dtype=torch.bool))  # nothing to remove
+    assert sd.size == 9
+
+
 def test_library_fails_loudly_without_gpu(pkg):
     """No CPU fallback: on a machine without a GPU the calls must raise, not silently compute elsewhere."""
     import torch

@@ -106,8 +106,11 @@ def test_add_new_and_noise(pkg, orc, synth):
     orc.add_noise(P["opacity_raw"], P["scaling_raw"], P["rotation_raw"], noise, ref_means, float(np.float32(s._optimizer.lr[0])) * 5e5)
     assert np.abs(s._splat_data.tensor("means").cpu().numpy() - ref_means).max() < 2e-5
     s._params.max_cap = 10**9
+    torch.manual_seed(7)
     with pytest.raises(RuntimeError, match="capacity"):
-        s.add_new_gs()
+        for _ in range(5):  # 8400 -> 8820 fits in 9000 rows, the next growth does not
+            s.add_new_gs()
+    assert s._splat_data.size == 8820
 
 
 def test_strategy_schedule_and_step(pkg, synth):
@@ -120,7 +123,6 @@ def test_strategy_schedule_and_step(pkg, synth):
     before = s._splat_data.flat.clone()
     s.step(5)
     assert s._optimizer.step_count == 1 and abs(s._optimizer.lr[0] - lr0 * 0.01 ** (1 / 30000)) < 1e-18
-    assert torch.equal(s._splat_data.tensor("shN"), before[: 0].new_tensor([]).reshape(0)) or True
     # shN untouched while iteration <= 1000, updated afterwards
     shn0 = s._splat_data.tensor("shN").clone()
     s.step(7)
