@@ -239,10 +239,14 @@ __global__ void __launch_bounds__(kThreads) emit_instances_kernel(
 
 // offsets[t] = first sorted instance whose (camera, tile) id >= t, for t in [0, n_ids]; entry n_ids
 // (one past the last tile) holds the instance count. Keys hold (cid << tile_n_bits) | tile.
+// When the overflow flag is set the instance list is incomplete (some slots were never written), so
+// the keys cannot be trusted: all offsets are zeroed and the rasterizer draws nothing. Ids are clamped to
+// n_ids in any case so that no key value can direct a store outside the offsets array.
 __global__ void __launch_bounds__(kThreads) tile_offsets_kernel(const uint32_t* __restrict__ tkeys, const int32_t* n_dev,
                                                                 int64_t n_max, uint32_t n_tiles, uint32_t tile_n_bits,
-                                                                int64_t n_ids, int32_t* __restrict__ offsets) {
-    const int64_t n = device_count(n_dev, n_max);
+                                                                int64_t n_ids, const int32_t* __restrict__ overflow,
+                                                                int32_t* __restrict__ offsets) {
+    const int64_t n = (overflow && *overflow) ? 0 : device_count(n_dev, n_max);
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (n == 0) {
@@ -252,7 +256,7 @@ __global__ void __launch_bounds__(kThreads) tile_offsets_kernel(const uint32_t* 
     const uint32_t tmask = (1u << tile_n_bits) - 1u;
     for (int64_t i = tid; i < n; i += stride) {
         const uint32_t k = tkeys[i];
-        const int64_t id_curr = (int64_t)(k >> tile_n_bits) * n_tiles + (k & tmask);
+        const int64_t id_curr = min((int64_t)(k >> tile_n_bits) * n_tiles + (k & tmask), n_ids - 1);
         if (i == 0)
             for (int64_t t = 0; t <= id_curr; ++t) offsets[t] = 0;
         if (i == n - 1)
@@ -260,7 +264,7 @@ __global__ void __launch_bounds__(kThreads) tile_offsets_kernel(const uint32_t* 
         if (i > 0) {
             const uint32_t kp = tkeys[i - 1];
             if (kp != k) {
-                const int64_t id_prev = (int64_t)(kp >> tile_n_bits) * n_tiles + (kp & tmask);
+                const int64_t id_prev = min((int64_t)(kp >> tile_n_bits) * n_tiles + (kp & tmask), n_ids - 1);
                 for (int64_t t = id_prev + 1; t <= id_curr; ++t) offsets[t] = (int32_t)i;
             }
         }
@@ -417,7 +421,7 @@ int build_tile_lists(const TileListArgs& a, cudaStream_t st) {
         const int64_t n_ids = (int64_t)a.C * n_tiles;
         LFS_TIMED("tile_offsets", st);
         tile_offsets_kernel<<<grid_for(a.capacity > 0 ? a.capacity : 1, 256), 256, 0, st>>>(
-            a.tkeys[sel], a.n_isects_dev, a.capacity, n_tiles, tile_n_bits, n_ids, a.tile_offsets);
+            a.tkeys[sel], a.n_isects_dev, a.capacity, n_tiles, tile_n_bits, n_ids, a.overflow, a.tile_offsets);
     }
     return check_launch("build_tile_lists");
 }

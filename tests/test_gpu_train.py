@@ -87,7 +87,8 @@ def test_accumulate_and_row_range(pkg, orc, synth):
     g1 = {k: t.clone() for k, t in r["grads"].tensors().items()}
     r["rast"].backward(r["v_render"], r["grads"], r["tbg"], accumulate=True)
     for k, t in r["grads"].tensors().items():
-        assert torch.allclose(t, 2 * g1[k], rtol=1e-3, atol=1e-9)  # atomic summation order differs run to run
+        # atomic summation order differs run to run, so compare in norm rather than element by element
+        assert rel_l2(t.cpu().numpy(), (2 * g1[k]).cpu().numpy()) < 1e-4, k
     # sharded Adam: two half ranges == one full range
     a, b = r["model"], r["model"].like()
     b.flat.copy_(a.flat)
