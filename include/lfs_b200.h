@@ -201,6 +201,7 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
 /* Backward of the same node (rasterizer_autograd.cpp:105 -> gsplat/Rasterization.cpp:470) followed by
  * the activation backward, for the camera whose forward state is in the workspace. alpha is the
  * forward's alpha output, v_render [H,W,3] and v_alpha [H,W,1] (may be NULL = zeros) the output gradients.
+ * Call it once per lfs_render_forward: it consumes the per-Gaussian accumulators that the forward zeroed.
  * grads: the six raw-parameter gradients; accumulate != 0 adds to them, else they are overwritten
  * (all N rows, zeros for Gaussians that were not visible). */
 int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, const float* background,

@@ -85,6 +85,8 @@ def test_accumulate_and_row_range(pkg, orc, synth):
     r = _run(pkg, orc, synth, 3000, 64, 48, 1, 21, np.zeros(3, np.float32))
     tr = pkg.trainer
     g1 = {k: t.clone() for k, t in r["grads"].tensors().items()}
+    # a second camera pass (same camera here) accumulated on top: forward, then backward with accumulate
+    r["rast"].forward(r["cam"], r["tbg"])
     r["rast"].backward(r["v_render"], r["grads"], r["tbg"], accumulate=True)
     for k, t in r["grads"].tensors().items():
         # atomic summation order differs run to run, so compare in norm rather than element by element
