@@ -261,6 +261,18 @@ int lfs_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw
                       int64_t* dead_indices, int64_t* alive_indices, float* alive_opacities,
                       int32_t* counts_dev, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference. Same result as lfs_mcmc_classify, but for callers that must not
+ * allocate device memory where they run the densification step (a trainer refining under the viewer's
+ * render lock, where an allocation can stall the frame in flight; a plugin host with a budget fixed at
+ * start-up). The scratch is a fixed array inside the library (about 2.1 MB per GPU, held until the
+ * process exits), so N is limited to LFS_NOALLOC_MAX_GAUSSIANS; larger N returns LFS_ECAPACITY. The first
+ * call on a device also looks up the array's device address; make that call before any stream capture.
+ * All calls on a device share the scratch: calls that overlap on the GPU race and corrupt each other. */
+#define LFS_NOALLOC_MAX_GAUSSIANS 262144
+int lfs_mcmc_classify_noalloc(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity,
+                              int64_t* dead_indices, int64_t* alive_indices, float* alive_opacities,
+                              int32_t* counts_dev, void* stream);
+
 /* mcmc.cpp:137: sampled = alive_indices.index_select(0, sampled_local): out[i] = index_map[local_indices[i]]. */
 int lfs_mcmc_map_indices(int n, const int64_t* local_indices, const int64_t* index_map, int64_t* out, void* stream);
 

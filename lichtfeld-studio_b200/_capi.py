@@ -70,6 +70,7 @@ _SIGNATURES = {
     "lfs_adam_step_splats": [i32, i32, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),
                              C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, i64, i64, f32, vp],
     "lfs_mcmc_classify": [i32, vp, vp, f32, vp, vp, vp, vp, vp, sz, vp],
+    "lfs_mcmc_classify_noalloc": [i32, vp, vp, f32, vp, vp, vp, vp, vp],
     "lfs_mcmc_map_indices": [i32, vp, vp, vp, vp],
     "lfs_mcmc_gather_ratios": [i32, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp],
     "lfs_mcmc_apply": [i32, i32, i32, vp, vp, vp, vp, f32, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats), vp],

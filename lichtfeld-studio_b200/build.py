@@ -22,6 +22,7 @@ SOURCES = [
     ("loss.cu", []),
     ("elementwise.cu", []),
     ("api.cu", []),
+    ("noalloc.cu", []),
     ("error.cu", []),
 ]
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
