@@ -179,7 +179,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     pkg = importlib.import_module("lichtfeld-studio_b200")
     synth, tr, capi = pkg.synth, pkg.trainer, pkg._capi
     capi.lib()  # fails loudly if the CUDA library is missing
@@ -193,9 +194,20 @@ def run_ours(args):
     poses, Kmat = synth.make_cameras(cfg)
     total_steps = args.warmup + args.steps
 
-    model = tr.SplatData(n, K_sh, dev).load(P)
+    dp = pkg.dp
+    cap = (n + 31) // 32 * 32
+    peer = None
+    if world > 1 and args.dp_mode == "fused_p2p":
+        numel = cap * tr.SplatData(1, K_sh, "cpu").row_floats
+        pf, gf, peer = dp.symmetric_flat_buffers(numel, dev)
+        model, grads = tr.SplatData(n, K_sh, dev, cap, flat=pf).load(P), tr.SplatData(n, K_sh, dev, cap, flat=gf)
+    else:
+        model, grads = tr.SplatData(n, K_sh, dev, cap).load(P), tr.SplatData(n, K_sh, dev, cap)
     held_out = tr.SplatData(n, K_sh, dev).load(P_target)
-    grads, m, v = model.like(), model.like(), model.like()
+    if world == 1:
+        m, v = model.like(), model.like()
+    else:
+        exchange = dp.GradExchange(model, grads, LRS, mode=args.dp_mode, peer_ptrs=peer)
     rast = tr.Rasterizer(model, W, H, deg, isect_capacity=max(12 * n, 1 << 22))
     rast_t = tr.Rasterizer(held_out, W, H, deg, isect_capacity=max(12 * n, 1 << 22))
     lossfn = tr.PhotometricLoss(W, H, dev)
@@ -229,8 +241,7 @@ def run_ours(args):
             tr.adam_step_splats(model, m, v, grads, LRS, step_count)
             return
         # gradients summed over cameras, mean over the batch folded into Adam's gradient read
-        dist.all_reduce(grads.flat)
-        tr.adam_step_splats(model, m, v, grads, LRS, step_count, grad_scale=1.0 / world)
+        exchange.step(2000 + step_count)
 
     def step(s, target, vm):
         out = rast.forward(tr.Camera(vm, Kt, W, H), bg)
@@ -289,12 +300,13 @@ def run_ours(args):
 
     # ---- per-kernel times (CUDA events inside the library), pair counts, rooflines --------------------
     kernels, roofline, extra = {}, None, {}
+    n_prof = 3
     if rank == 0:
         capi.profile_enable(True)
-        n_prof = 3
-        for s in range(n_prof):
-            step(s, targets_dev[s], vms_dev[s])
-        torch.cuda.synchronize()
+    for s in range(n_prof):  # every rank steps (the exchange is a collective); only rank 0 records events
+        step(s, targets_dev[s], vms_dev[s])
+    barrier()
+    if rank == 0:
         recs = capi.profile_collect()
         capi.profile_enable(False)
         for name, msv in recs:
@@ -345,7 +357,7 @@ def run_ours(args):
                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": world,
-                          "parallelism": f"dp{world}" if world > 1 else "single", "l2": "inputs larger than L2 "
+                          "parallelism": f"dp{world}:{args.dp_mode}" if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
                "clocks": clocks, "e2e": {"value": world * 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
                                          "d2h_bytes_per_step": d2h, "steps": n_e2e},
@@ -365,6 +377,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--dp-mode", default="fused_p2p", choices=["allreduce", "sharded", "fused_p2p"],
+                    help="gradient exchange for N > 1 (see lichtfeld-studio_b200/dp.py)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -249,6 +249,42 @@ int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const l
                          double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
                          int64_t first_row, int64_t n_rows, float grad_scale, void* stream);
 
+/* Fused Adam over up to 16 arbitrary contiguous segments in one launch (each with its own learning rate).
+ * lfs_adam_step_splats is the special case "six groups, one row range". Used for optimizer-state sharding
+ * by flat element range: a shard of the group-major parameter buffer is at most six segments. */
+typedef struct lfs_adam_segment {
+    float* param;
+    float* exp_avg;
+    float* exp_avg_sq;
+    const float* grad;
+    int64_t n;
+    float lr;
+} lfs_adam_segment;
+int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segments /* host */, double beta1, double beta2,
+                           double eps, int64_t step_count, float grad_scale, void* stream);
+
+/* Data-parallel exchange fused with the optimizer (no counterpart in the reference, which is single-GPU):
+ * ONE kernel that, for this rank's shard of the flat parameter buffer, loads the gradient of every rank
+ * through NVLink peer pointers, sums them in rank order (deterministic), applies Adam with the local
+ * moments, and stores the new parameters into every rank's parameter buffer. It replaces
+ * ncclReduceScatter -> Adam -> ncclAllGather. peer_grads[i] / peer_params[i] (host arrays of `world` device
+ * pointers) are the peer-mapped FULL flat buffers of rank (own_rank + i) % world, i.e. entry 0 is this
+ * rank's own buffer (the parameters are read from it; the sum runs in that rotated order); offset / n / lr / moments per segment describe
+ * the shard (offsets in elements from the start of the flat buffers; moments are shard-local buffers).
+ * The caller must order it against the other ranks: every rank's backward finished before, nobody reads
+ * parameters or rewrites gradients until all ranks finished after (e.g. a stream-ordered barrier). Plain
+ * peer loads / stores only; no multicast. */
+typedef struct lfs_dp_segment {
+    int64_t offset;      /* first element of the segment in the flat buffers */
+    int64_t n;           /* elements */
+    float* exp_avg;      /* local moments of this segment */
+    float* exp_avg_sq;
+    float lr;
+} lfs_dp_segment;
+int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,
+                                 const lfs_dp_segment* segments /* host */, double beta1, double beta2, double eps,
+                                 int64_t step_count, float grad_scale, void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* MCMC densification index work (src/training/strategies/mcmc.cpp:112-347)                    */
 /* ------------------------------------------------------------------------------------------ */

@@ -38,6 +38,15 @@ class RenderView(C.Structure):
                                           "flatten_ids", "last_ids", "records")]
 
 
+class AdamSegment(C.Structure):
+    _fields_ = [("param", C.c_void_p), ("exp_avg", C.c_void_p), ("exp_avg_sq", C.c_void_p), ("grad", C.c_void_p),
+                ("n", C.c_int64), ("lr", C.c_float)]
+
+
+class DpSegment(C.Structure):
+    _fields_ = [("offset", C.c_int64), ("n", C.c_int64), ("exp_avg", C.c_void_p), ("exp_avg_sq", C.c_void_p), ("lr", C.c_float)]
+
+
 class LfsError(RuntimeError):
     pass
 
@@ -69,6 +78,9 @@ _SIGNATURES = {
     "lfs_photometric_loss": [i32, i32, f32, f32, vp, vp, vp, vp, vp, sz, vp],
     "lfs_adam_step_splats": [i32, i32, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),
                              C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, i64, i64, f32, vp],
+    "lfs_adam_step_segments": [i32, C.POINTER(AdamSegment), C.c_double, C.c_double, C.c_double, i64, f32, vp],
+    "lfs_dp_reduce_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, C.POINTER(DpSegment), C.c_double,
+                                     C.c_double, C.c_double, i64, f32, vp],
     "lfs_mcmc_classify": [i32, vp, vp, f32, vp, vp, vp, vp, vp, sz, vp],
     "lfs_mcmc_classify_noalloc": [i32, vp, vp, f32, vp, vp, vp, vp, vp],
     "lfs_mcmc_map_indices": [i32, vp, vp, vp, vp],

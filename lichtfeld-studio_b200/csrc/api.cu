@@ -22,6 +22,7 @@ namespace {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline cudaStream_t S_(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 struct Carver {
     char* base;
@@ -351,6 +352,68 @@ int lfs_adam_step_splats(int N, int K, const lfs_splats* params, const lfs_splat
     G.n_groups = ng;
     G.beta1 = (float)beta1; G.beta2 = (float)beta2; G.eps = (float)eps; G.bc2_sqrt_rcp = (float)bc2; G.grad_scale = grad_scale;
     return launch_adam_groups(G, S(stream));
+}
+
+int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segs, double beta1, double beta2, double eps,
+                           int64_t step_count, float grad_scale, void* stream) {
+    LFS_REQUIRE(n_segments >= 0 && n_segments <= kMaxAdamSegments, "at most 16 segments");
+    LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
+    if (n_segments == 0) return LFS_OK;
+    LFS_REQUIRE(segs != nullptr, "null pointer");
+    const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
+    AdamSegments S{};
+    S.prefix4[0] = 0;
+    int ng = 0;
+    for (int k = 0; k < n_segments; ++k) {
+        LFS_REQUIRE(segs[k].n >= 0, "negative segment size");
+        if (segs[k].n == 0) continue;
+        LFS_REQUIRE(segs[k].param && segs[k].exp_avg && segs[k].exp_avg_sq && segs[k].grad, "null tensor in a segment");
+        AdamGroup g{segs[k].param, segs[k].exp_avg, segs[k].exp_avg_sq, segs[k].grad, segs[k].n, segs[k].lr * (float)bc1, 0};
+        g.aligned = aligned16(g.p) && aligned16(g.m) && aligned16(g.v) && aligned16(g.g);
+        S.g[ng] = g;
+        S.prefix4[ng + 1] = S.prefix4[ng] + (g.n + 3) / 4;
+        ++ng;
+    }
+    S.n = ng;
+    S.beta1 = (float)beta1; S.beta2 = (float)beta2; S.eps = (float)eps; S.bc2_sqrt_rcp = (float)bc2; S.grad_scale = grad_scale;
+    return launch_adam_segments(S, S_(stream));
+}
+
+int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,
+                                 const lfs_dp_segment* segs, double beta1, double beta2, double eps, int64_t step_count,
+                                 float grad_scale, void* stream) {
+    LFS_REQUIRE(world >= 1 && world <= kMaxPeers, "world must be in [1, 8]");
+    LFS_REQUIRE(n_segments >= 0 && n_segments <= 6, "at most 6 segments");
+    LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
+    LFS_REQUIRE(peer_grads && peer_params, "null pointer");
+    if (n_segments == 0) return LFS_OK;
+    LFS_REQUIRE(segs != nullptr, "null pointer");
+    const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
+    DpArgs A{};
+    A.world = world;
+    for (int r = 0; r < world; ++r) {
+        LFS_REQUIRE(peer_grads[r] && peer_params[r], "null peer pointer");
+        LFS_REQUIRE(aligned16(peer_grads[r]) && aligned16(peer_params[r]), "peer buffers must be 16-byte aligned");
+        A.grads[r] = peer_grads[r];
+        A.params[r] = peer_params[r];
+    }
+    A.prefix4[0] = 0;
+    int ns = 0;
+    for (int k = 0; k < n_segments; ++k) {
+        if (segs[k].n == 0) continue;
+        LFS_REQUIRE(segs[k].n > 0 && segs[k].offset >= 0, "bad segment");
+        LFS_REQUIRE(segs[k].n % 4 == 0 && segs[k].offset % 4 == 0, "segment offsets and sizes must be multiples of 4 elements");
+        LFS_REQUIRE(segs[k].exp_avg && segs[k].exp_avg_sq && aligned16(segs[k].exp_avg) && aligned16(segs[k].exp_avg_sq),
+                    "segment moments must be non-null and 16-byte aligned");
+        A.seg[ns] = DpSegment{segs[k].offset, segs[k].n, segs[k].exp_avg, segs[k].exp_avg_sq, segs[k].lr * (float)bc1};
+        A.prefix4[ns + 1] = A.prefix4[ns] + segs[k].n / 4;
+        ++ns;
+    }
+    A.n_segments = ns;
+    A.beta1 = (float)beta1; A.beta2 = (float)beta2; A.eps = (float)eps; A.bc2_sqrt_rcp = (float)bc2; A.grad_scale = grad_scale;
+    return launch_dp_reduce_adam_broadcast(A, S_(stream));
 }
 
 int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,

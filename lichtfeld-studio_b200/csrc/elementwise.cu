@@ -54,6 +54,74 @@ __global__ void __launch_bounds__(256) adam_groups_kernel(AdamGroups G) {
     }
 }
 
+__global__ void __launch_bounds__(256) adam_segments_kernel(AdamSegments S) {
+    const int64_t total4 = S.prefix4[S.n];
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < total4; q += (int64_t)gridDim.x * blockDim.x) {
+        int gi = 0;
+#pragma unroll
+        for (int k = 1; k < kMaxAdamSegments; ++k)
+            if (k < S.n && q >= S.prefix4[k]) gi = k;
+        const AdamGroup& grp = S.g[gi];
+        const int64_t e = (q - S.prefix4[gi]) * 4;
+        if (grp.aligned && e + 4 <= grp.n) {
+            float4 p = *reinterpret_cast<float4*>(grp.p + e);
+            float4 m = *reinterpret_cast<float4*>(grp.m + e);
+            float4 v = *reinterpret_cast<float4*>(grp.v + e);
+            const float4 g = *reinterpret_cast<const float4*>(grp.g + e);
+            adam_update(p.x, m.x, v.x, g.x * S.grad_scale, S.beta1, S.beta2, S.eps, grp.step_size, S.bc2_sqrt_rcp);
+            adam_update(p.y, m.y, v.y, g.y * S.grad_scale, S.beta1, S.beta2, S.eps, grp.step_size, S.bc2_sqrt_rcp);
+            adam_update(p.z, m.z, v.z, g.z * S.grad_scale, S.beta1, S.beta2, S.eps, grp.step_size, S.bc2_sqrt_rcp);
+            adam_update(p.w, m.w, v.w, g.w * S.grad_scale, S.beta1, S.beta2, S.eps, grp.step_size, S.bc2_sqrt_rcp);
+            *reinterpret_cast<float4*>(grp.p + e) = p;
+            *reinterpret_cast<float4*>(grp.m + e) = m;
+            *reinterpret_cast<float4*>(grp.v + e) = v;
+        } else {
+            for (int64_t i = e; i < e + 4 && i < grp.n; ++i) {
+                float p = grp.p[i], m = grp.m[i], v = grp.v[i];
+                adam_update(p, m, v, grp.g[i] * S.grad_scale, S.beta1, S.beta2, S.eps, grp.step_size, S.bc2_sqrt_rcp);
+                grp.p[i] = p; grp.m[i] = m; grp.v[i] = v;
+            }
+        }
+    }
+}
+
+// Reduce-scatter + Adam + all-gather in one pass over this rank's shard. Each element is summed by its
+// owner only, in rank order, so every rank ends up with bit-identical parameters. Peer traffic is plain
+// 16-byte loads / stores over NVLink.
+__global__ void __launch_bounds__(256) dp_reduce_adam_broadcast_kernel(DpArgs A) {
+    const int64_t total4 = A.prefix4[A.n_segments];
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < total4; q += (int64_t)gridDim.x * blockDim.x) {
+        int si = 0;
+#pragma unroll
+        for (int k = 1; k < 6; ++k)
+            if (k < A.n_segments && q >= A.prefix4[k]) si = k;
+        const DpSegment& sg = A.seg[si];
+        const int64_t e = (q - A.prefix4[si]) * 4;   // element within the segment (segments are 4-element aligned)
+        const int64_t f = sg.offset + e;              // element within the flat buffers
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            if (r < A.world) {
+                const float4 t = *reinterpret_cast<const float4*>(A.grads[r] + f);
+                g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+            }
+        }
+        float4 p = *reinterpret_cast<const float4*>(A.params[0] + f);
+        // every rank holds the same parameters; read the local copy (params[0] is this rank's own buffer)
+        float4 m = *reinterpret_cast<float4*>(sg.m + e);
+        float4 v = *reinterpret_cast<float4*>(sg.v + e);
+        adam_update(p.x, m.x, v.x, g.x * A.grad_scale, A.beta1, A.beta2, A.eps, sg.step_size, A.bc2_sqrt_rcp);
+        adam_update(p.y, m.y, v.y, g.y * A.grad_scale, A.beta1, A.beta2, A.eps, sg.step_size, A.bc2_sqrt_rcp);
+        adam_update(p.z, m.z, v.z, g.z * A.grad_scale, A.beta1, A.beta2, A.eps, sg.step_size, A.bc2_sqrt_rcp);
+        adam_update(p.w, m.w, v.w, g.w * A.grad_scale, A.beta1, A.beta2, A.eps, sg.step_size, A.bc2_sqrt_rcp);
+        *reinterpret_cast<float4*>(sg.m + e) = m;
+        *reinterpret_cast<float4*>(sg.v + e) = v;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (r < A.world) *reinterpret_cast<float4*>(A.params[r] + f) = p;
+    }
+}
+
 // ---- spherical harmonics, operator level ------------------------------------------------------
 __global__ void __launch_bounds__(256) sh_fwd_kernel(int n, int K, int degree, const float* __restrict__ dirs,
                                                      const float* __restrict__ coeffs, const uint8_t* __restrict__ masks,
@@ -253,6 +321,22 @@ int launch_adam_groups(const AdamGroups& G, cudaStream_t st) {
     LFS_TIMED("adam", st);
     adam_groups_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(G);
     return check_launch("adam_groups");
+}
+
+int launch_adam_segments(const AdamSegments& S, cudaStream_t st) {
+    const int64_t total4 = S.prefix4[S.n];
+    if (total4 == 0) return LFS_OK;
+    LFS_TIMED("adam", st);
+    adam_segments_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(S);
+    return check_launch("adam_segments");
+}
+
+int launch_dp_reduce_adam_broadcast(const DpArgs& A, cudaStream_t st) {
+    const int64_t total4 = A.prefix4[A.n_segments];
+    if (total4 == 0) return LFS_OK;
+    LFS_TIMED("dp_reduce_adam_broadcast", st);
+    dp_reduce_adam_broadcast_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(A);
+    return check_launch("dp_reduce_adam_broadcast");
 }
 
 int launch_sh_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks, float* colors, cudaStream_t st) {

@@ -19,6 +19,31 @@ struct AdamGroups {
 };
 
 int launch_adam_groups(const AdamGroups& G, cudaStream_t st);
+
+constexpr int kMaxAdamSegments = 16;
+struct AdamSegments {
+    AdamGroup g[kMaxAdamSegments];
+    int64_t prefix4[kMaxAdamSegments + 1];
+    int n;
+    float beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
+};
+int launch_adam_segments(const AdamSegments& S, cudaStream_t st);
+
+constexpr int kMaxPeers = 8;
+struct DpSegment {
+    int64_t offset, n;
+    float* m; float* v;
+    float step_size;
+};
+struct DpArgs {
+    const float* grads[kMaxPeers];
+    float* params[kMaxPeers];
+    DpSegment seg[6];
+    int64_t prefix4[7];
+    int world, n_segments;
+    float beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
+};
+int launch_dp_reduce_adam_broadcast(const DpArgs& A, cudaStream_t st);
 int launch_sh_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks, float* colors, cudaStream_t st);
 int launch_sh_bwd(int n, int K, int degree, const float* dirs, const uint8_t* masks, const float* v_colors, float* v_coeffs, cudaStream_t st);
 int launch_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,

@@ -1,0 +1,171 @@
+"""Camera-parallel data parallelism for the training step: each rank renders its own camera(s) against
+replicated Gaussians; the only exchange is the sum of the flat gradient buffer, followed by Adam.
+The reference is single-GPU (no collectives anywhere in its tree); this is the multi-GPU design of the
+training path, one process per GPU over torch.distributed.
+
+Three interchangeable exchanges (all leave bit-identical parameters on every rank):
+  "allreduce" : all_reduce(grads)              -> full fused Adam on every rank
+  "sharded"   : reduce_scatter(grads)          -> Adam on this rank's flat shard -> all_gather(params)
+  "fused_p2p" : one CUDA kernel per rank that reads every rank's gradient shard through NVLink peer
+                pointers, sums in a fixed order, applies Adam and writes the new parameters into every
+                rank's buffer (lfs_dp_reduce_adam_broadcast); needs symmetric (peer-mapped) buffers.
+The flat buffers are group-major [means | sh0 | shN | scaling | rotation | opacity] x capacity rows, so a
+contiguous shard intersects at most six groups, each with its own learning rate.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _capi as capi
+from .trainer import PARAM_NAMES, SplatData, row_widths
+
+
+def shard_bounds(total: int, world: int, rank: int, align: int = 4):
+    """Equal shards of ceil(total / world) rounded up to `align` elements; the last shards may be short or
+    empty. Returns (first, count, shard_len)."""
+    per = -(-total // world)
+    per = -(-per // align) * align
+    lo = min(rank * per, total)
+    hi = min(lo + per, total)
+    return lo, hi - lo, per
+
+
+def group_segments(capacity: int, K: int, lo: int, n: int, lrs, skip_shN: bool = False):
+    """Intersect the flat element range [lo, lo + n) with the six parameter groups.
+    Returns [(group index, flat offset, count, lr)]; the shN group is dropped when skip_shN."""
+    w = row_widths(K)
+    out, off = [], 0
+    for gi, name in enumerate(PARAM_NAMES):
+        size = capacity * w[name]
+        a, b = max(lo, off), min(lo + n, off + size)
+        if b > a and not (skip_shN and name == "shN"):
+            out.append((gi, a, b - a, float(lrs[gi])))
+        off += size
+    return out
+
+
+class GradExchange:
+    """Owns the sharded optimizer state and performs exchange + Adam for one rank."""
+
+    def __init__(self, model: SplatData, grads: SplatData, lrs, mode: str = "sharded", betas=(0.9, 0.999), eps=1e-15,
+                 group=None, peer_ptrs=None):
+        self.model, self.grads, self.lrs, self.mode = model, grads, [float(x) for x in lrs], mode
+        self.betas, self.eps, self.group = betas, eps, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        total = model.flat.numel()
+        self.lo, self.n, self.per = shard_bounds(total, self.world, self.rank)
+        dev = model.flat.device
+        if mode == "allreduce":
+            self.m, self.v = model.like(), model.like()
+        else:
+            # moments only for this rank's shard (optimizer-state sharding)
+            self.m = torch.zeros(self.per, dtype=torch.float32, device=dev)
+            self.v = torch.zeros(self.per, dtype=torch.float32, device=dev)
+            self.g_shard = torch.zeros(self.per, dtype=torch.float32, device=dev)
+            self.padded = self.per * self.world
+        if mode == "fused_p2p":
+            if peer_ptrs is None:
+                raise RuntimeError("fused_p2p needs the peer-mapped addresses of every rank's parameter and gradient buffers")
+            self.peer_grads, self.peer_params = peer_ptrs
+        self.step_count = 0
+
+    # -- helpers --------------------------------------------------------------------------------
+    def _stream(self):
+        return capi.vp(torch.cuda.current_stream().cuda_stream)
+
+    def _adam_shard(self, iteration: int, grad_shard: torch.Tensor, grad_scale: float):
+        segs = group_segments(self.model.capacity, self.model.K, self.lo, self.n, self.lrs, skip_shN=(iteration <= 1000))
+        arr = (capi.AdamSegment * max(len(segs), 1))()
+        base = self.model.flat.data_ptr()
+        for i, (gi, off, cnt, lr) in enumerate(segs):
+            rel = off - self.lo
+            arr[i] = capi.AdamSegment(base + 4 * off, self.m.data_ptr() + 4 * rel, self.v.data_ptr() + 4 * rel,
+                                      grad_shard.data_ptr() + 4 * rel, cnt, lr)
+        capi.call("lfs_adam_step_segments", len(segs), arr, self.betas[0], self.betas[1], self.eps, self.step_count,
+                  float(grad_scale), self._stream())
+
+    # -- the exchange ---------------------------------------------------------------------------
+    def step(self, iteration: int, grad_scale: float | None = None, adam_fn=None):
+        """Sum gradients over ranks and apply Adam. grad_scale defaults to 1 / world (mean over the camera
+        batch). adam_fn(param_view, m_view, v_view, grad_view, lr, step_count, grad_scale) replaces the CUDA
+        Adam for host-only testing of the exchange logic."""
+        self.step_count += 1
+        gs = 1.0 / self.world if grad_scale is None else grad_scale
+        model, grads = self.model, self.grads
+        if self.mode == "allreduce":
+            if self.world > 1:
+                dist.all_reduce(grads.flat, group=self.group)
+            if adam_fn is None:
+                from .trainer import adam_step_splats
+                self.m.size = self.v.size = grads.size = model.size
+                adam_step_splats(model, self.m, self.v, grads, self.lrs, self.step_count, self.betas[0], self.betas[1], self.eps,
+                                 skip_shN=(iteration <= 1000), grad_scale=gs)
+            else:
+                for gi, off, cnt, lr in group_segments(model.capacity, model.K, 0, model.flat.numel(), self.lrs, iteration <= 1000):
+                    adam_fn(model.flat[off:off + cnt], self.m.flat[off:off + cnt], self.v.flat[off:off + cnt],
+                            grads.flat[off:off + cnt], lr, self.step_count, gs)
+            return
+        if self.mode == "sharded":
+            total = model.flat.numel()
+            if self.world > 1:
+                if self.padded != total:
+                    src = torch.zeros(self.padded, dtype=torch.float32, device=grads.flat.device)
+                    src[:total].copy_(grads.flat)
+                else:
+                    src = grads.flat
+                dist.reduce_scatter_tensor(self.g_shard, src, group=self.group)
+            else:
+                self.g_shard[: self.n].copy_(grads.flat[self.lo:self.lo + self.n])
+            if adam_fn is None:
+                self._adam_shard(iteration, self.g_shard, gs)
+            else:
+                for gi, off, cnt, lr in group_segments(model.capacity, model.K, self.lo, self.n, self.lrs, iteration <= 1000):
+                    rel = off - self.lo
+                    adam_fn(model.flat[off:off + cnt], self.m[rel:rel + cnt], self.v[rel:rel + cnt], self.g_shard[rel:rel + cnt],
+                            lr, self.step_count, gs)
+            if self.world > 1:
+                if self.padded != total:
+                    out = torch.empty(self.padded, dtype=torch.float32, device=model.flat.device)
+                    mine = torch.zeros(self.per, dtype=torch.float32, device=model.flat.device)
+                    mine[: self.n].copy_(model.flat[self.lo:self.lo + self.n])
+                    dist.all_gather_into_tensor(out, mine, group=self.group)
+                    model.flat.copy_(out[:total])
+                else:
+                    dist.all_gather_into_tensor(model.flat, model.flat[self.lo:self.lo + self.n].clone(), group=self.group)
+            return
+        if self.mode == "fused_p2p":
+            # stream-ordered rendezvous: every rank's backward has written its gradients
+            token = torch.zeros(1, device=model.flat.device)
+            dist.all_reduce(token, group=self.group)
+            segs = group_segments(model.capacity, model.K, self.lo, self.n, self.lrs, skip_shN=(iteration <= 1000))
+            arr = (capi.DpSegment * max(len(segs), 1))()
+            for i, (gi, off, cnt, lr) in enumerate(segs):
+                rel = off - self.lo
+                arr[i] = capi.DpSegment(off, cnt, self.m.data_ptr() + 4 * rel, self.v.data_ptr() + 4 * rel, lr)
+            order = [(self.rank + i) % self.world for i in range(self.world)]
+            pg = (C.c_void_p * self.world)(*[self.peer_grads[r] for r in order])
+            pp = (C.c_void_p * self.world)(*[self.peer_params[r] for r in order])
+            capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
+                      self.step_count, float(gs), self._stream())
+            # nobody may read parameters or overwrite gradients before every rank's kernel has finished
+            dist.all_reduce(token, group=self.group)
+            return
+        raise ValueError(self.mode)
+
+
+def symmetric_flat_buffers(numel: int, device, group=None):
+    """Two peer-mapped float32 buffers (parameters, gradients) of `numel` elements and the device addresses
+    of every rank's copies, via torch's symmetric memory (CUDA VMM over NVLink). Returns
+    (param_flat, grad_flat, (peer_grad_ptrs, peer_param_ptrs))."""
+    import torch.distributed._symmetric_memory as symm_mem
+    name = (group or dist.group.WORLD).group_name
+    p = symm_mem.empty(numel, dtype=torch.float32, device=device)
+    g = symm_mem.empty(numel, dtype=torch.float32, device=device)
+    hp = symm_mem.rendezvous(p, name)
+    hg = symm_mem.rendezvous(g, name)
+    p.zero_(); g.zero_()
+    return p, g, ([int(x) for x in hg.buffer_ptrs], [int(x) for x in hp.buffer_ptrs])

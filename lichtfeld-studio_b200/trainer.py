@@ -33,7 +33,7 @@ class SplatData:
     `capacity` rows) so that gradients / moments of all groups can be reduced or updated as one
     range. `size` rows are live; densification appends rows in place instead of torch.cat."""
 
-    def __init__(self, n: int, sh_coeffs: int, device, capacity: int | None = None):
+    def __init__(self, n: int, sh_coeffs: int, device, capacity: int | None = None, flat: torch.Tensor | None = None):
         self.K = int(sh_coeffs)
         # a multiple of 4 rows keeps every group's start (and each quaternion row) 16-byte aligned
         self.capacity = (int(capacity or n) + 3) // 4 * 4
@@ -41,7 +41,12 @@ class SplatData:
         self.device = device
         w = row_widths(self.K)
         self.row_floats = sum(w.values())
-        self.flat = torch.zeros(self.capacity * self.row_floats, dtype=torch.float32, device=device)
+        numel = self.capacity * self.row_floats
+        if flat is None:
+            flat = torch.zeros(numel, dtype=torch.float32, device=device)
+        elif flat.numel() != numel or flat.dtype != torch.float32 or not flat.is_contiguous():
+            raise RuntimeError(f"flat buffer must be a contiguous float32 tensor of {numel} elements")
+        self.flat = flat  # may be peer-mapped (symmetric) memory for the fused multi-GPU exchange
         self._full = {}
         off = 0
         for name in PARAM_NAMES:

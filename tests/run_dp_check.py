@@ -1,0 +1,90 @@
+"""Multi-GPU check of the data-parallel training step (run under torchrun, one rank per GPU):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 tests/run_dp_check.py
+
+Every rank renders its own camera; the three exchanges (NCCL all-reduce, NCCL reduce-scatter + sharded Adam
++ all-gather, fused peer-memory kernel) must leave the same parameters on every rank, equal to what one GPU
+gets by rendering all cameras itself and averaging the gradients. Not collected by pytest."""
+import datetime
+import importlib
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
+    pkg = importlib.import_module("lichtfeld-studio_b200")
+    synth, tr, dp = pkg.synth, pkg.trainer, pkg.dp
+    n, W, H, deg, steps = 30000, 320, 208, 3, 3
+    K = (deg + 1) ** 2
+    P = synth.make_gaussians(n, 0, "clusters", deg)
+    poses = synth.hemisphere_poses(16, 5.0)
+    Kmat = torch.from_numpy(synth.intrinsics(280.0, 280.0, W / 2, H / 2)).to(dev)
+    bg = torch.zeros(3, device=dev)
+    targets = [torch.rand(3, H, W, generator=torch.Generator().manual_seed(s)).to(dev) for s in range(steps * world)]
+
+    def cam(i):
+        return tr.Camera(torch.from_numpy(poses[i % 16]).to(dev), Kmat, W, H)
+
+    def run(mode):
+        cap = (n + 31) // 32 * 32
+        numel = cap * tr.SplatData(1, K, "cpu").row_floats
+        peer = None
+        if mode == "fused_p2p":
+            pf, gf, peer = dp.symmetric_flat_buffers(numel, dev)
+            model, grads = tr.SplatData(n, K, dev, cap, flat=pf).load(P), tr.SplatData(n, K, dev, cap, flat=gf)
+        else:
+            model, grads = tr.SplatData(n, K, dev, cap).load(P), tr.SplatData(n, K, dev, cap)
+        rast, lossfn = tr.Rasterizer(model, W, H, deg), tr.PhotometricLoss(W, H, dev)
+        if mode == "local":  # one GPU renders the whole batch and averages
+            m, v = model.like(), model.like()
+            for s in range(steps):
+                for r in range(world):
+                    out = rast.forward(cam(s * world + r), bg)
+                    _, vr = lossfn(out.image, targets[s * world + r])
+                    rast.backward(vr, grads, bg, accumulate=(r > 0))
+                tr.adam_step_splats(model, m, v, grads, LRS, s + 1, skip_shN=False, grad_scale=1.0 / world)
+            return model.flat.clone()
+        ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer)
+        for s in range(steps):
+            out = rast.forward(cam(s * world + rank), bg)
+            _, vr = lossfn(out.image, targets[s * world + rank])
+            rast.backward(vr, grads, bg)
+            ex.step(2000 + s)
+        torch.cuda.synchronize()
+        return model.flat.clone()
+
+    ref = run("local")
+    ok = True
+    for mode in ("allreduce", "sharded", "fused_p2p"):
+        try:
+            out = run(mode)
+        except Exception as e:  # report and keep the ranks in lock step
+            print(f"[rank {rank}] {mode}: FAILED {type(e).__name__}: {e}", flush=True)
+            ok = False
+            break
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(gathered[0], g) for g in gathered)
+        rel = float((out - ref).norm() / (ref - tr.SplatData(n, K, dev, (n + 31) // 32 * 32).load(P).flat).norm())
+        if rank == 0:
+            print(f"{mode}: identical on all ranks = {same}; |update - local update| / |local update| = {rel:.2e}", flush=True)
+        ok = ok and same and rel < 2e-3
+    if rank == 0:
+        print("DP CHECK", "OK" if ok else "FAILED", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

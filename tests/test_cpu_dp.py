@@ -1,0 +1,81 @@
+"""World-size-2 gloo test of the data-parallel exchange logic on CPU: shard bounds, group segments,
+reduce-scatter / all-gather with padding, and that the all-reduce and the sharded exchange leave the
+same parameters on every rank as a single-process Adam on the summed gradients. The CUDA Adam is replaced
+by the oracle's Adam through the adam_fn hook; the collectives and the segment arithmetic are the code
+that runs on the GPUs."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+
+
+def test_shard_bounds_and_segments(pkg):
+    dp = pkg.dp
+    for total, world in ((59 * 12, 2), (59 * 100, 8), (1000, 3), (7, 4)):
+        seen = 0
+        for r in range(world):
+            lo, n, per = dp.shard_bounds(total, world, r)
+            assert lo == min(r * per, total) and per % 4 == 0 and per * world >= total
+            seen += n
+        assert seen == total
+    segs = dp.group_segments(8, 4, 0, 8 * 23, LRS)
+    assert [s[0] for s in segs] == [0, 1, 2, 3, 4, 5] and sum(s[2] for s in segs) == 8 * 23
+    assert [s[1] for s in segs] == [0, 24, 48, 120, 144, 176]
+    segs = dp.group_segments(8, 4, 30, 100, LRS, skip_shN=True)
+    assert [(s[0], s[1], s[2]) for s in segs] == [(1, 30, 18), (3, 120, 10)]
+    assert dp.group_segments(8, 1, 0, 8 * 14, LRS)[2][0] == 3  # K = 1: the empty shN group is skipped
+
+
+def _worker(rank, world, port, mode, tmp):
+    sys.path.insert(0, str(ROOT))
+    import importlib
+    pkg = importlib.import_module("lichtfeld-studio_b200")
+    from oracle import oracle as orc
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tr, dp = pkg.trainer, pkg.dp
+    n, K = 37, 4  # capacity 40 -> 920 floats: not a multiple of 2 * 4 * anything convenient => exercises padding
+    model, grads = tr.SplatData(n, K, "cpu"), tr.SplatData(n, K, "cpu")
+    g0 = torch.Generator().manual_seed(0)
+    model.flat.copy_(torch.randn(model.flat.numel(), generator=g0))
+
+    def adam_fn(p, m, v, g, lr, step, gs):
+        pa, ma, va = p.numpy(), m.numpy(), v.numpy()
+        orc.adam_step(pa, ma, va, (g.numpy() * np.float32(gs)).astype(np.float32), lr, 0.9, 0.999, 1e-15, step)
+
+    ex = dp.GradExchange(model, grads, LRS, mode=mode)
+    for it in (5, 1001):  # first with the shN group skipped, then with it
+        gr = torch.Generator().manual_seed(100 * it + rank)
+        grads.flat.copy_(torch.randn(grads.flat.numel(), generator=gr))
+        ex.step(it, adam_fn=adam_fn)
+    torch.save(model.flat.clone(), os.path.join(tmp, f"{mode}_{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["allreduce", "sharded"])
+def test_exchange_modes_agree_under_gloo(pkg, orc, tmp_path, mode):
+    world = 2
+    port = 29600 + (os.getpid() % 200) + (0 if mode == "allreduce" else 1)
+    mp.spawn(_worker, args=(world, port, mode, str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(tmp_path / f"{mode}_{r}.pt") for r in range(world)]
+    assert torch.equal(outs[0], outs[1])  # identical parameters on every rank
+    # single-process reference: Adam on the summed gradients, mean over the batch of `world` cameras
+    tr, dp = pkg.trainer, pkg.dp
+    n, K = 37, 4
+    model = tr.SplatData(n, K, "cpu")
+    model.flat.copy_(torch.randn(model.flat.numel(), generator=torch.Generator().manual_seed(0)))
+    m, v = torch.zeros_like(model.flat), torch.zeros_like(model.flat)
+    for step, it in enumerate((5, 1001), start=1):
+        g = sum(torch.randn(model.flat.numel(), generator=torch.Generator().manual_seed(100 * it + r)) for r in range(world))
+        for gi, off, cnt, lr in dp.group_segments(model.capacity, K, 0, model.flat.numel(), LRS, it <= 1000):
+            orc.adam_step(model.flat[off:off + cnt].numpy(), m[off:off + cnt].numpy(), v[off:off + cnt].numpy(),
+                          (g[off:off + cnt].numpy() * np.float32(0.5)).astype(np.float32), lr, 0.9, 0.999, 1e-15, step)
+    assert torch.allclose(outs[0], model.flat, rtol=1e-6, atol=1e-7)
