@@ -61,6 +61,7 @@ struct RenderWs {
     int32_t *radii, *tiles, *offs, *tile_offsets, *last_ids;
     float *means2d, *depths, *accum;
     float4* records;
+    uint2* bounds;
     uint32_t *gkeys[2], *gvals[2], *tkeys[2], *tvals[2];
     SortScratch scratch;
     size_t bytes;
@@ -82,6 +83,7 @@ RenderWs carve_render(const lfs_render_config& cfg, void* base) {
     w.offs = c.take<int32_t>(N);
     for (int k = 0; k < 2; ++k) { w.gkeys[k] = c.take<uint32_t>(N); w.gvals[k] = c.take<uint32_t>(N); }
     w.records = c.take<float4>(N * 4);
+    w.bounds = c.take<uint2>(N);
     w.accum = c.take<float>(N * 16);
     for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
     w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
@@ -207,6 +209,7 @@ size_t lfs_rasterize_workspace_bytes(int N) {
     Carver c(nullptr);
     c.take<CamDev>(1);
     c.take<float4>((size_t)N * 4);
+    c.take<uint2>((size_t)N);
     c.take<float>((size_t)N * 16);
     return c.total();
 }
@@ -235,11 +238,12 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, const f
     Carver c(workspace);
     CamDev* cam = c.take<CamDev>(1);
     float4* records = c.take<float4>((size_t)N * 4);
+    uint2* bounds = c.take<uint2>((size_t)N);
     rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
     if (rc != LFS_OK) return rc;
-    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, nullptr, S(stream));
+    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, bounds, nullptr, S(stream));
     if (rc != LFS_OK) return rc;
-    RasterArgs a{cam, records, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
+    RasterArgs a{cam, records, bounds, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
                  nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model};
     return launch_raster_fwd(a, renders, alphas, last_ids, S(stream));
 }
@@ -261,12 +265,13 @@ int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, const f
     Carver c(workspace);
     CamDev* cam = c.take<CamDev>(1);
     float4* records = c.take<float4>((size_t)N * 4);
+    uint2* bounds = c.take<uint2>((size_t)N);
     float* accum = c.take<float>((size_t)N * 16);
     rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
     if (rc != LFS_OK) return rc;
-    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, reinterpret_cast<float4*>(accum), S(stream));
+    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, bounds, reinterpret_cast<float4*>(accum), S(stream));
     if (rc != LFS_OK) return rc;
-    RasterArgs a{cam, records, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
+    RasterArgs a{cam, records, bounds, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
                  nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model};
     rc = launch_raster_bwd(a, render_alphas, last_ids, v_render_colors, v_render_alphas, accum, S(stream));
     if (rc != LFS_OK) return rc;
@@ -463,7 +468,7 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
     const ProjParams pp = make_proj_params(cfg->eps2d, cfg->near_plane, cfg->far_plane, cfg->radius_clip, cfg->ut);
     rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, cfg->camera_model, cfg->tile_size, tw,
-                             th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records,
+                             th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records, w.bounds,
                              reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
     if (rc != LFS_OK) return rc;
     TileListArgs a{};
@@ -476,7 +481,7 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     a.tile_offsets = w.tile_offsets; a.scratch = w.scratch;
     rc = build_tile_lists(a, st);
     if (rc != LFS_OK) return rc;
-    RasterArgs ra{w.cam, w.records, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
+    RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
                   cfg->image_width, cfg->image_height, tw, th, cfg->camera_model};
     rc = launch_raster_fwd(ra, render, alpha, w.last_ids, st);
     if (rc != LFS_OK) return rc;
@@ -496,7 +501,7 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
     cudaStream_t st = S(stream);
     const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
     const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
-    RasterArgs ra{w.cam, w.records, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
+    RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
                   cfg->image_width, cfg->image_height, tw, th, cfg->camera_model};
     rc = launch_raster_bwd(ra, alpha, w.last_ids, v_render, v_alpha, w.accum, st);
     if (rc != LFS_OK) return rc;

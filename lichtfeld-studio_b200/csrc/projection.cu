@@ -269,10 +269,54 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
 // Rasterizer record from activated parameters: M = diag(1/s) R^T with the quaternion
 // re-normalised, gro = M (ray_origin - mean).
 // ---------------------------------------------------------------------------------------------
+// Also computes the exact screen-space bounding box (in whole pixels, inclusive, clamped to 16 bits) of the
+// pixels whose ray can reach alpha >= 1/255: alpha = opacity * exp(-d^2/2) with d the distance from the ray to
+// the centre in the whitened frame, so those rays are exactly the ones that hit the ellipsoid
+// (x-mu)^T M^T M (x-mu) <= rho^2, rho^2 = 2 ln(255 opacity). Under a pinhole camera its outline is a conic whose
+// axis-aligned tangents follow from the dual quadric B = mu_c mu_c^T - Sigma_c:
+// x_n = (B02 -+ sqrt(B02^2 - B00 B22)) / B22 (same with index 1 for y). A margin keeps the box conservative under
+// rounding; when the ellipsoid reaches the camera plane (B22 <= 0) or the camera is not a pinhole the box is the
+// whole image. The rasterizer uses it only to skip (warp patch, Gaussian) pairs that cannot contribute.
 __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw, float qx, float qy, float qz,
-                                            f3 scale, float r, float g, float b, float opacity, float4* rec) {
+                                            f3 scale, float r, float g, float b, float opacity, float4* rec, uint2& box) {
     float R[9], inv_norm, qn[4];
     quat_to_rotmat_renorm(qw, qx, qy, qz, R, inv_norm, qn);
+    box = make_uint2(0xFFFF0000u, 0xFFFF0000u);  // (lo | hi << 16) per axis: everything
+    if (cam.model == LFS_PINHOLE) {
+        const float rho2 = 2.0f * (logf(fmaxf(255.0f * opacity, 1.0f)) + 0.03f);
+        // V = R_c R with R_c = Rinv^T ; Sigma_c = rho2 V S^2 V^T ; mu_c = R_c mean + t
+        float V[9];
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+#pragma unroll
+            for (int c = 0; c < 3; ++c)
+                V[a * 3 + c] = cam.Rinv[0 * 3 + a] * R[0 * 3 + c] + cam.Rinv[1 * 3 + a] * R[1 * 3 + c] + cam.Rinv[2 * 3 + a] * R[2 * 3 + c];
+        const float s2[3] = {rho2 * scale.x * scale.x, rho2 * scale.y * scale.y, rho2 * scale.z * scale.z};
+        const float mc[3] = {cam.Rinv[0] * mean.x + cam.Rinv[3] * mean.y + cam.Rinv[6] * mean.z + cam.tx,
+                             cam.Rinv[1] * mean.x + cam.Rinv[4] * mean.y + cam.Rinv[7] * mean.z + cam.ty,
+                             cam.Rinv[2] * mean.x + cam.Rinv[5] * mean.y + cam.Rinv[8] * mean.z + cam.tz};
+        auto sig = [&](int a, int c) { return V[a * 3] * s2[0] * V[c * 3] + V[a * 3 + 1] * s2[1] * V[c * 3 + 1] + V[a * 3 + 2] * s2[2] * V[c * 3 + 2]; };
+        const float B22 = mc[2] * mc[2] - sig(2, 2);
+        if (mc[2] > 0.f && B22 > 0.02f * mc[2] * mc[2]) {
+            uint32_t packed[2];
+            const float f[2] = {cam.fx, cam.fy}, c0[2] = {cam.cx, cam.cy};
+#pragma unroll
+            for (int ax = 0; ax < 2; ++ax) {
+                const float Ba2 = mc[ax] * mc[2] - sig(ax, 2);
+                const float Baa = mc[ax] * mc[ax] - sig(ax, ax);
+                const float disc = sqrtf(fmaxf(0.f, Ba2 * Ba2 - Baa * B22));
+                const float lo_n = (Ba2 - disc) / B22, hi_n = (Ba2 + disc) / B22;
+                const float fl = fabsf(f[ax]);
+                const float lo_px = fminf(f[ax] * lo_n, f[ax] * hi_n) + c0[ax], hi_px = fmaxf(f[ax] * lo_n, f[ax] * hi_n) + c0[ax];
+                const float margin = 0.75f + 2e-4f * (fabsf(lo_px) + fabsf(hi_px)) + 1e-3f * fl * (hi_n - lo_n);
+                // pixel j has its centre at j + 0.5
+                const float lo_j = floorf(lo_px - 0.5f - margin), hi_j = ceilf(hi_px - 0.5f + margin);
+                const uint32_t lo_u = (uint32_t)fminf(fmaxf(lo_j, 0.f), 65535.f), hi_u = (uint32_t)fminf(fmaxf(hi_j, 0.f), 65535.f);
+                packed[ax] = lo_u | (hi_u << 16);
+            }
+            box = make_uint2(packed[0], packed[1]);
+        }
+    }
     const float is[3] = {1.0f / scale.x, 1.0f / scale.y, 1.0f / scale.z};
     float M[9];
 #pragma unroll
@@ -292,17 +336,19 @@ __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw
 __global__ void __launch_bounds__(256) pack_records_kernel(
     int N, const float* __restrict__ means, const float* __restrict__ quats, const float* __restrict__ scales,
     const float* __restrict__ colors, const float* __restrict__ opacities, const CamDev* __restrict__ cams,
-    float4* __restrict__ records, float4* __restrict__ accum) {
+    float4* __restrict__ records, uint2* __restrict__ bounds, float4* __restrict__ accum) {
     const CamDev cam = cams[0];
     for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
         const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
         const f3 scale{scales[g * 3], scales[g * 3 + 1], scales[g * 3 + 2]};
         const float4 q = reinterpret_cast<const float4*>(quats)[g];
         float4 rec[4];
+        uint2 box;
         make_record(cam, mean, q.x, q.y, q.z, q.w, scale, colors[g * 3], colors[g * 3 + 1], colors[g * 3 + 2],
-                    opacities[g], rec);
+                    opacities[g], rec, box);
 #pragma unroll
         for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
+        bounds[g] = box;
         if (accum) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) accum[(size_t)g * 4 + k] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -311,10 +357,10 @@ __global__ void __launch_bounds__(256) pack_records_kernel(
 }
 
 int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
-                        const float* opacities, const CamDev* cam, float4* records, float4* accum, cudaStream_t st) {
+                        const float* opacities, const CamDev* cam, float4* records, uint2* bounds, float4* accum, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("pack_records", st);
-    pack_records_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, means, quats, scales, colors, opacities, cam, records, accum);
+    pack_records_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, means, quats, scales, colors, opacities, cam, records, bounds, accum);
     return check_launch("pack_records");
 }
 
@@ -331,7 +377,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
     uint32_t tw, uint32_t th,
     int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths,
     int32_t* __restrict__ tiles, uint32_t* __restrict__ sort_keys, uint32_t* __restrict__ sort_vals,
-    float4* __restrict__ records, float4* __restrict__ accum, int32_t* __restrict__ n_visible) {
+    float4* __restrict__ records, uint2* __restrict__ bounds, float4* __restrict__ accum, int32_t* __restrict__ n_visible) {
     // Each warp handles 32 consecutive Gaussians per iteration. Their higher-order SH rows ((K-1)*3 floats
     // each, contiguous in memory) are fetched as one coalesced run into shared memory when any of the 32
     // is visible, and every visible lane then reads its own row from there.
@@ -403,9 +449,11 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
             for (int c = 0; c < 3; ++c) rgb[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
 
             float4 rec[4];
-            make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, rec);
+            uint2 box;
+            make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, rec, box);
 #pragma unroll
             for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
+            bounds[g] = box;
 #pragma unroll
             for (int k = 0; k < 4; ++k) accum[(size_t)g * 4 + k] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -418,7 +466,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
                         int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
-                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, float4* accum,
+                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint2* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     const int grid = grid_for(N, 256);
@@ -433,12 +481,12 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
         project_pack_kernel<LFS_PINHOLE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
                                                                p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,
                                                                tw, th, radii, means2d, depths, tiles, sort_keys,
-                                                               sort_vals, records, accum, n_visible);
+                                                               sort_vals, records, bounds, accum, n_visible);
     else
         project_pack_kernel<LFS_FISHEYE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
                                                                p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,
                                                                tw, th, radii, means2d, depths, tiles, sort_keys,
-                                                               sort_vals, records, accum, n_visible);
+                                                               sort_vals, records, bounds, accum, n_visible);
     return check_launch("project_pack");
 }
 

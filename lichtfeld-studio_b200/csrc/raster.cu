@@ -37,6 +37,18 @@ __device__ __forceinline__ void pixel_of_thread(int tile, int tw, int& i, int& j
     j = (tile % tw) * 16 + lx;
 }
 
+// Warp patch of 8x4 pixels: inclusive pixel bounds packed like the Gaussian boxes (lo | hi << 16).
+__device__ __forceinline__ void warp_patch(int tile, int tw, uint32_t& px, uint32_t& py) {
+    const int warp = threadIdx.x >> 5;
+    const uint32_t x0 = (tile % tw) * 16 + (warp & 1) * 8, y0 = (tile / tw) * 16 + (warp >> 1) * 4;
+    px = x0 | ((x0 + 7) << 16);
+    py = y0 | ((y0 + 3) << 16);
+}
+__device__ __forceinline__ bool box_overlaps(uint2 box, uint32_t px, uint32_t py) {
+    return (box.x & 0xFFFFu) <= (px >> 16) && (box.x >> 16) >= (px & 0xFFFFu) &&
+           (box.y & 0xFFFFu) <= (py >> 16) && (box.y >> 16) >= (py & 0xFFFFu);
+}
+
 __device__ __forceinline__ int32_t load_count(const int32_t* n_dev, int64_t n_host) {
     return n_dev ? *n_dev : (int32_t)n_host;
 }
@@ -44,12 +56,14 @@ __device__ __forceinline__ int32_t load_count(const int32_t* n_dev, int64_t n_ho
 // ---------------------------------------------------------------------------------------------
 template <int MODEL>
 __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
-    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint32_t* __restrict__ flatten_ids,
+    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint2* __restrict__ bounds,
+    const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
     float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids) {
     __shared__ float4 srec[kBlock * 4];
     __shared__ float sthr[kBlock];
+    __shared__ uint2 sbox[kBlock];
 
     if (overflow && *overflow) return;
     const int tile = blockIdx.x;
@@ -60,6 +74,8 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     f3 d;
     const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
     bool done = !inside || !ray_ok;
+    uint32_t patch_x, patch_y;
+    warp_patch(tile, tw, patch_x, patch_y);
 
     const int32_t n_isects = load_count(n_isects_dev, n_isects_host);
     const int32_t range_start = tile_offsets[tile];
@@ -82,11 +98,24 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
                 srec[q] = v;
                 // exponent below which opacity * exp(p) < 1/255 for certain
                 if (part == 3) sthr[e] = -__logf(255.0f * v.w) - kRejectMargin;
+                if (part == 0) sbox[e] = bounds[g];
             }
         }
         __syncthreads();
         if (!__all_sync(0xffffffffu, done)) {
-            for (int t = 0; t < batch_size && !done; ++t) {
+            // entries of this batch whose box overlaps this warp's 8x4 patch: one ballot word per 32 entries
+            uint32_t live[kBlock / 32];
+#pragma unroll
+            for (int w = 0; w < kBlock / 32; ++w) {
+                const int e = w * 32 + (threadIdx.x & 31);
+                live[w] = __ballot_sync(0xffffffffu, e < batch_size && box_overlaps(sbox[e], patch_x, patch_y));
+            }
+#pragma unroll
+            for (int w = 0; w < kBlock / 32; ++w) {
+              uint32_t bits = live[w];
+              while (bits && !done) {
+                const int t = w * 32 + __ffs(bits) - 1;
+                bits &= bits - 1;
                 const float4 r0 = srec[t * 4 + 0], r1 = srec[t * 4 + 1], r2 = srec[t * 4 + 2];
                 const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
                 const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
@@ -108,6 +137,7 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
                 pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
                 cur_idx = (uint32_t)(batch_start + t);
                 T = next_T;
+              }
             }
         }
     }
@@ -164,7 +194,8 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16]) {
 
 template <int MODEL>
 __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
-    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint32_t* __restrict__ flatten_ids,
+    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint2* __restrict__ bounds,
+    const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
     const float* __restrict__ render_alphas, const int32_t* __restrict__ last_ids,
@@ -172,6 +203,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     __shared__ float4 srec[kBlock * 4];
     __shared__ float sthr[kBlock];
     __shared__ uint32_t sid[kBlock];
+    __shared__ uint2 sbox[kBlock];
     __shared__ __align__(16) float sacc[kBlock * 16];
     __shared__ int stouched[kBlock];
 
@@ -185,6 +217,8 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
     const bool active = inside && ray_ok;
     const int pid = min(i * W + j, W * H - 1);
+    uint32_t patch_x, patch_y;
+    warp_patch(tile, tw, patch_x, patch_y);
 
     const int32_t n_isects = load_count(n_isects_dev, n_isects_host);
     const int32_t range_start = tile_offsets[tile];
@@ -217,10 +251,25 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                 const float4 v = records[(size_t)g * 4 + part];
                 srec[q] = v;
                 if (part == 3) { sthr[e] = -__logf(255.0f * v.w) - kRejectMargin; sid[e] = g; }
+                if (part == 0) sbox[e] = bounds[g];
             }
         }
         __syncthreads();
-        for (int t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
+        // entries (back to front) that no pixel of this warp reaches (beyond its last contributor) or whose
+        // box misses this warp's 8x4 patch are dropped up front: one ballot word per 32 entries
+        const int t_begin = max(0, batch_end - warp_bin_final);
+        uint32_t live[kBlock / 32];
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w) {
+            const int e = w * 32 + lane;
+            live[w] = __ballot_sync(0xffffffffu, e >= t_begin && e < batch_size && box_overlaps(sbox[e], patch_x, patch_y));
+        }
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w) {
+          uint32_t bits = live[w];
+          while (bits) {
+            const int t = w * 32 + __ffs(bits) - 1;
+            bits &= bits - 1;
             bool valid = active && (batch_end - t <= bin_final);
             float ux, uy, uz, cx, cy, cz, uu;
             float4 r0, r1, r2;
@@ -283,6 +332,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
             const float total = warp_reduce16(v);
             if ((lane & 1) == 0) atomicAdd(&sacc[t * 16 + (lane >> 1)], total);
             if (lane == 0) stouched[t] = 1;
+          }
         }
         __syncthreads();
         // flush this batch's sums: four 16-byte reductions per touched Gaussian
@@ -471,11 +521,11 @@ int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t
     if (n_tiles == 0) return LFS_OK;
     LFS_TIMED("raster_fwd", st);
     if (a.model == LFS_PINHOLE)
-        raster_fwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+        raster_fwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
                                                                    a.H, a.tw, n_tiles, render, alphas, last_ids);
     else
-        raster_fwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+        raster_fwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
                                                                    a.H, a.tw, n_tiles, render, alphas, last_ids);
     return check_launch("raster_fwd");
@@ -487,12 +537,12 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     if (n_tiles == 0) return LFS_OK;
     LFS_TIMED("raster_bwd", st);
     if (a.model == LFS_PINHOLE)
-        raster_bwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+        raster_bwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
                                                                    a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
                                                                    v_alphas, accum);
     else
-        raster_bwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.flatten_ids, a.tile_offsets,
+        raster_bwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
                                                                    a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
                                                                    v_alphas, accum);
