@@ -61,7 +61,7 @@ struct RenderWs {
     int32_t *radii, *tiles, *offs, *tile_offsets, *last_ids;
     float *means2d, *depths, *accum;
     float4* records;
-    uint2* bounds;
+    uint4* bounds;
     uint32_t *gkeys[2], *gvals[2], *tkeys[2], *tvals[2];
     SortScratch scratch;
     size_t bytes;
@@ -83,7 +83,7 @@ RenderWs carve_render(const lfs_render_config& cfg, void* base) {
     w.offs = c.take<int32_t>(N);
     for (int k = 0; k < 2; ++k) { w.gkeys[k] = c.take<uint32_t>(N); w.gvals[k] = c.take<uint32_t>(N); }
     w.records = c.take<float4>(N * 4);
-    w.bounds = c.take<uint2>(N);
+    w.bounds = c.take<uint4>(N);
     w.accum = c.take<float>(N * 16);
     for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
     w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
@@ -209,7 +209,7 @@ size_t lfs_rasterize_workspace_bytes(int N) {
     Carver c(nullptr);
     c.take<CamDev>(1);
     c.take<float4>((size_t)N * 4);
-    c.take<uint2>((size_t)N);
+    c.take<uint4>((size_t)N);
     c.take<float>((size_t)N * 16);
     return c.total();
 }
@@ -238,7 +238,7 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, const f
     Carver c(workspace);
     CamDev* cam = c.take<CamDev>(1);
     float4* records = c.take<float4>((size_t)N * 4);
-    uint2* bounds = c.take<uint2>((size_t)N);
+    uint4* bounds = c.take<uint4>((size_t)N);
     rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
     if (rc != LFS_OK) return rc;
     rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, bounds, nullptr, S(stream));
@@ -265,7 +265,7 @@ int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, const f
     Carver c(workspace);
     CamDev* cam = c.take<CamDev>(1);
     float4* records = c.take<float4>((size_t)N * 4);
-    uint2* bounds = c.take<uint2>((size_t)N);
+    uint4* bounds = c.take<uint4>((size_t)N);
     float* accum = c.take<float>((size_t)N * 16);
     rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
     if (rc != LFS_OK) return rc;

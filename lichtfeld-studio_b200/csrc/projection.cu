@@ -278,10 +278,12 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
 // rounding; when the ellipsoid reaches the camera plane (B22 <= 0) or the camera is not a pinhole the box is the
 // whole image. The rasterizer uses it only to skip (warp patch, Gaussian) pairs that cannot contribute.
 __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw, float qx, float qy, float qz,
-                                            f3 scale, float r, float g, float b, float opacity, float4* rec, uint2& box) {
+                                            f3 scale, float r, float g, float b, float opacity, float4* rec, uint4& box) {
     float R[9], inv_norm, qn[4];
     quat_to_rotmat_renorm(qw, qx, qy, qz, R, inv_norm, qn);
-    box = make_uint2(0xFFFF0000u, 0xFFFF0000u);  // (lo | hi << 16) per axis: everything
+    // exponent below which opacity * exp(p) < 1/255 for certain, as float bits in .z
+    const uint32_t thr_bits = __float_as_uint(-logf(fmaxf(255.0f * opacity, 1e-30f)) - 0.02f);
+    box = make_uint4(0xFFFF0000u, 0xFFFF0000u, thr_bits, 0u);  // (lo | hi << 16) per axis: everything
     if (cam.model == LFS_PINHOLE) {
         const float rho2 = 2.0f * (logf(fmaxf(255.0f * opacity, 1.0f)) + 0.03f);
         // V = R_c R with R_c = Rinv^T ; Sigma_c = rho2 V S^2 V^T ; mu_c = R_c mean + t
@@ -314,7 +316,7 @@ __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw
                 const uint32_t lo_u = (uint32_t)fminf(fmaxf(lo_j, 0.f), 65535.f), hi_u = (uint32_t)fminf(fmaxf(hi_j, 0.f), 65535.f);
                 packed[ax] = lo_u | (hi_u << 16);
             }
-            box = make_uint2(packed[0], packed[1]);
+            box = make_uint4(packed[0], packed[1], thr_bits, 0u);
         }
     }
     const float is[3] = {1.0f / scale.x, 1.0f / scale.y, 1.0f / scale.z};
@@ -336,14 +338,14 @@ __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw
 __global__ void __launch_bounds__(256) pack_records_kernel(
     int N, const float* __restrict__ means, const float* __restrict__ quats, const float* __restrict__ scales,
     const float* __restrict__ colors, const float* __restrict__ opacities, const CamDev* __restrict__ cams,
-    float4* __restrict__ records, uint2* __restrict__ bounds, float4* __restrict__ accum) {
+    float4* __restrict__ records, uint4* __restrict__ bounds, float4* __restrict__ accum) {
     const CamDev cam = cams[0];
     for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
         const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
         const f3 scale{scales[g * 3], scales[g * 3 + 1], scales[g * 3 + 2]};
         const float4 q = reinterpret_cast<const float4*>(quats)[g];
         float4 rec[4];
-        uint2 box;
+        uint4 box;
         make_record(cam, mean, q.x, q.y, q.z, q.w, scale, colors[g * 3], colors[g * 3 + 1], colors[g * 3 + 2],
                     opacities[g], rec, box);
 #pragma unroll
@@ -357,7 +359,7 @@ __global__ void __launch_bounds__(256) pack_records_kernel(
 }
 
 int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
-                        const float* opacities, const CamDev* cam, float4* records, uint2* bounds, float4* accum, cudaStream_t st) {
+                        const float* opacities, const CamDev* cam, float4* records, uint4* bounds, float4* accum, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("pack_records", st);
     pack_records_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, means, quats, scales, colors, opacities, cam, records, bounds, accum);
@@ -377,7 +379,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
     uint32_t tw, uint32_t th,
     int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths,
     int32_t* __restrict__ tiles, uint32_t* __restrict__ sort_keys, uint32_t* __restrict__ sort_vals,
-    float4* __restrict__ records, uint2* __restrict__ bounds, float4* __restrict__ accum, int32_t* __restrict__ n_visible) {
+    float4* __restrict__ records, uint4* __restrict__ bounds, float4* __restrict__ accum, int32_t* __restrict__ n_visible) {
     // Each warp handles 32 consecutive Gaussians per iteration. Their higher-order SH rows ((K-1)*3 floats
     // each, contiguous in memory) are fetched as one coalesced run into shared memory when any of the 32
     // is visible, and every visible lane then reads its own row from there.
@@ -449,7 +451,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
             for (int c = 0; c < 3; ++c) rgb[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
 
             float4 rec[4];
-            uint2 box;
+            uint4 box;
             make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, rec, box);
 #pragma unroll
             for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
@@ -466,7 +468,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
                         int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
-                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint2* bounds, float4* accum,
+                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     const int grid = grid_for(N, 256);

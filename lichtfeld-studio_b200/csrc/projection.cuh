@@ -26,11 +26,11 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
                          float* means2d, float* depths, float* conics, float* compensations, cudaStream_t st);
 
 int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
-                        const float* opacities, const CamDev* cam, float4* records, uint2* bounds, float4* accum, cudaStream_t st);
+                        const float* opacities, const CamDev* cam, float4* records, uint4* bounds, float4* accum, cudaStream_t st);
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
                         int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
-                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint2* bounds, float4* accum,
+                        int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st);
 
 int launch_tile_count(int64_t total, const float* means2d, const int32_t* radii, int tile_size, int tw, int th,

@@ -26,7 +26,6 @@ namespace {
 
 constexpr int kBlock = 256;
 constexpr float kAlphaMin = 1.f / 255.f;
-constexpr float kRejectMargin = 0.02f;  // slack (in units of the exponent) of the exp-free rejection test
 
 __device__ __forceinline__ void pixel_of_thread(int tile, int tw, int& i, int& j) {
     // warps tile the 16x16 block as 2 x 4 patches of 8 x 4 pixels
@@ -54,16 +53,70 @@ __device__ __forceinline__ int32_t load_count(const int32_t* n_dev, int64_t n_ho
 }
 
 // ---------------------------------------------------------------------------------------------
+// Staging of one batch of tile entries into shared memory with 16-byte asynchronous copies
+// (cp.async: the entries are a gather by Gaussian index, so each copy is one quarter record or one
+// bounds row). Two buffers: batch b+1 is in flight while batch b is being blended.
+template <int BATCH>
+struct Stage {
+    float4 rec[BATCH * 4];  // packed records
+    uint4 box[BATCH];       // (x box, y box, rejection exponent as float bits, unused)
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// Each thread owns kParts quarter-record slots q = k * kBlock + tid of a batch: entry q >> 2, part q & 3.
+template <int BATCH>
+struct StageIds {
+    static constexpr int kParts = BATCH * 4 / kBlock;
+    uint32_t g[kParts];
+};
+
+// ids of the batch whose first list position is `first` and which runs forward (step +1) or backward (-1)
+template <int BATCH>
+__device__ __forceinline__ void load_ids(StageIds<BATCH>& ids, const uint32_t* __restrict__ flatten_ids, int32_t first,
+                                         int step, int batch_size) {
+#pragma unroll
+    for (int k = 0; k < StageIds<BATCH>::kParts; ++k) {
+        const int e = (k * kBlock + threadIdx.x) >> 2;
+        ids.g[k] = e < batch_size ? flatten_ids[first + step * e] : 0u;
+    }
+}
+
+template <int BATCH>
+__device__ __forceinline__ void issue_stage(Stage<BATCH>& st, uint32_t* sid, const StageIds<BATCH>& ids,
+                                            const float4* __restrict__ records, const uint4* __restrict__ bounds,
+                                            int batch_size) {
+#pragma unroll
+    for (int k = 0; k < StageIds<BATCH>::kParts; ++k) {
+        const int q = k * kBlock + threadIdx.x;
+        const int e = q >> 2, part = q & 3;
+        if (e < batch_size) {
+            cp_async16(&st.rec[q], records + (size_t)ids.g[k] * 4 + part);
+            if (part == 0) {
+                cp_async16(&st.box[e], bounds + ids.g[k]);
+                if (sid) sid[e] = ids.g[k];
+            }
+        }
+    }
+    cp_async_commit();
+}
+
+// ---------------------------------------------------------------------------------------------
 template <int MODEL>
 __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
-    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint2* __restrict__ bounds,
+    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
     float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids) {
-    __shared__ float4 srec[kBlock * 4];
-    __shared__ float sthr[kBlock];
-    __shared__ uint2 sbox[kBlock];
+    constexpr int BATCH = 256;
+    __shared__ Stage<BATCH> stage[2];
 
     if (overflow && *overflow) return;
     const int tile = blockIdx.x;
@@ -80,67 +133,77 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     const int32_t n_isects = load_count(n_isects_dev, n_isects_host);
     const int32_t range_start = tile_offsets[tile];
     const int32_t range_end = (tile == n_tiles - 1) ? n_isects : tile_offsets[tile + 1];
+    const int n_batches = (range_end - range_start + BATCH - 1) / BATCH;
 
     float T = 1.0f;
     uint32_t cur_idx = 0;
     float pr = 0.f, pg = 0.f, pb = 0.f;
 
-    for (int32_t batch_start = range_start; batch_start < range_end; batch_start += kBlock) {
-        if (__syncthreads_count(done) >= kBlock) break;
-        const int32_t batch_size = min(kBlock, range_end - batch_start);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int q = k * kBlock + threadIdx.x;
-            const int e = q >> 2, part = q & 3;
-            if (e < batch_size) {
-                const uint32_t g = flatten_ids[batch_start + e];
-                const float4 v = records[(size_t)g * 4 + part];
-                srec[q] = v;
-                // exponent below which opacity * exp(p) < 1/255 for certain
-                if (part == 3) sthr[e] = -__logf(255.0f * v.w) - kRejectMargin;
-                if (part == 0) sbox[e] = bounds[g];
-            }
+    StageIds<BATCH> ids;
+    if (n_batches > 0) {
+        load_ids(ids, flatten_ids, range_start, 1, min(BATCH, range_end - range_start));
+        issue_stage(stage[0], nullptr, ids, records, bounds, min(BATCH, range_end - range_start));
+        if (n_batches > 1) load_ids(ids, flatten_ids, range_start + BATCH, 1, min(BATCH, range_end - range_start - BATCH));
+    }
+    for (int b = 0; b < n_batches; ++b) {
+        const int32_t batch_start = range_start + b * BATCH;
+        const int32_t batch_size = min(BATCH, range_end - batch_start);
+        // next batch into the other buffer (its previous contents were consumed before the barrier that ended
+        // the previous iteration), then the ids of the batch after that
+        if (b + 1 < n_batches) {
+            issue_stage(stage[(b + 1) & 1], nullptr, ids, records, bounds, min(BATCH, range_end - batch_start - BATCH));
+            if (b + 2 < n_batches)
+                load_ids(ids, flatten_ids, batch_start + 2 * BATCH, 1, min(BATCH, range_end - batch_start - 2 * BATCH));
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
-        __syncthreads();
+        // everyone's copies of batch b have landed; leave early when every pixel of the tile is finished
+        if (__syncthreads_count(done) >= kBlock) break;
+        const Stage<BATCH>& st = stage[b & 1];
         if (!__all_sync(0xffffffffu, done)) {
             // entries of this batch whose box overlaps this warp's 8x4 patch: one ballot word per 32 entries
-            uint32_t live[kBlock / 32];
+            uint32_t live[BATCH / 32];
 #pragma unroll
-            for (int w = 0; w < kBlock / 32; ++w) {
+            for (int w = 0; w < BATCH / 32; ++w) {
                 const int e = w * 32 + (threadIdx.x & 31);
-                live[w] = __ballot_sync(0xffffffffu, e < batch_size && box_overlaps(sbox[e], patch_x, patch_y));
+                bool ov = false;
+                if (e < batch_size) { const uint4 bx = st.box[e]; ov = box_overlaps(make_uint2(bx.x, bx.y), patch_x, patch_y); }
+                live[w] = __ballot_sync(0xffffffffu, ov);
             }
 #pragma unroll
-            for (int w = 0; w < kBlock / 32; ++w) {
-              uint32_t bits = live[w];
-              while (bits && !done) {
-                const int t = w * 32 + __ffs(bits) - 1;
-                bits &= bits - 1;
-                const float4 r0 = srec[t * 4 + 0], r1 = srec[t * 4 + 1], r2 = srec[t * 4 + 2];
-                const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
-                const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
-                const float uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
-                const float cx = uy * r2.w - r1.w * uz;
-                const float cy = uz * r0.w - r2.w * ux;
-                const float cz = ux * r1.w - r0.w * uy;
-                const float cc = cx * cx + cy * cy + cz * cz;
-                const float uu = ux * ux + uy * uy + uz * uz;
-                // power = -0.5 cc / uu ; reject when power < thr  <=>  cc > -2 thr uu
-                if (cc > -2.0f * sthr[t] * uu) continue;
-                const float4 r3 = srec[t * 4 + 3];
-                const float power = -0.5f * __fdividef(cc, fmaxf(uu, 1e-37f));
-                const float alpha = fminf(0.999f, r3.w * __expf(power));
-                if (alpha < kAlphaMin) continue;
-                const float next_T = T * (1.0f - alpha);
-                if (next_T <= 1e-4f) { done = true; break; }
-                const float vis = alpha * T;
-                pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
-                cur_idx = (uint32_t)(batch_start + t);
-                T = next_T;
-              }
+            for (int w = 0; w < BATCH / 32; ++w) {
+                uint32_t bits = live[w];
+                while (bits && !done) {
+                    const int t = w * 32 + __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    const float4 r0 = st.rec[t * 4 + 0], r1 = st.rec[t * 4 + 1], r2 = st.rec[t * 4 + 2];
+                    const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
+                    const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
+                    const float uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
+                    const float cx = uy * r2.w - r1.w * uz;
+                    const float cy = uz * r0.w - r2.w * ux;
+                    const float cz = ux * r1.w - r0.w * uy;
+                    const float cc = cx * cx + cy * cy + cz * cz;
+                    const float uu = ux * ux + uy * uy + uz * uz;
+                    // power = -0.5 cc / uu ; reject when power < thr  <=>  cc > -2 thr uu
+                    if (cc > -2.0f * __uint_as_float(st.box[t].z) * uu) continue;
+                    const float4 r3 = st.rec[t * 4 + 3];
+                    const float power = -0.5f * __fdividef(cc, fmaxf(uu, 1e-37f));
+                    const float alpha = fminf(0.999f, r3.w * __expf(power));
+                    if (alpha < kAlphaMin) continue;
+                    const float next_T = T * (1.0f - alpha);
+                    if (next_T <= 1e-4f) { done = true; break; }
+                    const float vis = alpha * T;
+                    pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
+                    cur_idx = (uint32_t)(batch_start + t);
+                    T = next_T;
+                }
             }
         }
+        __syncthreads();  // buffer b & 1 may be refilled by the next iteration's issue
     }
+    cp_async_wait<0>();
     if (inside) {
         const int pid = i * W + j;
         alphas[pid] = 1.0f - T;
@@ -192,20 +255,24 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16]) {
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
-template <int MODEL>
+template <int BATCH>
+struct BwdShared {
+    Stage<BATCH> stage[2];
+    uint32_t sid[2][BATCH];
+    float sacc[BATCH * 16];
+    int stouched[BATCH];
+};
+
+template <int MODEL, int BATCH>
 __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
-    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint2* __restrict__ bounds,
+    const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
     const float* __restrict__ render_alphas, const int32_t* __restrict__ last_ids,
     const float* __restrict__ v_render, const float* __restrict__ v_alphas, float* __restrict__ accum) {
-    __shared__ float4 srec[kBlock * 4];
-    __shared__ float sthr[kBlock];
-    __shared__ uint32_t sid[kBlock];
-    __shared__ uint2 sbox[kBlock];
-    __shared__ __align__(16) float sacc[kBlock * 16];
-    __shared__ int stouched[kBlock];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    BwdShared<BATCH>& sm = *reinterpret_cast<BwdShared<BATCH>*>(smem_raw);
 
     if (overflow && *overflow) return;
     const int tile = blockIdx.x;
@@ -223,6 +290,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const int32_t n_isects = load_count(n_isects_dev, n_isects_host);
     const int32_t range_start = tile_offsets[tile];
     const int32_t range_end = (tile == n_tiles - 1) ? n_isects : tile_offsets[tile + 1];
+    const int n_batches = (range_end - range_start + BATCH - 1) / BATCH;
 
     const float T_final = 1.0f - render_alphas[pid];
     float T = T_final;
@@ -232,122 +300,127 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const float v_a = v_alphas ? v_alphas[pid] : 0.f;
     float bg_dot = 0.f;
     if (background) bg_dot = background[0] * vcr + background[1] * vcg + background[2] * vcb;
+    const float tail_c = T_final * (v_a - bg_dot);
     const int32_t warp_bin_final = __reduce_max_sync(0xffffffffu, bin_final);
     const int lane = threadIdx.x & 31;
 
+    for (int e = threadIdx.x; e < BATCH; e += kBlock) {
 #pragma unroll
-    for (int k = 0; k < 16; ++k) sacc[threadIdx.x * 16 + k] = 0.f;
-    stouched[threadIdx.x] = 0;
+        for (int k = 0; k < 16; ++k) sm.sacc[e * 16 + k] = 0.f;
+        sm.stouched[e] = 0;
+    }
 
-    for (int32_t batch_end = range_end - 1; batch_end >= range_start; batch_end -= kBlock) {
-        __syncthreads();
-        const int32_t batch_size = min(kBlock, batch_end + 1 - range_start);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int q = k * kBlock + threadIdx.x;
-            const int e = q >> 2, part = q & 3;
-            if (e < batch_size) {
-                const uint32_t g = flatten_ids[batch_end - e];
-                const float4 v = records[(size_t)g * 4 + part];
-                srec[q] = v;
-                if (part == 3) { sthr[e] = -__logf(255.0f * v.w) - kRejectMargin; sid[e] = g; }
-                if (part == 0) sbox[e] = bounds[g];
-            }
+    // batches run back to front: slot e of batch b holds list position batch_end - e
+    StageIds<BATCH> ids;
+    if (n_batches > 0) {
+        const int32_t be = range_end - 1;
+        load_ids(ids, flatten_ids, be, -1, min(BATCH, be + 1 - range_start));
+        issue_stage(sm.stage[0], sm.sid[0], ids, records, bounds, min(BATCH, be + 1 - range_start));
+        if (n_batches > 1) load_ids(ids, flatten_ids, be - BATCH, -1, min(BATCH, be - BATCH + 1 - range_start));
+    }
+    for (int b = 0; b < n_batches; ++b) {
+        const int32_t batch_end = range_end - 1 - b * BATCH;
+        const int32_t batch_size = min(BATCH, batch_end + 1 - range_start);
+        if (b + 1 < n_batches) {
+            issue_stage(sm.stage[(b + 1) & 1], sm.sid[(b + 1) & 1], ids, records, bounds,
+                        min(BATCH, batch_end - BATCH + 1 - range_start));
+            if (b + 2 < n_batches)
+                load_ids(ids, flatten_ids, batch_end - 2 * BATCH, -1, min(BATCH, batch_end - 2 * BATCH + 1 - range_start));
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
+        const Stage<BATCH>& st = sm.stage[b & 1];
         // entries (back to front) that no pixel of this warp reaches (beyond its last contributor) or whose
         // box misses this warp's 8x4 patch are dropped up front: one ballot word per 32 entries
         const int t_begin = max(0, batch_end - warp_bin_final);
-        uint32_t live[kBlock / 32];
+        uint32_t live[BATCH / 32];
 #pragma unroll
-        for (int w = 0; w < kBlock / 32; ++w) {
+        for (int w = 0; w < BATCH / 32; ++w) {
             const int e = w * 32 + lane;
-            live[w] = __ballot_sync(0xffffffffu, e >= t_begin && e < batch_size && box_overlaps(sbox[e], patch_x, patch_y));
+            bool ov = false;
+            if (e >= t_begin && e < batch_size) { const uint4 bx = st.box[e]; ov = box_overlaps(make_uint2(bx.x, bx.y), patch_x, patch_y); }
+            live[w] = __ballot_sync(0xffffffffu, ov);
         }
 #pragma unroll
-        for (int w = 0; w < kBlock / 32; ++w) {
-          uint32_t bits = live[w];
-          while (bits) {
-            const int t = w * 32 + __ffs(bits) - 1;
-            bits &= bits - 1;
-            bool valid = active && (batch_end - t <= bin_final);
-            float ux, uy, uz, cx, cy, cz, uu;
-            float4 r0, r1, r2;
-            if (valid) {
-                r0 = srec[t * 4 + 0]; r1 = srec[t * 4 + 1]; r2 = srec[t * 4 + 2];
-                ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
-                uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
-                uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
-                cx = uy * r2.w - r1.w * uz;
-                cy = uz * r0.w - r2.w * ux;
-                cz = ux * r1.w - r0.w * uy;
+        for (int w = 0; w < BATCH / 32; ++w) {
+            uint32_t bits = live[w];
+            while (bits) {
+                const int t = w * 32 + __ffs(bits) - 1;
+                bits &= bits - 1;
+                // Every lane evaluates the pair (the record reads are warp-wide broadcasts); lanes that are outside
+                // the image, beyond their last contributor or below the alpha threshold continue with alpha = vis = 0,
+                // which makes every term they add exactly zero, so no per-lane branching is needed below.
+                const float4 r0 = st.rec[t * 4 + 0], r1 = st.rec[t * 4 + 1], r2 = st.rec[t * 4 + 2];
+                const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
+                const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
+                const float uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
+                const float gx = r0.w, gy = r1.w, gz = r2.w;
+                float cx = uy * gz - gy * uz;
+                float cy = uz * gx - gz * ux;
+                float cz = ux * gy - gx * uy;
                 const float cc = cx * cx + cy * cy + cz * cz;
-                uu = ux * ux + uy * uy + uz * uz;
-                if (cc > -2.0f * sthr[t] * uu) valid = false;
-            }
-            float alpha = 0.f, vis = 0.f, inv = 0.f;
-            float4 r3 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (valid) {
-                r3 = srec[t * 4 + 3];
-                inv = rsqrtf(fmaxf(uu, 1e-37f));
+                const float uu = ux * ux + uy * uy + uz * uz;
+                bool valid = active && (batch_end - t <= bin_final) && !(cc > -2.0f * __uint_as_float(st.box[t].z) * uu);
+                if (!__any_sync(0xffffffffu, valid)) continue;
+                const float4 r3 = st.rec[t * 4 + 3];
+                const float inv = rsqrtf(fmaxf(uu, 1e-37f));
                 cx *= inv; cy *= inv; cz *= inv;  // cross(normalised u, gro)
                 const float power = -0.5f * (cx * cx + cy * cy + cz * cz);
-                vis = __expf(power);
-                alpha = fminf(0.999f, r3.w * vis);
-                if (alpha < kAlphaMin) valid = false;
-            }
-            if (!__any_sync(0xffffffffu, valid)) continue;
-            float v[16];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) v[k] = 0.f;
-            if (valid) {
-                const float ra = 1.0f / (1.0f - alpha);
-                T *= ra;
-                const float fac = alpha * T;
-                v[12] = fac * vcr; v[13] = fac * vcg; v[14] = fac * vcb;
-                float v_alpha = (r3.x * T - bufr * ra) * vcr + (r3.y * T - bufg * ra) * vcg + (r3.z * T - bufb * ra) * vcb;
-                v_alpha += T_final * ra * v_a;
-                v_alpha += -T_final * ra * bg_dot;
-                if (r3.w * vis <= 0.999f) {
-                    const float v_vis = r3.w * v_alpha;
-                    const float s = -vis * v_vis;  // v_c = s * c
-                    const float vcx = s * cx, vcy = s * cy, vcz = s * cz;
+                float vis = __expf(power);
+                float alpha = fminf(0.999f, r3.w * vis);
+                valid = valid && !(alpha < kAlphaMin);
+                if (!__any_sync(0xffffffffu, valid)) continue;
+                if (!valid) { vis = 0.f; alpha = 0.f; }
+                float v[16];
+                {
+                    const float ra = __frcp_rn(1.0f - alpha);
+                    T *= ra;
+                    const float fac = alpha * T;
+                    v[12] = fac * vcr; v[13] = fac * vcg; v[14] = fac * vcb;
+                    float v_alpha = (r3.x * T - bufr * ra) * vcr + (r3.y * T - bufg * ra) * vcg + (r3.z * T - bufb * ra) * vcb;
+                    v_alpha += ra * tail_c;  // T_final * ra * (v_alpha_out - background . v_colour_out)
+                    // geometry and opacity only while alpha is not clamped at 0.999
+                    const float gate = (r3.w * vis <= 0.999f) ? vis : 0.f;
+                    const float s = -gate * (r3.w * v_alpha);  // v_c = s * c with c = n x g
+                    // with n = u / |u|, gn = g . n and w = gn n - g (minus the part of g orthogonal to n):
+                    //   v_g = v_c x n = -s w,   v_u = (v_n - (v_n . n) n) / |u| = (s gn / |u|) w
                     const float nx = ux * inv, ny = uy * inv, nz = uz * inv;
-                    const float gx = r0.w, gy = r1.w, gz = r2.w;
-                    // v_n = -(v_c x g) = g x v_c ; v_g = v_c x n
-                    const float vnx = gy * vcz - vcy * gz, vny = gz * vcx - vcz * gx, vnz = gx * vcy - vcx * gy;
-                    const float vgx = vcy * nz - ny * vcz, vgy = vcz * nx - nz * vcx, vgz = vcx * ny - nx * vcy;
-                    // v_u = inv * v_n - inv^3 (v_n . u) u
-                    const float il3 = inv * inv * inv;
-                    const float dd = (vnx * ux + vny * uy + vnz * uz) * il3;
-                    const float vux = inv * vnx - dd * ux, vuy = inv * vny - dd * uy, vuz = inv * vnz - dd * uz;
+                    const float gn = gx * nx + gy * ny + gz * nz;
+                    const float wx = gn * nx - gx, wy = gn * ny - gy, wz = gn * nz - gz;
+                    const float ku = s * gn * inv;
+                    const float vux = ku * wx, vuy = ku * wy, vuz = ku * wz;
                     v[0] = vux * d.x; v[1] = vux * d.y; v[2] = vux * d.z;
                     v[3] = vuy * d.x; v[4] = vuy * d.y; v[5] = vuy * d.z;
                     v[6] = vuz * d.x; v[7] = vuz * d.y; v[8] = vuz * d.z;
-                    v[9] = vgx; v[10] = vgy; v[11] = vgz;
-                    v[15] = vis * v_alpha;
+                    v[9] = -s * wx; v[10] = -s * wy; v[11] = -s * wz;
+                    v[15] = gate * v_alpha;
+                    bufr += r3.x * fac; bufg += r3.y * fac; bufb += r3.z * fac;
                 }
-                bufr += r3.x * fac; bufg += r3.y * fac; bufb += r3.z * fac;
+                const float total = warp_reduce16(v);
+                if ((lane & 1) == 0) atomicAdd(&sm.sacc[t * 16 + (lane >> 1)], total);
+                if (lane == 0) sm.stouched[t] = 1;
             }
-            const float total = warp_reduce16(v);
-            if ((lane & 1) == 0) atomicAdd(&sacc[t * 16 + (lane >> 1)], total);
-            if (lane == 0) stouched[t] = 1;
-          }
         }
         __syncthreads();
         // flush this batch's sums: four 16-byte reductions per touched Gaussian
-        if (threadIdx.x < batch_size && stouched[threadIdx.x]) {
-            const uint32_t g = sid[threadIdx.x];
-            float4* dst = reinterpret_cast<float4*>(accum) + (size_t)g * 4;
-            float4* src = reinterpret_cast<float4*>(sacc) + threadIdx.x * 4;
+        for (int e = threadIdx.x; e < batch_size; e += kBlock) {
+            if (sm.stouched[e]) {
+                const uint32_t g = sm.sid[b & 1][e];
+                float4* dst = reinterpret_cast<float4*>(accum) + (size_t)g * 4;
+                float4* src = reinterpret_cast<float4*>(sm.sacc) + e * 4;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                atomicAdd(dst + k, src[k]);
-                src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int k = 0; k < 4; ++k) {
+                    atomicAdd(dst + k, src[k]);
+                    src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                sm.stouched[e] = 0;
             }
-            stouched[threadIdx.x] = 0;
         }
+        __syncthreads();  // accumulators are clean and buffer b & 1 is free before the next iteration refills it
     }
+    cp_async_wait<0>();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -536,13 +609,21 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
     LFS_TIMED("raster_bwd", st);
+    constexpr int kBwdBatch = 128;
+    const size_t smem = sizeof(BwdShared<kBwdBatch>);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(raster_bwd_kernel<LFS_PINHOLE, kBwdBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(raster_bwd_kernel<LFS_FISHEYE, kBwdBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
     if (a.model == LFS_PINHOLE)
-        raster_bwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
+        raster_bwd_kernel<LFS_PINHOLE, kBwdBatch><<<n_tiles, kBlock, smem, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
                                                                    a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
                                                                    v_alphas, accum);
     else
-        raster_bwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
+        raster_bwd_kernel<LFS_FISHEYE, kBwdBatch><<<n_tiles, kBlock, smem, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
                                                                    a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
                                                                    v_alphas, accum);

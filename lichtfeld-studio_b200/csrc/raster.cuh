@@ -8,7 +8,8 @@ namespace lfs {
 struct RasterArgs {
     const CamDev* cam;            // one camera
     const float4* records;        // [N] packed 64-byte records
-    const uint2* bounds;          // [N] inclusive pixel box (lo | hi << 16 for x, then y) outside of which alpha < 1/255
+    const uint4* bounds;          // [N] (x box, y box, rejection exponent, 0): inclusive pixel box (lo | hi << 16)
+                                  //     outside of which alpha < 1/255, and -ln(255 opacity) - margin as float bits
     const uint32_t* flatten_ids;  // depth-sorted Gaussian index per instance
     const int32_t* tile_offsets;  // [tw*th] first instance of each tile
     const int32_t* n_isects_dev;  // device-side instance count, or null to use n_isects_host
