@@ -369,6 +369,118 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def _kernel_means(recs):
+    agg = {}
+    for name, ms in recs:
+        agg.setdefault(name, []).append(ms)
+    return agg
+
+
+def run_forward_only(args):
+    """Forward-only render of a large scene (workloads wide_4k / wide_fisheye): tile-list length, time of the
+    tile-list stage (depth sort + scan + emit + tile sort + offsets) and Gpix/s over the seeded poses."""
+    import torch
+    pkg = importlib.import_module("lichtfeld-studio_b200")
+    synth, tr, capi = pkg.synth, pkg.trainer, pkg._capi
+    dev = torch.device("cuda", 0)
+    cfg = synth.CONFIGS[args.workload]
+    W, H, deg, n = cfg["W"], cfg["H"], cfg["sh_degree"], cfg["n"]
+    model = tr.SplatData(n, (deg + 1) ** 2, dev).load(synth.make_gaussians(n, 0, cfg["layout"], deg))
+    rast = tr.Rasterizer(model, W, H, deg, camera_model=cfg["model"], isect_capacity=4 * n)
+    poses, Kmat = synth.make_cameras(cfg)
+    Kt, bg = torch.from_numpy(Kmat).to(dev), torch.zeros(3, device=dev)
+    cams = [tr.Camera(torch.from_numpy(p).to(dev), Kt, W, H, camera_model=cfg["model"]) for p in poses]
+    for c in cams[: max(3, args.warmup)]:
+        rast.forward(c, bg)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0); sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(1, args.steps // len(cams)) if args.steps > len(cams) else 1
+    e0.record()
+    for _ in range(reps):
+        for c in cams:
+            rast.forward(c, bg)
+    e1.record(); torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / (reps * len(cams))
+    capi.profile_enable(True)
+    n_isects, n_vis = [], []
+    for c in cams:
+        out = rast.forward(c, bg)
+        st = out.status.cpu().numpy()
+        assert st[0] == 0, "tile-instance capacity exceeded"
+        n_isects.append(int(st[1])); n_vis.append(int(st[2]))
+    torch.cuda.synchronize()
+    km = {k: float(np.mean(v)) for k, v in _kernel_means(capi.profile_collect()).items()}
+    capi.profile_enable(False)
+    sort_ms = sum(km.get(k, 0.0) for k in ("radix_sort_depth", "exclusive_scan", "emit_instances", "radix_sort_tile", "tile_offsets"))
+    hbm_peak, kind = load_peaks()
+    V, I = float(np.mean(n_vis)), float(np.mean(n_isects))
+    tiles = ((W + 15) // 16) * ((H + 15) // 16)
+    sort_bytes = 20 * V + 36 * I + 4 * tiles
+    out = {"metric": "forward render Gpix/s", "value": W * H / (ms * 1e-3) / 1e9, "unit": "Gpix/s", "n_gpus": 1, "steps": reps * len(cams),
+           "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+           "data": "synthetic", "config": {"workload": args.workload, "gaussians": n, "image": [W, H], "poses": len(cams),
+                                           "camera": "fisheye" if cfg["model"] == 2 else "pinhole"},
+           "clocks": clocks, "n_isects_mean": I, "n_isects_max": int(np.max(n_isects)), "n_visible_mean": V, "tile_list_ms": sort_ms,
+           "kernel_ms": km, "gpu_launches": int(reps * len(cams) * 30),
+           "roofline": {"kernel": "tile-list stage (radix_* + scan_* + emit + offsets)", "bound": "hbm",
+                        "achieved": sort_bytes / (sort_ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                        "frac": sort_bytes / (sort_ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                        "note": f"20 V + 36 I + 4 tiles bytes, of {kind}; 21 launches, launch-latency bound at this size"}}
+    print(json.dumps(out), flush=True)
+
+
+def run_mcmc(args):
+    """MCMC densification step (workload mcmc_3m): relocate dead Gaussians, add 5 % new ones, inject noise."""
+    import torch
+    pkg = importlib.import_module("lichtfeld-studio_b200")
+    synth, tr, st, capi = pkg.synth, pkg.trainer, pkg.strategy, pkg._capi
+    dev = torch.device("cuda", 0)
+    cfg = synth.CONFIGS[args.workload]
+    n, deg = cfg["n"], cfg["sh_degree"]
+    P = synth.make_gaussians(n, 0, cfg["layout"], deg)
+    P["opacity_raw"][np.arange(n) % 20 == 7] = -6.0
+    cap = int(np.float32(1.05) * np.float32(n)) + 64
+    model = tr.SplatData(n, (deg + 1) ** 2, dev, capacity=cap).load(P)
+    backup = model.flat.clone()
+    s = st.MCMC(model)
+    s.initialize(st.OptimizationParameters(max_cap=cap, sh_degree=deg))
+    times, counts = [], None
+    for rep in range(args.warmup + args.steps):
+        model.size = s._optimizer.exp_avg.size = s._optimizer.exp_avg_sq.size = s.grads.size = n
+        model.flat.copy_(backup)
+        torch.manual_seed(1234)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if rep == args.warmup + args.steps - 1:
+            capi.profile_enable(True)
+        e0.record()
+        n_dead = s.relocate_gs()
+        n_new = s.add_new_gs()
+        s.inject_noise()
+        e1.record(); torch.cuda.synchronize()
+        if rep >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+        counts = (n_dead, n_new)
+    km = {k: float(np.sum(v)) for k, v in _kernel_means(capi.profile_collect()).items()}
+    capi.profile_enable(False)
+    ms = float(np.mean(times))
+    hbm_peak, kind = load_peaks()
+    M = counts[0] + counts[1]
+    bytes_alg = 56.0 * M + 56.0 * (n + counts[1]) + 12.0 * (n + counts[1]) + 2 * 236.0 * M
+    out = {"metric": "MCMC refine step (relocate + add + noise) ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+           "data": "synthetic", "config": {"workload": args.workload, "gaussians": n, "relocated": counts[0], "added": counts[1],
+                                           "rng": "torch CUDA generator seeded 1234 before relocate_gs"},
+           "kernel_ms_total": km, "gpu_launches": int(args.steps * 20),
+           "roofline": {"kernel": "whole refine step", "bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9, "peak": hbm_peak,
+                        "unit": "GB/s", "frac": bytes_alg / (ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                        "note": f"56 M + 68 N + 472 M bytes with M = {M} sampled rows, of {kind}; includes torch.multinomial / normal_ "
+                                "and two host reads of the dead / alive counts"}}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -382,6 +494,10 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in ("wide_4k", "wide_fisheye"):
+        run_forward_only(args)
+    elif args.workload == "mcmc_3m":
+        run_mcmc(args)
     else:
         run_ours(args)
 
