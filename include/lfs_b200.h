@@ -249,6 +249,15 @@ int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const l
                          double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
                          int64_t first_row, int64_t n_rows, float grad_scale, void* stream);
 
+/* src/training/kernels/regularization.cu:20 / :171 (compute_exp_l1_regularization_with_grad_cuda,
+ * compute_sigmoid_l1_regularization_with_grad_cuda), both in one launch and without the host read:
+ *   L_scale = scale_weight * mean(exp(scaling_raw)),     grad_scaling += scale_weight / (3N) * exp(scaling_raw)
+ *   L_opac  = opacity_weight * mean(sigmoid(opacity_raw)), grad_opacity += opacity_weight / N * s (1 - s)
+ * A weight of 0 skips that term (its gradient pointer may then be NULL). reg_loss_dev (device float[2])
+ * receives (L_scale, L_opac). */
+int lfs_regularization(int N, const float* scaling_raw, const float* opacity_raw, float scale_weight, float opacity_weight,
+                       float* grad_scaling, float* grad_opacity, float* reg_loss_dev, void* stream);
+
 /* Fused Adam over up to 16 arbitrary contiguous segments in one launch (each with its own learning rate).
  * lfs_adam_step_splats is the special case "six groups, one row range". Used for optimizer-state sharding
  * by flat element range: a shard of the group-major parameter buffer is at most six segments. */

@@ -359,6 +359,15 @@ int lfs_adam_step_splats(int N, int K, const lfs_splats* params, const lfs_splat
     return launch_adam_groups(G, S(stream));
 }
 
+int lfs_regularization(int N, const float* scaling_raw, const float* opacity_raw, float scale_weight, float opacity_weight,
+                       float* grad_scaling, float* grad_opacity, float* reg_loss_dev, void* stream) {
+    LFS_REQUIRE(N >= 0 && reg_loss_dev != nullptr, "bad arguments");
+    if (N > 0 && scale_weight != 0.f) LFS_REQUIRE(scaling_raw && grad_scaling, "null pointer");
+    if (N > 0 && opacity_weight != 0.f) LFS_REQUIRE(opacity_raw && grad_opacity, "null pointer");
+    return launch_regularization(N, scaling_raw, opacity_raw, scale_weight, opacity_weight, grad_scaling, grad_opacity,
+                                 reg_loss_dev, S(stream));
+}
+
 int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segs, double beta1, double beta2, double eps,
                            int64_t step_count, float grad_scale, void* stream) {
     LFS_REQUIRE(n_segments >= 0 && n_segments <= kMaxAdamSegments, "at most 16 segments");

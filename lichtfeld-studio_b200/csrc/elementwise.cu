@@ -122,6 +122,44 @@ __global__ void __launch_bounds__(256) dp_reduce_adam_broadcast_kernel(DpArgs A)
     }
 }
 
+// ---- scale / opacity L1 regularisers --------------------------------------------------------------
+__global__ void __launch_bounds__(256) regularization_kernel(int N, const float* __restrict__ scaling_raw,
+                                                             const float* __restrict__ opacity_raw, float scale_gs,
+                                                             float opac_gs, float* __restrict__ g_scaling,
+                                                             float* __restrict__ g_opacity, float* __restrict__ loss) {
+    __shared__ float red[2][8];
+    float ssum = 0.f, osum = 0.f;
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
+        if (scale_gs != 0.f) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float e = expf(scaling_raw[g * 3 + k]);
+                ssum += e;
+                g_scaling[g * 3 + k] += scale_gs * e;
+            }
+        }
+        if (opac_gs != 0.f) {
+            const float s = 1.0f / (1.0f + expf(-opacity_raw[g]));
+            osum += s;
+            g_opacity[g] += opac_gs * s * (1.0f - s);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+        osum += __shfl_xor_sync(0xffffffffu, osum, o);
+    }
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = ssum; red[1][threadIdx.x >> 5] = osum; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = 0.f, b = 0.f;
+        for (int k = 0; k < 8; ++k) { a += red[0][k]; b += red[1][k]; }
+        // grad scale = weight / n, so weight * mean = grad scale * sum
+        if (scale_gs != 0.f) atomicAdd(&loss[0], a * scale_gs);
+        if (opac_gs != 0.f) atomicAdd(&loss[1], b * opac_gs);
+    }
+}
+
 // ---- spherical harmonics, operator level ------------------------------------------------------
 __global__ void __launch_bounds__(256) sh_fwd_kernel(int n, int K, int degree, const float* __restrict__ dirs,
                                                      const float* __restrict__ coeffs, const uint8_t* __restrict__ masks,
@@ -337,6 +375,16 @@ int launch_dp_reduce_adam_broadcast(const DpArgs& A, cudaStream_t st) {
     LFS_TIMED("dp_reduce_adam_broadcast", st);
     dp_reduce_adam_broadcast_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(A);
     return check_launch("dp_reduce_adam_broadcast");
+}
+
+int launch_regularization(int N, const float* scaling_raw, const float* opacity_raw, float scale_weight, float opacity_weight,
+                          float* g_scaling, float* g_opacity, float* loss, cudaStream_t st) {
+    cudaMemsetAsync(loss, 0, 2 * sizeof(float), st);
+    if (N == 0) return LFS_OK;
+    LFS_TIMED("regularization", st);
+    regularization_kernel<<<grid_for(N, 256, 4), 256, 0, st>>>(N, scaling_raw, opacity_raw, scale_weight / (3.0f * (float)N),
+                                                               opacity_weight / (float)N, g_scaling, g_opacity, loss);
+    return check_launch("regularization");
 }
 
 int launch_sh_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks, float* colors, cudaStream_t st) {

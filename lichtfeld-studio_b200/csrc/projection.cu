@@ -372,7 +372,7 @@ int launch_pack_records(int N, const float* means, const float* quats, const flo
 // accumulator row. Invisible Gaussians get radii 0, tile count 0 and the sort key 0xFFFFFFFF.
 // ---------------------------------------------------------------------------------------------
 template <int MODEL>
-__global__ void __launch_bounds__(256) project_pack_kernel(
+__global__ void __launch_bounds__(256, 3) project_pack_kernel(
     int N, int K, int sh_degree, const float* __restrict__ means, const float* __restrict__ sh0,
     const float* __restrict__ shN, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
     const float* __restrict__ opacity_raw, const CamDev* __restrict__ cams, ProjParams pp, float tile_size,
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
     // Each warp handles 32 consecutive Gaussians per iteration. Their higher-order SH rows ((K-1)*3 floats
     // each, contiguous in memory) are fetched as one coalesced run into shared memory when any of the 32
     // is visible, and every visible lane then reads its own row from there.
-    extern __shared__ float s_rows[];
+    extern __shared__ __align__(16) float s_rows[];
     const CamDev cam = cams[0];
     const int rest = (K - 1) * 3;
     const int nb = (sh_degree + 1) * (sh_degree + 1);
@@ -391,6 +391,7 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
     float* my = s_rows + (size_t)warp * 32 * rest;
     const int n_chunks = (N + 31) / 32;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
+    const bool sh_aligned = (reinterpret_cast<uintptr_t>(shN) & 15) == 0 && ((32 * rest) & 3) == 0;
     int local_visible = 0;
     for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
         const int g = chunk * 32 + lane;
@@ -419,10 +420,19 @@ __global__ void __launch_bounds__(256) project_pack_kernel(
         }
         const bool any_vis = __any_sync(0xffffffffu, vis);
         if (any_vis && nb > 1) {
+            // one batch of asynchronous 16-byte copies (a single round trip instead of one per row slice); the
+            // chunk starts 16-byte aligned because it begins at a multiple of 32 rows
             const int n_rows = min(32, N - chunk * 32);
             const int total = n_rows * rest;
             const float* src = shN + (size_t)chunk * 32 * rest;
-            for (int i = lane; i < total; i += 32) my[i] = src[i];
+            const int total16 = sh_aligned ? (total >> 2) : 0;
+            for (int i = lane; i < total16; i += 32) {
+                const unsigned dst = (unsigned)__cvta_generic_to_shared(my + i * 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src + i * 4));
+            }
+            asm volatile("cp.async.commit_group;\n" ::);
+            for (int i = total16 * 4 + lane; i < total; i += 32) my[i] = src[i];
+            asm volatile("cp.async.wait_group 0;\n" ::);
         }
         __syncwarp();
         if (vis) {

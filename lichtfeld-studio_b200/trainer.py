@@ -188,6 +188,17 @@ class PhotometricLoss:
         return self.loss, self.v_render
 
 
+def regularization(model: SplatData, grads: SplatData, scale_reg: float, opacity_reg: float, out: torch.Tensor | None = None):
+    """Trainer::compute_scale_reg_loss / compute_opacity_reg_loss (src/training/trainer.cpp:136-174) in one launch:
+    adds the regularisers' gradients to `grads` and returns a device float[2] = (scale loss, opacity loss). Unlike the
+    reference there is no host read; call .tolist() on the result if the values are needed on the host."""
+    if out is None:
+        out = torch.zeros(2, dtype=torch.float32, device=model.device)
+    call("lfs_regularization", model.size, ptr(model._full["scaling_raw"]), ptr(model._full["opacity_raw"]), float(scale_reg),
+         float(opacity_reg), ptr(grads._full["scaling_raw"]), ptr(grads._full["opacity_raw"]), ptr(out), _stream())
+    return out
+
+
 def adam_step_splats(model: SplatData, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
                      beta1=0.9, beta2=0.999, eps=1e-15, skip_shN=False, first_row=0, n_rows=None, grad_scale=1.0):
     """One launch of the fused Adam over all six groups (FusedAdam::step)."""

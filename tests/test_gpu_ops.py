@@ -271,3 +271,27 @@ def test_error_behaviour(pkg):
     with pytest.raises(pkg.LfsError):
         pkg._capi.call("lfs_adam_step", None, None, None, None, 10, 0.1, 0.9, 0.999, 1e-8, 1.0, 1.0, None)
     assert b"null pointer" in pkg._capi.lib().lfs_last_error()
+
+
+def test_regularization_matches_reference_definition(pkg):
+    """Same checks as the reference's tests/test_regularization.cpp: loss within 1e-5 and gradient within 1e-6 of
+    weight * mean(exp(x)) / weight * mean(sigmoid(x)) and their derivatives, accumulated onto existing gradients."""
+    tr = pkg.trainer
+    rng = np.random.default_rng(8)
+    for n in (1, 777, 50_000):
+        model, grads = tr.SplatData(n, 4, DEV), tr.SplatData(n, 4, DEV)
+        sc = (rng.normal(size=(n, 3)) * 0.7 - 3).astype(np.float32)
+        op = rng.normal(size=(n, 1)).astype(np.float32) * 2
+        g0s = rng.normal(size=(n, 3)).astype(np.float32) * 1e-3
+        g0o = rng.normal(size=(n, 1)).astype(np.float32) * 1e-3
+        model.tensor("scaling_raw").copy_(T(sc)); model.tensor("opacity_raw").copy_(T(op))
+        grads.tensor("scaling_raw").copy_(T(g0s)); grads.tensor("opacity_raw").copy_(T(g0o))
+        out = tr.regularization(model, grads, 0.01, 0.02).cpu().numpy()
+        e = np.exp(sc.astype(np.float64)); s = 1 / (1 + np.exp(-op.astype(np.float64)))
+        assert abs(out[0] - 0.01 * e.mean()) < 1e-5 and abs(out[1] - 0.02 * s.mean()) < 1e-5
+        assert np.abs(grads.tensor("scaling_raw").cpu().numpy() - (g0s + 0.01 / (3 * n) * e)).max() < 1e-6
+        assert np.abs(grads.tensor("opacity_raw").cpu().numpy() - (g0o + 0.02 / n * s * (1 - s))).max() < 1e-6
+        # a zero weight leaves that group untouched
+        before = grads.tensor("opacity_raw").clone()
+        out = tr.regularization(model, grads, 0.01, 0.0).cpu().numpy()
+        assert out[1] == 0 and torch.equal(grads.tensor("opacity_raw"), before)
