@@ -2,11 +2,13 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Workload `train_1m` (default, N = 1): 1,000,000 Gaussians, SH degree 3, one 1296x840 pinhole camera
-per step out of 200 hemisphere poses, loss 0.8 L1 + 0.2 (1 - SSIM), Adam with the per-group rates of
-the reference's MCMC strategy. N > 1: workload `dp_3m` (3,000,000 Gaussians, 1600x1064), one camera
-per GPU per step (weak scaling), gradients reduce-scattered over NCCL, Adam on each rank's shard,
-parameters all-gathered. Synthetic seeded inputs stand in for the Mip-NeRF-360 shapes.
+Workload `train_1m` (default at every N): 1,000,000 Gaussians, SH degree 3, one 1296x840 pinhole camera
+per GPU per step out of 200 hemisphere poses, loss 0.8 L1 + 0.2 (1 - SSIM), Adam with the per-group rates
+of the reference's MCMC strategy. N > 1 is weak scaling by camera: each rank renders its own camera against
+replicated Gaussians, the gradients are summed and Adam applied by --dp-mode (default: one fused kernel over
+NVLink peer memory that does reduce-scatter + Adam + all-gather). `--workload dp_3m` is the 3,000,000
+Gaussian / 1600x1064 data-parallel configuration, `mcmc_3m` the densification step, `wide_4k` /
+`wide_fisheye` the forward-only renders. Synthetic seeded inputs stand in for the Mip-NeRF-360 shapes.
 
 Rank 0 prints ONE JSON line. `value` is steps/s with every input resident in HBM; `e2e` is the same
 step driven from pinned host memory (target image + camera copied in, loss read back each step).
@@ -150,7 +152,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    workload = args.workload or ("train_1m" if args.gpus == 1 else "dp_3m")
+    workload = args.workload or "train_1m"
     times = []
     for s in range(args.warmup + args.steps):
         full, desc, threads = cpu_step_sample(workload, step=s)
@@ -185,7 +187,7 @@ def run_ours(args):
     synth, tr, capi = pkg.synth, pkg.trainer, pkg._capi
     capi.lib()  # fails loudly if the CUDA library is missing
 
-    workload = args.workload or ("train_1m" if world == 1 else "dp_3m")
+    workload = args.workload or "train_1m"
     cfg = synth.CONFIGS[workload]
     W, H, deg, n = cfg["W"], cfg["H"], cfg["sh_degree"], cfg["n"]
     K_sh = (deg + 1) ** 2
@@ -330,8 +332,11 @@ def run_ours(args):
         t_adam = float(np.mean(kernels.get("adam", [float("nan")])))
         hbm_peak, peak_kind = load_peaks()
         ach = 370.0 * q_b / (t_bwd * 1e-3) / 1e12
+        # DRAM bytes of one raster_bwd launch from the committed ncu capture (profiles/raster_bwd_train_1m.md);
+        # it scales with the tile-instance count, so other workloads report null
+        traffic = 186.4e6 if workload == "train_1m" else None
         roofline = {"kernel": "raster_bwd_kernel", "bound": "fp32", "achieved": ach, "peak": fp32_peak, "unit": "TFLOP/s",
-                    "frac": ach / fp32_peak, "traffic": None,
+                    "frac": ach / fp32_peak, "traffic": traffic,
                     "note": f"370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms; peak = 148 SM x 128 lanes x 2 x "
                             f"{sm_clock:.0f} MHz sampled under load (no tensor cores on this path)"}
         adam_bytes = 28.0 * 59 * n if K_sh == 16 else 28.0 * model.row_floats * n
