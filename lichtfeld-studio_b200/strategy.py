@@ -241,3 +241,199 @@ class MCMC(IStrategy):
             noise.normal_()  # torch::randn_like
         call("lfs_add_noise", sd.size, ptr(sd._full["opacity_raw"]), ptr(sd._full["scaling_raw"]), ptr(sd._full["rotation_raw"]),
              ptr(noise), ptr(sd._full["means"]), current_lr, _stream())
+
+
+def _rewrite_rows(buffers, new_rows: dict, new_n: int):
+    """Replace the live rows of several SplatData buffers (parameters, moments) by freshly gathered rows.
+    new_rows[i] is a dict name -> tensor for buffers[i]; counterpart of update_param_with_optimizer
+    (src/training/strategies/strategy_utils.cpp:57) on capacity-reserved storage."""
+    for sd, rows in zip(buffers, new_rows):
+        if new_n > sd.capacity:
+            raise RuntimeError("SplatData capacity exhausted: reserve more rows")
+        sd.size = new_n
+        for name, t in rows.items():
+            sd.tensor(name).copy_(t.reshape(sd.tensor(name).shape))
+
+
+class DefaultStrategy(IStrategy):
+    """Adaptive density control of the original 3DGS (src/training/strategies/default_strategy.cpp):
+    duplicate small / split large Gaussians with a high image-plane gradient, prune transparent or huge
+    ones, reset opacities periodically. `densification_info` [2, N] (visibility count, accumulated
+    image-plane gradient norm) is an input: the reference's gsplat path does not fill it either; its
+    default EWA rasterizer does."""
+
+    def __init__(self, splat_data: SplatData):
+        self._splat_data = splat_data
+        self._params = None
+        self._optimizer = None
+        self._scheduler = None
+        self.grads = splat_data.like()
+        self.active_sh_degree = 0
+        self.densification_info = None
+
+    @dataclass
+    class Parameters(OptimizationParameters):
+        grad_threshold: float = 0.0002
+        prune_opacity: float = 0.005
+        grow_scale3d: float = 0.01
+        prune_scale3d: float = 0.1
+        reset_every: int = 3_000
+        pause_refine_after_reset: int = 0
+        revised_opacity: bool = False
+
+    # ------------------------------------------------------------------ IStrategy
+    def initialize(self, optim_params):
+        p = self._params = optim_params
+        sd = self._splat_data
+        self.densification_info = torch.zeros((2, sd.size), dtype=torch.float32, device=sd.device)
+        lrs = [p.means_lr * p.scene_scale, p.shs_lr, p.shs_lr / 20.0, p.scaling_lr, p.rotation_lr, p.opacity_lr]
+        self._optimizer = FusedAdam(sd, lrs, (0.9, 0.999), 1e-15)
+        self._scheduler = ExponentialLR(self._optimizer, 0.01 ** (1.0 / p.iterations), 0)
+
+    def is_refining(self, iter: int) -> bool:
+        p = self._params
+        return iter > p.start_refine and iter % p.refine_every == 0 and iter % p.reset_every >= p.pause_refine_after_reset
+
+    def get_model(self) -> SplatData:
+        return self._splat_data
+
+    def remove_gaussians(self, mask: torch.Tensor):
+        if int(mask.sum()) == 0:
+            return
+        self.remove(mask)
+
+    def post_backward(self, iter: int, render_output=None):
+        p = self._params
+        if iter % p.sh_degree_interval == 0:
+            self.active_sh_degree = min(self.active_sh_degree + 1, p.sh_degree)
+        if iter == p.stop_refine:
+            self.densification_info = torch.empty(0)
+        if iter >= p.stop_refine:
+            return
+        if self.is_refining(iter):
+            self.grow_gs(iter)
+            self.prune_gs(iter)
+            self.densification_info = torch.zeros((2, self._splat_data.size), dtype=torch.float32, device=self._splat_data.device)
+        if iter % p.reset_every == 0 and iter > 0:
+            self.reset_opacity()
+
+    def step(self, iter: int, grad_scale: float = 1.0):
+        if iter < self._params.iterations:
+            self._optimizer.step(iter, self.grads, grad_scale)
+            self._optimizer.zero_grad(True, iter)
+            self._scheduler.step()
+
+    # ------------------------------------------------------------------ pieces
+    def _buffers(self):
+        return (self._splat_data, self._optimizer.exp_avg, self._optimizer.exp_avg_sq)
+
+    def _sync_sizes(self):
+        n = self._splat_data.size
+        for sd in (self._optimizer.exp_avg, self._optimizer.exp_avg_sq, self.grads):
+            sd.size = n
+
+    def _activated(self):
+        sd = self._splat_data
+        return torch.sigmoid(sd.tensor("opacity_raw")).squeeze(-1), torch.exp(sd.tensor("scaling_raw")), \
+            torch.nn.functional.normalize(sd.tensor("rotation_raw"), dim=-1)
+
+    def duplicate(self, is_duplicated: torch.Tensor):
+        """default_strategy.cpp:49-87: append copies of the selected rows; their moments start at zero."""
+        self._sync_sizes()
+        idx = is_duplicated.nonzero().squeeze(-1)
+        n, k = self._splat_data.size, int(idx.numel())
+        rows = []
+        for bi, sd in enumerate(self._buffers()):
+            d = {}
+            for name in ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw"):
+                t = sd.tensor(name)
+                extra = t.index_select(0, idx) if bi == 0 else torch.zeros((k,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+                d[name] = torch.cat([t, extra], 0)
+            rows.append(d)
+        _rewrite_rows(self._buffers(), rows, n + k)
+        self._sync_sizes()
+
+    def split(self, is_split: torch.Tensor, noise: torch.Tensor | None = None):
+        """default_strategy.cpp:89-159: each selected Gaussian is replaced by two samples of itself with scale / 1.6;
+        the rest keep their order, the new rows are appended, their moments start at zero."""
+        from . import ops
+        self._sync_sizes()
+        sd = self._splat_data
+        idx = is_split.nonzero().squeeze(-1)
+        rest = (~is_split.bool()).nonzero().squeeze(-1)
+        k = int(idx.numel())
+        _, scales, quats = self._activated()
+        s_scales, s_quats = scales.index_select(0, idx), quats.index_select(0, idx).contiguous()
+        rotmats = ops.quats_to_rotmats(s_quats)  # [k, 3, 3]
+        if noise is None:
+            noise = torch.randn((2, k, 3), dtype=torch.float32, device=sd.device)
+        samples = torch.einsum("nij,nj,bnj->bni", rotmats, s_scales, noise)  # [2, k, 3]
+        rows = []
+        for bi, buf in enumerate(self._buffers()):
+            d = {}
+            for gi, name in enumerate(("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")):
+                t = buf.tensor(name)
+                rest_rows = t.index_select(0, rest)
+                if bi > 0:
+                    new = torch.zeros((2 * k,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+                else:
+                    sel = t.index_select(0, idx)
+                    if gi == 0:
+                        new = (sel.unsqueeze(0) + samples).reshape(-1, 3)
+                    elif gi == 3:
+                        new = torch.log(s_scales / 1.6).repeat(2, 1)
+                    elif gi == 5 and self._params.revised_opacity:
+                        new = torch.logit(1.0 - torch.sqrt(1.0 - torch.sigmoid(sel))).repeat(2, 1)
+                    else:
+                        new = sel.repeat((2,) + (1,) * (sel.dim() - 1))
+                d[name] = torch.cat([rest_rows, new], 0)
+            rows.append(d)
+        _rewrite_rows(self._buffers(), rows, int(rest.numel()) + 2 * k)
+        self._sync_sizes()
+
+    def grow_gs(self, iter: int):
+        """default_strategy.cpp:161-189."""
+        p, sd = self._params, self._splat_data
+        info = self.densification_info
+        grads = info[1] / torch.clamp_min(info[0], 1.0)
+        _, scales, _ = self._activated()
+        is_grad_high = grads > p.grad_threshold
+        is_small = scales.max(-1).values <= p.grow_scale3d * p.scene_scale
+        is_duplicated = is_grad_high & is_small
+        num_dup = int(is_duplicated.sum())
+        is_split = is_grad_high & ~is_small
+        num_split = int(is_split.sum())
+        if num_dup > 0:
+            self.duplicate(is_duplicated)
+        is_split = torch.cat([is_split, torch.zeros(num_dup, dtype=torch.bool, device=sd.device)])
+        if num_split > 0:
+            self.split(is_split)
+
+    def remove(self, is_prune: torch.Tensor):
+        """default_strategy.cpp:191-219."""
+        self._sync_sizes()
+        keep = (~is_prune.bool()).nonzero().squeeze(-1)
+        rows = [{name: sd.tensor(name).index_select(0, keep) for name in ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")}
+                for sd in self._buffers()]
+        _rewrite_rows(self._buffers(), rows, int(keep.numel()))
+        self._sync_sizes()
+
+    def prune_gs(self, iter: int):
+        """default_strategy.cpp:221-241."""
+        p, sd = self._params, self._splat_data
+        opac, scales, _ = self._activated()
+        is_prune = opac < p.prune_opacity
+        rot = sd.tensor("rotation_raw")
+        is_prune |= (rot * rot).sum(-1) < 1e-8
+        if iter > p.reset_every:
+            is_prune |= scales.max(-1).values > p.prune_scale3d * p.scene_scale
+        if int(is_prune.sum()) > 0:
+            self.remove(is_prune)
+
+    def reset_opacity(self):
+        """default_strategy.cpp:243-282: clamp the logits at logit(2 prune_opacity), zero the opacity moments."""
+        thr = torch.logit(torch.tensor(2.0 * self._params.prune_opacity)).item()
+        self._sync_sizes()
+        self._splat_data.tensor("opacity_raw").clamp_(max=thr)
+        self._optimizer.exp_avg.tensor("opacity_raw").zero_()
+        self._optimizer.exp_avg_sq.tensor("opacity_raw").zero_()

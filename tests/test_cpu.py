@@ -216,3 +216,51 @@ def test_library_fails_loudly_without_gpu(pkg):
         pkg.ops.quats_to_rotmats(torch.zeros(4, 4))
     with pytest.raises(pkg.LfsError):
         pkg._capi.call("lfs_quats_to_rotmats", 4, ctypes.c_void_p(256), ctypes.c_void_p(512), None)
+
+
+def test_default_strategy_adc_on_cpu_tensors(pkg):
+    """DefaultStrategy (src/training/strategies/default_strategy.cpp) duplicate / prune / reset on CPU tensors:
+    row order, appended rows, zeroed moments, size bookkeeping. split() needs the CUDA quats_to_rotmats."""
+    import torch
+    tr, st = pkg.trainer, pkg.strategy
+    n = 10
+    sd = tr.SplatData(n, 4, "cpu", capacity=40)
+    g = torch.Generator().manual_seed(0)
+    for name in tr.PARAM_NAMES:
+        sd.tensor(name).copy_(torch.randn(sd.tensor(name).shape, generator=g))
+    sd.tensor("scaling_raw").fill_(-6.0)           # small: exp(-6) = 0.0025 <= 0.01
+    sd.tensor("opacity_raw").fill_(2.0)
+    s = st.DefaultStrategy(sd)
+    p = st.DefaultStrategy.Parameters(sh_degree=1)
+    s.initialize(p)
+    assert s.is_refining(600) and not s.is_refining(500) and not s.is_refining(650)
+    s._optimizer.exp_avg.flat.fill_(1.0); s._optimizer.exp_avg_sq.flat.fill_(2.0)
+    before = {k: sd.tensor(k).clone() for k in tr.PARAM_NAMES}
+    s.densification_info = torch.zeros(2, n)
+    s.densification_info[0] = 4.0
+    s.densification_info[1, [1, 7]] = 4.0 * 0.001   # mean gradient 0.001 > 0.0002 for rows 1 and 7
+    s.grow_gs(600)
+    assert sd.size == 12 and s._optimizer.exp_avg.size == 12 and s.grads.size == 12
+    for k in tr.PARAM_NAMES:
+        assert torch.equal(sd.tensor(k)[:10], before[k]) and torch.equal(sd.tensor(k)[10:], before[k][[1, 7]])
+        assert s._optimizer.exp_avg.tensor(k)[:10].eq(1).all() and s._optimizer.exp_avg.tensor(k)[10:].eq(0).all()
+        assert s._optimizer.exp_avg_sq.tensor(k)[10:].eq(0).all()
+    # prune: transparent rows, zero quaternions and (after the first reset) huge Gaussians
+    sd.tensor("opacity_raw")[3] = -8.0
+    sd.tensor("rotation_raw")[5] = 0.0
+    sd.tensor("scaling_raw")[8] = 0.0            # exp(0) = 1 > 0.1
+    keep_means = sd.tensor("means").clone()
+    s.prune_gs(600)
+    assert sd.size == 10 and torch.equal(sd.tensor("means"), keep_means[[0, 1, 2, 4, 6, 7, 8, 9, 10, 11]])
+    s.prune_gs(3100)
+    assert sd.size == 9
+    s.reset_opacity()
+    lim = float(torch.logit(torch.tensor(0.01)))
+    assert float(sd.tensor("opacity_raw").max()) <= lim + 1e-6 and s._optimizer.exp_avg.tensor("opacity_raw").eq(0).all()
+    m = s._optimizer.exp_avg.tensor("means")   # the two duplicated rows keep their zero moments
+    assert m[:7].eq(1).all() and m[7:].eq(0).all()
+    mask = torch.zeros(9, dtype=torch.bool); mask[0] = True
+    s.remove_gaussians(mask)
+    assert sd.size == 8
+    s.post_backward(25000)
+    assert s.densification_info.numel() == 0
