@@ -110,21 +110,24 @@ int lfs_intersect_offset(int64_t n_isects, const int64_t* isect_ids, int C, int 
 size_t lfs_rasterize_workspace_bytes(int N);
 
 /* gsplat/Ops.h:97-125 rasterize_to_pixels_from_world_3dgs_fwd ->
- * gsplat/RasterizeToPixelsFromWorld3DGSFwd.cu:20 (CDIM = 3, one camera). backgrounds [3] or NULL.
- * renders [H,W,3], alphas [H,W,1], last_ids [H,W]. */
+ * gsplat/RasterizeToPixelsFromWorld3DGSFwd.cu:20, one camera. colors [N,channels] with channels 1, 3 or 4
+ * (the CDIM instantiations the render modes use, gsplat/Rasterization.cpp:107-110, :373-393).
+ * backgrounds [channels] or NULL. masks [tile_h*tile_w] bytes or NULL: a tile labelled 0 is filled with the
+ * background (alpha and last_ids 0 there; the reference leaves those two unwritten).
+ * renders [H,W,channels], alphas [H,W,1], last_ids [H,W]. */
 int lfs_rasterize_to_pixels_from_world_3dgs_fwd(
-    int N, int64_t n_isects, const float* means, const float* quats, const float* scales, const float* colors,
-    const float* opacities, const float* backgrounds, int image_width, int image_height, int tile_size,
+    int N, int64_t n_isects, int channels, const float* means, const float* quats, const float* scales, const float* colors,
+    const float* opacities, const float* backgrounds, const uint8_t* masks, int image_width, int image_height, int tile_size,
     const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     float* renders, float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes, void* stream);
 
 /* gsplat/Ops.h:127-160 rasterize_to_pixels_from_world_3dgs_bwd ->
  * gsplat/RasterizeToPixelsFromWorld3DGSBwd.cu:17. Writes (not accumulates) v_means [N,3],
- * v_quats [N,4], v_scales [N,3], v_colors [N,3], v_opacities [N]. */
+ * v_quats [N,4], v_scales [N,3], v_colors [N,channels], v_opacities [N]. Masked tiles contribute nothing. */
 int lfs_rasterize_to_pixels_from_world_3dgs_bwd(
-    int N, int64_t n_isects, const float* means, const float* quats, const float* scales, const float* colors,
-    const float* opacities, const float* backgrounds, int image_width, int image_height, int tile_size,
+    int N, int64_t n_isects, int channels, const float* means, const float* quats, const float* scales, const float* colors,
+    const float* opacities, const float* backgrounds, const uint8_t* masks, int image_width, int image_height, int tile_size,
     const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
@@ -172,6 +175,12 @@ typedef struct lfs_splats {
     float* opacity_raw;  /* [N,1] logit */
 } lfs_splats;
 
+/* RenderMode of src/training/rasterization/rasterizer.hpp: colour, accumulated depth, expected depth
+ * (= accumulated / max(alpha, 1e-10), src/training/rasterization/rasterizer.cpp:186-198), and both. */
+typedef enum lfs_render_mode {
+    LFS_RENDER_RGB = 0, LFS_RENDER_D = 1, LFS_RENDER_ED = 2, LFS_RENDER_RGB_D = 3, LFS_RENDER_RGB_ED = 4
+} lfs_render_mode;
+
 /* Constants of src/training/rasterization/rasterizer.cpp:90-94 plus the per-call inputs. */
 typedef struct lfs_render_config {
     int N;                 /* Gaussians */
@@ -183,6 +192,11 @@ typedef struct lfs_render_config {
     float eps2d, near_plane, far_plane, radius_clip;
     lfs_ut_params ut;
     int64_t isect_capacity; /* room for intersections in the workspace; overflow -> LFS_ECAPACITY flag */
+    /* FusedRasterizationSettings (src/training/rasterization/rasterizer_autograd.hpp); zero = the trainer's defaults */
+    int render_mode;        /* lfs_render_mode: channels of `render` are 3, 1, 1, 4, 4 */
+    int calc_compensations; /* `antialiased`: blended opacity = opacity * compensation (gsplat/Rasterization.cpp:396-399) */
+    float scaling_modifier; /* scales are multiplied by it; 0 means 1.0 */
+    const uint8_t* tile_masks; /* device [tile_h*tile_w] bytes or NULL (gsplat/Ops.h `masks`) */
 } lfs_render_config;
 
 size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);
@@ -190,8 +204,12 @@ size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);
 /* Forward of FusedRasterizationWithSHFunction (src/training/rasterization/rasterizer_autograd.cpp:11)
  * = gsplat::rasterize_from_world_with_sh_fwd (gsplat/Rasterization.cpp:279) including the SplatData
  * activations (src/core/splat_data.cpp:267-286), for one camera. viewmat [4,4], K [3,3],
- * radial_coeffs [4] or NULL, background [3] or NULL are device pointers.
- * Outputs: render [H,W,3] (unclamped), alpha [H,W,1]. Everything the backward needs stays in the
+ * radial_coeffs [4] or NULL, background [channels] or NULL are device pointers.
+ * Outputs: render [H,W,channels] (unclamped; channels by render_mode: colour first, depth last; in the two
+ * expected-depth modes the depth channel is already divided by max(alpha, 1e-10)), alpha [H,W,1].
+ * The depth channel's background is background[channels-1]; the reference passes its 3-float colour
+ * background to the 1-channel kernel (so depth gets the red value) and reads past it with 4 channels:
+ * callers that want the same pictures pass {r} resp. {r,g,b,0}. Everything the backward needs stays in the
  * workspace. status_dev (device int32[4]): [0] overflow flag, [1] n_isects, [2] n_visible. */
 int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat,
                        const float* K, const float* radial_coeffs, const float* background,
@@ -200,7 +218,10 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
 
 /* Backward of the same node (rasterizer_autograd.cpp:105 -> gsplat/Rasterization.cpp:470) followed by
  * the activation backward, for the camera whose forward state is in the workspace. alpha is the
- * forward's alpha output, v_render [H,W,3] and v_alpha [H,W,1] (may be NULL = zeros) the output gradients.
+ * forward's alpha output, v_render [H,W,channels] and v_alpha [H,W,1] (may be NULL = zeros) the output
+ * gradients (w.r.t. the divided depth in the expected-depth modes). As in the reference, the depth channel
+ * only acts on the parameters through alpha (its per-Gaussian gradient is dropped, gsplat/Rasterization.cpp:575-590)
+ * and the opacity gradient is not multiplied by the compensation.
  * Call it once per lfs_render_forward: it consumes the per-Gaussian accumulators that the forward zeroed.
  * grads: the six raw-parameter gradients; accumulate != 0 adds to them, else they are overwritten
  * (all N rows, zeros for Gaussians that were not visible). */

@@ -30,7 +30,8 @@ class RenderConfig(C.Structure):
     _fields_ = [("N", C.c_int), ("sh_coeffs", C.c_int), ("sh_degree", C.c_int), ("image_width", C.c_int),
                 ("image_height", C.c_int), ("tile_size", C.c_int), ("camera_model", C.c_int),
                 ("eps2d", C.c_float), ("near_plane", C.c_float), ("far_plane", C.c_float), ("radius_clip", C.c_float),
-                ("ut", UTParams), ("isect_capacity", C.c_int64)]
+                ("ut", UTParams), ("isect_capacity", C.c_int64), ("render_mode", C.c_int), ("calc_compensations", C.c_int),
+                ("scaling_modifier", C.c_float), ("tile_masks", C.c_void_p)]
 
 
 class RenderView(C.Structure):
@@ -62,9 +63,9 @@ _SIGNATURES = {
     "lfs_intersect_tile_count": [i32, i32, vp, vp, i32, i32, i32, vp, vp, vp],
     "lfs_intersect_tile_emit": [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, sz, vp],
     "lfs_intersect_offset": [i64, vp, i32, i32, i32, vp, vp],
-    "lfs_rasterize_to_pixels_from_world_3dgs_fwd": [i32, i64, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp,
+    "lfs_rasterize_to_pixels_from_world_3dgs_fwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp,
                                                     vp, vp, vp, vp, vp, vp, sz, vp],
-    "lfs_rasterize_to_pixels_from_world_3dgs_bwd": [i32, i64, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp,
+    "lfs_rasterize_to_pixels_from_world_3dgs_bwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp,
                                                     vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
     "lfs_fusedssim": [i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp],
     "lfs_fusedssim_backward": [i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp],

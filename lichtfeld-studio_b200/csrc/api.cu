@@ -59,7 +59,7 @@ struct RenderWs {
     CamDev* cam;
     int32_t* counters;  // [0] overflow, [1] n_isects, [2] n_visible
     int32_t *radii, *tiles, *offs, *tile_offsets, *last_ids;
-    float *means2d, *depths, *accum;
+    float *means2d, *depths, *accum, *extra_sum;
     float4* records;
     uint4* bounds;
     uint32_t *gkeys[2], *gvals[2], *tkeys[2], *tvals[2];
@@ -88,6 +88,7 @@ RenderWs carve_render(const lfs_render_config& cfg, void* base) {
     for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
     w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
     w.last_ids = c.take<int32_t>((size_t)cfg.image_width * cfg.image_height);
+    w.extra_sum = c.take<float>((size_t)cfg.image_width * cfg.image_height);  // blended depth before the division (ED modes)
     w.scratch = carve_scratch(c);
     w.bytes = c.total();
     return w;
@@ -101,8 +102,16 @@ int check_cfg(const lfs_render_config* cfg) {
     LFS_REQUIRE(cfg->sh_coeffs >= (cfg->sh_degree + 1) * (cfg->sh_degree + 1), "not enough SH coefficients for the degree");
     LFS_REQUIRE(cfg->camera_model == LFS_PINHOLE || cfg->camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
     LFS_REQUIRE(cfg->isect_capacity >= 0 && cfg->isect_capacity < ((int64_t)1 << 31), "isect_capacity out of range");
+    LFS_REQUIRE(cfg->render_mode >= LFS_RENDER_RGB && cfg->render_mode <= LFS_RENDER_RGB_ED, "render_mode must be in [0,4]");
+    LFS_REQUIRE(cfg->scaling_modifier >= 0.f, "scaling_modifier must be positive (0 = 1.0)");
     return LFS_OK;
 }
+
+int mode_channels(int render_mode) {
+    return render_mode == LFS_RENDER_RGB ? 3 : (render_mode == LFS_RENDER_D || render_mode == LFS_RENDER_ED) ? 1 : 4;
+}
+int mode_normalize(int render_mode) { return render_mode == LFS_RENDER_ED || render_mode == LFS_RENDER_RGB_ED; }
+float cfg_modifier(const lfs_render_config& cfg) { return cfg.scaling_modifier > 0.f ? cfg.scaling_modifier : 1.0f; }
 
 }  // namespace
 }  // namespace lfs
@@ -211,12 +220,14 @@ size_t lfs_rasterize_workspace_bytes(int N) {
     c.take<float4>((size_t)N * 4);
     c.take<uint4>((size_t)N);
     c.take<float>((size_t)N * 16);
+    c.take<float>((size_t)N);
     return c.total();
 }
 
-static int raster_common(int N, int64_t n_isects, int W, int H, int tile_size, int camera_model, const void* workspace,
-                         size_t workspace_bytes) {
+static int raster_common(int N, int64_t n_isects, int channels, int W, int H, int tile_size, int camera_model,
+                         const void* workspace, size_t workspace_bytes) {
     LFS_REQUIRE(N >= 0 && n_isects >= 0 && n_isects < ((int64_t)1 << 31) && W > 0 && H > 0, "bad sizes");
+    LFS_REQUIRE(channels == 1 || channels == 3 || channels == 4, "colours must have 1, 3 or 4 channels");
     LFS_REQUIRE(tile_size == 16, "tile_size must be 16");
     LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
     LFS_REQUIRE(workspace != nullptr, "null workspace");
@@ -224,14 +235,15 @@ static int raster_common(int N, int64_t n_isects, int W, int H, int tile_size, i
     return LFS_OK;
 }
 
-int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, const float* means, const float* quats,
+int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, int channels, const float* means, const float* quats,
                                                 const float* scales, const float* colors, const float* opacities,
-                                                const float* backgrounds, int W, int H, int tile_size, const float* viewmat0,
+                                                const float* backgrounds, const uint8_t* masks, int W, int H, int tile_size,
+                                                const float* viewmat0,
                                                 const float* K, int camera_model, const float* radial_coeffs,
                                                 const int32_t* tile_offsets, const int32_t* flatten_ids, float* renders,
                                                 float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes,
                                                 void* stream) {
-    int rc = raster_common(N, n_isects, W, H, tile_size, camera_model, workspace, workspace_bytes);
+    int rc = raster_common(N, n_isects, channels, W, H, tile_size, camera_model, workspace, workspace_bytes);
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(viewmat0 && K && tile_offsets && renders && alphas && last_ids, "null pointer");
     LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
@@ -241,23 +253,24 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, const f
     uint4* bounds = c.take<uint4>((size_t)N);
     rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
     if (rc != LFS_OK) return rc;
-    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, bounds, nullptr, S(stream));
+    rc = launch_pack_records(N, means, quats, scales, colors, channels, opacities, cam, records, bounds, nullptr, nullptr, S(stream));
     if (rc != LFS_OK) return rc;
     RasterArgs a{cam, records, bounds, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
-                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model};
-    return launch_raster_fwd(a, renders, alphas, last_ids, S(stream));
+                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model, channels, 0, masks};
+    return launch_raster_fwd(a, renders, alphas, last_ids, nullptr, S(stream));
 }
 
-int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, const float* means, const float* quats,
+int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, int channels, const float* means, const float* quats,
                                                 const float* scales, const float* colors, const float* opacities,
-                                                const float* backgrounds, int W, int H, int tile_size, const float* viewmat0,
+                                                const float* backgrounds, const uint8_t* masks, int W, int H, int tile_size,
+                                                const float* viewmat0,
                                                 const float* K, int camera_model, const float* radial_coeffs,
                                                 const int32_t* tile_offsets, const int32_t* flatten_ids,
                                                 const float* render_alphas, const int32_t* last_ids,
                                                 const float* v_render_colors, const float* v_render_alphas, float* v_means,
                                                 float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
                                                 void* workspace, size_t workspace_bytes, void* stream) {
-    int rc = raster_common(N, n_isects, W, H, tile_size, camera_model, workspace, workspace_bytes);
+    int rc = raster_common(N, n_isects, channels, W, H, tile_size, camera_model, workspace, workspace_bytes);
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(viewmat0 && K && tile_offsets && render_alphas && last_ids && v_render_colors, "null pointer");
     LFS_REQUIRE(v_means && v_quats && v_scales && v_colors && v_opacities, "null output pointer");
@@ -267,15 +280,18 @@ int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, const f
     float4* records = c.take<float4>((size_t)N * 4);
     uint4* bounds = c.take<uint4>((size_t)N);
     float* accum = c.take<float>((size_t)N * 16);
+    float* accum_extra = channels != 3 ? c.take<float>((size_t)N) : nullptr;
     rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, W, H, camera_model, cam, S(stream));
     if (rc != LFS_OK) return rc;
-    rc = launch_pack_records(N, means, quats, scales, colors, opacities, cam, records, bounds, reinterpret_cast<float4*>(accum), S(stream));
+    rc = launch_pack_records(N, means, quats, scales, colors, channels, opacities, cam, records, bounds,
+                             reinterpret_cast<float4*>(accum), accum_extra, S(stream));
     if (rc != LFS_OK) return rc;
     RasterArgs a{cam, records, bounds, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
-                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model};
-    rc = launch_raster_bwd(a, render_alphas, last_ids, v_render_colors, v_render_alphas, accum, S(stream));
+                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, camera_model, channels, 0, masks};
+    rc = launch_raster_bwd(a, render_alphas, last_ids, nullptr, v_render_colors, v_render_alphas, accum, accum_extra, S(stream));
     if (rc != LFS_OK) return rc;
-    return launch_grad_epilogue_op(N, cam, accum, means, quats, scales, v_means, v_quats, v_scales, v_colors, v_opacities, S(stream));
+    return launch_grad_epilogue_op(N, cam, accum, means, quats, scales, channels, accum_extra, v_means, v_quats, v_scales,
+                                   v_colors, v_opacities, S(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -476,7 +492,11 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     if (rc != LFS_OK) return rc;
     cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
     const ProjParams pp = make_proj_params(cfg->eps2d, cfg->near_plane, cfg->far_plane, cfg->radius_clip, cfg->ut);
-    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, cfg->camera_model, cfg->tile_size, tw,
+    PackOptions opt;
+    opt.scaling_modifier = cfg_modifier(*cfg);
+    opt.calc_compensations = cfg->calc_compensations;
+    opt.want_rgb = mode_channels(cfg->render_mode) != 1;
+    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, opt, cfg->camera_model, cfg->tile_size, tw,
                              th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records, w.bounds,
                              reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
     if (rc != LFS_OK) return rc;
@@ -491,8 +511,9 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     rc = build_tile_lists(a, st);
     if (rc != LFS_OK) return rc;
     RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
-                  cfg->image_width, cfg->image_height, tw, th, cfg->camera_model};
-    rc = launch_raster_fwd(ra, render, alpha, w.last_ids, st);
+                  cfg->image_width, cfg->image_height, tw, th, cfg->camera_model, mode_channels(cfg->render_mode),
+                  mode_normalize(cfg->render_mode), cfg->tile_masks};
+    rc = launch_raster_fwd(ra, render, alpha, w.last_ids, w.extra_sum, st);
     if (rc != LFS_OK) return rc;
     if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
     return check_launch("lfs_render_forward");
@@ -511,11 +532,12 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
     const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
     const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
     RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
-                  cfg->image_width, cfg->image_height, tw, th, cfg->camera_model};
-    rc = launch_raster_bwd(ra, alpha, w.last_ids, v_render, v_alpha, w.accum, st);
+                  cfg->image_width, cfg->image_height, tw, th, cfg->camera_model, mode_channels(cfg->render_mode),
+                  mode_normalize(cfg->render_mode), cfg->tile_masks};
+    rc = launch_raster_bwd(ra, alpha, w.last_ids, w.extra_sum, v_render, v_alpha, w.accum, nullptr, st);
     if (rc != LFS_OK) return rc;
     return launch_grad_epilogue_fused(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, w.accum, w.records, w.radii, *params,
-                                      *grads, accumulate, st);
+                                      *grads, accumulate, cfg_modifier(*cfg), st);
 }
 
 int lfs_render_workspace_view(const lfs_render_config* cfg, void* workspace, size_t workspace_bytes, lfs_render_view* view) {

@@ -278,12 +278,14 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
 // rounding; when the ellipsoid reaches the camera plane (B22 <= 0) or the camera is not a pinhole the box is the
 // whole image. The rasterizer uses it only to skip (warp patch, Gaussian) pairs that cannot contribute.
 __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw, float qx, float qy, float qz,
-                                            f3 scale, float r, float g, float b, float opacity, float4* rec, uint4& box) {
+                                            f3 scale, float r, float g, float b, float opacity, float extra, float4* rec,
+                                            uint4& box) {
     float R[9], inv_norm, qn[4];
     quat_to_rotmat_renorm(qw, qx, qy, qz, R, inv_norm, qn);
     // exponent below which opacity * exp(p) < 1/255 for certain, as float bits in .z
     const uint32_t thr_bits = __float_as_uint(-logf(fmaxf(255.0f * opacity, 1e-30f)) - 0.02f);
-    box = make_uint4(0xFFFF0000u, 0xFFFF0000u, thr_bits, 0u);  // (lo | hi << 16) per axis: everything
+    const uint32_t extra_bits = __float_as_uint(extra);  // blended into the last channel of 1- and 4-channel renders
+    box = make_uint4(0xFFFF0000u, 0xFFFF0000u, thr_bits, extra_bits);  // (lo | hi << 16) per axis: everything
     if (cam.model == LFS_PINHOLE) {
         const float rho2 = 2.0f * (logf(fmaxf(255.0f * opacity, 1.0f)) + 0.03f);
         // V = R_c R with R_c = Rinv^T ; Sigma_c = rho2 V S^2 V^T ; mu_c = R_c mean + t
@@ -316,7 +318,7 @@ __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw
                 const uint32_t lo_u = (uint32_t)fminf(fmaxf(lo_j, 0.f), 65535.f), hi_u = (uint32_t)fminf(fmaxf(hi_j, 0.f), 65535.f);
                 packed[ax] = lo_u | (hi_u << 16);
             }
-            box = make_uint4(packed[0], packed[1], thr_bits, 0u);
+            box = make_uint4(packed[0], packed[1], thr_bits, extra_bits);
         }
     }
     const float is[3] = {1.0f / scale.x, 1.0f / scale.y, 1.0f / scale.z};
@@ -337,8 +339,8 @@ __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw
 
 __global__ void __launch_bounds__(256) pack_records_kernel(
     int N, const float* __restrict__ means, const float* __restrict__ quats, const float* __restrict__ scales,
-    const float* __restrict__ colors, const float* __restrict__ opacities, const CamDev* __restrict__ cams,
-    float4* __restrict__ records, uint4* __restrict__ bounds, float4* __restrict__ accum) {
+    const float* __restrict__ colors, int channels, const float* __restrict__ opacities, const CamDev* __restrict__ cams,
+    float4* __restrict__ records, uint4* __restrict__ bounds, float4* __restrict__ accum, float* __restrict__ accum_extra) {
     const CamDev cam = cams[0];
     for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
         const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
@@ -346,8 +348,11 @@ __global__ void __launch_bounds__(256) pack_records_kernel(
         const float4 q = reinterpret_cast<const float4*>(quats)[g];
         float4 rec[4];
         uint4 box;
-        make_record(cam, mean, q.x, q.y, q.z, q.w, scale, colors[g * 3], colors[g * 3 + 1], colors[g * 3 + 2],
-                    opacities[g], rec, box);
+        // colours [N, channels]: channels 3 = rgb; 4 = rgb + extra; 1 = extra only
+        const float* col = colors + (size_t)g * channels;
+        const bool has_rgb = channels >= 3;
+        make_record(cam, mean, q.x, q.y, q.z, q.w, scale, has_rgb ? col[0] : 0.f, has_rgb ? col[1] : 0.f, has_rgb ? col[2] : 0.f,
+                    opacities[g], channels != 3 ? col[channels - 1] : 0.f, rec, box);
 #pragma unroll
         for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
         bounds[g] = box;
@@ -355,14 +360,17 @@ __global__ void __launch_bounds__(256) pack_records_kernel(
 #pragma unroll
             for (int k = 0; k < 4; ++k) accum[(size_t)g * 4 + k] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
+        if (accum_extra) accum_extra[g] = 0.f;
     }
 }
 
-int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
-                        const float* opacities, const CamDev* cam, float4* records, uint4* bounds, float4* accum, cudaStream_t st) {
+int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors, int channels,
+                        const float* opacities, const CamDev* cam, float4* records, uint4* bounds, float4* accum,
+                        float* accum_extra, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("pack_records", st);
-    pack_records_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, means, quats, scales, colors, opacities, cam, records, bounds, accum);
+    pack_records_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, means, quats, scales, colors, channels, opacities, cam, records,
+                                                          bounds, accum, accum_extra);
     return check_launch("pack_records");
 }
 
@@ -375,7 +383,7 @@ template <int MODEL>
 __global__ void __launch_bounds__(256, 3) project_pack_kernel(
     int N, int K, int sh_degree, const float* __restrict__ means, const float* __restrict__ sh0,
     const float* __restrict__ shN, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
-    const float* __restrict__ opacity_raw, const CamDev* __restrict__ cams, ProjParams pp, float tile_size,
+    const float* __restrict__ opacity_raw, const CamDev* __restrict__ cams, ProjParams pp, PackOptions opt, float tile_size,
     uint32_t tw, uint32_t th,
     int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths,
     int32_t* __restrict__ tiles, uint32_t* __restrict__ sort_keys, uint32_t* __restrict__ sort_vals,
@@ -406,6 +414,7 @@ __global__ void __launch_bounds__(256, 3) project_pack_kernel(
             opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
             scale = f3{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
                        (float)exp((double)scaling_raw[g * 3 + 2])};
+            if (opt.scaling_modifier != 1.0f) { scale.x *= opt.scaling_modifier; scale.y *= opt.scaling_modifier; scale.z *= opt.scaling_modifier; }
             const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
             const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
             const float nrm = fmaxf(sqrtf(n2), 1e-12f);
@@ -419,7 +428,7 @@ __global__ void __launch_bounds__(256, 3) project_pack_kernel(
             }
         }
         const bool any_vis = __any_sync(0xffffffffu, vis);
-        if (any_vis && nb > 1) {
+        if (any_vis && nb > 1 && opt.want_rgb) {
             // one batch of asynchronous 16-byte copies (a single round trip instead of one per row slice); the
             // chunk starts 16-byte aligned because it begins at a multiple of 32 rows
             const int n_rows = min(32, N - chunk * 32);
@@ -447,22 +456,26 @@ __global__ void __launch_bounds__(256, 3) project_pack_kernel(
             ++local_visible;
 
             // colour from SH along (mean - camera position)
-            float B[25];
-            sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
-            float rgb[3];
+            float rgb[3] = {0.f, 0.f, 0.f};
+            if (opt.want_rgb) {
+                float B[25];
+                sh_basis(sh_degree, mean.x - cam.campos[0], mean.y - cam.campos[1], mean.z - cam.campos[2], B);
 #pragma unroll
-            for (int c = 0; c < 3; ++c) rgb[c] = B[0] * sh0[g * 3 + c];
-            const float* row = my + lane * rest;
-            for (int k = 1; k < nb; ++k) {
+                for (int c = 0; c < 3; ++c) rgb[c] = B[0] * sh0[g * 3 + c];
+                const float* row = my + lane * rest;
+                for (int k = 1; k < nb; ++k) {
 #pragma unroll
-                for (int c = 0; c < 3; ++c) rgb[c] += B[k] * row[(k - 1) * 3 + c];
+                    for (int c = 0; c < 3; ++c) rgb[c] += B[k] * row[(k - 1) * 3 + c];
+                }
+#pragma unroll
+                for (int c = 0; c < 3; ++c) rgb[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
             }
-#pragma unroll
-            for (int c = 0; c < 3; ++c) rgb[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
+            // antialiased mode: the blended opacity carries the blur compensation (gsplat/Rasterization.cpp:396-399)
+            if (opt.calc_compensations) opacity *= o.compensation;
 
             float4 rec[4];
             uint4 box;
-            make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, rec, box);
+            make_record(cam, mean, qw, qx, qy, qz, scale, rgb[0], rgb[1], rgb[2], opacity, o.depth, rec, box);
 #pragma unroll
             for (int k = 0; k < 4; ++k) records[(size_t)g * 4 + k] = rec[k];
             bounds[g] = box;
@@ -477,7 +490,7 @@ __global__ void __launch_bounds__(256, 3) project_pack_kernel(
 }
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
-                        int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
+                        const PackOptions& opt, int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
                         int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st) {
     if (N == 0) return LFS_OK;
@@ -491,12 +504,12 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
     LFS_TIMED("project_pack", st);
     if (model == LFS_PINHOLE)
         project_pack_kernel<LFS_PINHOLE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
-                                                               p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,
+                                                               p.rotation_raw, p.opacity_raw, cam, pp, opt, (float)tile_size,
                                                                tw, th, radii, means2d, depths, tiles, sort_keys,
                                                                sort_vals, records, bounds, accum, n_visible);
     else
         project_pack_kernel<LFS_FISHEYE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
-                                                               p.rotation_raw, p.opacity_raw, cam, pp, (float)tile_size,
+                                                               p.rotation_raw, p.opacity_raw, cam, pp, opt, (float)tile_size,
                                                                tw, th, radii, means2d, depths, tiles, sort_keys,
                                                                sort_vals, records, bounds, accum, n_visible);
     return check_launch("project_pack");

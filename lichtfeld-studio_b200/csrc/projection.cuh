@@ -25,11 +25,21 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
                          const ProjParams& pp, int model, int32_t* radii,
                          float* means2d, float* depths, float* conics, float* compensations, cudaStream_t st);
 
-int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors,
-                        const float* opacities, const CamDev* cam, float4* records, uint4* bounds, float4* accum, cudaStream_t st);
+// colours [N, channels] with channels 1 (extra only), 3 (rgb) or 4 (rgb + extra); accum / accum_extra (may be null)
+// are zeroed for the backward.
+int launch_pack_records(int N, const float* means, const float* quats, const float* scales, const float* colors, int channels,
+                        const float* opacities, const CamDev* cam, float4* records, uint4* bounds, float4* accum,
+                        float* accum_extra, cudaStream_t st);
+
+// Per-render switches of the fused path (FusedRasterizationSettings, src/training/rasterization/rasterizer_autograd.hpp).
+struct PackOptions {
+    float scaling_modifier = 1.0f;  // scales are multiplied by it before projection and blending
+    int calc_compensations = 0;     // antialiased: blended opacity = opacity * sqrt(det(cov) / det(cov + eps2d I))
+    int want_rgb = 1;               // 0 in the depth-only render modes: SH colours are not evaluated
+};
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
-                        int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
+                        const PackOptions& opt, int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
                         int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st);
 

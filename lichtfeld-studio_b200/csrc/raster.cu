@@ -108,13 +108,19 @@ __device__ __forceinline__ void issue_stage(Stage<BATCH>& st, uint32_t* sid, con
 }
 
 // ---------------------------------------------------------------------------------------------
-template <int MODEL>
+// EXTRA = false: three colour channels (render mode RGB). EXTRA = true: `channels` is 1 or 4 and the last
+// channel blends the per-Gaussian value kept in bounds.w (the depth in the render modes D / ED / RGB_D /
+// RGB_ED of gsplat/Rasterization.cpp:373-393); `normalize` divides it by max(alpha, 1e-10) on output (the
+// expected-depth modes of src/training/rasterization/rasterizer.cpp:186-198) and keeps the undivided value
+// in extra_sum for the backward.
+template <int MODEL, bool EXTRA>
 __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
-    const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
-    float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids) {
+    const int32_t* __restrict__ overflow, const float* __restrict__ background, const uint8_t* __restrict__ masks,
+    int channels, int normalize, int W, int H, int tw, int n_tiles,
+    float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids, float* __restrict__ extra_sum) {
     constexpr int BATCH = 256;
     __shared__ Stage<BATCH> stage[2];
 
@@ -123,6 +129,18 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     int i, j;
     pixel_of_thread(tile, tw, i, j);
     const bool inside = (i < H && j < W);
+    if (masks && !masks[tile]) {
+        // a tile labelled false shows the background (gsplat/RasterizeToPixelsFromWorld3DGSFwd.cu:147-155)
+        if (inside) {
+            const int pid = i * W + j;
+            const int ch = EXTRA ? channels : 3;
+            for (int k = 0; k < ch; ++k) render[pid * ch + k] = background ? background[k] : 0.f;
+            alphas[pid] = 0.f;
+            last_ids[pid] = 0;
+            if (EXTRA && extra_sum) extra_sum[pid] = background ? background[ch - 1] : 0.f;
+        }
+        return;
+    }
     const CamDev& cam = cams[0];
     f3 d;
     const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
@@ -137,7 +155,7 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
 
     float T = 1.0f;
     uint32_t cur_idx = 0;
-    float pr = 0.f, pg = 0.f, pb = 0.f;
+    float pr = 0.f, pg = 0.f, pb = 0.f, px = 0.f;
 
     StageIds<BATCH> ids;
     if (n_batches > 0) {
@@ -196,6 +214,7 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
                     if (next_T <= 1e-4f) { done = true; break; }
                     const float vis = alpha * T;
                     pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
+                    if (EXTRA) px += __uint_as_float(st.box[t].w) * vis;
                     cur_idx = (uint32_t)(batch_start + t);
                     T = next_T;
                 }
@@ -207,10 +226,22 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     if (inside) {
         const int pid = i * W + j;
         alphas[pid] = 1.0f - T;
-        if (background) { pr += T * background[0]; pg += T * background[1]; pb += T * background[2]; }
-        render[pid * 3 + 0] = pr;
-        render[pid * 3 + 1] = pg;
-        render[pid * 3 + 2] = pb;
+        if (!EXTRA) {
+            if (background) { pr += T * background[0]; pg += T * background[1]; pb += T * background[2]; }
+            render[pid * 3 + 0] = pr;
+            render[pid * 3 + 1] = pg;
+            render[pid * 3 + 2] = pb;
+        } else {
+            if (channels == 4) {
+                if (background) { pr += T * background[0]; pg += T * background[1]; pb += T * background[2]; }
+                render[pid * 4 + 0] = pr;
+                render[pid * 4 + 1] = pg;
+                render[pid * 4 + 2] = pb;
+            }
+            if (background) px += T * background[channels - 1];
+            if (extra_sum) extra_sum[pid] = px;
+            render[pid * channels + channels - 1] = normalize ? px / fmaxf(1.0f - T, 1e-10f) : px;
+        }
         last_ids[pid] = (int32_t)cur_idx;
     }
 }
@@ -255,27 +286,40 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16]) {
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
+__device__ __forceinline__ float __reduce_add_sync_f32(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
 template <int BATCH>
 struct BwdShared {
     Stage<BATCH> stage[2];
     uint32_t sid[2][BATCH];
     float sacc[BATCH * 16];
+    float sextra[BATCH];
     int stouched[BATCH];
 };
 
-template <int MODEL, int BATCH>
+// EXTRA: the output has 1 or 4 channels and its last one blends bounds.w (see the forward). XGRAD: also return
+// the gradient of that per-Gaussian value in accum_extra [N] (operator-level colours with 1 or 4 channels;
+// the fused render modes drop it like gsplat/Rasterization.cpp:575-590 does).
+template <int MODEL, int BATCH, bool EXTRA, bool XGRAD>
 __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
-    const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw, int n_tiles,
-    const float* __restrict__ render_alphas, const int32_t* __restrict__ last_ids,
-    const float* __restrict__ v_render, const float* __restrict__ v_alphas, float* __restrict__ accum) {
+    const int32_t* __restrict__ overflow, const float* __restrict__ background, const uint8_t* __restrict__ masks,
+    int channels, int normalize, int W, int H, int tw, int n_tiles,
+    const float* __restrict__ render_alphas, const int32_t* __restrict__ last_ids, const float* __restrict__ extra_sum,
+    const float* __restrict__ v_render, const float* __restrict__ v_alphas, float* __restrict__ accum,
+    float* __restrict__ accum_extra) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     BwdShared<BATCH>& sm = *reinterpret_cast<BwdShared<BATCH>*>(smem_raw);
 
     if (overflow && *overflow) return;
     const int tile = blockIdx.x;
+    if (masks && !masks[tile]) return;  // gsplat/RasterizeToPixelsFromWorld3DGSBwd.cu:84
     int i, j;
     pixel_of_thread(tile, tw, i, j);
     const bool inside = (i < H && j < W);
@@ -294,12 +338,28 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
 
     const float T_final = 1.0f - render_alphas[pid];
     float T = T_final;
-    float bufr = 0.f, bufg = 0.f, bufb = 0.f;
+    float bufr = 0.f, bufg = 0.f, bufb = 0.f, bufx = 0.f;
     const int32_t bin_final = active ? last_ids[pid] : 0;
-    const float vcr = v_render[pid * 3 + 0], vcg = v_render[pid * 3 + 1], vcb = v_render[pid * 3 + 2];
-    const float v_a = v_alphas ? v_alphas[pid] : 0.f;
+    float vcr, vcg, vcb, vcx = 0.f;
+    float v_a = v_alphas ? v_alphas[pid] : 0.f;
+    if (!EXTRA) {
+        vcr = v_render[pid * 3 + 0]; vcg = v_render[pid * 3 + 1]; vcb = v_render[pid * 3 + 2];
+    } else {
+        vcr = vcg = vcb = 0.f;
+        if (channels == 4) { vcr = v_render[pid * 4 + 0]; vcg = v_render[pid * 4 + 1]; vcb = v_render[pid * 4 + 2]; }
+        vcx = v_render[pid * channels + channels - 1];
+        if (normalize) {
+            // output = sum / max(alpha, 1e-10): chain rule of the division and of clamp_min
+            const float a = 1.0f - T_final, ac = fmaxf(a, 1e-10f);
+            if (a > 1e-10f) v_a -= extra_sum[pid] / (ac * ac) * vcx;
+            vcx = vcx / ac;
+        }
+    }
     float bg_dot = 0.f;
-    if (background) bg_dot = background[0] * vcr + background[1] * vcg + background[2] * vcb;
+    if (background) {
+        if (!EXTRA || channels == 4) bg_dot = background[0] * vcr + background[1] * vcg + background[2] * vcb;
+        if (EXTRA) bg_dot += background[channels - 1] * vcx;
+    }
     const float tail_c = T_final * (v_a - bg_dot);
     const int32_t warp_bin_final = __reduce_max_sync(0xffffffffu, bin_final);
     const int lane = threadIdx.x & 31;
@@ -307,6 +367,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     for (int e = threadIdx.x; e < BATCH; e += kBlock) {
 #pragma unroll
         for (int k = 0; k < 16; ++k) sm.sacc[e * 16 + k] = 0.f;
+        sm.sextra[e] = 0.f;
         sm.stouched[e] = 0;
     }
 
@@ -380,6 +441,11 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                     const float fac = alpha * T;
                     v[12] = fac * vcr; v[13] = fac * vcg; v[14] = fac * vcb;
                     float v_alpha = (r3.x * T - bufr * ra) * vcr + (r3.y * T - bufg * ra) * vcg + (r3.z * T - bufb * ra) * vcb;
+                    float xval = 0.f;
+                    if (EXTRA) {
+                        xval = __uint_as_float(st.box[t].w);
+                        v_alpha += (xval * T - bufx * ra) * vcx;
+                    }
                     v_alpha += ra * tail_c;  // T_final * ra * (v_alpha_out - background . v_colour_out)
                     // geometry and opacity only while alpha is not clamped at 0.999
                     const float gate = (r3.w * vis <= 0.999f) ? vis : 0.f;
@@ -397,6 +463,11 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                     v[9] = -s * wx; v[10] = -s * wy; v[11] = -s * wz;
                     v[15] = gate * v_alpha;
                     bufr += r3.x * fac; bufg += r3.y * fac; bufb += r3.z * fac;
+                    if (EXTRA) bufx += xval * fac;
+                    if (XGRAD) {
+                        const float xs = __reduce_add_sync_f32(fac * vcx);
+                        if (lane == 0) atomicAdd(&sm.sextra[t], xs);
+                    }
                 }
                 const float total = warp_reduce16(v);
                 if ((lane & 1) == 0) atomicAdd(&sm.sacc[t * 16 + (lane >> 1)], total);
@@ -415,6 +486,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                     atomicAdd(dst + k, src[k]);
                     src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
+                if (XGRAD) { atomicAdd(accum_extra + g, sm.sextra[e]); sm.sextra[e] = 0.f; }
                 sm.stouched[e] = 0;
             }
         }
@@ -473,8 +545,9 @@ __device__ __forceinline__ void gaussian_vjp(const CamDev& cam, const float* acc
 
 __global__ void __launch_bounds__(256) grad_epilogue_op_kernel(
     int N, const CamDev* __restrict__ cams, const float* __restrict__ accum, const float* __restrict__ means,
-    const float* __restrict__ quats, const float* __restrict__ scales, float* __restrict__ v_means,
-    float* __restrict__ v_quats, float* __restrict__ v_scales, float* __restrict__ v_colors, float* __restrict__ v_opacities) {
+    const float* __restrict__ quats, const float* __restrict__ scales, int channels, const float* __restrict__ accum_extra,
+    float* __restrict__ v_means, float* __restrict__ v_quats, float* __restrict__ v_scales, float* __restrict__ v_colors,
+    float* __restrict__ v_opacities) {
     const CamDev& cam = cams[0];
     for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < N; g += gridDim.x * blockDim.x) {
         float acc[16];
@@ -486,7 +559,12 @@ __global__ void __launch_bounds__(256) grad_epilogue_op_kernel(
         gaussian_vjp(cam, acc, f3{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]}, q.x, q.y, q.z, q.w,
                      f3{scales[g * 3], scales[g * 3 + 1], scales[g * 3 + 2]}, o);
 #pragma unroll
-        for (int k = 0; k < 3; ++k) { v_means[g * 3 + k] = o.v_mean[k]; v_scales[g * 3 + k] = o.v_scale[k]; v_colors[g * 3 + k] = o.v_rgb[k]; }
+        for (int k = 0; k < 3; ++k) { v_means[g * 3 + k] = o.v_mean[k]; v_scales[g * 3 + k] = o.v_scale[k]; }
+        if (channels >= 3) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) v_colors[(size_t)g * channels + k] = o.v_rgb[k];
+        }
+        if (channels != 3) v_colors[(size_t)g * channels + channels - 1] = accum_extra[g];
 #pragma unroll
         for (int k = 0; k < 4; ++k) v_quats[g * 4 + k] = o.v_quat[k];
         v_opacities[g] = o.v_opac;
@@ -502,7 +580,7 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
     const float* __restrict__ means, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
     const float* __restrict__ opacity_raw,
     float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN, float* __restrict__ g_scaling,
-    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate) {
+    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate, float scaling_modifier) {
     extern __shared__ float s_rows[];
     const CamDev& cam = cams[0];
     const int rest = (K - 1) * 3;
@@ -527,8 +605,10 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
             for (int k = 0; k < 4; ++k) { const float4 t = a4[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
             const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
             const float opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
-            const f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
-                           (float)exp((double)scaling_raw[g * 3 + 2])};
+            // scale as blended: exp(raw) * modifier; d(scale)/d(raw) is the same product
+            f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
+                     (float)exp((double)scaling_raw[g * 3 + 2])};
+            if (scaling_modifier != 1.0f) { scale.x *= scaling_modifier; scale.y *= scaling_modifier; scale.z *= scaling_modifier; }
             const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
             const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
             const float nrm = fmaxf(sqrtf(n2), 1e-12f);
@@ -589,60 +669,69 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
 
 }  // namespace
 
-int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, cudaStream_t st) {
+int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, float* extra_sum, cudaStream_t st) {
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
+    if (a.channels != 1 && a.channels != 3 && a.channels != 4) { set_error("raster_fwd: channels must be 1, 3 or 4"); return LFS_EINVAL; }
     LFS_TIMED("raster_fwd", st);
-    if (a.model == LFS_PINHOLE)
-        raster_fwd_kernel<LFS_PINHOLE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
-                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
-                                                                   a.H, a.tw, n_tiles, render, alphas, last_ids);
-    else
-        raster_fwd_kernel<LFS_FISHEYE><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
-                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
-                                                                   a.H, a.tw, n_tiles, render, alphas, last_ids);
+#define LFS_FWD(MODEL, EXTRA)                                                                                              \
+    raster_fwd_kernel<MODEL, EXTRA><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,  \
+                                                                a.n_isects_dev, a.n_isects_host, a.overflow, a.background, \
+                                                                a.masks, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles,  \
+                                                                render, alphas, last_ids, extra_sum)
+    const bool extra = a.channels != 3;
+    if (a.model == LFS_PINHOLE) { if (extra) LFS_FWD(LFS_PINHOLE, true); else LFS_FWD(LFS_PINHOLE, false); }
+    else { if (extra) LFS_FWD(LFS_FISHEYE, true); else LFS_FWD(LFS_FISHEYE, false); }
+#undef LFS_FWD
     return check_launch("raster_fwd");
 }
 
-int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int32_t* last_ids, const float* v_render,
-                      const float* v_alphas, float* accum, cudaStream_t st) {
+int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int32_t* last_ids, const float* extra_sum,
+                      const float* v_render, const float* v_alphas, float* accum, float* accum_extra, cudaStream_t st) {
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
+    if (a.channels != 1 && a.channels != 3 && a.channels != 4) { set_error("raster_bwd: channels must be 1, 3 or 4"); return LFS_EINVAL; }
+    if (a.normalize && !extra_sum) { set_error("raster_bwd: expected-depth modes need the forward's blended sum"); return LFS_EINVAL; }
     LFS_TIMED("raster_bwd", st);
     constexpr int kBwdBatch = 128;
     const size_t smem = sizeof(BwdShared<kBwdBatch>);
     static bool attr_set = false;
+#define LFS_BWD_ATTR(MODEL, EXTRA, XGRAD) \
+    cudaFuncSetAttribute(raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
     if (!attr_set) {
-        cudaFuncSetAttribute(raster_bwd_kernel<LFS_PINHOLE, kBwdBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(raster_bwd_kernel<LFS_FISHEYE, kBwdBatch>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        LFS_BWD_ATTR(LFS_PINHOLE, false, false); LFS_BWD_ATTR(LFS_PINHOLE, true, false); LFS_BWD_ATTR(LFS_PINHOLE, true, true);
+        LFS_BWD_ATTR(LFS_FISHEYE, false, false); LFS_BWD_ATTR(LFS_FISHEYE, true, false); LFS_BWD_ATTR(LFS_FISHEYE, true, true);
         attr_set = true;
     }
-    if (a.model == LFS_PINHOLE)
-        raster_bwd_kernel<LFS_PINHOLE, kBwdBatch><<<n_tiles, kBlock, smem, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
-                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
-                                                                   a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
-                                                                   v_alphas, accum);
-    else
-        raster_bwd_kernel<LFS_FISHEYE, kBwdBatch><<<n_tiles, kBlock, smem, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,
-                                                                   a.n_isects_dev, a.n_isects_host, a.overflow, a.background, a.W,
-                                                                   a.H, a.tw, n_tiles, render_alphas, last_ids, v_render,
-                                                                   v_alphas, accum);
+#undef LFS_BWD_ATTR
+#define LFS_BWD(MODEL, EXTRA, XGRAD)                                                                                          \
+    raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD><<<n_tiles, kBlock, smem, st>>>(                                          \
+        a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets, a.n_isects_dev, a.n_isects_host, a.overflow, a.background, \
+        a.masks, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles, render_alphas, last_ids, extra_sum, v_render, v_alphas,   \
+        accum, accum_extra)
+    const bool extra = a.channels != 3, xgrad = extra && accum_extra != nullptr;
+    if (a.model == LFS_PINHOLE) {
+        if (!extra) LFS_BWD(LFS_PINHOLE, false, false); else if (!xgrad) LFS_BWD(LFS_PINHOLE, true, false); else LFS_BWD(LFS_PINHOLE, true, true);
+    } else {
+        if (!extra) LFS_BWD(LFS_FISHEYE, false, false); else if (!xgrad) LFS_BWD(LFS_FISHEYE, true, false); else LFS_BWD(LFS_FISHEYE, true, true);
+    }
+#undef LFS_BWD
     return check_launch("raster_bwd");
 }
 
 int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const float* means, const float* quats,
-                            const float* scales, float* v_means, float* v_quats, float* v_scales, float* v_colors,
-                            float* v_opacities, cudaStream_t st) {
+                            const float* scales, int channels, const float* accum_extra, float* v_means, float* v_quats,
+                            float* v_scales, float* v_colors, float* v_opacities, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("grad_epilogue", st);
-    grad_epilogue_op_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, cam, accum, means, quats, scales, v_means, v_quats,
-                                                              v_scales, v_colors, v_opacities);
+    grad_epilogue_op_kernel<<<grid_for(N, 256), 256, 0, st>>>(N, cam, accum, means, quats, scales, channels, accum_extra,
+                                                              v_means, v_quats, v_scales, v_colors, v_opacities);
     return check_launch("grad_epilogue_op");
 }
 
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
-                               int accumulate, cudaStream_t st) {
+                               int accumulate, float scaling_modifier, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("grad_epilogue", st);
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
@@ -652,7 +741,7 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
     grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
                                                                  p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
                                                                  g.sh0, g.shN, g.scaling_raw, g.rotation_raw,
-                                                                 g.opacity_raw, accumulate);
+                                                                 g.opacity_raw, accumulate, scaling_modifier);
     return check_launch("grad_epilogue_fused");
 }
 

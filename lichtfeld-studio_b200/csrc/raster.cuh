@@ -8,8 +8,9 @@ namespace lfs {
 struct RasterArgs {
     const CamDev* cam;            // one camera
     const float4* records;        // [N] packed 64-byte records
-    const uint4* bounds;          // [N] (x box, y box, rejection exponent, 0): inclusive pixel box (lo | hi << 16)
-                                  //     outside of which alpha < 1/255, and -ln(255 opacity) - margin as float bits
+    const uint4* bounds;          // [N] (x box, y box, rejection exponent, extra): inclusive pixel box (lo | hi << 16)
+                                  //     outside of which alpha < 1/255, -ln(255 opacity) - margin as float bits, and the
+                                  //     value blended into the last channel when channels is 1 or 4 (the depth)
     const uint32_t* flatten_ids;  // depth-sorted Gaussian index per instance
     const int32_t* tile_offsets;  // [tw*th] first instance of each tile
     const int32_t* n_isects_dev;  // device-side instance count, or null to use n_isects_host
@@ -17,16 +18,21 @@ struct RasterArgs {
     const float* background;      // [3] or null
     const int32_t* overflow;      // device flag: when set the lists are incomplete and nothing is drawn (may be null)
     int W, H, tw, th, model;
+    int channels = 3;             // 3 = colour; 1 = extra only; 4 = colour + extra
+    int normalize = 0;            // divide the extra channel by max(alpha, 1e-10) on output (expected depth)
+    const uint8_t* masks = nullptr;  // [tw*th] or null: tiles labelled 0 show the background and get no gradient
 };
 
-int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, cudaStream_t st);
-int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int32_t* last_ids, const float* v_render,
-                      const float* v_alphas, float* accum, cudaStream_t st);
+// extra_sum [H*W] (may be null unless a.normalize): the blended, undivided last channel, kept for the backward.
+int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, float* extra_sum, cudaStream_t st);
+// accum_extra [N] (zeroed by the caller) receives the gradient of the per-Gaussian extra value; null drops it.
+int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int32_t* last_ids, const float* extra_sum,
+                      const float* v_render, const float* v_alphas, float* accum, float* accum_extra, cudaStream_t st);
 int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const float* means, const float* quats,
-                            const float* scales, float* v_means, float* v_quats, float* v_scales, float* v_colors,
-                            float* v_opacities, cudaStream_t st);
+                            const float* scales, int channels, const float* accum_extra, float* v_means, float* v_quats,
+                            float* v_scales, float* v_colors, float* v_opacities, cudaStream_t st);
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
-                               int accumulate, cudaStream_t st);
+                               int accumulate, float scaling_modifier, cudaStream_t st);
 
 }  // namespace lfs

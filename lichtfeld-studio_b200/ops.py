@@ -145,7 +145,7 @@ def projection_ut_3dgs_fused(means, quats, scales, opacities, viewmats0, viewmat
     means2d = torch.empty((Cn, N, 2), dtype=torch.float32, device=dev)
     depths = torch.empty((Cn, N), dtype=torch.float32, device=dev)
     conics = torch.empty((Cn, N, 3), dtype=torch.float32, device=dev)
-    comps = torch.empty((Cn, N), dtype=torch.float32, device=dev) if calc_compensations else None
+    comps = torch.zeros((Cn, N), dtype=torch.float32, device=dev) if calc_compensations else None
     call("lfs_projection_ut_3dgs_fused", Cn, N, ptr(means), ptr(quats), ptr(scales), ptr(opacities), ptr(viewmats0), ptr(Ks),
          int(image_width), int(image_height), float(eps2d), float(near_plane), float(far_plane), float(radius_clip),
          int(camera_model), ut, ptr(radial_coeffs), ptr(radii), ptr(means2d), ptr(depths), ptr(conics), ptr(comps), _stream())
@@ -160,6 +160,16 @@ def _one_camera(viewmats0, Ks, tile_offsets, opacities):
         raise RuntimeError("packed mode is not supported")
 
 
+def _tile_masks(masks, image_width, image_height, tile_size):
+    """[C, tile_h, tile_w] bool -> contiguous uint8 view (the C ABI takes bytes)."""
+    if masks is None:
+        return None
+    tw, th = (int(image_width) + tile_size - 1) // tile_size, (int(image_height) + tile_size - 1) // tile_size
+    if masks.numel() != tw * th or masks.dtype != torch.bool or not masks.is_cuda:
+        raise RuntimeError(f"masks must be a CUDA bool tensor [1, {th}, {tw}]")
+    return masks.contiguous().view(torch.uint8)
+
+
 # gsplat/Ops.h:97-125
 def rasterize_to_pixels_from_world_3dgs_fwd(means, quats, scales, colors, opacities, backgrounds, masks, image_width,
                                             image_height, tile_size, viewmats0, viewmats1, Ks, camera_model,
@@ -171,20 +181,22 @@ def rasterize_to_pixels_from_world_3dgs_fwd(means, quats, scales, colors, opacit
         _check_input(t, n)
     _check_input(tile_offsets, "tile_offsets", torch.int32); _check_input(flatten_ids, "flatten_ids", torch.int32)
     _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
-    if masks is not None:
-        raise RuntimeError("tile masks are not supported")
-    if colors.shape[-1] != 3:
-        raise RuntimeError(f"Unsupported number of channels: {colors.shape[-1]}")
+    CH = int(colors.shape[-1])
+    if CH not in (1, 3, 4):
+        raise RuntimeError(f"Unsupported number of channels: {CH}")
+    masks = _tile_masks(masks, image_width, image_height, tile_size)
     _one_camera(viewmats0, Ks, tile_offsets, opacities)
     N, dev = means.shape[0], means.device
     H, W = int(image_height), int(image_width)
-    renders = torch.empty((1, H, W, 3), dtype=torch.float32, device=dev)
+    renders = torch.empty((1, H, W, CH), dtype=torch.float32, device=dev)
     alphas = torch.empty((1, H, W, 1), dtype=torch.float32, device=dev)
     last_ids = torch.empty((1, H, W), dtype=torch.int32, device=dev)
     bg = backgrounds if (backgrounds is not None and backgrounds.numel() > 0) else None
     ws = _ws(capi.lib().lfs_rasterize_workspace_bytes(N), dev)
-    call("lfs_rasterize_to_pixels_from_world_3dgs_fwd", N, flatten_ids.numel(), ptr(means), ptr(quats), ptr(scales), ptr(colors),
-         ptr(opacities), ptr(bg), W, H, int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model), ptr(radial_coeffs),
+    if bg is not None and bg.numel() < CH:
+        raise RuntimeError(f"backgrounds must have {CH} channels")
+    call("lfs_rasterize_to_pixels_from_world_3dgs_fwd", N, flatten_ids.numel(), CH, ptr(means), ptr(quats), ptr(scales), ptr(colors),
+         ptr(opacities), ptr(bg), ptr(masks), W, H, int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model), ptr(radial_coeffs),
          ptr(tile_offsets), ptr(flatten_ids), ptr(renders), ptr(alphas), ptr(last_ids), ptr(ws), ws.numel(), _stream())
     return renders, alphas, last_ids
 
@@ -201,16 +213,18 @@ def rasterize_to_pixels_from_world_3dgs_bwd(means, quats, scales, colors, opacit
         _check_input(t, n)
     _check_input(last_ids, "last_ids", torch.int32)
     _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
-    if masks is not None:
-        raise RuntimeError("tile masks are not supported")
+    CH = int(colors.shape[-1])
+    if CH not in (1, 3, 4):
+        raise RuntimeError(f"Unsupported number of channels: {CH}")
+    masks = _tile_masks(masks, image_width, image_height, tile_size)
     _one_camera(viewmats0, Ks, tile_offsets, opacities)
     N, dev = means.shape[0], means.device
     v_means, v_quats, v_scales = torch.empty_like(means), torch.empty_like(quats), torch.empty_like(scales)
     v_colors, v_opacities = torch.empty_like(colors), torch.empty_like(opacities)
     bg = backgrounds if (backgrounds is not None and backgrounds.numel() > 0) else None
     ws = _ws(capi.lib().lfs_rasterize_workspace_bytes(N), dev)
-    call("lfs_rasterize_to_pixels_from_world_3dgs_bwd", N, flatten_ids.numel(), ptr(means), ptr(quats), ptr(scales), ptr(colors),
-         ptr(opacities), ptr(bg), int(image_width), int(image_height), int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model),
+    call("lfs_rasterize_to_pixels_from_world_3dgs_bwd", N, flatten_ids.numel(), CH, ptr(means), ptr(quats), ptr(scales), ptr(colors),
+         ptr(opacities), ptr(bg), ptr(masks), int(image_width), int(image_height), int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model),
          ptr(radial_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(render_alphas), ptr(last_ids), ptr(v_render_colors),
          ptr(v_render_alphas), ptr(v_means), ptr(v_quats), ptr(v_scales), ptr(v_colors), ptr(v_opacities), ptr(ws), ws.numel(),
          _stream())
@@ -256,28 +270,35 @@ def rasterize_from_world_with_sh_fwd(means, quats, scales, opacities, sh_coeffs,
                                      far_plane, radius_clip, scaling_modifier, calc_compensations, render_mode,
                                      ut_params=None, rs_type=ShutterType.GLOBAL, radial_coeffs=None, tangential_coeffs=None,
                                      thin_prism_coeffs=None):
-    if render_mode != 0:
-        raise RuntimeError("only render_mode 0 (RGB) is supported")
-    if calc_compensations:
-        raise RuntimeError("calc_compensations is not supported")
+    if render_mode not in (0, 1, 2, 3, 4):
+        raise RuntimeError("render_mode must be 0=RGB, 1=D, 2=ED, 3=RGB_D or 4=RGB_ED")
     if opacities.dim() == 2:
         opacities = opacities.squeeze(-1)
     Cn = viewmats0.shape[0]
     scaled = scales * scaling_modifier if scaling_modifier != 1.0 else scales
     radii, means2d, depths, conics, comps = projection_ut_3dgs_fused(
         means, quats, scaled, opacities, viewmats0, viewmats1, Ks, image_width, image_height, eps2d, near_plane, far_plane,
-        radius_clip, False, camera_model, ut_params, rs_type, radial_coeffs, tangential_coeffs, thin_prism_coeffs)
+        radius_clip, bool(calc_compensations), camera_model, ut_params, rs_type, radial_coeffs, tangential_coeffs, thin_prism_coeffs)
     Rm, t = viewmats0[:, :3, :3], viewmats0[:, :3, 3]
     campos = -(Rm.double().transpose(1, 2) @ t.double().unsqueeze(-1)).squeeze(-1).float()  # inverse(viewmat)[:3, 3]
     dirs = (means.unsqueeze(0) - campos.unsqueeze(1)).contiguous()
     radii_masks = (radii > 0).all(-1)
-    rgb = spherical_harmonics_fwd(sh_degree, dirs, sh_coeffs.unsqueeze(0).expand(Cn, -1, -1, -1).contiguous(), radii_masks)
-    colors = torch.clamp_min(rgb + 0.5, 0.0)
+    if render_mode in (0, 3, 4):
+        rgb = spherical_harmonics_fwd(sh_degree, dirs, sh_coeffs.unsqueeze(0).expand(Cn, -1, -1, -1).contiguous(), radii_masks)
+        colors = torch.clamp_min(rgb + 0.5, 0.0)
+        if render_mode != 0:
+            colors = torch.cat([colors, depths.unsqueeze(-1)], -1)
+    else:
+        colors = depths.unsqueeze(-1)
+    colors = colors.contiguous()
+    final_opacities = opacities.unsqueeze(0)
+    if calc_compensations and comps is not None and comps.numel() > 0:
+        final_opacities = final_opacities * comps
     tw, th = (image_width + tile_size - 1) // tile_size, (image_height + tile_size - 1) // tile_size
     tiles_per_gauss, isect_ids, flatten_ids = intersect_tile(means2d, radii, depths, None, None, Cn, tile_size, tw, th, True)
     offsets = intersect_offset(isect_ids, Cn, tw, th)
     renders, alphas, last_ids = rasterize_to_pixels_from_world_3dgs_fwd(
-        means, quats, scaled, colors, opacities.unsqueeze(0), backgrounds, masks, image_width, image_height, tile_size,
+        means, quats, scaled, colors, final_opacities.contiguous(), backgrounds, masks, image_width, image_height, tile_size,
         viewmats0, viewmats1, Ks, camera_model, ut_params, rs_type, radial_coeffs, tangential_coeffs, thin_prism_coeffs,
         offsets, flatten_ids)
     return renders, alphas, radii, means2d, depths, colors, offsets, flatten_ids, last_ids, comps
@@ -289,23 +310,29 @@ def rasterize_from_world_with_sh_bwd(means, quats, scales, opacities, sh_coeffs,
                                      rs_type, radial_coeffs, tangential_coeffs, thin_prism_coeffs, render_alphas, last_ids,
                                      tile_offsets, flatten_ids, colors, radii, means2d, depths, compensations,
                                      v_render_colors, v_render_alphas):
-    if render_mode != 0:
-        raise RuntimeError("only render_mode 0 (RGB) is supported")
     if opacities.dim() == 2:
         opacities = opacities.squeeze(-1)
     Cn = viewmats0.shape[0]
     scaled = scales * scaling_modifier if scaling_modifier != 1.0 else scales
+    final_opacities = opacities.unsqueeze(0)
+    if calc_compensations and compensations is not None and compensations.numel() > 0:
+        final_opacities = final_opacities * compensations
     v_means, v_quats, v_scales, v_colors, v_opac = rasterize_to_pixels_from_world_3dgs_bwd(
-        means, quats, scaled, colors, opacities.unsqueeze(0), backgrounds, masks, image_width, image_height, tile_size,
+        means, quats, scaled, colors, final_opacities.contiguous(), backgrounds, masks, image_width, image_height, tile_size,
         viewmats0, viewmats1, Ks, camera_model, ut_params, rs_type, radial_coeffs, tangential_coeffs, thin_prism_coeffs,
         tile_offsets, flatten_ids, render_alphas, last_ids, v_render_colors, v_render_alphas)
     Rm, t = viewmats0[:, :3, :3], viewmats0[:, :3, 3]
     campos = -(Rm.double().transpose(1, 2) @ t.double().unsqueeze(-1)).squeeze(-1).float()
     dirs = (means.unsqueeze(0) - campos.unsqueeze(1)).contiguous()
     radii_masks = (radii > 0).all(-1)
-    v_pre = v_colors.clone()
-    v_pre.masked_fill_(colors <= 0.0, 0.0)
     K = sh_coeffs.shape[1]
-    v_sh, _ = spherical_harmonics_bwd(K, sh_degree, dirs.reshape(-1, 3), None, radii_masks.reshape(-1), v_pre.reshape(-1, 3), False)
-    v_sh = v_sh.reshape(Cn, -1, K, 3).sum(0)
+    if render_mode in (0, 3, 4):
+        # the depth channel's per-Gaussian gradient is dropped (gsplat/Rasterization.cpp:575-590)
+        v_pre = v_colors[..., :3].clone()
+        v_pre.masked_fill_(colors[..., :3] <= 0.0, 0.0)
+        v_sh, _ = spherical_harmonics_bwd(K, sh_degree, dirs.reshape(-1, 3), None, radii_masks.reshape(-1),
+                                          v_pre.reshape(-1, 3).contiguous(), False)
+        v_sh = v_sh.reshape(Cn, -1, K, 3).sum(0)
+    else:
+        v_sh = torch.zeros_like(sh_coeffs)
     return v_means, v_quats, v_scales * scaling_modifier, v_opac.squeeze(0), v_sh

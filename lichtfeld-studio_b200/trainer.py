@@ -94,11 +94,16 @@ class Camera:
 @dataclass
 class RenderOutput:
     """src/training/rasterization/rasterizer.hpp RenderOutput (fields the trainer uses)."""
-    image: torch.Tensor   # [H,W,3] unclamped render; the clamp / permute is folded into the loss kernel
+    image: torch.Tensor   # [H,W,3] unclamped render; the clamp / permute is folded into the loss kernel (None in D / ED)
     alpha: torch.Tensor   # [H,W,1]
     width: int
     height: int
     status: torch.Tensor  # int32[4] on device: overflow flag, n_isects, n_visible
+    depth: torch.Tensor | None = None   # [H,W,1] accumulated (D, RGB_D) or expected (ED, RGB_ED) depth
+    render: torch.Tensor | None = None  # [H,W,channels] as the kernel wrote it; v_render of backward() has this shape
+
+
+RENDER_RGB, RENDER_D, RENDER_ED, RENDER_RGB_D, RENDER_RGB_ED = 0, 1, 2, 3, 4  # RenderMode, rasterizer.hpp
 
 
 class Rasterizer:
@@ -106,15 +111,19 @@ class Rasterizer:
     workspace that carries the forward state to the backward."""
 
     def __init__(self, model: SplatData, width: int, height: int, sh_degree: int, camera_model=capi.PINHOLE,
-                 isect_capacity: int | None = None, eps2d=0.3, near_plane=0.01, far_plane=10000.0, radius_clip=0.0):
+                 isect_capacity: int | None = None, eps2d=0.3, near_plane=0.01, far_plane=10000.0, radius_clip=0.0,
+                 render_mode: int = RENDER_RGB, antialiased: bool = False, scaling_modifier: float = 1.0):
         self.model = model
         self.W, self.H = int(width), int(height)
         cap = int(isect_capacity) if isect_capacity is not None else max(8 * model.capacity, 1 << 20)
         self.cfg = RenderConfig(model.size, model.K, int(sh_degree), self.W, self.H, 16, int(camera_model),
-                                eps2d, near_plane, far_plane, radius_clip, UTParams(), cap)
+                                eps2d, near_plane, far_plane, radius_clip, UTParams(), cap, int(render_mode),
+                                1 if antialiased else 0, float(scaling_modifier), None)
+        self.channels = {RENDER_RGB: 3, RENDER_D: 1, RENDER_ED: 1, RENDER_RGB_D: 4, RENDER_RGB_ED: 4}[int(render_mode)]
+        self._masks = None
         self._alloc()
         dev = model.device
-        self.render = torch.empty((self.H, self.W, 3), dtype=torch.float32, device=dev)
+        self.render = torch.empty((self.H, self.W, self.channels), dtype=torch.float32, device=dev)
         self.alpha = torch.empty((self.H, self.W, 1), dtype=torch.float32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
 
@@ -129,6 +138,18 @@ class Rasterizer:
     def set_sh_degree(self, d: int):
         self.cfg.sh_degree = int(d)
 
+    def set_tile_masks(self, masks: torch.Tensor | None):
+        """[tile_h, tile_w] bool on the device, or None: tiles labelled False show the background and get no gradient
+        (the `masks` argument of gsplat/Ops.h:97-160)."""
+        if masks is None:
+            self._masks, self.cfg.tile_masks = None, None
+            return
+        tw, th = (self.W + 15) // 16, (self.H + 15) // 16
+        if masks.numel() != tw * th or masks.dtype != torch.bool or masks.device != self.render.device:
+            raise RuntimeError(f"tile masks must be a bool tensor [{th}, {tw}] on {self.model.device}")
+        self._masks = masks.contiguous().view(torch.uint8)
+        self.cfg.tile_masks = self._masks.data_ptr()
+
     def forward(self, cam: Camera, background: torch.Tensor | None) -> RenderOutput:
         if cam.width != self.W or cam.height != self.H:
             raise RuntimeError("camera size does not match the rasterizer")
@@ -137,7 +158,9 @@ class Rasterizer:
         p = self.model.struct()
         call("lfs_render_forward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), ptr(cam.radial),
              ptr(background), ptr(self.render), ptr(self.alpha), ptr(self.status), ptr(self.ws), self.ws.numel(), _stream())
-        return RenderOutput(self.render, self.alpha, self.W, self.H, self.status)
+        image = self.render if self.channels == 3 else (self.render[..., :3].contiguous() if self.channels == 4 else None)
+        depth = None if self.channels == 3 else self.render[..., self.channels - 1:]
+        return RenderOutput(image, self.alpha, self.W, self.H, self.status, depth, self.render)
 
     def backward(self, v_render: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
                  v_alpha: torch.Tensor | None = None, accumulate: bool = False):

@@ -677,13 +677,17 @@ static inline float safe_rsqrt_norm(V3 v, V3& out) {  // Utils.cuh:181-184
     return l;
 }
 
-int64_t orc_rasterize_fwd(
-    int N, int64_t n_isects,
-    const float* means, const float* quats, const float* scales, const float* colors, const float* opacities,
-    const float* background /*nullable [3]*/,
+// CH colour channels (1..4; the reference instantiates 1, 3, 4 for the render modes D, RGB, RGB_D of
+// gsplat/Rasterization.cpp:373-393) and optional per-tile masks (RasterizeToPixelsFromWorld3DGSFwd.cu:147-155:
+// a tile labelled false gets the background colour; alpha and last_ids, which the reference leaves
+// unwritten there, are written as 0).
+int64_t orc_rasterize_fwd_ch(
+    int N, int64_t n_isects, int CH,
+    const float* means, const float* quats, const float* scales, const float* colors /*[N,CH]*/, const float* opacities,
+    const float* background /*nullable [CH]*/, const uint8_t* masks /*nullable [th*tw]*/,
     int W, int H, int tile_size, const float* viewmat, const float* K, int camera_model, const float* radial,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
-    float* render_colors /*[H,W,3]*/, float* render_alphas /*[H,W]*/, int32_t* last_ids /*[H,W]*/,
+    float* render_colors /*[H,W,CH]*/, float* render_alphas /*[H,W]*/, int32_t* last_ids /*[H,W]*/,
     int tile_lo, int tile_hi /* only tiles in [tile_lo, tile_hi) are rendered; pass 0, -1 for all */) {
     const int tw = (W + tile_size - 1) / tile_size, th = (H + tile_size - 1) / tile_size;
     const Pose pose = pose_from_viewmat(viewmat);
@@ -697,6 +701,18 @@ int64_t orc_rasterize_fwd(
         const int32_t range_end = (tile == tw * th - 1) ? (int32_t)n_isects : tile_offsets[tile + 1];
         // per-entry precompute shared by the tile's pixels (the reference does it per batch)
         const int cnt = range_end - range_start;
+        if (masks && !masks[tile]) {
+            for (int ly = 0; ly < tile_size; ++ly)
+                for (int lx = 0; lx < tile_size; ++lx) {
+                    const int i = ty * tile_size + ly, j = tx * tile_size + lx;
+                    if (i >= H || j >= W) continue;
+                    const int pid = i * W + j;
+                    for (int k = 0; k < CH; ++k) render_colors[pid * CH + k] = background ? background[k] : 0.0f;
+                    render_alphas[pid] = 0.0f;
+                    last_ids[pid] = 0;
+                }
+            continue;
+        }
         std::vector<M3> Ms(cnt > 0 ? cnt : 0);
         for (int t = 0; t < cnt; ++t) {
             const int g = flatten_ids[range_start + t];
@@ -713,7 +729,7 @@ int64_t orc_rasterize_fwd(
                 world_ray(pose, cam, (float)j + 0.5f, (float)i + 0.5f, ro, rd, rv);
                 float T = 1.0f;
                 uint32_t cur_idx = 0;
-                float pix[3] = {0.f, 0.f, 0.f};
+                float pix[4] = {0.f, 0.f, 0.f, 0.f};
                 bool done = !rv;
                 for (int t = 0; t < cnt && !done; ++t) {
                     ++n_pairs;
@@ -729,18 +745,31 @@ int64_t orc_rasterize_fwd(
                     const float next_T = T * (1.0f - alpha);
                     if (next_T <= 1e-4f) { done = true; break; }
                     const float vis = alpha * T;
-                    for (int k = 0; k < 3; ++k) pix[k] += colors[g * 3 + k] * vis;
+                    for (int k = 0; k < CH; ++k) pix[k] += colors[g * CH + k] * vis;
                     cur_idx = (uint32_t)(range_start + t);
                     T = next_T;
                 }
                 const int pid = i * W + j;
                 render_alphas[pid] = 1.0f - T;
-                for (int k = 0; k < 3; ++k)
-                    render_colors[pid * 3 + k] = background ? (pix[k] + T * background[k]) : pix[k];
+                for (int k = 0; k < CH; ++k)
+                    render_colors[pid * CH + k] = background ? (pix[k] + T * background[k]) : pix[k];
                 last_ids[pid] = (int32_t)cur_idx;
             }
     }
     return n_pairs;
+}
+
+int64_t orc_rasterize_fwd(
+    int N, int64_t n_isects,
+    const float* means, const float* quats, const float* scales, const float* colors, const float* opacities,
+    const float* background /*nullable [3]*/,
+    int W, int H, int tile_size, const float* viewmat, const float* K, int camera_model, const float* radial,
+    const int32_t* tile_offsets, const int32_t* flatten_ids,
+    float* render_colors /*[H,W,3]*/, float* render_alphas /*[H,W]*/, int32_t* last_ids /*[H,W]*/,
+    int tile_lo, int tile_hi) {
+    return orc_rasterize_fwd_ch(N, n_isects, 3, means, quats, scales, colors, opacities, background, nullptr, W, H, tile_size,
+                                viewmat, K, camera_model, radial, tile_offsets, flatten_ids, render_colors, render_alphas,
+                                last_ids, tile_lo, tile_hi);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -749,10 +778,10 @@ int64_t orc_rasterize_fwd(
 // (tile by tile, pixel by pixel, back to front) so the result is run-to-run identical.
 // Outputs must be pre-zeroed. Returns the number of (pixel, entry) pairs walked.
 // ---------------------------------------------------------------------------------------------
-int64_t orc_rasterize_bwd(
-    int N, int64_t n_isects,
+int64_t orc_rasterize_bwd_ch(
+    int N, int64_t n_isects, int CH,
     const float* means, const float* quats, const float* scales, const float* colors, const float* opacities,
-    const float* background,
+    const float* background, const uint8_t* masks,
     int W, int H, int tile_size, const float* viewmat, const float* K, int camera_model, const float* radial,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
@@ -761,12 +790,12 @@ int64_t orc_rasterize_bwd(
     const int tw = (W + tile_size - 1) / tile_size, th = (H + tile_size - 1) / tile_size;
     const Pose pose = pose_from_viewmat(viewmat);
     const Camera cam = make_camera(camera_model, K, W, H, radial);
-    std::vector<double> acc((size_t)N * 14, 0.0);  // mean3 scale3 quat4 rgb3 opac1
+    std::vector<double> acc((size_t)N * 15, 0.0);  // mean3 scale3 quat4 colour4 opac1
     int64_t n_pairs = 0;
     // Tiles are processed sequentially for a fixed summation order; pixels inside a tile in parallel
     // into per-thread buffers would reorder sums, so parallelism is over tiles with a merge in tile order.
     const int n_tiles = tw * th;
-    std::vector<std::vector<std::pair<int, std::array<double, 14>>>> tile_out(n_tiles);
+    std::vector<std::vector<std::pair<int, std::array<double, 15>>>> tile_out(n_tiles);
     if (tile_hi < 0) tile_hi = n_tiles;
 #pragma omp parallel for schedule(dynamic, 1) reduction(+ : n_pairs)
     for (int tile = tile_lo; tile < tile_hi; ++tile) {
@@ -775,7 +804,8 @@ int64_t orc_rasterize_bwd(
         const int32_t range_end = (tile == n_tiles - 1) ? (int32_t)n_isects : tile_offsets[tile + 1];
         const int cnt = range_end - range_start;
         if (cnt <= 0) continue;
-        std::vector<std::array<double, 14>> loc(cnt);
+        if (masks && !masks[tile]) continue;  // ...Bwd.cu:84
+        std::vector<std::array<double, 15>> loc(cnt);
         for (auto& a : loc) a.fill(0.0);
         std::vector<char> touched(cnt, 0);
         for (int ly = 0; ly < tile_size; ++ly)
@@ -788,9 +818,10 @@ int64_t orc_rasterize_bwd(
                 const int pid = i * W + j;
                 const float T_final = 1.0f - render_alphas[pid];
                 float T = T_final;
-                float buffer[3] = {0.f, 0.f, 0.f};
+                float buffer[4] = {0.f, 0.f, 0.f, 0.f};
                 const int32_t bin_final = last_ids[pid];
-                const float vrc[3] = {v_render_colors[pid * 3], v_render_colors[pid * 3 + 1], v_render_colors[pid * 3 + 2]};
+                float vrc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int k = 0; k < CH; ++k) vrc[k] = v_render_colors[pid * CH + k];
                 const float vra = v_render_alphas[pid];
                 for (int idx = std::min(range_end - 1, bin_final); idx >= range_start; --idx) {
                     ++n_pairs;
@@ -818,14 +849,14 @@ int64_t orc_rasterize_bwd(
                     const float ra = 1.0f / (1.0f - alpha);
                     T *= ra;
                     const float fac = alpha * T;
-                    float v_rgb[3];
-                    for (int k = 0; k < 3; ++k) v_rgb[k] = fac * vrc[k];
+                    float v_rgb[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int k = 0; k < CH; ++k) v_rgb[k] = fac * vrc[k];
                     float v_alpha = 0.f;
-                    for (int k = 0; k < 3; ++k) v_alpha += (colors[g * 3 + k] * T - buffer[k] * ra) * vrc[k];
+                    for (int k = 0; k < CH; ++k) v_alpha += (colors[g * CH + k] * T - buffer[k] * ra) * vrc[k];
                     v_alpha += T_final * ra * vra;
                     if (background) {
                         float accum = 0.f;
-                        for (int k = 0; k < 3; ++k) accum += background[k] * vrc[k];
+                        for (int k = 0; k < CH; ++k) accum += background[k] * vrc[k];
                         v_alpha += -T_final * ra * accum;
                     }
                     V3 v_mean{0, 0, 0}, v_scale{0, 0, 0};
@@ -881,14 +912,14 @@ int64_t orc_rasterize_bwd(
                         v_scale.z = -is[2] * is[2] * (R.m[0][2] * vMt[2][0] + R.m[1][2] * vMt[2][1] + R.m[2][2] * vMt[2][2]);
                         v_opacity = vis * v_alpha;
                     }
-                    for (int k = 0; k < 3; ++k) buffer[k] += colors[g * 3 + k] * fac;
+                    for (int k = 0; k < CH; ++k) buffer[k] += colors[g * CH + k] * fac;
                     auto& a = loc[t];
                     touched[t] = 1;
                     a[0] += v_mean.x; a[1] += v_mean.y; a[2] += v_mean.z;
                     a[3] += v_scale.x; a[4] += v_scale.y; a[5] += v_scale.z;
                     a[6] += v_quat[0]; a[7] += v_quat[1]; a[8] += v_quat[2]; a[9] += v_quat[3];
-                    a[10] += v_rgb[0]; a[11] += v_rgb[1]; a[12] += v_rgb[2];
-                    a[13] += v_opacity;
+                    a[10] += v_rgb[0]; a[11] += v_rgb[1]; a[12] += v_rgb[2]; a[13] += v_rgb[3];
+                    a[14] += v_opacity;
                 }
             }
         auto& out = tile_out[tile];
@@ -897,16 +928,30 @@ int64_t orc_rasterize_bwd(
     }
     for (int tile = 0; tile < n_tiles; ++tile)
         for (auto& e : tile_out[tile])
-            for (int k = 0; k < 14; ++k) acc[(size_t)e.first * 14 + k] += e.second[k];
+            for (int k = 0; k < 15; ++k) acc[(size_t)e.first * 15 + k] += e.second[k];
     for (int g = 0; g < N; ++g) {
-        const double* a = &acc[(size_t)g * 14];
+        const double* a = &acc[(size_t)g * 15];
         for (int k = 0; k < 3; ++k) v_means[g * 3 + k] += (float)a[k];
         for (int k = 0; k < 3; ++k) v_scales[g * 3 + k] += (float)a[3 + k];
         for (int k = 0; k < 4; ++k) v_quats[g * 4 + k] += (float)a[6 + k];
-        for (int k = 0; k < 3; ++k) v_colors[g * 3 + k] += (float)a[10 + k];
-        v_opacities[g] += (float)a[13];
+        for (int k = 0; k < CH; ++k) v_colors[g * CH + k] += (float)a[10 + k];
+        v_opacities[g] += (float)a[14];
     }
     return n_pairs;
+}
+
+int64_t orc_rasterize_bwd(
+    int N, int64_t n_isects,
+    const float* means, const float* quats, const float* scales, const float* colors, const float* opacities,
+    const float* background,
+    int W, int H, int tile_size, const float* viewmat, const float* K, int camera_model, const float* radial,
+    const int32_t* tile_offsets, const int32_t* flatten_ids,
+    const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
+    float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities, int tile_lo, int tile_hi) {
+    return orc_rasterize_bwd_ch(N, n_isects, 3, means, quats, scales, colors, opacities, background, nullptr, W, H, tile_size,
+                                viewmat, K, camera_model, radial, tile_offsets, flatten_ids, render_alphas, last_ids,
+                                v_render_colors, v_render_alphas, v_means, v_quats, v_scales, v_colors, v_opacities, tile_lo,
+                                tile_hi);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -45,8 +45,8 @@ def lib():
     if _lib is None:
         _lib = C.CDLL(str(build()))
         _lib.orc_intersect_count.restype = C.c_int64
-        _lib.orc_rasterize_fwd.restype = C.c_int64
-        _lib.orc_rasterize_bwd.restype = C.c_int64
+        _lib.orc_rasterize_fwd_ch.restype = C.c_int64
+        _lib.orc_rasterize_bwd_ch.restype = C.c_int64
         _lib.orc_photometric_loss.restype = C.c_float
         _lib.orc_num_threads.restype = C.c_int
     return _lib
@@ -135,18 +135,20 @@ def intersect_offset(isect_ids, Cn, tw, th):
 
 
 def rasterize_fwd(means, quats, scales, colors, opacities, background, W, H, tile_size, viewmat, K,
-                  tile_offsets, flatten_ids, camera_model=PINHOLE, radial=None, tile_range=(0, -1)):
-    """One camera (the reference kernel supports C = 1 only). Returns render [H,W,3], alpha [H,W,1],
-    last_ids [H,W] and the number of (pixel, entry) pairs visited."""
+                  tile_offsets, flatten_ids, camera_model=PINHOLE, radial=None, tile_range=(0, -1), masks=None):
+    """One camera (the reference kernel supports C = 1 only). colors is [N, CH] with CH in 1..4.
+    Returns render [H,W,CH], alpha [H,W,1], last_ids [H,W] and the number of (pixel, entry) pairs visited."""
     a = [_f32(x) for x in (means, quats, scales, colors, opacities)]
+    CH = a[3].shape[-1] if a[3].ndim == 2 else 1
     bg = _f32(background)
-    render = np.zeros((H, W, 3), np.float32)
+    mk = None if masks is None else np.ascontiguousarray(masks, np.uint8)
+    render = np.zeros((H, W, CH), np.float32)
     alpha = np.zeros((H, W, 1), np.float32)
     last = np.zeros((H, W), np.int32)
     to = np.ascontiguousarray(tile_offsets, np.int32)
     fl = np.ascontiguousarray(flatten_ids, np.int32)
-    npairs = lib().orc_rasterize_fwd(
-        i32(a[0].shape[0]), i64(fl.size), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg),
+    npairs = lib().orc_rasterize_fwd_ch(
+        i32(a[0].shape[0]), i64(fl.size), i32(CH), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg), _p(mk),
         i32(W), i32(H), i32(tile_size), _p(_f32(viewmat)), _p(_f32(K)), i32(camera_model), _p(_f32(radial)),
         _p(to), _p(fl), _p(render), _p(alpha), _p(last), i32(tile_range[0]), i32(tile_range[1]))
     return render, alpha, last, int(npairs)
@@ -154,19 +156,21 @@ def rasterize_fwd(means, quats, scales, colors, opacities, background, W, H, til
 
 def rasterize_bwd(means, quats, scales, colors, opacities, background, W, H, tile_size, viewmat, K,
                   tile_offsets, flatten_ids, render_alphas, last_ids, v_render_colors, v_render_alphas,
-                  camera_model=PINHOLE, radial=None, tile_range=(0, -1)):
+                  camera_model=PINHOLE, radial=None, tile_range=(0, -1), masks=None):
     a = [_f32(x) for x in (means, quats, scales, colors, opacities)]
     N = a[0].shape[0]
+    CH = a[3].shape[-1] if a[3].ndim == 2 else 1
+    mk = None if masks is None else np.ascontiguousarray(masks, np.uint8)
     bg = _f32(background)
     to = np.ascontiguousarray(tile_offsets, np.int32)
     fl = np.ascontiguousarray(flatten_ids, np.int32)
     v_means = np.zeros((N, 3), np.float32)
     v_quats = np.zeros((N, 4), np.float32)
     v_scales = np.zeros((N, 3), np.float32)
-    v_colors = np.zeros((N, 3), np.float32)
+    v_colors = np.zeros((N, CH), np.float32)
     v_opac = np.zeros((N,), np.float32)
-    npairs = lib().orc_rasterize_bwd(
-        i32(N), i64(fl.size), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg),
+    npairs = lib().orc_rasterize_bwd_ch(
+        i32(N), i64(fl.size), i32(CH), _p(a[0]), _p(a[1]), _p(a[2]), _p(a[3]), _p(a[4]), _p(bg), _p(mk),
         i32(W), i32(H), i32(tile_size), _p(_f32(viewmat)), _p(_f32(K)), i32(camera_model), _p(_f32(radial)),
         _p(to), _p(fl), _p(_f32(render_alphas)), _p(np.ascontiguousarray(last_ids, np.int32)),
         _p(_f32(v_render_colors)), _p(_f32(v_render_alphas)),
@@ -271,52 +275,93 @@ def act_quat(raw):
 
 # ------------------------------------------------------------------ orchestration
 def render_fwd(params, viewmat, K, W, H, sh_degree, background=None, camera_model=PINHOLE, radial=None,
-               tile_size=16, eps2d=0.3, near=0.01, far=1e4, tile_range=(0, -1)):
-    """gsplat::rasterize_from_world_with_sh_fwd for one camera on raw SplatData parameters.
-    params: dict(means, sh0, shN, scaling_raw, rotation_raw, opacity_raw)."""
+               tile_size=16, eps2d=0.3, near=0.01, far=1e4, tile_range=(0, -1), render_mode=0,
+               calc_compensations=False, scaling_modifier=1.0, tile_masks=None):
+    """gsplat::rasterize_from_world_with_sh_fwd (gsplat/Rasterization.cpp:279-468) for one camera on raw SplatData
+    parameters, followed by the render-mode post-processing of rasterize()
+    (src/training/rasterization/rasterizer.cpp:171-198).
+    params: dict(means, sh0, shN, scaling_raw, rotation_raw, opacity_raw). render_mode: 0 RGB, 1 D, 2 ED, 3 RGB_D,
+    4 RGB_ED. background has as many entries as the render has channels."""
     means = _f32(params["means"])
     opac = act_opacity(params["opacity_raw"])
     scales = act_scale(params["scaling_raw"])
+    if scaling_modifier != 1.0:
+        scales = (scales * np.float32(scaling_modifier)).astype(np.float32)
     quats, qnorm = act_quat(params["rotation_raw"])
     sh = np.concatenate([params["sh0"], params["shN"]], axis=1).astype(np.float32)
     vm = _f32(viewmat).reshape(1, 4, 4)
     Kc = _f32(K).reshape(1, 3, 3)
     rc = None if radial is None else _f32(radial).reshape(1, 4)
-    radii, means2d, depths, conics, _ = projection_ut_3dgs_fused(
-        means, quats, scales, opac, vm, Kc, W, H, eps2d, near, far, 0.0, False, camera_model, UT_DEFAULT, rc)
+    radii, means2d, depths, conics, comps = projection_ut_3dgs_fused(
+        means, quats, scales, opac, vm, Kc, W, H, eps2d, near, far, 0.0, bool(calc_compensations), camera_model, UT_DEFAULT, rc)
     cp = campos(vm[0])
     dirs = (means - cp[None, :]).astype(np.float32)
     masks = (radii[0] > 0).all(-1)
-    rgb = spherical_harmonics_fwd(sh_degree, dirs, sh, masks)
-    colors = np.maximum(rgb + np.float32(0.5), np.float32(0.0)).astype(np.float32)
-    colors[~masks] = 0.0
+    if render_mode in (0, 3, 4):
+        rgb = spherical_harmonics_fwd(sh_degree, dirs, sh, masks)
+        colors = np.maximum(rgb + np.float32(0.5), np.float32(0.0)).astype(np.float32)
+        colors[~masks] = 0.0
+        if render_mode != 0:
+            colors = np.concatenate([colors, depths[0][:, None]], axis=1).astype(np.float32)
+    else:
+        colors = np.ascontiguousarray(depths[0][:, None], np.float32)
+    final_opac = (opac * comps[0]).astype(np.float32) if calc_compensations else opac
     tw, th = (W + tile_size - 1) // tile_size, (H + tile_size - 1) // tile_size
     tpg, ids, flat = intersect_tile(means2d, radii, depths, 1, tile_size, tw, th, True)
     offs = intersect_offset(ids, 1, tw, th)
-    render, alpha, last, npairs = rasterize_fwd(means, quats, scales, colors, opac, background, W, H, tile_size,
-                                                vm[0], Kc[0], offs[0], flat, camera_model, rc, tile_range)
-    return dict(render=render, alpha=alpha, last_ids=last, radii=radii[0], means2d=means2d[0], depths=depths[0],
-                colors=colors, tile_offsets=offs[0], flatten_ids=flat, isect_ids=ids, tiles_per_gauss=tpg[0],
-                masks=masks, dirs=dirs, opac=opac, scales=scales, quats=quats, qnorm=qnorm, sh=sh,
-                n_pairs_fwd=npairs, conics=conics[0])
+    render, alpha, last, npairs = rasterize_fwd(means, quats, scales, colors, final_opac, background, W, H, tile_size,
+                                                vm[0], Kc[0], offs[0], flat, camera_model, rc, tile_range, tile_masks)
+    out = dict(render=render, alpha=alpha, last_ids=last, radii=radii[0], means2d=means2d[0], depths=depths[0],
+               colors=colors, tile_offsets=offs[0], flatten_ids=flat, isect_ids=ids, tiles_per_gauss=tpg[0],
+               masks=masks, dirs=dirs, opac=opac, final_opac=final_opac, scales=scales, quats=quats, qnorm=qnorm, sh=sh,
+               n_pairs_fwd=npairs, conics=conics[0], render_mode=render_mode, tile_masks=tile_masks)
+    if render_mode != 0:
+        acc = render[..., -1:]
+        if render_mode in (2, 4):
+            depth = (acc / np.maximum(alpha, np.float32(1e-10))).astype(np.float32)
+            if tile_masks is not None:
+                # masked tiles: the reference divides by an alpha it never wrote there; defined here as "no division"
+                off = np.kron(~np.asarray(tile_masks, bool), np.ones((tile_size, tile_size), bool))[:H, :W]
+                depth[off] = acc[off]
+            out["depth"] = depth
+        else:
+            out["depth"] = acc
+        out["image"] = render[..., :3] if render_mode in (3, 4) else None
+    else:
+        out["image"], out["depth"] = render, None
+    return out
 
 
 def render_bwd(params, fwd, viewmat, K, W, H, sh_degree, v_render, v_alpha=None, background=None,
                camera_model=PINHOLE, radial=None, tile_size=16, tile_range=(0, -1)):
-    """gsplat::rasterize_from_world_with_sh_bwd followed by the activation backward; returns
-    gradients w.r.t. the six raw parameter tensors."""
+    """gsplat::rasterize_from_world_with_sh_bwd (gsplat/Rasterization.cpp:470-642) followed by the activation
+    backward; returns gradients w.r.t. the six raw parameter tensors. v_render has the channels of fwd["render"]; in
+    the expected-depth modes its last channel is the gradient of the DIVIDED depth and the chain rule of
+    depth = sum / clamp_min(alpha, 1e-10) (rasterizer.cpp:186-198, as autograd would apply it) comes first."""
     means = _f32(params["means"])
-    if v_alpha is None:
-        v_alpha = np.zeros((H, W, 1), np.float32)
+    mode = fwd.get("render_mode", 0)
+    v_render = _f32(v_render).copy()
+    v_alpha = np.zeros((H, W, 1), np.float32) if v_alpha is None else _f32(v_alpha).copy()
+    if mode in (2, 4):
+        a = fwd["alpha"]
+        ac = np.maximum(a, np.float32(1e-10))
+        vd = v_render[..., -1:]
+        v_alpha = (v_alpha + np.where(a > 1e-10, -fwd["render"][..., -1:] / (ac * ac) * vd, 0.0)).astype(np.float32)
+        v_render[..., -1:] = vd / ac
     rc = None if radial is None else _f32(radial).reshape(1, 4)
     v_means, v_quats, v_scales, v_colors, v_opac, npairs = rasterize_bwd(
-        means, fwd["quats"], fwd["scales"], fwd["colors"], fwd["opac"], background, W, H, tile_size,
+        means, fwd["quats"], fwd["scales"], fwd["colors"], fwd["final_opac"], background, W, H, tile_size,
         viewmat, K, fwd["tile_offsets"], fwd["flatten_ids"], fwd["alpha"], fwd["last_ids"], v_render, v_alpha,
-        camera_model, rc, tile_range)
-    v_pre = v_colors.copy()
-    v_pre[fwd["colors"] <= 0.0] = 0.0
+        camera_model, rc, tile_range, fwd.get("tile_masks"))
     K_sh = fwd["sh"].shape[1]
-    v_sh = spherical_harmonics_bwd(K_sh, sh_degree, fwd["dirs"], fwd["masks"], v_pre)
+    if mode in (0, 3, 4):
+        v_pre = v_colors[:, :3].copy()
+        v_pre[fwd["colors"][:, :3] <= 0.0] = 0.0
+        v_sh = spherical_harmonics_bwd(K_sh, sh_degree, fwd["dirs"], fwd["masks"], v_pre)
+    else:
+        v_sh = np.zeros((means.shape[0], K_sh, 3), np.float32)
+    # the opacity gradient is taken w.r.t. the compensated opacity and passed on unchanged; v_scales is w.r.t.
+    # the modified scale = exp(raw) * modifier (Rasterization.cpp:626), whose derivative w.r.t. raw is itself
     o, s, q, nrm = fwd["opac"], fwd["scales"], fwd["quats"], fwd["qnorm"]
     g_opacity = (v_opac * (o * (np.float32(1.0) - o))).astype(np.float32).reshape(-1, 1)
     g_scaling = (v_scales * s).astype(np.float32)
