@@ -357,6 +357,20 @@ int lfs_mcmc_apply(int N, int sh_coeffs, int n_sampled, const int64_t* sampled, 
                    const lfs_splats* params, const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq,
                    void* stream);
 
+/* ---- PLY export / import rows -------------------------------------------------------------- */
+
+/* The vertex rows of SplatData::save_ply (src/core/splat_data.cpp:402-418 attribute names, :483-503
+ * SplatData::to_point_cloud contents), built on the device in one pass instead of transpose / flatten /
+ * normalize / .cpu() per tensor: rows [N, 14 + 3*sh_coeffs] float32 =
+ *   x y z | nx ny nz = 0 | f_dc_0..2 | f_rest_0.. (channel-major: all R, then G, then B) |
+ *   opacity (raw logit) | scale_0..2 (raw log) | rot_0..3 (normalised, q / max(|q|, 1e-12)).
+ * Copy the buffer to the host and write it after the header: it is the binary_little_endian body. */
+int lfs_ply_pack_rows(int N, int sh_coeffs, const lfs_splats* params, float* rows, void* stream);
+
+/* Inverse (the layout src/loader/formats/ply.cpp reads): scatters rows into the six tensors; the normals
+ * are ignored and the quaternion is stored as found. */
+int lfs_ply_unpack_rows(int N, int sh_coeffs, const float* rows, const lfs_splats* params, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -5,7 +5,7 @@ of the reference's operator and strategy interfaces.
 The directory name contains a hyphen, so import it with importlib:
     lfs = importlib.import_module("lichtfeld-studio_b200")
 """
-from . import _capi, dp, ops, strategy, synth, trainer  # noqa: F401
+from . import _capi, dp, formats, ops, strategy, synth, trainer  # noqa: F401
 from ._capi import LfsError, UTParams  # noqa: F401
 
-__all__ = ["ops", "trainer", "strategy", "synth", "LfsError", "UTParams"]
+__all__ = ["ops", "trainer", "strategy", "synth", "formats", "dp", "LfsError", "UTParams"]

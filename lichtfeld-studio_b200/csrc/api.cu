@@ -471,6 +471,25 @@ int lfs_quats_to_rotmats(int n, const float* quats, float* rotmats, void* stream
     return launch_quats_to_rotmats(n, quats, rotmats, S(stream));
 }
 
+int lfs_ply_pack_rows(int N, int sh_coeffs, const lfs_splats* params, float* rows, void* stream) {
+    LFS_REQUIRE(N >= 0 && sh_coeffs >= 1, "bad sizes");
+    if (N == 0) return LFS_OK;
+    LFS_REQUIRE(params && rows && params->means && params->sh0 && params->scaling_raw && params->rotation_raw && params->opacity_raw,
+                "null pointer");
+    LFS_REQUIRE(sh_coeffs == 1 || params->shN, "null shN");
+    LFS_REQUIRE(aligned16(params->rotation_raw), "rotation_raw must be 16-byte aligned");
+    return launch_ply_rows(N, sh_coeffs, *params, rows, 0, S(stream));
+}
+
+int lfs_ply_unpack_rows(int N, int sh_coeffs, const float* rows, const lfs_splats* params, void* stream) {
+    LFS_REQUIRE(N >= 0 && sh_coeffs >= 1, "bad sizes");
+    if (N == 0) return LFS_OK;
+    LFS_REQUIRE(params && rows && params->means && params->sh0 && params->scaling_raw && params->rotation_raw && params->opacity_raw,
+                "null pointer");
+    LFS_REQUIRE(sh_coeffs == 1 || params->shN, "null shN");
+    return launch_ply_rows(N, sh_coeffs, *params, const_cast<float*>(rows), 1, S(stream));
+}
+
 // ---------------------------------------------------------------------------------------------
 size_t lfs_render_workspace_bytes(const lfs_render_config* cfg) {
     if (check_cfg(cfg) != LFS_OK) return 0;

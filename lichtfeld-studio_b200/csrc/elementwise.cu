@@ -415,6 +415,66 @@ int launch_quats_to_rotmats(int n, const float* quats, float* rotmats, cudaStrea
     return check_launch("quats_to_rotmats");
 }
 
+// ---------------------------------------------------------------------------------------------
+// PLY vertex rows (src/core/splat_data.cpp:402-418 attribute order, :483-503 contents):
+//   x y z | nx ny nz (zeros) | f_dc_0..2 | f_rest_* channel-major (transpose(1,2).flatten(1)) |
+//   opacity (raw logit) | scale_0..2 (raw log) | rot_0..3 (F.normalize: q / max(|q|, 1e-12))
+// One warp per row: lanes stride over the row's 14 + 3 K floats, so both the reads of the six tensors
+// and the interleaved row writes are contiguous runs. Explicit _rn arithmetic: the norm does not
+// depend on the compiler's FMA contraction.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ply_rows_pack_kernel(int N, int K, lfs_splats p, float* __restrict__ rows) {
+    const int width = 14 + 3 * K, rest = K - 1;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < N; g += warps) {
+        float* row = rows + (size_t)g * width;
+        const float4 q = reinterpret_cast<const float4*>(p.rotation_raw)[g];
+        const float n2 = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(q.x, q.x), __fmul_rn(q.y, q.y)), __fmul_rn(q.z, q.z)), __fmul_rn(q.w, q.w));
+        const float nrm = fmaxf(__fsqrt_rn(n2), 1e-12f);
+        for (int c = lane; c < width; c += 32) {
+            float v;
+            if (c < 3) v = p.means[g * 3 + c];
+            else if (c < 6) v = 0.f;
+            else if (c < 9) v = p.sh0[g * 3 + (c - 6)];
+            else if (c < 9 + 3 * rest) { const int i = c - 9, ch = i / rest, k = i % rest; v = p.shN[((size_t)g * rest + k) * 3 + ch]; }
+            else if (c == 9 + 3 * rest) v = p.opacity_raw[g];
+            else if (c < 13 + 3 * rest) v = p.scaling_raw[g * 3 + (c - 10 - 3 * rest)];
+            else { const int k = c - 13 - 3 * rest; v = __fdiv_rn(k == 0 ? q.x : k == 1 ? q.y : k == 2 ? q.z : q.w, nrm); }
+            row[c] = v;
+        }
+    }
+}
+
+// Inverse of ply_rows_pack_kernel (normals are ignored; the quaternion is stored as it is in the file).
+__global__ void __launch_bounds__(256) ply_rows_unpack_kernel(int N, int K, const float* __restrict__ rows, lfs_splats p) {
+    const int width = 14 + 3 * K, rest = K - 1;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < N; g += warps) {
+        const float* row = rows + (size_t)g * width;
+        for (int c = lane; c < width; c += 32) {
+            const float v = row[c];
+            if (c < 3) p.means[g * 3 + c] = v;
+            else if (c < 6) {}
+            else if (c < 9) p.sh0[g * 3 + (c - 6)] = v;
+            else if (c < 9 + 3 * rest) { const int i = c - 9, ch = i / rest, k = i % rest; p.shN[((size_t)g * rest + k) * 3 + ch] = v; }
+            else if (c == 9 + 3 * rest) p.opacity_raw[g] = v;
+            else if (c < 13 + 3 * rest) p.scaling_raw[g * 3 + (c - 10 - 3 * rest)] = v;
+            else p.rotation_raw[g * 4 + (c - 13 - 3 * rest)] = v;
+        }
+    }
+}
+
+int launch_ply_rows(int N, int K, const lfs_splats& p, float* rows, int unpack, cudaStream_t st) {
+    if (N == 0) return LFS_OK;
+    LFS_TIMED(unpack ? "ply_rows_unpack" : "ply_rows_pack", st);
+    const int grid = (int)min((int64_t)148 * 8, ((int64_t)N * 32 + 255) / 256);
+    if (unpack) ply_rows_unpack_kernel<<<grid, 256, 0, st>>>(N, K, rows, p);
+    else ply_rows_pack_kernel<<<grid, 256, 0, st>>>(N, K, p, rows);
+    return check_launch("ply_rows");
+}
+
 int launch_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity, int64_t* dead_indices,
                          int64_t* alive_indices, float* alive_opacities, int32_t* counts_dev, int32_t* flags, int32_t* offs,
                          int32_t* total_dev, const SortScratch& s, cudaStream_t st) {

@@ -53,6 +53,7 @@ int launch_relocation(int n, const float* opacities, const float* scales, const 
 int launch_add_noise(int n, const float* raw_opacities, const float* raw_scales, const float* raw_quats, const float* noise,
                      float* means, float lr, cudaStream_t st);
 int launch_quats_to_rotmats(int n, const float* quats, float* rotmats, cudaStream_t st);
+int launch_ply_rows(int N, int K, const lfs_splats& p, float* rows, int unpack, cudaStream_t st);
 int launch_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity, int64_t* dead_indices,
                          int64_t* alive_indices, float* alive_opacities, int32_t* counts_dev, int32_t* flags, int32_t* offs,
                          int32_t* total_dev, const SortScratch& s, cudaStream_t st);

@@ -264,3 +264,52 @@ def test_default_strategy_adc_on_cpu_tensors(pkg):
     assert sd.size == 8
     s.post_backward(25000)
     assert s.densification_info.numel() == 0
+
+
+def test_ply_header_reader_and_checkpoint_roundtrip(pkg, tmp_path):
+    """Header text of SplatData::save_ply (src/core/splat_data.cpp:113-169, :402-418), the reader on a file made with
+    numpy in a shuffled property order, and the checkpoint format on CPU tensors."""
+    import torch
+    fm, tr, st = pkg.formats, pkg.trainer, pkg.strategy
+    K = 4
+    names = fm.ply_attribute_names(K)
+    assert names[:9] == ["x", "y", "z", "nx", "ny", "nz", "f_dc_0", "f_dc_1", "f_dc_2"]
+    assert names[9] == "f_rest_0" and names[17] == "f_rest_8" and names[18:] == ["opacity", "scale_0", "scale_1", "scale_2", "rot_0", "rot_1", "rot_2", "rot_3"]
+    assert len(names) == 14 + 3 * K
+    hdr = fm.ply_header(5, K).decode()
+    assert hdr.startswith("ply\nformat binary_little_endian 1.0\nelement vertex 5\nproperty float x\n") and hdr.endswith("end_header\n")
+    rng = np.random.default_rng(0)
+    rows = rng.normal(size=(5, len(names))).astype(np.float32)
+    p = tmp_path / "a.ply"
+    p.write_bytes(fm.ply_header(5, K) + rows.tobytes())
+    n2, r2 = fm.read_ply(str(p))
+    assert n2 == names and np.array_equal(r2, rows)
+    with pytest.raises(RuntimeError):
+        (tmp_path / "bad.ply").write_bytes(b"plx\n")
+        fm.read_ply(str(tmp_path / "bad.ply"))
+
+    # checkpoint: parameters, moments, optimizer counters; restoring into a fresh strategy reproduces every buffer
+    def fresh(seed):
+        sd = tr.SplatData(9, K, "cpu", capacity=16)
+        g = torch.Generator().manual_seed(seed)
+        for name in tr.PARAM_NAMES:
+            sd.tensor(name).copy_(torch.randn(sd.tensor(name).shape, generator=g))
+        s = st.DefaultStrategy(sd)
+        s.initialize(st.DefaultStrategy.Parameters(sh_degree=1))
+        return s
+    a = fresh(1)
+    a._optimizer.exp_avg.flat.normal_(generator=torch.Generator().manual_seed(5))
+    a._optimizer.exp_avg_sq.flat.uniform_(generator=torch.Generator().manual_seed(6))
+    a._optimizer.step_count, a._optimizer.lr[0], a.active_sh_degree = 1234, 1.23e-4, 1
+    path = fm.save_checkpoint(a, str(tmp_path / "c.ckpt"), 777)
+    b = fresh(2)
+    b.get_model().size = 3   # a different size before the restore
+    assert fm.load_checkpoint(b, path) == 777
+    assert b.get_model().size == 9 and b._optimizer.step_count == 1234 and b._optimizer.lr == a._optimizer.lr and b.active_sh_degree == 1
+    for x, y in ((a.get_model(), b.get_model()), (a._optimizer.exp_avg, b._optimizer.exp_avg), (a._optimizer.exp_avg_sq, b._optimizer.exp_avg_sq)):
+        for name in tr.PARAM_NAMES:
+            assert torch.equal(x.tensor(name), y.tensor(name)), name
+    small = tr.SplatData(2, K, "cpu", capacity=4)
+    s2 = st.DefaultStrategy(small); s2.initialize(st.DefaultStrategy.Parameters(sh_degree=1))
+    with pytest.raises(RuntimeError):
+        fm.load_checkpoint(s2, path)
