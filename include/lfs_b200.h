@@ -65,15 +65,17 @@ int lfs_profile_collect(int max_records, const char** names, float* ms);
 /* ------------------------------------------------------------------------------------------ */
 
 /* gsplat/Ops.h:67-95 projection_ut_3dgs_fused -> gsplat/ProjectionUT3DGSFused.cu:17.
- * Global shutter; camera_model PINHOLE (no distortion) or FISHEYE (radial_coeffs [C,4] or NULL).
+ * Global shutter. camera_model FISHEYE: radial_coeffs [C,4] or NULL. camera_model PINHOLE: radial_coeffs [C,6],
+ * tangential_coeffs [C,2], thin_prism_coeffs [C,4], each or NULL; all NULL is the distortion-free pinhole, any
+ * present selects the OpenCV pinhole model (gsplat/ProjectionUT3DGSFused.cu:91-113, gsplat/Cameras.cuh:474-755).
  * opacities and compensations may be NULL. Outputs of culled Gaussians other than radii = 0 are
  * left untouched, like the reference. */
 int lfs_projection_ut_3dgs_fused(
     int C, int N, const float* means, const float* quats, const float* scales, const float* opacities,
     const float* viewmats0, const float* Ks, int image_width, int image_height,
     float eps2d, float near_plane, float far_plane, float radius_clip,
-    int camera_model, lfs_ut_params ut_params, const float* radial_coeffs,
-    int32_t* radii, float* means2d, float* depths, float* conics, float* compensations, void* stream);
+    int camera_model, lfs_ut_params ut_params, const float* radial_coeffs, const float* tangential_coeffs,
+    const float* thin_prism_coeffs, int32_t* radii, float* means2d, float* depths, float* conics, float* compensations, void* stream);
 
 /* gsplat/Ops.h:12-17 spherical_harmonics_fwd -> gsplat/SphericalHarmonicsCUDA.cu:374.
  * n elements, coeffs [n,K,3], masks (uint8, NULL = all), colors [n,3]. */
@@ -118,7 +120,8 @@ size_t lfs_rasterize_workspace_bytes(int N);
 int lfs_rasterize_to_pixels_from_world_3dgs_fwd(
     int N, int64_t n_isects, int channels, const float* means, const float* quats, const float* scales, const float* colors,
     const float* opacities, const float* backgrounds, const uint8_t* masks, int image_width, int image_height, int tile_size,
-    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs,
+    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs, const float* tangential_coeffs,
+    const float* thin_prism_coeffs,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     float* renders, float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes, void* stream);
 
@@ -128,7 +131,8 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(
 int lfs_rasterize_to_pixels_from_world_3dgs_bwd(
     int N, int64_t n_isects, int channels, const float* means, const float* quats, const float* scales, const float* colors,
     const float* opacities, const float* backgrounds, const uint8_t* masks, int image_width, int image_height, int tile_size,
-    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs,
+    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs, const float* tangential_coeffs,
+    const float* thin_prism_coeffs,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
     float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
@@ -197,6 +201,12 @@ typedef struct lfs_render_config {
     int calc_compensations; /* `antialiased`: blended opacity = opacity * compensation (gsplat/Rasterization.cpp:396-399) */
     float scaling_modifier; /* scales are multiplied by it; 0 means 1.0 */
     const uint8_t* tile_masks; /* device [tile_h*tile_w] bytes or NULL (gsplat/Ops.h `masks`) */
+    /* Lens distortion of this camera, device pointers or NULL. LFS_FISHEYE: radial_coeffs [4].
+     * LFS_PINHOLE: radial_coeffs [6] (k1..k6), tangential_coeffs [2], thin_prism_coeffs [4]; any of the three
+     * being non-NULL selects the OpenCV pinhole model (gsplat/ProjectionUT3DGSFused.cu:91-113). */
+    const float* radial_coeffs;
+    const float* tangential_coeffs;
+    const float* thin_prism_coeffs;
 } lfs_render_config;
 
 size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);
@@ -204,7 +214,7 @@ size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);
 /* Forward of FusedRasterizationWithSHFunction (src/training/rasterization/rasterizer_autograd.cpp:11)
  * = gsplat::rasterize_from_world_with_sh_fwd (gsplat/Rasterization.cpp:279) including the SplatData
  * activations (src/core/splat_data.cpp:267-286), for one camera. viewmat [4,4], K [3,3],
- * radial_coeffs [4] or NULL, background [channels] or NULL are device pointers.
+ * background [channels] or NULL are device pointers; the distortion coefficients are in cfg.
  * Outputs: render [H,W,channels] (unclamped; channels by render_mode: colour first, depth last; in the two
  * expected-depth modes the depth channel is already divided by max(alpha, 1e-10)), alpha [H,W,1].
  * The depth channel's background is background[channels-1]; the reference passes its 3-float colour
@@ -212,7 +222,7 @@ size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);
  * callers that want the same pictures pass {r} resp. {r,g,b,0}. Everything the backward needs stays in the
  * workspace. status_dev (device int32[4]): [0] overflow flag, [1] n_isects, [2] n_visible. */
 int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat,
-                       const float* K, const float* radial_coeffs, const float* background,
+                       const float* K, const float* background,
                        float* render, float* alpha, int32_t* status_dev,
                        void* workspace, size_t workspace_bytes, void* stream);
 

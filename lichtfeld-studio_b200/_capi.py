@@ -31,7 +31,8 @@ class RenderConfig(C.Structure):
                 ("image_height", C.c_int), ("tile_size", C.c_int), ("camera_model", C.c_int),
                 ("eps2d", C.c_float), ("near_plane", C.c_float), ("far_plane", C.c_float), ("radius_clip", C.c_float),
                 ("ut", UTParams), ("isect_capacity", C.c_int64), ("render_mode", C.c_int), ("calc_compensations", C.c_int),
-                ("scaling_modifier", C.c_float), ("tile_masks", C.c_void_p)]
+                ("scaling_modifier", C.c_float), ("tile_masks", C.c_void_p), ("radial_coeffs", C.c_void_p),
+                ("tangential_coeffs", C.c_void_p), ("thin_prism_coeffs", C.c_void_p)]
 
 
 class RenderView(C.Structure):
@@ -56,16 +57,16 @@ _lib = None
 vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 _SIGNATURES = {
-    "lfs_projection_ut_3dgs_fused": [i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, i32, UTParams, vp,
+    "lfs_projection_ut_3dgs_fused": [i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, i32, UTParams, vp, vp, vp,
                                      vp, vp, vp, vp, vp, vp],
     "lfs_spherical_harmonics_fwd": [i32, i32, i32, vp, vp, vp, vp, vp],
     "lfs_spherical_harmonics_bwd": [i32, i32, i32, vp, vp, vp, vp, vp],
     "lfs_intersect_tile_count": [i32, i32, vp, vp, i32, i32, i32, vp, vp, vp],
     "lfs_intersect_tile_emit": [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, sz, vp],
     "lfs_intersect_offset": [i64, vp, i32, i32, i32, vp, vp],
-    "lfs_rasterize_to_pixels_from_world_3dgs_fwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp,
+    "lfs_rasterize_to_pixels_from_world_3dgs_fwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, vp, vp,
                                                     vp, vp, vp, vp, vp, vp, sz, vp],
-    "lfs_rasterize_to_pixels_from_world_3dgs_bwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp,
+    "lfs_rasterize_to_pixels_from_world_3dgs_bwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, vp, vp,
                                                     vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
     "lfs_fusedssim": [i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp],
     "lfs_fusedssim_backward": [i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp],
@@ -75,7 +76,7 @@ _SIGNATURES = {
     "lfs_quats_to_rotmats": [i32, vp, vp, vp],
     "lfs_ply_pack_rows": [i32, i32, C.POINTER(Splats), vp, vp],
     "lfs_ply_unpack_rows": [i32, i32, vp, C.POINTER(Splats), vp],
-    "lfs_render_forward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
+    "lfs_render_forward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, sz, vp],
     "lfs_render_backward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, C.POINTER(Splats), i32, vp, sz, vp],
     "lfs_render_workspace_view": [C.POINTER(RenderConfig), vp, sz, C.POINTER(RenderView)],
     "lfs_photometric_loss": [i32, i32, f32, f32, vp, vp, vp, vp, vp, sz, vp],

@@ -58,11 +58,19 @@ struct CamDev {
     float campos[3];       // -R^T t (what inverse(viewmat)[:3,3] gives), used for SH directions
     float fx, fy, cx, cy;
     float k[4];            // fisheye radial coefficients
+    float dist[12];        // OpenCV pinhole distortion: k1..k6, p1, p2, s1..s4 (model == LFS_PINHOLE_OPENCV)
     float max_angle;       // fisheye
     float approx_b1;       // fisheye: linear term of the crude backward polynomial
     int W, H, model;
     int pad;
 };
+
+// Internal model id: LFS_PINHOLE with any of the three distortion tensors present selects the OpenCV pinhole
+// model (gsplat/ProjectionUT3DGSFused.cu:91-113); it never crosses the C ABI.
+constexpr int LFS_PINHOLE_OPENCV = 4;
+inline int effective_model(int model, const float* radial, const float* tangential, const float* thin_prism) {
+    return (model == LFS_PINHOLE && (radial || tangential || thin_prism)) ? LFS_PINHOLE_OPENCV : model;
+}
 
 // One packed 64-byte record per Gaussian for the rasterizer:
 //   r0 = (M00, M01, M02, gro.x)   M = diag(1/scale) * R^T
@@ -72,8 +80,9 @@ struct CamDev {
 constexpr int kRecordFloats = 16;
 
 // Host-side launchers shared between translation units (all asynchronous on `st`).
-int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, int W, int H,
-                        int model, CamDev* cams, cudaStream_t st);
+// radial: [C,4] for LFS_FISHEYE, [C,6] for LFS_PINHOLE; tangential [C,2] and thin_prism [C,4] only for LFS_PINHOLE.
+int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, const float* tangential,
+                        const float* thin_prism, int W, int H, int model, CamDev* cams, cudaStream_t st);
 
 // ---- sort.cu -------------------------------------------------------------------------------
 struct SortScratch {

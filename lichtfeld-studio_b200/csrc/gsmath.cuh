@@ -63,7 +63,8 @@ __device__ __forceinline__ void quat_to_rotmat_renorm(float w, float x, float y,
 }
 
 // ---------------------------------------------------------------------------------------------
-// Camera models (global shutter). Pinhole without distortion and the OpenCV fisheye model.
+// Camera models (global shutter): pinhole without distortion, OpenCV pinhole (radial, tangential, thin prism)
+// and the OpenCV fisheye model.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool in_bounds_margin(float px, float py, const CamDev& c, float margin) {
     const float mx = (float)c.W * margin, my = (float)c.H * margin;
@@ -105,11 +106,35 @@ __device__ __forceinline__ float fisheye_dpoly_even(const float* k, float x) {
 // Camera-space point -> image point. Returns validity (inside the image with margin, in front
 // of the camera, inside the fisheye cone). atan2 is evaluated in double and rounded so that a
 // host evaluation of the same expression gives the same float.
+// OpenCV pinhole distortion of a normalised point (gsplat/Cameras.cuh:504-533): radial factor and
+// tangential + thin-prism offset.
+__device__ __forceinline__ void opencv_distortion(const CamDev& c, float u, float v, float& icD, float& dx, float& dy) {
+    const float* k = c.dist;
+    const float u2 = u * u, v2 = v * v;
+    const float r2 = u2 + v2;
+    const float a1 = 2.f * u * v;
+    const float a2 = r2 + 2.f * u2;
+    const float a3 = r2 + 2.f * v2;
+    const float num = 1.f + r2 * (k[0] + r2 * (k[1] + r2 * k[2]));
+    const float den = 1.f + r2 * (k[3] + r2 * (k[4] + r2 * k[5]));
+    icD = num / den;
+    dx = k[6] * a1 + k[7] * a2 + r2 * (k[8] + r2 * k[9]);
+    dy = k[6] * a3 + k[7] * a1 + r2 * (k[10] + r2 * k[11]);
+}
+
 template <int MODEL>
 __device__ __forceinline__ bool cam_point_to_image(const CamDev& c, f3 p, float margin, float& ox, float& oy) {
     ox = 0.f; oy = 0.f;
     if (p.z <= 0.f) return false;
-    if (MODEL == LFS_PINHOLE) {
+    if (MODEL == LFS_PINHOLE_OPENCV) {
+        // gsplat/Cameras.cuh:535-597: points whose radial factor comes close to flipping are invalid
+        const float u = p.x / p.z, v = p.y / p.z;
+        float icD, dx, dy;
+        opencv_distortion(c, u, v, icD, dx, dy);
+        ox = (icD * u + dx) * c.fx + c.cx;
+        oy = (icD * v + dy) * c.fy + c.cy;
+        return icD > 0.8f && in_bounds_margin(ox, oy, c, margin);
+    } else if (MODEL == LFS_PINHOLE) {
         ox = (p.x / p.z) * c.fx + c.cx;
         oy = (p.y / p.z) * c.fy + c.cy;
         return in_bounds_margin(ox, oy, c, margin);
@@ -133,7 +158,48 @@ template <int MODEL>
 __device__ __forceinline__ bool image_to_cam_ray(const CamDev& c, float px, float py, f3& ray) {
     const float ux = (px - c.cx) / c.fx;
     const float uy = (py - c.cy) / c.fy;
-    if (MODEL == LFS_PINHOLE) {
+    if (MODEL == LFS_PINHOLE_OPENCV) {
+        // Newton inversion of the distortion, at most 5 steps (gsplat/Cameras.cuh:635-754). Once per pixel, so
+        // the Jacobian keeps the reference's mixed float / double literal arithmetic.
+        const float k1 = c.dist[0], k2 = c.dist[1], k3 = c.dist[2], k4 = c.dist[3], k5 = c.dist[4], k6 = c.dist[5];
+        const float p1 = c.dist[6], p2 = c.dist[7], s1 = c.dist[8], s2 = c.dist[9], s3 = c.dist[10], s4 = c.dist[11];
+        const float xd = ux, yd = uy;
+        float x = xd, y = yd;
+        bool converged = false;
+        for (int iter = 0; iter < 5; ++iter) {
+            const float r = x * x + y * y;
+            const float r2 = r * r;
+            const float alpha = 1.0f + r * (k1 + r * (k2 + r * k3));
+            const float beta = 1.0f + r * (k4 + r * (k5 + r * k6));
+            const float d = alpha / beta;
+            if (d <= 0.f) break;
+            const float fx = d * x + 2 * p1 * x * y + p2 * (r + 2 * x * x) + s1 * r + s2 * r2 - xd;
+            const float fy = d * y + 2 * p2 * x * y + p1 * (r + 2 * y * y) + s3 * r + s4 * r2 - yd;
+            const float alpha_r = (float)(k1 + r * (2.0 * k2 + r * (3.0 * k3)));
+            const float beta_r = (float)(k4 + r * (2.0 * k5 + r * (3.0 * k6)));
+            const float d_r = (alpha_r * beta - alpha * beta_r) / (beta * beta);
+            const float d_x = (float)(2.0 * x * d_r);
+            const float d_y = (float)(2.0 * y * d_r);
+            float fx_x = (float)(d + d_x * x + 2.0 * p1 * y + 6.0 * p2 * x);
+            fx_x = (float)(fx_x + 2.0 * x * (s1 + 2.0 * s2 * r));
+            float fx_y = (float)(d_y * x + 2.0 * p1 * x + 2.0 * p2 * y);
+            fx_y = (float)(fx_y + 2.0 * y * (s1 + 2.0 * s2 * r));
+            float fy_x = (float)(d_x * y + 2.0 * p2 * y + 2.0 * p1 * x);
+            fy_x = (float)(fy_x + 2.0 * x * (s3 + 2.0 * s4 * r));
+            float fy_y = (float)(d + d_y * y + 2.0 * p2 * x + 6.0 * p1 * y);
+            fy_y = (float)(fy_y + 2.0 * y * (s3 + 2.0 * s4 * r));
+            const float det = fx_y * fy_x - fx_x * fy_y;
+            if (fabsf(det) < 1e-6f) break;
+            const float dx = (fx * fy_y - fy * fx_y) / det;
+            const float dy = (fy * fx_x - fx * fy_x) / det;
+            x += dx;
+            y += dy;
+            if (fabsf(dx) < 1e-6f && fabsf(dy) < 1e-6f) { converged = true; break; }
+        }
+        const float len = sqrtf(x * x + y * y + 1.f);
+        ray = {x / len, y / len, 1.f / len};
+        return converged;
+    } else if (MODEL == LFS_PINHOLE) {
         const float len = sqrtf(ux * ux + uy * uy + 1.f);
         ray = {ux / len, uy / len, 1.f / len};
         return true;

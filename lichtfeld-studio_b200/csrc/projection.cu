@@ -12,8 +12,10 @@ namespace lfs {
 
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const float* __restrict__ K,
-                                           const float* __restrict__ radial4, int W, int H, int model) {
+                                           const float* __restrict__ radial4, const float* __restrict__ dist12, int W, int H,
+                                           int model) {
     CamDev c;
+    for (int i = 0; i < 12; ++i) c.dist[i] = dist12 ? dist12[i] : 0.f;
     // quaternion of the rotation block: the branch with the largest of (trace, +-diagonal sums)
     const float R00 = vm[0], R01 = vm[1], R02 = vm[2];
     const float R10 = vm[4], R11 = vm[5], R12 = vm[6];
@@ -94,15 +96,26 @@ __device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const f
 }
 
 __global__ void camera_setup_kernel(int C, const float* __restrict__ viewmats, const float* __restrict__ Ks,
-                                    const float* __restrict__ radial, int W, int H, int model, CamDev* cams) {
+                                    const float* __restrict__ radial, const float* __restrict__ tangential,
+                                    const float* __restrict__ thin_prism, int W, int H, int model, CamDev* cams) {
     const int cid = blockIdx.x * blockDim.x + threadIdx.x;
     if (cid >= C) return;
-    cams[cid] = make_cam(viewmats + cid * 16, Ks + cid * 9, radial ? radial + cid * 4 : nullptr, W, H, model);
+    if (model == LFS_PINHOLE_OPENCV) {
+        float d[12];
+        for (int i = 0; i < 6; ++i) d[i] = radial ? radial[cid * 6 + i] : 0.f;
+        for (int i = 0; i < 2; ++i) d[6 + i] = tangential ? tangential[cid * 2 + i] : 0.f;
+        for (int i = 0; i < 4; ++i) d[8 + i] = thin_prism ? thin_prism[cid * 4 + i] : 0.f;
+        cams[cid] = make_cam(viewmats + cid * 16, Ks + cid * 9, nullptr, d, W, H, model);
+    } else {
+        cams[cid] = make_cam(viewmats + cid * 16, Ks + cid * 9, (radial && model == LFS_FISHEYE) ? radial + cid * 4 : nullptr,
+                             nullptr, W, H, model);
+    }
 }
 
-int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, int W, int H,
-                        int model, CamDev* cams, cudaStream_t st) {
-    camera_setup_kernel<<<(C + 31) / 32, 32, 0, st>>>(C, viewmats, Ks, radial, W, H, model, cams);
+int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, const float* tangential,
+                        const float* thin_prism, int W, int H, int model, CamDev* cams, cudaStream_t st) {
+    camera_setup_kernel<<<(C + 31) / 32, 32, 0, st>>>(C, viewmats, Ks, radial, tangential, thin_prism, W, H,
+                                                      effective_model(model, radial, tangential, thin_prism), cams);
     return check_launch("camera_setup");
 }
 
@@ -216,14 +229,24 @@ template <int MODEL>
 __global__ void __launch_bounds__(256) projection_ut_kernel(
     int C, int N, const float* __restrict__ means, const float* __restrict__ quats, const float* __restrict__ scales,
     const float* __restrict__ opacities, const float* __restrict__ viewmats, const float* __restrict__ Ks,
-    const float* __restrict__ radial, int W, int H, ProjParams pp,
-    int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths, float* __restrict__ conics,
-    float* __restrict__ compensations) {
+    const float* __restrict__ radial, const float* __restrict__ tangential, const float* __restrict__ thin_prism, int W, int H,
+    ProjParams pp, int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths,
+    float* __restrict__ conics, float* __restrict__ compensations) {
     const int64_t total = (int64_t)C * N;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
         const int cid = (int)(idx / N);
         const int gid = (int)(idx % N);
-        const CamDev cam = make_cam(viewmats + cid * 16, Ks + cid * 9, radial ? radial + cid * 4 : nullptr, W, H, MODEL);
+        CamDev cam;
+        if (MODEL == LFS_PINHOLE_OPENCV) {
+            float d[12];
+            for (int i = 0; i < 6; ++i) d[i] = radial ? radial[cid * 6 + i] : 0.f;
+            for (int i = 0; i < 2; ++i) d[6 + i] = tangential ? tangential[cid * 2 + i] : 0.f;
+            for (int i = 0; i < 4; ++i) d[8 + i] = thin_prism ? thin_prism[cid * 4 + i] : 0.f;
+            cam = make_cam(viewmats + cid * 16, Ks + cid * 9, nullptr, d, W, H, MODEL);
+        } else {
+            cam = make_cam(viewmats + cid * 16, Ks + cid * 9, (radial && MODEL == LFS_FISHEYE) ? radial + cid * 4 : nullptr, nullptr,
+                           W, H, MODEL);
+        }
         const f3 mean{means[gid * 3], means[gid * 3 + 1], means[gid * 3 + 2]};
         const f3 scale{scales[gid * 3], scales[gid * 3 + 1], scales[gid * 3 + 2]};
         const float4 q = reinterpret_cast<const float4*>(quats)[gid];
@@ -249,19 +272,23 @@ __global__ void __launch_bounds__(256) projection_ut_kernel(
 }
 
 int launch_projection_ut(int C, int N, const float* means, const float* quats, const float* scales,
-                         const float* opacities, const float* viewmats, const float* Ks, const float* radial, int W, int H,
+                         const float* opacities, const float* viewmats, const float* Ks, const float* radial,
+                         const float* tangential, const float* thin_prism, int W, int H,
                          const ProjParams& pp, int model, int32_t* radii,
                          float* means2d, float* depths, float* conics, float* compensations, cudaStream_t st) {
     const int64_t total = (int64_t)C * N;
     if (total == 0) return LFS_OK;
     const int grid = grid_for(total, 256);
     LFS_TIMED("projection_ut", st);
-    if (model == LFS_PINHOLE)
-        projection_ut_kernel<LFS_PINHOLE><<<grid, 256, 0, st>>>(C, N, means, quats, scales, opacities, viewmats, Ks, radial,
-                                                                W, H, pp, radii, means2d, depths, conics, compensations);
-    else
-        projection_ut_kernel<LFS_FISHEYE><<<grid, 256, 0, st>>>(C, N, means, quats, scales, opacities, viewmats, Ks, radial,
-                                                                W, H, pp, radii, means2d, depths, conics, compensations);
+#define LFS_PROJ(MODEL)                                                                                                      \
+    projection_ut_kernel<MODEL><<<grid, 256, 0, st>>>(C, N, means, quats, scales, opacities, viewmats, Ks, radial, tangential, \
+                                                      thin_prism, W, H, pp, radii, means2d, depths, conics, compensations)
+    switch (effective_model(model, radial, tangential, thin_prism)) {
+        case LFS_PINHOLE: LFS_PROJ(LFS_PINHOLE); break;
+        case LFS_PINHOLE_OPENCV: LFS_PROJ(LFS_PINHOLE_OPENCV); break;
+        default: LFS_PROJ(LFS_FISHEYE); break;
+    }
+#undef LFS_PROJ
     return check_launch("projection_ut");
 }
 
@@ -500,18 +527,19 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
     if (smem > 48 * 1024) {
         cudaFuncSetAttribute(project_pack_kernel<LFS_PINHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(project_pack_kernel<LFS_FISHEYE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(project_pack_kernel<LFS_PINHOLE_OPENCV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     LFS_TIMED("project_pack", st);
-    if (model == LFS_PINHOLE)
-        project_pack_kernel<LFS_PINHOLE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
-                                                               p.rotation_raw, p.opacity_raw, cam, pp, opt, (float)tile_size,
-                                                               tw, th, radii, means2d, depths, tiles, sort_keys,
-                                                               sort_vals, records, bounds, accum, n_visible);
-    else
-        project_pack_kernel<LFS_FISHEYE><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw,
-                                                               p.rotation_raw, p.opacity_raw, cam, pp, opt, (float)tile_size,
-                                                               tw, th, radii, means2d, depths, tiles, sort_keys,
-                                                               sort_vals, records, bounds, accum, n_visible);
+#define LFS_PACK(MODEL)                                                                                                        \
+    project_pack_kernel<MODEL><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw, p.rotation_raw,   \
+                                                        p.opacity_raw, cam, pp, opt, (float)tile_size, tw, th, radii, means2d, \
+                                                        depths, tiles, sort_keys, sort_vals, records, bounds, accum, n_visible)
+    switch (model) {
+        case LFS_PINHOLE: LFS_PACK(LFS_PINHOLE); break;
+        case LFS_PINHOLE_OPENCV: LFS_PACK(LFS_PINHOLE_OPENCV); break;
+        default: LFS_PACK(LFS_FISHEYE); break;
+    }
+#undef LFS_PACK
     return check_launch("project_pack");
 }
 

@@ -681,6 +681,7 @@ int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t
                                                                 render, alphas, last_ids, extra_sum)
     const bool extra = a.channels != 3;
     if (a.model == LFS_PINHOLE) { if (extra) LFS_FWD(LFS_PINHOLE, true); else LFS_FWD(LFS_PINHOLE, false); }
+    else if (a.model == LFS_PINHOLE_OPENCV) { if (extra) LFS_FWD(LFS_PINHOLE_OPENCV, true); else LFS_FWD(LFS_PINHOLE_OPENCV, false); }
     else { if (extra) LFS_FWD(LFS_FISHEYE, true); else LFS_FWD(LFS_FISHEYE, false); }
 #undef LFS_FWD
     return check_launch("raster_fwd");
@@ -701,6 +702,8 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     if (!attr_set) {
         LFS_BWD_ATTR(LFS_PINHOLE, false, false); LFS_BWD_ATTR(LFS_PINHOLE, true, false); LFS_BWD_ATTR(LFS_PINHOLE, true, true);
         LFS_BWD_ATTR(LFS_FISHEYE, false, false); LFS_BWD_ATTR(LFS_FISHEYE, true, false); LFS_BWD_ATTR(LFS_FISHEYE, true, true);
+        LFS_BWD_ATTR(LFS_PINHOLE_OPENCV, false, false); LFS_BWD_ATTR(LFS_PINHOLE_OPENCV, true, false);
+        LFS_BWD_ATTR(LFS_PINHOLE_OPENCV, true, true);
         attr_set = true;
     }
 #undef LFS_BWD_ATTR
@@ -712,6 +715,9 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     const bool extra = a.channels != 3, xgrad = extra && accum_extra != nullptr;
     if (a.model == LFS_PINHOLE) {
         if (!extra) LFS_BWD(LFS_PINHOLE, false, false); else if (!xgrad) LFS_BWD(LFS_PINHOLE, true, false); else LFS_BWD(LFS_PINHOLE, true, true);
+    } else if (a.model == LFS_PINHOLE_OPENCV) {
+        if (!extra) LFS_BWD(LFS_PINHOLE_OPENCV, false, false); else if (!xgrad) LFS_BWD(LFS_PINHOLE_OPENCV, true, false);
+        else LFS_BWD(LFS_PINHOLE_OPENCV, true, true);
     } else {
         if (!extra) LFS_BWD(LFS_FISHEYE, false, false); else if (!xgrad) LFS_BWD(LFS_FISHEYE, true, false); else LFS_BWD(LFS_FISHEYE, true, true);
     }

@@ -118,7 +118,7 @@ def load_ply(path: str, device, capacity: int | None = None) -> SplatData:
                 canon[:, j] = rows[:, idx[x]]
         rows = canon
     model = SplatData(n, K, device, capacity)
-    dev_rows = torch.from_numpy(np.ascontiguousarray(rows)).to(device)
+    dev_rows = torch.from_numpy(np.array(rows, dtype=np.float32, order="C")).to(device)  # a writable copy
     p = model.struct()
     call("lfs_ply_unpack_rows", n, K, ptr(dev_rows), C.byref(p), _stream())
     return model

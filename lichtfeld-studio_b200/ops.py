@@ -34,13 +34,28 @@ def _ws(nbytes, device):
 
 
 def _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs):
+    """Checks the camera arguments and returns the three coefficient tensors in the widths the C ABI reads:
+    pinhole radial [C,6] (zero-padded: the reference kernel reads six floats whatever the tensor holds), tangential
+    [C,2], thin prism [C,4]; fisheye radial [C,4]."""
     if rs_type != ShutterType.GLOBAL or viewmats1 is not None:
         raise RuntimeError("only a global shutter is supported")
     if camera_model not in (CameraModelType.PINHOLE, CameraModelType.FISHEYE):
         raise RuntimeError("camera model must be PINHOLE or FISHEYE")
-    if tangential_coeffs is not None or thin_prism_coeffs is not None or \
-            (camera_model == CameraModelType.PINHOLE and radial_coeffs is not None):
-        raise RuntimeError("pinhole distortion coefficients are not supported")
+    if camera_model == CameraModelType.FISHEYE and (tangential_coeffs is not None or thin_prism_coeffs is not None):
+        raise RuntimeError("tangential / thin-prism coefficients belong to the pinhole model")
+
+    def widen(t, n):
+        if t is None:
+            return None
+        _check_input(t, "distortion coefficients")
+        t = t.reshape(-1, t.shape[-1])
+        if t.shape[-1] > n:
+            raise RuntimeError(f"at most {n} coefficients, got {t.shape[-1]}")
+        return t if t.shape[-1] == n else torch.nn.functional.pad(t, (0, n - t.shape[-1])).contiguous()
+
+    if camera_model == CameraModelType.PINHOLE:
+        return widen(radial_coeffs, 6), widen(tangential_coeffs, 2), widen(thin_prism_coeffs, 4)
+    return widen(radial_coeffs, 4), None, None
 
 
 # gsplat/Ops.h:12-17
@@ -138,7 +153,8 @@ def projection_ut_3dgs_fused(means, quats, scales, opacities, viewmats0, viewmat
         _check_input(t, n)
     if opacities is not None:
         _check_input(opacities, "opacities")
-    _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
+    radial_coeffs, tangential_coeffs, thin_prism_coeffs = _only_global_pinhole_fisheye(
+        camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
     ut = ut_params or UTParams()
     N, Cn, dev = means.shape[0], viewmats0.shape[0], means.device
     radii = torch.empty((Cn, N, 2), dtype=torch.int32, device=dev)
@@ -148,7 +164,7 @@ def projection_ut_3dgs_fused(means, quats, scales, opacities, viewmats0, viewmat
     comps = torch.zeros((Cn, N), dtype=torch.float32, device=dev) if calc_compensations else None
     call("lfs_projection_ut_3dgs_fused", Cn, N, ptr(means), ptr(quats), ptr(scales), ptr(opacities), ptr(viewmats0), ptr(Ks),
          int(image_width), int(image_height), float(eps2d), float(near_plane), float(far_plane), float(radius_clip),
-         int(camera_model), ut, ptr(radial_coeffs), ptr(radii), ptr(means2d), ptr(depths), ptr(conics), ptr(comps), _stream())
+         int(camera_model), ut, ptr(radial_coeffs), ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(radii), ptr(means2d), ptr(depths), ptr(conics), ptr(comps), _stream())
     return radii, means2d, depths, conics, comps
 
 
@@ -180,7 +196,8 @@ def rasterize_to_pixels_from_world_3dgs_fwd(means, quats, scales, colors, opacit
                  (viewmats0, "viewmats0"), (Ks, "Ks")):
         _check_input(t, n)
     _check_input(tile_offsets, "tile_offsets", torch.int32); _check_input(flatten_ids, "flatten_ids", torch.int32)
-    _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
+    radial_coeffs, tangential_coeffs, thin_prism_coeffs = _only_global_pinhole_fisheye(
+        camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
     CH = int(colors.shape[-1])
     if CH not in (1, 3, 4):
         raise RuntimeError(f"Unsupported number of channels: {CH}")
@@ -197,7 +214,7 @@ def rasterize_to_pixels_from_world_3dgs_fwd(means, quats, scales, colors, opacit
         raise RuntimeError(f"backgrounds must have {CH} channels")
     call("lfs_rasterize_to_pixels_from_world_3dgs_fwd", N, flatten_ids.numel(), CH, ptr(means), ptr(quats), ptr(scales), ptr(colors),
          ptr(opacities), ptr(bg), ptr(masks), W, H, int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model), ptr(radial_coeffs),
-         ptr(tile_offsets), ptr(flatten_ids), ptr(renders), ptr(alphas), ptr(last_ids), ptr(ws), ws.numel(), _stream())
+         ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(renders), ptr(alphas), ptr(last_ids), ptr(ws), ws.numel(), _stream())
     return renders, alphas, last_ids
 
 
@@ -212,7 +229,8 @@ def rasterize_to_pixels_from_world_3dgs_bwd(means, quats, scales, colors, opacit
                  (render_alphas, "render_alphas"), (v_render_colors, "v_render_colors"), (v_render_alphas, "v_render_alphas")):
         _check_input(t, n)
     _check_input(last_ids, "last_ids", torch.int32)
-    _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
+    radial_coeffs, tangential_coeffs, thin_prism_coeffs = _only_global_pinhole_fisheye(
+        camera_model, rs_type, viewmats1, tangential_coeffs, thin_prism_coeffs, radial_coeffs)
     CH = int(colors.shape[-1])
     if CH not in (1, 3, 4):
         raise RuntimeError(f"Unsupported number of channels: {CH}")
@@ -225,7 +243,7 @@ def rasterize_to_pixels_from_world_3dgs_bwd(means, quats, scales, colors, opacit
     ws = _ws(capi.lib().lfs_rasterize_workspace_bytes(N), dev)
     call("lfs_rasterize_to_pixels_from_world_3dgs_bwd", N, flatten_ids.numel(), CH, ptr(means), ptr(quats), ptr(scales), ptr(colors),
          ptr(opacities), ptr(bg), ptr(masks), int(image_width), int(image_height), int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model),
-         ptr(radial_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(render_alphas), ptr(last_ids), ptr(v_render_colors),
+         ptr(radial_coeffs), ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(render_alphas), ptr(last_ids), ptr(v_render_colors),
          ptr(v_render_alphas), ptr(v_means), ptr(v_quats), ptr(v_scales), ptr(v_colors), ptr(v_opacities), ptr(ws), ws.numel(),
          _stream())
     return v_means, v_quats, v_scales, v_colors, v_opacities

@@ -88,7 +88,27 @@ class Camera:
     width: int
     height: int
     camera_model: int = capi.PINHOLE
-    radial: torch.Tensor | None = None  # [4] fisheye coefficients
+    radial: torch.Tensor | None = None      # fisheye: [4] coefficients; pinhole: [6] radial distortion (k1..k6)
+    tangential: torch.Tensor | None = None  # pinhole: [2]
+    thin_prism: torch.Tensor | None = None  # pinhole: [4]
+
+    def coefficient_pointers(self):
+        """Device pointers in the widths the C ABI reads (pinhole radial 6, tangential 2, thin prism 4; fisheye radial 4);
+        shorter tensors are zero-padded once and cached, like rasterize() pads the loader's coefficient vectors
+        (src/training/rasterization/rasterizer.cpp:96-121)."""
+        if not hasattr(self, "_padded"):
+            def widen(t, n):
+                if t is None:
+                    return None
+                t = t.reshape(-1).float()
+                if t.numel() > n:
+                    raise RuntimeError(f"at most {n} distortion coefficients, got {t.numel()}")
+                return torch.nn.functional.pad(t, (0, n - t.numel())).contiguous()
+            fisheye = self.camera_model == capi.FISHEYE
+            if fisheye and (self.tangential is not None or self.thin_prism is not None):
+                raise RuntimeError("tangential / thin-prism coefficients belong to the pinhole model")
+            self._padded = (widen(self.radial, 4 if fisheye else 6), widen(self.tangential, 2), widen(self.thin_prism, 4))
+        return tuple(None if t is None else t.data_ptr() for t in self._padded)
 
 
 @dataclass
@@ -155,8 +175,9 @@ class Rasterizer:
             raise RuntimeError("camera size does not match the rasterizer")
         self.cfg.N = self.model.size
         self.cfg.camera_model = int(cam.camera_model)
+        self.cfg.radial_coeffs, self.cfg.tangential_coeffs, self.cfg.thin_prism_coeffs = cam.coefficient_pointers()
         p = self.model.struct()
-        call("lfs_render_forward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), ptr(cam.radial),
+        call("lfs_render_forward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K),
              ptr(background), ptr(self.render), ptr(self.alpha), ptr(self.status), ptr(self.ws), self.ws.numel(), _stream())
         image = self.render if self.channels == 3 else (self.render[..., :3].contiguous() if self.channels == 4 else None)
         depth = None if self.channels == 3 else self.render[..., self.channels - 1:]

@@ -162,6 +162,9 @@ struct Camera {
     float k[4];
     float max_angle;
     float approx_b1;  // approx_backward_poly = {0, approx_b1}
+    // OpenCV pinhole distortion (Cameras.cuh:481-486): used when `distorted`
+    bool distorted;
+    float radial[6], tangential[2], thin_prism[4];
 };
 
 inline float numerically_stable_norm2(float x, float y) {  // Cameras.cuh:77-89
@@ -221,7 +224,16 @@ Camera make_camera(int model, const float* K, uint32_t W, uint32_t H, const floa
     c.model = model;
     c.fx = K[0]; c.fy = K[4]; c.cx = K[2]; c.cy = K[5];
     c.W = W; c.H = H;
-    for (int i = 0; i < 4; ++i) c.k[i] = radial ? radial[i] : 0.f;
+    // `radial` is model dependent: FISHEYE -> 4 radial coefficients; PINHOLE -> 12 floats
+    // (k1..k6, p1, p2, s1..s4), whose presence selects OpenCVPinholeCameraModel like any of the three optional
+    // tensors does in gsplat/ProjectionUT3DGSFused.cu:91-113
+    if (model == PINHOLE && radial) {
+        c.distorted = true;
+        for (int i = 0; i < 6; ++i) c.radial[i] = radial[i];
+        for (int i = 0; i < 2; ++i) c.tangential[i] = radial[6 + i];
+        for (int i = 0; i < 4; ++i) c.thin_prism[i] = radial[8 + i];
+    }
+    for (int i = 0; i < 4; ++i) c.k[i] = (radial && model == FISHEYE) ? radial[i] : 0.f;
     if (model == FISHEYE) {
         const float mdx = std::max((float)W - c.cx, c.cx);
         const float mdy = std::max((float)H - c.cy, c.cy);
@@ -266,8 +278,32 @@ inline float poly_even5_d(const float* k, float x) {  // 1 + 3k1 x^2 + 5k2 x^4 +
 // camera_ray_to_image_point. Pinhole: Cameras.cuh:431-455. Fisheye: :894-959.
 // The two transcendental calls of the fisheye model (atan2) are evaluated in double and
 // rounded to float: the CUDA library does the same so that both sides agree bit for bit.
+// OpenCVPinholeCameraModel::compute_distortion, Cameras.cuh:504-533
+inline void opencv_distortion(const Camera& c, float u, float v, float& icD, float& dx, float& dy) {
+    const float u2 = u * u, v2 = v * v;
+    const float r2 = u2 + v2;
+    const float a1 = 2.f * u * v;
+    const float a2 = r2 + 2.f * u2;
+    const float a3 = r2 + 2.f * v2;
+    const float num = 1.f + r2 * (c.radial[0] + r2 * (c.radial[1] + r2 * c.radial[2]));
+    const float den = 1.f + r2 * (c.radial[3] + r2 * (c.radial[4] + r2 * c.radial[5]));
+    icD = num / den;
+    dx = c.tangential[0] * a1 + c.tangential[1] * a2 + r2 * (c.thin_prism[0] + r2 * c.thin_prism[1]);
+    dy = c.tangential[0] * a3 + c.tangential[1] * a1 + r2 * (c.thin_prism[2] + r2 * c.thin_prism[3]);
+}
+
 inline bool cam_point_to_image(const Camera& c, V3 p, float margin, V2& out) {
     out = {0.f, 0.f};
+    if (c.model == PINHOLE && c.distorted) {  // Cameras.cuh:535-597
+        if (p.z <= 0.f) return false;
+        const float u = p.x / p.z, v = p.y / p.z;
+        float icD, dx, dy;
+        opencv_distortion(c, u, v, icD, dx, dy);
+        const bool valid_radial = icD > 0.8f;
+        out.x = (icD * u + dx) * c.fx + c.cx;
+        out.y = (icD * v + dy) * c.fy + c.cy;
+        return valid_radial && in_bounds_margin(out, c, margin);
+    }
     if (c.model == PINHOLE) {
         if (p.z <= 0.f) return false;
         out.x = (p.x / p.z) * c.fx + c.cx;
@@ -296,6 +332,50 @@ inline bool cam_point_to_image(const Camera& c, V3 p, float margin, V2& out) {
 inline bool image_to_cam_ray(const Camera& c, float px, float py, V3& ray) {
     const float ux = (px - c.cx) / c.fx;
     const float uy = (py - c.cy) / c.fy;
+    if (c.model == PINHOLE && c.distorted) {
+        // compute_undistortion_newton with at most 5 iterations (Cameras.cuh:635-754); the Jacobian expressions mix
+        // float and double literals exactly as written there
+        const float k1 = c.radial[0], k2 = c.radial[1], k3 = c.radial[2], k4 = c.radial[3], k5 = c.radial[4], k6 = c.radial[5];
+        const float p1 = c.tangential[0], p2 = c.tangential[1];
+        const float s1 = c.thin_prism[0], s2 = c.thin_prism[1], s3 = c.thin_prism[2], s4 = c.thin_prism[3];
+        const float xd = ux, yd = uy;
+        float x = xd, y = yd;
+        const float eps = 1e-6f;
+        bool converged = false;
+        for (int iter = 0; iter < 5; ++iter) {
+            const float r = x * x + y * y;
+            const float r2 = r * r;
+            const float alpha = 1.0f + r * (k1 + r * (k2 + r * k3));
+            const float beta = 1.0f + r * (k4 + r * (k5 + r * k6));
+            const float d = alpha / beta;
+            if (d <= 0.f) break;
+            const float fx = d * x + 2 * p1 * x * y + p2 * (r + 2 * x * x) + s1 * r + s2 * r2 - xd;
+            const float fy = d * y + 2 * p2 * x * y + p1 * (r + 2 * y * y) + s3 * r + s4 * r2 - yd;
+            const float alpha_r = (float)(k1 + r * (2.0 * k2 + r * (3.0 * k3)));
+            const float beta_r = (float)(k4 + r * (2.0 * k5 + r * (3.0 * k6)));
+            const float d_r = (alpha_r * beta - alpha * beta_r) / (beta * beta);
+            const float d_x = (float)(2.0 * x * d_r);
+            const float d_y = (float)(2.0 * y * d_r);
+            float fx_x = (float)(d + d_x * x + 2.0 * p1 * y + 6.0 * p2 * x);
+            fx_x = (float)(fx_x + 2.0 * x * (s1 + 2.0 * s2 * r));
+            float fx_y = (float)(d_y * x + 2.0 * p1 * x + 2.0 * p2 * y);
+            fx_y = (float)(fx_y + 2.0 * y * (s1 + 2.0 * s2 * r));
+            float fy_x = (float)(d_x * y + 2.0 * p2 * y + 2.0 * p1 * x);
+            fy_x = (float)(fy_x + 2.0 * x * (s3 + 2.0 * s4 * r));
+            float fy_y = (float)(d + d_y * y + 2.0 * p2 * x + 6.0 * p1 * y);
+            fy_y = (float)(fy_y + 2.0 * y * (s3 + 2.0 * s4 * r));
+            const float det = fx_y * fy_x - fx_x * fy_y;
+            if (std::fabs(det) < eps) break;
+            const float dx = (fx * fy_y - fy * fx_y) / det;
+            const float dy = (fy * fx_x - fx * fy_x) / det;
+            x += dx;
+            y += dy;
+            if (std::fabs(dx) < eps && std::fabs(dy) < eps) { converged = true; break; }
+        }
+        const float len = std::sqrt(x * x + y * y + 1.f * 1.f);
+        ray = {x / len, y / len, 1.f / len};
+        return converged;
+    }
     if (c.model == PINHOLE) {
         const float len = std::sqrt(ux * ux + uy * uy + 1.f * 1.f);
         ray = {ux / len, uy / len, 1.f / len};
@@ -341,7 +421,7 @@ void orc_projection_ut_3dgs_fused(
     const float* means, const float* quats, const float* scales, const float* opacities /*nullable*/,
     const float* viewmats, const float* Ks, int W, int H,
     float eps2d, float near_plane, float far_plane, float radius_clip,
-    int camera_model, const float* ut, const float* radial_coeffs /*nullable, [C,4]*/,
+    int camera_model, const float* ut, const float* radial_coeffs /*nullable: fisheye [C,4]; pinhole [C,12] = k1..k6 p1 p2 s1..s4*/,
     int32_t* radii, float* means2d, float* depths, float* conics, float* compensations /*nullable*/) {
     const float alpha = ut[0], beta = ut[1], kappa = ut[2], margin = ut[3];
     const bool require_all = ut[4] != 0.f;
@@ -349,7 +429,7 @@ void orc_projection_ut_3dgs_fused(
     for (int cid = 0; cid < C; ++cid) {
         const Pose pose = pose_from_viewmat(viewmats + cid * 16);
         const Camera cam = make_camera(camera_model, Ks + cid * 9, W, H,
-                                       radial_coeffs ? radial_coeffs + cid * 4 : nullptr);
+                                       radial_coeffs ? radial_coeffs + cid * (camera_model == PINHOLE ? 12 : 4) : nullptr);
 #pragma omp parallel for schedule(static)
         for (int gid = 0; gid < N; ++gid) {
             const size_t idx = (size_t)cid * N + gid;
@@ -1201,6 +1281,23 @@ void orc_quats_to_rotmats(int n, const float* quats, float* rotmats) {
 void orc_campos(const float* vm, float* out) {
     for (int i = 0; i < 3; ++i)
         out[i] = (float)(-((double)vm[0 * 4 + i] * vm[3] + (double)vm[1 * 4 + i] * vm[7] + (double)vm[2 * 4 + i] * vm[11]));
+}
+
+// Camera model in isolation (for pinning the restatement): camera-space point -> pixel and pixel -> unit camera ray.
+// `dist` as in make_camera (fisheye: 4 floats; pinhole: 12 floats or null).
+int orc_cam_point_to_image(int model, const float* K, int W, int H, const float* dist, const float* p, float margin, float* out) {
+    const Camera cam = make_camera(model, K, W, H, dist);
+    V2 o;
+    const bool valid = cam_point_to_image(cam, V3{p[0], p[1], p[2]}, margin, o);
+    out[0] = o.x; out[1] = o.y;
+    return valid ? 1 : 0;
+}
+int orc_image_to_cam_ray(int model, const float* K, int W, int H, const float* dist, float px, float py, float* ray) {
+    const Camera cam = make_camera(model, K, W, H, dist);
+    V3 r;
+    const bool valid = image_to_cam_ray(cam, px, py, r);
+    ray[0] = r.x; ray[1] = r.y; ray[2] = r.z;
+    return valid ? 1 : 0;
 }
 
 int orc_num_threads() {

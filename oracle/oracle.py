@@ -257,6 +257,31 @@ def campos(viewmat):
     return out
 
 
+def cam_point_to_image(model, K, W, H, dist, p, margin=0.1):
+    out = np.zeros(2, np.float32)
+    ok = lib().orc_cam_point_to_image(i32(model), _p(_f32(K)), i32(W), i32(H), _p(_f32(dist)), _p(_f32(p)), C.c_float(margin), _p(out))
+    return out, bool(ok)
+
+
+def image_to_cam_ray(model, K, W, H, dist, px, py):
+    ray = np.zeros(3, np.float32)
+    ok = lib().orc_image_to_cam_ray(i32(model), _p(_f32(K)), i32(W), i32(H), _p(_f32(dist)), C.c_float(px), C.c_float(py), _p(ray))
+    return ray, bool(ok)
+
+
+def pack_distortion(radial=None, tangential=None, thin_prism=None):
+    """The 12-float OpenCV pinhole distortion block this oracle takes in place of the reference's three optional
+    tensors (k1..k6, p1, p2, s1..s4); shorter inputs are zero-padded. None when all three are absent."""
+    if radial is None and tangential is None and thin_prism is None:
+        return None
+    d = np.zeros(12, np.float32)
+    for off, n, a in ((0, 6, radial), (6, 2, tangential), (8, 4, thin_prism)):
+        if a is not None:
+            a = np.asarray(a, np.float32).reshape(-1)
+            d[off:off + min(n, a.size)] = a[:n]
+    return d
+
+
 # ------------------------------------------------------------------ activations
 def act_opacity(raw):
     return (1.0 / (1.0 + np.exp(-raw.astype(np.float64)))).astype(np.float32).reshape(-1)
@@ -291,7 +316,7 @@ def render_fwd(params, viewmat, K, W, H, sh_degree, background=None, camera_mode
     sh = np.concatenate([params["sh0"], params["shN"]], axis=1).astype(np.float32)
     vm = _f32(viewmat).reshape(1, 4, 4)
     Kc = _f32(K).reshape(1, 3, 3)
-    rc = None if radial is None else _f32(radial).reshape(1, 4)
+    rc = None if radial is None else _f32(radial).reshape(1, -1)
     radii, means2d, depths, conics, comps = projection_ut_3dgs_fused(
         means, quats, scales, opac, vm, Kc, W, H, eps2d, near, far, 0.0, bool(calc_compensations), camera_model, UT_DEFAULT, rc)
     cp = campos(vm[0])
@@ -348,7 +373,7 @@ def render_bwd(params, fwd, viewmat, K, W, H, sh_degree, v_render, v_alpha=None,
         vd = v_render[..., -1:]
         v_alpha = (v_alpha + np.where(a > 1e-10, -fwd["render"][..., -1:] / (ac * ac) * vd, 0.0)).astype(np.float32)
         v_render[..., -1:] = vd / ac
-    rc = None if radial is None else _f32(radial).reshape(1, 4)
+    rc = None if radial is None else _f32(radial).reshape(1, -1)
     v_means, v_quats, v_scales, v_colors, v_opac, npairs = rasterize_bwd(
         means, fwd["quats"], fwd["scales"], fwd["colors"], fwd["final_opac"], background, W, H, tile_size,
         viewmat, K, fwd["tile_offsets"], fwd["flatten_ids"], fwd["alpha"], fwd["last_ids"], v_render, v_alpha,

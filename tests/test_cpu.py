@@ -313,3 +313,37 @@ def test_ply_header_reader_and_checkpoint_roundtrip(pkg, tmp_path):
     s2 = st.DefaultStrategy(small); s2.initialize(st.DefaultStrategy.Parameters(sh_degree=1))
     with pytest.raises(RuntimeError):
         fm.load_checkpoint(s2, path)
+
+
+def test_oracle_opencv_distortion_closed_form_and_roundtrip(orc):
+    """Pins the oracle's OpenCV pinhole model (gsplat/Cameras.cuh:504-597, :635-754): the forward map against the
+    published OpenCV formula evaluated in float64, and pixel -> ray -> pixel through the Newton inversion."""
+    K = np.array([[210.0, 0, 162.0], [0, 205.0, 118.0], [0, 0, 1]], np.float32)
+    W, H = 320, 240
+    k = np.array([-0.22, 0.06, -0.004, 0.01, 0.002, 0.0]); p = np.array([0.0015, -0.002]); s = np.array([0.0008, 0.0, -0.0005, 0.0002])
+    dist = orc.pack_distortion(k, p, s)
+    rng = np.random.default_rng(0)
+    n_ok = 0
+    for _ in range(300):
+        pt = np.array([rng.uniform(-0.6, 0.6), rng.uniform(-0.45, 0.45), 1.0]) * rng.uniform(0.5, 5.0)
+        x, y = pt[0] / pt[2], pt[1] / pt[2]
+        r2 = x * x + y * y
+        icd = (1 + k[0] * r2 + k[1] * r2 ** 2 + k[2] * r2 ** 3) / (1 + k[3] * r2 + k[4] * r2 ** 2 + k[5] * r2 ** 3)
+        xd = x * icd + 2 * p[0] * x * y + p[1] * (r2 + 2 * x * x) + s[0] * r2 + s[1] * r2 * r2
+        yd = y * icd + p[0] * (r2 + 2 * y * y) + 2 * p[1] * x * y + s[2] * r2 + s[3] * r2 * r2
+        u, v = 210.0 * xd + 162.0, 205.0 * yd + 118.0
+        got, ok = orc.cam_point_to_image(0, K, W, H, dist, pt.astype(np.float32))
+        assert abs(got[0] - u) < 2e-3 and abs(got[1] - v) < 2e-3
+        inside = (-0.1 * W <= u < 1.1 * W) and (-0.1 * H <= v < 1.1 * H) and icd > 0.8
+        assert ok == inside
+        if ok:
+            ray, conv = orc.image_to_cam_ray(0, K, W, H, dist, float(got[0]), float(got[1]))
+            d = pt / np.linalg.norm(pt)
+            assert conv and np.abs(ray - d).max() < 2e-5
+            n_ok += 1
+    assert n_ok > 200
+    # behind the camera: invalid, projects to the origin; no distortion block: the plain pinhole
+    out, ok = orc.cam_point_to_image(0, K, W, H, dist, np.array([0.1, 0.1, -1.0], np.float32))
+    assert not ok and (out == 0).all()
+    out, ok = orc.cam_point_to_image(0, K, W, H, None, np.array([0.2, -0.1, 2.0], np.float32))
+    assert ok and abs(out[0] - (210 * 0.1 + 162)) < 1e-4 and abs(out[1] - (205 * -0.05 + 118)) < 1e-4
