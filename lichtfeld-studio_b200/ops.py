@@ -282,7 +282,7 @@ def adam_step_wrapper(param, exp_avg, exp_avg_sq, param_grad, lr, beta1, beta2, 
 
 
 # gsplat/Ops.h:162-270: the fused operator pair, composed from the operator-level entry points with
-# the same torch glue as gsplat/Rasterization.cpp:326-466 / :527-641. RGB mode (render_mode 0) only.
+# the same torch glue as gsplat/Rasterization.cpp:326-466 / :527-641 (all five render modes, compensations, masks).
 def rasterize_from_world_with_sh_fwd(means, quats, scales, opacities, sh_coeffs, sh_degree, backgrounds, masks, image_width,
                                      image_height, tile_size, viewmats0, viewmats1, Ks, camera_model, eps2d, near_plane,
                                      far_plane, radius_clip, scaling_modifier, calc_compensations, render_mode,

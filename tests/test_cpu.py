@@ -347,3 +347,37 @@ def test_oracle_opencv_distortion_closed_form_and_roundtrip(orc):
     assert not ok and (out == 0).all()
     out, ok = orc.cam_point_to_image(0, K, W, H, None, np.array([0.2, -0.1, 2.0], np.float32))
     assert ok and abs(out[0] - (210 * 0.1 + 162)) < 1e-4 and abs(out[1] - (205 * -0.05 + 118)) < 1e-4
+
+
+def _golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny_step.npz"))
+
+
+def test_oracle_reproduces_golden_step(orc):
+    """tests/golden/tiny_step.npz (written by tests/golden/make_golden.py from this oracle) anchors the oracle against
+    drift: integer results must match exactly, floats to a few ulp (libm's float exp may differ between hosts)."""
+    g = _golden()
+    P = {k: g[f"in_{k}"] for k in ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")}
+    W, H, deg = (int(x) for x in g["in_size"])
+    assert g["flatten_ids"].size > 2000
+    fwd = orc.render_fwd(P, g["in_viewmat"], g["in_K"], W, H, deg, background=g["in_bg"])
+    for k in ("radii", "tiles_per_gauss", "flatten_ids", "tile_offsets", "last_ids"):
+        assert np.array_equal(fwd[k], g[k]), k
+    vis = g["visible"]
+    assert np.array_equal(fwd["means2d"][vis].view(np.uint32), g["means2d"][vis].view(np.uint32))
+    assert np.abs(fwd["render"] - g["render"]).max() < 2e-6 and np.abs(fwd["alpha"] - g["alpha"]).max() < 2e-6
+    loss, gr, l1, ssim = orc.photometric_loss(fwd["render"], g["in_target"], 0.2)
+    assert np.allclose([loss, l1, ssim], g["loss"], atol=2e-6)
+    bwd = orc.render_bwd(P, fwd, g["in_viewmat"], g["in_K"], W, H, deg, g["v_render"], background=g["in_bg"])
+    for k in P:
+        assert np.allclose(bwd[k], g[f"grad_{k}"], rtol=1e-4, atol=1e-9), k
+    fd = orc.render_fwd(P, g["in_viewmat"], g["in_K"], W, H, deg, background=np.append(g["in_bg"], 0).astype(np.float32),
+                        radial=g["in_dist"], render_mode=4)
+    assert np.array_equal(fd["radii"], g["dist_radii"]) and np.array_equal(fd["flatten_ids"], g["dist_flatten_ids"])
+    assert np.abs(fd["render"] - g["dist_render"]).max() < 1e-5 and np.abs(fd["depth"] - g["dist_depth"]).max() < 1e-4
+    no, ns = orc.relocation(g["in_reloc_opacity"], g["in_reloc_scale"], g["in_reloc_ratios"], orc.binoms_table(51), 51)
+    assert np.allclose(no, g["reloc_opacity"], rtol=1e-6) and np.allclose(ns, g["reloc_scale"], rtol=1e-6)
+    p, m, v = g["in_adam_p"].copy(), g["in_adam_m"].copy(), g["in_adam_v"].copy()
+    orc.adam_step(p, m, v, g["in_adam_g"], 1e-3, 0.9, 0.999, 1e-15, 5)
+    assert np.allclose(p, g["adam_p"], rtol=1e-6) and np.array_equal(m, g["adam_m"]) and np.array_equal(v, g["adam_v"])

@@ -1,0 +1,68 @@
+"""The CUDA path against the committed vectors of tests/golden/tiny_step.npz (one small training step: lists, image,
+loss, raw-parameter gradients; a distorted RGB + expected-depth render; relocation; Adam)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+NAMES = ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")
+
+
+def T(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+@pytest.fixture(scope="module")
+def g():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny_step.npz"))
+
+
+def test_training_step_matches_golden(pkg, g):
+    tr = pkg.trainer
+    P = {k: g[f"in_{k}"] for k in NAMES}
+    W, H, deg = (int(x) for x in g["in_size"])
+    n = P["means"].shape[0]
+    model = tr.SplatData(n, (deg + 1) ** 2, DEV).load(P)
+    grads = model.like()
+    rast = tr.Rasterizer(model, W, H, deg)
+    lossfn = tr.PhotometricLoss(W, H, DEV, 0.2)
+    cam = tr.Camera(T(g["in_viewmat"]), T(g["in_K"]), W, H)
+    out = rast.forward(cam, T(g["in_bg"]))
+    st = rast.state()
+    for k in ("radii", "tiles_per_gauss", "flatten_ids"):
+        assert np.array_equal(st[k].cpu().numpy(), g[k]), k
+    assert np.array_equal(st["tile_offsets"].cpu().numpy()[:-1], g["tile_offsets"].reshape(-1))
+    vis = g["visible"]
+    assert np.array_equal(st["means2d"].cpu().numpy()[vis].view(np.uint32), g["means2d"][vis].view(np.uint32))
+    diff = np.abs(out.image.cpu().numpy() - g["render"]).max(-1)
+    assert (diff > 1e-4).sum() <= 2 and np.quantile(diff, 0.999) < 1e-4
+    loss, v_render = lossfn(out.image, T(g["in_target"]))
+    assert np.allclose(loss.cpu().numpy()[:3], g["loss"], atol=1e-5)
+    rast.backward(T(g["v_render"]), grads, T(g["in_bg"]))
+    for k in NAMES:
+        assert rel_l2(grads.tensor(k).cpu().numpy(), g[f"grad_{k}"]) < 1e-3, k
+    # distorted camera, RGB + expected depth
+    d = g["in_dist"]
+    rast2 = tr.Rasterizer(model, W, H, deg, render_mode=tr.RENDER_RGB_ED)
+    cam2 = tr.Camera(T(g["in_viewmat"]), T(g["in_K"]), W, H, radial=T(d[:6]), tangential=T(d[6:8]))
+    out2 = rast2.forward(cam2, T(np.append(g["in_bg"], 0).astype(np.float32)))
+    st2 = rast2.state()
+    assert np.array_equal(st2["radii"].cpu().numpy(), g["dist_radii"]) and np.array_equal(st2["flatten_ids"].cpu().numpy(), g["dist_flatten_ids"])
+    assert np.quantile(np.abs(out2.render.cpu().numpy()[..., :3] - g["dist_render"][..., :3]), 0.999) < 1e-4
+    assert np.quantile(np.abs(out2.depth.cpu().numpy() - g["dist_depth"]), 0.999) < 1e-3
+
+
+def test_relocation_and_adam_match_golden(pkg, g):
+    st = pkg.strategy
+    no, ns = pkg.ops.relocation(T(g["in_reloc_opacity"]), T(g["in_reloc_scale"]), T(g["in_reloc_ratios"]), T(st.binoms_table(51)), 51)
+    assert np.allclose(no.cpu().numpy(), g["reloc_opacity"], rtol=2e-5) and np.allclose(ns.cpu().numpy(), g["reloc_scale"], rtol=2e-5)
+    p, m, v = T(g["in_adam_p"]), T(g["in_adam_m"]), T(g["in_adam_v"])
+    bc1, bc2 = 1.0 - 0.9 ** 5, np.sqrt(1.0 - 0.999 ** 5)
+    pkg.ops.adam_step_wrapper(p, m, v, T(g["in_adam_g"]), 1e-3, 0.9, 0.999, 1e-15, float(1.0 / bc1), float(1.0 / bc2))
+    assert np.allclose(p.cpu().numpy(), g["adam_p"], rtol=1e-5, atol=1e-7)
+    assert np.allclose(m.cpu().numpy(), g["adam_m"], rtol=1e-6) and np.allclose(v.cpu().numpy(), g["adam_v"], rtol=1e-6)
