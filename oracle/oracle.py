@@ -29,11 +29,12 @@ _SRC = _HERE / "lfs_oracle.cpp"
 
 def build(force: bool = False) -> Path:
     """Compile the oracle with gcc (IEEE float32, no contraction, OpenMP)."""
-    if force or not _SO.exists() or _SO.stat().st_mtime < _SRC.stat().st_mtime:
+    srcs = [_SRC, _SRC.with_name("lfs_oracle_ewa.cpp")]
+    if force or not _SO.exists() or _SO.stat().st_mtime < max(s.stat().st_mtime for s in srcs):
         _SO.parent.mkdir(exist_ok=True)
         subprocess.check_call(
             ["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC",
-             "-o", str(_SO), str(_SRC)])
+             "-o", str(_SO)] + [str(s) for s in srcs])
     return _SO
 
 
@@ -49,6 +50,7 @@ def lib():
         _lib.orc_rasterize_bwd_ch.restype = C.c_int64
         _lib.orc_photometric_loss.restype = C.c_float
         _lib.orc_num_threads.restype = C.c_int
+        _lib.orc_ewa_lists.restype = C.c_int64
     return _lib
 
 
@@ -395,3 +397,66 @@ def render_bwd(params, fwd, viewmat, K, W, H, sh_degree, v_render, v_alpha=None,
     return dict(means=v_means, sh0=np.ascontiguousarray(v_sh[:, :1]), shN=np.ascontiguousarray(v_sh[:, 1:]),
                 scaling_raw=g_scaling, rotation_raw=g_rotation, opacity_raw=g_opacity,
                 v_colors=v_colors, v_opacities=v_opac, v_quats=v_quats, v_scales=v_scales, n_pairs_bwd=npairs)
+
+
+# ------------------------------------------------------------------ EWA (default, non --gut) rasterizer
+def ewa_forward(params, w2c, cam_position, W, H, fx, fy, cx, cy, active_sh_bases, background=None, near=0.01, far=1e10):
+    """fast_rasterize (src/training/rasterization/fast_rasterizer.cpp:13-71) for one camera on raw SplatData parameters:
+    preprocess -> lists -> blend. Returns image [3,H,W] (with background), alpha [H,W] and the intermediate state."""
+    means = _f32(params["means"])
+    N = means.shape[0]
+    sh0, shN = _f32(params["sh0"]).reshape(N, 3), _f32(params["shN"])
+    total_rest = shN.shape[1] if shN.ndim == 3 else 0
+    n_touched = np.zeros(N, np.int32)
+    bounds = np.zeros((N, 4), np.int32)
+    mean2d = np.zeros((N, 2), np.float32)
+    conic_opacity = np.zeros((N, 4), np.float32)
+    color = np.zeros((N, 3), np.float32)
+    depth = np.zeros(N, np.float32)
+    w2c, cam_position = _f32(w2c), _f32(cam_position)
+    f = lambda v: C.c_float(float(v))
+    lib().orc_ewa_preprocess(i32(N), _p(means), _p(_f32(params["scaling_raw"])), _p(_f32(params["rotation_raw"])),
+                             _p(_f32(params["opacity_raw"]).reshape(-1)), _p(sh0), _p(shN), _p(w2c), _p(cam_position),
+                             i32(active_sh_bases), i32(total_rest), i32(W), i32(H), f(fx), f(fy), f(cx), f(cy), f(near), f(far),
+                             _p(n_touched), _p(bounds), _p(mean2d), _p(conic_opacity), _p(color), _p(depth))
+    gw, gh = (W + 15) // 16, (H + 15) // 16
+    ids = np.zeros(max(int(n_touched.sum()), 1), np.int32)
+    offs = np.zeros(gw * gh + 1, np.int32)
+    n = lib().orc_ewa_lists(i32(N), _p(n_touched), _p(bounds), _p(mean2d), _p(conic_opacity), _p(depth), i32(W), i32(H), _p(ids), _p(offs))
+    ids = ids[:n]
+    image = np.zeros((3, H, W), np.float32)
+    alpha = np.zeros((H, W), np.float32)
+    n_contrib = np.zeros((H, W), np.int32)
+    bg = _f32(background)
+    lib().orc_ewa_blend_fwd(i32(W), i32(H), _p(ids if n else np.zeros(1, np.int32)), _p(offs), _p(mean2d), _p(conic_opacity), _p(color),
+                            _p(bg), _p(image), _p(alpha), _p(n_contrib))
+    return dict(image=image, alpha=alpha, n_contrib=n_contrib, n_touched=n_touched, bounds=bounds, mean2d=mean2d,
+                conic_opacity=conic_opacity, color=color, depth=depth, instance_ids=ids, tile_offsets=offs, background=bg,
+                cam=(w2c, cam_position, W, H, fx, fy, cx, cy, active_sh_bases, total_rest))
+
+
+def ewa_backward(params, fwd, grad_image, grad_alpha=None, densification_info=None):
+    """FastGSRasterize::backward (fast_rasterizer_autograd.cpp:88-165) incl. the background term of fast_rasterize;
+    grad_image [3,H,W] is w.r.t. the final image. Returns gradients w.r.t. the six raw tensors; densification_info
+    [2,N] is updated in place when given."""
+    w2c, cam_position, W, H, fx, fy, cx, cy, active, total_rest = fwd["cam"]
+    means = _f32(params["means"])
+    N = means.shape[0]
+    gm2, gcon, gop, gcol = (np.zeros((N, 2), np.float32), np.zeros((N, 3), np.float32), np.zeros(N, np.float32),
+                            np.zeros((N, 3), np.float32))
+    ids = fwd["instance_ids"] if fwd["instance_ids"].size else np.zeros(1, np.int32)
+    lib().orc_ewa_blend_bwd(i32(N), i32(W), i32(H), _p(ids), _p(fwd["tile_offsets"]), _p(fwd["mean2d"]), _p(fwd["conic_opacity"]),
+                            _p(fwd["color"]), _p(fwd["background"]), _p(fwd["alpha"]), _p(fwd["n_contrib"]), _p(_f32(grad_image)),
+                            _p(_f32(grad_alpha)), _p(gm2), _p(gcon), _p(gop), _p(gcol))
+    shN = _f32(params["shN"])
+    g_means, g_scales, g_rot = np.zeros((N, 3), np.float32), np.zeros((N, 3), np.float32), np.zeros((N, 4), np.float32)
+    g_sh0, g_shN = np.zeros((N, 1, 3), np.float32), np.zeros_like(shN)
+    f = lambda v: C.c_float(float(v))
+    lib().orc_ewa_preprocess_bwd(i32(N), _p(means), _p(_f32(params["scaling_raw"])), _p(_f32(params["rotation_raw"])), _p(shN),
+                                 _p(w2c), _p(cam_position), _p(fwd["n_touched"]), _p(gm2), _p(gcon), _p(gcol), i32(active),
+                                 i32(total_rest), i32(W), i32(H), f(fx), f(fy), f(cx), f(cy), _p(g_means), _p(g_scales), _p(g_rot),
+                                 _p(g_sh0), _p(g_shN), _p(densification_info))
+    vis = fwd["n_touched"] > 0
+    gop = np.where(vis, gop, 0).astype(np.float32)
+    return dict(means=g_means, sh0=g_sh0, shN=g_shN, scaling_raw=g_scales, rotation_raw=g_rot, opacity_raw=gop.reshape(N, 1),
+                grad_mean2d=gm2, grad_conic=gcon, grad_color=gcol)

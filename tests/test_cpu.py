@@ -381,3 +381,78 @@ def test_oracle_reproduces_golden_step(orc):
     p, m, v = g["in_adam_p"].copy(), g["in_adam_m"].copy(), g["in_adam_v"].copy()
     orc.adam_step(p, m, v, g["in_adam_g"], 1e-3, 0.9, 0.999, 1e-15, 5)
     assert np.allclose(p, g["adam_p"], rtol=1e-6) and np.array_equal(m, g["adam_m"]) and np.array_equal(v, g["adam_v"])
+
+
+def _ewa_scene(synth, n, W, H, deg, seed, fx):
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=seed, fx=fx)
+    return P, vm, K
+
+
+def test_oracle_ewa_analytic_single_gaussian(orc):
+    """Pins the EWA restatement (src/training/fastgs/rasterization/include/kernels_forward.cuh:19-192, :336-459) with a
+    closed form: an isotropic Gaussian on the optical axis projects to a circular 2-D Gaussian with variance
+    (f s / z)^2 + 0.3, and a pixel's alpha is opacity * exp(-r^2 / (2 var))."""
+    W = H = 64
+    f_, z, s, op_raw = 50.0, 4.0, 0.2, 1.5
+    P = dict(means=np.array([[0, 0, 0]], np.float32), sh0=np.array([[[0.7, -0.2, 3.0]]], np.float32), shN=np.zeros((1, 0, 3), np.float32),
+             scaling_raw=np.full((1, 3), np.log(s), np.float32), rotation_raw=np.array([[0.3, -0.5, 0.2, 0.7]], np.float32),
+             opacity_raw=np.array([[op_raw]], np.float32))
+    w2c = np.eye(4, dtype=np.float32); w2c[2, 3] = z
+    out = orc.ewa_forward(P, w2c, np.array([0, 0, -z], np.float32), W, H, f_, f_, 32.0, 32.0, 1)
+    var = (f_ * s / z) ** 2 + 0.3
+    op = 1 / (1 + np.exp(-op_raw))
+    assert np.allclose(out["mean2d"][0], [32.0, 32.0]) and np.allclose(out["conic_opacity"][0], [1 / var, 0, 1 / var, op], rtol=1e-5, atol=1e-7)
+    ys, xs = np.mgrid[0:H, 0:W] + 0.5
+    r2 = (xs - 32.0) ** 2 + (ys - 32.0) ** 2
+    a = np.minimum(op * np.exp(-r2 / (2 * var)), 0.999)
+    a[a < 1 / 255] = 0
+    assert np.abs(out["alpha"] - a).max() < 1e-5
+    col = np.maximum(0.5 + 0.28209479177387814 * P["sh0"][0, 0], 0)
+    assert np.abs(out["image"] - col[:, None, None] * a[None]).max() < 1e-5
+    # bounds: the tiles reached by sqrt(2 ln(255 op)) standard deviations, and exactly those are in the lists
+    ext = np.sqrt(2 * np.log(255 * op)) * np.sqrt(var) - 0.5
+    assert list(out["bounds"][0]) == [int(np.floor((32 - ext) / 16)), int(np.ceil((32 + ext) / 16))] * 2
+    assert out["n_touched"][0] == out["instance_ids"].size == 4
+
+
+def test_oracle_ewa_gradients_finite_difference(orc, synth):
+    """Backward of the EWA chain (blend, conic inverse, J W Sigma W^T J^T, quaternion / scale / sigmoid, SH incl. the
+    view-direction term) against central differences of the oracle's own forward."""
+    W, H, deg = 48, 40, 2
+    P, vm, K = _ewa_scene(synth, 50, W, H, deg, 4, 60.0)
+    P["scaling_raw"] += 1.4
+    campos = orc.campos(vm)
+    bg = np.array([0.3, 0.1, 0.2], np.float32)
+    rng = np.random.default_rng(1)
+    wi = rng.normal(size=(3, H, W)).astype(np.float32)
+    wa = rng.normal(size=(H, W)).astype(np.float32)
+
+    def fwd(Q):
+        f = orc.ewa_forward(Q, vm, campos, W, H, K[0, 0], K[1, 1], K[0, 2], K[1, 2], (deg + 1) ** 2, background=bg)
+        return float((f["image"].astype(np.float64) * wi).sum() + (f["alpha"].astype(np.float64) * wa).sum()), f
+
+    _, f = fwd(P)
+    dens = np.zeros((2, 50), np.float32)
+    bwd = orc.ewa_backward(P, f, wi, wa, dens)
+    vis = f["n_touched"] > 0
+    assert np.array_equal(dens[0], vis.astype(np.float32)) and (dens[1][vis] > 0).all()
+    assert np.allclose(dens[1], np.hypot(bwd["grad_mean2d"][:, 0] * W / 2, bwd["grad_mean2d"][:, 1] * H / 2) * vis, rtol=1e-5)
+    # the forward has jumps (1/255 alpha cut, tile membership), so a single step size can straddle one: a term counts
+    # as confirmed when any of three step sizes reproduces it to 4 % (most agree to 1e-4)
+    checked = 0
+    for name in ("means", "scaling_raw", "rotation_raw", "opacity_raw", "sh0", "shN"):
+        gflat = bwd[name].reshape(-1)
+        for idx in np.argsort(-np.abs(gflat))[:6]:
+            if abs(gflat[idx]) < 1e-6:
+                continue
+            errs = []
+            for eps in (1e-2, 3e-3, 1e-3):
+                vals = []
+                for sgn in (+1, -1):
+                    Q = {k: v.copy() for k, v in P.items()}
+                    Q[name].reshape(-1)[idx] += sgn * eps
+                    vals.append(fwd(Q)[0])
+                errs.append(abs((vals[0] - vals[1]) / (2 * eps) - gflat[idx]))
+            assert min(errs) < 0.04 * abs(gflat[idx]) + 1e-3, (name, idx, errs, gflat[idx])
+            checked += 1
+    assert checked >= 30
