@@ -367,6 +367,55 @@ int lfs_mcmc_apply(int N, int sh_coeffs, int n_sampled, const int64_t* sampled, 
                    const lfs_splats* params, const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq,
                    void* stream);
 
+/* ---- EWA rasterizer: the default (non --gut) training path ------------------------------- */
+
+/* FastGSSettings (src/training/fastgs/rasterization/include/rasterization_api.h:14-25) plus sizes. */
+typedef struct lfs_ewa_config {
+    int N;                 /* Gaussians */
+    int sh_coeffs;         /* K = SH bases stored per Gaussian (1 + shN rows) */
+    int active_sh_bases;   /* (active degree + 1)^2: 1, 4, 9 or 16 */
+    int image_width, image_height;
+    float focal_x, focal_y, center_x, center_y;
+    float near_plane, far_plane;    /* fast_rasterizer.cpp:33-34 uses 0.01 and 1e10 */
+    int64_t instance_capacity;      /* room for (Gaussian, tile) instances in the workspace */
+} lfs_ewa_config;
+
+size_t lfs_ewa_workspace_bytes(const lfs_ewa_config* cfg);
+
+/* fast_rasterize (src/training/rasterization/fast_rasterizer.cpp:13-71) = FastGSRasterize::forward
+ * (fast_rasterizer_autograd.cpp:8-86 -> fastgs/rasterization/src/forward.cu:17-199) plus the background blend, on the
+ * raw SplatData tensors. w2c [4,4] row-major, cam_position [3], background [3] or NULL are device pointers.
+ * Outputs: image [3,H,W] = blend + (1 - alpha) background, alpha [1,H,W]. status_dev (device int32[4], may be
+ * NULL): [0] capacity overflow flag (nothing is drawn), [1] n_instances, [2] n_visible. Unlike the reference there
+ * is no host synchronisation: counts stay on the device and the lists live in the caller's workspace.
+ * exp / log of the per-Gaussian stage are evaluated in double and rounded once (the reference calls expf / logf),
+ * and equal depths are ordered by Gaussian index (the reference's order there depends on atomic slot order). */
+int lfs_ewa_forward(const lfs_ewa_config* cfg, const lfs_splats* params, const float* w2c, const float* cam_position,
+                    const float* background, float* image, float* alpha, int32_t* status_dev,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* FastGSRasterize::backward (fast_rasterizer_autograd.cpp:88-165 -> fastgs/rasterization/src/backward.cu:12-116)
+ * for the camera whose forward state is in the workspace; call once per lfs_ewa_forward. grad_image [3,H,W] is
+ * the gradient of the FINAL image (the background term is folded in, pass the same background), grad_alpha
+ * [1,H,W] or NULL. grads: the six raw-parameter gradients, overwritten (all N rows) or added to.
+ * densification_info (device [2,N] or NULL): row 0 += 1 and row 1 += |d mean2d * (W/2, H/2)| for every Gaussian
+ * that reached a tile (kernels_backward.cuh:228-232). The camera-pose gradient (grad_w2c) is not produced. */
+int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const float* w2c, const float* cam_position,
+                     const float* background, const float* alpha, const float* grad_image, const float* grad_alpha,
+                     const lfs_splats* grads, int accumulate, float* densification_info,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device pointers into a workspace that holds a finished lfs_ewa_forward (tests, inspection). */
+typedef struct lfs_ewa_view {
+    const int32_t* n_touched;     /* [N] tiles reached per Gaussian (0 = culled) */
+    const uint16_t* bounds;       /* [N,4] x_min, x_max, y_min, y_max in tiles */
+    const float* records;         /* [N,12] mean2d 2, conic 3 (xx, xy at [2..3], yy at [4]), opacity, rgb (clamped), mask, threshold */
+    const uint32_t* instance_ids; /* [n_instances] */
+    const int32_t* tile_offsets;  /* [tiles + 1] */
+    const int32_t* n_contrib;     /* [H,W] */
+} lfs_ewa_view;
+int lfs_ewa_workspace_view(const lfs_ewa_config* cfg, void* workspace, size_t workspace_bytes, lfs_ewa_view* out);
+
 /* ---- PLY export / import rows -------------------------------------------------------------- */
 
 /* The vertex rows of SplatData::save_ply (src/core/splat_data.cpp:402-418 attribute names, :483-503

@@ -35,6 +35,16 @@ class RenderConfig(C.Structure):
                 ("tangential_coeffs", C.c_void_p), ("thin_prism_coeffs", C.c_void_p)]
 
 
+class EwaConfig(C.Structure):
+    _fields_ = [("N", C.c_int), ("sh_coeffs", C.c_int), ("active_sh_bases", C.c_int), ("image_width", C.c_int),
+                ("image_height", C.c_int), ("focal_x", C.c_float), ("focal_y", C.c_float), ("center_x", C.c_float),
+                ("center_y", C.c_float), ("near_plane", C.c_float), ("far_plane", C.c_float), ("instance_capacity", C.c_int64)]
+
+
+class EwaView(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("n_touched", "bounds", "records", "instance_ids", "tile_offsets", "n_contrib")]
+
+
 class RenderView(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("radii", "means2d", "depths", "tiles_per_gauss", "tile_offsets",
                                           "flatten_ids", "last_ids", "records")]
@@ -74,6 +84,9 @@ _SIGNATURES = {
     "lfs_relocation": [i32, vp, vp, vp, vp, i32, vp, vp, vp],
     "lfs_add_noise": [i32, vp, vp, vp, vp, vp, f32, vp],
     "lfs_quats_to_rotmats": [i32, vp, vp, vp],
+    "lfs_ewa_forward": [C.POINTER(EwaConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, sz, vp],
+    "lfs_ewa_backward": [C.POINTER(EwaConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, C.POINTER(Splats), i32, vp, vp, sz, vp],
+    "lfs_ewa_workspace_view": [C.POINTER(EwaConfig), vp, sz, C.POINTER(EwaView)],
     "lfs_ply_pack_rows": [i32, i32, C.POINTER(Splats), vp, vp],
     "lfs_ply_unpack_rows": [i32, i32, vp, C.POINTER(Splats), vp],
     "lfs_render_forward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, sz, vp],
@@ -96,6 +109,7 @@ _SIZE_FUNCS = {
     "lfs_intersect_tile_workspace_bytes": [i32, i32, i64],
     "lfs_rasterize_workspace_bytes": [i32],
     "lfs_render_workspace_bytes": [C.POINTER(RenderConfig)],
+    "lfs_ewa_workspace_bytes": [C.POINTER(EwaConfig)],
     "lfs_photometric_loss_workspace_bytes": [i32, i32],
     "lfs_mcmc_workspace_bytes": [i32],
 }

@@ -18,6 +18,8 @@ OBJ = HERE / "build"
 SOURCES = [
     ("projection.cu", ["--fmad=false"]),
     ("sort.cu", ["--fmad=false"]),
+    ("ewa.cu", ["--fmad=false"]),
+    ("ewa_raster.cu", []),
     ("raster.cu", []),
     ("loss.cu", []),
     ("elementwise.cu", []),

@@ -7,6 +7,7 @@
 #include "loss.cuh"
 #include "projection.cuh"
 #include "raster.cuh"
+#include "ewa.cuh"
 #include "sort.cuh"
 
 #define LFS_STR2(x) #x
@@ -92,6 +93,60 @@ RenderWs carve_render(const lfs_render_config& cfg, void* base) {
     w.scratch = carve_scratch(c);
     w.bytes = c.total();
     return w;
+}
+
+// ---- EWA workspace ----------------------------------------------------------------------------
+struct EwaWs {
+    int32_t* counters;  // [0] overflow, [1] n_instances, [2] n_visible
+    int32_t *n_touched, *offs, *tile_offsets, *n_contrib;
+    ushort4* bounds;
+    float4* records;
+    float* accum;
+    uint32_t *gkeys[2], *gvals[2], *tkeys[2], *tvals[2];
+    SortScratch scratch;
+    size_t bytes;
+};
+
+EwaWs carve_ewa(const lfs_ewa_config& cfg, void* base) {
+    Carver c(base);
+    EwaWs w;
+    const size_t N = (size_t)cfg.N, cap = (size_t)cfg.instance_capacity;
+    const int tw = (cfg.image_width + 15) / 16, th = (cfg.image_height + 15) / 16;
+    w.counters = c.take<int32_t>(16);
+    w.n_touched = c.take<int32_t>(N);
+    w.offs = c.take<int32_t>(N);
+    w.bounds = c.take<ushort4>(N);
+    w.records = c.take<float4>(N * 3);
+    w.accum = c.take<float>(N * 12);
+    for (int k = 0; k < 2; ++k) { w.gkeys[k] = c.take<uint32_t>(N); w.gvals[k] = c.take<uint32_t>(N); }
+    for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
+    w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
+    w.n_contrib = c.take<int32_t>((size_t)cfg.image_width * cfg.image_height);
+    w.scratch = carve_scratch(c);
+    w.bytes = c.total();
+    return w;
+}
+
+int check_ewa_cfg(const lfs_ewa_config* cfg) {
+    LFS_REQUIRE(cfg != nullptr, "null config");
+    LFS_REQUIRE(cfg->N >= 0 && cfg->image_width > 0 && cfg->image_height > 0, "bad sizes");
+    LFS_REQUIRE(cfg->image_width <= 65535 * 16 && cfg->image_height <= 65535 * 16, "image too large");
+    LFS_REQUIRE(cfg->sh_coeffs >= 1 && cfg->active_sh_bases >= 1 && cfg->active_sh_bases <= 16 && cfg->active_sh_bases <= cfg->sh_coeffs,
+                "active_sh_bases must be in [1, min(16, sh_coeffs)]");
+    LFS_REQUIRE(cfg->focal_x != 0.f && cfg->focal_y != 0.f, "zero focal length");
+    LFS_REQUIRE(cfg->instance_capacity >= 0 && cfg->instance_capacity < ((int64_t)1 << 31), "instance_capacity out of range");
+    return LFS_OK;
+}
+
+EwaCamera ewa_camera(const lfs_ewa_config& cfg, const float* w2c, const float* campos) {
+    EwaCamera cam;
+    cam.w2c = w2c; cam.campos = campos;
+    cam.fx = cfg.focal_x; cam.fy = cfg.focal_y; cam.cx = cfg.center_x; cam.cy = cfg.center_y;
+    cam.near_plane = cfg.near_plane; cam.far_plane = cfg.far_plane;
+    cam.W = cfg.image_width; cam.H = cfg.image_height;
+    cam.tw = (cfg.image_width + 15) / 16; cam.th = (cfg.image_height + 15) / 16;
+    cam.active_sh_bases = cfg.active_sh_bases; cam.total_rest = cfg.sh_coeffs - 1;
+    return cam;
 }
 
 int check_cfg(const lfs_render_config* cfg) {
@@ -486,6 +541,82 @@ int lfs_quats_to_rotmats(int n, const float* quats, float* rotmats, void* stream
     LFS_REQUIRE(quats && rotmats, "null pointer");
     LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
     return launch_quats_to_rotmats(n, quats, rotmats, S(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+size_t lfs_ewa_workspace_bytes(const lfs_ewa_config* cfg) {
+    if (check_ewa_cfg(cfg) != LFS_OK) return 0;
+    return carve_ewa(*cfg, nullptr).bytes;
+}
+
+int lfs_ewa_forward(const lfs_ewa_config* cfg, const lfs_splats* params, const float* w2c, const float* cam_position,
+                    const float* background, float* image, float* alpha, int32_t* status_dev, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    int rc = check_ewa_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && w2c && cam_position && image && alpha && workspace, "null pointer");
+    LFS_REQUIRE(aligned16(params->rotation_raw), "rotation_raw must be 16-byte aligned");
+    EwaWs w = carve_ewa(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_ewa_forward: workspace too small (%zu < %zu)", workspace_bytes, w.bytes); return LFS_ECAPACITY; }
+    cudaStream_t st = S(stream);
+    const EwaCamera cam = ewa_camera(*cfg, w2c, cam_position);
+    cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
+    rc = launch_ewa_preprocess(cfg->N, *params, cam, w.n_touched, w.bounds, w.records, w.gkeys[0], w.gvals[0],
+                               reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
+    if (rc != LFS_OK) return rc;
+    TileListArgs a{};
+    a.C = 1; a.N = cfg->N; a.tw = cam.tw; a.th = cam.th; a.tile_size = 16; a.sort = 1; a.keys_ready = 1;
+    a.tiles = w.n_touched;
+    for (int k = 0; k < 2; ++k) { a.gkeys[k] = w.gkeys[k]; a.gvals[k] = w.gvals[k]; a.tkeys[k] = w.tkeys[k]; a.tvals[k] = w.tvals[k]; }
+    a.offs = w.offs; a.n_isects_dev = w.counters + 1; a.capacity = cfg->instance_capacity; a.overflow = w.counters + 0;
+    int sel = 0;
+    a.sel_out = &sel;
+    a.tile_offsets = w.tile_offsets; a.scratch = w.scratch;
+    a.ewa_bounds = w.bounds; a.ewa_records = w.records;
+    rc = build_tile_lists(a, st);
+    if (rc != LFS_OK) return rc;
+    EwaBlendArgs b{w.records, w.tvals[sel], w.tile_offsets, w.counters + 0, background, cfg->image_width, cfg->image_height, cam.tw, cam.th};
+    rc = launch_ewa_blend_fwd(b, image, alpha, w.n_contrib, st);
+    if (rc != LFS_OK) return rc;
+    if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    return check_launch("lfs_ewa_forward");
+}
+
+int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const float* w2c, const float* cam_position,
+                     const float* background, const float* alpha, const float* grad_image, const float* grad_alpha,
+                     const lfs_splats* grads, int accumulate, float* densification_info, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+    int rc = check_ewa_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && w2c && cam_position && alpha && grad_image && grads && workspace, "null pointer");
+    LFS_REQUIRE(aligned16(params->rotation_raw) && aligned16(grads->rotation_raw), "rotation_raw tensors must be 16-byte aligned");
+    EwaWs w = carve_ewa(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_ewa_backward: workspace too small"); return LFS_ECAPACITY; }
+    cudaStream_t st = S(stream);
+    const EwaCamera cam = ewa_camera(*cfg, w2c, cam_position);
+    const int sel = sorted_sel((int)(bit_width_u32((uint32_t)cam.tw * cam.th) + 1));  // tile bits + one camera bit
+    EwaBlendArgs b{w.records, w.tvals[sel], w.tile_offsets, w.counters + 0, background, cfg->image_width, cfg->image_height, cam.tw, cam.th};
+    rc = launch_ewa_blend_bwd(b, alpha, w.n_contrib, grad_image, grad_alpha, w.accum, st);
+    if (rc != LFS_OK) return rc;
+    return launch_ewa_epilogue(cfg->N, cfg->sh_coeffs, *params, cam, w.n_touched, w.records, w.accum, *grads, accumulate,
+                               densification_info, st);
+}
+
+int lfs_ewa_workspace_view(const lfs_ewa_config* cfg, void* workspace, size_t workspace_bytes, lfs_ewa_view* out) {
+    int rc = check_ewa_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(workspace && out, "null pointer");
+    EwaWs w = carve_ewa(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_ewa_workspace_view: workspace too small"); return LFS_ECAPACITY; }
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
+    out->n_touched = w.n_touched;
+    out->bounds = reinterpret_cast<const uint16_t*>(w.bounds);
+    out->records = reinterpret_cast<const float*>(w.records);
+    out->instance_ids = w.tvals[sel];
+    out->tile_offsets = w.tile_offsets;
+    out->n_contrib = w.n_contrib;
+    return LFS_OK;
 }
 
 int lfs_ply_pack_rows(int N, int sh_coeffs, const lfs_splats* params, float* rows, void* stream) {

@@ -11,6 +11,7 @@
 // All passes are HBM-bound integer work; nothing here is shaped for tensor cores.
 #include "gsmath.cuh"
 #include "sort.cuh"
+#include "ewa_common.cuh"
 
 namespace lfs {
 
@@ -237,6 +238,34 @@ __global__ void __launch_bounds__(kThreads) emit_instances_kernel(
     }
 }
 
+// EWA path: one instance per tile of the bounds rectangle that the ellipse reaches (create_instances_cu,
+// src/training/fastgs/rasterization/include/kernels_forward.cuh:205-309), in row-major tile order.
+__global__ void __launch_bounds__(kThreads) ewa_emit_instances_kernel(
+    int64_t total, const uint32_t* __restrict__ order, const int32_t* __restrict__ tiles, const int32_t* __restrict__ offs,
+    const ushort4* __restrict__ ewa_bounds, const float4* __restrict__ rec, uint32_t tw, int64_t capacity,
+    uint32_t* __restrict__ tkeys, uint32_t* __restrict__ tvals, int32_t* __restrict__ overflow) {
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < total; r += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t idx = order ? order[r] : (uint32_t)r;
+        const int nt = tiles[idx];
+        if (nt <= 0) continue;
+        const int64_t base = offs[r];
+        if (base + nt > capacity) {
+            if (overflow) atomicExch(overflow, 1);
+            continue;
+        }
+        const ushort4 b = ewa_bounds[idx];
+        const float4 r0 = rec[(size_t)idx * 3], r1 = rec[(size_t)idx * 3 + 1], r2 = rec[(size_t)idx * 3 + 2];
+        int64_t cur = base;
+        for (uint32_t ty = b.z; ty < b.w; ++ty)
+            for (uint32_t tx = b.x; tx < b.y; ++tx)
+                if (ewa_tile_contributes(r0.x - 0.5f, r0.y - 0.5f, r0.z, r0.w, r1.x, tx, ty, r2.z) && cur < base + nt) {
+                    tkeys[cur] = ty * tw + tx;
+                    tvals[cur] = idx;
+                    ++cur;
+                }
+    }
+}
+
 // offsets[t] = first sorted instance whose (camera, tile) id >= t, for t in [0, n_ids]; entry n_ids
 // (one past the last tile) holds the instance count. Keys hold (cid << tile_n_bits) | tile.
 // When the overflow flag is set the instance list is incomplete (some slots were never written), so
@@ -404,6 +433,11 @@ int build_tile_lists(const TileListArgs& a, cudaStream_t st) {
     if (rc != LFS_OK) return rc;
     if (total > 0) {
         LFS_TIMED("emit_instances", st);
+        if (a.ewa_bounds)
+            ewa_emit_instances_kernel<<<grid_for(total, 256), 256, 0, st>>>(total, order, a.tiles, a.offs, a.ewa_bounds, a.ewa_records,
+                                                                            (uint32_t)a.tw, a.capacity, a.tkeys[0], a.tvals[0],
+                                                                            a.overflow);
+        else
         emit_instances_kernel<<<grid_for(total, 256), 256, 0, st>>>(total, a.N, order, a.tiles, a.offs, a.means2d, a.radii,
                                                                     (float)a.tile_size, (uint32_t)a.tw, (uint32_t)a.th,
                                                                     tile_n_bits, a.capacity, a.tkeys[0], a.tvals[0],

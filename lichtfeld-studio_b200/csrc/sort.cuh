@@ -25,6 +25,10 @@ struct TileListArgs {
     int* sel_out;          // host: which of tkeys/tvals holds the result
     int32_t* tile_offsets; // [C*tw*th + 1] or null
     SortScratch scratch;
+    // EWA path (C = 1): when set, a Gaussian's instances are the tiles of its bounds rectangle that pass the exact
+    // ellipse test (`tiles` holds that count); means2d / radii are unused
+    const ushort4* ewa_bounds = nullptr;  // [N] (x_min, x_max, y_min, y_max) in tiles
+    const float4* ewa_records = nullptr;  // [N*3], see ewa_common.cuh
 };
 
 int build_tile_lists(const TileListArgs& a, cudaStream_t st);

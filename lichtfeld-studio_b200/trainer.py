@@ -217,6 +217,88 @@ class Rasterizer:
                     records=grab(view.records, n * 16, torch.float32).view(n, 16), n_isects=n_isects)
 
 
+class FastRasterizer:
+    """fast_rasterize() + FastGSRasterize (src/training/rasterization/fast_rasterizer.cpp:13-71,
+    fast_rasterizer_autograd.cpp): the default, non --gut path. EWA splatting with exact per-tile culling on the raw
+    SplatData tensors; owns the workspace that carries the forward state to the backward. Image output is CHW like
+    the reference's; `world_view_transform` is the camera's viewmat, `cam_position` is derived from it once per
+    camera when not given."""
+
+    def __init__(self, model: SplatData, width: int, height: int, sh_degree: int, instance_capacity: int | None = None,
+                 near_plane: float = 0.01, far_plane: float = 1e10):
+        self.model = model
+        self.W, self.H = int(width), int(height)
+        cap = int(instance_capacity) if instance_capacity is not None else max(8 * model.capacity, 1 << 20)
+        self.cfg = capi.EwaConfig(model.size, model.K, (int(sh_degree) + 1) ** 2, self.W, self.H, 0.0, 0.0, 0.0, 0.0,
+                                  float(near_plane), float(far_plane), cap)
+        cfg = capi.EwaConfig.from_buffer_copy(self.cfg)
+        cfg.N, cfg.focal_x, cfg.focal_y = model.capacity, 1.0, 1.0
+        nbytes = capi.lib().lfs_ewa_workspace_bytes(C.byref(cfg))
+        if nbytes == 0:
+            raise capi.LfsError("lfs_ewa_workspace_bytes: " + capi.lib().lfs_last_error().decode())
+        dev = model.device
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.image = torch.empty((3, self.H, self.W), dtype=torch.float32, device=dev)
+        self.alpha = torch.empty((1, self.H, self.W), dtype=torch.float32, device=dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self._cam = None
+
+    def set_sh_degree(self, d: int):
+        self.cfg.active_sh_bases = (int(d) + 1) ** 2
+
+    @staticmethod
+    def cam_position(viewmat: torch.Tensor) -> torch.Tensor:
+        """-R^T t of the world-to-camera matrix (what Camera::cam_position holds)."""
+        Rm, t = viewmat[:3, :3].double(), viewmat[:3, 3].double()
+        return (-(Rm.T @ t)).float().contiguous()
+
+    def forward(self, cam: Camera, background: torch.Tensor | None, cam_position: torch.Tensor | None = None) -> RenderOutput:
+        if cam.width != self.W or cam.height != self.H:
+            raise RuntimeError("camera size does not match the rasterizer")
+        K = cam.K
+        if not hasattr(cam, "_intrinsics"):
+            cam._intrinsics = tuple(float(v) for v in (K[0, 0], K[1, 1], K[0, 2], K[1, 2]))  # one host read per camera
+            cam._campos = self.cam_position(cam.viewmat) if cam_position is None else cam_position
+        self.cfg.N = self.model.size
+        self.cfg.focal_x, self.cfg.focal_y, self.cfg.center_x, self.cfg.center_y = cam._intrinsics
+        self._cam = cam
+        p = self.model.struct()
+        call("lfs_ewa_forward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam._campos), ptr(background), ptr(self.image),
+             ptr(self.alpha), ptr(self.status), ptr(self.ws), self.ws.numel(), _stream())
+        return RenderOutput(self.image, self.alpha, self.W, self.H, self.status)
+
+    def backward(self, grad_image: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
+                 grad_alpha: torch.Tensor | None = None, accumulate: bool = False, densification_info: torch.Tensor | None = None):
+        """grad_image [3,H,W] w.r.t. the final (background-blended) image; densification_info [2,N] is updated in place."""
+        cam = self._cam
+        p, g = self.model.struct(), grads.struct()
+        call("lfs_ewa_backward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam._campos), ptr(background), ptr(self.alpha),
+             ptr(grad_image), ptr(grad_alpha), C.byref(g), 1 if accumulate else 0, ptr(densification_info), ptr(self.ws),
+             self.ws.numel(), _stream())
+
+    def state(self) -> dict:
+        """Copies of the forward state (synchronises): per-Gaussian records, bounds, tile lists."""
+        view = capi.EwaView()
+        cfg = capi.EwaConfig.from_buffer_copy(self.cfg)
+        cfg.N = self.model.capacity
+        call("lfs_ewa_workspace_view", C.byref(cfg), ptr(self.ws), self.ws.numel(), C.byref(view))
+        torch.cuda.synchronize()
+        n, tiles = self.model.size, ((self.W + 15) // 16) * ((self.H + 15) // 16)
+        n_inst = int(self.status[1].item())
+        base = self.ws.data_ptr()
+
+        def grab(p, count, dtype):
+            nbytes = count * torch.empty(0, dtype=dtype).element_size()
+            return self.ws[p - base:p - base + nbytes].view(dtype).clone()
+
+        rec = grab(view.records, n * 12, torch.float32).view(n, 12)
+        return dict(n_touched=grab(view.n_touched, n, torch.int32), bounds=grab(view.bounds, n * 4, torch.int16).view(n, 4),
+                    mean2d=rec[:, 0:2], conic_opacity=torch.stack([rec[:, 2], rec[:, 3], rec[:, 4], rec[:, 5]], 1),
+                    color=rec[:, 6:9], instance_ids=grab(view.instance_ids, n_inst, torch.int32),
+                    tile_offsets=grab(view.tile_offsets, tiles + 1, torch.int32),
+                    n_contrib=grab(view.n_contrib, self.W * self.H, torch.int32).view(self.H, self.W), n_instances=n_inst)
+
+
 class PhotometricLoss:
     """Trainer::compute_photometric_loss and its backward in two kernels."""
 
