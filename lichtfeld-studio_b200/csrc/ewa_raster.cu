@@ -295,32 +295,58 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
 // Per-Gaussian gradient stage: from (d mean2d, d conic, sum alpha dL/dalpha, d colour) to the six raw tensors.
 // cov2d = A Sigma A^T + 0.3 I with A = J W (2x3), Sigma = R diag(exp(2 s)) R^T, conic = cov2d^-1.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) ewa_epilogue_kernel(
+// Each warp handles 32 consecutive Gaussians per iteration: their shN rows ((K-1)*3 floats each, contiguous in
+// memory) are read as one coalesced run into shared memory, every lane then works on its own row in place
+// (coefficient in, gradient out), and the 32 gradient rows leave as one coalesced run.
+__global__ void __launch_bounds__(256) ewa_epilogue_kernel(
     int N, int K, const float* __restrict__ means, const float* __restrict__ shN, const float* __restrict__ scaling_raw,
     const float* __restrict__ rotation_raw, EwaCamera cam, const int32_t* __restrict__ n_touched, const float4* __restrict__ records,
     const float* __restrict__ accum, float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN,
     float* __restrict__ g_scaling, float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate,
     float* __restrict__ densification_info) {
+    extern __shared__ float s_rows[];
     float r1[4], r2[4], r3[4], campos[3];
 #pragma unroll
     for (int k = 0; k < 4; ++k) { r1[k] = cam.w2c[k]; r2[k] = cam.w2c[4 + k]; r3[k] = cam.w2c[8 + k]; }
 #pragma unroll
     for (int k = 0; k < 3; ++k) campos[k] = cam.campos[k];
     const int rest = (K - 1) * 3;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < N; i += gridDim.x * blockDim.x) {
-        float gm[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, g0[3] = {0.f, 0.f, 0.f}, go = 0.f;
-        float* out_rest = g_shN + (size_t)i * rest;
-        const bool visible = n_touched[i] > 0;
-        if (!visible) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my = s_rows + (size_t)warp * 32 * rest;
+    const int n_chunks = (N + 31) / 32;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    const int nb = cam.active_sh_bases > 9 ? 16 : cam.active_sh_bases > 4 ? 9 : cam.active_sh_bases > 1 ? 4 : 1;
+    for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
+        const int i = chunk * 32 + lane;
+        const bool in_range = i < N;
+        const bool visible = in_range && n_touched[i] > 0;
+        const bool any_visible = __any_sync(0xffffffffu, visible);
+        const int n_rows = min(32, N - chunk * 32);
+        const int total = n_rows * rest;
+        float* dst_rows = g_shN + (size_t)chunk * 32 * rest;
+        if (!any_visible) {
+            // nothing in this chunk reached a tile: zeros (or untouched when accumulating)
             if (!accumulate) {
-                for (int k = 0; k < rest; ++k) out_rest[k] = 0.f;
+                for (int k = lane; k < total; k += 32) dst_rows[k] = 0.f;
+                if (in_range) {
 #pragma unroll
-                for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] = 0.f; g_sh0[i * 3 + k] = 0.f; g_scaling[i * 3 + k] = 0.f; }
-                reinterpret_cast<float4*>(g_rotation)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                g_opacity[i] = 0.f;
+                    for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] = 0.f; g_sh0[i * 3 + k] = 0.f; g_scaling[i * 3 + k] = 0.f; }
+                    reinterpret_cast<float4*>(g_rotation)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    g_opacity[i] = 0.f;
+                }
             }
             continue;
         }
+        if (nb > 1) {
+            const float* src_rows = shN + (size_t)chunk * 32 * rest;
+            for (int k = lane; k < total; k += 32) my[k] = src_rows[k];
+        }
+        __syncwarp();
+        float* out_rest = my + lane * rest;   // this lane's row: coefficients now, gradients afterwards
+        float gm[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, g0[3] = {0.f, 0.f, 0.f}, go = 0.f;
+        if (!visible) {
+            for (int k = 0; k < rest; ++k) out_rest[k] = 0.f;
+        } else {
         float acc[12];
         const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)i * 3;
 #pragma unroll
@@ -334,21 +360,19 @@ __global__ void __launch_bounds__(128) ewa_epilogue_kernel(
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) g0[ch] = 0.28209479177387814f * gc[ch];
         float dmc[3] = {0.f, 0.f, 0.f};
-        const int nb = cam.active_sh_bases > 9 ? 16 : cam.active_sh_bases > 4 ? 9 : cam.active_sh_bases > 1 ? 4 : 1;
         if (nb > 1) {
             const float xr = m0 - campos[0], yr = m1 - campos[1], zr = m2 - campos[2];
             const float inv = rsqrtf(xr * xr + yr * yr + zr * zr);
             const float x = xr * inv, y = yr * inv, z = zr * inv;
             const float xx = x * x, yy = y * y, zz = z * z, xy = x * y, xz = x * z, yz = y * z;
-            const float* co = shN + (size_t)i * rest;
+            const float* co = out_rest;
             float gd[3] = {0.f, 0.f, 0.f};
             // basis value B and its derivative (Dx, Dy, Dz) with respect to the unit direction, one row at a time
             auto row = [&](int k, float B, float Dx, float Dy, float Dz) {
                 const float c0 = co[(k - 1) * 3], c1 = co[(k - 1) * 3 + 1], c2 = co[(k - 1) * 3 + 2];
                 const float cgd = c0 * gc[0] + c1 * gc[1] + c2 * gc[2];
                 gd[0] += Dx * cgd; gd[1] += Dy * cgd; gd[2] += Dz * cgd;
-                if (accumulate) { out_rest[(k - 1) * 3] += B * gc[0]; out_rest[(k - 1) * 3 + 1] += B * gc[1]; out_rest[(k - 1) * 3 + 2] += B * gc[2]; }
-                else { out_rest[(k - 1) * 3] = B * gc[0]; out_rest[(k - 1) * 3 + 1] = B * gc[1]; out_rest[(k - 1) * 3 + 2] = B * gc[2]; }
+                out_rest[(k - 1) * 3] = B * gc[0]; out_rest[(k - 1) * 3 + 1] = B * gc[1]; out_rest[(k - 1) * 3 + 2] = B * gc[2];
             };
             row(1, -0.48860251190291987f * y, 0.f, -0.48860251190291987f, 0.f);
             row(2, 0.48860251190291987f * z, 0.f, 0.f, 0.48860251190291987f);
@@ -369,7 +393,7 @@ __global__ void __launch_bounds__(128) ewa_epilogue_kernel(
                 row(14, 1.4453057213202769f * z * (xx - yy), 2.8906114426405538f * xz, -2.8906114426405538f * yz, 1.4453057213202769f * xx - 1.4453057213202769f * yy);
                 row(15, 0.59004358992664352f * x * (-xx + 3.0f * yy), -1.7701307697799304f * xx + 1.7701307697799304f * yy, 3.5402615395598609f * xy, 0.f);
             }
-            if (!accumulate) for (int k = (nb - 1) * 3; k < rest; ++k) out_rest[k] = 0.f;
+            for (int k = (nb - 1) * 3; k < rest; ++k) out_rest[k] = 0.f;
             // through the normalisation: (|r|^2 I - r r^T) gd / |r|^3
             const float xxr = xr * xr, yyr = yr * yr, zzr = zr * zr, xyr = xr * yr, xzr = xr * zr, yzr = yr * zr;
             const float n2 = xxr + yyr + zzr;
@@ -377,7 +401,7 @@ __global__ void __launch_bounds__(128) ewa_epilogue_kernel(
             dmc[0] = ((yyr + zzr) * gd[0] - xyr * gd[1] - xzr * gd[2]) * s;
             dmc[1] = (-xyr * gd[0] + (xxr + zzr) * gd[1] - yzr * gd[2]) * s;
             dmc[2] = (-xzr * gd[0] - yzr * gd[1] + (xxr + yyr) * gd[2]) * s;
-        } else if (!accumulate) {
+        } else {
             for (int k = 0; k < rest; ++k) out_rest[k] = 0.f;
         }
         // ---- geometry, recomputed as in the forward
@@ -468,17 +492,27 @@ __global__ void __launch_bounds__(128) ewa_epilogue_kernel(
             const float sx = m2x * (0.5f * Wf), sy = m2y * (0.5f * Hf);
             densification_info[N + i] += sqrtf(sx * sx + sy * sy);
         }
+        }  // visible
+        __syncwarp();
         if (accumulate) {
-#pragma unroll
-            for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] += gm[k]; g_sh0[i * 3 + k] += g0[k]; g_scaling[i * 3 + k] += gs[k]; }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) g_rotation[i * 4 + k] += gq[k];
-            g_opacity[i] += go;
+            for (int k = lane; k < total; k += 32) dst_rows[k] += my[k];
         } else {
+            for (int k = lane; k < total; k += 32) dst_rows[k] = my[k];
+        }
+        __syncwarp();
+        if (in_range && (visible || !accumulate)) {
+            if (accumulate) {
 #pragma unroll
-            for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] = gm[k]; g_sh0[i * 3 + k] = g0[k]; g_scaling[i * 3 + k] = gs[k]; }
-            reinterpret_cast<float4*>(g_rotation)[i] = make_float4(gq[0], gq[1], gq[2], gq[3]);
-            g_opacity[i] = go;
+                for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] += gm[k]; g_sh0[i * 3 + k] += g0[k]; g_scaling[i * 3 + k] += gs[k]; }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) g_rotation[i * 4 + k] += gq[k];
+                g_opacity[i] += go;
+            } else {
+#pragma unroll
+                for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] = gm[k]; g_sh0[i * 3 + k] = g0[k]; g_scaling[i * 3 + k] = gs[k]; }
+                reinterpret_cast<float4*>(g_rotation)[i] = make_float4(gq[0], gq[1], gq[2], gq[3]);
+                g_opacity[i] = go;
+            }
         }
     }
 }
@@ -508,7 +542,10 @@ int launch_ewa_epilogue(int N, int K, const lfs_splats& p, const EwaCamera& cam,
                         const float* accum, const lfs_splats& g, int accumulate, float* densification_info, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("ewa_epilogue", st);
-    ewa_epilogue_kernel<<<grid_for(N, 128), 128, 0, st>>>(N, K, p.means, p.shN, p.scaling_raw, p.rotation_raw, cam, n_touched, records,
+    const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
+    if (smem > 200 * 1024) { set_error("ewa_epilogue: too many SH coefficients"); return LFS_EINVAL; }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(ewa_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ewa_epilogue_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, p.means, p.shN, p.scaling_raw, p.rotation_raw, cam, n_touched, records,
                                                           accum, g.means, g.sh0, g.shN, g.scaling_raw, g.rotation_raw, g.opacity_raw,
                                                           accumulate, densification_info);
     return check_launch("ewa_epilogue");
