@@ -137,12 +137,18 @@ __global__ void __launch_bounds__(kThreads) radix_scan_kernel(uint32_t* __restri
     if (threadIdx.x == 0) digit_totals[blockIdx.x] = (uint32_t)carry;
 }
 
+// Stable scatter of one radix pass. A CTA walks its chunk in tiles of 2048 pairs: every item gets its rank among
+// the equal digits of the tile (warp match + per-warp counters), the tile is reordered by digit in shared memory,
+// and then consecutive threads write consecutive addresses of each digit's output run, so the global stores are
+// contiguous runs instead of 4-byte scatters.
 __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out,
     uint32_t* __restrict__ vals_out, const int32_t* n_dev, int64_t n_max, int shift, uint32_t mask, int nb,
     const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_totals) {
-    __shared__ uint32_t cnt[kWarps][256];
-    __shared__ uint32_t gbase[256];
+    __shared__ uint32_t cnt[kWarps][256];   // per-warp digit counts, then per-warp start inside the tile
+    __shared__ uint32_t gbase[256];         // where the next item of digit d from this CTA goes
+    __shared__ uint32_t tstart[256];        // start of digit d inside the reordered tile
+    __shared__ uint32_t skeys[kTile], svals[kTile];
     __shared__ int sm[33];
     const int64_t n = device_count(n_dev, n_max);
     const int64_t chunk = (n + nb - 1) / nb;
@@ -156,6 +162,7 @@ __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
         gbase[threadIdx.x] = (uint32_t)digit_base + hist[(size_t)threadIdx.x * nb + blockIdx.x];
     }
     for (int64_t tile_lo = lo; tile_lo < hi; tile_lo += kTile) {
+        const int tile_n = (int)min((int64_t)kTile, hi - tile_lo);
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] = 0;
         __syncthreads();
@@ -183,15 +190,19 @@ __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
         }
         __syncthreads();
         {
-            // digit threadIdx.x: exclusive prefix over the warps, offset by the running global base
-            uint32_t run = gbase[threadIdx.x];
+            // digit threadIdx.x: exclusive prefix over the warps and the digit's total in this tile
+            uint32_t run = 0;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
                 const uint32_t c = cnt[w][threadIdx.x];
                 cnt[w][threadIdx.x] = run;
                 run += c;
             }
-            gbase[threadIdx.x] = run;
+            int total;
+            const int start = block_excl_scan((int)run, total, sm);  // start of this digit inside the tile
+            tstart[threadIdx.x] = (uint32_t)start;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] += (uint32_t)start;
         }
         __syncthreads();
 #pragma unroll
@@ -200,9 +211,29 @@ __global__ void __launch_bounds__(kThreads) radix_scatter_kernel(
             if (i < hi) {
                 const uint32_t d = (key[r] >> shift) & mask;
                 const uint32_t pos = cnt[warp][d] + rank[r];
-                keys_out[pos] = key[r];
-                vals_out[pos] = val[r];
+                skeys[pos] = key[r];
+                svals[pos] = val[r];
             }
+        }
+        __syncthreads();
+        // write out: item j of the reordered tile belongs to digit d = digit(skeys[j]) and goes to
+        // gbase[d] + (j - tstart[d]); neighbouring j of one digit are neighbouring addresses
+#pragma unroll
+        for (int r = 0; r < kItems; ++r) {
+            const int j = r * kThreads + threadIdx.x;
+            if (j < tile_n) {
+                const uint32_t k = skeys[j];
+                const uint32_t d = (k >> shift) & mask;
+                const uint32_t pos = gbase[d] + ((uint32_t)j - tstart[d]);
+                keys_out[pos] = k;
+                vals_out[pos] = svals[j];
+            }
+        }
+        __syncthreads();
+        {
+            // advance the global bases by this tile's digit totals
+            const uint32_t next = threadIdx.x + 1 < 256 ? tstart[threadIdx.x + 1] : (uint32_t)tile_n;
+            gbase[threadIdx.x] += next - tstart[threadIdx.x];
         }
         __syncthreads();
     }
