@@ -295,10 +295,10 @@ __device__ __forceinline__ float __reduce_add_sync_f32(float x) {
 template <int BATCH>
 struct BwdShared {
     Stage<BATCH> stage[2];
-    uint32_t sid[2][BATCH];
-    float sacc[BATCH * 16];
-    float sextra[BATCH];
-    int stouched[BATCH];
+    uint32_t sid[3][BATCH];      // Gaussian index per slot; three deep: batch b+1 is staged while batch b-1 is flushed
+    float sacc[2][BATCH * 16];   // per-slot sums of the batch being walked / the batch being flushed
+    float sextra[2][BATCH];
+    int stouched[2][BATCH];
 };
 
 // EXTRA: the output has 1 or 4 channels and its last one blends bounds.w (see the forward). XGRAD: also return
@@ -364,12 +364,31 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const int32_t warp_bin_final = __reduce_max_sync(0xffffffffu, bin_final);
     const int lane = threadIdx.x & 31;
 
-    for (int e = threadIdx.x; e < BATCH; e += kBlock) {
+    for (int e = threadIdx.x; e < 2 * BATCH; e += kBlock) {
 #pragma unroll
-        for (int k = 0; k < 16; ++k) sm.sacc[e * 16 + k] = 0.f;
-        sm.sextra[e] = 0.f;
-        sm.stouched[e] = 0;
+        for (int k = 0; k < 16; ++k) (&sm.sacc[0][0])[e * 16 + k] = 0.f;
+        (&sm.sextra[0][0])[e] = 0.f;
+        (&sm.stouched[0][0])[e] = 0;
     }
+    // flush the sums of batch k (four 16-byte reductions per touched Gaussian) and leave its buffers zeroed
+    auto flush = [&](int k) {
+        const int size_k = min(BATCH, range_end - k * BATCH - range_start);
+        float* acc_k = sm.sacc[k & 1];
+        for (int e = threadIdx.x; e < size_k; e += kBlock) {
+            if (sm.stouched[k & 1][e]) {
+                const uint32_t g = sm.sid[k % 3][e];
+                float4* dst = reinterpret_cast<float4*>(accum) + (size_t)g * 4;
+                float4* src = reinterpret_cast<float4*>(acc_k) + e * 4;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    atomicAdd(dst + q, src[q]);
+                    src[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                if (XGRAD) { atomicAdd(accum_extra + g, sm.sextra[k & 1][e]); sm.sextra[k & 1][e] = 0.f; }
+                sm.stouched[k & 1][e] = 0;
+            }
+        }
+    };
 
     // batches run back to front: slot e of batch b holds list position batch_end - e
     StageIds<BATCH> ids;
@@ -379,19 +398,21 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
         issue_stage(sm.stage[0], sm.sid[0], ids, records, bounds, min(BATCH, be + 1 - range_start));
         if (n_batches > 1) load_ids(ids, flatten_ids, be - BATCH, -1, min(BATCH, be - BATCH + 1 - range_start));
     }
+    // One barrier per batch: after it, batch b is in shared memory and every warp has finished walking batch b-1,
+    // so batch b+1 may be staged over b-1's records and b-1's sums may be flushed while batch b is walked.
     for (int b = 0; b < n_batches; ++b) {
         const int32_t batch_end = range_end - 1 - b * BATCH;
         const int32_t batch_size = min(BATCH, batch_end + 1 - range_start);
+        cp_async_wait<0>();
+        __syncthreads();
         if (b + 1 < n_batches) {
-            issue_stage(sm.stage[(b + 1) & 1], sm.sid[(b + 1) & 1], ids, records, bounds,
+            issue_stage(sm.stage[(b + 1) & 1], sm.sid[(b + 1) % 3], ids, records, bounds,
                         min(BATCH, batch_end - BATCH + 1 - range_start));
             if (b + 2 < n_batches)
                 load_ids(ids, flatten_ids, batch_end - 2 * BATCH, -1, min(BATCH, batch_end - 2 * BATCH + 1 - range_start));
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
+        if (b > 0) flush(b - 1);
+        float* sacc = sm.sacc[b & 1];
         const Stage<BATCH>& st = sm.stage[b & 1];
         // entries (back to front) that no pixel of this warp reaches (beyond its last contributor) or whose
         // box misses this warp's 8x4 patch are dropped up front: one ballot word per 32 entries
@@ -466,32 +487,17 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                     if (EXTRA) bufx += xval * fac;
                     if (XGRAD) {
                         const float xs = __reduce_add_sync_f32(fac * vcx);
-                        if (lane == 0) atomicAdd(&sm.sextra[t], xs);
+                        if (lane == 0) atomicAdd(&sm.sextra[b & 1][t], xs);
                     }
                 }
                 const float total = warp_reduce16(v);
-                if ((lane & 1) == 0) atomicAdd(&sm.sacc[t * 16 + (lane >> 1)], total);
-                if (lane == 0) sm.stouched[t] = 1;
+                if ((lane & 1) == 0) atomicAdd(&sacc[t * 16 + (lane >> 1)], total);
+                if (lane == 0) sm.stouched[b & 1][t] = 1;
             }
         }
-        __syncthreads();
-        // flush this batch's sums: four 16-byte reductions per touched Gaussian
-        for (int e = threadIdx.x; e < batch_size; e += kBlock) {
-            if (sm.stouched[e]) {
-                const uint32_t g = sm.sid[b & 1][e];
-                float4* dst = reinterpret_cast<float4*>(accum) + (size_t)g * 4;
-                float4* src = reinterpret_cast<float4*>(sm.sacc) + e * 4;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    atomicAdd(dst + k, src[k]);
-                    src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                if (XGRAD) { atomicAdd(accum_extra + g, sm.sextra[e]); sm.sextra[e] = 0.f; }
-                sm.stouched[e] = 0;
-            }
-        }
-        __syncthreads();  // accumulators are clean and buffer b & 1 is free before the next iteration refills it
     }
+    __syncthreads();
+    if (n_batches > 0) flush(n_batches - 1);
     cp_async_wait<0>();
 }
 
