@@ -184,9 +184,9 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
     const float* __restrict__ grad_alpha, float* __restrict__ accum) {
     constexpr int BATCH = 128;
     __shared__ float4 rec[2][BATCH * 3];
-    __shared__ uint32_t sid[2][BATCH];
-    __shared__ __align__(16) float sacc[BATCH * 12];
-    __shared__ int stouched[BATCH];
+    __shared__ uint32_t sid[3][BATCH];                  // three deep: batch b+1 is staged while batch b-1 is flushed
+    __shared__ __align__(16) float sacc_all[2][BATCH * 12];
+    __shared__ int stouched_all[2][BATCH];
     if (overflow && *overflow) return;
     const int tile = blockIdx.x;
     int i, j;
@@ -208,10 +208,10 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
     int32_t tile_last = __reduce_max_sync(0xffffffffu, my_last);
     __shared__ int32_t s_last[kBlock / 32];
     if (lane == 0) s_last[warp] = tile_last;
-    for (int e = threadIdx.x; e < BATCH; e += kBlock) {
+    for (int e = threadIdx.x; e < 2 * BATCH; e += kBlock) {
 #pragma unroll
-        for (int k = 0; k < 12; ++k) sacc[e * 12 + k] = 0.f;
-        stouched[e] = 0;
+        for (int k = 0; k < 12; ++k) (&sacc_all[0][0])[e * 12 + k] = 0.f;
+        (&stouched_all[0][0])[e] = 0;
     }
     __syncthreads();
     const int32_t warp_last = tile_last;
@@ -222,17 +222,35 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
     const int32_t top = range_start + tile_last - 1;  // list position of the first entry walked
 
     float T = T_final, ar = 0.f, ag = 0.f, ab = 0.f;
+    // flush the sums of batch k (three 16-byte reductions per touched Gaussian) and leave its buffers zeroed
+    auto flush = [&](int k) {
+        const int size_k = min(BATCH, tile_last - k * BATCH);
+        for (int e = threadIdx.x; e < size_k; e += kBlock) {
+            if (stouched_all[k & 1][e]) {
+                float4* dst = reinterpret_cast<float4*>(accum) + (size_t)sid[k % 3][e] * 3;
+                float4* src = reinterpret_cast<float4*>(sacc_all[k & 1]) + e * 3;
+#pragma unroll
+                for (int q = 0; q < 3; ++q) {
+                    atomicAdd(dst + q, src[q]);
+                    src[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                stouched_all[k & 1][e] = 0;
+            }
+        }
+    };
     if (n_batches > 0) stage_batch<BATCH>(rec[0], sid[0], records, ids, top, -1, min(BATCH, tile_last));
+    // One barrier per batch: after it, batch b is in shared memory and every warp has finished walking batch b-1,
+    // so batch b+1 may be staged over b-1's records and b-1's sums may be flushed while batch b is walked.
     for (int b = 0; b < n_batches; ++b) {
         const int32_t batch_top = top - b * BATCH;                    // slot t holds list position batch_top - t
         const int batch_size = min(BATCH, tile_last - b * BATCH);
-        if (b + 1 < n_batches) {
-            stage_batch<BATCH>(rec[(b + 1) & 1], sid[(b + 1) & 1], records, ids, batch_top - BATCH, -1, min(BATCH, tile_last - (b + 1) * BATCH));
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        cp_async_wait<0>();
         __syncthreads();
+        if (b + 1 < n_batches)
+            stage_batch<BATCH>(rec[(b + 1) & 1], sid[(b + 1) % 3], records, ids, batch_top - BATCH, -1, min(BATCH, tile_last - (b + 1) * BATCH));
+        if (b > 0) flush(b - 1);
+        float* sacc = sacc_all[b & 1];
+        int* stouched = stouched_all[b & 1];
         const float4* st = rec[b & 1];
         // slots whose tile-local position is at or beyond this warp's deepest contributor are dropped up front
         const int t_begin = max(0, (batch_top - range_start) - (warp_last - 1));
@@ -273,21 +291,9 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
                 if (lane == 0) { atomicAdd(&sacc[t * 12 + 8], v8); stouched[t] = 1; }
             }
         }
-        __syncthreads();
-        for (int e = threadIdx.x; e < batch_size; e += kBlock) {
-            if (stouched[e]) {
-                float4* dst = reinterpret_cast<float4*>(accum) + (size_t)sid[b & 1][e] * 3;
-                float4* src = reinterpret_cast<float4*>(sacc) + e * 3;
-#pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    atomicAdd(dst + k, src[k]);
-                    src[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                stouched[e] = 0;
-            }
-        }
-        __syncthreads();
     }
+    __syncthreads();
+    if (n_batches > 0) flush(n_batches - 1);
     cp_async_wait<0>();
 }
 
