@@ -59,7 +59,7 @@ SortScratch carve_scratch(Carver& c) {
 struct RenderWs {
     CamDev* cam;
     int32_t* counters;  // [0] overflow, [1] n_isects, [2] n_visible
-    int32_t *radii, *tiles, *offs, *tile_offsets, *last_ids;
+    int32_t *radii, *tiles, *offs, *tile_offsets, *last_ids, *tile_order;
     float *means2d, *depths, *accum, *extra_sum;
     float4* records;
     uint4* bounds;
@@ -88,6 +88,7 @@ RenderWs carve_render(const lfs_render_config& cfg, void* base) {
     w.accum = c.take<float>(N * 16);
     for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
     w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
+    w.tile_order = c.take<int32_t>((size_t)tw * th);
     w.last_ids = c.take<int32_t>((size_t)cfg.image_width * cfg.image_height);
     w.extra_sum = c.take<float>((size_t)cfg.image_width * cfg.image_height);  // blended depth before the division (ED modes)
     w.scratch = carve_scratch(c);
@@ -98,7 +99,7 @@ RenderWs carve_render(const lfs_render_config& cfg, void* base) {
 // ---- EWA workspace ----------------------------------------------------------------------------
 struct EwaWs {
     int32_t* counters;  // [0] overflow, [1] n_instances, [2] n_visible
-    int32_t *n_touched, *offs, *tile_offsets, *n_contrib;
+    int32_t *n_touched, *offs, *tile_offsets, *n_contrib, *tile_order;
     ushort4* bounds;
     float4* records;
     float* accum;
@@ -122,6 +123,7 @@ EwaWs carve_ewa(const lfs_ewa_config& cfg, void* base) {
     for (int k = 0; k < 2; ++k) { w.tkeys[k] = c.take<uint32_t>(cap); w.tvals[k] = c.take<uint32_t>(cap); }
     w.tile_offsets = c.take<int32_t>((size_t)tw * th + 1);
     w.n_contrib = c.take<int32_t>((size_t)cfg.image_width * cfg.image_height);
+    w.tile_order = c.take<int32_t>((size_t)tw * th);
     w.scratch = carve_scratch(c);
     w.bytes = c.total();
     return w;
@@ -575,7 +577,10 @@ int lfs_ewa_forward(const lfs_ewa_config* cfg, const lfs_splats* params, const f
     a.ewa_bounds = w.bounds; a.ewa_records = w.records;
     rc = build_tile_lists(a, st);
     if (rc != LFS_OK) return rc;
-    EwaBlendArgs b{w.records, w.tvals[sel], w.tile_offsets, w.counters + 0, background, cfg->image_width, cfg->image_height, cam.tw, cam.th};
+    rc = launch_tile_order(cam.tw * cam.th, w.tile_offsets, w.tile_order, st);
+    if (rc != LFS_OK) return rc;
+    EwaBlendArgs b{w.records, w.tvals[sel], w.tile_offsets, w.counters + 0, background, cfg->image_width, cfg->image_height, cam.tw, cam.th,
+                   w.tile_order};
     rc = launch_ewa_blend_fwd(b, image, alpha, w.n_contrib, st);
     if (rc != LFS_OK) return rc;
     if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
@@ -595,7 +600,8 @@ int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const 
     cudaStream_t st = S(stream);
     const EwaCamera cam = ewa_camera(*cfg, w2c, cam_position);
     const int sel = sorted_sel((int)(bit_width_u32((uint32_t)cam.tw * cam.th) + 1));  // tile bits + one camera bit
-    EwaBlendArgs b{w.records, w.tvals[sel], w.tile_offsets, w.counters + 0, background, cfg->image_width, cfg->image_height, cam.tw, cam.th};
+    EwaBlendArgs b{w.records, w.tvals[sel], w.tile_offsets, w.counters + 0, background, cfg->image_width, cfg->image_height, cam.tw, cam.th,
+                   w.tile_order};
     rc = launch_ewa_blend_bwd(b, alpha, w.n_contrib, grad_image, grad_alpha, w.accum, st);
     if (rc != LFS_OK) return rc;
     return launch_ewa_epilogue(cfg->N, cfg->sh_coeffs, *params, cam, w.n_touched, w.records, w.accum, *grads, accumulate,
@@ -678,9 +684,11 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     a.tile_offsets = w.tile_offsets; a.scratch = w.scratch;
     rc = build_tile_lists(a, st);
     if (rc != LFS_OK) return rc;
+    rc = launch_tile_order(tw * th, w.tile_offsets, w.tile_order, st);
+    if (rc != LFS_OK) return rc;
     RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
                   cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
-                  mode_normalize(cfg->render_mode), cfg->tile_masks};
+                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order};
     rc = launch_raster_fwd(ra, render, alpha, w.last_ids, w.extra_sum, st);
     if (rc != LFS_OK) return rc;
     if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
@@ -701,7 +709,7 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
     const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
     RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
                   cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
-                  mode_normalize(cfg->render_mode), cfg->tile_masks};
+                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order};
     rc = launch_raster_bwd(ra, alpha, w.last_ids, w.extra_sum, v_render, v_alpha, w.accum, nullptr, st);
     if (rc != LFS_OK) return rc;
     return launch_grad_epilogue_fused(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, w.accum, w.records, w.radii, *params,

@@ -27,6 +27,7 @@ struct EwaBlendArgs {
     const int32_t* overflow;      // device flag: lists incomplete, draw nothing (may be null)
     const float* background;      // [3] or null
     int W, H, tw, th;
+    const int32_t* tile_order = nullptr;  // [tw*th] or null: CTA b works on tile tile_order[b] (longest lists first)
 };
 // image [3,H,W] (background included), alpha [H,W], n_contrib [H,W] = 1 + list position of the last contributor
 int launch_ewa_blend_fwd(const EwaBlendArgs& a, float* image, float* alpha, int32_t* n_contrib, cudaStream_t st);

@@ -71,11 +71,11 @@ __device__ __forceinline__ void cull_batch(const float4* rec, int lo, int hi, fl
 
 __global__ void __launch_bounds__(kBlock) ewa_blend_fwd_kernel(
     const float4* __restrict__ records, const uint32_t* __restrict__ ids, const int32_t* __restrict__ tile_offsets,
-    const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw,
-    float* __restrict__ image, float* __restrict__ alpha_map, int32_t* __restrict__ n_contrib) {
+    const int32_t* __restrict__ overflow, const float* __restrict__ background, const int32_t* __restrict__ tile_order,
+    int W, int H, int tw, float* __restrict__ image, float* __restrict__ alpha_map, int32_t* __restrict__ n_contrib) {
     constexpr int BATCH = 256;
     __shared__ float4 rec[2][BATCH * 3];
-    const int tile = blockIdx.x;
+    const int tile = tile_order ? tile_order[blockIdx.x] : blockIdx.x;
     int i, j;
     pixel_of_thread(tile, tw, i, j);
     const bool inside = i < H && j < W;
@@ -179,8 +179,9 @@ __device__ __forceinline__ float warp_sum(float x) {
 
 __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
     const float4* __restrict__ records, const uint32_t* __restrict__ ids, const int32_t* __restrict__ tile_offsets,
-    const int32_t* __restrict__ overflow, const float* __restrict__ background, int W, int H, int tw,
-    const float* __restrict__ alpha_map, const int32_t* __restrict__ n_contrib, const float* __restrict__ grad_image,
+    const int32_t* __restrict__ overflow, const float* __restrict__ background, const int32_t* __restrict__ tile_order,
+    int W, int H, int tw, const float* __restrict__ alpha_map, const int32_t* __restrict__ n_contrib,
+    const float* __restrict__ grad_image,
     const float* __restrict__ grad_alpha, float* __restrict__ accum) {
     constexpr int BATCH = 128;
     __shared__ float4 rec[2][BATCH * 3];
@@ -188,7 +189,7 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
     __shared__ __align__(16) float sacc_all[2][BATCH * 12];
     __shared__ int stouched_all[2][BATCH];
     if (overflow && *overflow) return;
-    const int tile = blockIdx.x;
+    const int tile = tile_order ? tile_order[blockIdx.x] : blockIdx.x;
     int i, j;
     pixel_of_thread(tile, tw, i, j);
     const bool inside = i < H && j < W;
@@ -529,8 +530,8 @@ int launch_ewa_blend_fwd(const EwaBlendArgs& a, float* image, float* alpha, int3
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
     LFS_TIMED("ewa_blend_fwd", st);
-    ewa_blend_fwd_kernel<<<n_tiles, kBlock, 0, st>>>(a.records, a.instance_ids, a.tile_offsets, a.overflow, a.background, a.W, a.H,
-                                                     a.tw, image, alpha, n_contrib);
+    ewa_blend_fwd_kernel<<<n_tiles, kBlock, 0, st>>>(a.records, a.instance_ids, a.tile_offsets, a.overflow, a.background, a.tile_order,
+                                                     a.W, a.H, a.tw, image, alpha, n_contrib);
     return check_launch("ewa_blend_fwd");
 }
 
@@ -539,8 +540,8 @@ int launch_ewa_blend_bwd(const EwaBlendArgs& a, const float* alpha, const int32_
     const int n_tiles = a.tw * a.th;
     if (n_tiles == 0) return LFS_OK;
     LFS_TIMED("ewa_blend_bwd", st);
-    ewa_blend_bwd_kernel<<<n_tiles, kBlock, 0, st>>>(a.records, a.instance_ids, a.tile_offsets, a.overflow, a.background, a.W, a.H,
-                                                     a.tw, alpha, n_contrib, grad_image, grad_alpha, accum);
+    ewa_blend_bwd_kernel<<<n_tiles, kBlock, 0, st>>>(a.records, a.instance_ids, a.tile_offsets, a.overflow, a.background, a.tile_order,
+                                                     a.W, a.H, a.tw, alpha, n_contrib, grad_image, grad_alpha, accum);
     return check_launch("ewa_blend_bwd");
 }
 

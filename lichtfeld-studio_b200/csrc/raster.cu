@@ -119,13 +119,13 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, const uint8_t* __restrict__ masks,
-    int channels, int normalize, int W, int H, int tw, int n_tiles,
+    const int32_t* __restrict__ tile_order, int channels, int normalize, int W, int H, int tw, int n_tiles,
     float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids, float* __restrict__ extra_sum) {
     constexpr int BATCH = 256;
     __shared__ Stage<BATCH> stage[2];
 
     if (overflow && *overflow) return;
-    const int tile = blockIdx.x;
+    const int tile = tile_order ? tile_order[blockIdx.x] : blockIdx.x;
     int i, j;
     pixel_of_thread(tile, tw, i, j);
     const bool inside = (i < H && j < W);
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, const uint8_t* __restrict__ masks,
-    int channels, int normalize, int W, int H, int tw, int n_tiles,
+    const int32_t* __restrict__ tile_order, int channels, int normalize, int W, int H, int tw, int n_tiles,
     const float* __restrict__ render_alphas, const int32_t* __restrict__ last_ids, const float* __restrict__ extra_sum,
     const float* __restrict__ v_render, const float* __restrict__ v_alphas, float* __restrict__ accum,
     float* __restrict__ accum_extra) {
@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     BwdShared<BATCH>& sm = *reinterpret_cast<BwdShared<BATCH>*>(smem_raw);
 
     if (overflow && *overflow) return;
-    const int tile = blockIdx.x;
+    const int tile = tile_order ? tile_order[blockIdx.x] : blockIdx.x;
     if (masks && !masks[tile]) return;  // gsplat/RasterizeToPixelsFromWorld3DGSBwd.cu:84
     int i, j;
     pixel_of_thread(tile, tw, i, j);
@@ -683,7 +683,7 @@ int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t
 #define LFS_FWD(MODEL, EXTRA)                                                                                              \
     raster_fwd_kernel<MODEL, EXTRA><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,  \
                                                                 a.n_isects_dev, a.n_isects_host, a.overflow, a.background, \
-                                                                a.masks, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles,  \
+                                                                a.masks, a.tile_order, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles,  \
                                                                 render, alphas, last_ids, extra_sum)
     const bool extra = a.channels != 3;
     if (a.model == LFS_PINHOLE) { if (extra) LFS_FWD(LFS_PINHOLE, true); else LFS_FWD(LFS_PINHOLE, false); }
@@ -716,7 +716,8 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
 #define LFS_BWD(MODEL, EXTRA, XGRAD)                                                                                          \
     raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD><<<n_tiles, kBlock, smem, st>>>(                                          \
         a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets, a.n_isects_dev, a.n_isects_host, a.overflow, a.background, \
-        a.masks, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles, render_alphas, last_ids, extra_sum, v_render, v_alphas,   \
+        a.masks, a.tile_order, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles, render_alphas, last_ids, extra_sum, v_render,   \
+        v_alphas,                                                                                                            \
         accum, accum_extra)
     const bool extra = a.channels != 3, xgrad = extra && accum_extra != nullptr;
     if (a.model == LFS_PINHOLE) {

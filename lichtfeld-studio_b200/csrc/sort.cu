@@ -491,6 +491,41 @@ int build_tile_lists(const TileListArgs& a, cudaStream_t st) {
     return check_launch("build_tile_lists");
 }
 
+// Launch order of the tile CTAs: tiles with the longest lists first, so that the last wave of a rasterizer launch
+// is made of short tiles. 132 buckets by the leading one and the next two bits of the list length (a
+// floating-point-like key with a 2-bit mantissa); the order inside a bucket is arbitrary. offsets has n_tiles + 1
+// entries.
+__device__ __forceinline__ int tile_order_bucket(int c) {
+    if (c <= 0) return 131;
+    const int lz = __clz(c);                              // 0 .. 31, small = long list
+    const int shift = max(0, 29 - lz);                    // bring the two bits below the leading one down
+    const int mant = (c >> shift) & 3;
+    return lz * 4 + (3 - mant);
+}
+
+__global__ void __launch_bounds__(1024) tile_order_kernel(int n_tiles, const int32_t* __restrict__ offsets,
+                                                          int32_t* __restrict__ order) {
+    __shared__ int hist[132], cursor[132];
+    if (threadIdx.x < 132) hist[threadIdx.x] = 0;
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) atomicAdd(&hist[tile_order_bucket(offsets[t + 1] - offsets[t])], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int b = 0; b < 132; ++b) { cursor[b] = run; run += hist[b]; }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_tiles; t += blockDim.x)
+        order[atomicAdd(&cursor[tile_order_bucket(offsets[t + 1] - offsets[t])], 1)] = t;
+}
+
+int launch_tile_order(int n_tiles, const int32_t* offsets, int32_t* order, cudaStream_t st) {
+    if (n_tiles <= 0) return LFS_OK;
+    LFS_TIMED("tile_order", st);
+    tile_order_kernel<<<1, 1024, 0, st>>>(n_tiles, offsets, order);
+    return check_launch("tile_order");
+}
+
 int launch_compose_isect_ids(int64_t n, const uint32_t* tkeys, const uint32_t* tvals, const float* depths,
                              int64_t* isect_ids, int32_t* flatten_ids, cudaStream_t st) {
     if (n <= 0) return LFS_OK;

@@ -33,6 +33,8 @@ struct TileListArgs {
 
 int build_tile_lists(const TileListArgs& a, cudaStream_t st);
 
+// order [n_tiles]: tile indices, longest lists first; offsets [n_tiles + 1]
+int launch_tile_order(int n_tiles, const int32_t* offsets, int32_t* order, cudaStream_t st);
 int launch_compose_isect_ids(int64_t n, const uint32_t* tkeys, const uint32_t* tvals, const float* depths,
                              int64_t* isect_ids, int32_t* flatten_ids, cudaStream_t st);
 int launch_isect_offset(int64_t n, const int64_t* isect_ids, int C, int tw, int th, int32_t* offsets, cudaStream_t st);
