@@ -294,8 +294,8 @@ __device__ __forceinline__ float __reduce_add_sync_f32(float x) {
 
 template <int BATCH>
 struct BwdShared {
-    Stage<BATCH> stage[2];
-    uint32_t sid[3][BATCH];      // Gaussian index per slot; three deep: batch b+1 is staged while batch b-1 is flushed
+    Stage<BATCH> stage[3];       // batch b is walked while b+1 and b+2 are in flight
+    uint32_t sid[4][BATCH];      // Gaussian index per slot; four deep: batch b+2 is staged while batch b-1 is flushed
     float sacc[2][BATCH * 16];   // per-slot sums of the batch being walked / the batch being flushed
     float sextra[2][BATCH];
     int stouched[2][BATCH];
@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
         float* acc_k = sm.sacc[k & 1];
         for (int e = threadIdx.x; e < size_k; e += kBlock) {
             if (sm.stouched[k & 1][e]) {
-                const uint32_t g = sm.sid[k % 3][e];
+                const uint32_t g = sm.sid[k & 3][e];
                 float4* dst = reinterpret_cast<float4*>(accum) + (size_t)g * 4;
                 float4* src = reinterpret_cast<float4*>(acc_k) + e * 4;
 #pragma unroll
@@ -392,28 +392,31 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
 
     // batches run back to front: slot e of batch b holds list position batch_end - e
     StageIds<BATCH> ids;
+    auto batch_count = [&](int k) { return min(BATCH, range_end - k * BATCH - range_start); };
+    auto batch_top = [&](int k) { return range_end - 1 - k * BATCH; };
     if (n_batches > 0) {
-        const int32_t be = range_end - 1;
-        load_ids(ids, flatten_ids, be, -1, min(BATCH, be + 1 - range_start));
-        issue_stage(sm.stage[0], sm.sid[0], ids, records, bounds, min(BATCH, be + 1 - range_start));
-        if (n_batches > 1) load_ids(ids, flatten_ids, be - BATCH, -1, min(BATCH, be - BATCH + 1 - range_start));
+        load_ids(ids, flatten_ids, batch_top(0), -1, batch_count(0));
+        issue_stage(sm.stage[0], sm.sid[0], ids, records, bounds, batch_count(0));
+        if (n_batches > 1) {
+            load_ids(ids, flatten_ids, batch_top(1), -1, batch_count(1));
+            issue_stage(sm.stage[1], sm.sid[1], ids, records, bounds, batch_count(1));
+            if (n_batches > 2) load_ids(ids, flatten_ids, batch_top(2), -1, batch_count(2));
+        }
     }
     // One barrier per batch: after it, batch b is in shared memory and every warp has finished walking batch b-1,
-    // so batch b+1 may be staged over b-1's records and b-1's sums may be flushed while batch b is walked.
+    // so batch b+2 may be staged over b-1's records and b-1's sums may be flushed while batch b is walked.
     for (int b = 0; b < n_batches; ++b) {
-        const int32_t batch_end = range_end - 1 - b * BATCH;
-        const int32_t batch_size = min(BATCH, batch_end + 1 - range_start);
-        cp_async_wait<0>();
+        const int32_t batch_end = batch_top(b);
+        const int32_t batch_size = batch_count(b);
+        if (b + 1 < n_batches) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads();
-        if (b + 1 < n_batches) {
-            issue_stage(sm.stage[(b + 1) & 1], sm.sid[(b + 1) % 3], ids, records, bounds,
-                        min(BATCH, batch_end - BATCH + 1 - range_start));
-            if (b + 2 < n_batches)
-                load_ids(ids, flatten_ids, batch_end - 2 * BATCH, -1, min(BATCH, batch_end - 2 * BATCH + 1 - range_start));
+        if (b + 2 < n_batches) {
+            issue_stage(sm.stage[(b + 2) % 3], sm.sid[(b + 2) & 3], ids, records, bounds, batch_count(b + 2));
+            if (b + 3 < n_batches) load_ids(ids, flatten_ids, batch_top(b + 3), -1, batch_count(b + 3));
         }
         if (b > 0) flush(b - 1);
         float* sacc = sm.sacc[b & 1];
-        const Stage<BATCH>& st = sm.stage[b & 1];
+        const Stage<BATCH>& st = sm.stage[b % 3];
         // entries (back to front) that no pixel of this warp reaches (beyond its last contributor) or whose
         // box misses this warp's 8x4 patch are dropped up front: one ballot word per 32 entries
         const int t_begin = max(0, batch_end - warp_bin_final);
