@@ -4,8 +4,8 @@
 // Replaces src/training/kernels/ssim.cu:64 (K9) and :284 (K10), the crop / pad / mean glue of
 // include/kernels/fused_ssim.cuh:59-67, :85-96, :117-122, torch::l1_loss of
 // src/training/trainer.cpp:126 and the clamp + permute of src/training/rasterization/rasterizer.cpp:205.
-// HBM-bound stencil work: each CTA stages a 26x26 halo tile in shared memory and runs the 11-tap
-// horizontal and vertical passes from there.
+// Stencil work: each CTA stages the 42x42 halo tile of a 32x32 output tile of one channel in shared memory and runs
+// the 11-tap horizontal and vertical passes from register windows (4 outputs per 14 loaded values).
 #include "common.cuh"
 #include "loss.cuh"
 
@@ -13,9 +13,13 @@ namespace lfs {
 
 namespace {
 
-constexpr int kB = 16;           // tile edge
+constexpr int kT = 32;             // output tile edge
 constexpr int kHalo = 5;
-constexpr int kS = kB + 2 * kHalo;  // 26
+constexpr int kS = kT + 2 * kHalo;   // 42: halo tile edge
+constexpr int kSX = kS + 1;          // 43: row stride of the staged images (conflict-free for lanes that walk rows)
+constexpr int kSH = kT + 1;          // 33: row stride of the horizontally filtered planes
+constexpr int kThreadsLoss = 256;
+constexpr int kColGroups = kT / 4;   // a horizontal work item filters 4 adjacent columns of one row
 
 __constant__ float cTaps[11] = {
     0.001028380123898387f, 0.0075987582094967365f, 0.036000773310661316f, 0.10936068743467331f,
@@ -34,85 +38,103 @@ __device__ __forceinline__ float load_chw(const float* img, int c, int y, int x,
     return img[(size_t)c * H * W + (size_t)y * W + x];
 }
 
-// Forward. Plain mode writes ssim_map and the three derivative maps. Fused mode writes the
-// derivative maps already multiplied by dL/dmap (map_grad inside the valid crop, 0 outside) and
-// accumulates sum(ssim over the crop) and sum(|img1 - img2|) into sums[0], sums[1].
+// 11-tap filter at centre index ci of a register window, symmetric pairs first (the reference's order of additions)
+__device__ __forceinline__ float tap11(const float* v, int ci) {
+    float a = 0.f;
+#pragma unroll
+    for (int d = 1; d <= kHalo; ++d) a += (v[ci - d] + v[ci + d]) * cTaps[kHalo - d];
+    return a + v[ci] * cTaps[kHalo];
+}
+
+// One CTA filters a 32x32 output tile of one channel (blockIdx.z). The 42x42 halo tile is staged in shared memory;
+// the horizontal pass gives every thread 4 adjacent outputs of one row from a 14-value register window (7 shared
+// loads per output instead of 44), the vertical pass 4 stacked outputs of one column from 14-value windows of the five
+// filtered planes.
+//
+// Forward. Plain mode writes ssim_map and the three derivative maps. Fused mode writes the derivative maps already
+// multiplied by dL/dmap (map_grad inside the valid crop, 0 outside) and accumulates sum(ssim over the crop) and
+// sum(|img1 - img2|) into sums[0], sums[1].
 template <bool FUSED>
-__global__ void __launch_bounds__(kB* kB) ssim_fwd_kernel(int CH, int H, int W, float C1, float C2,
-                                                          const float* __restrict__ img1, const float* __restrict__ img2,
-                                                          float* __restrict__ ssim_map, float* __restrict__ dm_dmu1,
-                                                          float* __restrict__ dm_dsigma1_sq, float* __restrict__ dm_dsigma12,
-                                                          float map_grad, int crop, double* __restrict__ sums) {
-    __shared__ float sX[kS][kS + 1], sY[kS][kS + 1];
-    __shared__ float sH[kS][kB][5];
-    __shared__ float red[2][kB * kB / 32];
-    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kB + tx;
-    const int x = blockIdx.x * kB + tx, y = blockIdx.y * kB + ty;
+__global__ void __launch_bounds__(kThreadsLoss) ssim_fwd_kernel(int CH, int H, int W, float C1, float C2,
+                                                               const float* __restrict__ img1, const float* __restrict__ img2,
+                                                               float* __restrict__ ssim_map, float* __restrict__ dm_dmu1,
+                                                               float* __restrict__ dm_dsigma1_sq, float* __restrict__ dm_dsigma12,
+                                                               float map_grad, int crop, double* __restrict__ sums) {
+    __shared__ float sX[kS][kSX], sY[kS][kSX];
+    __shared__ float sH[5][kS][kSH];
+    __shared__ float red[2][kThreadsLoss / 32];
+    const int tid = threadIdx.x, c = blockIdx.z;
+    const int bx0 = blockIdx.x * kT, by0 = blockIdx.y * kT;
+    for (int q = tid; q < kS * kS; q += kThreadsLoss) {
+        const int ly = q / kS, lx = q - ly * kS;
+        sX[ly][lx] = load_img1<FUSED>(img1, c, by0 + ly - kHalo, bx0 + lx - kHalo, H, W);
+        sY[ly][lx] = load_chw(img2, c, by0 + ly - kHalo, bx0 + lx - kHalo, H, W);
+    }
+    __syncthreads();
+    for (int item = tid; item < kS * kColGroups; item += kThreadsLoss) {
+        const int cg = item / kS, row = item - cg * kS;
+        float xv[14], yv[14], q[14];
+#pragma unroll
+        for (int j = 0; j < 14; ++j) { xv[j] = sX[row][cg * 4 + j]; yv[j] = sY[row][cg * 4 + j]; }
+#pragma unroll
+        for (int o = 0; o < 4; ++o) sH[0][row][cg * 4 + o] = tap11(xv, o + kHalo);
+#pragma unroll
+        for (int o = 0; o < 4; ++o) sH[2][row][cg * 4 + o] = tap11(yv, o + kHalo);
+#pragma unroll
+        for (int j = 0; j < 14; ++j) q[j] = xv[j] * xv[j];
+#pragma unroll
+        for (int o = 0; o < 4; ++o) sH[1][row][cg * 4 + o] = tap11(q, o + kHalo);
+#pragma unroll
+        for (int j = 0; j < 14; ++j) q[j] = yv[j] * yv[j];
+#pragma unroll
+        for (int o = 0; o < 4; ++o) sH[3][row][cg * 4 + o] = tap11(q, o + kHalo);
+#pragma unroll
+        for (int j = 0; j < 14; ++j) q[j] = xv[j] * yv[j];
+#pragma unroll
+        for (int o = 0; o < 4; ++o) sH[4][row][cg * 4 + o] = tap11(q, o + kHalo);
+    }
+    __syncthreads();
+    const int col = tid & 31, strip = tid >> 5;
+    float out[4][5];
+#pragma unroll
+    for (int k = 0; k < 5; ++k) {
+        float h[14];
+#pragma unroll
+        for (int j = 0; j < 14; ++j) h[j] = sH[k][strip * 4 + j][col];
+#pragma unroll
+        for (int o = 0; o < 4; ++o) out[o][k] = tap11(h, o + kHalo);
+    }
     float ssim_acc = 0.f, l1_acc = 0.f;
-    for (int c = 0; c < CH; ++c) {
-        for (int q = tid; q < kS * kS; q += kB * kB) {
-            const int ly = q / kS, lx = q % kS;
-            const int gy = blockIdx.y * kB + ly - kHalo, gx = blockIdx.x * kB + lx - kHalo;
-            sX[ly][lx] = load_img1<FUSED>(img1, c, gy, gx, H, W);
-            sY[ly][lx] = load_chw(img2, c, gy, gx, H, W);
-        }
-        __syncthreads();
-        for (int ly = ty; ly < kS; ly += kB) {
-            const int lx = tx + kHalo;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, a4 = 0.f;
+    const int x = bx0 + col;
 #pragma unroll
-            for (int d = 1; d <= kHalo; ++d) {
-                const float w = cTaps[kHalo - d];
-                const float Xl = sX[ly][lx - d], Yl = sY[ly][lx - d], Xr = sX[ly][lx + d], Yr = sY[ly][lx + d];
-                a0 += (Xl + Xr) * w;
-                a1 += ((Xl * Xl) + (Xr * Xr)) * w;
-                a2 += (Yl + Yr) * w;
-                a3 += ((Yl * Yl) + (Yr * Yr)) * w;
-                a4 += ((Xl * Yl) + (Xr * Yr)) * w;
-            }
-            const float cX = sX[ly][lx], cY = sY[ly][lx], wc = cTaps[kHalo];
-            a0 += cX * wc; a1 += (cX * cX) * wc; a2 += cY * wc; a3 += (cY * cY) * wc; a4 += (cX * cY) * wc;
-            sH[ly][tx][0] = a0; sH[ly][tx][1] = a1; sH[ly][tx][2] = a2; sH[ly][tx][3] = a3; sH[ly][tx][4] = a4;
-        }
-        __syncthreads();
-        {
-            const int ly = ty + kHalo;
-            float o[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int d = 1; d <= kHalo; ++d) {
-                const float w = cTaps[kHalo - d];
-#pragma unroll
-                for (int k = 0; k < 5; ++k) o[k] += (sH[ly - d][tx][k] + sH[ly + d][tx][k]) * w;
-            }
-#pragma unroll
-            for (int k = 0; k < 5; ++k) o[k] += sH[ly][tx][k] * cTaps[kHalo];
-            if (x < W && y < H) {
-                const float mu1 = o[0], mu2 = o[2];
-                const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
-                const float sigma1_sq = o[1] - mu1_sq, sigma2_sq = o[3] - mu2_sq, sigma12 = o[4] - mu1 * mu2;
-                const float A = mu1_sq + mu2_sq + C1, B = sigma1_sq + sigma2_sq + C2;
-                const float C_ = 2.f * mu1 * mu2 + C1, D_ = 2.f * sigma12 + C2;
-                const float val = (C_ * D_) / (A * B);
-                const float g_mu1 = ((mu2 * 2.f * D_) / (A * B) - (mu2 * 2.f * C_) / (A * B) -
-                                     (mu1 * 2.f * C_ * D_) / (A * A * B) + (mu1 * 2.f * C_ * D_) / (A * B * B));
-                const float g_s1 = (-C_ * D_) / (A * B * B);
-                const float g_s12 = (2.f * C_) / (A * B);
-                const size_t gi = (size_t)c * H * W + (size_t)y * W + x;
-                if (FUSED) {
-                    const bool in_crop = !crop || (x >= kHalo && x < W - kHalo && y >= kHalo && y < H - kHalo);
-                    const float chain = in_crop ? map_grad : 0.f;
-                    dm_dmu1[gi] = g_mu1 * chain;
-                    dm_dsigma1_sq[gi] = g_s1 * chain;
-                    dm_dsigma12[gi] = g_s12 * chain;
-                    if (in_crop) ssim_acc += val;
-                    l1_acc += fabsf(sX[ty + kHalo][tx + kHalo] - sY[ty + kHalo][tx + kHalo]);
-                } else {
-                    ssim_map[gi] = val;
-                    if (dm_dmu1) { dm_dmu1[gi] = g_mu1; dm_dsigma1_sq[gi] = g_s1; dm_dsigma12[gi] = g_s12; }
-                }
+    for (int o = 0; o < 4; ++o) {
+        const int y = by0 + strip * 4 + o;
+        if (x < W && y < H) {
+            const float mu1 = out[o][0], mu2 = out[o][2];
+            const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
+            const float sigma1_sq = out[o][1] - mu1_sq, sigma2_sq = out[o][3] - mu2_sq, sigma12 = out[o][4] - mu1 * mu2;
+            const float A = mu1_sq + mu2_sq + C1, B = sigma1_sq + sigma2_sq + C2;
+            const float C_ = 2.f * mu1 * mu2 + C1, D_ = 2.f * sigma12 + C2;
+            const float val = (C_ * D_) / (A * B);
+            const float g_mu1 = ((mu2 * 2.f * D_) / (A * B) - (mu2 * 2.f * C_) / (A * B) -
+                                 (mu1 * 2.f * C_ * D_) / (A * A * B) + (mu1 * 2.f * C_ * D_) / (A * B * B));
+            const float g_s1 = (-C_ * D_) / (A * B * B);
+            const float g_s12 = (2.f * C_) / (A * B);
+            const size_t gi = (size_t)c * H * W + (size_t)y * W + x;
+            if (FUSED) {
+                const bool in_crop = !crop || (x >= kHalo && x < W - kHalo && y >= kHalo && y < H - kHalo);
+                const float chain = in_crop ? map_grad : 0.f;
+                dm_dmu1[gi] = g_mu1 * chain;
+                dm_dsigma1_sq[gi] = g_s1 * chain;
+                dm_dsigma12[gi] = g_s12 * chain;
+                if (in_crop) ssim_acc += val;
+                const int ly = strip * 4 + o + kHalo, lx = col + kHalo;
+                l1_acc += fabsf(sX[ly][lx] - sY[ly][lx]);
+            } else {
+                ssim_map[gi] = val;
+                if (dm_dmu1) { dm_dmu1[gi] = g_mu1; dm_dsigma1_sq[gi] = g_s1; dm_dsigma12[gi] = g_s12; }
             }
         }
-        __syncthreads();
     }
     if (FUSED) {
 #pragma unroll
@@ -123,66 +145,68 @@ __global__ void __launch_bounds__(kB* kB) ssim_fwd_kernel(int CH, int H, int W, 
         if ((tid & 31) == 0) { red[0][tid >> 5] = ssim_acc; red[1][tid >> 5] = l1_acc; }
         __syncthreads();
         if (tid == 0) {
-            double s = 0.0, l = 0.0;
-            for (int k = 0; k < kB * kB / 32; ++k) { s += red[0][k]; l += red[1][k]; }
-            atomicAdd(&sums[0], s);
-            atomicAdd(&sums[1], l);
+            double s_ = 0.0, l_ = 0.0;
+            for (int k = 0; k < kThreadsLoss / 32; ++k) { s_ += red[0][k]; l_ += red[1][k]; }
+            atomicAdd(&sums[0], s_);
+            atomicAdd(&sums[1], l_);
         }
     }
 }
 
-// Backward. Plain mode: maps are multiplied by dL_dmap on load and dL_dimg1 is CHW. Fused mode: the maps
-// are pre-multiplied, the L1 sign term and the clamp mask are applied and the output is the HWC
-// gradient of the unclamped render, scaled by grad_scale.
+// Backward, same tiling. Plain mode: maps are multiplied by dL_dmap on load and dL_dimg1 is CHW. Fused mode: the maps
+// are pre-multiplied, the L1 sign term and the clamp mask are applied and the output is the HWC gradient of the
+// unclamped render, scaled by grad_scale.
 template <bool FUSED>
-__global__ void __launch_bounds__(kB* kB) ssim_bwd_kernel(int CH, int H, int W, const float* __restrict__ img1,
-                                                          const float* __restrict__ img2, const float* __restrict__ dL_dmap,
-                                                          const float* __restrict__ dm_dmu1, const float* __restrict__ dm_dsigma1_sq,
-                                                          const float* __restrict__ dm_dsigma12, float* __restrict__ dL_dimg1,
-                                                          float l1_grad, float grad_scale) {
-    __shared__ float sD[3][kS][kS + 1];
-    __shared__ float sH[kS][kB][3];
-    const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * kB + tx;
-    const int x = blockIdx.x * kB + tx, y = blockIdx.y * kB + ty;
-    for (int c = 0; c < CH; ++c) {
-        for (int q = tid; q < kS * kS; q += kB * kB) {
-            const int ly = q / kS, lx = q % kS;
-            const int gy = blockIdx.y * kB + ly - kHalo, gx = blockIdx.x * kB + lx - kHalo;
-            const float chain = FUSED ? 1.f : load_chw(dL_dmap, c, gy, gx, H, W);
-            sD[0][ly][lx] = load_chw(dm_dmu1, c, gy, gx, H, W) * chain;
-            sD[1][ly][lx] = load_chw(dm_dsigma1_sq, c, gy, gx, H, W) * chain;
-            sD[2][ly][lx] = load_chw(dm_dsigma12, c, gy, gx, H, W) * chain;
+__global__ void __launch_bounds__(kThreadsLoss) ssim_bwd_kernel(int CH, int H, int W, const float* __restrict__ img1,
+                                                               const float* __restrict__ img2, const float* __restrict__ dL_dmap,
+                                                               const float* __restrict__ dm_dmu1, const float* __restrict__ dm_dsigma1_sq,
+                                                               const float* __restrict__ dm_dsigma12, float* __restrict__ dL_dimg1,
+                                                               float l1_grad, float grad_scale) {
+    __shared__ float sD[3][kS][kSX];
+    __shared__ float sH[3][kS][kSH];
+    const int tid = threadIdx.x, c = blockIdx.z;
+    const int bx0 = blockIdx.x * kT, by0 = blockIdx.y * kT;
+    for (int q = tid; q < kS * kS; q += kThreadsLoss) {
+        const int ly = q / kS, lx = q - ly * kS;
+        const int gy = by0 + ly - kHalo, gx = bx0 + lx - kHalo;
+        const float chain = FUSED ? 1.f : load_chw(dL_dmap, c, gy, gx, H, W);
+        sD[0][ly][lx] = load_chw(dm_dmu1, c, gy, gx, H, W) * chain;
+        sD[1][ly][lx] = load_chw(dm_dsigma1_sq, c, gy, gx, H, W) * chain;
+        sD[2][ly][lx] = load_chw(dm_dsigma12, c, gy, gx, H, W) * chain;
+    }
+    __syncthreads();
+    for (int item = tid; item < kS * kColGroups; item += kThreadsLoss) {
+        const int cg = item / kS, row = item - cg * kS;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            float v[14];
+#pragma unroll
+            for (int j = 0; j < 14; ++j) v[j] = sD[k][row][cg * 4 + j];
+#pragma unroll
+            for (int o = 0; o < 4; ++o) sH[k][row][cg * 4 + o] = tap11(v, o + kHalo);
         }
-        __syncthreads();
-        for (int ly = ty; ly < kS; ly += kB) {
-            const int lx = tx + kHalo;
-            float a[3] = {0.f, 0.f, 0.f};
+    }
+    __syncthreads();
+    const int col = tid & 31, strip = tid >> 5;
+    float s[4][3];
 #pragma unroll
-            for (int d = 1; d <= kHalo; ++d) {
-                const float w = cTaps[kHalo - d];
+    for (int k = 0; k < 3; ++k) {
+        float h[14];
 #pragma unroll
-                for (int k = 0; k < 3; ++k) a[k] += (sD[k][ly][lx - d] + sD[k][ly][lx + d]) * w;
-            }
+        for (int j = 0; j < 14; ++j) h[j] = sH[k][strip * 4 + j][col];
 #pragma unroll
-            for (int k = 0; k < 3; ++k) { a[k] += sD[k][ly][lx] * cTaps[kHalo]; sH[ly][tx][k] = a[k]; }
-        }
-        __syncthreads();
+        for (int o = 0; o < 4; ++o) s[o][k] = tap11(h, o + kHalo);
+    }
+    const int x = bx0 + col;
+#pragma unroll
+    for (int o = 0; o < 4; ++o) {
+        const int y = by0 + strip * 4 + o;
         if (x < W && y < H) {
-            const int ly = ty + kHalo;
-            float s[3] = {0.f, 0.f, 0.f};
-#pragma unroll
-            for (int d = 1; d <= kHalo; ++d) {
-                const float w = cTaps[kHalo - d];
-#pragma unroll
-                for (int k = 0; k < 3; ++k) s[k] += (sH[ly - d][tx][k] + sH[ly + d][tx][k]) * w;
-            }
-#pragma unroll
-            for (int k = 0; k < 3; ++k) s[k] += sH[ly][tx][k] * cTaps[kHalo];
             if (FUSED) {
                 const float raw = img1[((size_t)y * W + x) * 3 + c];
                 const float p1 = fminf(1.f, fmaxf(0.f, raw));
                 const float p2 = img2[(size_t)c * H * W + (size_t)y * W + x];
-                float g = s[0] + (2.f * p1) * s[1] + (p2)*s[2];
+                float g = s[o][0] + (2.f * p1) * s[o][1] + (p2)*s[o][2];
                 const float diff = p1 - p2;
                 g += l1_grad * (diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f));
                 if (!(raw >= 0.f && raw <= 1.f)) g = 0.f;
@@ -190,10 +214,9 @@ __global__ void __launch_bounds__(kB* kB) ssim_bwd_kernel(int CH, int H, int W, 
             } else {
                 const size_t gi = (size_t)c * H * W + (size_t)y * W + x;
                 const float p1 = img1[gi], p2 = img2[gi];
-                dL_dimg1[gi] = s[0] + (2.f * p1) * s[1] + (p2)*s[2];
+                dL_dimg1[gi] = s[o][0] + (2.f * p1) * s[o][1] + (p2)*s[o][2];
             }
         }
-        __syncthreads();
     }
 }
 
@@ -210,7 +233,7 @@ __global__ void loss_finalize_kernel(const double* sums, double n_all, double n_
 int launch_fusedssim(int CH, int H, int W, float C1, float C2, const float* img1, const float* img2, float* ssim_map,
                      float* dm1, float* ds1, float* ds12, cudaStream_t st) {
     if (CH * H * W == 0) return LFS_OK;
-    dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    dim3 grid((W + kT - 1) / kT, (H + kT - 1) / kT, CH), block(kThreadsLoss);
     ssim_fwd_kernel<false><<<grid, block, 0, st>>>(CH, H, W, C1, C2, img1, img2, ssim_map, dm1, ds1, ds12, 0.f, 0, nullptr);
     return check_launch("fusedssim");
 }
@@ -218,7 +241,7 @@ int launch_fusedssim(int CH, int H, int W, float C1, float C2, const float* img1
 int launch_fusedssim_backward(int CH, int H, int W, const float* img1, const float* img2, const float* dL_dmap,
                               const float* dm1, const float* ds1, const float* ds12, float* dL_dimg1, cudaStream_t st) {
     if (CH * H * W == 0) return LFS_OK;
-    dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    dim3 grid((W + kT - 1) / kT, (H + kT - 1) / kT, CH), block(kThreadsLoss);
     ssim_bwd_kernel<false><<<grid, block, 0, st>>>(CH, H, W, img1, img2, dL_dmap, dm1, ds1, ds12, dL_dimg1, 0.f, 1.f);
     return check_launch("fusedssim_backward");
 }
@@ -237,7 +260,7 @@ int launch_photometric_loss(int H, int W, float lambda, float grad_scale, const 
     const float map_grad = (float)(-(double)lambda / n_valid);
     const float l1_grad = (float)((1.0 - (double)lambda) / n_all);
     cudaMemsetAsync(sums, 0, 2 * sizeof(double), st);
-    dim3 grid((W + kB - 1) / kB, (H + kB - 1) / kB), block(kB, kB);
+    dim3 grid((W + kT - 1) / kT, (H + kT - 1) / kT, 3), block(kThreadsLoss);
     {
     LFS_TIMED("loss_fwd", st);
     ssim_fwd_kernel<true><<<grid, block, 0, st>>>(3, H, W, (float)(0.01 * 0.01), (float)(0.03 * 0.03), render_hwc,
