@@ -167,7 +167,7 @@ def run_reference(args):
            "e2e": {"value": val, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "note": "CPU oracle (scalar C++ restatement, OpenMP over tiles / Gaussians): the reference has no CPU path and "
                    "its CUDA sources need glm, which is not installed"}
-    print(json.dumps(out), flush=True)
+    print(json.dumps(_finite(out)), flush=True)
 
 
 # --------------------------------------------------------------------------------------------- GPU arm
@@ -373,8 +373,9 @@ def run_ours(args):
                     "note": f"370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms; peak = 148 SM x 128 lanes x 2 x "
                             f"{sm_clock:.0f} MHz sampled under load (no tensor cores on this path)"}
         adam_bytes = 28.0 * 59 * n if K_sh == 16 else 28.0 * model.row_floats * n
-        extra = {"roofline_adam": {"kernel": "adam_groups_kernel", "bound": "hbm", "achieved": adam_bytes / (t_adam * 1e-3) / 1e9,
-                                   "peak": hbm_peak, "unit": "GB/s", "frac": adam_bytes / (t_adam * 1e-3) / 1e9 / hbm_peak,
+        adam_gbs = adam_bytes / (t_adam * 1e-3) / 1e9 if np.isfinite(t_adam) else None   # N > 1: Adam runs inside the exchange
+        extra = {"roofline_adam": {"kernel": "adam_groups_kernel", "bound": "hbm", "achieved": adam_gbs,
+                                   "peak": hbm_peak, "unit": "GB/s", "frac": adam_gbs / hbm_peak if adam_gbs else None,
                                    "traffic": None, "note": f"28 B x {model.row_floats} floats x {n} Gaussians, of {peak_kind}"},
                  "roofline_raster_fwd": {"kernel": "raster_fwd_kernel", "bound": "fp32",
                                          "achieved": 70.0 * q_list / (t_fwd * 1e-3) / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
@@ -402,9 +403,20 @@ def run_ours(args):
                "gpu_launches": int(round(gpu_launches_step * args.steps)), "roofline": roofline, "cpu_baseline": cpu,
                "gpix_per_s_step": world * W * H / (ms_per_step * 1e-3) / 1e9}
         out.update(extra)
-        print(json.dumps(out), flush=True)
+        print(json.dumps(_finite(out)), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _finite(x):
+    """Strict JSON has no NaN / Infinity: replace non-finite floats by null."""
+    if isinstance(x, dict):
+        return {k: _finite(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [_finite(v) for v in x]
+    if isinstance(x, float) and not np.isfinite(x):
+        return None
+    return x
 
 
 def _kernel_means(recs):
@@ -466,7 +478,7 @@ def run_forward_only(args):
                         "achieved": sort_bytes / (sort_ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                         "frac": sort_bytes / (sort_ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
                         "note": f"20 V + 36 I + 4 tiles bytes, of {kind}; 21 launches, launch-latency bound at this size"}}
-    print(json.dumps(out), flush=True)
+    print(json.dumps(_finite(out)), flush=True)
 
 
 def run_ewa(args):
@@ -533,7 +545,7 @@ def run_ewa(args):
            "roofline": {"kernel": "adam_groups_kernel", "bound": "hbm", "achieved": adam_bytes / (t_adam * 1e-3) / 1e9, "peak": hbm_peak,
                         "unit": "GB/s", "frac": adam_bytes / (t_adam * 1e-3) / 1e9 / hbm_peak, "traffic": None,
                         "note": f"the blend kernels are instruction-issue bound; the streaming kernel shown is Adam, of {kind}"}}
-    print(json.dumps(out), flush=True)
+    print(json.dumps(_finite(out)), flush=True)
 
 
 def run_mcmc(args):
@@ -583,7 +595,7 @@ def run_mcmc(args):
                         "unit": "GB/s", "frac": bytes_alg / (ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
                         "note": f"56 M + 68 N + 472 M bytes with M = {M} sampled rows, of {kind}; includes torch.multinomial / normal_ "
                                 "and two host reads of the dead / alive counts"}}
-    print(json.dumps(out), flush=True)
+    print(json.dumps(_finite(out)), flush=True)
 
 
 def main():

@@ -164,10 +164,13 @@ def symmetric_flat_buffers(numel: int, device, group=None):
     import torch.distributed._symmetric_memory as symm_mem
     name = (group or dist.group.WORLD).group_name
     if hasattr(symm_mem, "enable_symm_mem_for_group"):
-        try:
-            symm_mem.enable_symm_mem_for_group(name)
-        except Exception:
-            pass  # newer torch enables it implicitly
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")   # deprecated (a no-op) in newer torch, required by older ones
+            try:
+                symm_mem.enable_symm_mem_for_group(name)
+            except Exception:
+                pass
     p = symm_mem.empty(numel, dtype=torch.float32, device=device)
     g = symm_mem.empty(numel, dtype=torch.float32, device=device)
     hp = symm_mem.rendezvous(p, name)
