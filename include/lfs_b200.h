@@ -226,6 +226,17 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
                        float* render, float* alpha, int32_t* status_dev,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same forward in two calls, for callers that overlap the optimizer with the next step: the tile lists depend
+ * on means / scales / rotations / opacities only, so lfs_render_forward_lists can start as soon as those four
+ * tensors are updated, while the SH tensors (three quarters of the parameter bytes) are still being updated on
+ * another stream; lfs_render_forward_shade (SH colours into the per-Gaussian records, then blending) follows once
+ * that stream is done. lists + shade on one workspace = lfs_render_forward, bit for bit. */
+int lfs_render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat,
+                             const float* K, void* workspace, size_t workspace_bytes, void* stream);
+int lfs_render_forward_shade(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
+                             float* render, float* alpha, int32_t* status_dev,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Backward of the same node (rasterizer_autograd.cpp:105 -> gsplat/Rasterization.cpp:470) followed by
  * the activation backward, for the camera whose forward state is in the workspace. alpha is the
  * forward's alpha output, v_render [H,W,channels] and v_alpha [H,W,1] (may be NULL = zeros) the output

@@ -90,6 +90,8 @@ _SIGNATURES = {
     "lfs_ply_pack_rows": [i32, i32, C.POINTER(Splats), vp, vp],
     "lfs_ply_unpack_rows": [i32, i32, vp, C.POINTER(Splats), vp],
     "lfs_render_forward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, sz, vp],
+    "lfs_render_forward_lists": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, sz, vp],
+    "lfs_render_forward_shade": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, sz, vp],
     "lfs_render_backward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, C.POINTER(Splats), i32, vp, sz, vp],
     "lfs_render_workspace_view": [C.POINTER(RenderConfig), vp, sz, C.POINTER(RenderView)],
     "lfs_photometric_loss": [i32, i32, f32, f32, vp, vp, vp, vp, vp, sz, vp],

@@ -650,6 +650,47 @@ size_t lfs_render_workspace_bytes(const lfs_render_config* cfg) {
     return carve_render(*cfg, nullptr).bytes;
 }
 
+// Shared body of the forward: per-Gaussian stage + tile lists (stage 1), shading + blending (stage 2).
+static int render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
+                                int with_colors, RenderWs& w, int* sel_out, cudaStream_t st) {
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    int rc = launch_camera_setup(1, viewmat, K, cfg->radial_coeffs, cfg->tangential_coeffs, cfg->thin_prism_coeffs, cfg->image_width,
+                                 cfg->image_height, cfg->camera_model, w.cam, st);
+    if (rc != LFS_OK) return rc;
+    cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
+    const ProjParams pp = make_proj_params(cfg->eps2d, cfg->near_plane, cfg->far_plane, cfg->radius_clip, cfg->ut);
+    PackOptions opt;
+    opt.scaling_modifier = cfg_modifier(*cfg);
+    opt.calc_compensations = cfg->calc_compensations;
+    opt.want_rgb = with_colors && mode_channels(cfg->render_mode) != 1;
+    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, opt, cfg_model(*cfg), cfg->tile_size, tw,
+                             th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records, w.bounds,
+                             reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
+    if (rc != LFS_OK) return rc;
+    TileListArgs a{};
+    a.C = 1; a.N = cfg->N; a.tw = tw; a.th = th; a.tile_size = cfg->tile_size; a.sort = 1; a.keys_ready = 1;
+    a.means2d = w.means2d; a.radii = w.radii; a.depths = w.depths; a.tiles = w.tiles;
+    for (int k = 0; k < 2; ++k) { a.gkeys[k] = w.gkeys[k]; a.gvals[k] = w.gvals[k]; a.tkeys[k] = w.tkeys[k]; a.tvals[k] = w.tvals[k]; }
+    a.offs = w.offs; a.n_isects_dev = w.counters + 1; a.capacity = cfg->isect_capacity; a.overflow = w.counters + 0;
+    a.sel_out = sel_out;
+    a.tile_offsets = w.tile_offsets; a.scratch = w.scratch;
+    rc = build_tile_lists(a, st);
+    if (rc != LFS_OK) return rc;
+    return launch_tile_order(tw * th, w.tile_offsets, w.tile_order, st);
+}
+
+static int render_forward_blend(const lfs_render_config* cfg, const float* background, float* render, float* alpha,
+                                int32_t* status_dev, RenderWs& w, int sel, cudaStream_t st) {
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
+                  cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
+                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order};
+    int rc = launch_raster_fwd(ra, render, alpha, w.last_ids, w.extra_sum, st);
+    if (rc != LFS_OK) return rc;
+    if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    return LFS_OK;
+}
+
 int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
                        const float* background, float* render, float* alpha,
                        int32_t* status_dev, void* workspace, size_t workspace_bytes, void* stream) {
@@ -660,39 +701,45 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     RenderWs w = carve_render(*cfg, workspace);
     if (workspace_bytes < w.bytes) { set_error("lfs_render_forward: workspace too small (%zu < %zu)", workspace_bytes, w.bytes); return LFS_ECAPACITY; }
     cudaStream_t st = S(stream);
-    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
-    rc = launch_camera_setup(1, viewmat, K, cfg->radial_coeffs, cfg->tangential_coeffs, cfg->thin_prism_coeffs, cfg->image_width,
-                             cfg->image_height, cfg->camera_model, w.cam, st);
-    if (rc != LFS_OK) return rc;
-    cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
-    const ProjParams pp = make_proj_params(cfg->eps2d, cfg->near_plane, cfg->far_plane, cfg->radius_clip, cfg->ut);
-    PackOptions opt;
-    opt.scaling_modifier = cfg_modifier(*cfg);
-    opt.calc_compensations = cfg->calc_compensations;
-    opt.want_rgb = mode_channels(cfg->render_mode) != 1;
-    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, opt, cfg_model(*cfg), cfg->tile_size, tw,
-                             th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records, w.bounds,
-                             reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
-    if (rc != LFS_OK) return rc;
-    TileListArgs a{};
-    a.C = 1; a.N = cfg->N; a.tw = tw; a.th = th; a.tile_size = cfg->tile_size; a.sort = 1; a.keys_ready = 1;
-    a.means2d = w.means2d; a.radii = w.radii; a.depths = w.depths; a.tiles = w.tiles;
-    for (int k = 0; k < 2; ++k) { a.gkeys[k] = w.gkeys[k]; a.gvals[k] = w.gvals[k]; a.tkeys[k] = w.tkeys[k]; a.tvals[k] = w.tvals[k]; }
-    a.offs = w.offs; a.n_isects_dev = w.counters + 1; a.capacity = cfg->isect_capacity; a.overflow = w.counters + 0;
     int sel = 0;
-    a.sel_out = &sel;
-    a.tile_offsets = w.tile_offsets; a.scratch = w.scratch;
-    rc = build_tile_lists(a, st);
+    rc = render_forward_lists(cfg, params, viewmat, K, 1, w, &sel, st);
     if (rc != LFS_OK) return rc;
-    rc = launch_tile_order(tw * th, w.tile_offsets, w.tile_order, st);
+    rc = render_forward_blend(cfg, background, render, alpha, status_dev, w, sel, st);
     if (rc != LFS_OK) return rc;
-    RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
-                  cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
-                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order};
-    rc = launch_raster_fwd(ra, render, alpha, w.last_ids, w.extra_sum, st);
-    if (rc != LFS_OK) return rc;
-    if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
     return check_launch("lfs_render_forward");
+}
+
+int lfs_render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && viewmat && K && workspace, "null pointer");
+    LFS_REQUIRE(aligned16(params->rotation_raw), "rotation_raw must be 16-byte aligned");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_render_forward_lists: workspace too small"); return LFS_ECAPACITY; }
+    int sel = 0;
+    rc = render_forward_lists(cfg, params, viewmat, K, 0, w, &sel, S(stream));
+    if (rc != LFS_OK) return rc;
+    return check_launch("lfs_render_forward_lists");
+}
+
+int lfs_render_forward_shade(const lfs_render_config* cfg, const lfs_splats* params, const float* background, float* render,
+                             float* alpha, int32_t* status_dev, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && render && alpha && workspace, "null pointer");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_render_forward_shade: workspace too small"); return LFS_ECAPACITY; }
+    cudaStream_t st = S(stream);
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
+    if (mode_channels(cfg->render_mode) != 1) {
+        rc = launch_sh_color(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, w.radii, w.records, st);
+        if (rc != LFS_OK) return rc;
+    }
+    rc = render_forward_blend(cfg, background, render, alpha, status_dev, w, sel, st);
+    if (rc != LFS_OK) return rc;
+    return check_launch("lfs_render_forward_shade");
 }
 
 int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, const float* background, const float* alpha,

@@ -516,6 +516,69 @@ __global__ void __launch_bounds__(256, 3) project_pack_kernel(
     if (lane == 0 && local_visible) atomicAdd(n_visible, local_visible);
 }
 
+// Colours of the visible Gaussians into their packed records, for callers that build the tile lists first
+// (project_pack with want_rgb = 0) and shade later, e.g. while the SH coefficients are still being updated on another
+// stream. Same arithmetic and staging as the colour part of project_pack_kernel.
+__global__ void __launch_bounds__(256) sh_color_kernel(int N, int K, int sh_degree, const float* __restrict__ means,
+                                                       const float* __restrict__ sh0, const float* __restrict__ shN,
+                                                       const CamDev* __restrict__ cams, const int32_t* __restrict__ radii,
+                                                       float4* __restrict__ records) {
+    extern __shared__ __align__(16) float s_rows[];
+    const float cx = cams[0].campos[0], cy = cams[0].campos[1], cz = cams[0].campos[2];
+    const int rest = (K - 1) * 3;
+    const int nb = (sh_degree + 1) * (sh_degree + 1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my = s_rows + (size_t)warp * 32 * rest;
+    const int n_chunks = (N + 31) / 32;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    const bool sh_aligned = (reinterpret_cast<uintptr_t>(shN) & 15) == 0 && ((32 * rest) & 3) == 0;
+    for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
+        const int g = chunk * 32 + lane;
+        const bool vis = g < N && radii[g * 2] > 0 && radii[g * 2 + 1] > 0;
+        if (!__any_sync(0xffffffffu, vis)) continue;
+        if (nb > 1) {
+            const int total = min(32, N - chunk * 32) * rest;
+            const float* src = shN + (size_t)chunk * 32 * rest;
+            const int total16 = sh_aligned ? (total >> 2) : 0;
+            for (int i = lane; i < total16; i += 32) {
+                const unsigned dst = (unsigned)__cvta_generic_to_shared(my + i * 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src + i * 4));
+            }
+            asm volatile("cp.async.commit_group;\n" ::);
+            for (int i = total16 * 4 + lane; i < total; i += 32) my[i] = src[i];
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncwarp();
+        if (vis) {
+            float B[25];
+            sh_basis(sh_degree, means[g * 3] - cx, means[g * 3 + 1] - cy, means[g * 3 + 2] - cz, B);
+            float rgb[3];
+#pragma unroll
+            for (int c = 0; c < 3; ++c) rgb[c] = B[0] * sh0[g * 3 + c];
+            const float* row = my + lane * rest;
+            for (int k = 1; k < nb; ++k) {
+#pragma unroll
+                for (int c = 0; c < 3; ++c) rgb[c] += B[k] * row[(k - 1) * 3 + c];
+            }
+            float* out = reinterpret_cast<float*>(records + (size_t)g * 4 + 3);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) out[c] = fmaxf(rgb[c] + 0.5f, 0.0f);
+        }
+        __syncwarp();
+    }
+}
+
+int launch_sh_color(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const int32_t* radii, float4* records,
+                    cudaStream_t st) {
+    if (N == 0) return LFS_OK;
+    const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
+    if (smem > 200 * 1024) { set_error("sh_color: too many SH coefficients"); return LFS_EINVAL; }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(sh_color_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    LFS_TIMED("sh_color", st);
+    sh_color_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, cam, radii, records);
+    return check_launch("sh_color");
+}
+
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
                         const PackOptions& opt, int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
                         int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,

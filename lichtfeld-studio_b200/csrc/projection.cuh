@@ -44,6 +44,10 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
                         int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st);
 
+// colours (SH + 0.5, clamped at 0) of the visible Gaussians into records[g*4+3].xyz
+int launch_sh_color(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const int32_t* radii, float4* records,
+                    cudaStream_t st);
+
 int launch_tile_count(int64_t total, const float* means2d, const int32_t* radii, int tile_size, int tw, int th,
                       int32_t* tiles, cudaStream_t st);
 

@@ -183,6 +183,27 @@ class Rasterizer:
         depth = None if self.channels == 3 else self.render[..., self.channels - 1:]
         return RenderOutput(image, self.alpha, self.W, self.H, self.status, depth, self.render)
 
+    def forward_lists(self, cam: Camera):
+        """First half of forward(): per-Gaussian stage without colours and the tile lists. Needs only means, scales,
+        rotations and opacities, so it can run while the SH tensors are still being updated on another stream."""
+        if cam.width != self.W or cam.height != self.H:
+            raise RuntimeError("camera size does not match the rasterizer")
+        self.cfg.N = self.model.size
+        self.cfg.camera_model = int(cam.camera_model)
+        self.cfg.radial_coeffs, self.cfg.tangential_coeffs, self.cfg.thin_prism_coeffs = cam.coefficient_pointers()
+        p = self.model.struct()
+        call("lfs_render_forward_lists", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), ptr(self.ws), self.ws.numel(),
+             _stream())
+
+    def forward_shade(self, background: torch.Tensor | None) -> RenderOutput:
+        """Second half: SH colours of the visible Gaussians, then blending. forward_lists + forward_shade == forward."""
+        p = self.model.struct()
+        call("lfs_render_forward_shade", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.render), ptr(self.alpha),
+             ptr(self.status), ptr(self.ws), self.ws.numel(), _stream())
+        image = self.render if self.channels == 3 else (self.render[..., :3].contiguous() if self.channels == 4 else None)
+        depth = None if self.channels == 3 else self.render[..., self.channels - 1:]
+        return RenderOutput(image, self.alpha, self.W, self.H, self.status, depth, self.render)
+
     def backward(self, v_render: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
                  v_alpha: torch.Tensor | None = None, accumulate: bool = False):
         p, g = self.model.struct(), grads.struct()
@@ -312,6 +333,29 @@ class PhotometricLoss:
         call("lfs_photometric_loss", self.H, self.W, self.lam, float(grad_scale), ptr(render_hwc), ptr(target_chw),
              ptr(self.v_render) if want_grad else None, ptr(self.loss), ptr(self.ws), self.ws.numel(), _stream())
         return self.loss, self.v_render
+
+
+GEOMETRY_GROUPS = ("means", "scaling_raw", "rotation_raw", "opacity_raw")   # what the tile lists depend on
+COLOR_GROUPS = ("sh0", "shN")
+
+
+def adam_step_groups(model: SplatData, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
+                     groups, beta1=0.9, beta2=0.999, eps=1e-15, grad_scale=1.0):
+    """The fused Adam on a subset of the six parameter groups (one launch). Splitting FusedAdam::step into the geometry
+    groups and the colour groups lets the colour update (three quarters of the bytes) run on a second stream while the
+    next step's projection and tile lists are built from the geometry groups."""
+    segs = []
+    for name in groups:
+        gi = PARAM_NAMES.index(name)
+        n = model.size * model._w[name]
+        if n == 0:
+            continue
+        segs.append(capi.AdamSegment(model._full[name].data_ptr(), exp_avg._full[name].data_ptr(), exp_avg_sq._full[name].data_ptr(),
+                                     grads._full[name].data_ptr(), n, float(lrs[gi])))
+    if not segs:
+        return
+    arr = (capi.AdamSegment * len(segs))(*segs)
+    call("lfs_adam_step_segments", len(segs), arr, float(beta1), float(beta2), float(eps), int(step_count), float(grad_scale), _stream())
 
 
 def regularization(model: SplatData, grads: SplatData, scale_reg: float, opacity_reg: float, out: torch.Tensor | None = None):

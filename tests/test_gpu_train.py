@@ -9,6 +9,7 @@ from conftest import make_scene, rel_l2
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+NAMES = ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")
 
 
 def T(a):
@@ -115,3 +116,35 @@ def test_isect_overflow_is_reported(pkg, orc, synth):
     torch.cuda.synchronize()
     st = out.status.cpu().numpy()
     assert st[0] == 1 and st[1] > 100
+
+
+def test_split_forward_and_split_adam_equal_the_fused_calls(pkg, synth):
+    """forward_lists + forward_shade == forward and Adam(geometry groups) + Adam(colour groups) == Adam(all), bit for bit."""
+    tr = pkg.trainer
+    n, W, H, deg = 12000, 200, 120, 3
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=12)
+    model = tr.SplatData(n, 16, DEV).load(P)
+    cam = tr.Camera(T(vm), T(K), W, H)
+    bg = T(np.array([0.3, 0.1, 0.6], np.float32))
+    a = tr.Rasterizer(model, W, H, deg)
+    b = tr.Rasterizer(model, W, H, deg)
+    out_a = a.forward(cam, bg)
+    b.forward_lists(cam)
+    out_b = b.forward_shade(bg)
+    assert torch.equal(out_a.image, out_b.image) and torch.equal(out_a.alpha, out_b.alpha)
+    sa, sb = a.state(), b.state()
+    vis = (sa["radii"] > 0).all(-1)   # records of culled Gaussians are never written
+    assert torch.equal(sa["radii"], sb["radii"]) and torch.equal(sa["records"][vis], sb["records"][vis])
+    rng = np.random.default_rng(0)
+    v = T(rng.normal(size=(H, W, 3)).astype(np.float32))
+    ga, gb = model.like(), model.like()
+    a.backward(v, ga, bg)
+    b.backward(v, gb, bg)
+    for name in NAMES:
+        assert rel_l2(ga.tensor(name).cpu().numpy(), gb.tensor(name).cpu().numpy()) < 1e-5, name
+    m1, v1, m2, v2 = model.like(), model.like(), model.like(), model.like()
+    model2 = tr.SplatData(n, 16, DEV).load(P)
+    tr.adam_step_splats(model, m1, v1, ga, LRS, 3)
+    tr.adam_step_groups(model2, m2, v2, ga, LRS, 3, tr.GEOMETRY_GROUPS)
+    tr.adam_step_groups(model2, m2, v2, ga, LRS, 3, tr.COLOR_GROUPS)
+    assert torch.equal(model.flat, model2.flat) and torch.equal(m1.flat, m2.flat) and torch.equal(v1.flat, v2.flat)
