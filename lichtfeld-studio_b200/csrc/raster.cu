@@ -192,7 +192,10 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
 #pragma unroll
             for (int w = 0; w < BATCH / 32; ++w) {
                 uint32_t bits = live[w];
-                while (bits && !done) {
+                // Every lane evaluates the entry (the record reads are warp-wide broadcasts); lanes that are finished,
+                // below the power threshold or below the alpha threshold carry alpha = 0, which leaves their state
+                // untouched, so the body has no per-lane branches.
+                while (bits) {
                     const int t = w * 32 + __ffs(bits) - 1;
                     bits &= bits - 1;
                     const float4 r0 = st.rec[t * 4 + 0], r1 = st.rec[t * 4 + 1], r2 = st.rec[t * 4 + 2];
@@ -205,18 +208,20 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
                     const float cc = cx * cx + cy * cy + cz * cz;
                     const float uu = ux * ux + uy * uy + uz * uz;
                     // power = -0.5 cc / uu ; reject when power < thr  <=>  cc > -2 thr uu
-                    if (cc > -2.0f * __uint_as_float(st.box[t].z) * uu) continue;
+                    bool valid = !done && !(cc > -2.0f * __uint_as_float(st.box[t].z) * uu);
+                    if (!__any_sync(0xffffffffu, valid)) continue;
                     const float4 r3 = st.rec[t * 4 + 3];
                     const float power = -0.5f * __fdividef(cc, fmaxf(uu, 1e-37f));
-                    const float alpha = fminf(0.999f, r3.w * __expf(power));
-                    if (alpha < kAlphaMin) continue;
+                    float alpha = fminf(0.999f, r3.w * __expf(power));
+                    valid = valid && !(alpha < kAlphaMin);
                     const float next_T = T * (1.0f - alpha);
-                    if (next_T <= 1e-4f) { done = true; break; }
+                    if (valid && next_T <= 1e-4f) { done = true; valid = false; }
+                    if (!valid) alpha = 0.f;
                     const float vis = alpha * T;
                     pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
                     if (EXTRA) px += __uint_as_float(st.box[t].w) * vis;
-                    cur_idx = (uint32_t)(batch_start + t);
-                    T = next_T;
+                    if (valid) { cur_idx = (uint32_t)(batch_start + t); T = next_T; }
+                    if (__all_sync(0xffffffffu, done)) break;
                 }
             }
         }
