@@ -192,10 +192,7 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
 #pragma unroll
             for (int w = 0; w < BATCH / 32; ++w) {
                 uint32_t bits = live[w];
-                // Every lane evaluates the entry (the record reads are warp-wide broadcasts); lanes that are finished,
-                // below the power threshold or below the alpha threshold carry alpha = 0, which leaves their state
-                // untouched, so the body has no per-lane branches.
-                while (bits) {
+                while (bits && !done) {
                     const int t = w * 32 + __ffs(bits) - 1;
                     bits &= bits - 1;
                     const float4 r0 = st.rec[t * 4 + 0], r1 = st.rec[t * 4 + 1], r2 = st.rec[t * 4 + 2];
@@ -208,20 +205,18 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
                     const float cc = cx * cx + cy * cy + cz * cz;
                     const float uu = ux * ux + uy * uy + uz * uz;
                     // power = -0.5 cc / uu ; reject when power < thr  <=>  cc > -2 thr uu
-                    bool valid = !done && !(cc > -2.0f * __uint_as_float(st.box[t].z) * uu);
-                    if (!__any_sync(0xffffffffu, valid)) continue;
+                    if (cc > -2.0f * __uint_as_float(st.box[t].z) * uu) continue;
                     const float4 r3 = st.rec[t * 4 + 3];
                     const float power = -0.5f * __fdividef(cc, fmaxf(uu, 1e-37f));
-                    float alpha = fminf(0.999f, r3.w * __expf(power));
-                    valid = valid && !(alpha < kAlphaMin);
+                    const float alpha = fminf(0.999f, r3.w * __expf(power));
+                    if (alpha < kAlphaMin) continue;
                     const float next_T = T * (1.0f - alpha);
-                    if (valid && next_T <= 1e-4f) { done = true; valid = false; }
-                    if (!valid) alpha = 0.f;
+                    if (next_T <= 1e-4f) { done = true; break; }
                     const float vis = alpha * T;
                     pr += r3.x * vis; pg += r3.y * vis; pb += r3.z * vis;
                     if (EXTRA) px += __uint_as_float(st.box[t].w) * vis;
-                    if (valid) { cur_idx = (uint32_t)(batch_start + t); T = next_T; }
-                    if (__all_sync(0xffffffffu, done)) break;
+                    cur_idx = (uint32_t)(batch_start + t);
+                    T = next_T;
                 }
             }
         }
