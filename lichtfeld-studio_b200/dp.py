@@ -47,6 +47,34 @@ def group_segments(capacity: int, K: int, lo: int, n: int, lrs, skip_shN: bool =
     return out
 
 
+GEOMETRY_CLASS = ("means", "scaling_raw", "rotation_raw", "opacity_raw")   # what projection and tile lists read
+COLOR_CLASS = ("sh0", "shN")
+
+
+def class_segments(capacity: int, K: int, names, world: int, rank: int, lrs, skip_shN: bool = False, align: int = 4):
+    """Shard the groups `names` (a class of parameter groups) over `world` ranks: the class's flat ranges are laid end
+    to end, cut into equal shards (rounded up to `align` elements) and mapped back to the flat buffer.
+    Returns (segments [(group index, flat offset, count, lr, offset inside this rank's class shard)], shard length).
+    Every element of the class belongs to exactly one rank. The partition does not depend on skip_shN (the moments
+    keep their place); a skipped shN group only drops its segments."""
+    w = row_widths(K)
+    ranges, off = [], 0
+    for gi, name in enumerate(PARAM_NAMES):
+        size = capacity * w[name]
+        if name in names and size > 0:
+            ranges.append((gi, off, size))
+        off += size
+    total = sum(r[2] for r in ranges)
+    lo, n, per = shard_bounds(total, world, rank, align)
+    out, pos = [], 0
+    for gi, goff, size in ranges:
+        a, b = max(lo, pos), min(lo + n, pos + size)
+        if b > a and not (skip_shN and PARAM_NAMES[gi] == "shN"):
+            out.append((gi, goff + (a - pos), b - a, float(lrs[gi]), a - lo))
+        pos += size
+    return out, per
+
+
 class GradExchange:
     """Owns the sharded optimizer state and performs exchange + Adam for one rank."""
 
@@ -72,6 +100,7 @@ class GradExchange:
                 raise RuntimeError("fused_p2p needs the peer-mapped addresses of every rank's parameter and gradient buffers")
             self.peer_grads, self.peer_params = peer_ptrs
         self.step_count = 0
+        self._split = None   # lazily built state of step_split()
 
     # -- helpers --------------------------------------------------------------------------------
     def _stream(self):
@@ -155,6 +184,64 @@ class GradExchange:
             dist.all_reduce(token, group=self.group)
             return
         raise ValueError(self.mode)
+
+    # -- split exchange: geometry groups now, colour groups under the next step's projection and sorting -------
+    def _split_state(self, side_stream):
+        if self._split is None:
+            dev = self.model.flat.device
+            st = {"side": side_stream, "group_b": dist.new_group() if self.world > 1 else None,
+                  "ev_grads": torch.cuda.Event(), "ev_color": torch.cuda.Event(), "pending": False}
+            for cls, names in (("geo", GEOMETRY_CLASS), ("col", COLOR_CLASS)):
+                _, per = class_segments(self.model.capacity, self.model.K, names, self.world, self.rank, self.lrs)
+                st[cls + "_m"] = torch.zeros(max(per, 4), dtype=torch.float32, device=dev)
+                st[cls + "_v"] = torch.zeros(max(per, 4), dtype=torch.float32, device=dev)
+            st["token_a"] = torch.zeros(1, device=dev)
+            st["token_b"] = torch.zeros(1, device=dev)
+            self._split = st
+        return self._split
+
+    def _fused_call(self, segs, m, v, gs):
+        arr = (capi.DpSegment * max(len(segs), 1))()
+        for i, (gi, off, cnt, lr, rel) in enumerate(segs):
+            arr[i] = capi.DpSegment(off, cnt, m.data_ptr() + 4 * rel, v.data_ptr() + 4 * rel, lr)
+        order = [(self.rank + i) % self.world for i in range(self.world)]
+        pg = (C.c_void_p * self.world)(*[self.peer_grads[r] for r in order])
+        pp = (C.c_void_p * self.world)(*[self.peer_params[r] for r in order])
+        capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
+                  self.step_count, float(gs), self._stream())
+
+    def step_split(self, iteration: int, side_stream, grad_scale: float | None = None):
+        """fused_p2p in two parts. On the current stream: rendezvous, reduce + Adam + broadcast of the geometry groups
+        (means, scales, rotations, opacities), rendezvous. On `side_stream`: the same for the colour groups (sh0, shN:
+        three quarters of the bytes), finishing with its own rendezvous on a second communicator. The caller may start
+        the next step's projection and tile lists right away and must call wait_color() before anything reads the
+        colour groups or overwrites the gradients."""
+        if self.mode != "fused_p2p":
+            raise RuntimeError("step_split needs mode fused_p2p")
+        st = self._split_state(side_stream)
+        self.step_count += 1
+        gs = 1.0 / self.world if grad_scale is None else grad_scale
+        model = self.model
+        skip = iteration <= 1000
+        main = torch.cuda.current_stream()
+        # every rank's backward has written its gradients
+        dist.all_reduce(st["token_a"], group=self.group)
+        st["ev_grads"].record(main)
+        segs, _ = class_segments(model.capacity, model.K, GEOMETRY_CLASS, self.world, self.rank, self.lrs)
+        self._fused_call(segs, st["geo_m"], st["geo_v"], gs)
+        dist.all_reduce(st["token_a"], group=self.group)      # every rank's geometry kernel has finished
+        with torch.cuda.stream(st["side"]):
+            st["side"].wait_event(st["ev_grads"])
+            segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
+            self._fused_call(segs, st["col_m"], st["col_v"], gs)
+            dist.all_reduce(st["token_b"], group=st["group_b"])  # every rank's colour kernel has finished
+            st["ev_color"].record(st["side"])
+        st["pending"] = True
+
+    def wait_color(self):
+        """Make the current stream wait for the colour part of the last step_split()."""
+        if self._split is not None and self._split["pending"]:
+            torch.cuda.current_stream().wait_event(self._split["ev_color"])
 
 
 def symmetric_flat_buffers(numel: int, device, group=None):

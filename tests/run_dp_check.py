@@ -41,7 +41,7 @@ def main():
         cap = (n + 31) // 32 * 32
         numel = cap * tr.SplatData(1, K, "cpu").row_floats
         peer = None
-        if mode == "fused_p2p":
+        if mode.startswith("fused_p2p"):
             pf, gf, peer = dp.symmetric_flat_buffers(numel, dev)
             model, grads = tr.SplatData(n, K, dev, cap, flat=pf).load(P), tr.SplatData(n, K, dev, cap, flat=gf)
         else:
@@ -56,6 +56,20 @@ def main():
                     rast.backward(vr, grads, bg, accumulate=(r > 0))
                 tr.adam_step_splats(model, m, v, grads, LRS, s + 1, skip_shN=False, grad_scale=1.0 / world)
             return model.flat.clone()
+        if mode == "fused_p2p_split":
+            # geometry groups exchanged on the main stream, colour groups on a side stream under the next step's lists
+            ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
+            side = torch.cuda.Stream(device=dev)
+            for s in range(steps):
+                rast.forward_lists(cam(s * world + rank))
+                ex.wait_color()
+                out = rast.forward_shade(bg)
+                _, vr = lossfn(out.image, targets[s * world + rank])
+                rast.backward(vr, grads, bg)
+                ex.step_split(2000 + s, side)
+            ex.wait_color()
+            torch.cuda.synchronize()
+            return model.flat.clone()
         ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer)
         for s in range(steps):
             out = rast.forward(cam(s * world + rank), bg)
@@ -67,7 +81,7 @@ def main():
 
     ref = run("local")
     ok = True
-    for mode in ("allreduce", "sharded", "fused_p2p"):
+    for mode in ("allreduce", "sharded", "fused_p2p", "fused_p2p_split"):
         try:
             out = run(mode)
         except Exception as e:  # report and keep the ranks in lock step

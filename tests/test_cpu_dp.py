@@ -79,3 +79,32 @@ def test_exchange_modes_agree_under_gloo(pkg, orc, tmp_path, mode):
             orc.adam_step(model.flat[off:off + cnt].numpy(), m[off:off + cnt].numpy(), v[off:off + cnt].numpy(),
                           (g[off:off + cnt].numpy() * np.float32(0.5)).astype(np.float32), lr, 0.9, 0.999, 1e-15, step)
     assert torch.allclose(outs[0], model.flat, rtol=1e-6, atol=1e-7)
+
+
+def test_class_segments_partition_each_class_exactly_once(pkg):
+    """The split exchange shards the geometry class and the colour class separately: over all ranks every element of
+    a class is covered exactly once, offsets and counts stay 4-element aligned, moments offsets are consistent, and
+    skipping shN only removes segments."""
+    dp, tr = pkg.dp, pkg.trainer
+    for capacity, K, world in ((1000, 16, 8), (64, 4, 3), (20, 1, 2), (4096, 25, 5)):
+        w = tr.row_widths(K)
+        total = capacity * sum(w.values())
+        lrs = [1, 2, 3, 4, 5, 6]
+        for names in (dp.GEOMETRY_CLASS, dp.COLOR_CLASS):
+            cover = np.zeros(total, np.int32)
+            for rank in range(world):
+                segs, per = dp.class_segments(capacity, K, names, world, rank, lrs)
+                segs_skip, per2 = dp.class_segments(capacity, K, names, world, rank, lrs, skip_shN=True)
+                assert per == per2 and len(segs) <= 6
+                assert [s for s in segs if tr.PARAM_NAMES[s[0]] != "shN"] == segs_skip
+                used = 0
+                for gi, off, cnt, lr, rel in segs:
+                    assert cnt > 0 and off % 4 == 0 and rel % 4 == 0 and lr == lrs[gi] and rel + cnt <= per
+                    assert rel == used          # the shard's moments are laid out in segment order
+                    used += cnt
+                    cover[off:off + cnt] += 1
+            off = 0
+            for name in tr.PARAM_NAMES:
+                size = capacity * w[name]
+                assert (cover[off:off + size] == (1 if name in names else 0)).all(), name
+                off += size
