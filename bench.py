@@ -254,7 +254,7 @@ def run_ours(args):
     overlap = world == 1 and args.overlap
     state = {"color_pending": False}
 
-    dp_split = world > 1 and args.dp_mode == "fused_p2p" and args.dp_split
+    dp_split = world > 1 and args.dp_mode == "fused_p2p" and not args.no_dp_split
 
     def step(s, target, vm):
         cam = tr.Camera(vm, Kt, W, H)
@@ -650,9 +650,10 @@ def main():
     ap.add_argument("--overlap", action="store_true",
                     help="single GPU: split optimizer, colour groups on a side stream under the next step's projection and "
                          "tile lists (measured: no gain on B200, 2.975 ms against 2.964 ms; both sides are memory-latency sensitive)")
-    ap.add_argument("--dp-split", action="store_true",
-                    help="N > 1, fused_p2p: exchange the geometry groups first and the colour groups on a side stream under the "
-                         "next step's projection and tile lists (measured: 3.373 ms against 3.391 ms at 4 GPUs, no gain at 2)")
+    ap.add_argument("--no-dp-split", action="store_true",
+                    help="N > 1, fused_p2p: exchange all groups in one kernel after the backward. Default: geometry groups first, "
+                         "colour groups on a side stream (one CTA per SM) under the next step's projection and tile lists "
+                         "(3.27 ms against 3.39 ms at 4 GPUs)")
     ap.add_argument("--dp-mode", default="fused_p2p", choices=["allreduce", "sharded", "fused_p2p"],
                     help="gradient exchange for N > 1 (see lichtfeld-studio_b200/dp.py)")
     args = ap.parse_args()

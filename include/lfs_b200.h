@@ -322,6 +322,8 @@ int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segments /* h
  * pointers) are the peer-mapped FULL flat buffers of rank (own_rank + i) % world, i.e. entry 0 is this
  * rank's own buffer (the parameters are read from it; the sum runs in that rotated order); offset / n / lr / moments per segment describe
  * the shard (offsets in elements from the start of the flat buffers; moments are shard-local buffers).
+ * ctas_per_sm: launch footprint, 0 = default (16 CTAs of 256 threads per SM); the kernel is NVLink-bound and keeps its
+ * speed with 2 - 4, which leaves thread slots for kernels running next to it on other streams.
  * The caller must order it against the other ranks: every rank's backward finished before, nobody reads
  * parameters or rewrites gradients until all ranks finished after (e.g. a stream-ordered barrier). Plain
  * peer loads / stores only; no multicast. */
@@ -334,7 +336,7 @@ typedef struct lfs_dp_segment {
 } lfs_dp_segment;
 int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,
                                  const lfs_dp_segment* segments /* host */, double beta1, double beta2, double eps,
-                                 int64_t step_count, float grad_scale, void* stream);
+                                 int64_t step_count, float grad_scale, int ctas_per_sm, void* stream);
 
 /* ------------------------------------------------------------------------------------------ */
 /* MCMC densification index work (src/training/strategies/mcmc.cpp:112-347)                    */

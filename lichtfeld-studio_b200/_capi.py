@@ -100,7 +100,7 @@ _SIGNATURES = {
     "lfs_regularization": [i32, vp, vp, f32, f32, vp, vp, vp, vp],
     "lfs_adam_step_segments": [i32, C.POINTER(AdamSegment), C.c_double, C.c_double, C.c_double, i64, f32, vp],
     "lfs_dp_reduce_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, C.POINTER(DpSegment), C.c_double,
-                                     C.c_double, C.c_double, i64, f32, vp],
+                                     C.c_double, C.c_double, i64, f32, i32, vp],
     "lfs_mcmc_classify": [i32, vp, vp, f32, vp, vp, vp, vp, vp, sz, vp],
     "lfs_mcmc_classify_noalloc": [i32, vp, vp, f32, vp, vp, vp, vp, vp],
     "lfs_mcmc_map_indices": [i32, vp, vp, vp, vp],

@@ -486,7 +486,7 @@ int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segs, double 
 
 int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,
                                  const lfs_dp_segment* segs, double beta1, double beta2, double eps, int64_t step_count,
-                                 float grad_scale, void* stream) {
+                                 float grad_scale, int ctas_per_sm, void* stream) {
     LFS_REQUIRE(world >= 1 && world <= kMaxPeers, "world must be in [1, 8]");
     LFS_REQUIRE(n_segments >= 0 && n_segments <= 6, "at most 6 segments");
     LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
@@ -517,7 +517,8 @@ int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, floa
     }
     A.n_segments = ns;
     A.beta1 = (float)beta1; A.beta2 = (float)beta2; A.eps = (float)eps; A.bc2_sqrt_rcp = (float)bc2; A.grad_scale = grad_scale;
-    return launch_dp_reduce_adam_broadcast(A, S_(stream));
+    LFS_REQUIRE(ctas_per_sm >= 0 && ctas_per_sm <= 16, "ctas_per_sm must be in [0, 16]");
+    return launch_dp_reduce_adam_broadcast(A, ctas_per_sm, S_(stream));
 }
 
 int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,

@@ -43,7 +43,7 @@ struct DpArgs {
     int world, n_segments;
     float beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
 };
-int launch_dp_reduce_adam_broadcast(const DpArgs& A, cudaStream_t st);
+int launch_dp_reduce_adam_broadcast(const DpArgs& A, int ctas_per_sm, cudaStream_t st);
 int launch_regularization(int N, const float* scaling_raw, const float* opacity_raw, float scale_weight, float opacity_weight,
                           float* g_scaling, float* g_opacity, float* loss, cudaStream_t st);
 int launch_sh_fwd(int n, int K, int degree, const float* dirs, const float* coeffs, const uint8_t* masks, float* colors, cudaStream_t st);

@@ -15,6 +15,7 @@ contiguous shard intersects at most six groups, each with its own learning rate.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -101,6 +102,7 @@ class GradExchange:
             self.peer_grads, self.peer_params = peer_ptrs
         self.step_count = 0
         self._split = None   # lazily built state of step_split()
+        self.color_ctas_per_sm = int(os.environ.get("LFS_DP_COLOR_CTAS", "1"))   # launch footprint of the overlapped part
 
     # -- helpers --------------------------------------------------------------------------------
     def _stream(self):
@@ -179,7 +181,7 @@ class GradExchange:
             pg = (C.c_void_p * self.world)(*[self.peer_grads[r] for r in order])
             pp = (C.c_void_p * self.world)(*[self.peer_params[r] for r in order])
             capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
-                      self.step_count, float(gs), self._stream())
+                      self.step_count, float(gs), 0, self._stream())
             # nobody may read parameters or overwrite gradients before every rank's kernel has finished
             dist.all_reduce(token, group=self.group)
             return
@@ -200,7 +202,7 @@ class GradExchange:
             self._split = st
         return self._split
 
-    def _fused_call(self, segs, m, v, gs):
+    def _fused_call(self, segs, m, v, gs, ctas_per_sm=0):
         arr = (capi.DpSegment * max(len(segs), 1))()
         for i, (gi, off, cnt, lr, rel) in enumerate(segs):
             arr[i] = capi.DpSegment(off, cnt, m.data_ptr() + 4 * rel, v.data_ptr() + 4 * rel, lr)
@@ -208,7 +210,7 @@ class GradExchange:
         pg = (C.c_void_p * self.world)(*[self.peer_grads[r] for r in order])
         pp = (C.c_void_p * self.world)(*[self.peer_params[r] for r in order])
         capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
-                  self.step_count, float(gs), self._stream())
+                  self.step_count, float(gs), int(ctas_per_sm), self._stream())
 
     def step_split(self, iteration: int, side_stream, grad_scale: float | None = None):
         """fused_p2p in two parts. On the current stream: rendezvous, reduce + Adam + broadcast of the geometry groups
@@ -233,7 +235,8 @@ class GradExchange:
         with torch.cuda.stream(st["side"]):
             st["side"].wait_event(st["ev_grads"])
             segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
-            self._fused_call(segs, st["col_m"], st["col_v"], gs)
+            # small footprint: this kernel shares the SMs with the next step's projection and sorting
+            self._fused_call(segs, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
             dist.all_reduce(st["token_b"], group=st["group_b"])  # every rank's colour kernel has finished
             st["ev_color"].record(st["side"])
         st["pending"] = True
