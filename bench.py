@@ -285,7 +285,7 @@ def run_ours(args):
         tr.adam_step_groups(model, m, v, grads, LRS, s + 1, tr.GEOMETRY_GROUPS)
         with torch.cuda.stream(side):
             side.wait_event(ev_bwd)
-            tr.adam_step_groups(model, m, v, grads, LRS, s + 1, tr.COLOR_GROUPS)
+            tr.adam_step_groups(model, m, v, grads, LRS, s + 1, tr.COLOR_GROUPS, ctas_per_sm=args.overlap_ctas)
             ev_color.record(side)
         state["color_pending"] = True
         return loss
@@ -647,6 +647,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--overlap-ctas", type=int, default=2, help="launch footprint (CTAs per SM) of the overlapped colour-group Adam")
     ap.add_argument("--overlap", action="store_true",
                     help="single GPU: split optimizer, colour groups on a side stream under the next step's projection and "
                          "tile lists (measured: no gain on B200, 2.975 ms against 2.964 ms; both sides are memory-latency sensitive)")

@@ -311,8 +311,10 @@ typedef struct lfs_adam_segment {
     int64_t n;
     float lr;
 } lfs_adam_segment;
+/* ctas_per_sm: launch footprint, 0 = default (16 CTAs of 256 threads per SM); a small value leaves thread slots for
+ * kernels that run next to this one on other streams. */
 int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segments /* host */, double beta1, double beta2,
-                           double eps, int64_t step_count, float grad_scale, void* stream);
+                           double eps, int64_t step_count, float grad_scale, int ctas_per_sm, void* stream);
 
 /* Data-parallel exchange fused with the optimizer (no counterpart in the reference, which is single-GPU):
  * ONE kernel that, for this rank's shard of the flat parameter buffer, loads the gradient of every rank

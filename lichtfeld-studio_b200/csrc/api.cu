@@ -459,7 +459,8 @@ int lfs_regularization(int N, const float* scaling_raw, const float* opacity_raw
 }
 
 int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segs, double beta1, double beta2, double eps,
-                           int64_t step_count, float grad_scale, void* stream) {
+                           int64_t step_count, float grad_scale, int ctas_per_sm, void* stream) {
+    LFS_REQUIRE(ctas_per_sm >= 0 && ctas_per_sm <= 16, "ctas_per_sm must be in [0, 16]");
     LFS_REQUIRE(n_segments >= 0 && n_segments <= kMaxAdamSegments, "at most 16 segments");
     LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
     if (n_segments == 0) return LFS_OK;
@@ -481,7 +482,7 @@ int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segs, double 
     }
     S.n = ng;
     S.beta1 = (float)beta1; S.beta2 = (float)beta2; S.eps = (float)eps; S.bc2_sqrt_rcp = (float)bc2; S.grad_scale = grad_scale;
-    return launch_adam_segments(S, S_(stream));
+    return launch_adam_segments(S, ctas_per_sm, S_(stream));
 }
 
 int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,

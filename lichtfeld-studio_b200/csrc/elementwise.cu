@@ -361,11 +361,11 @@ int launch_adam_groups(const AdamGroups& G, cudaStream_t st) {
     return check_launch("adam_groups");
 }
 
-int launch_adam_segments(const AdamSegments& S, cudaStream_t st) {
+int launch_adam_segments(const AdamSegments& S, int ctas_per_sm, cudaStream_t st) {
     const int64_t total4 = S.prefix4[S.n];
     if (total4 == 0) return LFS_OK;
     LFS_TIMED("adam", st);
-    adam_segments_kernel<<<grid_for(total4, 256, 16), 256, 0, st>>>(S);
+    adam_segments_kernel<<<grid_for(total4, 256, ctas_per_sm > 0 ? ctas_per_sm : 16), 256, 0, st>>>(S);
     return check_launch("adam_segments");
 }
 

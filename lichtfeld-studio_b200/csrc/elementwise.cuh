@@ -27,7 +27,7 @@ struct AdamSegments {
     int n;
     float beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
 };
-int launch_adam_segments(const AdamSegments& S, cudaStream_t st);
+int launch_adam_segments(const AdamSegments& S, int ctas_per_sm, cudaStream_t st);
 
 constexpr int kMaxPeers = 8;
 struct DpSegment {

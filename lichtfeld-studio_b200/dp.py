@@ -117,7 +117,7 @@ class GradExchange:
             arr[i] = capi.AdamSegment(base + 4 * off, self.m.data_ptr() + 4 * rel, self.v.data_ptr() + 4 * rel,
                                       grad_shard.data_ptr() + 4 * rel, cnt, lr)
         capi.call("lfs_adam_step_segments", len(segs), arr, self.betas[0], self.betas[1], self.eps, self.step_count,
-                  float(grad_scale), self._stream())
+                  float(grad_scale), 0, self._stream())
 
     # -- the exchange ---------------------------------------------------------------------------
     def step(self, iteration: int, grad_scale: float | None = None, adam_fn=None):

@@ -340,7 +340,7 @@ COLOR_GROUPS = ("sh0", "shN")
 
 
 def adam_step_groups(model: SplatData, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
-                     groups, beta1=0.9, beta2=0.999, eps=1e-15, grad_scale=1.0):
+                     groups, beta1=0.9, beta2=0.999, eps=1e-15, grad_scale=1.0, ctas_per_sm=0):
     """The fused Adam on a subset of the six parameter groups (one launch). Splitting FusedAdam::step into the geometry
     groups and the colour groups lets the colour update (three quarters of the bytes) run on a second stream while the
     next step's projection and tile lists are built from the geometry groups."""
@@ -355,7 +355,8 @@ def adam_step_groups(model: SplatData, exp_avg: SplatData, exp_avg_sq: SplatData
     if not segs:
         return
     arr = (capi.AdamSegment * len(segs))(*segs)
-    call("lfs_adam_step_segments", len(segs), arr, float(beta1), float(beta2), float(eps), int(step_count), float(grad_scale), _stream())
+    call("lfs_adam_step_segments", len(segs), arr, float(beta1), float(beta2), float(eps), int(step_count), float(grad_scale),
+         int(ctas_per_sm), _stream())
 
 
 def regularization(model: SplatData, grads: SplatData, scale_reg: float, opacity_reg: float, out: torch.Tensor | None = None):
