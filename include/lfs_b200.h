@@ -65,16 +65,18 @@ int lfs_profile_collect(int max_records, const char** names, float* ms);
 /* ------------------------------------------------------------------------------------------ */
 
 /* gsplat/Ops.h:67-95 projection_ut_3dgs_fused -> gsplat/ProjectionUT3DGSFused.cu:17.
- * Global shutter. camera_model FISHEYE: radial_coeffs [C,4] or NULL. camera_model PINHOLE: radial_coeffs [C,6],
+ * Shutter: rs_type is the reference's ShutterType (0 top-to-bottom, 1 left-to-right, 2 bottom-to-top, 3 right-to-left,
+ * 4 global, gsplat/Cameras.h); viewmats1 [C,4,4] (or NULL = the start pose) is the end-of-frame pose of a rolling
+ * shutter (gsplat/Cameras.cuh:33-71, :346-413). camera_model FISHEYE: radial_coeffs [C,4] or NULL. camera_model PINHOLE: radial_coeffs [C,6],
  * tangential_coeffs [C,2], thin_prism_coeffs [C,4], each or NULL; all NULL is the distortion-free pinhole, any
  * present selects the OpenCV pinhole model (gsplat/ProjectionUT3DGSFused.cu:91-113, gsplat/Cameras.cuh:474-755).
  * opacities and compensations may be NULL. Outputs of culled Gaussians other than radii = 0 are
  * left untouched, like the reference. */
 int lfs_projection_ut_3dgs_fused(
     int C, int N, const float* means, const float* quats, const float* scales, const float* opacities,
-    const float* viewmats0, const float* Ks, int image_width, int image_height,
+    const float* viewmats0, const float* viewmats1, const float* Ks, int image_width, int image_height,
     float eps2d, float near_plane, float far_plane, float radius_clip,
-    int camera_model, lfs_ut_params ut_params, const float* radial_coeffs, const float* tangential_coeffs,
+    int camera_model, lfs_ut_params ut_params, int rs_type, const float* radial_coeffs, const float* tangential_coeffs,
     const float* thin_prism_coeffs, int32_t* radii, float* means2d, float* depths, float* conics, float* compensations, void* stream);
 
 /* gsplat/Ops.h:12-17 spherical_harmonics_fwd -> gsplat/SphericalHarmonicsCUDA.cu:374.
@@ -120,8 +122,8 @@ size_t lfs_rasterize_workspace_bytes(int N);
 int lfs_rasterize_to_pixels_from_world_3dgs_fwd(
     int N, int64_t n_isects, int channels, const float* means, const float* quats, const float* scales, const float* colors,
     const float* opacities, const float* backgrounds, const uint8_t* masks, int image_width, int image_height, int tile_size,
-    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs, const float* tangential_coeffs,
-    const float* thin_prism_coeffs,
+    const float* viewmat0, const float* viewmat1, const float* K, int camera_model, int rs_type, const float* radial_coeffs,
+    const float* tangential_coeffs, const float* thin_prism_coeffs,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     float* renders, float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes, void* stream);
 
@@ -131,8 +133,8 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(
 int lfs_rasterize_to_pixels_from_world_3dgs_bwd(
     int N, int64_t n_isects, int channels, const float* means, const float* quats, const float* scales, const float* colors,
     const float* opacities, const float* backgrounds, const uint8_t* masks, int image_width, int image_height, int tile_size,
-    const float* viewmat0, const float* K, int camera_model, const float* radial_coeffs, const float* tangential_coeffs,
-    const float* thin_prism_coeffs,
+    const float* viewmat0, const float* viewmat1, const float* K, int camera_model, int rs_type, const float* radial_coeffs,
+    const float* tangential_coeffs, const float* thin_prism_coeffs,
     const int32_t* tile_offsets, const int32_t* flatten_ids,
     const float* render_alphas, const int32_t* last_ids, const float* v_render_colors, const float* v_render_alphas,
     float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
@@ -207,6 +209,11 @@ typedef struct lfs_render_config {
     const float* radial_coeffs;
     const float* tangential_coeffs;
     const float* thin_prism_coeffs;
+    /* Rolling shutter: 0 = global (default), 1 = top-to-bottom, 2 = left-to-right, 3 = bottom-to-top, 4 = right-to-left
+     * (the reference's ShutterType + 1, so that a zeroed config is a global shutter). viewmat_end: device [4,4]
+     * end-of-frame world-to-camera matrix or NULL (= the start pose). */
+    int shutter;
+    const float* viewmat_end;
 } lfs_render_config;
 
 size_t lfs_render_workspace_bytes(const lfs_render_config* cfg);

@@ -32,7 +32,8 @@ class RenderConfig(C.Structure):
                 ("eps2d", C.c_float), ("near_plane", C.c_float), ("far_plane", C.c_float), ("radius_clip", C.c_float),
                 ("ut", UTParams), ("isect_capacity", C.c_int64), ("render_mode", C.c_int), ("calc_compensations", C.c_int),
                 ("scaling_modifier", C.c_float), ("tile_masks", C.c_void_p), ("radial_coeffs", C.c_void_p),
-                ("tangential_coeffs", C.c_void_p), ("thin_prism_coeffs", C.c_void_p)]
+                ("tangential_coeffs", C.c_void_p), ("thin_prism_coeffs", C.c_void_p), ("shutter", C.c_int),
+                ("viewmat_end", C.c_void_p)]
 
 
 class EwaConfig(C.Structure):
@@ -67,16 +68,16 @@ _lib = None
 vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 _SIGNATURES = {
-    "lfs_projection_ut_3dgs_fused": [i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, i32, UTParams, vp, vp, vp,
+    "lfs_projection_ut_3dgs_fused": [i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, i32, UTParams, i32, vp, vp, vp,
                                      vp, vp, vp, vp, vp, vp],
     "lfs_spherical_harmonics_fwd": [i32, i32, i32, vp, vp, vp, vp, vp],
     "lfs_spherical_harmonics_bwd": [i32, i32, i32, vp, vp, vp, vp, vp],
     "lfs_intersect_tile_count": [i32, i32, vp, vp, i32, i32, i32, vp, vp, vp],
     "lfs_intersect_tile_emit": [i32, i32, vp, vp, vp, vp, i32, i32, i32, i32, i64, vp, vp, vp, sz, vp],
     "lfs_intersect_offset": [i64, vp, i32, i32, i32, vp, vp],
-    "lfs_rasterize_to_pixels_from_world_3dgs_fwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, vp, vp,
+    "lfs_rasterize_to_pixels_from_world_3dgs_fwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, i32, i32, vp, vp, vp,
                                                     vp, vp, vp, vp, vp, vp, sz, vp],
-    "lfs_rasterize_to_pixels_from_world_3dgs_bwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, vp, vp, vp,
+    "lfs_rasterize_to_pixels_from_world_3dgs_bwd": [i32, i64, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, i32, i32, vp, vp, vp,
                                                     vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
     "lfs_fusedssim": [i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp],
     "lfs_fusedssim_backward": [i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp],

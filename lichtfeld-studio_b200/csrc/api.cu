@@ -161,6 +161,7 @@ int check_cfg(const lfs_render_config* cfg) {
     LFS_REQUIRE(cfg->isect_capacity >= 0 && cfg->isect_capacity < ((int64_t)1 << 31), "isect_capacity out of range");
     LFS_REQUIRE(cfg->render_mode >= LFS_RENDER_RGB && cfg->render_mode <= LFS_RENDER_RGB_ED, "render_mode must be in [0,4]");
     LFS_REQUIRE(cfg->scaling_modifier >= 0.f, "scaling_modifier must be positive (0 = 1.0)");
+    LFS_REQUIRE(cfg->shutter >= 0 && cfg->shutter <= 4, "shutter must be 0 (global) or 1..4 (rolling)");
     LFS_REQUIRE(cfg->camera_model == LFS_PINHOLE || (!cfg->tangential_coeffs && !cfg->thin_prism_coeffs),
                 "tangential / thin-prism coefficients belong to the pinhole model");
     return LFS_OK;
@@ -173,6 +174,9 @@ int mode_normalize(int render_mode) { return render_mode == LFS_RENDER_ED || ren
 int cfg_model(const lfs_render_config& cfg) {
     return effective_model(cfg.camera_model, cfg.radial_coeffs, cfg.tangential_coeffs, cfg.thin_prism_coeffs);
 }
+// cfg.shutter: 0 = global, 1..4 = the reference's ShutterType 0..3
+int cfg_rs_type(const lfs_render_config& cfg) { return cfg.shutter == 0 ? LFS_SHUTTER_GLOBAL : cfg.shutter - 1; }
+int cfg_rolling(const lfs_render_config& cfg) { return (cfg.shutter != 0 || cfg.viewmat_end != nullptr) ? 1 : 0; }
 float cfg_modifier(const lfs_render_config& cfg) { return cfg.scaling_modifier > 0.f ? cfg.scaling_modifier : 1.0f; }
 
 }  // namespace
@@ -189,9 +193,9 @@ const char* lfs_build_info(void) { return "lfs_b200 0.1 (sm_100a, CUDA " LFS_STR
 
 // ---------------------------------------------------------------------------------------------
 int lfs_projection_ut_3dgs_fused(int C, int N, const float* means, const float* quats, const float* scales,
-                                 const float* opacities, const float* viewmats0, const float* Ks, int W, int H, float eps2d,
-                                 float near_plane, float far_plane, float radius_clip, int camera_model, lfs_ut_params ut,
-                                 const float* radial_coeffs, const float* tangential_coeffs, const float* thin_prism_coeffs,
+                                 const float* opacities, const float* viewmats0, const float* viewmats1, const float* Ks, int W,
+                                 int H, float eps2d, float near_plane, float far_plane, float radius_clip, int camera_model,
+                                 lfs_ut_params ut, int rs_type, const float* radial_coeffs, const float* tangential_coeffs, const float* thin_prism_coeffs,
                                  int32_t* radii, float* means2d, float* depths, float* conics,
                                  float* compensations, void* stream) {
     LFS_REQUIRE(C >= 0 && N >= 0 && W > 0 && H > 0, "bad sizes");
@@ -201,7 +205,8 @@ int lfs_projection_ut_3dgs_fused(int C, int N, const float* means, const float* 
     LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
     LFS_REQUIRE(camera_model == LFS_PINHOLE || (!tangential_coeffs && !thin_prism_coeffs),
                 "tangential / thin-prism coefficients belong to the pinhole model");
-    return launch_projection_ut(C, N, means, quats, scales, opacities, viewmats0, Ks, radial_coeffs, tangential_coeffs,
+    LFS_REQUIRE(rs_type >= 0 && rs_type <= LFS_SHUTTER_GLOBAL, "rs_type must be a ShutterType (0..4)");
+    return launch_projection_ut(C, N, means, quats, scales, opacities, viewmats0, viewmats1, rs_type, Ks, radial_coeffs, tangential_coeffs,
                                 thin_prism_coeffs, W, H,
                                 make_proj_params(eps2d, near_plane, far_plane, radius_clip, ut), camera_model, radii,
                                 means2d, depths, conics, compensations, S(stream));
@@ -304,8 +309,8 @@ static int raster_common(int N, int64_t n_isects, int channels, int W, int H, in
 int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, int channels, const float* means, const float* quats,
                                                 const float* scales, const float* colors, const float* opacities,
                                                 const float* backgrounds, const uint8_t* masks, int W, int H, int tile_size,
-                                                const float* viewmat0,
-                                                const float* K, int camera_model, const float* radial_coeffs,
+                                                const float* viewmat0, const float* viewmat1,
+                                                const float* K, int camera_model, int rs_type, const float* radial_coeffs,
                                                 const float* tangential_coeffs, const float* thin_prism_coeffs,
                                                 const int32_t* tile_offsets, const int32_t* flatten_ids, float* renders,
                                                 float* alphas, int32_t* last_ids, void* workspace, size_t workspace_bytes,
@@ -320,21 +325,24 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, int cha
     uint4* bounds = c.take<uint4>((size_t)N);
     LFS_REQUIRE(camera_model == LFS_PINHOLE || (!tangential_coeffs && !thin_prism_coeffs),
                 "tangential / thin-prism coefficients belong to the pinhole model");
-    rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, tangential_coeffs, thin_prism_coeffs, W, H, camera_model, cam, S(stream));
+    LFS_REQUIRE(rs_type >= 0 && rs_type <= LFS_SHUTTER_GLOBAL, "rs_type must be a ShutterType (0..4)");
+    rc = launch_camera_setup(1, viewmat0, viewmat1, rs_type, K, radial_coeffs, tangential_coeffs, thin_prism_coeffs, W, H, camera_model,
+                             cam, S(stream));
     const int eff_model = effective_model(camera_model, radial_coeffs, tangential_coeffs, thin_prism_coeffs);
+    const int rolling = (rs_type != LFS_SHUTTER_GLOBAL || viewmat1 != nullptr) ? 1 : 0;
     if (rc != LFS_OK) return rc;
     rc = launch_pack_records(N, means, quats, scales, colors, channels, opacities, cam, records, bounds, nullptr, nullptr, S(stream));
     if (rc != LFS_OK) return rc;
     RasterArgs a{cam, records, bounds, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
-                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, eff_model, channels, 0, masks};
+                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, eff_model, channels, 0, masks, nullptr, rolling};
     return launch_raster_fwd(a, renders, alphas, last_ids, nullptr, S(stream));
 }
 
 int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, int channels, const float* means, const float* quats,
                                                 const float* scales, const float* colors, const float* opacities,
                                                 const float* backgrounds, const uint8_t* masks, int W, int H, int tile_size,
-                                                const float* viewmat0,
-                                                const float* K, int camera_model, const float* radial_coeffs,
+                                                const float* viewmat0, const float* viewmat1,
+                                                const float* K, int camera_model, int rs_type, const float* radial_coeffs,
                                                 const float* tangential_coeffs, const float* thin_prism_coeffs,
                                                 const int32_t* tile_offsets, const int32_t* flatten_ids,
                                                 const float* render_alphas, const int32_t* last_ids,
@@ -354,14 +362,17 @@ int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, int cha
     float* accum_extra = channels != 3 ? c.take<float>((size_t)N) : nullptr;
     LFS_REQUIRE(camera_model == LFS_PINHOLE || (!tangential_coeffs && !thin_prism_coeffs),
                 "tangential / thin-prism coefficients belong to the pinhole model");
-    rc = launch_camera_setup(1, viewmat0, K, radial_coeffs, tangential_coeffs, thin_prism_coeffs, W, H, camera_model, cam, S(stream));
+    LFS_REQUIRE(rs_type >= 0 && rs_type <= LFS_SHUTTER_GLOBAL, "rs_type must be a ShutterType (0..4)");
+    rc = launch_camera_setup(1, viewmat0, viewmat1, rs_type, K, radial_coeffs, tangential_coeffs, thin_prism_coeffs, W, H, camera_model,
+                             cam, S(stream));
     const int eff_model = effective_model(camera_model, radial_coeffs, tangential_coeffs, thin_prism_coeffs);
+    const int rolling = (rs_type != LFS_SHUTTER_GLOBAL || viewmat1 != nullptr) ? 1 : 0;
     if (rc != LFS_OK) return rc;
     rc = launch_pack_records(N, means, quats, scales, colors, channels, opacities, cam, records, bounds,
                              reinterpret_cast<float4*>(accum), accum_extra, S(stream));
     if (rc != LFS_OK) return rc;
     RasterArgs a{cam, records, bounds, reinterpret_cast<const uint32_t*>(flatten_ids), tile_offsets, nullptr, n_isects, backgrounds,
-                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, eff_model, channels, 0, masks};
+                 nullptr, W, H, (W + 15) / 16, (H + 15) / 16, eff_model, channels, 0, masks, nullptr, rolling};
     rc = launch_raster_bwd(a, render_alphas, last_ids, nullptr, v_render_colors, v_render_alphas, accum, accum_extra, S(stream));
     if (rc != LFS_OK) return rc;
     return launch_grad_epilogue_op(N, cam, accum, means, quats, scales, channels, accum_extra, v_means, v_quats, v_scales,
@@ -656,8 +667,8 @@ size_t lfs_render_workspace_bytes(const lfs_render_config* cfg) {
 static int render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
                                 int with_colors, RenderWs& w, int* sel_out, cudaStream_t st) {
     const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
-    int rc = launch_camera_setup(1, viewmat, K, cfg->radial_coeffs, cfg->tangential_coeffs, cfg->thin_prism_coeffs, cfg->image_width,
-                                 cfg->image_height, cfg->camera_model, w.cam, st);
+    int rc = launch_camera_setup(1, viewmat, cfg->viewmat_end, cfg_rs_type(*cfg), K, cfg->radial_coeffs, cfg->tangential_coeffs,
+                                 cfg->thin_prism_coeffs, cfg->image_width, cfg->image_height, cfg->camera_model, w.cam, st);
     if (rc != LFS_OK) return rc;
     cudaMemsetAsync(w.counters, 0, 16 * sizeof(int32_t), st);
     const ProjParams pp = make_proj_params(cfg->eps2d, cfg->near_plane, cfg->far_plane, cfg->radius_clip, cfg->ut);
@@ -665,7 +676,7 @@ static int render_forward_lists(const lfs_render_config* cfg, const lfs_splats* 
     opt.scaling_modifier = cfg_modifier(*cfg);
     opt.calc_compensations = cfg->calc_compensations;
     opt.want_rgb = with_colors && mode_channels(cfg->render_mode) != 1;
-    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, opt, cfg_model(*cfg), cfg->tile_size, tw,
+    rc = launch_project_pack(cfg->N, cfg->sh_coeffs, cfg->sh_degree, *params, w.cam, pp, opt, cfg_model(*cfg), cfg_rolling(*cfg), cfg->tile_size, tw,
                              th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records, w.bounds,
                              reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
     if (rc != LFS_OK) return rc;
@@ -686,7 +697,7 @@ static int render_forward_blend(const lfs_render_config* cfg, const float* backg
     const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
     RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
                   cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
-                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order};
+                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order, cfg_rolling(*cfg)};
     int rc = launch_raster_fwd(ra, render, alpha, w.last_ids, w.extra_sum, st);
     if (rc != LFS_OK) return rc;
     if (status_dev) cudaMemcpyAsync(status_dev, w.counters, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
@@ -758,7 +769,7 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
     const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
     RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
                   cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
-                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order};
+                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order, cfg_rolling(*cfg)};
     rc = launch_raster_bwd(ra, alpha, w.last_ids, w.extra_sum, v_render, v_alpha, w.accum, nullptr, st);
     if (rc != LFS_OK) return rc;
     return launch_grad_epilogue_fused(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, w.accum, w.records, w.radii, *params,

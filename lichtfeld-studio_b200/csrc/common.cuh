@@ -62,8 +62,15 @@ struct CamDev {
     float max_angle;       // fisheye
     float approx_b1;       // fisheye: linear term of the crude backward polynomial
     int W, H, model;
-    int pad;
+    int rs_type;           // ShutterType of the reference: 0..3 rolling (top-to-bottom, left-to-right, bottom-to-top,
+                           // right-to-left), 4 global
+    // rolling shutter: end-of-frame pose (equal to the start pose without one) and the centre-of-frame pose that
+    // gives the depth of a Gaussian (gsplat/ProjectionUT3DGSFused.cu:73-77)
+    int has_end;
+    float q1w, q1x, q1y, q1z, t1x, t1y, t1z;
+    float qcw, qcx, qcy, qcz, tcx, tcy, tcz;
 };
+constexpr int LFS_SHUTTER_GLOBAL = 4;
 
 // Internal model id: LFS_PINHOLE with any of the three distortion tensors present selects the OpenCV pinhole
 // model (gsplat/ProjectionUT3DGSFused.cu:91-113); it never crosses the C ABI.
@@ -81,8 +88,10 @@ constexpr int kRecordFloats = 16;
 
 // Host-side launchers shared between translation units (all asynchronous on `st`).
 // radial: [C,4] for LFS_FISHEYE, [C,6] for LFS_PINHOLE; tangential [C,2] and thin_prism [C,4] only for LFS_PINHOLE.
-int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, const float* tangential,
-                        const float* thin_prism, int W, int H, int model, CamDev* cams, cudaStream_t st);
+// viewmats1 [C,4,4] or null (no end pose), rs_type = ShutterType (4 = global)
+int launch_camera_setup(int C, const float* viewmats, const float* viewmats1, int rs_type, const float* Ks, const float* radial,
+                        const float* tangential, const float* thin_prism, int W, int H, int model, CamDev* cams,
+                        cudaStream_t st);
 
 // ---- sort.cu -------------------------------------------------------------------------------
 struct SortScratch {

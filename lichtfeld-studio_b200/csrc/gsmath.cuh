@@ -238,6 +238,83 @@ __device__ __forceinline__ bool pixel_world_dir(const CamDev& c, float px, float
 }
 
 // ---------------------------------------------------------------------------------------------
+// Rolling shutter (gsplat/Cameras.cuh:33-71, :253-413): the pose is interpolated between a start and an end pose
+// by the frame time of the image row / column.
+// ---------------------------------------------------------------------------------------------
+struct PoseQ { float w, x, y, z; f3 t; };
+
+// glm::slerp; acos / sin through double and rounded once, like the host restatement
+__device__ __forceinline__ void quat_slerp(float xw, float xx, float xy, float xz, float yw, float yx, float yy, float yz, float a,
+                                           float& ow, float& ox, float& oy, float& oz) {
+    float cosTheta = xx * yx + xy * yy + xz * yz + xw * yw;
+    if (cosTheta < 0.f) { yw = -yw; yx = -yx; yy = -yy; yz = -yz; cosTheta = -cosTheta; }
+    if (cosTheta > 1.f - FLT_EPSILON) {
+        ow = xw * (1.f - a) + yw * a; ox = xx * (1.f - a) + yx * a; oy = xy * (1.f - a) + yy * a; oz = xz * (1.f - a) + yz * a;
+        return;
+    }
+    const float angle = (float)acos((double)cosTheta);
+    const float s0 = (float)sin((double)((1.f - a) * angle)), s1 = (float)sin((double)(a * angle)), sn = (float)sin((double)angle);
+    ow = (s0 * xw + s1 * yw) / sn; ox = (s0 * xx + s1 * yx) / sn; oy = (s0 * xy + s1 * yy) / sn; oz = (s0 * xz + s1 * yz) / sn;
+}
+
+__device__ __forceinline__ PoseQ shutter_pose(const CamDev& c, float t) {
+    PoseQ p;
+    if (!c.has_end) { p.w = c.qw; p.x = c.qx; p.y = c.qy; p.z = c.qz; p.t = f3{c.tx, c.ty, c.tz}; return p; }
+    p.t = (1.f - t) * f3{c.tx, c.ty, c.tz} + t * f3{c.t1x, c.t1y, c.t1z};
+    quat_slerp(c.qw, c.qx, c.qy, c.qz, c.q1w, c.q1x, c.q1y, c.q1z, t, p.w, p.x, p.y, p.z);
+    return p;
+}
+
+__device__ __forceinline__ float shutter_time(const CamDev& c, float px, float py) {
+    switch (c.rs_type) {
+        case 0: return floorf(py) / (float)(c.H - 1);
+        case 1: return floorf(px) / (float)(c.W - 1);
+        case 2: return ((float)c.H - ceilf(py)) / (float)(c.H - 1);
+        case 3: return ((float)c.W - ceilf(px)) / (float)(c.W - 1);
+        default: return 0.f;
+    }
+}
+
+// World point -> image point. RS = false: the start pose. RS = true: start (else end) projection as the initial
+// guess, then ten rounds of pixel -> frame time -> pose -> projection (Cameras.cuh:346-413).
+template <int MODEL, bool RS>
+__device__ __forceinline__ bool world_point_to_image(const CamDev& c, f3 world, float margin, float& ox, float& oy) {
+    const f3 t0{c.tx, c.ty, c.tz};
+    const bool v0 = cam_point_to_image<MODEL>(c, quat_rotate(c.qw, c.qx, c.qy, c.qz, world) + t0, margin, ox, oy);
+    if (!RS || c.rs_type == LFS_SHUTTER_GLOBAL) return v0;
+    float ex, ey;
+    const bool v1 = cam_point_to_image<MODEL>(c, quat_rotate(c.q1w, c.q1x, c.q1y, c.q1z, world) + f3{c.t1x, c.t1y, c.t1z}, margin, ex, ey);
+    if (!v0) {
+        ox = ex; oy = ey;
+        if (!v1) return false;
+    }
+    for (int j = 0; j < 10; ++j) {
+        const PoseQ p = shutter_pose(c, shutter_time(c, ox, oy));
+        cam_point_to_image<MODEL>(c, quat_rotate(p.w, p.x, p.y, p.z, world) + p.t, margin, ox, oy);
+    }
+    return true;
+}
+
+// Rolling-shutter pixel ray: direction and the offset of its origin from the start-pose origin c.ro
+// (image_point_to_world_ray_shutter_pose, Cameras.cuh:322-339).
+template <int MODEL>
+__device__ __forceinline__ bool pixel_world_ray_rs(const CamDev& c, float px, float py, f3& d, f3& origin_offset) {
+    f3 cr;
+    const bool valid = image_to_cam_ray<MODEL>(c, px, py, cr);
+    const PoseQ p = shutter_pose(c, shutter_time(c, px, py));
+    const float dq = p.x * p.x + p.y * p.y + p.z * p.z + p.w * p.w;
+    float Ri[9];
+    quat_to_mat_unit(p.w / dq, -p.x / dq, -p.y / dq, -p.z / dq, Ri);
+    d.x = Ri[0] * cr.x + Ri[1] * cr.y + Ri[2] * cr.z;
+    d.y = Ri[3] * cr.x + Ri[4] * cr.y + Ri[5] * cr.z;
+    d.z = Ri[6] * cr.x + Ri[7] * cr.y + Ri[8] * cr.z;
+    origin_offset.x = ((-Ri[0]) * p.t.x + (-Ri[1]) * p.t.y + (-Ri[2]) * p.t.z) - c.ro[0];
+    origin_offset.y = ((-Ri[3]) * p.t.x + (-Ri[4]) * p.t.y + (-Ri[5]) * p.t.z) - c.ro[1];
+    origin_offset.z = ((-Ri[6]) * p.t.x + (-Ri[7]) * p.t.y + (-Ri[8]) * p.t.z) - c.ro[2];
+    return valid;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Real SH basis up to degree 4 at a direction that is normalised here (Sloan's recurrences).
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void sh_basis(int degree, float dx, float dy, float dz, float* B) {

@@ -11,12 +11,8 @@
 namespace lfs {
 
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const float* __restrict__ K,
-                                           const float* __restrict__ radial4, const float* __restrict__ dist12, int W, int H,
-                                           int model) {
-    CamDev c;
-    for (int i = 0; i < 12; ++i) c.dist[i] = dist12 ? dist12[i] : 0.f;
-    // quaternion of the rotation block: the branch with the largest of (trace, +-diagonal sums)
+// quaternion of the rotation block of a row-major 4x4 matrix: the branch with the largest of (trace, +-diagonal sums)
+__device__ __forceinline__ void quat_of_viewmat(const float* __restrict__ vm, float& qw, float& qx, float& qy, float& qz) {
     const float R00 = vm[0], R01 = vm[1], R02 = vm[2];
     const float R10 = vm[4], R11 = vm[5], R12 = vm[6];
     const float R20 = vm[8], R21 = vm[9], R22 = vm[10];
@@ -28,11 +24,19 @@ __device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const f
     if (fz4 > fb) { fb = fz4; big = 3; }
     const float bv = sqrtf(fb + 1.0f) * 0.5f;
     const float mult = 0.25f / bv;
-    float qw, qx, qy, qz;
     if (big == 0)      { qw = bv; qx = (R21 - R12) * mult; qy = (R02 - R20) * mult; qz = (R10 - R01) * mult; }
     else if (big == 1) { qw = (R21 - R12) * mult; qx = bv; qy = (R10 + R01) * mult; qz = (R02 + R20) * mult; }
     else if (big == 2) { qw = (R02 - R20) * mult; qx = (R10 + R01) * mult; qy = bv; qz = (R21 + R12) * mult; }
     else               { qw = (R10 - R01) * mult; qx = (R02 + R20) * mult; qy = (R21 + R12) * mult; qz = bv; }
+}
+
+__device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const float* __restrict__ vm1, int rs_type,
+                                           const float* __restrict__ K, const float* __restrict__ radial4,
+                                           const float* __restrict__ dist12, int W, int H, int model) {
+    CamDev c;
+    for (int i = 0; i < 12; ++i) c.dist[i] = dist12 ? dist12[i] : 0.f;
+    float qw, qx, qy, qz;
+    quat_of_viewmat(vm, qw, qx, qy, qz);
     c.qw = qw; c.qx = qx; c.qy = qy; c.qz = qz;
     c.tx = vm[3]; c.ty = vm[7]; c.tz = vm[11];
     // inverse quaternion -> rotation matrix -> ray origin
@@ -43,7 +47,18 @@ __device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const f
     for (int i = 0; i < 3; ++i)
         c.campos[i] = (float)(-((double)vm[0 * 4 + i] * vm[3] + (double)vm[1 * 4 + i] * vm[7] + (double)vm[2 * 4 + i] * vm[11]));
     c.fx = K[0]; c.fy = K[4]; c.cx = K[2]; c.cy = K[5];
-    c.W = W; c.H = H; c.model = model; c.pad = 0;
+    c.W = W; c.H = H; c.model = model;
+    // rolling shutter: end pose and the centre-of-frame pose (equal to the start pose without an end pose)
+    c.rs_type = rs_type;
+    c.has_end = vm1 != nullptr;
+    c.q1w = qw; c.q1x = qx; c.q1y = qy; c.q1z = qz; c.t1x = c.tx; c.t1y = c.ty; c.t1z = c.tz;
+    c.qcw = qw; c.qcx = qx; c.qcy = qy; c.qcz = qz; c.tcx = c.tx; c.tcy = c.ty; c.tcz = c.tz;
+    if (vm1) {
+        quat_of_viewmat(vm1, c.q1w, c.q1x, c.q1y, c.q1z);
+        c.t1x = vm1[3]; c.t1y = vm1[7]; c.t1z = vm1[11];
+        const PoseQ pc = shutter_pose(c, 0.5f);
+        c.qcw = pc.w; c.qcx = pc.x; c.qcy = pc.y; c.qcz = pc.z; c.tcx = pc.t.x; c.tcy = pc.t.y; c.tcz = pc.t.z;
+    }
     for (int i = 0; i < 4; ++i) c.k[i] = radial4 ? radial4[i] : 0.f;
     c.max_angle = 0.f; c.approx_b1 = 0.f;
     if (model == LFS_FISHEYE) {
@@ -95,26 +110,29 @@ __device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const f
     return c;
 }
 
-__global__ void camera_setup_kernel(int C, const float* __restrict__ viewmats, const float* __restrict__ Ks,
-                                    const float* __restrict__ radial, const float* __restrict__ tangential,
-                                    const float* __restrict__ thin_prism, int W, int H, int model, CamDev* cams) {
+__global__ void camera_setup_kernel(int C, const float* __restrict__ viewmats, const float* __restrict__ viewmats1, int rs_type,
+                                    const float* __restrict__ Ks, const float* __restrict__ radial,
+                                    const float* __restrict__ tangential, const float* __restrict__ thin_prism, int W, int H,
+                                    int model, CamDev* cams) {
     const int cid = blockIdx.x * blockDim.x + threadIdx.x;
     if (cid >= C) return;
+    const float* vm1 = viewmats1 ? viewmats1 + cid * 16 : nullptr;
     if (model == LFS_PINHOLE_OPENCV) {
         float d[12];
         for (int i = 0; i < 6; ++i) d[i] = radial ? radial[cid * 6 + i] : 0.f;
         for (int i = 0; i < 2; ++i) d[6 + i] = tangential ? tangential[cid * 2 + i] : 0.f;
         for (int i = 0; i < 4; ++i) d[8 + i] = thin_prism ? thin_prism[cid * 4 + i] : 0.f;
-        cams[cid] = make_cam(viewmats + cid * 16, Ks + cid * 9, nullptr, d, W, H, model);
+        cams[cid] = make_cam(viewmats + cid * 16, vm1, rs_type, Ks + cid * 9, nullptr, d, W, H, model);
     } else {
-        cams[cid] = make_cam(viewmats + cid * 16, Ks + cid * 9, (radial && model == LFS_FISHEYE) ? radial + cid * 4 : nullptr,
-                             nullptr, W, H, model);
+        cams[cid] = make_cam(viewmats + cid * 16, vm1, rs_type, Ks + cid * 9,
+                             (radial && model == LFS_FISHEYE) ? radial + cid * 4 : nullptr, nullptr, W, H, model);
     }
 }
 
-int launch_camera_setup(int C, const float* viewmats, const float* Ks, const float* radial, const float* tangential,
-                        const float* thin_prism, int W, int H, int model, CamDev* cams, cudaStream_t st) {
-    camera_setup_kernel<<<(C + 31) / 32, 32, 0, st>>>(C, viewmats, Ks, radial, tangential, thin_prism, W, H,
+int launch_camera_setup(int C, const float* viewmats, const float* viewmats1, int rs_type, const float* Ks, const float* radial,
+                        const float* tangential, const float* thin_prism, int W, int H, int model, CamDev* cams,
+                        cudaStream_t st) {
+    camera_setup_kernel<<<(C + 31) / 32, 32, 0, st>>>(C, viewmats, viewmats1, rs_type, Ks, radial, tangential, thin_prism, W, H,
                                                       effective_model(model, radial, tangential, thin_prism), cams);
     return check_launch("camera_setup");
 }
@@ -130,7 +148,7 @@ struct ProjOut {
     int rx, ry;
 };
 
-template <int MODEL>
+template <int MODEL, bool RS>
 __device__ __forceinline__ bool project_gaussian(const CamDev& cam, const ProjParams& pp, f3 mean, float qw, float qx,
                                                  float qy, float qz, f3 scale, bool has_opacity, float opacity_in,
                                                  ProjOut& o) {
@@ -140,8 +158,9 @@ __device__ __forceinline__ bool project_gaussian(const CamDev& cam, const ProjPa
         if (len <= 0.0f) { qw = 1.f; qx = 0.f; qy = 0.f; qz = 0.f; }
         else { const float inv = 1.0f / len; qw *= inv; qx *= inv; qy *= inv; qz *= inv; }
     }
-    const f3 t{cam.tx, cam.ty, cam.tz};
-    const f3 mean_c = quat_rotate(cam.qw, cam.qx, cam.qy, cam.qz, mean) + t;
+    // depth and culling with the centre-of-frame pose (the start pose for a global shutter)
+    const f3 mean_c = RS ? quat_rotate(cam.qcw, cam.qcx, cam.qcy, cam.qcz, mean) + f3{cam.tcx, cam.tcy, cam.tcz}
+                         : quat_rotate(cam.qw, cam.qx, cam.qy, cam.qz, mean) + f3{cam.tx, cam.ty, cam.tz};
     if (mean_c.z < pp.near_plane || mean_c.z > pp.far_plane) return false;
     o.depth = mean_c.z;
 
@@ -168,8 +187,7 @@ __device__ __forceinline__ bool project_gaussian(const CamDev& cam, const ProjPa
             p = (i <= 3) ? (mean + delta) : (mean - delta);
         }
         float px, py;
-        const bool pv = cam_point_to_image<MODEL>(cam, quat_rotate(cam.qw, cam.qx, cam.qy, cam.qz, p) + t,
-                                                  pp.margin, px, py);
+        const bool pv = world_point_to_image<MODEL, RS>(cam, p, pp.margin, px, py);
         if (pp.require_all) {
             valid &= pv;
             if (!pv) return false;
@@ -225,10 +243,11 @@ __device__ __forceinline__ bool project_gaussian(const CamDev& cam, const ProjPa
 // ---------------------------------------------------------------------------------------------
 // Operator-level projection kernel: [C,N] outputs in the reference layouts.
 // ---------------------------------------------------------------------------------------------
-template <int MODEL>
+template <int MODEL, bool RS>
 __global__ void __launch_bounds__(256) projection_ut_kernel(
     int C, int N, const float* __restrict__ means, const float* __restrict__ quats, const float* __restrict__ scales,
-    const float* __restrict__ opacities, const float* __restrict__ viewmats, const float* __restrict__ Ks,
+    const float* __restrict__ opacities, const float* __restrict__ viewmats, const float* __restrict__ viewmats1, int rs_type,
+    const float* __restrict__ Ks,
     const float* __restrict__ radial, const float* __restrict__ tangential, const float* __restrict__ thin_prism, int W, int H,
     ProjParams pp, int32_t* __restrict__ radii, float* __restrict__ means2d, float* __restrict__ depths,
     float* __restrict__ conics, float* __restrict__ compensations) {
@@ -242,17 +261,17 @@ __global__ void __launch_bounds__(256) projection_ut_kernel(
             for (int i = 0; i < 6; ++i) d[i] = radial ? radial[cid * 6 + i] : 0.f;
             for (int i = 0; i < 2; ++i) d[6 + i] = tangential ? tangential[cid * 2 + i] : 0.f;
             for (int i = 0; i < 4; ++i) d[8 + i] = thin_prism ? thin_prism[cid * 4 + i] : 0.f;
-            cam = make_cam(viewmats + cid * 16, Ks + cid * 9, nullptr, d, W, H, MODEL);
+            cam = make_cam(viewmats + cid * 16, viewmats1 ? viewmats1 + cid * 16 : nullptr, rs_type, Ks + cid * 9, nullptr, d, W, H, MODEL);
         } else {
-            cam = make_cam(viewmats + cid * 16, Ks + cid * 9, (radial && MODEL == LFS_FISHEYE) ? radial + cid * 4 : nullptr, nullptr,
-                           W, H, MODEL);
+            cam = make_cam(viewmats + cid * 16, viewmats1 ? viewmats1 + cid * 16 : nullptr, rs_type, Ks + cid * 9,
+                           (radial && MODEL == LFS_FISHEYE) ? radial + cid * 4 : nullptr, nullptr, W, H, MODEL);
         }
         const f3 mean{means[gid * 3], means[gid * 3 + 1], means[gid * 3 + 2]};
         const f3 scale{scales[gid * 3], scales[gid * 3 + 1], scales[gid * 3 + 2]};
         const float4 q = reinterpret_cast<const float4*>(quats)[gid];
         ProjOut o;
-        const bool vis = project_gaussian<MODEL>(cam, pp, mean, q.x, q.y, q.z, q.w, scale, opacities != nullptr,
-                                                 opacities ? opacities[gid] : 0.f, o);
+        const bool vis = project_gaussian<MODEL, RS>(cam, pp, mean, q.x, q.y, q.z, q.w, scale, opacities != nullptr,
+                                                     opacities ? opacities[gid] : 0.f, o);
         if (!vis) {
             radii[idx * 2] = 0;
             radii[idx * 2 + 1] = 0;
@@ -272,23 +291,27 @@ __global__ void __launch_bounds__(256) projection_ut_kernel(
 }
 
 int launch_projection_ut(int C, int N, const float* means, const float* quats, const float* scales,
-                         const float* opacities, const float* viewmats, const float* Ks, const float* radial,
-                         const float* tangential, const float* thin_prism, int W, int H,
+                         const float* opacities, const float* viewmats, const float* viewmats1, int rs_type, const float* Ks,
+                         const float* radial, const float* tangential, const float* thin_prism, int W, int H,
                          const ProjParams& pp, int model, int32_t* radii,
                          float* means2d, float* depths, float* conics, float* compensations, cudaStream_t st) {
     const int64_t total = (int64_t)C * N;
     if (total == 0) return LFS_OK;
     const int grid = grid_for(total, 256);
     LFS_TIMED("projection_ut", st);
-#define LFS_PROJ(MODEL)                                                                                                      \
-    projection_ut_kernel<MODEL><<<grid, 256, 0, st>>>(C, N, means, quats, scales, opacities, viewmats, Ks, radial, tangential, \
-                                                      thin_prism, W, H, pp, radii, means2d, depths, conics, compensations)
+    const bool rs = rs_type != LFS_SHUTTER_GLOBAL || viewmats1 != nullptr;
+#define LFS_PROJ2(MODEL, RS)                                                                                                  \
+    projection_ut_kernel<MODEL, RS><<<grid, 256, 0, st>>>(C, N, means, quats, scales, opacities, viewmats, viewmats1, rs_type, Ks, \
+                                                          radial, tangential, thin_prism, W, H, pp, radii, means2d, depths,   \
+                                                          conics, compensations)
+#define LFS_PROJ(MODEL) do { if (rs) LFS_PROJ2(MODEL, true); else LFS_PROJ2(MODEL, false); } while (0)
     switch (effective_model(model, radial, tangential, thin_prism)) {
         case LFS_PINHOLE: LFS_PROJ(LFS_PINHOLE); break;
         case LFS_PINHOLE_OPENCV: LFS_PROJ(LFS_PINHOLE_OPENCV); break;
         default: LFS_PROJ(LFS_FISHEYE); break;
     }
 #undef LFS_PROJ
+#undef LFS_PROJ2
     return check_launch("projection_ut");
 }
 
@@ -313,7 +336,7 @@ __device__ __forceinline__ void make_record(const CamDev& cam, f3 mean, float qw
     const uint32_t thr_bits = __float_as_uint(-logf(fmaxf(255.0f * opacity, 1e-30f)) - 0.02f);
     const uint32_t extra_bits = __float_as_uint(extra);  // blended into the last channel of 1- and 4-channel renders
     box = make_uint4(0xFFFF0000u, 0xFFFF0000u, thr_bits, extra_bits);  // (lo | hi << 16) per axis: everything
-    if (cam.model == LFS_PINHOLE) {
+    if (cam.model == LFS_PINHOLE && cam.rs_type == LFS_SHUTTER_GLOBAL && !cam.has_end) {   // one pose for every pixel
         const float rho2 = 2.0f * (logf(fmaxf(255.0f * opacity, 1.0f)) + 0.03f);
         // V = R_c R with R_c = Rinv^T ; Sigma_c = rho2 V S^2 V^T ; mu_c = R_c mean + t
         float V[9];
@@ -406,7 +429,7 @@ int launch_pack_records(int N, const float* means, const float* quats, const flo
 // tile count, depth sort key, SH colour (+0.5, clamped at 0), packed record, zeroed gradient
 // accumulator row. Invisible Gaussians get radii 0, tile count 0 and the sort key 0xFFFFFFFF.
 // ---------------------------------------------------------------------------------------------
-template <int MODEL>
+template <int MODEL, bool RS>
 __global__ void __launch_bounds__(256, 3) project_pack_kernel(
     int N, int K, int sh_degree, const float* __restrict__ means, const float* __restrict__ sh0,
     const float* __restrict__ shN, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
@@ -446,7 +469,7 @@ __global__ void __launch_bounds__(256, 3) project_pack_kernel(
             const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
             const float nrm = fmaxf(sqrtf(n2), 1e-12f);
             qw = qr.x / nrm; qx = qr.y / nrm; qy = qr.z / nrm; qz = qr.w / nrm;
-            vis = project_gaussian<MODEL>(cam, pp, mean, qw, qx, qy, qz, scale, true, opacity, o);
+            vis = project_gaussian<MODEL, RS>(cam, pp, mean, qw, qx, qy, qz, scale, true, opacity, o);
             sort_vals[g] = (uint32_t)g;
             if (!vis) {
                 radii[g * 2] = 0; radii[g * 2 + 1] = 0;
@@ -580,7 +603,7 @@ int launch_sh_color(int N, int K, int sh_degree, const lfs_splats& p, const CamD
 }
 
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
-                        const PackOptions& opt, int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
+                        const PackOptions& opt, int model, int rolling, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
                         int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st) {
     if (N == 0) return LFS_OK;
@@ -588,21 +611,25 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
     if (smem > 200 * 1024) { set_error("project_pack: too many SH coefficients"); return LFS_EINVAL; }
     if (smem > 48 * 1024) {
-        cudaFuncSetAttribute(project_pack_kernel<LFS_PINHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(project_pack_kernel<LFS_FISHEYE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(project_pack_kernel<LFS_PINHOLE_OPENCV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+#define LFS_PACK_ATTR(MODEL)                                                                                        \
+    cudaFuncSetAttribute(project_pack_kernel<MODEL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    cudaFuncSetAttribute(project_pack_kernel<MODEL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        LFS_PACK_ATTR(LFS_PINHOLE); LFS_PACK_ATTR(LFS_FISHEYE); LFS_PACK_ATTR(LFS_PINHOLE_OPENCV);
+#undef LFS_PACK_ATTR
     }
     LFS_TIMED("project_pack", st);
-#define LFS_PACK(MODEL)                                                                                                        \
-    project_pack_kernel<MODEL><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw, p.rotation_raw,   \
-                                                        p.opacity_raw, cam, pp, opt, (float)tile_size, tw, th, radii, means2d, \
-                                                        depths, tiles, sort_keys, sort_vals, records, bounds, accum, n_visible)
+#define LFS_PACK2(MODEL, RS)                                                                                                       \
+    project_pack_kernel<MODEL, RS><<<grid, 256, smem, st>>>(N, K, sh_degree, p.means, p.sh0, p.shN, p.scaling_raw, p.rotation_raw,  \
+                                                            p.opacity_raw, cam, pp, opt, (float)tile_size, tw, th, radii, means2d, \
+                                                            depths, tiles, sort_keys, sort_vals, records, bounds, accum, n_visible)
+#define LFS_PACK(MODEL) do { if (rolling) LFS_PACK2(MODEL, true); else LFS_PACK2(MODEL, false); } while (0)
     switch (model) {
         case LFS_PINHOLE: LFS_PACK(LFS_PINHOLE); break;
         case LFS_PINHOLE_OPENCV: LFS_PACK(LFS_PINHOLE_OPENCV); break;
         default: LFS_PACK(LFS_FISHEYE); break;
     }
 #undef LFS_PACK
+#undef LFS_PACK2
     return check_launch("project_pack");
 }
 

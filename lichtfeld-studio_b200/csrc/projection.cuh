@@ -21,8 +21,9 @@ inline ProjParams make_proj_params(float eps2d, float near_plane, float far_plan
 }
 
 int launch_projection_ut(int C, int N, const float* means, const float* quats, const float* scales,
-                         const float* opacities, const float* viewmats, const float* Ks, const float* radial,
-                         const float* tangential, const float* thin_prism, int W, int H, const ProjParams& pp, int model, int32_t* radii,
+                         const float* opacities, const float* viewmats, const float* viewmats1, int rs_type, const float* Ks,
+                         const float* radial, const float* tangential, const float* thin_prism, int W, int H, const ProjParams& pp,
+                         int model, int32_t* radii,
                          float* means2d, float* depths, float* conics, float* compensations, cudaStream_t st);
 
 // colours [N, channels] with channels 1 (extra only), 3 (rgb) or 4 (rgb + extra); accum / accum_extra (may be null)
@@ -38,9 +39,9 @@ struct PackOptions {
     int want_rgb = 1;               // 0 in the depth-only render modes: SH colours are not evaluated
 };
 
-// model: the effective (internal) model id, see effective_model()
+// model: the effective (internal) model id, see effective_model(); rolling: the camera has a rolling shutter or an end pose
 int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const CamDev* cam, const ProjParams& pp,
-                        const PackOptions& opt, int model, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
+                        const PackOptions& opt, int model, int rolling, int tile_size, int tw, int th, int32_t* radii, float* means2d, float* depths,
                         int32_t* tiles, uint32_t* sort_keys, uint32_t* sort_vals, float4* records, uint4* bounds, float4* accum,
                         int32_t* n_visible, cudaStream_t st);
 

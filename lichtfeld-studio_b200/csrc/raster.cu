@@ -113,7 +113,9 @@ __device__ __forceinline__ void issue_stage(Stage<BATCH>& st, uint32_t* sid, con
 // RGB_ED of gsplat/Rasterization.cpp:373-393); `normalize` divides it by max(alpha, 1e-10) on output (the
 // expected-depth modes of src/training/rasterization/rasterizer.cpp:186-198) and keeps the undivided value
 // in extra_sum for the backward.
-template <int MODEL, bool EXTRA>
+// RS: rolling shutter. Every pixel has its own pose, hence its own ray origin; the record's gro = M (o_start - mu) is
+// corrected per pair by M (o_pixel - o_start).
+template <int MODEL, bool EXTRA, bool RS>
 __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
     const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
@@ -142,8 +144,9 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
         return;
     }
     const CamDev& cam = cams[0];
-    f3 d;
-    const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
+    f3 d, oo{0.f, 0.f, 0.f};
+    const bool ray_ok = RS ? pixel_world_ray_rs<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d, oo)
+                           : pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
     bool done = !inside || !ray_ok;
     uint32_t patch_x, patch_y;
     warp_patch(tile, tw, patch_x, patch_y);
@@ -199,9 +202,15 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
                     const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
                     const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
                     const float uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
-                    const float cx = uy * r2.w - r1.w * uz;
-                    const float cy = uz * r0.w - r2.w * ux;
-                    const float cz = ux * r1.w - r0.w * uy;
+                    float gx = r0.w, gy = r1.w, gz = r2.w;
+                    if (RS) {
+                        gx += r0.x * oo.x + r0.y * oo.y + r0.z * oo.z;
+                        gy += r1.x * oo.x + r1.y * oo.y + r1.z * oo.z;
+                        gz += r2.x * oo.x + r2.y * oo.y + r2.z * oo.z;
+                    }
+                    const float cx = uy * gz - gy * uz;
+                    const float cy = uz * gx - gz * ux;
+                    const float cz = ux * gy - gx * uy;
                     const float cc = cx * cx + cy * cy + cz * cz;
                     const float uu = ux * ux + uy * uy + uz * uz;
                     // power = -0.5 cc / uu ; reject when power < thr  <=>  cc > -2 thr uu
@@ -304,7 +313,7 @@ struct BwdShared {
 // EXTRA: the output has 1 or 4 channels and its last one blends bounds.w (see the forward). XGRAD: also return
 // the gradient of that per-Gaussian value in accum_extra [N] (operator-level colours with 1 or 4 channels;
 // the fused render modes drop it like gsplat/Rasterization.cpp:575-590 does).
-template <int MODEL, int BATCH, bool EXTRA, bool XGRAD>
+template <int MODEL, int BATCH, bool EXTRA, bool XGRAD, bool RS>
 __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
@@ -324,8 +333,9 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     pixel_of_thread(tile, tw, i, j);
     const bool inside = (i < H && j < W);
     const CamDev& cam = cams[0];
-    f3 d;
-    const bool ray_ok = pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
+    f3 d, oo{0.f, 0.f, 0.f};
+    const bool ray_ok = RS ? pixel_world_ray_rs<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d, oo)
+                           : pixel_world_dir<MODEL>(cam, (float)j + 0.5f, (float)i + 0.5f, d);
     const bool active = inside && ray_ok;
     const int pid = min(i * W + j, W * H - 1);
     uint32_t patch_x, patch_y;
@@ -441,7 +451,12 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                 const float ux = r0.x * d.x + r0.y * d.y + r0.z * d.z;
                 const float uy = r1.x * d.x + r1.y * d.y + r1.z * d.z;
                 const float uz = r2.x * d.x + r2.y * d.y + r2.z * d.z;
-                const float gx = r0.w, gy = r1.w, gz = r2.w;
+                float gx = r0.w, gy = r1.w, gz = r2.w;
+                if (RS) {
+                    gx += r0.x * oo.x + r0.y * oo.y + r0.z * oo.z;
+                    gy += r1.x * oo.x + r1.y * oo.y + r1.z * oo.z;
+                    gz += r2.x * oo.x + r2.y * oo.y + r2.z * oo.z;
+                }
                 float cx = uy * gz - gy * uz;
                 float cy = uz * gx - gz * ux;
                 float cz = ux * gy - gx * uy;
@@ -485,6 +500,12 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                     v[3] = vuy * d.x; v[4] = vuy * d.y; v[5] = vuy * d.z;
                     v[6] = vuz * d.x; v[7] = vuz * d.y; v[8] = vuz * d.z;
                     v[9] = -s * wx; v[10] = -s * wy; v[11] = -s * wz;
+                    if (RS) {
+                        // g = M (o_start - mu) + M (o_pixel - o_start): the second term adds v_g (x) (o_pixel - o_start) to v_M
+                        v[0] += v[9] * oo.x;  v[1] += v[9] * oo.y;  v[2] += v[9] * oo.z;
+                        v[3] += v[10] * oo.x; v[4] += v[10] * oo.y; v[5] += v[10] * oo.z;
+                        v[6] += v[11] * oo.x; v[7] += v[11] * oo.y; v[8] += v[11] * oo.z;
+                    }
                     v[15] = gate * v_alpha;
                     bufr += r3.x * fac; bufg += r3.y * fac; bufb += r3.z * fac;
                     if (EXTRA) bufx += xval * fac;
@@ -683,15 +704,17 @@ int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t
     if (n_tiles == 0) return LFS_OK;
     if (a.channels != 1 && a.channels != 3 && a.channels != 4) { set_error("raster_fwd: channels must be 1, 3 or 4"); return LFS_EINVAL; }
     LFS_TIMED("raster_fwd", st);
-#define LFS_FWD(MODEL, EXTRA)                                                                                              \
-    raster_fwd_kernel<MODEL, EXTRA><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,  \
-                                                                a.n_isects_dev, a.n_isects_host, a.overflow, a.background, \
-                                                                a.masks, a.tile_order, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles,  \
-                                                                render, alphas, last_ids, extra_sum)
+#define LFS_FWD3(MODEL, EXTRA, RS)                                                                                         \
+    raster_fwd_kernel<MODEL, EXTRA, RS><<<n_tiles, kBlock, 0, st>>>(a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets,   \
+                                                                    a.n_isects_dev, a.n_isects_host, a.overflow, a.background,  \
+                                                                    a.masks, a.tile_order, a.channels, a.normalize, a.W, a.H,   \
+                                                                    a.tw, n_tiles, render, alphas, last_ids, extra_sum)
+#define LFS_FWD(MODEL, EXTRA) do { if (a.rolling) LFS_FWD3(MODEL, EXTRA, true); else LFS_FWD3(MODEL, EXTRA, false); } while (0)
     const bool extra = a.channels != 3;
     if (a.model == LFS_PINHOLE) { if (extra) LFS_FWD(LFS_PINHOLE, true); else LFS_FWD(LFS_PINHOLE, false); }
     else if (a.model == LFS_PINHOLE_OPENCV) { if (extra) LFS_FWD(LFS_PINHOLE_OPENCV, true); else LFS_FWD(LFS_PINHOLE_OPENCV, false); }
     else { if (extra) LFS_FWD(LFS_FISHEYE, true); else LFS_FWD(LFS_FISHEYE, false); }
+#undef LFS_FWD3
 #undef LFS_FWD
     return check_launch("raster_fwd");
 }
@@ -706,8 +729,11 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     constexpr int kBwdBatch = 128;
     const size_t smem = sizeof(BwdShared<kBwdBatch>);
     static bool attr_set = false;
-#define LFS_BWD_ATTR(MODEL, EXTRA, XGRAD) \
-    cudaFuncSetAttribute(raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+#define LFS_BWD_ATTR(MODEL, EXTRA, XGRAD)                                                                                     \
+    cudaFuncSetAttribute(raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                         (int)smem);                                                                                           \
+    cudaFuncSetAttribute(raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                         (int)smem)
     if (!attr_set) {
         LFS_BWD_ATTR(LFS_PINHOLE, false, false); LFS_BWD_ATTR(LFS_PINHOLE, true, false); LFS_BWD_ATTR(LFS_PINHOLE, true, true);
         LFS_BWD_ATTR(LFS_FISHEYE, false, false); LFS_BWD_ATTR(LFS_FISHEYE, true, false); LFS_BWD_ATTR(LFS_FISHEYE, true, true);
@@ -716,12 +742,12 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
         attr_set = true;
     }
 #undef LFS_BWD_ATTR
-#define LFS_BWD(MODEL, EXTRA, XGRAD)                                                                                          \
-    raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD><<<n_tiles, kBlock, smem, st>>>(                                          \
+#define LFS_BWD4(MODEL, EXTRA, XGRAD, RS)                                                                                     \
+    raster_bwd_kernel<MODEL, kBwdBatch, EXTRA, XGRAD, RS><<<n_tiles, kBlock, smem, st>>>(                                      \
         a.cam, a.records, a.bounds, a.flatten_ids, a.tile_offsets, a.n_isects_dev, a.n_isects_host, a.overflow, a.background, \
-        a.masks, a.tile_order, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles, render_alphas, last_ids, extra_sum, v_render,   \
-        v_alphas,                                                                                                            \
-        accum, accum_extra)
+        a.masks, a.tile_order, a.channels, a.normalize, a.W, a.H, a.tw, n_tiles, render_alphas, last_ids, extra_sum, v_render, \
+        v_alphas, accum, accum_extra)
+#define LFS_BWD(MODEL, EXTRA, XGRAD) do { if (a.rolling) LFS_BWD4(MODEL, EXTRA, XGRAD, true); else LFS_BWD4(MODEL, EXTRA, XGRAD, false); } while (0)
     const bool extra = a.channels != 3, xgrad = extra && accum_extra != nullptr;
     if (a.model == LFS_PINHOLE) {
         if (!extra) LFS_BWD(LFS_PINHOLE, false, false); else if (!xgrad) LFS_BWD(LFS_PINHOLE, true, false); else LFS_BWD(LFS_PINHOLE, true, true);
@@ -731,6 +757,7 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     } else {
         if (!extra) LFS_BWD(LFS_FISHEYE, false, false); else if (!xgrad) LFS_BWD(LFS_FISHEYE, true, false); else LFS_BWD(LFS_FISHEYE, true, true);
     }
+#undef LFS_BWD4
 #undef LFS_BWD
     return check_launch("raster_bwd");
 }

@@ -22,6 +22,7 @@ struct RasterArgs {
     int normalize = 0;            // divide the extra channel by max(alpha, 1e-10) on output (expected depth)
     const uint8_t* masks = nullptr;  // [tw*th] or null: tiles labelled 0 show the background and get no gradient
     const int32_t* tile_order = nullptr;  // [tw*th] or null: CTA b works on tile tile_order[b] (longest lists first)
+    int rolling = 0;              // the camera has a rolling shutter or an end pose: per-pixel ray origins
 };
 
 // extra_sum [H*W] (may be null unless a.normalize): the blended, undivided last channel, kept for the backward.

@@ -37,8 +37,10 @@ def _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_co
     """Checks the camera arguments and returns the three coefficient tensors in the widths the C ABI reads:
     pinhole radial [C,6] (zero-padded: the reference kernel reads six floats whatever the tensor holds), tangential
     [C,2], thin prism [C,4]; fisheye radial [C,4]."""
-    if rs_type != ShutterType.GLOBAL or viewmats1 is not None:
-        raise RuntimeError("only a global shutter is supported")
+    if int(rs_type) not in (0, 1, 2, 3, 4):
+        raise RuntimeError("rs_type must be a ShutterType")
+    if viewmats1 is not None:
+        _check_input(viewmats1, "viewmats1")
     if camera_model not in (CameraModelType.PINHOLE, CameraModelType.FISHEYE):
         raise RuntimeError("camera model must be PINHOLE or FISHEYE")
     if camera_model == CameraModelType.FISHEYE and (tangential_coeffs is not None or thin_prism_coeffs is not None):
@@ -162,9 +164,9 @@ def projection_ut_3dgs_fused(means, quats, scales, opacities, viewmats0, viewmat
     depths = torch.empty((Cn, N), dtype=torch.float32, device=dev)
     conics = torch.empty((Cn, N, 3), dtype=torch.float32, device=dev)
     comps = torch.zeros((Cn, N), dtype=torch.float32, device=dev) if calc_compensations else None
-    call("lfs_projection_ut_3dgs_fused", Cn, N, ptr(means), ptr(quats), ptr(scales), ptr(opacities), ptr(viewmats0), ptr(Ks),
-         int(image_width), int(image_height), float(eps2d), float(near_plane), float(far_plane), float(radius_clip),
-         int(camera_model), ut, ptr(radial_coeffs), ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(radii), ptr(means2d), ptr(depths), ptr(conics), ptr(comps), _stream())
+    call("lfs_projection_ut_3dgs_fused", Cn, N, ptr(means), ptr(quats), ptr(scales), ptr(opacities), ptr(viewmats0), ptr(viewmats1),
+         ptr(Ks), int(image_width), int(image_height), float(eps2d), float(near_plane), float(far_plane), float(radius_clip),
+         int(camera_model), ut, int(rs_type), ptr(radial_coeffs), ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(radii), ptr(means2d), ptr(depths), ptr(conics), ptr(comps), _stream())
     return radii, means2d, depths, conics, comps
 
 
@@ -213,7 +215,8 @@ def rasterize_to_pixels_from_world_3dgs_fwd(means, quats, scales, colors, opacit
     if bg is not None and bg.numel() < CH:
         raise RuntimeError(f"backgrounds must have {CH} channels")
     call("lfs_rasterize_to_pixels_from_world_3dgs_fwd", N, flatten_ids.numel(), CH, ptr(means), ptr(quats), ptr(scales), ptr(colors),
-         ptr(opacities), ptr(bg), ptr(masks), W, H, int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model), ptr(radial_coeffs),
+         ptr(opacities), ptr(bg), ptr(masks), W, H, int(tile_size), ptr(viewmats0), ptr(viewmats1), ptr(Ks), int(camera_model),
+         int(rs_type), ptr(radial_coeffs),
          ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(renders), ptr(alphas), ptr(last_ids), ptr(ws), ws.numel(), _stream())
     return renders, alphas, last_ids
 
@@ -242,8 +245,8 @@ def rasterize_to_pixels_from_world_3dgs_bwd(means, quats, scales, colors, opacit
     bg = backgrounds if (backgrounds is not None and backgrounds.numel() > 0) else None
     ws = _ws(capi.lib().lfs_rasterize_workspace_bytes(N), dev)
     call("lfs_rasterize_to_pixels_from_world_3dgs_bwd", N, flatten_ids.numel(), CH, ptr(means), ptr(quats), ptr(scales), ptr(colors),
-         ptr(opacities), ptr(bg), ptr(masks), int(image_width), int(image_height), int(tile_size), ptr(viewmats0), ptr(Ks), int(camera_model),
-         ptr(radial_coeffs), ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(render_alphas), ptr(last_ids), ptr(v_render_colors),
+         ptr(opacities), ptr(bg), ptr(masks), int(image_width), int(image_height), int(tile_size), ptr(viewmats0), ptr(viewmats1), ptr(Ks),
+         int(camera_model), int(rs_type), ptr(radial_coeffs), ptr(tangential_coeffs), ptr(thin_prism_coeffs), ptr(tile_offsets), ptr(flatten_ids), ptr(render_alphas), ptr(last_ids), ptr(v_render_colors),
          ptr(v_render_alphas), ptr(v_means), ptr(v_quats), ptr(v_scales), ptr(v_colors), ptr(v_opacities), ptr(ws), ws.numel(),
          _stream())
     return v_means, v_quats, v_scales, v_colors, v_opacities

@@ -91,6 +91,8 @@ class Camera:
     radial: torch.Tensor | None = None      # fisheye: [4] coefficients; pinhole: [6] radial distortion (k1..k6)
     tangential: torch.Tensor | None = None  # pinhole: [2]
     thin_prism: torch.Tensor | None = None  # pinhole: [4]
+    shutter: int = 0                        # 0 global, 1 top-to-bottom, 2 left-to-right, 3 bottom-to-top, 4 right-to-left
+    viewmat_end: torch.Tensor | None = None  # [4,4] end-of-frame pose of a rolling shutter (None = the start pose)
 
     def coefficient_pointers(self):
         """Device pointers in the widths the C ABI reads (pinhole radial 6, tangential 2, thin prism 4; fisheye radial 4);
@@ -176,6 +178,8 @@ class Rasterizer:
         self.cfg.N = self.model.size
         self.cfg.camera_model = int(cam.camera_model)
         self.cfg.radial_coeffs, self.cfg.tangential_coeffs, self.cfg.thin_prism_coeffs = cam.coefficient_pointers()
+        self.cfg.shutter = int(cam.shutter)
+        self.cfg.viewmat_end = None if cam.viewmat_end is None else cam.viewmat_end.data_ptr()
         p = self.model.struct()
         call("lfs_render_forward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K),
              ptr(background), ptr(self.render), ptr(self.alpha), ptr(self.status), ptr(self.ws), self.ws.numel(), _stream())
@@ -191,6 +195,8 @@ class Rasterizer:
         self.cfg.N = self.model.size
         self.cfg.camera_model = int(cam.camera_model)
         self.cfg.radial_coeffs, self.cfg.tangential_coeffs, self.cfg.thin_prism_coeffs = cam.coefficient_pointers()
+        self.cfg.shutter = int(cam.shutter)
+        self.cfg.viewmat_end = None if cam.viewmat_end is None else cam.viewmat_end.data_ptr()
         p = self.model.struct()
         call("lfs_render_forward_lists", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), ptr(self.ws), self.ws.numel(),
              _stream())

@@ -152,6 +152,42 @@ inline Pose pose_from_viewmat(const float* vm) {
     return {quat_cast(vm), V3{vm[3], vm[7], vm[11]}};
 }
 
+// ---- rolling shutter (Cameras.cuh:33-71, :253-413) ------------------------------------------------------
+// ShutterType of gsplat/Cameras.h
+enum Shutter { ROLLING_TOP_TO_BOTTOM = 0, ROLLING_LEFT_TO_RIGHT = 1, ROLLING_BOTTOM_TO_TOP = 2, ROLLING_RIGHT_TO_LEFT = 3, GLOBAL = 4 };
+
+struct ShutterCtx {   // set by orc_set_shutter for the calls that follow (test infrastructure: one global context)
+    bool has_end = false;
+    float vm1[16] = {0};
+    int type = GLOBAL;
+};
+ShutterCtx g_shutter;
+
+struct RSPose { Pose start, end; bool has_end; int type; };
+
+// glm::slerp(x, y, a). acos / sin go through double and are rounded once (the CUDA library does the same).
+inline Q4 quat_slerp(Q4 x, Q4 y, float a) {
+    Q4 z = y;
+    float cosTheta = x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;   // glm dot order x, y, z, w
+    if (cosTheta < 0.f) { z = {-y.w, -y.x, -y.y, -y.z}; cosTheta = -cosTheta; }
+    if (cosTheta > 1.f - std::numeric_limits<float>::epsilon()) {
+        auto mix = [a](float u, float v) { return u * (1.f - a) + v * a; };
+        return {mix(x.w, z.w), mix(x.x, z.x), mix(x.y, z.y), mix(x.z, z.z)};
+    }
+    const float angle = (float)std::acos((double)cosTheta);
+    const float s0 = (float)std::sin((double)((1.f - a) * angle)), s1 = (float)std::sin((double)(a * angle));
+    const float sn = (float)std::sin((double)angle);
+    return {(s0 * x.w + s1 * z.w) / sn, (s0 * x.x + s1 * z.x) / sn, (s0 * x.y + s1 * z.y) / sn, (s0 * x.z + s1 * z.z) / sn};
+}
+
+// interpolate_shutter_pose (Cameras.cuh:268-280). Without an end pose both poses coincide and the start pose is
+// returned unchanged (slerp(q, q, a) is taken as q).
+inline Pose shutter_pose(const RSPose& rs, float t) {
+    if (!rs.has_end) return rs.start;
+    const V3 tr = (1.f - t) * rs.start.t + t * rs.end.t;
+    return {quat_slerp(rs.start.q, rs.end.q, t), tr};
+}
+
 enum CameraModel { PINHOLE = 0, ORTHO = 1, FISHEYE = 2, EQUIRECTANGULAR = 3 };
 
 struct Camera {
@@ -273,6 +309,26 @@ inline float poly_even5_d(const float* k, float x) {  // 1 + 3k1 x^2 + 5k2 x^4 +
     const float co[5] = {1.f, 3 * k[0], 5 * k[1], 7 * k[2], 9 * k[3]};
     for (int i = 4; i >= 0; --i) y = x2 * y + co[i];
     return y;
+}
+
+inline RSPose rs_from_viewmat(const float* vm) {
+    RSPose r;
+    r.start = pose_from_viewmat(vm);
+    r.has_end = g_shutter.has_end;
+    r.end = g_shutter.has_end ? pose_from_viewmat(g_shutter.vm1) : r.start;
+    r.type = g_shutter.type;
+    return r;
+}
+
+// shutter_relative_frame_time (Cameras.cuh:293-320)
+inline float shutter_time(int type, float px, float py, uint32_t W, uint32_t H) {
+    switch (type) {
+    case ROLLING_TOP_TO_BOTTOM: return std::floor(py) / (float)(H - 1);
+    case ROLLING_LEFT_TO_RIGHT: return std::floor(px) / (float)(W - 1);
+    case ROLLING_BOTTOM_TO_TOP: return ((float)H - std::ceil(py)) / (float)(H - 1);
+    case ROLLING_RIGHT_TO_LEFT: return ((float)W - std::ceil(px)) / (float)(W - 1);
+    default: return 0.f;
+    }
 }
 
 // camera_ray_to_image_point. Pinhole: Cameras.cuh:431-455. Fisheye: :894-959.
@@ -406,9 +462,41 @@ inline bool image_to_cam_ray(const Camera& c, float px, float py, V3& ray) {
     return false;
 }
 
+// world_point_to_image_point_shutter_pose (Cameras.cuh:346-413): project with the start pose; for a rolling shutter
+// take the start (else the end) projection as the initial guess and iterate 10 times pixel -> frame time -> pose ->
+// projection. The result of the last iteration is returned as valid whatever its own validity was, as in the reference.
+inline bool world_point_to_image(const Camera& c, const RSPose& rs, V3 world, float margin, V2& out) {
+    V2 p0;
+    const bool v0 = cam_point_to_image(c, quat_rotate(rs.start.q, world) + rs.start.t, margin, p0);
+    if (rs.type == GLOBAL) { out = p0; return v0; }
+    V2 p1;
+    const bool v1 = cam_point_to_image(c, quat_rotate(rs.end.q, world) + rs.end.t, margin, p1);
+    V2 prev;
+    if (v0) prev = p0;
+    else if (v1) prev = p1;
+    else { out = p1; return false; }
+    for (int j = 0; j < 10; ++j) {
+        const float t = shutter_time(rs.type, prev.x, prev.y, c.W, c.H);
+        const Pose ps = shutter_pose(rs, t);
+        V2 pj;
+        cam_point_to_image(c, quat_rotate(ps.q, world) + ps.t, margin, pj);
+        prev = pj;
+    }
+    out = prev;
+    return true;
+}
+
 }  // namespace
 
 extern "C" {
+
+// Rolling-shutter context for the calls that follow: viewmat1 (row-major 4x4 end-of-frame pose, may be null = same as
+// the start pose) and the ShutterType (4 = GLOBAL). Not thread safe; tests set it, call, and reset it.
+void orc_set_shutter(const float* viewmat1, int rs_type) {
+    g_shutter.has_end = viewmat1 != nullptr;
+    if (viewmat1) std::memcpy(g_shutter.vm1, viewmat1, 16 * sizeof(float));
+    g_shutter.type = rs_type;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Projection: gsplat/ProjectionUT3DGSFused.cu:17-210, Cameras.cuh:1070-1186, Utils.cuh:171-179.
@@ -427,7 +515,8 @@ void orc_projection_ut_3dgs_fused(
     const bool require_all = ut[4] != 0.f;
     const float ALPHA_THRESHOLD = 1.f / 255.f;
     for (int cid = 0; cid < C; ++cid) {
-        const Pose pose = pose_from_viewmat(viewmats + cid * 16);
+        const RSPose rs = rs_from_viewmat(viewmats + cid * 16);
+        const Pose pose = shutter_pose(rs, 0.5f);   // centre-of-frame pose for depth and culling (ProjectionUT3DGSFused.cu:73-77)
         const Camera cam = make_camera(camera_model, Ks + cid * 9, W, H,
                                        radial_coeffs ? radial_coeffs + cid * (camera_model == PINHOLE ? 12 : 4) : nullptr);
 #pragma omp parallel for schedule(static)
@@ -467,7 +556,7 @@ void orc_projection_ut_3dgs_fused(
             bool early = false;
             for (int i = 0; i < 7; ++i) {
                 V2 p;
-                const bool pv = cam_point_to_image(cam, quat_rotate(pose.q, pts[i]) + pose.t, margin, p);
+                const bool pv = world_point_to_image(cam, rs, pts[i], margin, p);
                 if (require_all) {
                     valid &= pv;
                     if (!pv) { early = true; break; }
@@ -739,10 +828,12 @@ void orc_intersect_offset(int64_t n_isects, const int64_t* isect_ids, int C, uin
 // Also returns n_pairs = number of list entries visited (up to and including the terminating
 // one), the implementation-independent work count used by the benchmark's flop figure.
 // ---------------------------------------------------------------------------------------------
-static void world_ray(const Pose& pose, const Camera& cam, float px, float py, V3& ro, V3& rd, bool& valid) {
+static void world_ray(const RSPose& rs, const Camera& cam, float px, float py, V3& ro, V3& rd, bool& valid) {
     V3 cr;
     valid = image_to_cam_ray(cam, px, py, cr);
     if (!valid) { ro = {0, 0, 0}; rd = {0, 0, 0}; return; }
+    // image_point_to_world_ray_shutter_pose, Cameras.cuh:322-339: the pose of this pixel's row / column
+    const Pose pose = shutter_pose(rs, shutter_time(rs.type, px, py, cam.W, cam.H));
     // ShutterPose::camera_ray_to_world_ray, Cameras.cuh:261-265
     const M3 Rinv = mat3_cast(quat_inverse(pose.q));
     M3 nR;
@@ -770,7 +861,7 @@ int64_t orc_rasterize_fwd_ch(
     float* render_colors /*[H,W,CH]*/, float* render_alphas /*[H,W]*/, int32_t* last_ids /*[H,W]*/,
     int tile_lo, int tile_hi /* only tiles in [tile_lo, tile_hi) are rendered; pass 0, -1 for all */) {
     const int tw = (W + tile_size - 1) / tile_size, th = (H + tile_size - 1) / tile_size;
-    const Pose pose = pose_from_viewmat(viewmat);
+    const RSPose pose = rs_from_viewmat(viewmat);
     const Camera cam = make_camera(camera_model, K, W, H, radial);
     int64_t n_pairs = 0;
     if (tile_hi < 0) tile_hi = tw * th;
@@ -868,7 +959,7 @@ int64_t orc_rasterize_bwd_ch(
     float* v_means, float* v_quats, float* v_scales, float* v_colors, float* v_opacities,
     int tile_lo, int tile_hi /* only tiles in [tile_lo, tile_hi) contribute; pass 0, -1 for all */) {
     const int tw = (W + tile_size - 1) / tile_size, th = (H + tile_size - 1) / tile_size;
-    const Pose pose = pose_from_viewmat(viewmat);
+    const RSPose pose = rs_from_viewmat(viewmat);
     const Camera cam = make_camera(camera_model, K, W, H, radial);
     std::vector<double> acc((size_t)N * 15, 0.0);  // mean3 scale3 quat4 colour4 opac1
     int64_t n_pairs = 0;

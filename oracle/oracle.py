@@ -271,6 +271,25 @@ def image_to_cam_ray(model, K, W, H, dist, px, py):
     return ray, bool(ok)
 
 
+GLOBAL_SHUTTER = 4   # ShutterType of gsplat/Cameras.h: 0 top-to-bottom, 1 left-to-right, 2 bottom-to-top, 3 right-to-left, 4 global
+
+
+class shutter:
+    """Context manager: the projection / rasterizer calls inside use a rolling shutter between the start pose (their
+    viewmat argument) and `viewmat1` (the reference's viewmats1), ShutterType `rs_type`."""
+
+    def __init__(self, viewmat1, rs_type):
+        self.vm1, self.type = (None if viewmat1 is None else _f32(viewmat1).reshape(4, 4)), int(rs_type)
+
+    def __enter__(self):
+        lib().orc_set_shutter(_p(self.vm1), i32(self.type))
+        return self
+
+    def __exit__(self, *exc):
+        lib().orc_set_shutter(None, i32(GLOBAL_SHUTTER))
+        return False
+
+
 def pack_distortion(radial=None, tangential=None, thin_prism=None):
     """The 12-float OpenCV pinhole distortion block this oracle takes in place of the reference's three optional
     tensors (k1..k6, p1, p2, s1..s4); shorter inputs are zero-padded. None when all three are absent."""

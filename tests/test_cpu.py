@@ -456,3 +456,37 @@ def test_oracle_ewa_gradients_finite_difference(orc, synth):
             assert min(errs) < 0.04 * abs(gflat[idx]) + 1e-3, (name, idx, errs, gflat[idx])
             checked += 1
     assert checked >= 30
+
+
+def test_oracle_rolling_shutter_rows_equal_global_renders_at_the_row_pose(orc, synth):
+    """Pins the rolling-shutter restatement (gsplat/Cameras.cuh:253-413): with a top-to-bottom shutter every image row
+    is seen from the pose interpolated at that row's frame time, so row y of the rolling render equals row y of a
+    global-shutter render from that pose (up to Gaussians whose tile lists differ by the iterative projection)."""
+    n, W, H, deg = 1500, 64, 48, 1
+    cfg, P, vm0, K = make_scene(synth, n, W, H, deg, seed=7, fx=70.0)
+    P["scaling_raw"] += 1.0
+    vm1 = vm0.copy()
+    vm1[0, 3] += 0.30          # the camera translates during the exposure (slerp of equal rotations stays put)
+    vm1[1, 3] -= 0.10
+    with orc.shutter(vm0, 0):
+        same = orc.render_fwd(P, vm0, K, W, H, deg)
+    ref0 = orc.render_fwd(P, vm0, K, W, H, deg)
+    assert np.array_equal(same["flatten_ids"], ref0["flatten_ids"]) and np.abs(same["render"] - ref0["render"]).max() == 0.0
+    with orc.shutter(vm1, 0):
+        roll = orc.render_fwd(P, vm0, K, W, H, deg)
+    assert np.abs(roll["render"] - ref0["render"]).max() > 0.05        # the motion is visible
+    for y in (0, 17, 30, 47):
+        t = np.float32(np.floor(y + 0.5) / (H - 1))
+        vmy = vm0.copy()
+        vmy[:3, 3] = (np.float32(1) - t) * vm0[:3, 3] + t * vm1[:3, 3]
+        glob = orc.render_fwd(P, vmy, K, W, H, deg)
+        diff = np.abs(roll["render"][y] - glob["render"][y]).max(-1)
+        assert np.quantile(diff, 0.9) < 2e-3 and diff.max() < 0.1, (y, diff.max())
+    # left-to-right: columns instead of rows
+    with orc.shutter(vm1, 1):
+        roll_x = orc.render_fwd(P, vm0, K, W, H, deg)
+    x = 40
+    t = np.float32(np.floor(x + 0.5) / (W - 1))
+    vmx = vm0.copy(); vmx[:3, 3] = (np.float32(1) - t) * vm0[:3, 3] + t * vm1[:3, 3]
+    diff = np.abs(roll_x["render"][:, x] - orc.render_fwd(P, vmx, K, W, H, deg)["render"][:, x]).max(-1)
+    assert np.quantile(diff, 0.9) < 2e-3
