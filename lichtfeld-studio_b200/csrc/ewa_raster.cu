@@ -140,36 +140,26 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_fwd_kernel(
     }
 }
 
-// 8 values per lane -> per-value sums over the warp; value L(lane) = 4 * bit4 + 2 * bit3 + bit2 of the lane index is
-// returned in every lane (all four lanes of a group hold the same total).
-__device__ __forceinline__ float warp_reduce8(float (&v)[8]) {
-    const int lane = threadIdx.x & 31;
-    {
-        const bool hi = lane & 16;
+// 9 values per lane -> per-value sums over the warp, value k left in lanes 2k and 2k+1 (lanes 18..31 repeat value 8).
+// The transpose goes through shared memory owned by the warp instead of a shuffle butterfly: row k (36 floats, 32 used)
+// holds value k of the 32 lanes. The row stride of 36 floats puts the 16-byte loads of one quarter-warp (lane = 2 k + h
+// reads the 16 lanes of half h of row k) on eight different bank groups, and the scalar stores of one row are contiguous.
+// The closing shuffle needs every lane's sum, hence every lane's loads, before any lane returns, so the next call may
+// overwrite the rows.
+constexpr int kRedStride = 36;
+__device__ __forceinline__ float warp_reduce9(const float (&v)[9], float* __restrict__ red, int lane) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float send = hi ? v[k] : v[k + 4];
-            const float keep = hi ? v[k + 4] : v[k];
-            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-        }
-    }
-    {
-        const bool hi = lane & 8;
+    for (int k = 0; k < 9; ++k) red[k * kRedStride + lane] = v[k];
+    __syncwarp();
+    const int k = min(lane >> 1, 8), h = lane & 1;
+    const float4* half = reinterpret_cast<const float4*>(red + k * kRedStride + 16 * h);
+    float s = 0.f;
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const float send = hi ? v[k] : v[k + 2];
-            const float keep = hi ? v[k + 2] : v[k];
-            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-        }
+    for (int q = 0; q < 4; ++q) {
+        const float4 x = half[q];
+        s += (x.x + x.y) + (x.z + x.w);
     }
-    {
-        const bool hi = lane & 4;
-        const float send = hi ? v[0] : v[1];
-        const float keep = hi ? v[1] : v[0];
-        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
-    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+    return s + __shfl_xor_sync(0xffffffffu, s, 1);
 }
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
@@ -177,7 +167,7 @@ __device__ __forceinline__ float warp_sum(float x) {
     return x;
 }
 
-__global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
+__global__ void __launch_bounds__(kBlock, 4) ewa_blend_bwd_kernel(
     const float4* __restrict__ records, const uint32_t* __restrict__ ids, const int32_t* __restrict__ tile_offsets,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, const int32_t* __restrict__ tile_order,
     int W, int H, int tw, const float* __restrict__ alpha_map, const int32_t* __restrict__ n_contrib,
@@ -188,6 +178,7 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
     __shared__ uint32_t sid[3][BATCH];                  // three deep: batch b+1 is staged while batch b-1 is flushed
     __shared__ __align__(16) float sacc_all[2][BATCH * 12];
     __shared__ int stouched_all[2][BATCH];
+    __shared__ __align__(16) float red_all[kBlock / 32][9 * kRedStride];  // per-warp transpose rows of warp_reduce9
     if (overflow && *overflow) return;
     const int tile = tile_order ? tile_order[blockIdx.x] : blockIdx.x;
     int i, j;
@@ -277,7 +268,7 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
                 const float dL_da = ga_common * rcp + (T * r1.z - ar * rcp) * gr + (T * r1.w - ag * rcp) * gg + (T * blue - ab * rcp) * gb;
                 ar += wgt * r1.z; ag += wgt * r1.w; ab += wgt * blue;
                 const float h = -a * dL_da;
-                float v[8];
+                float v[9];
                 v[0] = h * (r0.z * dx + r0.w * dy);
                 v[1] = h * (r0.w * dx + r1.x * dy);
                 v[2] = 0.5f * h * dx * dx;
@@ -286,10 +277,10 @@ __global__ void __launch_bounds__(kBlock) ewa_blend_bwd_kernel(
                 v[5] = a * dL_da;
                 v[6] = wgt * gr;
                 v[7] = wgt * gg;
-                const float v8 = warp_sum(wgt * gb);
-                const float total = warp_reduce8(v);
-                if ((lane & 3) == 0) atomicAdd(&sacc[t * 12 + (lane >> 2)], total);
-                if (lane == 0) { atomicAdd(&sacc[t * 12 + 8], v8); stouched[t] = 1; }
+                v[8] = wgt * gb;
+                const float total = warp_reduce9(v, red_all[warp], lane);
+                if ((lane & 1) == 0 && lane < 18) atomicAdd(&sacc[t * 12 + (lane >> 1)], total);
+                if (lane == 0) stouched[t] = 1;
             }
         }
     }

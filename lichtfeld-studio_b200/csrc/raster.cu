@@ -73,7 +73,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Each thread owns kParts quarter-record slots q = k * kBlock + tid of a batch: entry q >> 2, part q & 3.
 template <int BATCH>
 struct StageIds {
-    static constexpr int kParts = BATCH * 4 / kBlock;
+    static constexpr int kParts = (BATCH * 4 + kBlock - 1) / kBlock;
     uint32_t g[kParts];
 };
 
@@ -257,42 +257,24 @@ __global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
 
 // ---------------------------------------------------------------------------------------------
 // 16 values per lane -> per-value sums over the warp, value k left in lanes 2k and 2k+1.
-__device__ __forceinline__ float warp_reduce16(float (&v)[16]) {
-    const int lane = threadIdx.x & 31;
-    {
-        const bool hi = lane & 16;
+// The transpose goes through shared memory owned by the warp instead of a shuffle butterfly (about 40 issue slots
+// against 90): row k (36 floats, 32 used) holds value k of the 32 lanes. The row stride of 36 floats puts the 16-byte
+// loads of one quarter-warp (lane = 2 k + h reads the 16 lanes of half h of row k) on eight different bank groups, and
+// the scalar stores of one row are contiguous. The closing shuffle needs every lane's sum, hence every lane's loads,
+// before any lane returns, so the next call may overwrite the rows.
+constexpr int kRedStride = 36;
+__device__ __forceinline__ float warp_reduce16(const float (&v)[16], float* __restrict__ red, int lane) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float send = hi ? v[k] : v[k + 8];
-            const float keep = hi ? v[k + 8] : v[k];
-            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-        }
-    }
-    {
-        const bool hi = lane & 8;
+    for (int k = 0; k < 16; ++k) red[k * kRedStride + lane] = v[k];
+    __syncwarp();
+    const float4* half = reinterpret_cast<const float4*>(red + (lane >> 1) * kRedStride + 16 * (lane & 1));
+    float s = 0.f;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float send = hi ? v[k] : v[k + 4];
-            const float keep = hi ? v[k + 4] : v[k];
-            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-        }
+    for (int q = 0; q < 4; ++q) {
+        const float4 x = half[q];
+        s += (x.x + x.y) + (x.z + x.w);
     }
-    {
-        const bool hi = lane & 4;
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const float send = hi ? v[k] : v[k + 2];
-            const float keep = hi ? v[k + 2] : v[k];
-            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-        }
-    }
-    {
-        const bool hi = lane & 2;
-        const float send = hi ? v[0] : v[1];
-        const float keep = hi ? v[1] : v[0];
-        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-    }
-    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+    return s + __shfl_xor_sync(0xffffffffu, s, 1);
 }
 
 __device__ __forceinline__ float __reduce_add_sync_f32(float x) {
@@ -308,6 +290,7 @@ struct BwdShared {
     float sacc[2][BATCH * 16];   // per-slot sums of the batch being walked / the batch being flushed
     float sextra[2][BATCH];
     int stouched[2][BATCH];
+    float red[kBlock / 32][16 * kRedStride];  // per-warp transpose rows of warp_reduce16
 };
 
 // EXTRA: the output has 1 or 4 channels and its last one blends bounds.w (see the forward). XGRAD: also return
@@ -373,6 +356,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
     const float tail_c = T_final * (v_a - bg_dot);
     const int32_t warp_bin_final = __reduce_max_sync(0xffffffffu, bin_final);
     const int lane = threadIdx.x & 31;
+    float* red = sm.red[threadIdx.x >> 5];
 
     for (int e = threadIdx.x; e < 2 * BATCH; e += kBlock) {
 #pragma unroll
@@ -514,7 +498,7 @@ __global__ void __launch_bounds__(kBlock) raster_bwd_kernel(
                         if (lane == 0) atomicAdd(&sm.sextra[b & 1][t], xs);
                     }
                 }
-                const float total = warp_reduce16(v);
+                const float total = warp_reduce16(v, red, lane);
                 if ((lane & 1) == 0) atomicAdd(&sacc[t * 16 + (lane >> 1)], total);
                 if (lane == 0) sm.stouched[b & 1][t] = 1;
             }
@@ -726,7 +710,10 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     if (a.channels != 1 && a.channels != 3 && a.channels != 4) { set_error("raster_bwd: channels must be 1, 3 or 4"); return LFS_EINVAL; }
     if (a.normalize && !extra_sum) { set_error("raster_bwd: expected-depth modes need the forward's blended sum"); return LFS_EINVAL; }
     LFS_TIMED("raster_bwd", st);
-    constexpr int kBwdBatch = 128;
+#ifndef LFS_BWD_BATCH
+#define LFS_BWD_BATCH 64
+#endif
+    constexpr int kBwdBatch = LFS_BWD_BATCH;
     const size_t smem = sizeof(BwdShared<kBwdBatch>);
     static bool attr_set = false;
 #define LFS_BWD_ATTR(MODEL, EXTRA, XGRAD)                                                                                     \
