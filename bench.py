@@ -255,6 +255,7 @@ def run_ours(args):
     state = {"color_pending": False}
 
     dp_split = world > 1 and args.dp_mode == "fused_p2p" and not args.no_dp_split
+    rank1_sh = world == 1 and not overlap and not args.materialize_sh_grad
 
     def step(s, target, vm):
         cam = tr.Camera(vm, Kt, W, H)
@@ -277,6 +278,12 @@ def run_ours(args):
                 main.wait_event(ev_color)      # the colour groups of the previous step are up to date
             out = rast.forward_shade(bg)
         loss, v_render = lossfn(out.image, target)
+        if rank1_sh:
+            # one camera per step on one GPU: the shN gradient (three quarters of the gradient bytes) is never written;
+            # the optimizer rebuilds its rows from the sh0 gradient and the view direction
+            rast.backward(v_render, grads, bg, write_shN=False)
+            rast.adam_step_rank1_sh(m, v, grads, LRS, s + 1)
+            return loss
         rast.backward(v_render, grads, bg)
         if not overlap:
             exchange_and_adam(s + 1)
@@ -413,10 +420,20 @@ def run_ours(args):
                     "note": f"370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms; peak = 148 SM x 128 lanes x 2 x "
                             f"{sm_clock:.0f} MHz sampled under load (no tensor cores on this path)"}
         adam_bytes = 28.0 * 59 * n if K_sh == 16 else 28.0 * model.row_floats * n
+        adam_kernel = "adam_groups_kernel"
+        adam_note = f"28 B x {model.row_floats} floats x {n} Gaussians"
+        if "adam_sh_rank1" in kernels:
+            # the shN update without a gradient tensor: parameters and both moments read and written once (24 B per
+            # element), 12 B of means and 12 B of sh0 gradient per Gaussian
+            rest = model.row_floats - 14
+            t_adam = float(np.sum(kernels["adam_sh_rank1"]) / n_prof)
+            adam_bytes = (24.0 * rest + 24.0) * n
+            adam_kernel = "adam_sh_rank1_kernel"
+            adam_note = f"(24 B x {rest} shN floats + 24 B) x {n} Gaussians"
         adam_gbs = adam_bytes / (t_adam * 1e-3) / 1e9 if np.isfinite(t_adam) else None   # N > 1: Adam runs inside the exchange
-        extra = {"roofline_adam": {"kernel": "adam_groups_kernel", "bound": "hbm", "achieved": adam_gbs,
+        extra = {"roofline_adam": {"kernel": adam_kernel, "bound": "hbm", "achieved": adam_gbs,
                                    "peak": hbm_peak, "unit": "GB/s", "frac": adam_gbs / hbm_peak if adam_gbs else None,
-                                   "traffic": None, "note": f"28 B x {model.row_floats} floats x {n} Gaussians, of {peak_kind}"},
+                                   "traffic": None, "note": f"{adam_note}, of {peak_kind}"},
                  "roofline_raster_fwd": {"kernel": "raster_fwd_kernel", "bound": "fp32",
                                          "achieved": 70.0 * q_list / (t_fwd * 1e-3) / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
                                          "frac": 70.0 * q_list / (t_fwd * 1e-3) / 1e12 / fp32_peak,
@@ -436,7 +453,7 @@ def run_ours(args):
                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": world,
-                          "optimizer_overlap": bool(overlap),
+                          "optimizer_overlap": bool(overlap), "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else "materialised",
                           "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
                "clocks": clocks, "e2e": {"value": world * 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
@@ -651,6 +668,8 @@ def main():
     ap.add_argument("--overlap", action="store_true",
                     help="single GPU: split optimizer, colour groups on a side stream under the next step's projection and "
                          "tile lists (measured: no gain on B200, 2.975 ms against 2.964 ms; both sides are memory-latency sensitive)")
+    ap.add_argument("--materialize-sh-grad", action="store_true",
+                    help="single GPU: write the shN gradient and run lfs_adam_step_splats instead of lfs_adam_step_splats_rank1_sh")
     ap.add_argument("--no-dp-split", action="store_true",
                     help="N > 1, fused_p2p: exchange all groups in one kernel after the backward. Default: geometry groups first, "
                          "colour groups on a side stream (one CTA per SM) under the next step's projection and tile lists "

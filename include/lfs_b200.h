@@ -252,7 +252,8 @@ int lfs_render_forward_shade(const lfs_render_config* cfg, const lfs_splats* par
  * and the opacity gradient is not multiplied by the compensation.
  * Call it once per lfs_render_forward: it consumes the per-Gaussian accumulators that the forward zeroed.
  * grads: the six raw-parameter gradients; accumulate != 0 adds to them, else they are overwritten
- * (all N rows, zeros for Gaussians that were not visible). */
+ * (all N rows, zeros for Gaussians that were not visible). grads->shN may be NULL: that gradient is then not written
+ * (see lfs_adam_step_splats_rank1_sh). */
 int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
                         const float* alpha, const float* v_render, const float* v_alpha, const lfs_splats* grads,
                         int accumulate, void* workspace, size_t workspace_bytes, void* stream);
@@ -297,6 +298,19 @@ int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const l
                          const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr,
                          double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
                          int64_t first_row, int64_t n_rows, float grad_scale, void* stream);
+
+/* FusedAdam::step (src/training/optimizers/fused_adam.cpp:22-95) after a ONE-camera lfs_render_backward whose
+ * grads->shN was NULL: the higher-order SH gradient is never materialised. For one camera, row g of that gradient is the
+ * outer product of the SH basis of Gaussian g's view direction with its clamped colour gradient, and grads->sh0 holds
+ * Y_0 times that colour gradient (gsplat/SphericalHarmonicsCUDA.cu:113-371), so the kernel that updates shN rebuilds the
+ * rows on the fly from grads->sh0, params->means and the camera of the forward state in `workspace` (the one the backward
+ * used). The other five groups are updated from their gradient tensors as in lfs_adam_step_splats. Saves the write and the
+ * read of 12 (K-1) N gradient bytes per step; the result equals backward-with-shN + lfs_adam_step_splats up to one
+ * rounding of the colour gradient. Not for gradients accumulated over several cameras (their sum is no outer product). */
+int lfs_adam_step_splats_rank1_sh(const lfs_render_config* cfg, const lfs_splats* params, const lfs_splats* exp_avg,
+                                  const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr /* host[6] */,
+                                  double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
+                                  float grad_scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /* src/training/kernels/regularization.cu:20 / :171 (compute_exp_l1_regularization_with_grad_cuda,
  * compute_sigmoid_l1_regularization_with_grad_cuda), both in one launch and without the host read:

@@ -98,6 +98,9 @@ _SIGNATURES = {
     "lfs_photometric_loss": [i32, i32, f32, f32, vp, vp, vp, vp, vp, sz, vp],
     "lfs_adam_step_splats": [i32, i32, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),
                              C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, i64, i64, f32, vp],
+    "lfs_adam_step_splats_rank1_sh": [C.POINTER(RenderConfig), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),
+                                      C.POINTER(Splats), C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, f32,
+                                      vp, sz, vp],
     "lfs_regularization": [i32, vp, vp, f32, f32, vp, vp, vp, vp],
     "lfs_adam_step_segments": [i32, C.POINTER(AdamSegment), C.c_double, C.c_double, C.c_double, i64, f32, i32, vp],
     "lfs_dp_reduce_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, C.POINTER(DpSegment), C.c_double,

@@ -776,6 +776,30 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
                                       *grads, accumulate, cfg_modifier(*cfg), st);
 }
 
+int lfs_adam_step_splats_rank1_sh(const lfs_render_config* cfg, const lfs_splats* params, const lfs_splats* exp_avg,
+                                  const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr, double beta1,
+                                  double beta2, double eps, int64_t step_count, int skip_shN, float grad_scale,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && exp_avg && exp_avg_sq && grads && lr && workspace, "null pointer");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_adam_step_splats_rank1_sh: workspace too small"); return LFS_ECAPACITY; }
+    // shN first: its gradient rows depend on the means, which the second launch updates
+    if (!skip_shN && cfg->sh_coeffs > 1 && cfg->N > 0) {
+        LFS_REQUIRE(params->shN && exp_avg->shN && exp_avg_sq->shN && grads->sh0 && params->means, "null tensor in a parameter group");
+        const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+        const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
+        rc = launch_adam_sh_rank1(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, params->means, grads->sh0, params->shN,
+                                  exp_avg->shN, exp_avg_sq->shN, (float)((double)lr[2]) * (float)bc1, (float)beta1, (float)beta2,
+                                  (float)eps, (float)bc2, grad_scale, S(stream));
+        if (rc != LFS_OK) return rc;
+    }
+    // the five small groups from their gradient tensors, exactly as lfs_adam_step_splats does
+    return lfs_adam_step_splats(cfg->N, cfg->sh_coeffs, params, exp_avg, exp_avg_sq, grads, lr, beta1, beta2, eps, step_count,
+                                /*skip_shN=*/1, 0, cfg->N, grad_scale, stream);
+}
+
 int lfs_render_workspace_view(const lfs_render_config* cfg, void* workspace, size_t workspace_bytes, lfs_render_view* view) {
     int rc = check_cfg(cfg);
     if (rc != LFS_OK) return rc;

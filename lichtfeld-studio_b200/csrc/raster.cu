@@ -646,13 +646,13 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
 #pragma unroll
             for (int k = 0; k < 3; ++k) g0[k] = B[0] * vc[k];
         }
-        for (int k = 1; k < K; ++k) {
-            const float w = k < nb ? B[k] : 0.f;
+        if (g_shN) {  // NULL: the caller forms these rows itself from the sh0 gradient (adam_sh_rank1_kernel)
+            for (int k = 1; k < K; ++k) {
+                const float w = k < nb ? B[k] : 0.f;
 #pragma unroll
-            for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] = w * vc[c];
-        }
-        __syncwarp();
-        {
+                for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] = w * vc[c];
+            }
+            __syncwarp();
             const int n_rows = min(32, N - chunk * 32);
             const int total = n_rows * rest;
             float* dst = g_shN + (size_t)chunk * 32 * rest;
@@ -662,8 +662,8 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
             } else {
                 for (int i = lane; i < total; i += 32) dst[i] = my[i];
             }
+            __syncwarp();
         }
-        __syncwarp();
         if (in_range && (visible || !accumulate)) {
             if (accumulate) {
 #pragma unroll
@@ -678,6 +678,110 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
                 g_opacity[g] = go;
             }
         }
+    }
+}
+
+// Adam on the higher-order SH coefficients without a gradient tensor. For one camera the gradient row of a Gaussian
+// is the outer product of the SH basis of its view direction with the clamped colour gradient vc, and the sh0
+// gradient already holds Y00 * vc; so the rows are rebuilt here, 32 Gaussians per warp in shared memory, and the
+// parameter / moment rows (one contiguous run per warp) are streamed through once, 16 bytes per lane and U vectors of
+// each tensor in flight. Same update arithmetic as the optimizer kernels.
+struct AdamRank1 {
+    float* p; float* m; float* v;
+    float step_size, beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
+    int vec;  // the three pointers are 16-byte aligned
+};
+__device__ __forceinline__ void adam_rank1_update(float& p, float& m, float& v, float g, const AdamRank1& A) {
+    const float m1 = A.beta1 * m + (1.0f - A.beta1) * g;
+    const float m2 = A.beta2 * v + (1.0f - A.beta2) * g * g;
+    const float denom = sqrtf(m2) * A.bc2_sqrt_rcp + A.eps;
+    p -= A.step_size * m1 / denom;
+    m = m1;
+    v = m2;
+}
+// KT: the number of SH coefficients when known at compile time (16 = degree 3, the training default; the row loop
+// then unrolls and the basis stays in registers), 0 = generic.
+template <int KT>
+__global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, int sh_degree, const CamDev* __restrict__ cams,
+                                                               const float* __restrict__ means, const float* __restrict__ g_sh0,
+                                                               AdamRank1 A) {
+    extern __shared__ __align__(16) float s_rows[];
+    constexpr int U = 3;
+    const int K = KT ? KT : K_rt;
+    const float cx = cams[0].campos[0], cy = cams[0].campos[1], cz = cams[0].campos[2];
+    const int rest = (K - 1) * 3;
+    const int nb = (sh_degree + 1) * (sh_degree + 1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my = s_rows + (size_t)warp * 32 * rest;
+    const int n_chunks = (N + 31) / 32;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
+        const int g = chunk * 32 + lane;
+        float vc[3] = {0.f, 0.f, 0.f};
+        if (g < N) {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) vc[c] = g_sh0[g * 3 + c] / 0.2820947917738781f;
+        }
+        float B[25];
+#pragma unroll
+        for (int k = 0; k < 25; ++k) B[k] = 0.f;
+        if (vc[0] != 0.f || vc[1] != 0.f || vc[2] != 0.f)
+            sh_basis(sh_degree, means[g * 3] - cx, means[g * 3 + 1] - cy, means[g * 3 + 2] - cz, B);
+        if (KT) {
+#pragma unroll
+            for (int k = 1; k < (KT ? KT : 1); ++k) {
+                const float w = k < nb ? B[k] : 0.f;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] = w * vc[c];
+            }
+        } else {
+            for (int k = 1; k < K; ++k) {
+                const float w = k < nb ? B[k] : 0.f;
+#pragma unroll
+                for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] = w * vc[c];
+            }
+        }
+        __syncwarp();
+        const int total = min(32, N - chunk * 32) * rest;
+        const size_t base = (size_t)chunk * 32 * rest;
+        float* __restrict__ pp = A.p + base;
+        float* __restrict__ mm = A.m + base;
+        float* __restrict__ vv = A.v + base;
+        int done = 0;
+        if (A.vec) {
+            const int total4 = total >> 2;
+            float4* __restrict__ p4 = reinterpret_cast<float4*>(pp);
+            float4* __restrict__ m4 = reinterpret_cast<float4*>(mm);
+            float4* __restrict__ v4 = reinterpret_cast<float4*>(vv);
+            const float4* __restrict__ g4 = reinterpret_cast<const float4*>(my);
+            for (int i0 = lane; i0 < total4; i0 += 32 * U) {
+                float4 p[U], m[U], v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int i = i0 + 32 * u;
+                    if (i < total4) { p[u] = p4[i]; m[u] = m4[i]; v[u] = v4[i]; }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int i = i0 + 32 * u;
+                    if (i < total4) {
+                        const float4 gr = g4[i];
+                        adam_rank1_update(p[u].x, m[u].x, v[u].x, gr.x * A.grad_scale, A);
+                        adam_rank1_update(p[u].y, m[u].y, v[u].y, gr.y * A.grad_scale, A);
+                        adam_rank1_update(p[u].z, m[u].z, v[u].z, gr.z * A.grad_scale, A);
+                        adam_rank1_update(p[u].w, m[u].w, v[u].w, gr.w * A.grad_scale, A);
+                        p4[i] = p[u]; m4[i] = m[u]; v4[i] = v[u];
+                    }
+                }
+            }
+            done = total4 << 2;
+        }
+        for (int i = done + lane; i < total; i += 32) {
+            float p = pp[i], m = mm[i], v = vv[i];
+            adam_rank1_update(p, m, v, my[i] * A.grad_scale, A);
+            pp[i] = p; mm[i] = m; vv[i] = v;
+        }
+        __syncwarp();
     }
 }
 
@@ -773,6 +877,22 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
                                                                  g.sh0, g.shN, g.scaling_raw, g.rotation_raw,
                                                                  g.opacity_raw, accumulate, scaling_modifier);
     return check_launch("grad_epilogue_fused");
+}
+
+int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const float* means, const float* g_sh0, float* p,
+                         float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
+                         float grad_scale, cudaStream_t st) {
+    if (N == 0 || K <= 1) return LFS_OK;
+    LFS_TIMED("adam_sh_rank1", st);
+    const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
+    if (smem > 200 * 1024) { set_error("adam_sh_rank1: too many SH coefficients"); return LFS_EINVAL; }
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(adam_sh_rank1_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    AdamRank1 A{p, m, v, step_size, beta1, beta2, eps, bc2_sqrt_rcp, grad_scale,
+                (int)(((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0)};
+    if (K == 16) adam_sh_rank1_kernel<16><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, means, g_sh0, A);
+    else adam_sh_rank1_kernel<0><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, means, g_sh0, A);
+    return check_launch("adam_sh_rank1");
 }
 
 }  // namespace lfs

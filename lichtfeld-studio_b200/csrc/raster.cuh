@@ -36,5 +36,10 @@ int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const 
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
                                int accumulate, float scaling_modifier, cudaStream_t st);
+// Adam on the shN tensor with the gradient rows rebuilt from the sh0 gradient of a one-camera backward
+// (g_shN[k][c] = Y_k(direction) * g_sh0[c] / Y_0); p, m, v are the shN parameter and moment tensors [N, K-1, 3].
+int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const float* means, const float* g_sh0, float* p,
+                         float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
+                         float grad_scale, cudaStream_t st);
 
 }  // namespace lfs

@@ -211,10 +211,23 @@ class Rasterizer:
         return RenderOutput(image, self.alpha, self.W, self.H, self.status, depth, self.render)
 
     def backward(self, v_render: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
-                 v_alpha: torch.Tensor | None = None, accumulate: bool = False):
+                 v_alpha: torch.Tensor | None = None, accumulate: bool = False, write_shN: bool = True):
+        """write_shN=False leaves grads' shN tensor untouched (one-camera steps that update shN with adam_step_rank1_sh)."""
         p, g = self.model.struct(), grads.struct()
+        if not write_shN:
+            g.shN = None
         call("lfs_render_backward", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.alpha), ptr(v_render), ptr(v_alpha),
              C.byref(g), 1 if accumulate else 0, ptr(self.ws), self.ws.numel(), _stream())
+
+    def adam_step_rank1_sh(self, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
+                           beta1=0.9, beta2=0.999, eps=1e-15, skip_shN=False, grad_scale=1.0):
+        """FusedAdam::step after backward(write_shN=False) of ONE camera: the shN rows are updated from gradient rows
+        rebuilt on the fly as (SH basis of the view direction) x (sh0 gradient / Y_0); the other groups as usual."""
+        p, m, v, g = self.model.struct(), exp_avg.struct(), exp_avg_sq.struct(), grads.struct()
+        lr = (C.c_float * 6)(*[float(x) for x in lrs])
+        call("lfs_adam_step_splats_rank1_sh", C.byref(self.cfg), C.byref(p), C.byref(m), C.byref(v), C.byref(g), lr, float(beta1),
+             float(beta2), float(eps), int(step_count), 1 if skip_shN else 0, float(grad_scale), ptr(self.ws), self.ws.numel(),
+             _stream())
 
 
     def state(self) -> dict:

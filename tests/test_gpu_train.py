@@ -148,3 +148,63 @@ def test_split_forward_and_split_adam_equal_the_fused_calls(pkg, synth):
     tr.adam_step_groups(model2, m2, v2, ga, LRS, 3, tr.GEOMETRY_GROUPS)
     tr.adam_step_groups(model2, m2, v2, ga, LRS, 3, tr.COLOR_GROUPS)
     assert torch.equal(model.flat, model2.flat) and torch.equal(m1.flat, m2.flat) and torch.equal(v1.flat, v2.flat)
+
+
+@pytest.mark.parametrize("n,W,H,deg,skip_shN", [(12000, 200, 120, 3, False), (5003, 97, 61, 2, False), (5003, 97, 61, 3, True),
+                                                 (4001, 80, 64, 0, False)])
+def test_rank1_sh_adam_equals_materialised_gradient(pkg, synth, n, W, H, deg, skip_shN):
+    """backward(write_shN=False) + lfs_adam_step_splats_rank1_sh == backward + lfs_adam_step_splats: the shN gradient
+    rows rebuilt inside the optimizer from the sh0 gradient equal the materialised ones up to rounding."""
+    tr = pkg.trainer
+    K = (deg + 1) ** 2
+    cfg, P, vm, Kmat = make_scene(synth, n, W, H, deg, seed=21)
+    cam = tr.Camera(T(vm), T(Kmat), W, H)
+    bg = T(np.array([0.3, 0.1, 0.6], np.float32))
+    rng = np.random.default_rng(5)
+    v_render = T(rng.normal(size=(H, W, 3)).astype(np.float32))
+    models, moments = [], []
+    for _ in range(2):
+        model = tr.SplatData(n, K, DEV).load(P)
+        m, v = model.like(), model.like()
+        # non-zero moments make the update a smooth function of the gradient (no sign flips on tiny gradients)
+        gen = torch.Generator(device=DEV).manual_seed(77)
+        m.flat.copy_(torch.randn(m.flat.shape, generator=gen, device=DEV) * 1e-3)
+        v.flat.copy_(torch.rand(v.flat.shape, generator=gen, device=DEV) * 1e-4 + 1e-6)
+        models.append(model); moments.append((m, v))
+    ra, rb = tr.Rasterizer(models[0], W, H, deg), tr.Rasterizer(models[1], W, H, deg)
+    ra.forward(cam, bg)
+    ga = models[0].like()
+    ra.backward(v_render, ga, bg)
+    tr.adam_step_splats(models[0], moments[0][0], moments[0][1], ga, LRS, 3, skip_shN=skip_shN, grad_scale=0.5)
+    rb.forward(cam, bg)
+    gb = models[1].like()
+    if K > 1:
+        gb.tensor("shN").fill_(123.0)
+    rb.backward(v_render, gb, bg, write_shN=False)
+    if K > 1:
+        assert bool((gb.tensor("shN") == 123.0).all())       # not written
+    rb.adam_step_rank1_sh(moments[1][0], moments[1][1], gb, LRS, 3, skip_shN=skip_shN, grad_scale=0.5)
+    vis = (ra.state()["radii"] > 0).all(-1)
+    assert 0 < int(vis.sum()) < n
+    worst = {}
+    for name in NAMES:
+        pa, pb = models[0].tensor(name), models[1].tensor(name)
+        if pa.numel() == 0:
+            continue
+        p0 = torch.from_numpy(np.ascontiguousarray(P[name], dtype=np.float32)).reshape(pa.shape).to(DEV)
+        d_a, d_b = (pa - p0).cpu().numpy(), (pb - p0).cpu().numpy()
+        if name == "shN" and skip_shN:
+            assert not d_a.any() and not d_b.any()
+        else:
+            assert np.abs(d_a).max() > 0
+            # the steps are ~1e-5 of the parameter values, so float32 subtraction alone costs ~1e-4 here; the moments
+            # below carry the gradient at full precision
+            assert rel_l2(d_b, d_a) < 1e-3, name
+        for k in range(2):
+            worst[(name, k)] = rel_l2(moments[1][k].tensor(name).cpu().numpy(), moments[0][k].tensor(name).cpu().numpy())
+    assert max(worst.values()) < 1e-5, worst
+    # Gaussians that were not visible take a zero gradient in both paths: identical rows
+    hidden = (~vis).cpu().numpy()
+    if K > 1 and not skip_shN:
+        assert np.array_equal(models[1].tensor("shN").cpu().numpy()[hidden], models[0].tensor("shN").cpu().numpy()[hidden])
+        assert np.array_equal(moments[1][0].tensor("shN").cpu().numpy()[hidden], moments[0][0].tensor("shN").cpu().numpy()[hidden])
