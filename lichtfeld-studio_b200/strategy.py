@@ -57,9 +57,18 @@ class FusedAdam:
         self.exp_avg, self.exp_avg_sq = model.like(), model.like()
         self.step_count = 0
 
-    def step(self, iteration: int, grads: SplatData, grad_scale: float = 1.0, first_row: int = 0, n_rows=None):
+    def step(self, iteration: int, grads: SplatData, grad_scale: float = 1.0, first_row: int = 0, n_rows=None,
+             rasterizer=None):
+        """rasterizer: the Rasterizer whose backward(write_shN=False) of ONE camera produced `grads`; the shN rows are then
+        updated from gradient rows rebuilt inside the optimizer kernel (lfs_adam_step_splats_rank1_sh)."""
         self.step_count += 1  # advances for the skipped shN group as well (fused_adam.cpp:66-70)
         self.exp_avg.size = self.exp_avg_sq.size = grads.size = self.model.size
+        if rasterizer is not None:
+            if first_row != 0 or n_rows not in (None, self.model.size):
+                raise RuntimeError("the rank-1 shN update covers all rows")
+            rasterizer.adam_step_rank1_sh(self.exp_avg, self.exp_avg_sq, grads, self.lr, self.step_count, self.betas[0],
+                                          self.betas[1], self.eps, skip_shN=(iteration <= 1000), grad_scale=grad_scale)
+            return
         adam_step_splats(self.model, self.exp_avg, self.exp_avg_sq, grads, self.lr, self.step_count, self.betas[0], self.betas[1],
                          self.eps, skip_shN=(iteration <= 1000), first_row=first_row, n_rows=n_rows, grad_scale=grad_scale)
 
@@ -151,9 +160,9 @@ class MCMC(IStrategy):
             self.add_new_gs()
         self.inject_noise()
 
-    def step(self, iter: int, grad_scale: float = 1.0):
+    def step(self, iter: int, grad_scale: float = 1.0, rasterizer=None):
         if iter < self._params.iterations:
-            self._optimizer.step(iter, self.grads, grad_scale)
+            self._optimizer.step(iter, self.grads, grad_scale, rasterizer=rasterizer)
             self._optimizer.zero_grad(True, iter)
             self._scheduler.step()
 
