@@ -108,3 +108,32 @@ def test_backward_is_linear_in_the_output_gradient(pkg, full):
     grads = model.like(); grads.flat.copy_(outs[2])
     for name in ("means", "shN", "opacity_raw"):
         assert float(grads.tensor(name)[~vis].abs().max()) == 0.0
+
+
+def test_rank1_sh_update_equals_materialised_gradient_update(pkg, full):
+    """At full size: Adam moments after backward(write_shN=False) + the rank-1 shN update equal those after the plain
+    backward + Adam (the gradient rows rebuilt inside the optimizer are the materialised ones up to rounding)."""
+    tr = pkg.trainer
+    rast, model = full["rast"], full["model"]
+    lrs = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+    g = torch.Generator(device=DEV).manual_seed(9)
+    v = (torch.randn(full["H"], full["W"], 3, device=DEV, generator=g) * 1e-3).contiguous()
+    saved = model.flat.clone()
+    moments = []
+    for rank1 in (False, True):
+        model.flat.copy_(saved)
+        m, s = model.like(), model.like()
+        rast.forward(full["cam"], full["bg"])
+        grads = model.like()
+        if rank1:
+            rast.backward(v, grads, full["bg"], write_shN=False)
+            rast.adam_step_rank1_sh(m, s, grads, lrs, 1)
+        else:
+            rast.backward(v, grads, full["bg"])
+            tr.adam_step_splats(model, m, s, grads, lrs, 1)
+        moments.append((m.flat.clone(), s.flat.clone()))
+    model.flat.copy_(saved)
+    for k in range(2):
+        a, b = moments[0][k], moments[1][k]
+        assert float(a.abs().max()) > 0
+        assert float((a - b).norm() / a.norm()) < 1e-5, k
