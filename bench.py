@@ -256,6 +256,7 @@ def run_ours(args):
 
     dp_split = world > 1 and args.dp_mode == "fused_p2p" and not args.no_dp_split
     rank1_sh = world == 1 and not overlap and not args.materialize_sh_grad
+    dp_rank1 = dp_split and not args.materialize_sh_grad
 
     def step(s, target, vm):
         cam = tr.Camera(vm, Kt, W, H)
@@ -266,8 +267,9 @@ def run_ours(args):
             exchange.wait_color()
             out = rast.forward_shade(bg)
             loss, v_render = lossfn(out.image, target)
-            rast.backward(v_render, grads, bg)
-            exchange.step_split(2000 + s + 1, side)
+            # one camera per rank: the shN gradient crosses NVLink as its two rank-1 factors (24 bytes per Gaussian)
+            rast.backward(v_render, grads, bg, sh_factors=dp_rank1)
+            exchange.step_split(2000 + s + 1, side, rank1_sh=dp_rank1, sh_degree=deg)
             return loss
         if not overlap:
             out = rast.forward(cam, bg)
@@ -453,7 +455,7 @@ def run_ours(args):
                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": world,
-                          "optimizer_overlap": bool(overlap), "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else "materialised",
+                          "optimizer_overlap": bool(overlap), "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else ("rank-1 factors over NVLink" if dp_rank1 else "materialised"),
                           "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
                "clocks": clocks, "e2e": {"value": world * 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
@@ -669,7 +671,7 @@ def main():
                     help="single GPU: split optimizer, colour groups on a side stream under the next step's projection and "
                          "tile lists (measured: no gain on B200, 2.975 ms against 2.964 ms; both sides are memory-latency sensitive)")
     ap.add_argument("--materialize-sh-grad", action="store_true",
-                    help="single GPU: write the shN gradient and run lfs_adam_step_splats instead of lfs_adam_step_splats_rank1_sh")
+                    help="write the shN gradient rows (lfs_adam_step_splats / element-wise exchange) instead of using their rank-1 form")
     ap.add_argument("--no-dp-split", action="store_true",
                     help="N > 1, fused_p2p: exchange all groups in one kernel after the backward. Default: geometry groups first, "
                          "colour groups on a side stream (one CTA per SM) under the next step's projection and tile lists "

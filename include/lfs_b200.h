@@ -155,6 +155,20 @@ int lfs_adam_step(float* param, float* exp_avg, float* exp_avg_sq, const float* 
                   float lr, float beta1, float beta2, float eps, float bias_correction1_rcp,
                   float bias_correction2_sqrt_rcp, void* stream);
 
+/* Data-parallel exchange of the higher-order SH gradient in rank-1 form, fused with the optimizer (no counterpart in
+ * the reference). Every rank ran lfs_render_backward for ONE camera with LFS_BACKWARD_SH_FACTORS; this rank owns the
+ * elements [lo, lo + n) of the shN tensor [N_capacity, K-1, 3]. For the rows that intersect them the kernel loads every
+ * rank's 24-byte factor row through NVLink peer pointers, sums the outer products (SH basis of the direction) x (colour
+ * gradient) in the order given, applies Adam with this rank's moments (exp_avg / exp_avg_sq are indexed from `lo`) and
+ * stores the new coefficients into every rank's shN tensor. peer_factors[i] / peer_shN[i] (host arrays of `world` device
+ * pointers) belong to rank (own_rank + i) % world, entry 0 is this rank's own. It moves 24 N / world bytes per peer in
+ * instead of 12 (K-1) N / world; ordering against the other ranks as for lfs_dp_reduce_adam_broadcast. Rows >= N
+ * (capacity padding) take a zero gradient. Plain peer loads / stores only; no multicast. */
+int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, float* const* peer_shN, int N, int sh_coeffs,
+                                   int sh_degree, int64_t lo, int64_t n, float* exp_avg, float* exp_avg_sq, float lr,
+                                   double beta1, double beta2, double eps, int64_t step_count, float grad_scale,
+                                   int ctas_per_sm, void* stream);
+
 /* gsplat/Ops.h:50-57 relocation -> gsplat/RelocationCUDA.cu:12. */
 int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms,
                    int n_max, float* new_opacities, float* new_scales, void* stream);
@@ -251,9 +265,15 @@ int lfs_render_forward_shade(const lfs_render_config* cfg, const lfs_splats* par
  * only acts on the parameters through alpha (its per-Gaussian gradient is dropped, gsplat/Rasterization.cpp:575-590)
  * and the opacity gradient is not multiplied by the compensation.
  * Call it once per lfs_render_forward: it consumes the per-Gaussian accumulators that the forward zeroed.
- * grads: the six raw-parameter gradients; accumulate != 0 adds to them, else they are overwritten
- * (all N rows, zeros for Gaussians that were not visible). grads->shN may be NULL: that gradient is then not written
- * (see lfs_adam_step_splats_rank1_sh). */
+ * grads: the six raw-parameter gradients. `accumulate` is a set of lfs_backward_flags: with LFS_BACKWARD_ACCUMULATE the
+ * gradients are added to, else they are overwritten (all N rows, zeros for Gaussians that were not visible).
+ * grads->shN may be NULL: that gradient is then not written (see lfs_adam_step_splats_rank1_sh). With
+ * LFS_BACKWARD_SH_FACTORS the start of grads->shN receives, instead of the rows, their two factors as [N,6] floats
+ * (clamped colour gradient, unit view direction) for lfs_dp_sh_rank1_adam_broadcast; not together with ACCUMULATE. */
+typedef enum lfs_backward_flags {
+    LFS_BACKWARD_ACCUMULATE = 1,
+    LFS_BACKWARD_SH_FACTORS = 2
+} lfs_backward_flags;
 int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
                         const float* alpha, const float* v_render, const float* v_alpha, const lfs_splats* grads,
                         int accumulate, void* workspace, size_t workspace_bytes, void* stream);

@@ -533,6 +533,34 @@ int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, floa
     return launch_dp_reduce_adam_broadcast(A, ctas_per_sm, S_(stream));
 }
 
+int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, float* const* peer_shN, int N, int sh_coeffs,
+                                   int sh_degree, int64_t lo, int64_t n, float* exp_avg, float* exp_avg_sq, float lr,
+                                   double beta1, double beta2, double eps, int64_t step_count, float grad_scale,
+                                   int ctas_per_sm, void* stream) {
+    LFS_REQUIRE(world >= 1 && world <= kRank1MaxPeers, "world must be in [1, 8]");
+    LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
+    LFS_REQUIRE(N >= 0 && sh_coeffs >= 1 && sh_degree >= 0 && (sh_degree + 1) * (sh_degree + 1) <= sh_coeffs, "bad sizes");
+    LFS_REQUIRE(lo >= 0 && n >= 0, "bad element range");
+    LFS_REQUIRE(ctas_per_sm >= 0 && ctas_per_sm <= 16, "ctas_per_sm must be in [0, 16]");
+    if (n == 0 || sh_coeffs == 1) return LFS_OK;
+    LFS_REQUIRE(peer_factors && peer_shN && exp_avg && exp_avg_sq, "null pointer");
+    const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
+    DpRank1 A{};
+    A.world = world; A.N = N; A.lo = lo; A.n = n; A.m = exp_avg; A.v = exp_avg_sq;
+    bool vec = lo % 4 == 0 && aligned16(exp_avg) && aligned16(exp_avg_sq);
+    for (int r = 0; r < world; ++r) {
+        LFS_REQUIRE(peer_factors[r] && peer_shN[r], "null peer pointer");
+        LFS_REQUIRE((reinterpret_cast<uintptr_t>(peer_factors[r]) & 7) == 0, "factor buffers must be 8-byte aligned");
+        A.factors[r] = peer_factors[r];
+        A.shN[r] = peer_shN[r];
+        vec = vec && aligned16(peer_shN[r]);
+    }
+    A.vec = vec;
+    A.adam = AdamRank1{nullptr, nullptr, nullptr, lr * (float)bc1, (float)beta1, (float)beta2, (float)eps, (float)bc2, grad_scale, 0};
+    return launch_dp_sh_rank1(sh_coeffs, sh_degree, A, ctas_per_sm, S_(stream));
+}
+
 int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,
                    float* new_opacities, float* new_scales, void* stream) {
     LFS_REQUIRE(n >= 0 && n_max > 0, "bad sizes");
@@ -772,8 +800,11 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
                   mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order, cfg_rolling(*cfg)};
     rc = launch_raster_bwd(ra, alpha, w.last_ids, w.extra_sum, v_render, v_alpha, w.accum, nullptr, st);
     if (rc != LFS_OK) return rc;
+    const int sh_factors = (accumulate & LFS_BACKWARD_SH_FACTORS) != 0;
+    if (sh_factors) LFS_REQUIRE(!(accumulate & LFS_BACKWARD_ACCUMULATE), "the shN factors of several cameras cannot be accumulated");
+    if (sh_factors && grads->shN) LFS_REQUIRE((reinterpret_cast<uintptr_t>(grads->shN) & 7) == 0, "grads->shN must be 8-byte aligned");
     return launch_grad_epilogue_fused(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, w.accum, w.records, w.radii, *params,
-                                      *grads, accumulate, cfg_modifier(*cfg), st);
+                                      *grads, accumulate & LFS_BACKWARD_ACCUMULATE, cfg_modifier(*cfg), sh_factors, st);
 }
 
 int lfs_adam_step_splats_rank1_sh(const lfs_render_config* cfg, const lfs_splats* params, const lfs_splats* exp_avg,

@@ -594,7 +594,7 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
     const float* __restrict__ means, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
     const float* __restrict__ opacity_raw,
     float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN, float* __restrict__ g_scaling,
-    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate, float scaling_modifier) {
+    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate, float scaling_modifier, int sh_factors) {
     extern __shared__ float s_rows[];
     const CamDev& cam = cams[0];
     const int rest = (K - 1) * 3;
@@ -646,7 +646,20 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
 #pragma unroll
             for (int k = 0; k < 3; ++k) g0[k] = B[0] * vc[k];
         }
-        if (g_shN) {  // NULL: the caller forms these rows itself from the sh0 gradient (adam_sh_rank1_kernel)
+        if (g_shN && sh_factors) {
+            // the two factors of the rank-1 rows instead of the rows: [N,6] = (clamped colour gradient, unit view direction)
+            // at the start of the shN gradient tensor, for the data-parallel exchange that sums the outer products
+            if (in_range) {
+                float dx = 0.f, dy = 0.f, dz = 0.f;
+                if (visible) {
+                    dx = means[g * 3] - cam.campos[0]; dy = means[g * 3 + 1] - cam.campos[1]; dz = means[g * 3 + 2] - cam.campos[2];
+                    const float inorm = rsqrtf(dx * dx + dy * dy + dz * dz);
+                    dx *= inorm; dy *= inorm; dz *= inorm;
+                }
+                float2* f = reinterpret_cast<float2*>(g_shN) + (size_t)g * 3;
+                f[0] = make_float2(vc[0], vc[1]); f[1] = make_float2(vc[2], dx); f[2] = make_float2(dy, dz);
+            }
+        } else if (g_shN) {  // NULL: the caller forms these rows itself from the sh0 gradient (adam_sh_rank1_kernel)
             for (int k = 1; k < K; ++k) {
                 const float w = k < nb ? B[k] : 0.f;
 #pragma unroll
@@ -686,11 +699,6 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
 // gradient already holds Y00 * vc; so the rows are rebuilt here, 32 Gaussians per warp in shared memory, and the
 // parameter / moment rows (one contiguous run per warp) are streamed through once, 16 bytes per lane and U vectors of
 // each tensor in flight. Same update arithmetic as the optimizer kernels.
-struct AdamRank1 {
-    float* p; float* m; float* v;
-    float step_size, beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
-    int vec;  // the three pointers are 16-byte aligned
-};
 __device__ __forceinline__ void adam_rank1_update(float& p, float& m, float& v, float g, const AdamRank1& A) {
     const float m1 = A.beta1 * m + (1.0f - A.beta1) * g;
     const float m2 = A.beta2 * v + (1.0f - A.beta2) * g * g;
@@ -785,6 +793,102 @@ __global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, 
     }
 }
 
+// Data-parallel form of adam_sh_rank1_kernel: this rank owns the elements [lo, lo + n) of the shN tensor. For the rows
+// that intersect them, the gradient row is the sum over ranks of (SH basis of that rank's view direction) x (that
+// rank's clamped colour gradient), both read from the rank's factor buffer [N,6] through its peer pointer (24 bytes per
+// row and rank instead of the 12 (K-1) bytes of a materialised row); then Adam with the shard-local moments and 16-byte
+// stores of the new coefficients into every rank's parameter buffer. Plain peer loads and stores; the caller orders the
+// launch against the other ranks.
+template <int KT>
+__global__ void __launch_bounds__(256) dp_sh_rank1_kernel(int K_rt, int sh_degree, DpRank1 A) {
+    extern __shared__ __align__(16) float s_rows[];
+    constexpr int U = 2;
+    const int K = KT ? KT : K_rt;
+    const int rest = (K - 1) * 3;
+    const int nb = (sh_degree + 1) * (sh_degree + 1);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* my = s_rows + (size_t)warp * 32 * rest;
+    const int64_t hi = A.lo + A.n;
+    const int64_t chunk_elems = (int64_t)32 * rest;
+    const int64_t first_chunk = A.lo / chunk_elems, last_chunk = (hi - 1) / chunk_elems;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int64_t chunk = first_chunk + blockIdx.x * (blockDim.x >> 5) + warp; chunk <= last_chunk; chunk += warps_total) {
+        const int64_t g = chunk * 32 + lane;
+        for (int j = 0; j < rest; ++j) my[lane * rest + j] = 0.f;
+        if (g < A.N) {
+            for (int r = 0; r < A.world; ++r) {
+                const float2* f = reinterpret_cast<const float2*>(A.factors[r]) + g * 3;
+                const float2 f0 = f[0], f1 = f[1], f2 = f[2];
+                const float vc[3] = {f0.x, f0.y, f1.x};
+                if (vc[0] == 0.f && vc[1] == 0.f && vc[2] == 0.f) continue;
+                float B[25];
+#pragma unroll
+                for (int k = 0; k < 25; ++k) B[k] = 0.f;
+                sh_basis(sh_degree, f1.y, f2.x, f2.y, B);
+                if (KT) {
+#pragma unroll
+                    for (int k = 1; k < (KT ? KT : 1); ++k) {
+                        const float w = k < nb ? B[k] : 0.f;
+#pragma unroll
+                        for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] += w * vc[c];
+                    }
+                } else {
+                    for (int k = 1; k < K; ++k) {
+                        const float w = k < nb ? B[k] : 0.f;
+#pragma unroll
+                        for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] += w * vc[c];
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        const int64_t c0 = chunk * chunk_elems;
+        const int64_t e0 = max(A.lo, c0), e1 = min(hi, c0 + chunk_elems);
+        const int total = (int)(e1 - e0);
+        const float* __restrict__ grad = my + (e0 - c0);
+        const float* __restrict__ pp = A.shN[0] + e0;   // every rank holds the same coefficients; read the local copy
+        float* __restrict__ mm = A.m + (e0 - A.lo);
+        float* __restrict__ vv = A.v + (e0 - A.lo);
+        int done = 0;
+        if (A.vec) {
+            const int total4 = total >> 2;
+            const float4* __restrict__ p4 = reinterpret_cast<const float4*>(pp);
+            float4* __restrict__ m4 = reinterpret_cast<float4*>(mm);
+            float4* __restrict__ v4 = reinterpret_cast<float4*>(vv);
+            const float4* __restrict__ g4 = reinterpret_cast<const float4*>(grad);
+            for (int i0 = lane; i0 < total4; i0 += 32 * U) {
+                float4 p[U], m[U], v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int i = i0 + 32 * u;
+                    if (i < total4) { p[u] = p4[i]; m[u] = m4[i]; v[u] = v4[i]; }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int i = i0 + 32 * u;
+                    if (i < total4) {
+                        const float4 gr = g4[i];
+                        adam_rank1_update(p[u].x, m[u].x, v[u].x, gr.x * A.adam.grad_scale, A.adam);
+                        adam_rank1_update(p[u].y, m[u].y, v[u].y, gr.y * A.adam.grad_scale, A.adam);
+                        adam_rank1_update(p[u].z, m[u].z, v[u].z, gr.z * A.adam.grad_scale, A.adam);
+                        adam_rank1_update(p[u].w, m[u].w, v[u].w, gr.w * A.adam.grad_scale, A.adam);
+                        m4[i] = m[u]; v4[i] = v[u];
+                        for (int r = 0; r < A.world; ++r) reinterpret_cast<float4*>(A.shN[r] + e0)[i] = p[u];
+                    }
+                }
+            }
+            done = total4 << 2;
+        }
+        for (int i = done + lane; i < total; i += 32) {
+            float p = pp[i], m = mm[i], v = vv[i];
+            adam_rank1_update(p, m, v, grad[i] * A.adam.grad_scale, A.adam);
+            mm[i] = m; vv[i] = v;
+            for (int r = 0; r < A.world; ++r) A.shN[r][e0 + i] = p;
+        }
+        __syncwarp();
+    }
+}
+
 }  // namespace
 
 int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t* last_ids, float* extra_sum, cudaStream_t st) {
@@ -865,7 +969,7 @@ int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const 
 
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
-                               int accumulate, float scaling_modifier, cudaStream_t st) {
+                               int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED("grad_epilogue", st);
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
@@ -875,7 +979,7 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
     grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
                                                                  p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
                                                                  g.sh0, g.shN, g.scaling_raw, g.rotation_raw,
-                                                                 g.opacity_raw, accumulate, scaling_modifier);
+                                                                 g.opacity_raw, accumulate, scaling_modifier, sh_factors);
     return check_launch("grad_epilogue_fused");
 }
 
@@ -893,6 +997,20 @@ int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const f
     if (K == 16) adam_sh_rank1_kernel<16><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, means, g_sh0, A);
     else adam_sh_rank1_kernel<0><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, means, g_sh0, A);
     return check_launch("adam_sh_rank1");
+}
+
+int launch_dp_sh_rank1(int K, int sh_degree, const DpRank1& A, int ctas_per_sm, cudaStream_t st) {
+    if (A.n == 0 || K <= 1) return LFS_OK;
+    LFS_TIMED("dp_sh_rank1", st);
+    const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
+    if (smem > 200 * 1024) { set_error("dp_sh_rank1: too many SH coefficients"); return LFS_EINVAL; }
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(dp_sh_rank1_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int64_t chunks = (A.lo + A.n - 1) / (32 * (K - 1) * 3) - A.lo / (32 * (K - 1) * 3) + 1;
+    const int grid = grid_for(chunks * 32, 256, ctas_per_sm > 0 ? ctas_per_sm : 4);
+    if (K == 16) dp_sh_rank1_kernel<16><<<grid, 256, smem, st>>>(K, sh_degree, A);
+    else dp_sh_rank1_kernel<0><<<grid, 256, smem, st>>>(K, sh_degree, A);
+    return check_launch("dp_sh_rank1");
 }
 
 }  // namespace lfs

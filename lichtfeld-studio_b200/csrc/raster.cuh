@@ -35,11 +35,29 @@ int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const 
                             float* v_scales, float* v_colors, float* v_opacities, cudaStream_t st);
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
-                               int accumulate, float scaling_modifier, cudaStream_t st);
+                               int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st);
 // Adam on the shN tensor with the gradient rows rebuilt from the sh0 gradient of a one-camera backward
 // (g_shN[k][c] = Y_k(direction) * g_sh0[c] / Y_0); p, m, v are the shN parameter and moment tensors [N, K-1, 3].
 int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const float* means, const float* g_sh0, float* p,
                          float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
                          float grad_scale, cudaStream_t st);
+
+struct AdamRank1 {
+    float* p; float* m; float* v;
+    float step_size, beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
+    int vec;  // the three pointers are 16-byte aligned
+};
+// Data-parallel rank-1 shN update (see dp_sh_rank1_kernel). factors[i] / shN[i]: peer-mapped factor buffer [N,6] and shN
+// parameter tensor of rank (own + i) % world; [lo, lo + n) this rank's element range of the shN tensor; m / v its moments.
+constexpr int kRank1MaxPeers = 8;
+struct DpRank1 {
+    const float* factors[kRank1MaxPeers];
+    float* shN[kRank1MaxPeers];
+    int64_t lo, n;
+    float* m; float* v;
+    AdamRank1 adam;   // p / m / v unused here
+    int world, N, vec;
+};
+int launch_dp_sh_rank1(int K, int sh_degree, const DpRank1& A, int ctas_per_sm, cudaStream_t st);
 
 }  // namespace lfs

@@ -212,14 +212,31 @@ class GradExchange:
         capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
                   self.step_count, float(gs), int(ctas_per_sm), self._stream())
 
-    def step_split(self, iteration: int, side_stream, grad_scale: float | None = None):
+    def _rank1_call(self, seg, m, v, gs, sh_degree, ctas_per_sm=0):
+        """The shN part of this rank's colour shard from every rank's factor buffer (see Rasterizer.backward(sh_factors=True))."""
+        gi, off, cnt, lr, rel = seg
+        w = row_widths(self.model.K)
+        shn_off = self.model.capacity * (w["means"] + w["sh0"])      # flat offset of the shN tensor (group-major layout)
+        order = [(self.rank + i) % self.world for i in range(self.world)]
+        pf = (C.c_void_p * self.world)(*[self.peer_grads[r] + 4 * shn_off for r in order])
+        ps = (C.c_void_p * self.world)(*[self.peer_params[r] + 4 * shn_off for r in order])
+        capi.call("lfs_dp_sh_rank1_adam_broadcast", self.world, pf, ps, self.model.size, self.model.K, int(sh_degree),
+                  off - shn_off, cnt, capi.vp(m.data_ptr() + 4 * rel), capi.vp(v.data_ptr() + 4 * rel), float(lr), self.betas[0],
+                  self.betas[1], self.eps, self.step_count, float(gs), int(ctas_per_sm), self._stream())
+
+    def step_split(self, iteration: int, side_stream, grad_scale: float | None = None, rank1_sh: bool = False,
+                   sh_degree: int | None = None):
         """fused_p2p in two parts. On the current stream: rendezvous, reduce + Adam + broadcast of the geometry groups
         (means, scales, rotations, opacities), rendezvous. On `side_stream`: the same for the colour groups (sh0, shN:
         three quarters of the bytes), finishing with its own rendezvous on a second communicator. The caller may start
         the next step's projection and tile lists right away and must call wait_color() before anything reads the
-        colour groups or overwrites the gradients."""
+        colour groups or overwrites the gradients. rank1_sh: every rank rendered ONE camera and ran
+        backward(sh_factors=True); the shN gradient then crosses NVLink as 24 bytes per Gaussian and rank (sh_degree = the
+        degree the forward used)."""
         if self.mode != "fused_p2p":
             raise RuntimeError("step_split needs mode fused_p2p")
+        if rank1_sh and sh_degree is None:
+            raise RuntimeError("rank1_sh needs the SH degree of the forward")
         st = self._split_state(side_stream)
         self.step_count += 1
         gs = 1.0 / self.world if grad_scale is None else grad_scale
@@ -236,7 +253,17 @@ class GradExchange:
             st["side"].wait_event(st["ev_grads"])
             segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
             # small footprint: this kernel shares the SMs with the next step's projection and sorting
-            self._fused_call(segs, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
+            if rank1_sh:
+                # every rank's backward wrote the factors of its rank-1 shN rows instead of the rows: sh0 goes through the
+                # element-wise kernel, shN through the kernel that sums the outer products
+                plain = [sg for sg in segs if PARAM_NAMES[sg[0]] != "shN"]
+                if plain:
+                    self._fused_call(plain, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
+                for sg in segs:
+                    if PARAM_NAMES[sg[0]] == "shN":
+                        self._rank1_call(sg, st["col_m"], st["col_v"], gs, sh_degree, ctas_per_sm=self.color_ctas_per_sm)
+            else:
+                self._fused_call(segs, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
             dist.all_reduce(st["token_b"], group=st["group_b"])  # every rank's colour kernel has finished
             st["ev_color"].record(st["side"])
         st["pending"] = True

@@ -211,13 +211,17 @@ class Rasterizer:
         return RenderOutput(image, self.alpha, self.W, self.H, self.status, depth, self.render)
 
     def backward(self, v_render: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
-                 v_alpha: torch.Tensor | None = None, accumulate: bool = False, write_shN: bool = True):
-        """write_shN=False leaves grads' shN tensor untouched (one-camera steps that update shN with adam_step_rank1_sh)."""
+                 v_alpha: torch.Tensor | None = None, accumulate: bool = False, write_shN: bool = True,
+                 sh_factors: bool = False):
+        """write_shN=False leaves grads' shN tensor untouched (one-camera steps that update shN with adam_step_rank1_sh).
+        sh_factors=True writes the two factors of the rank-1 shN rows, [N,6], at the start of grads' shN tensor instead
+        of the rows (data-parallel steps of one camera per rank, GradExchange.step_split(rank1_sh=True))."""
         p, g = self.model.struct(), grads.struct()
         if not write_shN:
             g.shN = None
+        flags = (1 if accumulate else 0) | (2 if sh_factors else 0)
         call("lfs_render_backward", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.alpha), ptr(v_render), ptr(v_alpha),
-             C.byref(g), 1 if accumulate else 0, ptr(self.ws), self.ws.numel(), _stream())
+             C.byref(g), flags, ptr(self.ws), self.ws.numel(), _stream())
 
     def adam_step_rank1_sh(self, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
                            beta1=0.9, beta2=0.999, eps=1e-15, skip_shN=False, grad_scale=1.0):

@@ -56,6 +56,20 @@ def main():
                     rast.backward(vr, grads, bg, accumulate=(r > 0))
                 tr.adam_step_splats(model, m, v, grads, LRS, s + 1, skip_shN=False, grad_scale=1.0 / world)
             return model.flat.clone()
+        if mode == "fused_p2p_split_rank1":
+            # as fused_p2p_split, with the shN gradient crossing NVLink as its two rank-1 factors
+            ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
+            side = torch.cuda.Stream(device=dev)
+            for s in range(steps):
+                rast.forward_lists(cam(s * world + rank))
+                ex.wait_color()
+                out = rast.forward_shade(bg)
+                _, vr = lossfn(out.image, targets[s * world + rank])
+                rast.backward(vr, grads, bg, sh_factors=True)
+                ex.step_split(2000 + s, side, rank1_sh=True, sh_degree=deg)
+            ex.wait_color()
+            torch.cuda.synchronize()
+            return model.flat.clone()
         if mode == "fused_p2p_split":
             # geometry groups exchanged on the main stream, colour groups on a side stream under the next step's lists
             ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
@@ -81,7 +95,7 @@ def main():
 
     ref = run("local")
     ok = True
-    for mode in ("allreduce", "sharded", "fused_p2p", "fused_p2p_split"):
+    for mode in ("allreduce", "sharded", "fused_p2p", "fused_p2p_split", "fused_p2p_split_rank1"):
         try:
             out = run(mode)
         except Exception as e:  # report and keep the ranks in lock step
