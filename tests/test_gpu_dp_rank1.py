@@ -79,3 +79,15 @@ def test_two_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg):
     f = facs[0].tensor("shN").reshape(-1)[: n * 6].reshape(n, 6)
     nz = f[:, :3].abs().sum(1) > 0
     assert bool(nz.any()) and float((f[nz, 3:].norm(dim=1) - 1).abs().max()) < 1e-5
+
+
+def test_factors_cannot_be_accumulated(pkg, synth):
+    tr, capi = pkg.trainer, pkg._capi
+    n, W, H, deg = 2000, 64, 48, 1
+    cfg, P, vm, Kmat = make_scene(synth, n, W, H, deg, seed=4)
+    model = tr.SplatData(n, 4, DEV).load(P)
+    rast = tr.Rasterizer(model, W, H, deg)
+    rast.forward(tr.Camera(T(vm), T(Kmat), W, H), None)
+    v = torch.zeros(H, W, 3, device=DEV)
+    with pytest.raises(capi.LfsError):
+        rast.backward(v, model.like(), None, accumulate=True, sh_factors=True)
