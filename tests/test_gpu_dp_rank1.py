@@ -1,5 +1,5 @@
-"""The data-parallel rank-1 shN update (lfs_dp_sh_rank1_adam_broadcast) on ONE GPU: the "ranks" are two cameras whose
-factor buffers and parameter copies live on the same device, so the kernel's peer pointers are plain local pointers.
+"""The data-parallel rank-1 shN update (lfs_dp_sh_rank1_adam_broadcast) on ONE GPU: the "ranks" are cameras whose
+factor buffers and parameter copies live on the same device (2, 4 and 8 of them), so the kernel's peer pointers are plain local pointers.
 Reference: the materialised gradients of both cameras accumulated, then lfs_adam_step_splats."""
 import ctypes as C
 
@@ -18,17 +18,17 @@ def T(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
-@pytest.mark.parametrize("n,deg", [(6000, 3), (4004, 2)])
-def test_two_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg):
+@pytest.mark.parametrize("n,deg,world", [(6000, 3, 2), (4004, 2, 2), (6000, 3, 4), (5000, 3, 8)])
+def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world):
     tr, capi = pkg.trainer, pkg._capi
     W, H, K = 160, 120, (deg + 1) ** 2
     rest = (K - 1) * 3
     cfg, P, vm0, Kmat = make_scene(synth, n, W, H, deg, seed=31)
     poses = synth.hemisphere_poses(8, 4.0)
-    cams = [tr.Camera(T(vm0), T(Kmat), W, H), tr.Camera(T(poses[3]), T(Kmat), W, H)]
+    cams = [tr.Camera(T(vm0), T(Kmat), W, H)] + [tr.Camera(T(poses[(3 * r) % 8]), T(Kmat), W, H) for r in range(1, world)]
     bg = T(np.array([0.1, 0.4, 0.2], np.float32))
     rng = np.random.default_rng(2)
-    vr = [T(rng.normal(size=(H, W, 3)).astype(np.float32)) for _ in range(2)]
+    vr = [T(rng.normal(size=(H, W, 3)).astype(np.float32)) for _ in range(world)]
 
     def fresh():
         model = tr.SplatData(n, K, DEV).load(P)
@@ -42,15 +42,15 @@ def test_two_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg):
     ref, m_ref, v_ref = fresh()
     rast = tr.Rasterizer(ref, W, H, deg)
     grads = ref.like()
-    for r in range(2):
+    for r in range(world):
         rast.forward(cams[r], bg)
         rast.backward(vr[r], grads, bg, accumulate=(r > 0))
-    tr.adam_step_splats(ref, m_ref, v_ref, grads, LRS, 2, grad_scale=0.5)
+    tr.adam_step_splats(ref, m_ref, v_ref, grads, LRS, 2, grad_scale=1.0 / world)
 
     # emulated ranks: each camera's factors, then the kernel with two "peers"
-    copies = [fresh(), fresh()]
+    copies = [fresh() for _ in range(world)]
     facs = []
-    for r in range(2):
+    for r in range(world):
         model = copies[r][0]
         rr = tr.Rasterizer(model, W, H, deg)
         g = model.like()
@@ -62,15 +62,16 @@ def test_two_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg):
     cut = (total // 2) // 4 * 4 + 4          # a 4-aligned cut inside a row
     assert cut % rest != 0
     stream = capi.vp(torch.cuda.current_stream().cuda_stream)
-    pf = (C.c_void_p * 2)(facs[0].tensor("shN").data_ptr(), facs[1].tensor("shN").data_ptr())
-    ps = (C.c_void_p * 2)(copies[0][0].tensor("shN").data_ptr(), copies[1][0].tensor("shN").data_ptr())
+    pf = (C.c_void_p * world)(*[facs[r].tensor("shN").data_ptr() for r in range(world)])
+    ps = (C.c_void_p * world)(*[copies[r][0].tensor("shN").data_ptr() for r in range(world)])
     for lo, cnt in ((0, cut), (cut, total - cut)):
-        capi.call("lfs_dp_sh_rank1_adam_broadcast", 2, pf, ps, n, K, deg, lo, cnt,
+        capi.call("lfs_dp_sh_rank1_adam_broadcast", world, pf, ps, n, K, deg, lo, cnt,
                   capi.vp(m_own.tensor("shN").data_ptr() + 4 * lo), capi.vp(v_own.tensor("shN").data_ptr() + 4 * lo),
-                  LRS[2], 0.9, 0.999, 1e-15, 2, 0.5, 0, stream)
+                  LRS[2], 0.9, 0.999, 1e-15, 2, 1.0 / world, 0, stream)
     torch.cuda.synchronize()
-    a, b = copies[0][0].tensor("shN"), copies[1][0].tensor("shN")
-    assert torch.equal(a, b)                                   # both "ranks" received the same coefficients
+    a = copies[0][0].tensor("shN")
+    for r in range(1, world):
+        assert torch.equal(a, copies[r][0].tensor("shN"))      # every "rank" received the same coefficients
     p0 = T(P["shN"]).reshape(a.shape)
     assert rel_l2((a - p0).cpu().numpy(), (ref.tensor("shN") - p0).cpu().numpy()) < 1e-3
     assert rel_l2(m_own.tensor("shN").cpu().numpy(), m_ref.tensor("shN").cpu().numpy()) < 1e-5
