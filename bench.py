@@ -570,8 +570,13 @@ def run_ewa(args):
         hwc.copy_(out.image.permute(1, 2, 0))        # the loss kernels read HWC; two small layout copies per step
         loss, v_hwc = lossfn(hwc, target)
         chw.copy_(v_hwc.permute(2, 0, 1))
-        rast.backward(chw, grads, bg, densification_info=dens)
-        tr.adam_step_splats(model, m, v, grads, lrs, s + 1)
+        if args.materialize_sh_grad:
+            rast.backward(chw, grads, bg, densification_info=dens)
+            tr.adam_step_splats(model, m, v, grads, lrs, s + 1)
+        else:
+            # one camera per step: the shN gradient rows are rebuilt inside the optimizer kernel
+            rast.backward(chw, grads, bg, densification_info=dens, write_shN=False)
+            rast.adam_step_rank1_sh(m, v, grads, lrs, s + 1)
         return out
 
     for s in range(max(3, args.warmup)):

@@ -461,6 +461,15 @@ int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const 
                      const lfs_splats* grads, int accumulate, float* densification_info,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* FusedAdam::step after a ONE-camera lfs_ewa_backward whose grads->shN was NULL (that gradient is then not written):
+ * the shN rows are updated from gradient rows rebuilt on the fly as (SH basis of the view direction from cam_position) x
+ * (grads->sh0 / Y_0), the other five groups from their gradient tensors. Same contract as lfs_adam_step_splats_rank1_sh;
+ * cam_position [3] is the device pointer given to the backward. */
+int lfs_ewa_adam_step_rank1_sh(const lfs_ewa_config* cfg, const lfs_splats* params, const float* cam_position,
+                               const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq, const lfs_splats* grads,
+                               const float* lr /* host[6] */, double beta1, double beta2, double eps, int64_t step_count,
+                               int skip_shN, float grad_scale, void* stream);
+
 /* Device pointers into a workspace that holds a finished lfs_ewa_forward (tests, inspection). */
 typedef struct lfs_ewa_view {
     const int32_t* n_touched;     /* [N] tiles reached per Gaussian (0 = culled) */

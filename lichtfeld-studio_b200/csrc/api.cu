@@ -1,6 +1,7 @@
 // extern "C" entry points declared in include/lfs_b200.h: argument checks, workspace carving and
 // the launch sequences. No allocation happens here; every call is asynchronous on the caller's stream.
 #include <cmath>
+#include <cstddef>
 #include <cstring>
 
 #include "elementwise.cuh"
@@ -649,6 +650,30 @@ int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const 
                                densification_info, st);
 }
 
+int lfs_ewa_adam_step_rank1_sh(const lfs_ewa_config* cfg, const lfs_splats* params, const float* cam_position,
+                               const lfs_splats* exp_avg, const lfs_splats* exp_avg_sq, const lfs_splats* grads,
+                               const float* lr, double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
+                               float grad_scale, void* stream) {
+    int rc = check_ewa_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && exp_avg && exp_avg_sq && grads && lr && cam_position, "null pointer");
+    LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
+    // shN first: its gradient rows depend on the means, which the second launch updates
+    if (!skip_shN && cfg->sh_coeffs > 1 && cfg->N > 0) {
+        LFS_REQUIRE(params->shN && exp_avg->shN && exp_avg_sq->shN && grads->sh0 && params->means, "null tensor in a parameter group");
+        int degree = 0;
+        while ((degree + 1) * (degree + 1) < cfg->active_sh_bases) ++degree;
+        const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+        const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
+        rc = launch_adam_sh_rank1(cfg->N, cfg->sh_coeffs, degree, cam_position, params->means, grads->sh0, params->shN,
+                                  exp_avg->shN, exp_avg_sq->shN, (float)((double)lr[2]) * (float)bc1, (float)beta1, (float)beta2,
+                                  (float)eps, (float)bc2, grad_scale, S(stream));
+        if (rc != LFS_OK) return rc;
+    }
+    return lfs_adam_step_splats(cfg->N, cfg->sh_coeffs, params, exp_avg, exp_avg_sq, grads, lr, beta1, beta2, eps, step_count,
+                                /*skip_shN=*/1, 0, cfg->N, grad_scale, stream);
+}
+
 int lfs_ewa_workspace_view(const lfs_ewa_config* cfg, void* workspace, size_t workspace_bytes, lfs_ewa_view* out) {
     int rc = check_ewa_cfg(cfg);
     if (rc != LFS_OK) return rc;
@@ -821,7 +846,8 @@ int lfs_adam_step_splats_rank1_sh(const lfs_render_config* cfg, const lfs_splats
         LFS_REQUIRE(params->shN && exp_avg->shN && exp_avg_sq->shN && grads->sh0 && params->means, "null tensor in a parameter group");
         const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
         const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
-        rc = launch_adam_sh_rank1(cfg->N, cfg->sh_coeffs, cfg->sh_degree, w.cam, params->means, grads->sh0, params->shN,
+        const float* campos = reinterpret_cast<const float*>(reinterpret_cast<const char*>(w.cam) + offsetof(CamDev, campos));
+        rc = launch_adam_sh_rank1(cfg->N, cfg->sh_coeffs, cfg->sh_degree, campos, params->means, grads->sh0, params->shN,
                                   exp_avg->shN, exp_avg_sq->shN, (float)((double)lr[2]) * (float)bc1, (float)beta1, (float)beta2,
                                   (float)eps, (float)bc2, grad_scale, S(stream));
         if (rc != LFS_OK) return rc;

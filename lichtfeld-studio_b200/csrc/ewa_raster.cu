@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(256) ewa_epilogue_kernel(
         if (!any_visible) {
             // nothing in this chunk reached a tile: zeros (or untouched when accumulating)
             if (!accumulate) {
-                for (int k = lane; k < total; k += 32) dst_rows[k] = 0.f;
+                if (g_shN) for (int k = lane; k < total; k += 32) dst_rows[k] = 0.f;
                 if (in_range) {
 #pragma unroll
                     for (int k = 0; k < 3; ++k) { g_means[i * 3 + k] = 0.f; g_sh0[i * 3 + k] = 0.f; g_scaling[i * 3 + k] = 0.f; }
@@ -492,7 +492,9 @@ __global__ void __launch_bounds__(256) ewa_epilogue_kernel(
         }
         }  // visible
         __syncwarp();
-        if (accumulate) {
+        if (!g_shN) {
+            // the caller rebuilds these rows from the sh0 gradient (lfs_ewa_adam_step_rank1_sh)
+        } else if (accumulate) {
             for (int k = lane; k < total; k += 32) dst_rows[k] += my[k];
         } else {
             for (int k = lane; k < total; k += 32) dst_rows[k] = my[k];

@@ -710,13 +710,13 @@ __device__ __forceinline__ void adam_rank1_update(float& p, float& m, float& v, 
 // KT: the number of SH coefficients when known at compile time (16 = degree 3, the training default; the row loop
 // then unrolls and the basis stays in registers), 0 = generic.
 template <int KT>
-__global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, int sh_degree, const CamDev* __restrict__ cams,
+__global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, int sh_degree, const float* __restrict__ campos,
                                                                const float* __restrict__ means, const float* __restrict__ g_sh0,
                                                                AdamRank1 A) {
     extern __shared__ __align__(16) float s_rows[];
     constexpr int U = 3;
     const int K = KT ? KT : K_rt;
-    const float cx = cams[0].campos[0], cy = cams[0].campos[1], cz = cams[0].campos[2];
+    const float cx = campos[0], cy = campos[1], cz = campos[2];
     const int rest = (K - 1) * 3;
     const int nb = (sh_degree + 1) * (sh_degree + 1);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -983,7 +983,7 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
     return check_launch("grad_epilogue_fused");
 }
 
-int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const float* means, const float* g_sh0, float* p,
+int launch_adam_sh_rank1(int N, int K, int sh_degree, const float* campos, const float* means, const float* g_sh0, float* p,
                          float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
                          float grad_scale, cudaStream_t st) {
     if (N == 0 || K <= 1) return LFS_OK;
@@ -994,8 +994,8 @@ int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const f
         cudaFuncSetAttribute(adam_sh_rank1_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     AdamRank1 A{p, m, v, step_size, beta1, beta2, eps, bc2_sqrt_rcp, grad_scale,
                 (int)(((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0)};
-    if (K == 16) adam_sh_rank1_kernel<16><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, means, g_sh0, A);
-    else adam_sh_rank1_kernel<0><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, means, g_sh0, A);
+    if (K == 16) adam_sh_rank1_kernel<16><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, campos, means, g_sh0, A);
+    else adam_sh_rank1_kernel<0><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, campos, means, g_sh0, A);
     return check_launch("adam_sh_rank1");
 }
 

@@ -38,7 +38,8 @@ int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, c
                                int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st);
 // Adam on the shN tensor with the gradient rows rebuilt from the sh0 gradient of a one-camera backward
 // (g_shN[k][c] = Y_k(direction) * g_sh0[c] / Y_0); p, m, v are the shN parameter and moment tensors [N, K-1, 3].
-int launch_adam_sh_rank1(int N, int K, int sh_degree, const CamDev* cam, const float* means, const float* g_sh0, float* p,
+// campos: device [3], the camera position in world space that the backward used.
+int launch_adam_sh_rank1(int N, int K, int sh_degree, const float* campos, const float* means, const float* g_sh0, float* p,
                          float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
                          float grad_scale, cudaStream_t st);
 

@@ -312,13 +312,25 @@ class FastRasterizer:
         return RenderOutput(self.image, self.alpha, self.W, self.H, self.status)
 
     def backward(self, grad_image: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
-                 grad_alpha: torch.Tensor | None = None, accumulate: bool = False, densification_info: torch.Tensor | None = None):
-        """grad_image [3,H,W] w.r.t. the final (background-blended) image; densification_info [2,N] is updated in place."""
+                 grad_alpha: torch.Tensor | None = None, accumulate: bool = False, densification_info: torch.Tensor | None = None,
+                 write_shN: bool = True):
+        """grad_image [3,H,W] w.r.t. the final (background-blended) image; densification_info [2,N] is updated in place.
+        write_shN=False leaves grads' shN tensor untouched (one-camera steps that update shN with adam_step_rank1_sh)."""
         cam = self._cam
         p, g = self.model.struct(), grads.struct()
+        if not write_shN:
+            g.shN = None
         call("lfs_ewa_backward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam._campos), ptr(background), ptr(self.alpha),
              ptr(grad_image), ptr(grad_alpha), C.byref(g), 1 if accumulate else 0, ptr(densification_info), ptr(self.ws),
              self.ws.numel(), _stream())
+
+    def adam_step_rank1_sh(self, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
+                           beta1=0.9, beta2=0.999, eps=1e-15, skip_shN=False, grad_scale=1.0):
+        """FusedAdam::step after backward(write_shN=False) of ONE camera (see Rasterizer.adam_step_rank1_sh)."""
+        p, m, v, g = self.model.struct(), exp_avg.struct(), exp_avg_sq.struct(), grads.struct()
+        lr = (C.c_float * 6)(*[float(x) for x in lrs])
+        call("lfs_ewa_adam_step_rank1_sh", C.byref(self.cfg), C.byref(p), ptr(self._cam._campos), C.byref(m), C.byref(v), C.byref(g),
+             lr, float(beta1), float(beta2), float(eps), int(step_count), 1 if skip_shN else 0, float(grad_scale), _stream())
 
     def state(self) -> dict:
         """Copies of the forward state (synchronises): per-Gaussian records, bounds, tile lists."""

@@ -124,3 +124,45 @@ def test_default_strategy_trains_on_the_ewa_path(pkg, synth):
         s.step(it)
     assert losses[1] < losses[0] and all(np.isfinite(losses))
     assert model.size > n   # the statistics written by the backward drove a densification step
+
+
+@pytest.mark.parametrize("n,W,H,deg,active", [(12000, 200, 120, 3, 3), (5003, 97, 61, 3, 1)])
+def test_ewa_rank1_sh_adam_equals_materialised_gradient(pkg, synth, n, W, H, deg, active):
+    """backward(write_shN=False) + lfs_ewa_adam_step_rank1_sh == backward + lfs_adam_step_splats on the EWA path."""
+    tr = pkg.trainer
+    lrs = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+    K = (deg + 1) ** 2
+    cfg, P, vm, Kmat = make_scene(synth, n, W, H, deg, seed=14)
+    P["scaling_raw"] = (P["scaling_raw"] + np.float32(0.8)).astype(np.float32)
+    cam = tr.Camera(T(vm), T(Kmat), W, H)
+    bg = T(np.array([0.3, 0.1, 0.6], np.float32))
+    g_img = T(np.random.default_rng(3).normal(size=(3, H, W)).astype(np.float32))
+    res = []
+    for rank1 in (False, True):
+        model = tr.SplatData(n, K, DEV).load(P)
+        m, v = model.like(), model.like()
+        gen = torch.Generator(device=DEV).manual_seed(77)
+        m.flat.copy_(torch.randn(m.flat.shape, generator=gen, device=DEV) * 1e-3)
+        v.flat.copy_(torch.rand(v.flat.shape, generator=gen, device=DEV) * 1e-4 + 1e-6)
+        rast = tr.FastRasterizer(model, W, H, active)
+        rast.forward(cam, bg)
+        grads = model.like()
+        if rank1:
+            grads.tensor("shN").fill_(7.0)
+            rast.backward(g_img, grads, bg, write_shN=False)
+            assert bool((grads.tensor("shN") == 7.0).all())
+            rast.adam_step_rank1_sh(m, v, grads, lrs, 3, grad_scale=0.5)
+        else:
+            rast.backward(g_img, grads, bg)
+            tr.adam_step_splats(model, m, v, grads, lrs, 3, grad_scale=0.5)
+        res.append((model, m, v))
+    worst = {}
+    for name in NAMES:
+        for k in (1, 2):
+            a, b = res[0][k].tensor(name).cpu().numpy(), res[1][k].tensor(name).cpu().numpy()
+            worst[(name, k)] = rel_l2(b, a)
+        p0 = T(P[name]).reshape(res[0][0].tensor(name).shape)
+        d_a, d_b = (res[0][0].tensor(name) - p0).cpu().numpy(), (res[1][0].tensor(name) - p0).cpu().numpy()
+        assert np.abs(d_a).max() > 0
+        assert rel_l2(d_b, d_a) < 1e-3, name
+    assert max(worst.values()) < 1e-5, worst
