@@ -18,8 +18,9 @@ def T(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
-@pytest.mark.parametrize("n,deg,world", [(6000, 3, 2), (4004, 2, 2), (6000, 3, 4), (5000, 3, 8)])
-def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world):
+@pytest.mark.parametrize("n,deg,world,active,pad", [(6000, 3, 2, 3, 0), (4004, 2, 2, 2, 0), (6000, 3, 4, 3, 0), (5000, 3, 8, 3, 0),
+                                                      (5001, 3, 2, 2, 59)])   # active degree below the stored one, padded capacity
+def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world, active, pad):
     tr, capi = pkg.trainer, pkg._capi
     W, H, K = 160, 120, (deg + 1) ** 2
     rest = (K - 1) * 3
@@ -31,7 +32,7 @@ def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world):
     vr = [T(rng.normal(size=(H, W, 3)).astype(np.float32)) for _ in range(world)]
 
     def fresh():
-        model = tr.SplatData(n, K, DEV).load(P)
+        model = tr.SplatData(n, K, DEV, n + pad).load(P)
         m, v = model.like(), model.like()
         gen = torch.Generator(device=DEV).manual_seed(5)
         m.flat.copy_(torch.randn(m.flat.shape, generator=gen, device=DEV) * 1e-3)
@@ -40,7 +41,7 @@ def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world):
 
     # reference: accumulate both cameras' materialised gradients, one Adam step with the mean
     ref, m_ref, v_ref = fresh()
-    rast = tr.Rasterizer(ref, W, H, deg)
+    rast = tr.Rasterizer(ref, W, H, active)
     grads = ref.like()
     for r in range(world):
         rast.forward(cams[r], bg)
@@ -52,20 +53,20 @@ def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world):
     facs = []
     for r in range(world):
         model = copies[r][0]
-        rr = tr.Rasterizer(model, W, H, deg)
+        rr = tr.Rasterizer(model, W, H, active)
         g = model.like()
         rr.forward(cams[r], bg)
         rr.backward(vr[r], g, bg, sh_factors=True)
         facs.append(g)
     _, m_own, v_own = copies[0]
-    total = n * rest
+    total = copies[0][0].capacity * rest          # the whole tensor, rows beyond n included (zero gradient there)
     cut = (total // 2) // 4 * 4 + 4          # a 4-aligned cut inside a row
     assert cut % rest != 0
     stream = capi.vp(torch.cuda.current_stream().cuda_stream)
     pf = (C.c_void_p * world)(*[facs[r].tensor("shN").data_ptr() for r in range(world)])
     ps = (C.c_void_p * world)(*[copies[r][0].tensor("shN").data_ptr() for r in range(world)])
     for lo, cnt in ((0, cut), (cut, total - cut)):
-        capi.call("lfs_dp_sh_rank1_adam_broadcast", world, pf, ps, n, K, deg, lo, cnt,
+        capi.call("lfs_dp_sh_rank1_adam_broadcast", world, pf, ps, n, K, active, lo, cnt,
                   capi.vp(m_own.tensor("shN").data_ptr() + 4 * lo), capi.vp(v_own.tensor("shN").data_ptr() + 4 * lo),
                   LRS[2], 0.9, 0.999, 1e-15, 2, 1.0 / world, 0, stream)
     torch.cuda.synchronize()
