@@ -606,7 +606,25 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
     for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
         const int g = chunk * 32 + lane;
         const bool in_range = g < N;
-        const bool visible = in_range && radii[g * 2] > 0 && radii[g * 2 + 1] > 0;
+        // Everything a visible Gaussian needs is requested together with its radii (one round trip to memory instead of
+        // two); for the others the values are dropped.
+        int2 rad = make_int2(0, 0);
+        float4 a_in[4], qr = make_float4(1.f, 0.f, 0.f, 0.f), r3 = make_float4(0.f, 0.f, 0.f, 0.f);
+        float m_in[3] = {0.f, 0.f, 0.f}, s_in[3] = {0.f, 0.f, 0.f}, o_in = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a_in[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in_range) {
+            rad = reinterpret_cast<const int2*>(radii)[g];
+            const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) a_in[k] = a4[k];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) { m_in[k] = means[g * 3 + k]; s_in[k] = scaling_raw[g * 3 + k]; }
+            o_in = opacity_raw[g];
+            qr = reinterpret_cast<const float4*>(rotation_raw)[g];
+            r3 = records[(size_t)g * 4 + 3];
+        }
+        const bool visible = in_range && rad.x > 0 && rad.y > 0;
         float gm[3] = {0.f, 0.f, 0.f}, g0[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, go = 0.f;
         float vc[3] = {0.f, 0.f, 0.f};
         float B[25];
@@ -614,16 +632,13 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
         for (int k = 0; k < 25; ++k) B[k] = 0.f;
         if (visible) {
             float acc[16];
-            const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { const float4 t = a4[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
-            const f3 mean{means[g * 3], means[g * 3 + 1], means[g * 3 + 2]};
-            const float opacity = (float)(1.0 / (1.0 + exp(-(double)opacity_raw[g])));
+            for (int k = 0; k < 4; ++k) { const float4 t = a_in[k]; acc[k * 4] = t.x; acc[k * 4 + 1] = t.y; acc[k * 4 + 2] = t.z; acc[k * 4 + 3] = t.w; }
+            const f3 mean{m_in[0], m_in[1], m_in[2]};
+            const float opacity = (float)(1.0 / (1.0 + exp(-(double)o_in)));
             // scale as blended: exp(raw) * modifier; d(scale)/d(raw) is the same product
-            f3 scale{(float)exp((double)scaling_raw[g * 3]), (float)exp((double)scaling_raw[g * 3 + 1]),
-                     (float)exp((double)scaling_raw[g * 3 + 2])};
+            f3 scale{(float)exp((double)s_in[0]), (float)exp((double)s_in[1]), (float)exp((double)s_in[2])};
             if (scaling_modifier != 1.0f) { scale.x *= scaling_modifier; scale.y *= scaling_modifier; scale.z *= scaling_modifier; }
-            const float4 qr = reinterpret_cast<const float4*>(rotation_raw)[g];
             const float n2 = ((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w;
             const float nrm = fmaxf(sqrtf(n2), 1e-12f);
             const float q[4] = {qr.x / nrm, qr.y / nrm, qr.z / nrm, qr.w / nrm};
@@ -638,7 +653,6 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
 #pragma unroll
             for (int k = 0; k < 3; ++k) gm[k] = o.v_mean[k];
             // colour clamp mask, then SH backward
-            const float4 r3 = records[(size_t)g * 4 + 3];
             vc[0] = r3.x <= 0.f ? 0.f : o.v_rgb[0];
             vc[1] = r3.y <= 0.f ? 0.f : o.v_rgb[1];
             vc[2] = r3.z <= 0.f ? 0.f : o.v_rgb[2];
@@ -652,7 +666,7 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
             if (in_range) {
                 float dx = 0.f, dy = 0.f, dz = 0.f;
                 if (visible) {
-                    dx = means[g * 3] - cam.campos[0]; dy = means[g * 3 + 1] - cam.campos[1]; dz = means[g * 3 + 2] - cam.campos[2];
+                    dx = m_in[0] - cam.campos[0]; dy = m_in[1] - cam.campos[1]; dz = m_in[2] - cam.campos[2];
                     const float inorm = rsqrtf(dx * dx + dy * dy + dz * dz);
                     dx *= inorm; dy *= inorm; dz *= inorm;
                 }
