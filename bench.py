@@ -220,7 +220,7 @@ def run_ours(args):
     def pose_of(step):
         return poses[synth.pose_index(step * world + rank, cfg["n_poses"])]
 
-    n_e2e = min(args.steps, 20)
+    n_e2e = min(args.steps, 50)
     targets_dev, targets_host, vms_dev, vms_host = [], [], [], []
     for s in range(max(total_steps, n_e2e)):
         vm = torch.from_numpy(pose_of(s)).to(dev)
