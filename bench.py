@@ -101,6 +101,7 @@ def cpu_step_sample(workload: str, n_rows: int = 6, step: int = 0):
     over the image height, their time scaled to the whole image. Returns (seconds for a full step,
     description, threads)."""
     from oracle import oracle as orc
+    orc.use_all_cores()
     synth = importlib.import_module("lichtfeld-studio_b200").synth
     cfg = synth.CONFIGS[workload]
     W, H, deg, n = cfg["W"], cfg["H"], cfg["sh_degree"], cfg["n"]

@@ -78,6 +78,17 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_cores() -> int:
+    """Launchers such as torch.distributed.run export OMP_NUM_THREADS=1; the timed CPU baseline wants every host core.
+    Sets the OpenMP thread count of the loaded library to the number of cores this process may run on."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    fn = lib().omp_set_num_threads          # resolved through the library's OpenMP runtime dependency
+    fn.argtypes, fn.restype = [C.c_int], None
+    fn(int(n))
+    return num_threads()
+
+
 # ------------------------------------------------------------------ operators
 def projection_ut_3dgs_fused(means, quats, scales, opacities, viewmats, Ks, W, H, eps2d=0.3,
                              near=0.01, far=1e4, radius_clip=0.0, calc_compensations=False,
