@@ -281,9 +281,13 @@ def run_ours(args):
                 main.wait_event(ev_color)      # the colour groups of the previous step are up to date
             out = rast.forward_shade(bg)
         loss, v_render = lossfn(out.image, target)
+        if rank1_sh and args.one_call_optimizer:
+            # one camera per step on one GPU: backward and optimizer in one call, no gradient tensor at all
+            rast.backward_adam(v_render, m, v, LRS, s + 1, bg)
+            return loss
         if rank1_sh:
-            # one camera per step on one GPU: the shN gradient (three quarters of the gradient bytes) is never written;
-            # the optimizer rebuilds its rows from the sh0 gradient and the view direction
+            # the same with the reference's two calls: the shN gradient (three quarters of the gradient bytes) is never
+            # written; the optimizer rebuilds its rows from the sh0 gradient and the view direction
             rast.backward(v_render, grads, bg, write_shN=False)
             rast.adam_step_rank1_sh(m, v, grads, LRS, s + 1)
             return loss
@@ -456,7 +460,8 @@ def run_ours(args):
                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": world,
-                          "optimizer_overlap": bool(overlap), "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else ("rank-1 factors over NVLink" if dp_rank1 else "materialised"),
+                          "optimizer_overlap": bool(overlap), "optimizer": ("inside lfs_render_backward_adam" if (rank1_sh and args.one_call_optimizer) else "separate call"),
+                          "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else ("rank-1 factors over NVLink" if dp_rank1 else "materialised"),
                           "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
                "clocks": clocks, "e2e": {"value": world * 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
@@ -678,6 +683,9 @@ def main():
                          "tile lists (measured: no gain on B200, 2.975 ms against 2.964 ms; both sides are memory-latency sensitive)")
     ap.add_argument("--materialize-sh-grad", action="store_true",
                     help="write the shN gradient rows (lfs_adam_step_splats / element-wise exchange) instead of using their rank-1 form")
+    ap.add_argument("--one-call-optimizer", action="store_true",
+                    help="single GPU: lfs_render_backward_adam (no gradient tensor at all; same speed) instead of "
+                         "lfs_render_backward + lfs_adam_step_splats_rank1_sh")
     ap.add_argument("--no-dp-split", action="store_true",
                     help="N > 1, fused_p2p: exchange all groups in one kernel after the backward. Default: geometry groups first, "
                          "colour groups on a side stream (one CTA per SM) under the next step's projection and tile lists "

@@ -319,6 +319,22 @@ int lfs_adam_step_splats(int N, int sh_coeffs, const lfs_splats* params, const l
                          double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
                          int64_t first_row, int64_t n_rows, float grad_scale, void* stream);
 
+/* lfs_render_backward and FusedAdam::step (src/training/optimizers/fused_adam.cpp:22-95) in one call, for steps of ONE
+ * camera; no gradient tensor exists. The per-Gaussian gradient stage applies Adam to the five small groups (means, sh0,
+ * scales, rotations, opacities) in place as it produces their gradients and leaves the two rank-1 factors of the shN
+ * gradient (clamped colour gradient, unit view direction) in the workspace; a second kernel rebuilds the shN gradient rows
+ * from them and streams the shN coefficients and moments through once. Arguments as in lfs_render_backward and
+ * lfs_adam_step_splats (lr[6] host values in group order, bias corrections from the double betas, skip_shN for
+ * `iteration <= 1000`, grad_scale multiplies the gradient). The result equals lfs_render_backward(accumulate = 0)
+ * followed by lfs_adam_step_splats over all rows up to the rounding of the backward's atomic sums; Gaussians that were
+ * not visible take a zero gradient (their moments decay). Not for batches of several cameras, data-parallel steps, or
+ * callers that add regularisers or inspect gradients between the two reference calls. */
+int lfs_render_backward_adam(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
+                             const float* alpha, const float* v_render, const float* v_alpha, const lfs_splats* exp_avg,
+                             const lfs_splats* exp_avg_sq, const float* lr /* host[6] */, double beta1, double beta2,
+                             double eps, int64_t step_count, int skip_shN, float grad_scale, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* FusedAdam::step (src/training/optimizers/fused_adam.cpp:22-95) after a ONE-camera lfs_render_backward whose
  * grads->shN was NULL: the higher-order SH gradient is never materialised. For one camera, row g of that gradient is the
  * outer product of the SH basis of Gaussian g's view direction with its clamped colour gradient, and grads->sh0 holds

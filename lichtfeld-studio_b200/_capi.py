@@ -96,6 +96,8 @@ _SIGNATURES = {
     "lfs_render_forward_lists": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, sz, vp],
     "lfs_render_forward_shade": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, sz, vp],
     "lfs_render_backward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, C.POINTER(Splats), i32, vp, sz, vp],
+    "lfs_render_backward_adam": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, C.POINTER(Splats), C.POINTER(Splats),
+                                 C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, f32, vp, sz, vp],
     "lfs_render_workspace_view": [C.POINTER(RenderConfig), vp, sz, C.POINTER(RenderView)],
     "lfs_photometric_loss": [i32, i32, f32, f32, vp, vp, vp, vp, vp, sz, vp],
     "lfs_adam_step_splats": [i32, i32, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),

@@ -832,6 +832,53 @@ int lfs_render_backward(const lfs_render_config* cfg, const lfs_splats* params, 
                                       *grads, accumulate & LFS_BACKWARD_ACCUMULATE, cfg_modifier(*cfg), sh_factors, st);
 }
 
+int lfs_render_backward_adam(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
+                             const float* alpha, const float* v_render, const float* v_alpha, const lfs_splats* exp_avg,
+                             const lfs_splats* exp_avg_sq, const float* lr, double beta1, double beta2, double eps,
+                             int64_t step_count, int skip_shN, float grad_scale, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+    int rc = check_cfg(cfg);
+    if (rc != LFS_OK) return rc;
+    LFS_REQUIRE(params && alpha && v_render && exp_avg && exp_avg_sq && lr && workspace, "null pointer");
+    LFS_REQUIRE(step_count >= 1, "step_count must be >= 1");
+    LFS_REQUIRE(aligned16(params->rotation_raw), "rotation_raw must be 16-byte aligned");
+    RenderWs w = carve_render(*cfg, workspace);
+    if (workspace_bytes < w.bytes) { set_error("lfs_render_backward_adam: workspace too small"); return LFS_ECAPACITY; }
+    const int K = cfg->sh_coeffs;
+    // the same host arithmetic as lfs_adam_step_splats
+    const double bc1 = 1.0 / (1.0 - std::pow(beta1, (double)step_count));
+    const double bc2 = 1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step_count));
+    float* P[5] = {params->means, params->sh0, params->scaling_raw, params->rotation_raw, params->opacity_raw};
+    float* M[5] = {exp_avg->means, exp_avg->sh0, exp_avg->scaling_raw, exp_avg->rotation_raw, exp_avg->opacity_raw};
+    float* V[5] = {exp_avg_sq->means, exp_avg_sq->sh0, exp_avg_sq->scaling_raw, exp_avg_sq->rotation_raw, exp_avg_sq->opacity_raw};
+    const int lr_index[5] = {0, 1, 3, 4, 5};
+    AdamSmall A{};
+    for (int k = 0; k < 5; ++k) {
+        if (cfg->N > 0) LFS_REQUIRE(P[k] && M[k] && V[k], "null tensor in a parameter group");
+        A.p[k] = P[k]; A.m[k] = M[k]; A.v[k] = V[k];
+        A.step_size[k] = (float)((double)lr[lr_index[k]]) * (float)bc1;
+    }
+    A.beta1 = (float)beta1; A.beta2 = (float)beta2; A.eps = (float)eps; A.bc2_sqrt_rcp = (float)bc2; A.grad_scale = grad_scale;
+    const bool with_shN = !skip_shN && K > 1 && cfg->N > 0;
+    if (with_shN) LFS_REQUIRE(params->shN && exp_avg->shN && exp_avg_sq->shN, "null tensor in a parameter group");
+    cudaStream_t st = S(stream);
+    const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
+    const int sel = sorted_sel((int)(bit_width_u32((uint32_t)tw * th) + 1));
+    RasterArgs ra{w.cam, w.records, w.bounds, w.tvals[sel], w.tile_offsets, w.counters + 1, 0, background, w.counters + 0,
+                  cfg->image_width, cfg->image_height, tw, th, cfg_model(*cfg), mode_channels(cfg->render_mode),
+                  mode_normalize(cfg->render_mode), cfg->tile_masks, w.tile_order, cfg_rolling(*cfg)};
+    rc = launch_raster_bwd(ra, alpha, w.last_ids, w.extra_sum, v_render, v_alpha, w.accum, nullptr, st);
+    if (rc != LFS_OK) return rc;
+    lfs_splats none{};
+    rc = launch_grad_epilogue_fused(cfg->N, K, cfg->sh_degree, w.cam, w.accum, w.records, w.radii, *params, none, 0,
+                                    cfg_modifier(*cfg), 1, st, &A);
+    if (rc != LFS_OK || !with_shN) return rc;
+    // the factors of the shN rows are now in the rows of the 16 sums (stride 16 floats)
+    return launch_adam_sh_rank1(cfg->N, K, cfg->sh_degree, nullptr, nullptr, nullptr, params->shN, exp_avg->shN, exp_avg_sq->shN,
+                                (float)((double)lr[2]) * (float)bc1, (float)beta1, (float)beta2, (float)eps, (float)bc2, grad_scale,
+                                st, w.accum, 16);
+}
+
 int lfs_adam_step_splats_rank1_sh(const lfs_render_config* cfg, const lfs_splats* params, const lfs_splats* exp_avg,
                                   const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr, double beta1,
                                   double beta2, double eps, int64_t step_count, int skip_shN, float grad_scale,

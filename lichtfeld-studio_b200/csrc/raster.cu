@@ -585,16 +585,43 @@ __global__ void __launch_bounds__(256) grad_epilogue_op_kernel(
     }
 }
 
+__device__ __forceinline__ void adam_small_update(float& p, float& m, float& v, float g, float step_size, const AdamSmall& A) {
+    const float m1 = A.beta1 * m + (1.0f - A.beta1) * g;
+    const float m2 = A.beta2 * v + (1.0f - A.beta2) * g * g;
+    const float denom = sqrtf(m2) * A.bc2_sqrt_rcp + A.eps;
+    p -= step_size * m1 / denom;
+    m = m1;
+    v = m2;
+}
+// One row of W floats of small group `gi` (index into AdamSmall): p_in are the parameter values already in registers.
+template <int W>
+__device__ __forceinline__ void adam_small_row(const AdamSmall& A, int gi, size_t row, const float* p_in, const float* grad) {
+    float* mm = A.m[gi] + row * W;
+    float* vv = A.v[gi] + row * W;
+    float* pp = A.p[gi] + row * W;
+    float p[W], m[W], v[W];
+#pragma unroll
+    for (int k = 0; k < W; ++k) { p[k] = p_in[k]; m[k] = mm[k]; v[k] = vv[k]; }
+#pragma unroll
+    for (int k = 0; k < W; ++k) adam_small_update(p[k], m[k], v[k], grad[k] * A.grad_scale, A.step_size[gi], A);
+#pragma unroll
+    for (int k = 0; k < W; ++k) { pp[k] = p[k]; mm[k] = m[k]; vv[k] = v[k]; }
+}
+
 // Fused-path epilogue: raw-parameter gradients (activation backward folded in) and the SH backward.
 // Each warp handles 32 consecutive Gaussians per iteration; their shN gradient rows (the bulk of the
 // output, (K-1)*3 floats each) are staged in shared memory and written as one contiguous run.
-__global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
-    int N, int K, int sh_degree, const CamDev* __restrict__ cams, const float* __restrict__ accum,
+// ADAM: the five small groups (means, sh0, scales, rotations, opacities) are not written as gradients but applied at
+// once, in place, with the moments in A (the parameter pointers below alias A.p, hence no __restrict__ on them); the
+// shN gradient leaves as its two rank-1 factors (sh_factors) for adam_sh_rank1_kernel.
+template <bool ADAM>
+__global__ void __launch_bounds__(256, 4) grad_epilogue_fused_kernel(
+    int N, int K, int sh_degree, const CamDev* __restrict__ cams, const float* accum /* ADAM: aliased by g_shN */,
     const float4* __restrict__ records, const int32_t* __restrict__ radii,
-    const float* __restrict__ means, const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw,
-    const float* __restrict__ opacity_raw,
-    float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN, float* __restrict__ g_scaling,
-    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate, float scaling_modifier, int sh_factors) {
+    const float* means, const float* sh0, const float* scaling_raw, const float* rotation_raw, const float* opacity_raw,
+    float* __restrict__ g_means, float* __restrict__ g_sh0, float* g_shN, float* __restrict__ g_scaling,
+    float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate, float scaling_modifier, int sh_factors,
+    AdamSmall A) {
     extern __shared__ float s_rows[];
     const CamDev& cam = cams[0];
     const int rest = (K - 1) * 3;
@@ -670,7 +697,8 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
                     const float inorm = rsqrtf(dx * dx + dy * dy + dz * dz);
                     dx *= inorm; dy *= inorm; dz *= inorm;
                 }
-                float2* f = reinterpret_cast<float2*>(g_shN) + (size_t)g * 3;
+                // ADAM: the factors go into the Gaussian's own (now consumed) row of 16 sums
+                float2* f = ADAM ? reinterpret_cast<float2*>(g_shN) + (size_t)g * 8 : reinterpret_cast<float2*>(g_shN) + (size_t)g * 3;
                 f[0] = make_float2(vc[0], vc[1]); f[1] = make_float2(vc[2], dx); f[2] = make_float2(dy, dz);
             }
         } else if (g_shN) {  // NULL: the caller forms these rows itself from the sh0 gradient (adam_sh_rank1_kernel)
@@ -691,7 +719,17 @@ __global__ void __launch_bounds__(256) grad_epilogue_fused_kernel(
             }
             __syncwarp();
         }
-        if (in_range && (visible || !accumulate)) {
+        if (ADAM) {
+            if (in_range) {
+                const float c_in[3] = {sh0[g * 3], sh0[g * 3 + 1], sh0[g * 3 + 2]};
+                const float q_in[4] = {qr.x, qr.y, qr.z, qr.w};
+                adam_small_row<3>(A, 0, (size_t)g, m_in, gm);
+                adam_small_row<3>(A, 1, (size_t)g, c_in, g0);
+                adam_small_row<3>(A, 2, (size_t)g, s_in, gs);
+                adam_small_row<4>(A, 3, (size_t)g, q_in, gq);
+                adam_small_row<1>(A, 4, (size_t)g, &o_in, &go);
+            }
+        } else if (in_range && (visible || !accumulate)) {
             if (accumulate) {
 #pragma unroll
                 for (int k = 0; k < 3; ++k) { g_means[g * 3 + k] += gm[k]; g_sh0[g * 3 + k] += g0[k]; g_scaling[g * 3 + k] += gs[k]; }
@@ -726,11 +764,12 @@ __device__ __forceinline__ void adam_rank1_update(float& p, float& m, float& v, 
 template <int KT>
 __global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, int sh_degree, const float* __restrict__ campos,
                                                                const float* __restrict__ means, const float* __restrict__ g_sh0,
-                                                               AdamRank1 A) {
+                                                               const float* __restrict__ factors, int factor_stride, AdamRank1 A) {
     extern __shared__ __align__(16) float s_rows[];
     constexpr int U = 3;
     const int K = KT ? KT : K_rt;
-    const float cx = campos[0], cy = campos[1], cz = campos[2];
+    float cx = 0.f, cy = 0.f, cz = 0.f;
+    if (!factors) { cx = campos[0]; cy = campos[1]; cz = campos[2]; }
     const int rest = (K - 1) * 3;
     const int nb = (sh_degree + 1) * (sh_degree + 1);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -739,16 +778,25 @@ __global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, 
     const int warps_total = gridDim.x * (blockDim.x >> 5);
     for (int chunk = blockIdx.x * (blockDim.x >> 5) + warp; chunk < n_chunks; chunk += warps_total) {
         const int g = chunk * 32 + lane;
-        float vc[3] = {0.f, 0.f, 0.f};
+        float vc[3] = {0.f, 0.f, 0.f}, dir[3] = {0.f, 0.f, 0.f};
         if (g < N) {
+            if (factors) {
+                // written by the gradient stage: (clamped colour gradient, unit view direction)
+                const float2* f = reinterpret_cast<const float2*>(factors + (size_t)g * factor_stride);
+                const float2 f0 = f[0], f1 = f[1], f2 = f[2];
+                vc[0] = f0.x; vc[1] = f0.y; vc[2] = f1.x; dir[0] = f1.y; dir[1] = f2.x; dir[2] = f2.y;
+            } else {
 #pragma unroll
-            for (int c = 0; c < 3; ++c) vc[c] = g_sh0[g * 3 + c] / 0.2820947917738781f;
+                for (int c = 0; c < 3; ++c) vc[c] = g_sh0[g * 3 + c] / 0.2820947917738781f;
+            }
         }
         float B[25];
 #pragma unroll
         for (int k = 0; k < 25; ++k) B[k] = 0.f;
-        if (vc[0] != 0.f || vc[1] != 0.f || vc[2] != 0.f)
-            sh_basis(sh_degree, means[g * 3] - cx, means[g * 3 + 1] - cy, means[g * 3 + 2] - cz, B);
+        if (vc[0] != 0.f || vc[1] != 0.f || vc[2] != 0.f) {
+            if (!factors) { dir[0] = means[g * 3] - cx; dir[1] = means[g * 3 + 1] - cy; dir[2] = means[g * 3 + 2] - cz; }
+            sh_basis(sh_degree, dir[0], dir[1], dir[2], B);
+        }
         if (KT) {
 #pragma unroll
             for (int k = 1; k < (KT ? KT : 1); ++k) {
@@ -983,23 +1031,29 @@ int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const 
 
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
-                               int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st) {
+                               int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st, const AdamSmall* adam) {
     if (N == 0) return LFS_OK;
-    LFS_TIMED("grad_epilogue", st);
+    LFS_TIMED(adam ? "grad_epilogue_adam" : "grad_epilogue", st);
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
     if (smem > 200 * 1024) { set_error("grad_epilogue_fused: too many SH coefficients"); return LFS_EINVAL; }
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(grad_epilogue_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    grad_epilogue_fused_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, cam, accum, records, radii, p.means,
-                                                                 p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
-                                                                 g.sh0, g.shN, g.scaling_raw, g.rotation_raw,
-                                                                 g.opacity_raw, accumulate, scaling_modifier, sh_factors);
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(grad_epilogue_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(grad_epilogue_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (adam)
+        grad_epilogue_fused_kernel<true><<<grid_for(N, 256), 256, smem, st>>>(
+            N, K, sh_degree, cam, accum, records, radii, p.means, p.sh0, p.scaling_raw, p.rotation_raw, p.opacity_raw, nullptr,
+            nullptr, const_cast<float*>(accum), nullptr, nullptr, nullptr, 0, scaling_modifier, 1, *adam);
+    else
+        grad_epilogue_fused_kernel<false><<<grid_for(N, 256), 256, smem, st>>>(
+            N, K, sh_degree, cam, accum, records, radii, p.means, p.sh0, p.scaling_raw, p.rotation_raw, p.opacity_raw, g.means,
+            g.sh0, g.shN, g.scaling_raw, g.rotation_raw, g.opacity_raw, accumulate, scaling_modifier, sh_factors, AdamSmall{});
     return check_launch("grad_epilogue_fused");
 }
 
 int launch_adam_sh_rank1(int N, int K, int sh_degree, const float* campos, const float* means, const float* g_sh0, float* p,
                          float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
-                         float grad_scale, cudaStream_t st) {
+                         float grad_scale, cudaStream_t st, const float* factors, int factor_stride) {
     if (N == 0 || K <= 1) return LFS_OK;
     LFS_TIMED("adam_sh_rank1", st);
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
@@ -1008,8 +1062,8 @@ int launch_adam_sh_rank1(int N, int K, int sh_degree, const float* campos, const
         cudaFuncSetAttribute(adam_sh_rank1_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     AdamRank1 A{p, m, v, step_size, beta1, beta2, eps, bc2_sqrt_rcp, grad_scale,
                 (int)(((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0)};
-    if (K == 16) adam_sh_rank1_kernel<16><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, campos, means, g_sh0, A);
-    else adam_sh_rank1_kernel<0><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, campos, means, g_sh0, A);
+    if (K == 16) adam_sh_rank1_kernel<16><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, campos, means, g_sh0, factors, factor_stride, A);
+    else adam_sh_rank1_kernel<0><<<grid_for(N, 256), 256, smem, st>>>(N, K, sh_degree, campos, means, g_sh0, factors, factor_stride, A);
     return check_launch("adam_sh_rank1");
 }
 

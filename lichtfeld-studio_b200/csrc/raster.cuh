@@ -33,15 +33,27 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
 int launch_grad_epilogue_op(int N, const CamDev* cam, const float* accum, const float* means, const float* quats,
                             const float* scales, int channels, const float* accum_extra, float* v_means, float* v_quats,
                             float* v_scales, float* v_colors, float* v_opacities, cudaStream_t st);
+// In-place Adam of the five small groups inside the gradient stage: index 0..4 = means, sh0, scaling_raw, rotation_raw,
+// opacity_raw. step_size = lr * bias_correction1_rcp.
+struct AdamSmall {
+    float* p[5]; float* m[5]; float* v[5];
+    float step_size[5];
+    float beta1, beta2, eps, bc2_sqrt_rcp, grad_scale;
+};
+// adam != nullptr: no gradient tensor is written (g is ignored); each Gaussian's row of 16 sums in `accum` receives the six
+// floats of its rank-1 shN factors and the small groups are updated in place (one camera per step only).
 int launch_grad_epilogue_fused(int N, int K, int sh_degree, const CamDev* cam, const float* accum,
                                const float4* records, const int32_t* radii, const lfs_splats& p, const lfs_splats& g,
-                               int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st);
+                               int accumulate, float scaling_modifier, int sh_factors, cudaStream_t st,
+                               const AdamSmall* adam = nullptr);
 // Adam on the shN tensor with the gradient rows rebuilt from the sh0 gradient of a one-camera backward
 // (g_shN[k][c] = Y_k(direction) * g_sh0[c] / Y_0); p, m, v are the shN parameter and moment tensors [N, K-1, 3].
 // campos: device [3], the camera position in world space that the backward used.
 int launch_adam_sh_rank1(int N, int K, int sh_degree, const float* campos, const float* means, const float* g_sh0, float* p,
                          float* m, float* v, float step_size, float beta1, float beta2, float eps, float bc2_sqrt_rcp,
-                         float grad_scale, cudaStream_t st);
+                         float grad_scale, cudaStream_t st, const float* factors = nullptr, int factor_stride = 0);
+// factors != nullptr: the (colour gradient, unit direction) rows written by the gradient stage, `factor_stride` floats
+// apart, replace campos / means / g_sh0.
 
 struct AdamRank1 {
     float* p; float* m; float* v;

@@ -223,6 +223,17 @@ class Rasterizer:
         call("lfs_render_backward", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.alpha), ptr(v_render), ptr(v_alpha),
              C.byref(g), flags, ptr(self.ws), self.ws.numel(), _stream())
 
+    def backward_adam(self, v_render: torch.Tensor, exp_avg: SplatData, exp_avg_sq: SplatData, lrs, step_count: int,
+                      background: torch.Tensor | None = None, v_alpha: torch.Tensor | None = None, beta1=0.9, beta2=0.999,
+                      eps=1e-15, skip_shN=False, grad_scale=1.0):
+        """backward() and FusedAdam::step in one call for steps of ONE camera: the gradients never go to memory (the small
+        groups are updated inside the per-Gaussian gradient stage, shN from its rank-1 factors)."""
+        p, m, v = self.model.struct(), exp_avg.struct(), exp_avg_sq.struct()
+        lr = (C.c_float * 6)(*[float(x) for x in lrs])
+        call("lfs_render_backward_adam", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.alpha), ptr(v_render),
+             ptr(v_alpha), C.byref(m), C.byref(v), lr, float(beta1), float(beta2), float(eps), int(step_count),
+             1 if skip_shN else 0, float(grad_scale), ptr(self.ws), self.ws.numel(), _stream())
+
     def adam_step_rank1_sh(self, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,
                            beta1=0.9, beta2=0.999, eps=1e-15, skip_shN=False, grad_scale=1.0):
         """FusedAdam::step after backward(write_shN=False) of ONE camera: the shN rows are updated from gradient rows

@@ -208,3 +208,52 @@ def test_rank1_sh_adam_equals_materialised_gradient(pkg, synth, n, W, H, deg, sk
     if K > 1 and not skip_shN:
         assert np.array_equal(models[1].tensor("shN").cpu().numpy()[hidden], models[0].tensor("shN").cpu().numpy()[hidden])
         assert np.array_equal(moments[1][0].tensor("shN").cpu().numpy()[hidden], moments[0][0].tensor("shN").cpu().numpy()[hidden])
+
+
+@pytest.mark.parametrize("n,W,H,deg,skip_shN", [(12000, 200, 120, 3, False), (5003, 97, 61, 2, False), (5003, 97, 61, 3, True),
+                                                 (4001, 80, 64, 0, False)])
+def test_backward_adam_equals_backward_then_adam(pkg, synth, n, W, H, deg, skip_shN):
+    """lfs_render_backward_adam == lfs_render_backward + lfs_adam_step_splats up to the rounding of the atomic sums."""
+    tr = pkg.trainer
+    K = (deg + 1) ** 2
+    cfg, P, vm, Kmat = make_scene(synth, n, W, H, deg, seed=23)
+    cam = tr.Camera(T(vm), T(Kmat), W, H)
+    bg = T(np.array([0.3, 0.1, 0.6], np.float32))
+    v_render = T(np.random.default_rng(6).normal(size=(H, W, 3)).astype(np.float32))
+    res = []
+    for fused in (False, True):
+        model = tr.SplatData(n, K, DEV).load(P)
+        m, v = model.like(), model.like()
+        gen = torch.Generator(device=DEV).manual_seed(78)
+        m.flat.copy_(torch.randn(m.flat.shape, generator=gen, device=DEV) * 1e-3)
+        v.flat.copy_(torch.rand(v.flat.shape, generator=gen, device=DEV) * 1e-4 + 1e-6)
+        rast = tr.Rasterizer(model, W, H, deg)
+        rast.forward(cam, bg)
+        if fused:
+            rast.backward_adam(v_render, m, v, LRS, 3, bg, skip_shN=skip_shN, grad_scale=0.5)
+        else:
+            grads = model.like()
+            rast.backward(v_render, grads, bg)
+            tr.adam_step_splats(model, m, v, grads, LRS, 3, skip_shN=skip_shN, grad_scale=0.5)
+        res.append((model, m, v, (rast.state()["radii"] > 0).all(-1)))
+    vis = res[0][3]
+    assert 0 < int(vis.sum()) < n
+    worst = {}
+    for name in NAMES:
+        pa, pb = res[0][0].tensor(name), res[1][0].tensor(name)
+        if pa.numel() == 0:
+            continue
+        p0 = torch.from_numpy(np.ascontiguousarray(P[name], dtype=np.float32)).reshape(pa.shape).to(DEV)
+        d_a, d_b = (pa - p0).cpu().numpy(), (pb - p0).cpu().numpy()
+        if name == "shN" and skip_shN:
+            assert not d_a.any() and not d_b.any()
+        else:
+            assert np.abs(d_a).max() > 0
+            assert rel_l2(d_b, d_a) < 1e-3, name      # float32 subtraction of ~1e-5 steps; the moments are the sharp check
+        for k in (1, 2):
+            worst[(name, k)] = rel_l2(res[1][k].tensor(name).cpu().numpy(), res[0][k].tensor(name).cpu().numpy())
+    assert max(worst.values()) < 1e-5, worst
+    hidden = (~vis).cpu().numpy()
+    for name in ("means", "opacity_raw"):
+        assert np.array_equal(res[1][1].tensor(name).cpu().numpy()[hidden], res[0][1].tensor(name).cpu().numpy()[hidden])
+        assert np.array_equal(res[1][0].tensor(name).cpu().numpy()[hidden], res[0][0].tensor(name).cpu().numpy()[hidden])
