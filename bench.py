@@ -421,7 +421,7 @@ def run_ours(args):
         ach = 370.0 * q_b / (t_bwd * 1e-3) / 1e12
         # DRAM bytes of one raster_bwd launch from the committed ncu capture (profiles/raster_bwd_train_1m.md);
         # it scales with the tile-instance count, so other workloads report null
-        traffic = 179.1e6 if workload == "train_1m" else None
+        traffic = 180.7e6 if workload == "train_1m" else None
         roofline = {"kernel": "raster_bwd_kernel", "bound": "fp32", "achieved": ach, "peak": fp32_peak, "unit": "TFLOP/s",
                     "frac": ach / fp32_peak, "traffic": traffic,
                     "note": f"370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms; peak = 148 SM x 128 lanes x 2 x "
