@@ -115,15 +115,17 @@ __device__ __forceinline__ void issue_stage(Stage<BATCH>& st, uint32_t* sid, con
 // in extra_sum for the backward.
 // RS: rolling shutter. Every pixel has its own pose, hence its own ray origin; the record's gro = M (o_start - mu) is
 // corrected per pair by M (o_pixel - o_start).
+// The plain pinhole RGB instantiation fits 40 registers (12 bytes of spills outside the loop) and, with 192-record batches
+// (30 KB for the two staging buffers), six CTAs per SM; the other instantiations keep their 48 - 64 registers.
 template <int MODEL, bool EXTRA, bool RS>
-__global__ void __launch_bounds__(kBlock) raster_fwd_kernel(
+__global__ void __launch_bounds__(kBlock, (MODEL == LFS_PINHOLE && !RS && !EXTRA) ? 6 : 4) raster_fwd_kernel(
     const CamDev* __restrict__ cams, const float4* __restrict__ records, const uint4* __restrict__ bounds,
     const uint32_t* __restrict__ flatten_ids,
     const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ n_isects_dev, int64_t n_isects_host,
     const int32_t* __restrict__ overflow, const float* __restrict__ background, const uint8_t* __restrict__ masks,
     const int32_t* __restrict__ tile_order, int channels, int normalize, int W, int H, int tw, int n_tiles,
     float* __restrict__ render, float* __restrict__ alphas, int32_t* __restrict__ last_ids, float* __restrict__ extra_sum) {
-    constexpr int BATCH = 256;
+    constexpr int BATCH = 192;
     __shared__ Stage<BATCH> stage[2];
 
     if (overflow && *overflow) return;
