@@ -28,7 +28,7 @@ __device__ __forceinline__ void ewa_sh_basis(float x, float y, float z, int nb, 
     B[15] = 0.59004358992664352f * x * (-xx + 3.0f * yy);
 }
 
-__global__ void __launch_bounds__(256) ewa_preprocess_kernel(
+__global__ void __launch_bounds__(256, 4) ewa_preprocess_kernel(
     int N, const float* __restrict__ means, const float* __restrict__ sh0, const float* __restrict__ shN,
     const float* __restrict__ scaling_raw, const float* __restrict__ rotation_raw, const float* __restrict__ opacity_raw,
     EwaCamera cam, int32_t* __restrict__ n_touched, ushort4* __restrict__ bounds, float4* __restrict__ records,

@@ -292,7 +292,8 @@ __global__ void __launch_bounds__(kBlock, 4) ewa_blend_bwd_kernel(
 // Each warp handles 32 consecutive Gaussians per iteration: their shN rows ((K-1)*3 floats each, contiguous in
 // memory) are read as one coalesced run into shared memory, every lane then works on its own row in place
 // (coefficient in, gradient out), and the 32 gradient rows leave as one coalesced run.
-__global__ void __launch_bounds__(256) ewa_epilogue_kernel(
+// capped at 64 registers (the compiler takes 114 unasked): this stage is latency bound and wants the fourth resident CTA
+__global__ void __launch_bounds__(256, 4) ewa_epilogue_kernel(
     int N, int K, const float* __restrict__ means, const float* __restrict__ shN, const float* __restrict__ scaling_raw,
     const float* __restrict__ rotation_raw, EwaCamera cam, const int32_t* __restrict__ n_touched, const float4* __restrict__ records,
     const float* __restrict__ accum, float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN,
