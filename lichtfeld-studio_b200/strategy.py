@@ -122,6 +122,9 @@ class MCMC(IStrategy):
         self._scheduler = None
         self.grads = splat_data.like()
         self.active_sh_degree = 0
+        # False once a refinement has replaced the parameter rows of this iteration: the reference's new leaf tensors
+        # have no .grad, so FusedAdam::step skips them before it counts the step (fused_adam.cpp:46-48)
+        self._grads_valid = True
 
     # ------------------------------------------------------------------ IStrategy
     def initialize(self, optim_params: OptimizationParameters):
@@ -161,8 +164,13 @@ class MCMC(IStrategy):
         self.inject_noise()
 
     def step(self, iter: int, grad_scale: float = 1.0, rasterizer=None):
+        """mcmc.cpp:395-402. On an iteration whose post_backward appended or removed rows the optimizer does nothing and
+        does not count the step (the gradients belong to the old rows); the scheduler still runs. The next backward
+        writes every gradient row again."""
         if iter < self._params.iterations:
-            self._optimizer.step(iter, self.grads, grad_scale, rasterizer=rasterizer)
+            if self._grads_valid:
+                self._optimizer.step(iter, self.grads, grad_scale, rasterizer=rasterizer)
+            self._grads_valid = True
             self._optimizer.zero_grad(True, iter)
             self._scheduler.step()
 
@@ -182,6 +190,7 @@ class MCMC(IStrategy):
             for n, t in kept.items():
                 sd.tensor(n).copy_(t)
         self.grads.size = new_n
+        self._grads_valid = False
 
     # ------------------------------------------------------------------ pieces
     @staticmethod
@@ -192,7 +201,8 @@ class MCMC(IStrategy):
             return torch.multinomial(weights, n, replacement)
         w = (weights / weights.sum()).cpu()
         cdf = w.cumsum(0).numpy()
-        u = np.random.default_rng().random(n).astype(np.float32)
+        # drawn from torch's generator so that ranks seeded alike stay replicated
+        u = torch.rand(n, dtype=torch.float32, device=weights.device).cpu().numpy()
         return torch.from_numpy(np.minimum(np.searchsorted(cdf, u, side="left"), weights.numel() - 1)).to(weights.device)
 
     def _relocate_with(self, sampled: torch.Tensor, dst, n: int):
@@ -239,6 +249,7 @@ class MCMC(IStrategy):
         self._relocate_with(sampled, None, n_new)
         for s in (sd, opt.exp_avg, opt.exp_avg_sq, self.grads):
             s.size = current_n + n_new
+        self._grads_valid = False   # the reference concatenates into new leaves without .grad (mcmc.cpp:254-259)
         return n_new
 
     def inject_noise(self, noise: torch.Tensor | None = None):
@@ -279,6 +290,7 @@ class DefaultStrategy(IStrategy):
         self.grads = splat_data.like()
         self.active_sh_degree = 0
         self.densification_info = None
+        self._grads_valid = True   # see MCMC: row surgery invalidates this iteration's gradients
 
     @dataclass
     class Parameters(OptimizationParameters):
@@ -327,8 +339,13 @@ class DefaultStrategy(IStrategy):
             self.reset_opacity()
 
     def step(self, iter: int, grad_scale: float = 1.0):
+        """default_strategy.cpp step(): duplicate / split / remove go through update_param_with_optimizer
+        (strategy_utils.cpp:57), whose new leaf tensors have no .grad, so on those iterations FusedAdam::step skips every
+        group before counting the step; the scheduler still runs."""
         if iter < self._params.iterations:
-            self._optimizer.step(iter, self.grads, grad_scale)
+            if self._grads_valid:
+                self._optimizer.step(iter, self.grads, grad_scale)
+            self._grads_valid = True
             self._optimizer.zero_grad(True, iter)
             self._scheduler.step()
 
@@ -361,6 +378,7 @@ class DefaultStrategy(IStrategy):
             rows.append(d)
         _rewrite_rows(self._buffers(), rows, n + k)
         self._sync_sizes()
+        self._grads_valid = False
 
     def split(self, is_split: torch.Tensor, noise: torch.Tensor | None = None):
         """default_strategy.cpp:89-159: each selected Gaussian is replaced by two samples of itself with scale / 1.6;
@@ -399,6 +417,7 @@ class DefaultStrategy(IStrategy):
             rows.append(d)
         _rewrite_rows(self._buffers(), rows, int(rest.numel()) + 2 * k)
         self._sync_sizes()
+        self._grads_valid = False
 
     def grow_gs(self, iter: int):
         """default_strategy.cpp:161-189."""
@@ -426,6 +445,7 @@ class DefaultStrategy(IStrategy):
                 for sd in self._buffers()]
         _rewrite_rows(self._buffers(), rows, int(keep.numel()))
         self._sync_sizes()
+        self._grads_valid = False
 
     def prune_gs(self, iter: int):
         """default_strategy.cpp:221-241."""

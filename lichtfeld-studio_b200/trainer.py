@@ -249,12 +249,11 @@ class Rasterizer:
         """Copies of the forward state in the workspace (per-Gaussian projection outputs and tile lists);
         synchronises. For inspection, tests and strategies that need radii / means2d."""
         view = capi.RenderView()
-        cfg = RenderConfig.from_buffer_copy(self.cfg)
-        cfg.N = self.model.capacity
+        cfg = RenderConfig.from_buffer_copy(self.cfg)   # the layout of the last forward: its N, not the capacity
         call("lfs_render_workspace_view", C.byref(cfg), ptr(self.ws), self.ws.numel(), C.byref(view))
         torch.cuda.synchronize()
         n_isects = int(self.status[1].item())
-        n, tiles = self.model.size, ((self.W + 15) // 16) * ((self.H + 15) // 16)
+        n, tiles = int(self.cfg.N), ((self.W + 15) // 16) * ((self.H + 15) // 16)
         base = self.ws.data_ptr()
 
         def grab(p, count, dtype):
@@ -346,11 +345,10 @@ class FastRasterizer:
     def state(self) -> dict:
         """Copies of the forward state (synchronises): per-Gaussian records, bounds, tile lists."""
         view = capi.EwaView()
-        cfg = capi.EwaConfig.from_buffer_copy(self.cfg)
-        cfg.N = self.model.capacity
+        cfg = capi.EwaConfig.from_buffer_copy(self.cfg)   # the layout of the last forward: its N, not the capacity
         call("lfs_ewa_workspace_view", C.byref(cfg), ptr(self.ws), self.ws.numel(), C.byref(view))
         torch.cuda.synchronize()
-        n, tiles = self.model.size, ((self.W + 15) // 16) * ((self.H + 15) // 16)
+        n, tiles = int(self.cfg.N), ((self.W + 15) // 16) * ((self.H + 15) // 16)
         n_inst = int(self.status[1].item())
         base = self.ws.data_ptr()
 

@@ -1,5 +1,6 @@
-"""CPU-only checks: the oracle against analytic cases and finite differences (its only pins: the reference
-ships no golden vectors for this path), the seeded generator, the host-side logic and the C ABI surface."""
+"""CPU-only checks: the oracle against analytic cases, finite differences and the committed outputs of the reference's
+own CUDA build (tests/golden/reference_step.npz; the reference itself ships no golden vectors for this path), the seeded
+generator, the host-side logic and the C ABI surface."""
 import ctypes
 import re
 from pathlib import Path
@@ -381,6 +382,65 @@ def test_oracle_reproduces_golden_step(orc):
     p, m, v = g["in_adam_p"].copy(), g["in_adam_m"].copy(), g["in_adam_v"].copy()
     orc.adam_step(p, m, v, g["in_adam_g"], 1e-3, 0.9, 0.999, 1e-15, 5)
     assert np.allclose(p, g["adam_p"], rtol=1e-6) and np.array_equal(m, g["adam_m"]) and np.array_equal(v, g["adam_v"])
+
+
+def test_oracle_matches_reference_cuda_golden(orc):
+    """PINS THE ORACLE TO THE REFERENCE: tests/golden/reference_step.npz holds what the reference's own, unmodified CUDA
+    kernels (oracle/_ref, built by oracle/ref_build.py, run on a B200 by tests/golden/make_reference_golden.py) produce
+    for the inputs of tiny_step.npz. Integer work on identical inputs must agree bit for bit; from raw parameters the
+    reference's --use_fast_math arithmetic may move a radius by one for a handful of Gaussians; images 1e-4 (a few
+    pixels may flip at the 1/255 alpha cut), gradients 1e-3 relative L2, loss 1e-6."""
+    import os
+    g, r = _golden(), np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_step.npz"))
+    names = ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")
+    P = {k: g[f"in_{k}"] for k in names}
+    W, H, deg = (int(x) for x in g["in_size"])
+    vm, K, bg = g["in_viewmat"], g["in_K"], g["in_bg"]
+    n = P["means"].shape[0]
+    # projection from the activated parameters
+    q, _ = orc.act_quat(P["rotation_raw"])
+    pr = orc.projection_ut_3dgs_fused(P["means"], q, orc.act_scale(P["scaling_raw"]), orc.act_opacity(P["opacity_raw"]), vm[None], K[None],
+                                      W, H, calc_compensations=True)
+    vis_ref, vis = r["visible"], (pr[0][0] > 0).all(-1)
+    assert vis_ref.sum() > 300
+    assert (vis != vis_ref).sum() <= 1 and (pr[0][0] != r["radii"]).any(-1).sum() <= 2
+    both = vis & vis_ref
+    assert np.abs(pr[1][0][both] - r["means2d"][both]).max() < 0.02
+    assert np.array_equal(pr[2][0][both].view(np.uint32), r["depths"][both].view(np.uint32))
+    assert rel_l2(pr[3][0][both], r["conics"][both]) < 1e-3 and np.abs(pr[4][0][both] - r["compensations"][both]).max() < 1e-3
+    # tile lists from the REFERENCE's projection outputs: bit-exact
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    tpg, ids, flat = orc.intersect_tile(r["means2d"][None], r["radii"][None], r["depths"][None], 1, 16, tw, th, True)
+    assert np.array_equal(tpg[0], r["tiles_per_gauss"]) and np.array_equal(ids, r["isect_ids"]) and np.array_equal(flat, r["flatten_ids"])
+    assert np.array_equal(orc.intersect_offset(ids, 1, tw, th)[0], r["tile_offsets"])
+    # the training step
+    fwd = orc.render_fwd(P, vm, K, W, H, deg, background=bg)
+    d = np.abs(np.clip(fwd["render"].transpose(2, 0, 1), 0, 1) - r["image"]).max(0)
+    assert (d > 1e-4).sum() <= 4 and np.quantile(d, 0.998) < 1e-4, d.max()
+    assert (np.abs(fwd["alpha"][..., 0] - r["alpha"][0]) > 1e-4).sum() <= 4
+    loss, gr, l1, ssim = orc.photometric_loss(fwd["render"], g["in_target"], 0.2)
+    assert abs(loss - float(r["loss"])) < 1e-6
+    bwd = orc.render_bwd(P, fwd, vm, K, W, H, deg, gr, background=bg)
+    for k in names:
+        assert rel_l2(bwd[k], r[f"grad_{k}"]) < 1e-3, k
+    # SSIM map of the reference's own image
+    m, dm1, _, _ = orc.fusedssim(np.clip(r["image"], 0, 1), g["in_target"], 1e-4, 9e-4)
+    assert np.abs(m - r["ssim_map"]).max() < 3e-5 and rel_l2(dm1, r["ssim_dm_dmu1"]) < 1e-5
+    # the default (EWA) path
+    K_ = K
+    ef = orc.ewa_forward(P, vm, orc.campos(vm), W, H, K_[0, 0], K_[1, 1], K_[0, 2], K_[1, 2], (deg + 1) ** 2, background=bg)
+    d = np.abs(ef["image"] - r["ewa_image"]).max(0)
+    assert (d > 1e-4).sum() <= 4 and np.quantile(d, 0.998) < 1e-4, d.max()
+    # relocation (the reference's pow is fast-math), Adam, noise, rotation matrices
+    no, ns = orc.relocation(g["in_reloc_opacity"], g["in_reloc_scale"], g["in_reloc_ratios"], orc.binoms_table(51), 51)
+    assert np.allclose(no, r["reloc_opacity"], rtol=1e-3) and np.allclose(ns, r["reloc_scale"], rtol=1e-3)
+    p, mo, v = g["in_adam_p"].copy(), g["in_adam_m"].copy(), g["in_adam_v"].copy()
+    orc.adam_step(p, mo, v, g["in_adam_g"], 1e-3, 0.9, 0.999, 1e-15, 5)
+    assert np.allclose(p, r["adam_p"], rtol=1e-5, atol=1e-7) and np.allclose(mo, r["adam_m"], rtol=1e-6) and np.allclose(v, r["adam_v"], rtol=1e-6)
+    moved = P["means"].copy()
+    orc.add_noise(P["opacity_raw"], P["scaling_raw"], P["rotation_raw"], r["in_noise"], moved, 80.0)
+    assert rel_l2(moved - P["means"], r["noise_means"] - P["means"]) < 1e-4
+    assert np.abs(orc.quats_to_rotmats(P["rotation_raw"]) - r["rotmats"]).max() < 1e-6
 
 
 def _ewa_scene(synth, n, W, H, deg, seed, fx):

@@ -121,3 +121,50 @@ def test_strategy_drives_training_steps(pkg, synth):
         s.step(it)
     assert model.size > n and s._optimizer.exp_avg.size == model.size
     assert vals[1] < vals[0] and all(np.isfinite(vals))   # the first two steps run before any refinement
+
+
+def test_refinement_iteration_skips_adam(pkg, synth):
+    """An iteration whose post_backward rewrites the rows runs no Adam and does not count the step, as in the reference:
+    update_param_with_optimizer installs new leaf tensors without .grad, so FusedAdam::step `continue`s before
+    step_count++ (src/training/optimizers/fused_adam.cpp:46-48). Checked against a numpy oracle that applies the row
+    surgery to parameters and moments and skips the optimizer."""
+    n = 2000
+    s, P = make(pkg, synth, n, grow_scale3d=0.02)
+    sd = s.get_model()
+    names = ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")
+    # one ordinary step first, so that the moments are non-trivial
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    s.grads.size = sd.size
+    s.grads.flat.normal_(generator=gen)
+    s.grads.flat.mul_(1e-3)
+    s.step(501)
+    assert s._optimizer.step_count == 1
+    before = {k: {nm: b.tensor(nm).clone() for nm in names} for k, b in (("p", sd), ("m", s._optimizer.exp_avg), ("v", s._optimizer.exp_avg_sq))}
+    lr0 = s._optimizer.lr[0]
+    # refinement iteration: duplicate every seventh Gaussian (all count as small by a generous threshold)
+    s._params.grow_scale3d = 1e9
+    info = torch.zeros((2, n), device=DEV)
+    info[0] = 1.0
+    hot = torch.arange(n, device=DEV) % 7 == 0
+    info[1, hot] = 1.0
+    s.densification_info = info
+    s.grads.flat.normal_(generator=gen)          # this iteration's (now stale) gradients
+    s.grow_gs(600)
+    k = int(hot.sum())
+    assert sd.size == n + k
+    s.step(600)
+    assert s._optimizer.step_count == 1                       # not counted
+    assert s._optimizer.lr[0] == lr0 * s._scheduler.gamma     # the scheduler still ran
+    idx = hot.nonzero().squeeze(-1)
+    for nm in names:
+        exp_p = torch.cat([before["p"][nm], before["p"][nm].index_select(0, idx)], 0)
+        assert torch.equal(sd.tensor(nm), exp_p), nm
+        for key, buf in (("m", s._optimizer.exp_avg), ("v", s._optimizer.exp_avg_sq)):
+            exp_m = torch.cat([before[key][nm], torch.zeros_like(before[key][nm].index_select(0, idx))], 0)
+            assert torch.equal(buf.tensor(nm), exp_m), (nm, key)
+    # the following iteration steps again
+    s.grads.size = sd.size
+    s.grads.flat.normal_(generator=gen)
+    s.step(601)
+    assert s._optimizer.step_count == 2
+    assert not torch.equal(sd.tensor("means")[:n], before["p"]["means"])

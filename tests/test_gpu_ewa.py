@@ -166,3 +166,23 @@ def test_ewa_rank1_sh_adam_equals_materialised_gradient(pkg, synth, n, W, H, deg
         assert np.abs(d_a).max() > 0
         assert rel_l2(d_b, d_a) < 1e-3, name
     assert max(worst.values()) < 1e-5, worst
+
+
+def test_ewa_state_with_reserved_capacity(pkg, orc, synth):
+    """FastRasterizer.state() uses the layout of the last forward when the model reserves more rows than it holds."""
+    tr = pkg.trainer
+    n, W, H, deg = 5001, 96, 80, 1
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=4)
+    P["scaling_raw"] = (P["scaling_raw"] + np.float32(1.0)).astype(np.float32)
+    fwd = orc.ewa_forward(P, vm, orc.campos(vm), W, H, K[0, 0], K[1, 1], K[0, 2], K[1, 2], 4, background=None)
+    model = tr.SplatData(n, 4, DEV, capacity=n + 1003).load(P)
+    rast = tr.FastRasterizer(model, W, H, deg)
+    rast.forward(tr.Camera(T(vm), T(K), W, H), None)
+    st = rast.state()
+    vis = fwd["n_touched"] > 0
+    assert np.array_equal(st["n_touched"].cpu().numpy(), fwd["n_touched"])
+    assert np.array_equal(st["bounds"].cpu().numpy()[vis].astype(np.int32), fwd["bounds"][vis])
+    assert np.array_equal(st["mean2d"].cpu().numpy()[vis].view(np.uint32), fwd["mean2d"][vis].view(np.uint32))
+    assert np.array_equal(st["instance_ids"].cpu().numpy(), fwd["instance_ids"])
+    assert np.array_equal(st["tile_offsets"].cpu().numpy(), fwd["tile_offsets"])
+    assert (st["n_contrib"].cpu().numpy() != fwd["n_contrib"]).sum() <= 2

@@ -257,3 +257,26 @@ def test_backward_adam_equals_backward_then_adam(pkg, synth, n, W, H, deg, skip_
     for name in ("means", "opacity_raw"):
         assert np.array_equal(res[1][1].tensor(name).cpu().numpy()[hidden], res[0][1].tensor(name).cpu().numpy()[hidden])
         assert np.array_equal(res[1][0].tensor(name).cpu().numpy()[hidden], res[0][0].tensor(name).cpu().numpy()[hidden])
+
+
+def test_state_with_reserved_capacity(pkg, orc, synth):
+    """state() reads the workspace with the layout of the last forward (N = live rows), also when the model reserves
+    more rows than it holds and the row count is not a multiple of four."""
+    tr = pkg.trainer
+    n, W, H, deg = 5001, 96, 80, 1
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=4)
+    bg = np.zeros(3, np.float32)
+    fwd = orc.render_fwd(P, vm, K, W, H, deg, background=bg)
+    model = tr.SplatData(n, (deg + 1) ** 2, DEV, capacity=n + 1003).load(P)
+    assert model.capacity != model.size
+    rast = tr.Rasterizer(model, W, H, deg)
+    rast.forward(tr.Camera(T(vm), T(K), W, H), T(bg))
+    st = rast.state()
+    vis = fwd["masks"]
+    assert np.array_equal(st["radii"].cpu().numpy(), fwd["radii"])
+    assert np.array_equal(st["means2d"].cpu().numpy()[vis].view(np.uint32), fwd["means2d"][vis].view(np.uint32))
+    assert np.array_equal(st["depths"].cpu().numpy()[vis].view(np.uint32), fwd["depths"][vis].view(np.uint32))
+    assert np.array_equal(st["tiles_per_gauss"].cpu().numpy(), fwd["tiles_per_gauss"])
+    assert np.array_equal(st["flatten_ids"].cpu().numpy(), fwd["flatten_ids"])
+    assert np.array_equal(st["tile_offsets"].cpu().numpy()[:-1], fwd["tile_offsets"].reshape(-1))
+    assert (st["last_ids"].cpu().numpy() != fwd["last_ids"]).sum() <= 2
