@@ -1,19 +1,26 @@
 """Benchmark of the Gaussian-splatting training step (forward + L1/SSIM loss + backward + fused Adam).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--batch B]
 
 Workload `train_1m` (default at every N): 1,000,000 Gaussians, SH degree 3, one 1296x840 pinhole camera
 per GPU per step out of 200 hemisphere poses, loss 0.8 L1 + 0.2 (1 - SSIM), Adam with the per-group rates
 of the reference's MCMC strategy. N > 1 is weak scaling by camera: each rank renders its own camera against
 replicated Gaussians, the gradients are summed and Adam applied by --dp-mode (default: one fused kernel over
-NVLink peer memory that does reduce-scatter + Adam + all-gather). `--workload dp_3m` is the 3,000,000
+NVLink peer memory that does reduce-scatter + Adam + all-gather). `--batch B` fixes the camera batch of one
+optimizer step (each rank renders B / N cameras and accumulates). `--workload dp_3m` is the 3,000,000
 Gaussian / 1600x1064 data-parallel configuration, `mcmc_3m` the densification step, `wide_4k` /
-`wide_fisheye` the forward-only renders. Synthetic seeded inputs stand in for the Mip-NeRF-360 shapes.
+`wide_fisheye` the forward-only renders, `ewa_1m` the default (non --gut) rasterizer on the train_1m scene.
+Synthetic seeded inputs stand in for the Mip-NeRF-360 shapes.
 
-Rank 0 prints ONE JSON line. `value` is steps/s with every input resident in HBM; `e2e` is the same
-step driven from pinned host memory (target image + camera copied in, loss read back each step).
-`--impl reference` times the CPU oracle (the reference has no CPU implementation of this path and its
-CUDA sources need the glm library, which is not on the machine) on the host cores.
+Rank 0 prints ONE JSON line. `value` is (camera-)steps/s with every input resident in HBM, from one CUDA-event
+bracket around the K timed steps (max over ranks); `step_ms` holds the median / p10 / p90 of the per-step event
+intervals. `e2e` is the same step driven from pinned host memory (target image + camera copied in, loss read back
+each step).
+
+`--impl reference` times the REFERENCE'S OWN CUDA implementation of the same step on the same GPU: the reference's
+unmodified kernels, autograd nodes and FusedAdam, built by oracle/ref_build.py into oracle/_ref (never this
+repository's library). Under torchrun only rank 0 runs it, on one GPU, and reports that one GPU's rate (the reference
+has no multi-GPU path). Where that build is absent the arm falls back to the CPU oracle on the host cores and says so.
 """
 from __future__ import annotations
 
@@ -35,6 +42,10 @@ if str(ROOT) not in sys.path:
 
 LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]  # means, sh0, shN, scaling, rotation, opacity
 METRIC = "train steps/s (fwd+loss+bwd+Adam)"
+# Profiler counters of ONE raster_bwd_kernel launch on train_1m (ncu, --clock-control none): DRAM bytes read + written,
+# share of issue slots used, share of issued warp instructions on the FMA pipe relative to the FP32 peak rate. They are
+# reported next to the event-timed figures because a kernel's traffic and pipe utilisation cannot be read outside a profiler.
+NCU_RASTER_BWD = {"dram_bytes": 180.7e6, "issue_slots_active": 0.82, "fma_pipe_of_fp32_peak": 0.42, "shared_pipe": 0.77}
 
 
 def load_peaks():
@@ -149,10 +160,8 @@ def cpu_step_sample(workload: str, n_rows: int = 6, step: int = 0):
     return full, desc, orc.num_threads()
 
 
-def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+def run_reference_cpu(args, why: str):
+    """Fallback of the reference arm where the reference's CUDA build is absent: the CPU oracle port on the host cores."""
     workload = args.workload or "train_1m"
     times = []
     for s in range(args.warmup + args.steps):
@@ -160,15 +169,144 @@ def run_reference(args):
         if s >= args.warmup:
             times.append(full)
     sec = float(np.mean(times))
-    val = args.gpus / sec if args.gpus > 1 else 1.0 / sec
-    out = {"impl": "reference", "metric": METRIC, "value": val, "unit": "steps/s", "n_gpus": args.gpus, "steps": args.steps,
-           "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "f32", "data": "synthetic", "config": {"workload": workload},
+    val = 1.0 / sec
+    out = {"impl": "reference", "reference_class": "CPU oracle port (" + why + ")", "metric": METRIC, "value": val, "unit": "steps/s",
+           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": workload},
            "cpu_baseline": {"value": val, "unit": "steps/s", "cores": threads, "kind": "port", "sample": desc},
-           "e2e": {"value": val, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-           "note": "CPU oracle (scalar C++ restatement, OpenMP over tiles / Gaussians): the reference has no CPU path and "
-                   "its CUDA sources need glm, which is not installed"}
+           "e2e": {"value": val, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(_finite(out)), flush=True)
+
+
+def _reference_line(args, workload, metric, unit, value, ms, higher, config, e2e, sample, extra=None):
+    out = {"impl": "reference", "reference_class": "the reference's own CUDA sources (unmodified), built into oracle/_ref",
+           "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "gpus_used": 1, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms, "higher_is_better": higher, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": config,
+           "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": "reference",
+                            "sample": sample + " (runs on the GPU: the reference has no CPU implementation of this path; one host thread drives it)"},
+           "e2e": e2e}
+    if extra:
+        out.update(extra)
+    print(json.dumps(_finite(out)), flush=True)
+
+
+def run_reference(args):
+    """The reference arm: the reference's own CUDA step (oracle/_ref) on ONE GPU, same workload, same K and W, same per-step
+    host-to-device upload and loss read-back in its end-to-end figure. Rank 0 only; one GPU's rate at every --gpus."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = args.workload or "train_1m"
+    from oracle import reference as R
+    import torch
+    if not R.available():
+        return run_reference_cpu(args, "oracle/_ref is not built here")
+    if not torch.cuda.is_available():
+        return run_reference_cpu(args, "no GPU")
+    synth = importlib.import_module("lichtfeld-studio_b200").synth
+    cfg = synth.CONFIGS["train_1m" if workload == "ewa_1m" else workload]
+    if workload == "ewa_1m":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's default (EWA) rasterizer fails on the host from about 200,000 Gaussians "
+                          "in this toolchain (garbage bucket count -> `numel: integer multiplication overflow`); by reading, its tile count and "
+                          "tile emission evaluate the same float test in two kernels under --use_fast_math, which can disagree and write out "
+                          "of range, so it is not run at this size"}), flush=True)
+        return
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    W, H, deg, n = cfg["W"], cfg["H"], cfg["sh_degree"], cfg["n"]
+    T = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    P = synth.make_gaussians(n, 0, cfg["layout"], deg)
+    if workload == "mcmc_3m":
+        P["opacity_raw"][np.arange(n) % 20 == 7] = -6.0
+        cap = int(np.float32(1.05) * np.float32(n)) + 64
+        times, counts = [], None
+        for rep in range(args.warmup + args.steps):
+            m = R.McmcReference(P, 0.005, cap, dev)
+            torch.manual_seed(1234)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            nd = m.relocate_gs()
+            na = m.add_new_gs()
+            m.inject_noise(1.6e-4 * 5e5)
+            e1.record(); torch.cuda.synchronize()
+            if rep >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+            counts = (nd, na)
+            del m
+        ms = float(np.mean(times))
+        return _reference_line(args, workload, "MCMC refine step (relocate + add + noise) ms", "ms", ms, ms, False,
+                               {"workload": workload, "gaussians": n, "relocated": counts[0], "added": counts[1]},
+                               {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8},
+                               "MCMC::relocate_gs / add_new_gs / inject_noise with the reference's ATen calls and kernels")
+    poses, Kmat = synth.make_cameras(cfg)
+    Kt, bg = T(Kmat[None]), torch.zeros(3, device=dev)
+    if workload in ("wide_4k", "wide_fisheye"):
+        t = R.make_trainer(P, LRS, deg, device=dev)
+        vms = [T(p[None]) for p in poses]
+        for vm in vms[: max(3, args.warmup)]:
+            t.render_no_grad(True, vm, Kt, W, H, bg, cfg["model"])
+        torch.cuda.synchronize()
+        reps = max(1, args.steps // len(vms)) if args.steps > len(vms) else 1
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for vm in vms:
+                t.render_no_grad(True, vm, Kt, W, H, bg, cfg["model"])
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (reps * len(vms))
+        val = W * H / (ms * 1e-3) / 1e9
+        return _reference_line(args, workload, "forward render Gpix/s", "Gpix/s", val, ms, True,
+                               {"workload": workload, "gaussians": n, "image": [W, H], "poses": len(vms)},
+                               {"value": val, "unit": "Gpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                               "rasterize() of the reference (projection, SH, tile lists, blending) over the seeded poses")
+    # training step (train_1m / dp_3m scenes): render, loss, backward, loss.item(), FusedAdam step, one camera per step
+    t = R.make_trainer(P, LRS, deg, device=dev)
+    held = R.make_trainer(synth.make_gaussians(n, 1000, cfg["layout"], deg), LRS, deg, device=dev)
+    total = args.warmup + args.steps
+    n_e2e = min(args.steps, 50)
+    vms, targets = [], []
+    for s in range(max(total, n_e2e)):
+        vm = T(poses[synth.pose_index(s, cfg["n_poses"])][None])
+        vms.append(vm)
+        targets.append(held.render_no_grad(True, vm, Kt, W, H, bg, 0).image.contiguous())
+    del held
+    torch.cuda.empty_cache()
+    it0 = 2000   # past the iteration up to which the reference skips the shN group
+    for s in range(args.warmup):
+        t.train_step(it0 + s, True, vms[s], Kt, W, H, bg, targets[s], 0.2, 0.0, 0.0)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev.index or 0); sampler.start()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    evs[0].record()
+    for k, s in enumerate(range(args.warmup, total)):
+        t.train_step(it0 + s, True, vms[s], Kt, W, H, bg, targets[s], 0.2, 0.0, 0.0)
+        evs[k + 1].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = evs[0].elapsed_time(evs[-1]) / args.steps
+    per = np.array([evs[k].elapsed_time(evs[k + 1]) for k in range(args.steps)])
+    # end to end: target image and camera from pinned host memory every step, loss read back every step
+    th = [x.cpu().pin_memory() for x in targets[:n_e2e]]
+    vh = [x.cpu().pin_memory() for x in vms[:n_e2e]]
+    tgt, vmb = torch.empty_like(targets[0]), torch.empty_like(vms[0])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(n_e2e):
+        tgt.copy_(th[s], non_blocking=True)
+        vmb.copy_(vh[s], non_blocking=True)
+        t.train_step(it0 + total + s, True, vmb, Kt, W, H, bg, tgt, 0.2, 0.0, 0.0)
+    e1.record(); torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    _reference_line(args, workload, METRIC, "steps/s", 1e3 / ms, ms, True,
+                    {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": 1,
+                     "path": "rasterize() -> FusedRasterizationWithSHFunction -> gsplat::rasterize_from_world_with_sh_fwd/_bwd, fused_ssim, FusedAdam"},
+                    {"value": 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": th[0].numel() * 4 + 64, "d2h_bytes_per_step": 4, "steps": n_e2e},
+                    "Trainer::train_step's render + photometric loss + backward + loss.item() + MCMC::step (FusedAdam, zero_grad, scheduler)",
+                    {"clocks": clocks, "step_ms": {"median": float(np.median(per)), "p10": float(np.percentile(per, 10)),
+                                                   "p90": float(np.percentile(per, 90))}})
 
 
 # --------------------------------------------------------------------------------------------- GPU arm
@@ -197,6 +335,11 @@ def run_ours(args):
     poses, Kmat = synth.make_cameras(cfg)
     total_steps = args.warmup + args.steps
 
+    # cameras of one optimizer step: `world` by default (one per rank), or a fixed --batch spread over the ranks
+    batch = args.batch or world
+    if batch % world:
+        raise SystemExit(f"--batch {batch} must be a multiple of the number of GPUs ({world})")
+    cams_per_rank = batch // world
     dp = pkg.dp
     cap = (n + 31) // 32 * 32
     peer = None
@@ -218,22 +361,28 @@ def run_ours(args):
     Kt = torch.from_numpy(Kmat).to(dev)
 
     # the camera of (step, rank) and its target, rendered from the held-out Gaussians with this library
-    def pose_of(step):
-        return poses[synth.pose_index(step * world + rank, cfg["n_poses"])]
+    def pose_of(step, c=0):
+        return poses[synth.pose_index((step * cams_per_rank + c) * world + rank, cfg["n_poses"])]
 
     n_e2e = min(args.steps, 50)
+    # per step: [cams_per_rank, 3, H, W] targets and [cams_per_rank, 4, 4] poses
     targets_dev, targets_host, vms_dev, vms_host = [], [], [], []
-    for s in range(max(total_steps, n_e2e)):
-        vm = torch.from_numpy(pose_of(s)).to(dev)
-        out = rast_t.forward(tr.Camera(vm, Kt, W, H), bg)
-        tgt = out.image.clamp(0, 1).permute(2, 0, 1).contiguous()
-        targets_dev.append(tgt)
-        vms_dev.append(vm)
+    n_distinct = max(total_steps, n_e2e) if cams_per_rank == 1 else min(max(total_steps, n_e2e), 8)   # bounded memory for batches
+    for s in range(n_distinct):
+        tg, vm_l = [], []
+        for c in range(cams_per_rank):
+            vm = torch.from_numpy(pose_of(s, c)).to(dev)
+            out = rast_t.forward(tr.Camera(vm, Kt, W, H), bg)
+            tg.append(out.image.clamp(0, 1).permute(2, 0, 1).contiguous())
+            vm_l.append(vm)
+        targets_dev.append(torch.stack(tg))
+        vms_dev.append(torch.stack(vm_l))
         if s < n_e2e:
-            targets_host.append(tgt.cpu().pin_memory())
-            vms_host.append(torch.from_numpy(pose_of(s)).pin_memory())
+            targets_host.append(targets_dev[-1].cpu().pin_memory())
+            vms_host.append(vms_dev[-1].cpu().pin_memory())
     del rast_t, held_out
     torch.cuda.synchronize()
+    pick = lambda lst, s: lst[s % len(lst)]
 
     flat_len = model.flat.numel()
     shard = (flat_len + world - 1) // world
@@ -256,10 +405,29 @@ def run_ours(args):
     state = {"color_pending": False}
 
     dp_split = world > 1 and args.dp_mode == "fused_p2p" and not args.no_dp_split
-    rank1_sh = world == 1 and not overlap and not args.materialize_sh_grad
-    dp_rank1 = dp_split and not args.materialize_sh_grad
+    # the rank-1 form of the shN gradient exists for ONE camera per rank; a sum over cameras is materialised
+    rank1_sh = world == 1 and cams_per_rank == 1 and not overlap and not args.materialize_sh_grad
+    dp_rank1 = dp_split and cams_per_rank == 1 and not args.materialize_sh_grad
+    inv_batch = 1.0 / batch
+
+    def step_batch(s, targets, vms):
+        """One optimizer step over cams_per_rank cameras on this rank: gradients accumulate, then exchange + Adam with the
+        mean over the whole batch folded into Adam's gradient read."""
+        last = None
+        for c in range(cams_per_rank):
+            out = rast.forward(tr.Camera(vms[c], Kt, W, H), bg)
+            last, v_render = lossfn(out.image, targets[c])
+            rast.backward(v_render, grads, bg, accumulate=(c > 0))
+        if world == 1:
+            tr.adam_step_splats(model, m, v, grads, LRS, s + 1, grad_scale=inv_batch)
+        else:
+            exchange.step(2000 + s + 1, grad_scale=inv_batch)   # all groups in one exchange after the last backward
+        return last
 
     def step(s, target, vm):
+        if cams_per_rank > 1:
+            return step_batch(s, target, vm)
+        target, vm = target[0], vm[0]
         cam = tr.Camera(vm, Kt, W, H)
         if dp_split:
             # N > 1: the geometry groups are exchanged first; the colour groups (three quarters of the bytes) cross
@@ -311,24 +479,30 @@ def run_ours(args):
 
     # ---- device-resident timing -------------------------------------------------------------
     for s in range(args.warmup):
-        step(s, targets_dev[s], vms_dev[s])
+        step(s, pick(targets_dev, s), pick(vms_dev, s))
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for s in range(args.warmup, total_steps):
-        step(s, targets_dev[s], vms_dev[s])
-    e1.record()
+    # one bracket around the K timed steps (the reported figure) and an event after every step (the series)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    evs[0].record()
+    for k, s in enumerate(range(args.warmup, total_steps)):
+        step(s, pick(targets_dev, s), pick(vms_dev, s))
+        evs[k + 1].record()
     barrier()
-    ms_total = e0.elapsed_time(e1)
+    ms_total = evs[0].elapsed_time(evs[-1])
+    per_step = torch.tensor([evs[k].elapsed_time(evs[k + 1]) for k in range(args.steps)], device=dev, dtype=torch.float64)
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms_total], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
+        dist.all_reduce(per_step, op=dist.ReduceOp.MAX)      # a step takes as long as its slowest rank
     ms_per_step = ms_total / args.steps
+    per_step = per_step.cpu().numpy()
+    step_ms = {"median": float(np.median(per_step)), "p10": float(np.percentile(per_step, 10)), "p90": float(np.percentile(per_step, 90)),
+               "min": float(per_step.min()), "max": float(per_step.max())}
     status = rast.status.cpu().numpy()
 
     # ---- end to end from pinned host memory ---------------------------------------------------
@@ -339,7 +513,7 @@ def run_ours(args):
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream()
     tgt_bufs = [torch.empty_like(targets_dev[0]) for _ in range(2)]
-    vm_bufs = [torch.empty((4, 4), device=dev) for _ in range(2)]
+    vm_bufs = [torch.empty_like(vms_dev[0]) for _ in range(2)]
     loss_pinned = [torch.empty(4, dtype=torch.float32).pin_memory() for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
@@ -351,11 +525,12 @@ def run_ours(args):
         with torch.cuda.stream(copy_stream):
             if s >= 2:
                 copy_stream.wait_event(consumed[k])   # step s-2 has finished with this buffer
-            tgt_bufs[k].copy_(targets_host[s], non_blocking=True)
-            vm_bufs[k].copy_(vms_host[s], non_blocking=True)
+            tgt_bufs[k].copy_(pick(targets_host, s), non_blocking=True)
+            vm_bufs[k].copy_(pick(vms_host, s), non_blocking=True)
             ready[k].record(copy_stream)
 
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     upload(0)
     for s in range(n_e2e):
@@ -382,23 +557,46 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = float(t.item())
     ms_e2e /= n_e2e
-    h2d = targets_host[0].numel() * 4 + 64
+    h2d = targets_host[0].numel() * 4 + vms_host[0].numel() * 4
     d2h = loss_host.numel() * 4
 
     # ---- per-kernel times (CUDA events inside the library), pair counts, rooflines --------------------
     kernels, roofline, extra = {}, None, {}
     n_prof = 3
-    if rank == 0:
-        capi.profile_enable(True)
-    for s in range(n_prof):  # every rank steps (the exchange is a collective); only rank 0 records events
-        step(s, targets_dev[s], vms_dev[s])
+    capi.profile_enable(True)          # every rank records: the per-rank spread of the backward is part of the report
+    if world > 1:
+        exchange.timing = []
+    for s in range(n_prof):
+        step(s, pick(targets_dev, s), pick(vms_dev, s))
     barrier()
+    recs = capi.profile_collect()
+    capi.profile_enable(False)
+    for name, msv in recs:
+        kernels.setdefault(name, []).append(msv)
+    rendezvous = {}
+    if world > 1:
+        for name, msv in exchange.collect_timing():
+            rendezvous.setdefault(name, []).append(msv)
+        exchange.timing = None
+    per_rank = None
+    if world > 1:
+        mine = torch.tensor([float(np.sum(kernels.get(k, [0.0])) / n_prof) for k in ("raster_bwd", "raster_fwd", "project_pack")],
+                            device=dev, dtype=torch.float64)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        allr = torch.stack(allr).cpu().numpy()
+        per_rank = {k: {"min": float(allr[:, i].min()), "max": float(allr[:, i].max())} for i, k in enumerate(("raster_bwd", "raster_fwd", "project_pack"))}
+    # every rank must hold the same parameters after the timed steps: integer checksum of the raw bits
+    dp_check = None
+    if world > 1:
+        bits = model.flat.view(torch.int32).to(torch.int64)
+        chk = torch.stack([bits.sum(), (bits * (torch.arange(bits.numel(), device=dev) % 1021 + 1)).sum()])
+        allc = [torch.empty_like(chk) for _ in range(world)]
+        dist.all_gather(allc, chk)
+        same_params = all(bool(torch.equal(allc[0], c)) for c in allc)
+        small = dp_self_check(pkg, dev, rank, world, args.dp_mode, dp_split, dp_rank1)
+        dp_check = {"ok": bool(same_params and small["ok"]), "bench_parameters_identical_on_all_ranks": bool(same_params), **small}
     if rank == 0:
-        recs = capi.profile_collect()
-        capi.profile_enable(False)
-        for name, msv in recs:
-            kernels.setdefault(name, []).append(msv)
-        launches_per_step = len(recs) / n_prof
         # launches inside one call that are not individually bracketed: scan = 3 kernels, sort = 3 per pass
         per_step_kernels = {"exclusive_scan": 3, "radix_sort_depth": 12, "radix_sort_tile": 6}
         gpu_launches_step = sum(per_step_kernels.get(k, 1) * len(vs) / n_prof for k, vs in kernels.items()) + 4
@@ -411,21 +609,27 @@ def run_ours(args):
         q_b = int(torch.clamp(torch.minimum(last, end - 1) - start + 1, min=0).sum().item())
         q_list = int((end - start).sum().item())
         sm_clock = (clocks or {}).get("sm_mhz") or 1965.0
-        fp32_peak = 148 * 128 * 2 * sm_clock * 1e6 / 1e12
-        t_bwd = float(np.mean(kernels.get("raster_bwd", [float("nan")])))
-        t_fwd = float(np.mean(kernels.get("raster_fwd", [float("nan")])))
+        n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        fp32_peak = n_sm * 128 * 2 * sm_clock * 1e6 / 1e12
+        calls = cams_per_rank * n_prof
+        t_bwd = float(np.sum(kernels.get("raster_bwd", [float("nan")])) / calls)
+        t_fwd = float(np.sum(kernels.get("raster_fwd", [float("nan")])) / calls)
         # per step: the split optimizer launches "adam" twice (geometry groups, colour groups); the roofline figure uses
         # the sum of both (each is timed alone on its stream, but they may overlap other kernels)
         t_adam = float(np.sum(kernels["adam"]) / n_prof) if "adam" in kernels else float("nan")
         hbm_peak, peak_kind = load_peaks()
         ach = 370.0 * q_b / (t_bwd * 1e-3) / 1e12
-        # DRAM bytes of one raster_bwd launch from the committed ncu capture (profiles/raster_bwd_train_1m.md);
-        # it scales with the tile-instance count, so other workloads report null
-        traffic = 180.7e6 if workload == "train_1m" else None
+        # DRAM bytes and pipe utilisation of one raster_bwd launch come from an ncu capture of this kernel on this workload
+        # (they cannot be read outside a profiler); other workloads report null
+        ncu = NCU_RASTER_BWD if workload == "train_1m" else None
         roofline = {"kernel": "raster_bwd_kernel", "bound": "fp32", "achieved": ach, "peak": fp32_peak, "unit": "TFLOP/s",
-                    "frac": ach / fp32_peak, "traffic": traffic,
-                    "note": f"370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms; peak = 148 SM x 128 lanes x 2 x "
-                            f"{sm_clock:.0f} MHz sampled under load (no tensor cores on this path)"}
+                    "frac": ach / fp32_peak, "traffic": ncu["dram_bytes"] if ncu else None,
+                    "pairs_per_s": q_b / (t_bwd * 1e-3),
+                    "utilisation_ncu": ncu,
+                    "note": f"achieved / frac follow the fixed accounting 370 flop x {q_b} (pixel,Gaussian) pairs / {t_bwd:.3f} ms, i.e. the REFERENCE's "
+                            f"arithmetic per pair; this kernel executes fewer flops per pair (per-Gaussian work is hoisted out of the pair loop), so "
+                            f"frac can exceed 1 and is NOT pipe utilisation. Utilisation is utilisation_ncu (issue slots, FMA pipe) from the "
+                            f"profiler capture. peak = {n_sm} SM x 128 lanes x 2 x {sm_clock:.0f} MHz sampled under load (no tensor cores on this path)"}
         adam_bytes = 28.0 * 59 * n if K_sh == 16 else 28.0 * model.row_floats * n
         adam_kernel = "adam_groups_kernel"
         adam_note = f"28 B x {model.row_floats} floats x {n} Gaussians"
@@ -438,40 +642,121 @@ def run_ours(args):
             adam_kernel = "adam_sh_rank1_kernel"
             adam_note = f"(24 B x {rest} shN floats + 24 B) x {n} Gaussians"
         adam_gbs = adam_bytes / (t_adam * 1e-3) / 1e9 if np.isfinite(t_adam) else None   # N > 1: Adam runs inside the exchange
+        list_keys = ("radix_sort_depth", "exclusive_scan", "emit_instances", "radix_sort_tile", "tile_offsets", "tile_order")
+        t_lists = sum(float(np.sum(kernels[k])) / calls for k in list_keys if k in kernels)
+        V, I = float(status[2]), float(status[1])
+        tiles = ((W + 15) // 16) * ((H + 15) // 16)
+        list_bytes = 20 * V + 36 * I + 4 * tiles
+        t_pp = float(np.sum(kernels.get("project_pack", [float("nan")])) / calls)
+        pp_bytes = 52.0 * n + 216.0 * V
         extra = {"roofline_adam": {"kernel": adam_kernel, "bound": "hbm", "achieved": adam_gbs,
                                    "peak": hbm_peak, "unit": "GB/s", "frac": adam_gbs / hbm_peak if adam_gbs else None,
                                    "traffic": None, "note": f"{adam_note}, of {peak_kind}"},
                  "roofline_raster_fwd": {"kernel": "raster_fwd_kernel", "bound": "fp32",
                                          "achieved": 70.0 * q_list / (t_fwd * 1e-3) / 1e12, "peak": fp32_peak, "unit": "TFLOP/s",
                                          "frac": 70.0 * q_list / (t_fwd * 1e-3) / 1e12 / fp32_peak,
-                                         "note": f"70 flop x {q_list} list entries x pixels (upper bound of pairs visited)"},
+                                         "note": f"70 flop x {q_list} list entries x pixels (upper bound of pairs visited); same caveat as raster_bwd"},
+                 "roofline_tile_lists": {"kernel": "depth sort + scan + emit + tile sort + offsets + order", "bound": "hbm",
+                                         "achieved": list_bytes / (t_lists * 1e-3) / 1e9 if t_lists else None, "peak": hbm_peak, "unit": "GB/s",
+                                         "frac": list_bytes / (t_lists * 1e-3) / 1e9 / hbm_peak if t_lists else None, "ms": t_lists,
+                                         "note": f"20 V + 36 I + 4 tiles bytes, of {peak_kind}"},
+                 "roofline_project_pack": {"kernel": "project_pack_kernel", "bound": "hbm", "achieved": pp_bytes / (t_pp * 1e-3) / 1e9,
+                                           "peak": hbm_peak, "unit": "GB/s", "frac": pp_bytes / (t_pp * 1e-3) / 1e9 / hbm_peak,
+                                           "note": f"52 N + 216 V bytes, of {peak_kind}"},
                  "kernel_ms": {k: float(np.sum(vs) / n_prof) for k, vs in kernels.items()},
                  "n_isects": int(status[1]), "n_visible": int(status[2]), "pairs_bwd": q_b, "pairs_list": q_list,
-                 "gpix_per_s_fwd": W * H / (sum(float(np.mean(kernels[k])) for k in kernels if k in (
-                     "project_pack", "radix_sort_depth", "exclusive_scan", "emit_instances", "radix_sort_tile", "tile_offsets",
-                     "raster_fwd")) * 1e-3) / 1e9}
+                 "gpix_per_s_fwd": W * H / ((t_pp + t_lists + t_fwd) * 1e-3) / 1e9}
+        if world > 1:
+            extra["rendezvous_ms"] = {k: float(np.sum(vs) / n_prof) for k, vs in rendezvous.items()}
+            extra["per_rank_kernel_ms"] = per_rank
+            extra["dp_check"] = dp_check
 
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu:
             full, desc, threads = cpu_step_sample(workload)
             cpu = {"value": 1.0 / full, "unit": "steps/s", "cores": threads, "kind": "port", "sample": desc}
-        out = {"metric": METRIC, "value": world * 1e3 / ms_per_step, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
-               "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        unit = "steps/s" if batch == 1 else "camera-steps/s"
+        out = {"metric": METRIC, "value": batch * 1e3 / ms_per_step, "unit": unit, "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": ms_per_step, "step_ms": step_ms, "optimizer_steps_per_s": 1e3 / ms_per_step,
+               "higher_is_better": True, "scaling": "weak" if not args.batch else "strong",
                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-               "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": world,
+               "config": {"workload": workload, "gaussians": n, "image": [W, H], "sh_degree": deg, "cameras_per_step": batch,
+                          "cameras_per_rank": cams_per_rank,
                           "optimizer_overlap": bool(overlap), "optimizer": ("inside lfs_render_backward_adam" if (rank1_sh and args.one_call_optimizer) else "separate call"),
                           "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else ("rank-1 factors over NVLink" if dp_rank1 else "materialised"),
-                          "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
+                          "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split and cams_per_rank == 1 else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
-               "clocks": clocks, "e2e": {"value": world * 1e3 / ms_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
+               "clocks": clocks, "e2e": {"value": batch * 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": h2d,
                                          "d2h_bytes_per_step": d2h, "steps": n_e2e},
                "gpu_launches": int(round(gpu_launches_step * args.steps)), "roofline": roofline, "cpu_baseline": cpu,
-               "gpix_per_s_step": world * W * H / (ms_per_step * 1e-3) / 1e9}
+               "gpix_per_s_step": batch * W * H / (ms_per_step * 1e-3) / 1e9}
         out.update(extra)
         print(json.dumps(_finite(out)), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def dp_self_check(pkg, dev, rank, world, mode, split, rank1):
+    """Cross-rank correctness of the exchange the benchmark just timed, on a small scene: three data-parallel steps with
+    the same mode flags must leave bit-identical parameters on every rank, equal (to gradient-summation rounding) to what
+    ONE process gets by rendering every camera itself, accumulating the gradients and applying Adam to their mean."""
+    import torch
+    import torch.distributed as dist
+    synth, tr, dp = pkg.synth, pkg.trainer, pkg.dp
+    n, W, H, deg, steps = 30000, 320, 208, 3, 3
+    K = (deg + 1) ** 2
+    P = synth.make_gaussians(n, 0, "clusters", deg)
+    poses = synth.hemisphere_poses(16, 5.0)
+    Kmat = torch.from_numpy(synth.intrinsics(280.0, 280.0, W / 2, H / 2)).to(dev)
+    bg = torch.zeros(3, device=dev)
+    targets = [torch.rand(3, H, W, generator=torch.Generator().manual_seed(s)).to(dev) for s in range(steps * world)]
+    cam = lambda i: tr.Camera(torch.from_numpy(poses[i % 16]).to(dev), Kmat, W, H)
+    cap = (n + 31) // 32 * 32
+    # one process, all cameras
+    model, grads = tr.SplatData(n, K, dev, cap).load(P), tr.SplatData(n, K, dev, cap)
+    rast, lossfn = tr.Rasterizer(model, W, H, deg), tr.PhotometricLoss(W, H, dev)
+    m, v = model.like(), model.like()
+    for s in range(steps):
+        for r in range(world):
+            out = rast.forward(cam(s * world + r), bg)
+            _, vr = lossfn(out.image, targets[s * world + r])
+            rast.backward(vr, grads, bg, accumulate=(r > 0))
+        tr.adam_step_splats(model, m, v, grads, LRS, s + 1, skip_shN=False, grad_scale=1.0 / world)
+    local = model.flat.clone()
+    start = tr.SplatData(n, K, dev, cap).load(P).flat.clone()
+    # the exchange under test
+    peer = None
+    if mode == "fused_p2p":
+        numel = cap * tr.SplatData(1, K, "cpu").row_floats
+        pf, gf, peer = dp.symmetric_flat_buffers(numel, dev)
+        model, grads = tr.SplatData(n, K, dev, cap, flat=pf).load(P), tr.SplatData(n, K, dev, cap, flat=gf)
+    else:
+        model, grads = tr.SplatData(n, K, dev, cap).load(P), tr.SplatData(n, K, dev, cap)
+    rast = tr.Rasterizer(model, W, H, deg)
+    ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer)
+    side = torch.cuda.Stream(device=dev)
+    for s in range(steps):
+        if split:
+            rast.forward_lists(cam(s * world + rank))
+            ex.wait_color()
+            out = rast.forward_shade(bg)
+        else:
+            out = rast.forward(cam(s * world + rank), bg)
+        _, vr = lossfn(out.image, targets[s * world + rank])
+        rast.backward(vr, grads, bg, sh_factors=bool(split and rank1))
+        if split:
+            ex.step_split(2000 + s, side, rank1_sh=bool(rank1), sh_degree=deg)
+        else:
+            ex.step(2000 + s)
+    ex.wait_color()
+    torch.cuda.synchronize()
+    outp = model.flat.clone()
+    gathered = [torch.empty_like(outp) for _ in range(world)]
+    dist.all_gather(gathered, outp)
+    same = all(bool(torch.equal(gathered[0], g)) for g in gathered)
+    rel = float((outp - local).norm() / (local - start).norm())
+    return {"small_scene_identical_on_all_ranks": bool(same), "small_scene_update_error_vs_one_process": rel, "ok": bool(same and rel < 2e-3)}
 
 
 def _finite(x):
@@ -676,20 +961,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
+    ap.add_argument("--batch", type=int, default=0,
+                    help="cameras of one optimizer step, fixed over the number of GPUs (each rank renders batch / gpus cameras and "
+                         "accumulates); default: one camera per GPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--overlap-ctas", type=int, default=2, help="launch footprint (CTAs per SM) of the overlapped colour-group Adam")
     ap.add_argument("--overlap", action="store_true",
-                    help="single GPU: split optimizer, colour groups on a side stream under the next step's projection and "
-                         "tile lists (measured: no gain on B200, 2.975 ms against 2.964 ms; both sides are memory-latency sensitive)")
+                    help="single GPU: split optimizer, colour groups on a side stream under the next step's projection and tile lists")
     ap.add_argument("--materialize-sh-grad", action="store_true",
                     help="write the shN gradient rows (lfs_adam_step_splats / element-wise exchange) instead of using their rank-1 form")
     ap.add_argument("--one-call-optimizer", action="store_true",
-                    help="single GPU: lfs_render_backward_adam (no gradient tensor at all; same speed) instead of "
+                    help="single GPU: lfs_render_backward_adam (no gradient tensor at all) instead of "
                          "lfs_render_backward + lfs_adam_step_splats_rank1_sh")
     ap.add_argument("--no-dp-split", action="store_true",
                     help="N > 1, fused_p2p: exchange all groups in one kernel after the backward. Default: geometry groups first, "
-                         "colour groups on a side stream (one CTA per SM) under the next step's projection and tile lists "
-                         "(3.27 ms against 3.39 ms at 4 GPUs)")
+                         "colour groups on a side stream (one CTA per SM) under the next step's projection and tile lists")
     ap.add_argument("--dp-mode", default="fused_p2p", choices=["allreduce", "sharded", "fused_p2p"],
                     help="gradient exchange for N > 1 (see lichtfeld-studio_b200/dp.py)")
     args = ap.parse_args()

@@ -372,7 +372,9 @@ int launch_adam_segments(const AdamSegments& S, int ctas_per_sm, cudaStream_t st
 int launch_dp_reduce_adam_broadcast(const DpArgs& A, int ctas_per_sm, cudaStream_t st) {
     const int64_t total4 = A.prefix4[A.n_segments];
     if (total4 == 0) return LFS_OK;
-    LFS_TIMED("dp_reduce_adam_broadcast", st);
+    // two names so that a profile tells the exchange on the caller's stream from the small-footprint launch that
+    // overlaps the next step's kernels on a side stream
+    LFS_TIMED(ctas_per_sm > 0 ? "dp_exchange_side" : "dp_exchange_main", st);
     // NVLink-bound: a few CTAs per SM keep enough 16-byte requests in flight; a caller that runs other kernels
     // next to this one asks for a small footprint so that those kernels find free thread slots
     dp_reduce_adam_broadcast_kernel<<<grid_for(total4, 256, ctas_per_sm > 0 ? ctas_per_sm : 16), 256, 0, st>>>(A);

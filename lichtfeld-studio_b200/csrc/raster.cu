@@ -1071,7 +1071,7 @@ int launch_adam_sh_rank1(int N, int K, int sh_degree, const float* campos, const
 
 int launch_dp_sh_rank1(int K, int sh_degree, const DpRank1& A, int ctas_per_sm, cudaStream_t st) {
     if (A.n == 0 || K <= 1) return LFS_OK;
-    LFS_TIMED("dp_sh_rank1", st);
+    LFS_TIMED("dp_exchange_side_sh_rank1", st);
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
     if (smem > 200 * 1024) { set_error("dp_sh_rank1: too many SH coefficients"); return LFS_EINVAL; }
     if (smem > 48 * 1024)

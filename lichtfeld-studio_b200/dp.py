@@ -102,11 +102,32 @@ class GradExchange:
             self.peer_grads, self.peer_params = peer_ptrs
         self.step_count = 0
         self._split = None   # lazily built state of step_split()
+        self.timing = None   # set to a list to collect (name, start event, end event) of every rendezvous
         self.color_ctas_per_sm = int(os.environ.get("LFS_DP_COLOR_CTAS", "1"))   # launch footprint of the overlapped part
 
     # -- helpers --------------------------------------------------------------------------------
     def _stream(self):
         return capi.vp(torch.cuda.current_stream().cuda_stream)
+
+    def _rendezvous(self, token, group, name):
+        """Stream-ordered 4-byte all-reduce: no rank's later kernels start before every rank's earlier ones finished.
+        When `timing` is a list, the wait (which includes waiting for the slowest rank) is bracketed by events."""
+        if self.timing is None:
+            dist.all_reduce(token, group=group)
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.all_reduce(token, group=group)
+        e1.record()
+        self.timing.append((name, e0, e1))
+
+    def collect_timing(self):
+        """[(name, ms)] of the recorded rendezvous; synchronises."""
+        torch.cuda.synchronize()
+        out = [(n, a.elapsed_time(b)) for n, a, b in (self.timing or [])]
+        if self.timing is not None:
+            self.timing = []
+        return out
 
     def _adam_shard(self, iteration: int, grad_shard: torch.Tensor, grad_scale: float):
         segs = group_segments(self.model.capacity, self.model.K, self.lo, self.n, self.lrs, skip_shN=(iteration <= 1000))
@@ -171,7 +192,7 @@ class GradExchange:
         if self.mode == "fused_p2p":
             # stream-ordered rendezvous: every rank's backward has written its gradients
             token = torch.zeros(1, device=model.flat.device)
-            dist.all_reduce(token, group=self.group)
+            self._rendezvous(token, self.group, "rendezvous_gradients_written")
             segs = group_segments(model.capacity, model.K, self.lo, self.n, self.lrs, skip_shN=(iteration <= 1000))
             arr = (capi.DpSegment * max(len(segs), 1))()
             for i, (gi, off, cnt, lr) in enumerate(segs):
@@ -183,7 +204,7 @@ class GradExchange:
             capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
                       self.step_count, float(gs), 0, self._stream())
             # nobody may read parameters or overwrite gradients before every rank's kernel has finished
-            dist.all_reduce(token, group=self.group)
+            self._rendezvous(token, self.group, "rendezvous_exchange_done")
             return
         raise ValueError(self.mode)
 
@@ -244,11 +265,11 @@ class GradExchange:
         skip = iteration <= 1000
         main = torch.cuda.current_stream()
         # every rank's backward has written its gradients
-        dist.all_reduce(st["token_a"], group=self.group)
+        self._rendezvous(st["token_a"], self.group, "rendezvous_gradients_written")
         st["ev_grads"].record(main)
         segs, _ = class_segments(model.capacity, model.K, GEOMETRY_CLASS, self.world, self.rank, self.lrs)
         self._fused_call(segs, st["geo_m"], st["geo_v"], gs)
-        dist.all_reduce(st["token_a"], group=self.group)      # every rank's geometry kernel has finished
+        self._rendezvous(st["token_a"], self.group, "rendezvous_geometry_done")      # every rank's geometry kernel has finished
         with torch.cuda.stream(st["side"]):
             st["side"].wait_event(st["ev_grads"])
             segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
@@ -264,7 +285,7 @@ class GradExchange:
                         self._rank1_call(sg, st["col_m"], st["col_v"], gs, sh_degree, ctas_per_sm=self.color_ctas_per_sm)
             else:
                 self._fused_call(segs, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
-            dist.all_reduce(st["token_b"], group=st["group_b"])  # every rank's colour kernel has finished
+            self._rendezvous(st["token_b"], st["group_b"], "rendezvous_color_done_side")  # every rank's colour kernel has finished
             st["ev_color"].record(st["side"])
         st["pending"] = True
 
