@@ -138,7 +138,8 @@ class McmcReference:
         for n in NAMES:
             self.m[n].index_put_((sampled,), torch.zeros((), device=sampled.device))
             self.v[n].index_put_((sampled,), torch.zeros((), device=sampled.device))
-        self.last.update(dead_indices=dead_indices, alive_indices=alive_indices, relocate_sampled=sampled, relocate_ratios=ratios)
+        self.last.update(dead_indices=dead_indices, alive_indices=alive_indices, relocate_sampled=sampled, relocate_ratios=ratios,
+                         relocate_sampled_local=sampled_local)
         return int(n_dead)
 
     def add_new_gs(self) -> int:
