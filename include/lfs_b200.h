@@ -307,6 +307,13 @@ int lfs_photometric_loss(int H, int W, float lambda_dssim, float grad_scale, con
                          const float* target_chw, float* v_render_hwc, float* loss_dev,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* v_bg_color of the autograd node (src/training/rasterization/rasterizer_autograd.cpp:206-209):
+ * v_background[c] = sum over pixels of v_render[p, c] * (1 - alpha[p]), for callers whose background colour is a trained
+ * parameter. v_render [H,W,channels] (channels 1..4), alpha [H,W,1] the forward's alpha, v_background device float[channels].
+ * workspace: 32 bytes of 8-byte aligned device scratch. */
+int lfs_background_gradient(int H, int W, int channels, const float* v_render, const float* alpha, float* v_background,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* FusedAdam::step over all six groups in one launch (src/training/optimizers/fused_adam.cpp:22-95,
  * group order and learning rates of src/training/strategies/mcmc.cpp:487-492). lr[6] host values in
  * group order means, sh0, shN, scaling, rotation, opacity; step_count >= 1 is the optimizer step
@@ -415,6 +422,8 @@ int lfs_mcmc_classify(int N, const float* opacity_raw, const float* rotation_raw
  * start-up). The scratch is a fixed array inside the library (about 2.1 MB per GPU, held until the
  * process exits), so N is limited to LFS_NOALLOC_MAX_GAUSSIANS; larger N returns LFS_ECAPACITY. The first
  * call on a device also looks up the array's device address; make that call before any stream capture.
+ * The array used is the one of the device that is CURRENT when the call is made, so the device that owns `stream` must be
+ * current (a stream of another device would be paired with the wrong copy of the array).
  * All calls on a device share the scratch: calls that overlap on the GPU race and corrupt each other. */
 #define LFS_NOALLOC_MAX_GAUSSIANS 262144
 int lfs_mcmc_classify_noalloc(int N, const float* opacity_raw, const float* rotation_raw, float min_opacity,

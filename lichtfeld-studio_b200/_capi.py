@@ -100,6 +100,7 @@ _SIGNATURES = {
                                  C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, f32, vp, sz, vp],
     "lfs_render_workspace_view": [C.POINTER(RenderConfig), vp, sz, C.POINTER(RenderView)],
     "lfs_photometric_loss": [i32, i32, f32, f32, vp, vp, vp, vp, vp, sz, vp],
+    "lfs_background_gradient": [i32, i32, i32, vp, vp, vp, vp, sz, vp],
     "lfs_adam_step_splats": [i32, i32, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),
                              C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, i64, i64, f32, vp],
     "lfs_adam_step_splats_rank1_sh": [C.POINTER(RenderConfig), C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),

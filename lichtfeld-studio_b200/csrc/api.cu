@@ -403,6 +403,16 @@ int lfs_fusedssim_backward(int CH, int H, int W, float C1, float C2, const float
 
 size_t lfs_photometric_loss_workspace_bytes(int H, int W) { return photometric_workspace_bytes(H, W); }
 
+int lfs_background_gradient(int H, int W, int channels, const float* v_render, const float* alpha, float* v_background,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+    LFS_REQUIRE(H >= 0 && W >= 0 && channels >= 1 && channels <= 4, "bad size");
+    LFS_REQUIRE(v_background && workspace, "null pointer");
+    if ((int64_t)H * W > 0) LFS_REQUIRE(v_render && alpha, "null pointer");
+    if (workspace_bytes < 32) { set_error("lfs_background_gradient: workspace too small (32 bytes)"); return LFS_ECAPACITY; }
+    LFS_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 7) == 0, "workspace must be 8-byte aligned");
+    return launch_background_gradient(H, W, channels, v_render, alpha, v_background, workspace, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int lfs_photometric_loss(int H, int W, float lambda_dssim, float grad_scale, const float* render_hwc, const float* target_chw,
                          float* v_render_hwc, float* loss_dev, void* workspace, size_t workspace_bytes, void* stream) {
     LFS_REQUIRE(H > 0 && W > 0, "bad sizes");

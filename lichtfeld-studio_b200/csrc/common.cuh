@@ -35,12 +35,13 @@ struct KernelTimer {
         }                                              \
     } while (0)
 
-// The B200 has 148 SMs; persistent / grid-stride kernels are sized in multiples of it.
-constexpr int kNumSMs = 148;
+// Persistent / grid-stride kernels are sized in multiples of the SM count of the current device (148 on a B200),
+// read once per device from cudaDevAttrMultiProcessorCount.
+int num_sms();
 
 inline int grid_for(int64_t n, int block, int max_blocks_per_sm = 8) {
     int64_t g = (n + block - 1) / block;
-    const int64_t cap = (int64_t)kNumSMs * max_blocks_per_sm;
+    const int64_t cap = (int64_t)num_sms() * max_blocks_per_sm;
     if (g > cap) g = cap;
     if (g < 1) g = 1;
     return (int)g;
@@ -98,8 +99,9 @@ struct SortScratch {
     uint32_t* hist;       // [kRadixBlocks * 256]
     uint32_t* block_sums; // [kScanBlocks + 1]
 };
-constexpr int kRadixBlocks = kNumSMs * 4;
-constexpr int kScanBlocks = kNumSMs * 4;
+// Capacity of the scratch arrays; the launches use min(4 x SM count, capacity) blocks.
+constexpr int kRadixBlocks = 1024;
+constexpr int kScanBlocks = 1024;
 size_t sort_scratch_bytes();
 
 // Stable LSD radix sort of (key, value) uint32 pairs over key bits [0, key_bits). n is read from

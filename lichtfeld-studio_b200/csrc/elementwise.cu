@@ -473,7 +473,7 @@ __global__ void __launch_bounds__(256) ply_rows_unpack_kernel(int N, int K, cons
 int launch_ply_rows(int N, int K, const lfs_splats& p, float* rows, int unpack, cudaStream_t st) {
     if (N == 0) return LFS_OK;
     LFS_TIMED(unpack ? "ply_rows_unpack" : "ply_rows_pack", st);
-    const int grid = (int)min((int64_t)148 * 8, ((int64_t)N * 32 + 255) / 256);
+    const int grid = (int)min((int64_t)num_sms() * 8, ((int64_t)N * 32 + 255) / 256);
     if (unpack) ply_rows_unpack_kernel<<<grid, 256, 0, st>>>(N, K, rows, p);
     else ply_rows_pack_kernel<<<grid, 256, 0, st>>>(N, K, p, rows);
     return check_launch("ply_rows");

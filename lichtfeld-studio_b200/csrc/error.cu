@@ -27,6 +27,18 @@ int check_launch(const char* what) {
 
 const char* last_error() { return g_err; }
 
+int num_sms() {
+    static int cached[64] = {};   // per device ordinal; 0 = not read yet
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 namespace {
 struct ProfRec { const char* name; cudaEvent_t a, b; };
 bool g_prof = false;

@@ -246,6 +246,46 @@ int launch_fusedssim_backward(int CH, int H, int W, const float* img1, const flo
     return check_launch("fusedssim_backward");
 }
 
+namespace {
+// out[c] += sum over pixels of v_render[p, c] * (1 - alpha[p]); one double atomic per CTA and channel.
+__global__ void __launch_bounds__(256) background_gradient_kernel(int64_t P, int CH, const float* __restrict__ v_render,
+                                                                  const float* __restrict__ alpha, double* __restrict__ acc) {
+    double s[4] = {0.0, 0.0, 0.0, 0.0};
+    for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < P; p += (int64_t)gridDim.x * blockDim.x) {
+        const float w = 1.0f - alpha[p];
+        for (int c = 0; c < CH; ++c) s[c] += (double)(v_render[p * CH + c] * w);
+    }
+    __shared__ double red[8][4];
+    for (int c = 0; c < CH; ++c) {
+        double v = s[c];
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5][c] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < CH) {
+        double v = 0.0;
+        for (int w = 0; w < 8; ++w) v += red[w][threadIdx.x];
+        atomicAdd(acc + threadIdx.x, v);
+    }
+}
+__global__ void background_gradient_finalize_kernel(int CH, const double* __restrict__ acc, float* __restrict__ out) {
+    if (threadIdx.x < CH) out[threadIdx.x] = (float)acc[threadIdx.x];
+}
+}  // namespace
+
+int launch_background_gradient(int H, int W, int CH, const float* v_render, const float* alpha, float* v_background,
+                               void* workspace, cudaStream_t st) {
+    double* acc = reinterpret_cast<double*>(workspace);
+    cudaMemsetAsync(acc, 0, 4 * sizeof(double), st);
+    const int64_t P = (int64_t)H * W;
+    if (P > 0) {
+        LFS_TIMED("background_gradient", st);
+        background_gradient_kernel<<<grid_for(P, 256, 4), 256, 0, st>>>(P, CH, v_render, alpha, acc);
+    }
+    background_gradient_finalize_kernel<<<1, 32, 0, st>>>(CH, acc, v_background);
+    return check_launch("background_gradient");
+}
+
 size_t photometric_workspace_bytes(int H, int W) { return 256 + (size_t)3 * 3 * H * W * sizeof(float); }
 
 int launch_photometric_loss(int H, int W, float lambda, float grad_scale, const float* render_hwc, const float* target_chw,

@@ -33,8 +33,10 @@ static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 constexpr int kMaxDevices = 64;
 unsigned char* g_scratch_addr[kMaxDevices] = {};  // device address of g_scratch, per device, filled on first use
 
-// Device address of this device's copy of the scratch array. The first call on a device resolves it
-// with cudaGetSymbolAddress (that device must be current, which it is: we ask which one is current).
+// Device address of the CURRENT device's copy of the scratch array. The first call on a device resolves it
+// with cudaGetSymbolAddress (that device must be current, which it is: we ask which one is current). The caller's
+// stream must belong to that same device; the entry point cannot check this from a bare stream handle.
+// Two host threads that make their first call at the same time both store the same address, which is harmless.
 int scratch_base(unsigned char** out) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);

@@ -64,6 +64,8 @@ __device__ __forceinline__ CamDev make_cam(const float* __restrict__ vm, const f
     if (model == LFS_FISHEYE) {
         const float mdx = fmaxf((float)W - c.cx, c.cx), mdy = fmaxf((float)H - c.cy, c.cy);
         const float max_radius_pixels = sqrtf(mdx * mdx + mdy * mdy);
+        // Largest usable angle of the OpenCV fisheye polynomial, in the operation order of compute_opencv_fisheye_max_angle
+        // (gsplat/Cameras.cuh:760-815), since the clamp feeds the bit-exact tile lists:
         // smallest positive root of 1 + a x + b x^2 + c x^3 (x = theta^2), k4 == 0 only
         const float a = 3.f * c.k[0], b = 5.f * c.k[1], cc = 7.f * c.k[2];
         float root = FLT_MAX;

@@ -5,18 +5,19 @@
 // (K8) with the VJPs of gsplat/Utils.cuh:104-194, gsplat/SphericalHarmonicsCUDA.cu:445 (K3) and the
 // activation backward that autograd performs for src/core/splat_data.cpp:267-286.
 //
-// Design (FP32-pipe bound, no tensor cores: the largest contraction is 3x3):
+// Design (instruction-issue bound, no tensor cores: the largest contraction is 3x3):
 //  * one CTA per 16x16 tile, one thread per pixel, warps cover 8x4 pixel patches;
-//  * the tile's depth-sorted Gaussians are staged in shared memory in batches of 256 packed
-//    64-byte records (M = S^-1 R^T, gro = M (o - mu), colour, opacity) built once per Gaussian,
+//  * the tile's depth-sorted Gaussians are staged in shared memory in batches (192 records forward, 64 backward) of
+//    packed 64-byte records (M = S^-1 R^T, gro = M (o - mu), colour, opacity) built once per Gaussian,
 //    so no quaternion -> matrix work is repeated per tile or per pixel;
+//  * per warp, a ballot over the batch keeps the records whose screen-space box overlaps the warp's 8x4 patch;
 //  * per pair the response is -0.5 |u x gro|^2 / |u|^2 with u = M d (same value as the normalised
 //    cross-product form), preceded by an exp-free conservative rejection test;
 //  * backward: every (warp, Gaussian) contribution is 16 numbers that are LINEAR in the per-pixel
-//    terms (sum v_u (x) d, sum v_gro, v_rgb, v_opacity). They are summed with a 16-shuffle halving
-//    butterfly, combined across the 8 warps in shared memory, and leave the CTA as four float4
-//    reductions per (tile, Gaussian). The nonlinear quaternion / scale VJP runs once per Gaussian in
-//    the epilogue instead of once per pixel pair.
+//    terms (sum v_u (x) d, sum v_gro, v_rgb, v_opacity). They are summed over the warp by a transpose through
+//    padded shared-memory rows (warp_reduce16), combined across the 8 warps by shared-memory atomics, and leave the
+//    CTA as four float4 reductions per (tile, Gaussian). The nonlinear quaternion / scale VJP runs once per Gaussian
+//    in the epilogue instead of once per pixel pair.
 #include "gsmath.cuh"
 #include "raster.cuh"
 

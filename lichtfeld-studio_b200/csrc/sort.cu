@@ -401,7 +401,7 @@ int exclusive_scan_gather(const int32_t* src, const uint32_t* idx, int64_t n, in
         return LFS_OK;
     }
     int nb = (int)((n + kTile - 1) / kTile);
-    if (nb > kScanBlocks) nb = kScanBlocks;
+    nb = min(nb, min(4 * num_sms(), kScanBlocks));
     const int64_t chunk = (n + nb - 1) / nb;
     LFS_TIMED("exclusive_scan", st);
     scan_reduce_kernel<<<nb, kThreads, 0, st>>>(src, idx, n, chunk, s.block_sums);
@@ -416,7 +416,7 @@ int radix_sort_pairs(uint32_t* keys[2], uint32_t* vals[2], const int32_t* n_dev,
     const int passes = (key_bits + 7) / 8;
     const int bits = (key_bits + passes - 1) / passes;
     int nb = (int)((n_max + kTile - 1) / kTile);
-    if (nb > kRadixBlocks) nb = kRadixBlocks;
+    nb = min(nb, min(4 * num_sms(), kRadixBlocks));
     int cur = 0;
     LFS_TIMED(key_bits == 32 ? "radix_sort_depth" : "radix_sort_tile", st);
     for (int p = 0; p < passes; ++p) {

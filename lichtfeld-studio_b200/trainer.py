@@ -223,6 +223,16 @@ class Rasterizer:
         call("lfs_render_backward", C.byref(self.cfg), C.byref(p), ptr(background), ptr(self.alpha), ptr(v_render), ptr(v_alpha),
              C.byref(g), flags, ptr(self.ws), self.ws.numel(), _stream())
 
+    def background_gradient(self, v_render: torch.Tensor) -> torch.Tensor:
+        """v_bg_color of the autograd node (rasterizer_autograd.cpp:206-209): sum over pixels of v_render (1 - alpha) per
+        channel, for trainers whose background colour is a parameter. Uses the alpha of the last forward."""
+        if not hasattr(self, "_bg_ws"):
+            self._bg_ws = torch.empty(4, dtype=torch.float64, device=self.render.device)
+        out = torch.empty(self.channels, dtype=torch.float32, device=self.render.device)
+        call("lfs_background_gradient", self.H, self.W, self.channels, ptr(v_render), ptr(self.alpha), ptr(out), ptr(self._bg_ws),
+             self._bg_ws.numel() * 8, _stream())
+        return out
+
     def backward_adam(self, v_render: torch.Tensor, exp_avg: SplatData, exp_avg_sq: SplatData, lrs, step_count: int,
                       background: torch.Tensor | None = None, v_alpha: torch.Tensor | None = None, beta1=0.9, beta2=0.999,
                       eps=1e-15, skip_shN=False, grad_scale=1.0):

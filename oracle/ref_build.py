@@ -89,6 +89,7 @@ def _nvcc() -> str:
 def _includes(root: Path) -> list[str]:
     from torch.utils import cpp_extension as ce
     inc = [str(HERE / "glm_standin")] + [str(root / d) for d in INCLUDE_DIRS] + ce.include_paths()
+    inc += [str(HERE.parent / "lichtfeld-studio_b200" / "csrc")]   # gsplat_ops_pybind.inc, the bindings shared with the operator shim
     inc += [sysconfig.get_paths()["include"], "/usr/local/cuda/include"]
     return [f"-I{p}" for p in inc]
 
@@ -130,7 +131,8 @@ def build(force: bool = False, verbose: bool = False) -> Path | None:
     harness = HERE / "ref_harness.cpp"
     obj = OBJ_DIR / "ref_harness.o"
     objs.append(obj)
-    if force or _stale(obj, [harness] + standin_headers):
+    shared_bindings = HERE.parent / "lichtfeld-studio_b200" / "csrc" / "gsplat_ops_pybind.inc"
+    if force or _stale(obj, [harness, shared_bindings] + standin_headers):
         jobs.append(["g++"] + CXX_FLAGS + defs + inc + ["-c", str(harness), "-o", str(obj)])
     if jobs:
         workers = max(1, min(len(jobs), (os.cpu_count() or 4)))

@@ -301,88 +301,8 @@ namespace {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "The reference's own CUDA build of the training-step path (test infrastructure / timed comparator)";
 
-    // ---- gsplat/Ops.h, one binding per operator; enums travel as ints, UT parameters take their defaults
-    m.def("spherical_harmonics_fwd", [](int degrees_to_use, Tensor dirs, Tensor coeffs, OptTensor masks) {
-        return gsplat::spherical_harmonics_fwd(degrees_to_use, dirs, coeffs, masks);
-    });
-    m.def("spherical_harmonics_bwd", [](int K, int degrees_to_use, Tensor dirs, Tensor coeffs, OptTensor masks,
-                                        Tensor v_colors, bool compute_v_dirs) {
-        return gsplat::spherical_harmonics_bwd(K, degrees_to_use, dirs, coeffs, masks, v_colors, compute_v_dirs);
-    });
-    m.def("intersect_tile", [](Tensor means2d, Tensor radii, Tensor depths, OptTensor camera_ids, OptTensor gaussian_ids,
-                               int C, int tile_size, int tile_width, int tile_height, bool sort) {
-        return gsplat::intersect_tile(means2d, radii, depths, camera_ids, gaussian_ids, C, tile_size, tile_width,
-                                      tile_height, sort);
-    });
-    m.def("intersect_offset", [](Tensor isect_ids, int C, int tile_width, int tile_height) {
-        return gsplat::intersect_offset(isect_ids, C, tile_width, tile_height);
-    });
-    m.def("quats_to_rotmats", [](Tensor quats) { return gsplat::quats_to_rotmats(quats); });
-    m.def("relocation", [](Tensor opacities, Tensor scales, Tensor ratios, Tensor binoms, int n_max) {
-        return gsplat::relocation(opacities, scales, ratios, binoms, n_max);
-    });
-    m.def("add_noise", [](Tensor raw_opacities, Tensor raw_scales, Tensor raw_quats, Tensor noise, Tensor means,
-                          float current_lr) {
-        gsplat::add_noise(raw_opacities, raw_scales, raw_quats, noise, means, current_lr);
-    });
-    m.def("projection_ut_3dgs_fused",
-          [](Tensor means, Tensor quats, Tensor scales, OptTensor opacities, Tensor viewmats0, OptTensor viewmats1, Tensor Ks,
-             int image_width, int image_height, float eps2d, float near_plane, float far_plane, float radius_clip,
-             bool calc_compensations, int camera_model, py::object ut_params, int rs_type, OptTensor radial, OptTensor tangential,
-             OptTensor thin_prism) {
-              return gsplat::projection_ut_3dgs_fused(
-                  means, quats, scales, opacities, viewmats0, viewmats1, Ks, image_width, image_height, eps2d, near_plane,
-                  far_plane, radius_clip, calc_compensations, static_cast<gsplat::CameraModelType>(camera_model),
-                  ut_from(ut_params), static_cast<ShutterType>(rs_type), radial, tangential, thin_prism);
-          });
-    m.def("rasterize_to_pixels_from_world_3dgs_fwd",
-          [](Tensor means, Tensor quats, Tensor scales, Tensor colors, Tensor opacities, OptTensor backgrounds, OptTensor masks,
-             int image_width, int image_height, int tile_size, Tensor viewmats0, OptTensor viewmats1, Tensor Ks,
-             int camera_model, py::object ut_params, int rs_type, OptTensor radial, OptTensor tangential, OptTensor thin_prism,
-             Tensor tile_offsets, Tensor flatten_ids) {
-              return gsplat::rasterize_to_pixels_from_world_3dgs_fwd(
-                  means, quats, scales, colors, opacities, backgrounds, masks, image_width, image_height, tile_size,
-                  viewmats0, viewmats1, Ks, static_cast<gsplat::CameraModelType>(camera_model), ut_from(ut_params),
-                  static_cast<ShutterType>(rs_type), radial, tangential, thin_prism, tile_offsets, flatten_ids);
-          });
-    m.def("rasterize_to_pixels_from_world_3dgs_bwd",
-          [](Tensor means, Tensor quats, Tensor scales, Tensor colors, Tensor opacities, OptTensor backgrounds, OptTensor masks,
-             int image_width, int image_height, int tile_size, Tensor viewmats0, OptTensor viewmats1, Tensor Ks,
-             int camera_model, py::object ut_params, int rs_type, OptTensor radial, OptTensor tangential, OptTensor thin_prism,
-             Tensor tile_offsets, Tensor flatten_ids, Tensor render_alphas, Tensor last_ids, Tensor v_render_colors, Tensor v_render_alphas) {
-              return gsplat::rasterize_to_pixels_from_world_3dgs_bwd(
-                  means, quats, scales, colors, opacities, backgrounds, masks, image_width, image_height, tile_size,
-                  viewmats0, viewmats1, Ks, static_cast<gsplat::CameraModelType>(camera_model), ut_from(ut_params),
-                  static_cast<ShutterType>(rs_type), radial, tangential, thin_prism, tile_offsets, flatten_ids,
-                  render_alphas, last_ids, v_render_colors, v_render_alphas);
-          });
-    m.def("rasterize_from_world_with_sh_fwd",
-          [](Tensor means, Tensor quats, Tensor scales, Tensor opacities, Tensor sh_coeffs, int sh_degree, OptTensor backgrounds,
-             OptTensor masks, int image_width, int image_height, int tile_size, Tensor viewmats0, OptTensor viewmats1,
-             Tensor Ks, int camera_model, float eps2d, float near_plane, float far_plane, float radius_clip,
-             float scaling_modifier, bool calc_compensations, int render_mode, py::object ut_params, int rs_type, OptTensor radial,
-             OptTensor tangential, OptTensor thin_prism) {
-              return gsplat::rasterize_from_world_with_sh_fwd(
-                  means, quats, scales, opacities, sh_coeffs, sh_degree, backgrounds, masks, image_width, image_height,
-                  tile_size, viewmats0, viewmats1, Ks, static_cast<gsplat::CameraModelType>(camera_model), eps2d,
-                  near_plane, far_plane, radius_clip, scaling_modifier, calc_compensations, render_mode, ut_from(ut_params),
-                  static_cast<ShutterType>(rs_type), radial, tangential, thin_prism);
-          });
-    m.def("rasterize_from_world_with_sh_bwd",
-          [](Tensor means, Tensor quats, Tensor scales, Tensor opacities, Tensor sh_coeffs, int sh_degree, OptTensor backgrounds,
-             OptTensor masks, int image_width, int image_height, int tile_size, Tensor viewmats0, OptTensor viewmats1,
-             Tensor Ks, int camera_model, float eps2d, float near_plane, float far_plane, float radius_clip,
-             float scaling_modifier, bool calc_compensations, int render_mode, py::object ut_params, int rs_type, OptTensor radial,
-             OptTensor tangential, OptTensor thin_prism, Tensor render_alphas, Tensor last_ids, Tensor tile_offsets,
-             Tensor flatten_ids, Tensor colors, Tensor radii, Tensor means2d, Tensor depths, Tensor compensations,
-             Tensor v_render_colors, Tensor v_render_alphas) {
-              return gsplat::rasterize_from_world_with_sh_bwd(
-                  means, quats, scales, opacities, sh_coeffs, sh_degree, backgrounds, masks, image_width, image_height,
-                  tile_size, viewmats0, viewmats1, Ks, static_cast<gsplat::CameraModelType>(camera_model), eps2d,
-                  near_plane, far_plane, radius_clip, scaling_modifier, calc_compensations, render_mode, ut_from(ut_params),
-                  static_cast<ShutterType>(rs_type), radial, tangential, thin_prism, render_alphas, last_ids, tile_offsets,
-                  flatten_ids, colors, radii, means2d, depths, compensations, v_render_colors, v_render_alphas);
-          });
+    // ---- gsplat/Ops.h, one binding per operator (the same bindings the operator shim of this repository exposes)
+#include "gsplat_ops_pybind.inc"
 
     // ---- loss, optimizer, regularizers, EWA rasterizer
     m.def("fusedssim", [](float C1, float C2, Tensor img1, Tensor img2, bool train) {

@@ -131,3 +131,28 @@ def test_expected_depth_of_an_opaque_wall_is_its_distance(pkg, synth):
     zc = d[solid]
     # the depth of a Gaussian is its centre's camera z (4 on the wall)
     assert np.abs(zc - 4.0).max() < 1e-3
+
+
+def test_background_gradient_matches_the_autograd_node(pkg, synth):
+    """v_bg_color = (v_render_colors * (1 - render_alphas)).sum over the image (rasterizer_autograd.cpp:206-209), against the
+    same expression in torch (float64 sum) and against a finite difference of the render in the background colour."""
+    tr = pkg.trainer
+    n, W, H, deg = 4000, 90, 70, 1
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=8)
+    model = tr.SplatData(n, 4, DEV).load(P)
+    for mode, ch in ((tr.RENDER_RGB, 3), (tr.RENDER_RGB_D, 4)):
+        rast = tr.Rasterizer(model, W, H, deg, render_mode=mode)
+        bg = torch.tensor([0.3, 0.6, 0.1, 0.0][:ch], device=DEV)
+        cam = tr.Camera(T(vm), T(K), W, H)
+        out = rast.forward(cam, bg)
+        gen = torch.Generator(device=DEV).manual_seed(ch)
+        v = torch.randn((H, W, ch), generator=gen, device=DEV)
+        got = rast.background_gradient(v)
+        want = (v.double() * (1.0 - out.alpha.double())).sum((0, 1))
+        assert torch.allclose(got.double(), want, rtol=1e-5, atol=1e-5)
+        # d(sum v * render)/d(bg_0) by a central difference (the render is linear in the background)
+        r0 = out.render.clone()
+        bg2 = bg.clone(); bg2[0] += 0.5
+        r1 = rast.forward(cam, bg2).render
+        fd = float(((r1 - r0).double() * v.double()).sum() / 0.5)
+        assert abs(fd - float(want[0])) < 1e-3 * max(1.0, abs(float(want[0])))

@@ -55,6 +55,24 @@ def test_noalloc_matches_workspace_entry_point_twice(pkg):
         assert (out[0][n_dead:] == -1).all() and (out[1][n_alive:] == -1).all()
 
 
+def test_noalloc_at_its_size_limit_and_with_no_gaussians(pkg):
+    """N equal to the built-in maximum is served; N = 0 writes the counts {0, 0} and touches nothing else."""
+    rng = np.random.default_rng(3)
+    n = 262144
+    op = (rng.normal(size=(n, 1)) - 1).astype(np.float32)
+    op[::7] = -7.0
+    rot = rng.normal(size=(n, 4)).astype(np.float32)
+    t_op, t_rot = torch.from_numpy(op).to(DEV), torch.from_numpy(rot).to(DEV)
+    ref = _classify(pkg, "workspace", t_op, t_rot, 0.005)
+    out = _classify(pkg, "noalloc", t_op, t_rot, 0.005)
+    n_dead, n_alive = ref[3]
+    assert n_dead + n_alive == n and np.array_equal(out[3], ref[3])
+    assert np.array_equal(out[0][:n_dead], ref[0][:n_dead]) and np.array_equal(out[1][:n_alive], ref[1][:n_alive])
+    empty_op, empty_rot = torch.empty((0, 1), device=DEV), torch.empty((0, 4), device=DEV)
+    out = _classify(pkg, "noalloc", empty_op, empty_rot, 0.005)
+    assert out[3].tolist() == [0, 0]
+
+
 def test_noalloc_rejects_sizes_beyond_its_scratch(pkg):
     capi = pkg._capi
     n = 262144 + 1
