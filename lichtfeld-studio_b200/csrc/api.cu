@@ -158,7 +158,10 @@ int check_cfg(const lfs_render_config* cfg) {
     LFS_REQUIRE(cfg->tile_size == 16, "tile_size must be 16");
     LFS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 4, "sh_degree must be in [0,4]");
     LFS_REQUIRE(cfg->sh_coeffs >= (cfg->sh_degree + 1) * (cfg->sh_degree + 1), "not enough SH coefficients for the degree");
-    LFS_REQUIRE(cfg->camera_model == LFS_PINHOLE || cfg->camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
+    LFS_REQUIRE(cfg->camera_model == LFS_PINHOLE || cfg->camera_model == LFS_FISHEYE || cfg->camera_model == LFS_EQUIRECTANGULAR,
+                "camera model must be PINHOLE, FISHEYE or EQUIRECTANGULAR");
+    LFS_REQUIRE(cfg->camera_model != LFS_EQUIRECTANGULAR || (cfg->shutter == 0 && !cfg->viewmat_end && !cfg->radial_coeffs),
+                "the equirectangular model has a global shutter and no distortion coefficients");
     LFS_REQUIRE(cfg->isect_capacity >= 0 && cfg->isect_capacity < ((int64_t)1 << 31), "isect_capacity out of range");
     LFS_REQUIRE(cfg->render_mode >= LFS_RENDER_RGB && cfg->render_mode <= LFS_RENDER_RGB_ED, "render_mode must be in [0,4]");
     LFS_REQUIRE(cfg->scaling_modifier >= 0.f, "scaling_modifier must be positive (0 = 1.0)");
@@ -200,7 +203,10 @@ int lfs_projection_ut_3dgs_fused(int C, int N, const float* means, const float* 
                                  int32_t* radii, float* means2d, float* depths, float* conics,
                                  float* compensations, void* stream) {
     LFS_REQUIRE(C >= 0 && N >= 0 && W > 0 && H > 0, "bad sizes");
-    LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
+    LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE || camera_model == LFS_EQUIRECTANGULAR,
+                "camera model must be PINHOLE, FISHEYE or EQUIRECTANGULAR");
+    LFS_REQUIRE(camera_model != LFS_EQUIRECTANGULAR || (rs_type == LFS_SHUTTER_GLOBAL && !viewmats1 && !radial_coeffs),
+                "the equirectangular model has a global shutter and no distortion coefficients");
     if ((int64_t)C * N == 0) return LFS_OK;
     LFS_REQUIRE(means && quats && scales && viewmats0 && Ks && radii && means2d && depths && conics, "null pointer");
     LFS_REQUIRE(aligned16(quats), "quats must be 16-byte aligned");
@@ -301,7 +307,8 @@ static int raster_common(int N, int64_t n_isects, int channels, int W, int H, in
     LFS_REQUIRE(N >= 0 && n_isects >= 0 && n_isects < ((int64_t)1 << 31) && W > 0 && H > 0, "bad sizes");
     LFS_REQUIRE(channels == 1 || channels == 3 || channels == 4, "colours must have 1, 3 or 4 channels");
     LFS_REQUIRE(tile_size == 16, "tile_size must be 16");
-    LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE, "camera model must be PINHOLE or FISHEYE");
+    LFS_REQUIRE(camera_model == LFS_PINHOLE || camera_model == LFS_FISHEYE || camera_model == LFS_EQUIRECTANGULAR,
+                "camera model must be PINHOLE, FISHEYE or EQUIRECTANGULAR");
     LFS_REQUIRE(workspace != nullptr, "null workspace");
     if (workspace_bytes < lfs_rasterize_workspace_bytes(N)) { set_error("rasterize: workspace too small"); return LFS_ECAPACITY; }
     return LFS_OK;
@@ -331,6 +338,8 @@ int lfs_rasterize_to_pixels_from_world_3dgs_fwd(int N, int64_t n_isects, int cha
                              cam, S(stream));
     const int eff_model = effective_model(camera_model, radial_coeffs, tangential_coeffs, thin_prism_coeffs);
     const int rolling = (rs_type != LFS_SHUTTER_GLOBAL || viewmat1 != nullptr) ? 1 : 0;
+    LFS_REQUIRE(camera_model != LFS_EQUIRECTANGULAR || (!rolling && !radial_coeffs),
+                "the equirectangular model has a global shutter and no distortion coefficients");
     if (rc != LFS_OK) return rc;
     rc = launch_pack_records(N, means, quats, scales, colors, channels, opacities, cam, records, bounds, nullptr, nullptr, S(stream));
     if (rc != LFS_OK) return rc;
@@ -368,6 +377,8 @@ int lfs_rasterize_to_pixels_from_world_3dgs_bwd(int N, int64_t n_isects, int cha
                              cam, S(stream));
     const int eff_model = effective_model(camera_model, radial_coeffs, tangential_coeffs, thin_prism_coeffs);
     const int rolling = (rs_type != LFS_SHUTTER_GLOBAL || viewmat1 != nullptr) ? 1 : 0;
+    LFS_REQUIRE(camera_model != LFS_EQUIRECTANGULAR || (!rolling && !radial_coeffs),
+                "the equirectangular model has a global shutter and no distortion coefficients");
     if (rc != LFS_OK) return rc;
     rc = launch_pack_records(N, means, quats, scales, colors, channels, opacities, cam, records, bounds,
                              reinterpret_cast<float4*>(accum), accum_extra, S(stream));

@@ -125,6 +125,15 @@ __device__ __forceinline__ void opencv_distortion(const CamDev& c, float u, floa
 template <int MODEL>
 __device__ __forceinline__ bool cam_point_to_image(const CamDev& c, f3 p, float margin, float& ox, float& oy) {
     ox = 0.f; oy = 0.f;
+    if (MODEL == LFS_EQUIRECTANGULAR) {
+        // gsplat/Cameras.cuh:1013-1026: azimuth / elevation of the camera-space point, the whole sphere on the image; the
+        // reference computes the bounds check and then reports every point valid, behind the camera included
+        const float azimuth = atan2f(p.x, p.z);
+        const float elevation = asinf(p.y / sqrtf(p.x * p.x + p.y * p.y + p.z * p.z));
+        ox = (azimuth / (2.0f * 3.14159265358979323846f) + 0.5f) * (float)c.W;
+        oy = (elevation / 3.14159265358979323846f + 0.5f) * (float)c.H;
+        return true;
+    }
     if (p.z <= 0.f) return false;
     if (MODEL == LFS_PINHOLE_OPENCV) {
         // gsplat/Cameras.cuh:535-597: points whose radial factor comes close to flipping are invalid
@@ -156,6 +165,18 @@ __device__ __forceinline__ bool cam_point_to_image(const CamDev& c, f3 p, float 
 // Pixel centre -> unit camera ray. Fisheye inverts the forward polynomial with up to 20 Newton steps.
 template <int MODEL>
 __device__ __forceinline__ bool image_to_cam_ray(const CamDev& c, float px, float py, f3& ray) {
+    if (MODEL == LFS_EQUIRECTANGULAR) {
+        // gsplat/Cameras.cuh:1028-1037: the angles and the trigonometry are double in the reference (2.0 * PI * ...)
+        const double kPi = (double)3.14159265358979323846f;
+        const double azimuth = 2.0 * kPi * (px / (float)c.W - 0.5);
+        const double elevation = kPi * (py / (float)c.H - 0.5);
+        const float dx = (float)(cos(elevation) * sin(azimuth));
+        const float dy = (float)sin(elevation);
+        const float dz = (float)(cos(azimuth) * cos(elevation));
+        const float len = sqrtf(dx * dx + dy * dy + dz * dz);
+        ray = {dx / len, dy / len, dz / len};
+        return true;
+    }
     const float ux = (px - c.cx) / c.fx;
     const float uy = (py - c.cy) / c.fy;
     if (MODEL == LFS_PINHOLE_OPENCV) {

@@ -8,7 +8,7 @@
 // (gsplat/Rasterization.cpp:326-466, :527-641).
 //
 // Differences that a caller can observe: packed mode (camera_ids / gaussian_ids) and compute_v_dirs raise, like the
-// features the reference's trainer never requests; ORTHO / EQUIRECTANGULAR cameras raise; outputs the reference leaves
+// features the reference's trainer never requests; the ORTHO camera raises; outputs the reference leaves
 // uninitialised for culled Gaussians are left uninitialised here as well.
 #ifdef LFS_SHIM_USE_REFERENCE_HEADERS
 #include "Ops.h"
@@ -66,11 +66,17 @@ namespace gsplat {
         Coeffs camera_args(CameraModelType camera_model, ShutterType rs_type, const at::optional<at::Tensor>& viewmats1,
                            const at::optional<at::Tensor>& radial, const at::optional<at::Tensor>& tangential,
                            const at::optional<at::Tensor>& thin_prism) {
-            (void)rs_type;
             if (viewmats1.has_value() && viewmats1->defined()) check_input(*viewmats1, "viewmats1");
-            TORCH_CHECK(camera_model == CameraModelType::PINHOLE || camera_model == CameraModelType::FISHEYE,
-                        "camera model must be PINHOLE or FISHEYE");
+            TORCH_CHECK(camera_model == CameraModelType::PINHOLE || camera_model == CameraModelType::FISHEYE ||
+                            camera_model == CameraModelType::EQUIRECTANGULAR,
+                        "camera model must be PINHOLE, FISHEYE or EQUIRECTANGULAR");
             Coeffs c;
+            if (camera_model == CameraModelType::EQUIRECTANGULAR) {
+                TORCH_CHECK(rs_type == ShutterType::GLOBAL && fptr(viewmats1) == nullptr && fptr(radial) == nullptr &&
+                                fptr(tangential) == nullptr && fptr(thin_prism) == nullptr,
+                            "the equirectangular model has a global shutter and no distortion coefficients");
+                return c;
+            }
             if (camera_model == CameraModelType::PINHOLE) {
                 c.radial = widen(radial, 6);
                 c.tangential = widen(tangential, 2);

@@ -163,7 +163,8 @@ __device__ __forceinline__ bool project_gaussian(const CamDev& cam, const ProjPa
     // depth and culling with the centre-of-frame pose (the start pose for a global shutter)
     const f3 mean_c = RS ? quat_rotate(cam.qcw, cam.qcx, cam.qcy, cam.qcz, mean) + f3{cam.tcx, cam.tcy, cam.tcz}
                          : quat_rotate(cam.qw, cam.qx, cam.qy, cam.qz, mean) + f3{cam.tx, cam.ty, cam.tz};
-    if (mean_c.z < pp.near_plane || mean_c.z > pp.far_plane) return false;
+    // the equirectangular model sees the whole sphere: no near-plane cull (gsplat/ProjectionUT3DGSFused.cu:78)
+    if ((mean_c.z < pp.near_plane && MODEL != LFS_EQUIRECTANGULAR) || mean_c.z > pp.far_plane) return false;
     o.depth = mean_c.z;
 
     const float D = 3.0f;
@@ -310,6 +311,7 @@ int launch_projection_ut(int C, int N, const float* means, const float* quats, c
     switch (effective_model(model, radial, tangential, thin_prism)) {
         case LFS_PINHOLE: LFS_PROJ(LFS_PINHOLE); break;
         case LFS_PINHOLE_OPENCV: LFS_PROJ(LFS_PINHOLE_OPENCV); break;
+        case LFS_EQUIRECTANGULAR: LFS_PROJ(LFS_EQUIRECTANGULAR); break;
         default: LFS_PROJ(LFS_FISHEYE); break;
     }
 #undef LFS_PROJ
@@ -616,7 +618,7 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
 #define LFS_PACK_ATTR(MODEL)                                                                                        \
     cudaFuncSetAttribute(project_pack_kernel<MODEL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     cudaFuncSetAttribute(project_pack_kernel<MODEL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-        LFS_PACK_ATTR(LFS_PINHOLE); LFS_PACK_ATTR(LFS_FISHEYE); LFS_PACK_ATTR(LFS_PINHOLE_OPENCV);
+        LFS_PACK_ATTR(LFS_PINHOLE); LFS_PACK_ATTR(LFS_FISHEYE); LFS_PACK_ATTR(LFS_PINHOLE_OPENCV); LFS_PACK_ATTR(LFS_EQUIRECTANGULAR);
 #undef LFS_PACK_ATTR
     }
     LFS_TIMED("project_pack", st);
@@ -628,6 +630,7 @@ int launch_project_pack(int N, int K, int sh_degree, const lfs_splats& p, const 
     switch (model) {
         case LFS_PINHOLE: LFS_PACK(LFS_PINHOLE); break;
         case LFS_PINHOLE_OPENCV: LFS_PACK(LFS_PINHOLE_OPENCV); break;
+        case LFS_EQUIRECTANGULAR: LFS_PACK(LFS_EQUIRECTANGULAR); break;
         default: LFS_PACK(LFS_FISHEYE); break;
     }
 #undef LFS_PACK

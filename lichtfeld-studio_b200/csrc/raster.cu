@@ -970,6 +970,7 @@ int launch_raster_fwd(const RasterArgs& a, float* render, float* alphas, int32_t
     const bool extra = a.channels != 3;
     if (a.model == LFS_PINHOLE) { if (extra) LFS_FWD(LFS_PINHOLE, true); else LFS_FWD(LFS_PINHOLE, false); }
     else if (a.model == LFS_PINHOLE_OPENCV) { if (extra) LFS_FWD(LFS_PINHOLE_OPENCV, true); else LFS_FWD(LFS_PINHOLE_OPENCV, false); }
+    else if (a.model == LFS_EQUIRECTANGULAR) { if (extra) LFS_FWD3(LFS_EQUIRECTANGULAR, true, false); else LFS_FWD3(LFS_EQUIRECTANGULAR, false, false); }
     else { if (extra) LFS_FWD(LFS_FISHEYE, true); else LFS_FWD(LFS_FISHEYE, false); }
 #undef LFS_FWD3
 #undef LFS_FWD
@@ -999,6 +1000,7 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
         LFS_BWD_ATTR(LFS_FISHEYE, false, false); LFS_BWD_ATTR(LFS_FISHEYE, true, false); LFS_BWD_ATTR(LFS_FISHEYE, true, true);
         LFS_BWD_ATTR(LFS_PINHOLE_OPENCV, false, false); LFS_BWD_ATTR(LFS_PINHOLE_OPENCV, true, false);
         LFS_BWD_ATTR(LFS_PINHOLE_OPENCV, true, true);
+        LFS_BWD_ATTR(LFS_EQUIRECTANGULAR, false, false); LFS_BWD_ATTR(LFS_EQUIRECTANGULAR, true, false); LFS_BWD_ATTR(LFS_EQUIRECTANGULAR, true, true);
         attr_set = true;
     }
 #undef LFS_BWD_ATTR
@@ -1014,6 +1016,9 @@ int launch_raster_bwd(const RasterArgs& a, const float* render_alphas, const int
     } else if (a.model == LFS_PINHOLE_OPENCV) {
         if (!extra) LFS_BWD(LFS_PINHOLE_OPENCV, false, false); else if (!xgrad) LFS_BWD(LFS_PINHOLE_OPENCV, true, false);
         else LFS_BWD(LFS_PINHOLE_OPENCV, true, true);
+    } else if (a.model == LFS_EQUIRECTANGULAR) {
+        if (!extra) LFS_BWD4(LFS_EQUIRECTANGULAR, false, false, false); else if (!xgrad) LFS_BWD4(LFS_EQUIRECTANGULAR, true, false, false);
+        else LFS_BWD4(LFS_EQUIRECTANGULAR, true, true, false);
     } else {
         if (!extra) LFS_BWD(LFS_FISHEYE, false, false); else if (!xgrad) LFS_BWD(LFS_FISHEYE, true, false); else LFS_BWD(LFS_FISHEYE, true, true);
     }

@@ -41,8 +41,12 @@ def _only_global_pinhole_fisheye(camera_model, rs_type, viewmats1, tangential_co
         raise RuntimeError("rs_type must be a ShutterType")
     if viewmats1 is not None:
         _check_input(viewmats1, "viewmats1")
-    if camera_model not in (CameraModelType.PINHOLE, CameraModelType.FISHEYE):
-        raise RuntimeError("camera model must be PINHOLE or FISHEYE")
+    if camera_model not in (CameraModelType.PINHOLE, CameraModelType.FISHEYE, CameraModelType.EQUIRECTANGULAR):
+        raise RuntimeError("camera model must be PINHOLE, FISHEYE or EQUIRECTANGULAR")
+    if camera_model == CameraModelType.EQUIRECTANGULAR:
+        if int(rs_type) != 4 or viewmats1 is not None or radial_coeffs is not None or tangential_coeffs is not None or thin_prism_coeffs is not None:
+            raise RuntimeError("the equirectangular model has a global shutter and no distortion coefficients")
+        return None, None, None
     if camera_model == CameraModelType.FISHEYE and (tangential_coeffs is not None or thin_prism_coeffs is not None):
         raise RuntimeError("tangential / thin-prism coefficients belong to the pinhole model")
 

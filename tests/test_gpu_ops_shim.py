@@ -115,5 +115,5 @@ def test_shim_operators_equal_the_ctypes_mirror(pkg, synth, R, shim):
     # error behaviour: the reference's TORCH_CHECKs surface as RuntimeError
     with pytest.raises(RuntimeError, match="CUDA"):
         shim.quats_to_rotmats(torch.zeros(4, 4))
-    with pytest.raises(RuntimeError, match="PINHOLE or FISHEYE"):
+    with pytest.raises(RuntimeError, match="PINHOLE, FISHEYE or EQUIRECTANGULAR"):
         shim.projection_ut_3dgs_fused(means, q, s, o, vmt, None, Kt, W, H, 0.3, 0.01, 1e4, 0.0, True, 1, None, 4, None, None, None)

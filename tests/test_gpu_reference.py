@@ -299,3 +299,59 @@ def test_ewa_step_against_reference(pkg, synth, R):
         a = grads.tensor(name).cpu().numpy()
         if a.size:
             assert rel_l2(a, r["grad_" + name]) < 1e-3, name
+
+
+def test_equirectangular_camera_against_reference(pkg, synth, R, ref):
+    """CameraModelType::EQUIRECTANGULAR (gsplat/Cameras.cuh:1003-1039): the whole sphere on a 2:1 image, no near-plane cull,
+    Gaussians behind the camera carry a negative depth whose bit pattern sorts after every positive one
+    (gsplat/IntersectTile.cu:96-98). Projection, lists, forward image and the backward of the operator pair against the
+    reference itself, with the camera INSIDE the scene so that every direction is populated."""
+    ops = pkg.ops
+    n, W, H, deg = 20000, 256, 128, 2
+    P = synth.make_gaussians(n, 6, "cube", deg)
+    P["scaling_raw"] = (P["scaling_raw"] + np.float32(0.7)).astype(np.float32)
+    means, q, s, o, sh = R.activated(P)
+    vm = np.eye(4, dtype=np.float32)
+    vm[:3, 3] = [0.05, -0.02, 0.1]                      # camera close to the centre of the cube of Gaussians
+    K = synth.intrinsics(100.0, 100.0, W / 2, H / 2)    # unused by the model, passed like the trainer does
+    vmt, Kt = T(vm[None]), T(K[None])
+    a = ref.projection_ut_3dgs_fused(means, q, s, o, vmt, None, Kt, W, H, 0.3, 0.01, 1e4, 0.0, False, 3, None, 4, None, None, None)
+    b = ops.projection_ut_3dgs_fused(means, q, s, o, vmt, None, Kt, W, H, 0.3, 0.01, 1e4, 0.0, False, 3)
+    va, vb = (a[0] > 0).all(-1), (b[0] > 0).all(-1)
+    assert int(va.sum()) > 5000 and int((a[2][va] < 0).sum()) > 1000          # behind the camera too
+    assert int((va != vb).sum()) <= n // 1000 and int((a[0] != b[0]).any(-1).sum()) <= n // 500
+    both = va & vb
+    assert float((a[1][both] - b[1][both]).abs().max()) < 0.05
+    assert torch.equal(a[2][both], b[2][both])
+    # lists from the reference's projection: bit-exact, negative depths included
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    ia = ref.intersect_tile(a[1], a[0], a[2], None, None, 1, 16, tw, th, True)
+    ib = ops.intersect_tile(a[1], a[0], a[2], None, None, 1, 16, tw, th, True)
+    assert all(torch.equal(x, y) for x, y in zip(ia, ib)) and ia[2].numel() > 20000
+    oa = ref.intersect_offset(ia[1], 1, tw, th)
+    assert torch.equal(oa, ops.intersect_offset(ia[1], 1, tw, th))
+    # rasterizer pair on identical inputs
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    colors = torch.rand((1, n, 3), generator=gen, device=DEV)
+    common = (means, q, s, colors, o[None].contiguous(), T(np.array([[0.1, 0.2, 0.3]], np.float32)), None, W, H, 16, vmt, None, Kt, 3,
+              None, 4, None, None, None, oa, ia[2])
+    fa = ref.rasterize_to_pixels_from_world_3dgs_fwd(*common)
+    fb = ops.rasterize_to_pixels_from_world_3dgs_fwd(*common)
+    d = (fa[0] - fb[0]).abs().amax(-1)
+    assert int((d > 1e-4).sum()) <= 8 and float(torch.quantile(d.flatten(), 0.9995)) < 1e-4, float(d.max())
+    vr = torch.randn(fa[0].shape, generator=gen, device=DEV)
+    va_ = torch.randn(fa[1].shape, generator=gen, device=DEV) * 0.1
+    ba = ref.rasterize_to_pixels_from_world_3dgs_bwd(*common, fa[1], fa[2], vr, va_)
+    bb = ops.rasterize_to_pixels_from_world_3dgs_bwd(*common, fa[1], fa[2], vr, va_)
+    for name, x, y in zip(("v_means", "v_quats", "v_scales", "v_colors", "v_opacities"), ba, bb):
+        assert rel_l2(y.cpu().numpy(), x.cpu().numpy()) < 1e-3, name
+    # the fused path from raw parameters against the reference's rasterize()
+    tr = pkg.trainer
+    t = R.make_trainer(P, [0.0] * 6, deg)
+    bg = T(np.array([0.1, 0.2, 0.3], np.float32))
+    rr = t.render_no_grad(True, vmt, Kt, W, H, bg, 3)
+    model = tr.SplatData(n, (deg + 1) ** 2, DEV).load(P)
+    rast = tr.Rasterizer(model, W, H, deg, camera_model=3)
+    out = rast.forward(tr.Camera(T(vm), T(K), W, H, camera_model=3), bg)
+    d = (out.image.permute(2, 0, 1).clamp(0, 1) - rr.image).abs().amax(0)
+    assert int((d > 1e-4).sum()) <= 40 and float(torch.quantile(d.flatten(), 0.998)) < 1e-4, float(d.max())
