@@ -169,6 +169,27 @@ int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, 
                                    double beta1, double beta2, double eps, int64_t step_count, float grad_scale,
                                    int ctas_per_sm, void* stream);
 
+/* Ordering between the ranks of a data-parallel step by flags in peer-mapped memory, with bounded waits (no counterpart
+ * in the reference). Every rank owns a flag array of LFS_DP_FLAG_WORDS int32 (zero-initialised, mapped on every peer):
+ * word [slot * LFS_DP_MAX_WORLD + r] is written by rank r only. lfs_dp_signal, enqueued after a producer kernel, stores
+ * `value` (a step number that only grows) into this rank's word of slot `slot` in EVERY rank's array (peer_flags: host
+ * array of `world` device pointers indexed by rank). lfs_dp_wait, enqueued before a consumer kernel, spins on the local
+ * array until all `world` words of the slot have reached `value`, for at most timeout_ns nanoseconds; when the time runs
+ * out it sets status[0] = 1, status[1] = bit mask of the ranks that were missing, status[2] = slot, status[3] = value
+ * (device int32[4], zeroed by the caller) and returns, so a rank that stopped stepping shows up as a status word, never
+ * as a hung stream. The kernels that follow then run on incomplete data: the host must read the status before it trusts
+ * the step. */
+#define LFS_DP_MAX_WORLD 16
+#define LFS_DP_FLAG_SLOTS 8
+#define LFS_DP_FLAG_WORDS (LFS_DP_MAX_WORLD * LFS_DP_FLAG_SLOTS)
+int lfs_dp_signal(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, void* stream);
+int lfs_dp_wait(int world, const int32_t* flags, int slot, int32_t value, uint64_t timeout_ns, int32_t* status_dev, void* stream);
+/* lfs_dp_signal followed by lfs_dp_wait on this rank's own array (peer_flags[own_rank]) in ONE launch: the rendezvous of the
+ * data-parallel step ("no rank goes on before every rank got here"). status[2..3] keep the slot and value of the first wait
+ * that ran out. */
+int lfs_dp_barrier(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, uint64_t timeout_ns,
+                   int32_t* status_dev, void* stream);
+
 /* gsplat/Ops.h:50-57 relocation -> gsplat/RelocationCUDA.cu:12. */
 int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms,
                    int n_max, float* new_opacities, float* new_scales, void* stream);

@@ -11,6 +11,8 @@ LIB_PATH = _HERE / "liblfs_b200.so"
 
 LFS_OK, LFS_EINVAL, LFS_ECAPACITY, LFS_ECUDA, LFS_EUNSUPPORTED = 0, -1, -2, -3, -4
 PINHOLE, ORTHO, FISHEYE, EQUIRECTANGULAR = 0, 1, 2, 3
+LFS_DP_MAX_WORLD, LFS_DP_FLAG_SLOTS = 16, 8
+LFS_DP_FLAG_WORDS = LFS_DP_MAX_WORLD * LFS_DP_FLAG_SLOTS
 
 
 class UTParams(C.Structure):
@@ -110,6 +112,9 @@ _SIGNATURES = {
     "lfs_adam_step_segments": [i32, C.POINTER(AdamSegment), C.c_double, C.c_double, C.c_double, i64, f32, i32, vp],
     "lfs_dp_reduce_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, C.POINTER(DpSegment), C.c_double,
                                      C.c_double, C.c_double, i64, f32, i32, vp],
+    "lfs_dp_signal": [i32, C.POINTER(C.c_void_p), i32, i32, i32, vp],
+    "lfs_dp_wait": [i32, vp, i32, i32, C.c_uint64, vp, vp],
+    "lfs_dp_barrier": [i32, C.POINTER(C.c_void_p), i32, i32, i32, C.c_uint64, vp, vp],
     "lfs_dp_sh_rank1_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, i32, i32, i64, i64, vp, vp, f32,
                                        C.c_double, C.c_double, C.c_double, i64, f32, i32, vp],
     "lfs_mcmc_classify": [i32, vp, vp, f32, vp, vp, vp, vp, vp, sz, vp],

@@ -583,6 +583,32 @@ int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, 
     return launch_dp_sh_rank1(sh_coeffs, sh_degree, A, ctas_per_sm, S_(stream));
 }
 
+int lfs_dp_signal(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, void* stream) {
+    LFS_REQUIRE(world >= 1 && world <= LFS_DP_MAX_WORLD && own_rank >= 0 && own_rank < world, "bad world / rank");
+    LFS_REQUIRE(slot >= 0 && slot < LFS_DP_FLAG_SLOTS, "bad slot");
+    LFS_REQUIRE(peer_flags != nullptr, "null pointer");
+    for (int i = 0; i < world; ++i) LFS_REQUIRE(peer_flags[i] != nullptr, "null peer flag array");
+    return launch_dp_signal(world, peer_flags, own_rank, slot, value, S(stream));
+}
+
+int lfs_dp_wait(int world, const int32_t* flags, int slot, int32_t value, uint64_t timeout_ns, int32_t* status_dev, void* stream) {
+    LFS_REQUIRE(world >= 1 && world <= LFS_DP_MAX_WORLD, "bad world");
+    LFS_REQUIRE(slot >= 0 && slot < LFS_DP_FLAG_SLOTS, "bad slot");
+    LFS_REQUIRE(flags && status_dev, "null pointer");
+    LFS_REQUIRE(timeout_ns > 0 && timeout_ns <= 60ull * 1000000000ull, "timeout must be in (0, 60 s]");
+    return launch_dp_wait(world, flags, slot, value, timeout_ns, status_dev, S(stream));
+}
+
+int lfs_dp_barrier(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, uint64_t timeout_ns,
+                   int32_t* status_dev, void* stream) {
+    LFS_REQUIRE(world >= 1 && world <= LFS_DP_MAX_WORLD && own_rank >= 0 && own_rank < world, "bad world / rank");
+    LFS_REQUIRE(slot >= 0 && slot < LFS_DP_FLAG_SLOTS, "bad slot");
+    LFS_REQUIRE(peer_flags != nullptr && status_dev != nullptr, "null pointer");
+    for (int i = 0; i < world; ++i) LFS_REQUIRE(peer_flags[i] != nullptr, "null peer flag array");
+    LFS_REQUIRE(timeout_ns > 0 && timeout_ns <= 60ull * 1000000000ull, "timeout must be in (0, 60 s]");
+    return launch_dp_barrier(world, peer_flags, own_rank, slot, value, timeout_ns, status_dev, S(stream));
+}
+
 int lfs_relocation(int n, const float* opacities, const float* scales, const int32_t* ratios, const float* binoms, int n_max,
                    float* new_opacities, float* new_scales, void* stream) {
     LFS_REQUIRE(n >= 0 && n_max > 0, "bad sizes");

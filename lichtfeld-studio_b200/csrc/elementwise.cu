@@ -381,6 +381,92 @@ int launch_dp_reduce_adam_broadcast(const DpArgs& A, int ctas_per_sm, cudaStream
     return check_launch("dp_reduce_adam_broadcast");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Cross-GPU ordering by flags in peer-mapped memory (no counterpart in the reference, which is single-GPU).
+// dp_signal_kernel runs after a producer kernel on the same stream and stores a step number into one word of every
+// peer's flag array; dp_wait_kernel spins until the words written by all ranks have reached a step number, for at most
+// timeout_ns (globaltimer). On expiry it records which ranks were missing and RETURNS: the stream goes on, nothing
+// hangs, and the host reads the status word to learn that a rank stopped stepping.
+// ---------------------------------------------------------------------------------------------
+struct DpPeers { int32_t* flags[LFS_DP_MAX_WORLD]; };
+
+__global__ void dp_signal_kernel(DpPeers peers, int world, int own_rank, int slot, int32_t value) {
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    __threadfence_system();   // this stream's earlier writes (also to peer memory) are ordered before the flag
+    int32_t* dst = peers.flags[r] + slot * LFS_DP_MAX_WORLD + own_rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dst), "r"(value) : "memory");
+}
+
+// Lane r waits until rank r's word of `slot` shows `value` or a later step, for at most timeout_ns of the global timer. A
+// wait that runs out records itself in status[0..3] = {1, bit mask of the missing ranks, slot, value of the FIRST failed
+// wait} and returns like a satisfied one: nothing ever spins without a limit, and the host learns of it from the status.
+__device__ __forceinline__ void dp_wait_lane(const int32_t* __restrict__ flags, int world, int slot, int32_t value,
+                                             unsigned long long timeout_ns, int32_t* __restrict__ status) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        const int32_t* src = flags + slot * LFS_DP_MAX_WORLD + r;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        bool ok = false;
+        for (;;) {
+            int32_t seen;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(src) : "memory");
+            if (seen - value >= 0) { ok = true; break; }          // step numbers only grow (wrap-safe comparison)
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > timeout_ns) break;
+            __nanosleep(100);
+        }
+        if (!ok) {
+            atomicOr(&status[1], 1 << r);         // ranks that were missing
+            if (atomicOr(&status[0], 1) == 0) {   // a wait ran out; the first one names slot and step
+                status[2] = slot;
+                status[3] = value;
+            }
+        }
+    }
+    __syncwarp();
+    __threadfence_system();   // data written before the flags is visible to the kernels that follow on this stream
+}
+
+__global__ void dp_wait_kernel(const int32_t* __restrict__ flags, int world, int slot, int32_t value, unsigned long long timeout_ns,
+                               int32_t* __restrict__ status) {
+    dp_wait_lane(flags, world, slot, value, timeout_ns, status);
+}
+
+// signal + wait in one launch: the rendezvous of the data-parallel step
+__global__ void dp_barrier_kernel(DpPeers peers, int world, int own_rank, int slot, int32_t value, unsigned long long timeout_ns,
+                                  int32_t* __restrict__ status) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        __threadfence_system();
+        int32_t* dst = peers.flags[r] + slot * LFS_DP_MAX_WORLD + own_rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dst), "r"(value) : "memory");
+    }
+    dp_wait_lane(peers.flags[own_rank], world, slot, value, timeout_ns, status);
+}
+
+int launch_dp_signal(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, cudaStream_t st) {
+    DpPeers p;
+    for (int i = 0; i < LFS_DP_MAX_WORLD; ++i) p.flags[i] = i < world ? peer_flags[i] : nullptr;
+    dp_signal_kernel<<<1, 32, 0, st>>>(p, world, own_rank, slot, value);
+    return check_launch("dp_signal");
+}
+
+int launch_dp_wait(int world, const int32_t* flags, int slot, int32_t value, uint64_t timeout_ns, int32_t* status, cudaStream_t st) {
+    dp_wait_kernel<<<1, 32, 0, st>>>(flags, world, slot, value, (unsigned long long)timeout_ns, status);
+    return check_launch("dp_wait");
+}
+
+int launch_dp_barrier(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, uint64_t timeout_ns, int32_t* status,
+                      cudaStream_t st) {
+    DpPeers p;
+    for (int i = 0; i < LFS_DP_MAX_WORLD; ++i) p.flags[i] = i < world ? peer_flags[i] : nullptr;
+    dp_barrier_kernel<<<1, 32, 0, st>>>(p, world, own_rank, slot, value, (unsigned long long)timeout_ns, status);
+    return check_launch("dp_barrier");
+}
+
 int launch_regularization(int N, const float* scaling_raw, const float* opacity_raw, float scale_weight, float opacity_weight,
                           float* g_scaling, float* g_opacity, float* loss, cudaStream_t st) {
     cudaMemsetAsync(loss, 0, 2 * sizeof(float), st);

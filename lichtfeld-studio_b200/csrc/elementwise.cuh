@@ -64,4 +64,11 @@ int launch_mcmc_apply(int N, int K, int n, const int64_t* sampled, const int64_t
                       const float* new_scales, float min_opacity, const lfs_splats& p, const lfs_splats* m, const lfs_splats* v,
                       cudaStream_t st);
 
+// Flag-based ordering between ranks (see dp_signal_kernel / dp_wait_kernel). peer_flags[i]: rank i's flag array as mapped
+// on this GPU (host array of `world` device pointers, entry own_rank is the local array).
+int launch_dp_signal(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, cudaStream_t st);
+int launch_dp_wait(int world, const int32_t* flags, int slot, int32_t value, uint64_t timeout_ns, int32_t* status, cudaStream_t st);
+int launch_dp_barrier(int world, int32_t* const* peer_flags, int own_rank, int slot, int32_t value, uint64_t timeout_ns, int32_t* status,
+                      cudaStream_t st);
+
 }  // namespace lfs

@@ -79,8 +79,16 @@ def class_segments(capacity: int, K: int, names, world: int, rank: int, lrs, ski
 class GradExchange:
     """Owns the sharded optimizer state and performs exchange + Adam for one rank."""
 
+    # slots of the flag array (lfs_dp_signal / lfs_dp_wait)
+    SLOT_GRADS, SLOT_EXCHANGED, SLOT_COLOR = 0, 1, 2
+
     def __init__(self, model: SplatData, grads: SplatData, lrs, mode: str = "sharded", betas=(0.9, 0.999), eps=1e-15,
-                 group=None, peer_ptrs=None):
+                 group=None, peer_ptrs=None, ordering: str | None = None, wait_timeout_s: float = 20.0):
+        """ordering (fused_p2p only; default: environment LFS_DP_ORDERING, else "flags"): how the ranks' kernels are ordered
+        around the peer-memory exchange. "flags": every rank stores its step number into a flag word of every peer
+        (lfs_dp_signal) and waits, for at most `wait_timeout_s` (<= 60), until all its own words show the step
+        (lfs_dp_wait); a wait that runs out sets a status word that raise_if_failed() reports, and the stream carries on.
+        "nccl": stream-ordered 4-byte all-reduces."""
         self.model, self.grads, self.lrs, self.mode = model, grads, [float(x) for x in lrs], mode
         self.betas, self.eps, self.group = betas, eps, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -100,26 +108,53 @@ class GradExchange:
             if peer_ptrs is None:
                 raise RuntimeError("fused_p2p needs the peer-mapped addresses of every rank's parameter and gradient buffers")
             self.peer_grads, self.peer_params = peer_ptrs
+        ordering = ordering or os.environ.get("LFS_DP_ORDERING", "flags")
+        if ordering not in ("flags", "nccl"):
+            raise ValueError(f"ordering {ordering!r}: expected 'flags' or 'nccl'")
+        self.flags, self.peer_flags = None, None
+        if mode == "fused_p2p" and self.world > 1 and ordering == "flags":
+            self.flags, self.peer_flags = symmetric_flags(dev, group)
+        self.ordering = ordering if self.flags is not None else "nccl"
+        self.wait_timeout_ns = int(wait_timeout_s * 1e9)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev) if self.flags is not None else None
         self.step_count = 0
         self._split = None   # lazily built state of step_split()
         self.timing = None   # set to a list to collect (name, start event, end event) of every rendezvous
         self.color_ctas_per_sm = int(os.environ.get("LFS_DP_COLOR_CTAS", "1"))   # launch footprint of the overlapped part
+        self.color_after_geometry = os.environ.get("LFS_DP_COLOR_AFTER_GEOMETRY", "0") not in ("", "0")
 
     # -- helpers --------------------------------------------------------------------------------
     def _stream(self):
         return capi.vp(torch.cuda.current_stream().cuda_stream)
 
-    def _rendezvous(self, token, group, name):
-        """Stream-ordered 4-byte all-reduce: no rank's later kernels start before every rank's earlier ones finished.
-        When `timing` is a list, the wait (which includes waiting for the slowest rank) is bracketed by events."""
-        if self.timing is None:
+    def _rendezvous(self, token, group, name, slot=None):
+        """No rank's later kernels start before every rank's earlier ones (on the current stream) finished. With flags:
+        lfs_dp_barrier (signal + bounded wait) on slot `slot` with this step's number (bounded wait, see raise_if_failed); else a
+        stream-ordered 4-byte all-reduce. When `timing` is a list the wait (which includes waiting for the slowest rank) is
+        bracketed by events."""
+        if self.timing is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        if self.flags is not None and slot is not None:
+            pf = (C.c_void_p * self.world)(*self.peer_flags)
+            capi.call("lfs_dp_barrier", self.world, pf, self.rank, int(slot), int(self.step_count), self.wait_timeout_ns,
+                      capi.vp(self.status.data_ptr()), self._stream())
+        else:
             dist.all_reduce(token, group=group)
+        if self.timing is not None:
+            e1.record()
+            self.timing.append((name, e0, e1))
+
+    def raise_if_failed(self):
+        """Reads the status word of the bounded waits (synchronises). Raises when a wait ran out, naming the ranks whose
+        flag never arrived: they stopped stepping (crashed, hung on the host, or left the job)."""
+        if self.status is None:
             return
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        dist.all_reduce(token, group=group)
-        e1.record()
-        self.timing.append((name, e0, e1))
+        st = self.status.tolist()
+        if st[0]:
+            missing = [r for r in range(self.world) if st[1] >> r & 1]
+            raise RuntimeError(f"data-parallel step: ranks {missing} did not reach step {st[3]} (flag slot {st[2]}) within "
+                               f"{self.wait_timeout_ns / 1e9:.1f} s; the parameters of this step are not valid")
 
     def collect_timing(self):
         """[(name, ms)] of the recorded rendezvous; synchronises."""
@@ -192,7 +227,7 @@ class GradExchange:
         if self.mode == "fused_p2p":
             # stream-ordered rendezvous: every rank's backward has written its gradients
             token = torch.zeros(1, device=model.flat.device)
-            self._rendezvous(token, self.group, "rendezvous_gradients_written")
+            self._rendezvous(token, self.group, "rendezvous_gradients_written", self.SLOT_GRADS)
             segs = group_segments(model.capacity, model.K, self.lo, self.n, self.lrs, skip_shN=(iteration <= 1000))
             arr = (capi.DpSegment * max(len(segs), 1))()
             for i, (gi, off, cnt, lr) in enumerate(segs):
@@ -204,7 +239,7 @@ class GradExchange:
             capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
                       self.step_count, float(gs), 0, self._stream())
             # nobody may read parameters or overwrite gradients before every rank's kernel has finished
-            self._rendezvous(token, self.group, "rendezvous_exchange_done")
+            self._rendezvous(token, self.group, "rendezvous_exchange_done", self.SLOT_EXCHANGED)
             return
         raise ValueError(self.mode)
 
@@ -213,7 +248,7 @@ class GradExchange:
         if self._split is None:
             dev = self.model.flat.device
             st = {"side": side_stream, "group_b": dist.new_group() if self.world > 1 else None,
-                  "ev_grads": torch.cuda.Event(), "ev_color": torch.cuda.Event(), "pending": False}
+                  "ev_grads": torch.cuda.Event(), "ev_geo": torch.cuda.Event(), "ev_color": torch.cuda.Event(), "pending": False}
             for cls, names in (("geo", GEOMETRY_CLASS), ("col", COLOR_CLASS)):
                 _, per = class_segments(self.model.capacity, self.model.K, names, self.world, self.rank, self.lrs)
                 st[cls + "_m"] = torch.zeros(max(per, 4), dtype=torch.float32, device=dev)
@@ -265,13 +300,17 @@ class GradExchange:
         skip = iteration <= 1000
         main = torch.cuda.current_stream()
         # every rank's backward has written its gradients
-        self._rendezvous(st["token_a"], self.group, "rendezvous_gradients_written")
+        self._rendezvous(st["token_a"], self.group, "rendezvous_gradients_written", self.SLOT_GRADS)
         st["ev_grads"].record(main)
         segs, _ = class_segments(model.capacity, model.K, GEOMETRY_CLASS, self.world, self.rank, self.lrs)
         self._fused_call(segs, st["geo_m"], st["geo_v"], gs)
-        self._rendezvous(st["token_a"], self.group, "rendezvous_geometry_done")      # every rank's geometry kernel has finished
+        if self.color_after_geometry:
+            st["ev_geo"].record(main)
+        self._rendezvous(st["token_a"], self.group, "rendezvous_geometry_done", self.SLOT_EXCHANGED)   # every rank's geometry kernel has finished
         with torch.cuda.stream(st["side"]):
-            st["side"].wait_event(st["ev_grads"])
+            # the colour exchange starts once every rank's gradients are written; optionally only after this rank's geometry
+            # kernel, so that the exchange on the critical path has the NVLink ports to itself
+            st["side"].wait_event(st["ev_geo"] if self.color_after_geometry else st["ev_grads"])
             segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
             # small footprint: this kernel shares the SMs with the next step's projection and sorting
             if rank1_sh:
@@ -285,7 +324,7 @@ class GradExchange:
                         self._rank1_call(sg, st["col_m"], st["col_v"], gs, sh_degree, ctas_per_sm=self.color_ctas_per_sm)
             else:
                 self._fused_call(segs, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
-            self._rendezvous(st["token_b"], st["group_b"], "rendezvous_color_done_side")  # every rank's colour kernel has finished
+            self._rendezvous(st["token_b"], st["group_b"], "rendezvous_color_done_side", self.SLOT_COLOR)  # every rank's colour kernel has finished
             st["ev_color"].record(st["side"])
         st["pending"] = True
 
@@ -315,3 +354,16 @@ def symmetric_flat_buffers(numel: int, device, group=None):
     hg = symm_mem.rendezvous(g, name)
     p.zero_(); g.zero_()
     return p, g, ([int(x) for x in hg.buffer_ptrs], [int(x) for x in hp.buffer_ptrs])
+
+
+def symmetric_flags(device, group=None):
+    """One zeroed, peer-mapped int32 flag array per rank for lfs_dp_signal / lfs_dp_wait. Returns (local tensor,
+    [device address of every rank's array, indexed by rank])."""
+    import torch.distributed._symmetric_memory as symm_mem
+    name = (group or dist.group.WORLD).group_name
+    f = symm_mem.empty(capi.LFS_DP_FLAG_WORDS, dtype=torch.int32, device=device)
+    h = symm_mem.rendezvous(f, name)
+    f.zero_()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)      # nobody signals before every array is zeroed
+    return f, [int(x) for x in h.buffer_ptrs]

@@ -94,6 +94,7 @@ def main():
         return model.flat.clone()
 
     ref = run("local")
+    start = tr.SplatData(n, K, dev, (n + 31) // 32 * 32).load(P).flat
     ok = True
     for mode in ("allreduce", "sharded", "fused_p2p", "fused_p2p_split", "fused_p2p_split_rank1"):
         try:
@@ -111,7 +112,53 @@ def main():
         ok = ok and same and rel < 2e-3
     if rank == 0:
         print("DP CHECK", "OK" if ok else "FAILED", flush=True)
+    for ordering in ("flags", "nccl"):          # both orderings give the same parameters, bit for bit
+        os.environ["LFS_DP_ORDERING"] = ordering
+        res = run("fused_p2p_split_rank1")
+        if ordering == "flags":
+            first = res
+        elif rank == 0:     # the backward sums with atomics, so two runs agree to rounding, not bit for bit
+            print(f"orderings flags / nccl: |difference| / |update| = {float((first - res).norm() / (first - start).norm()):.2e}", flush=True)
+    os.environ["LFS_DP_ORDERING"] = "flags"
+    failure_detection(dp, tr, dev, rank, world, n, K, P)
     dist.destroy_process_group()
+
+
+def failure_detection(dp, tr, dev, rank, world, n, K, P):
+    """The last rank stops stepping after step 1, between steps, with nothing of its own in flight; it stays alive (its memory
+    stays mapped) and waits on the host. The others run step 2: their bounded wait for its flag gives up, the status word
+    names it, raise_if_failed() raises, and their CUDA contexts stay usable."""
+    cap = (n + 31) // 32 * 32
+    numel = cap * tr.SplatData(1, K, "cpu").row_floats
+    pf, gf, peer = dp.symmetric_flat_buffers(numel, dev)
+    model, grads = tr.SplatData(n, K, dev, cap, flat=pf).load(P), tr.SplatData(n, K, dev, cap, flat=gf)
+    grads.flat.fill_(1e-3)
+    ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer, wait_timeout_s=0.5)
+    ex.step(2000)
+    ex.raise_if_failed()                       # step 1: everybody took part
+    torch.cuda.synchronize()
+    store = dist.distributed_c10d._get_default_store()
+    leaver = world - 1
+    if rank == leaver:
+        store.set("dp_failure/left", "1")      # what a heartbeat would stop saying
+        store.wait([f"dp_failure/done{r}" for r in range(world - 1)], datetime.timedelta(seconds=60))
+        verdict = True
+    else:
+        store.wait(["dp_failure/left"], datetime.timedelta(seconds=60))
+        ex.step(2001)                          # the leaver's flag never arrives
+        try:
+            ex.raise_if_failed()
+            verdict = False
+        except RuntimeError as e:
+            verdict = f"ranks [{leaver}]" in str(e)
+            if rank == 0:
+                print("detected:", e, flush=True)
+        alive = float((torch.ones(1024, device=dev) * 2).sum())    # the context still works
+        verdict = verdict and alive == 2048.0
+        store.set(f"dp_failure/done{rank}", "1" if verdict else "0")
+    votes = [store.get(f"dp_failure/done{r}") == b"1" for r in range(world - 1)]
+    if rank == 0:
+        print("DP FAILURE DETECTION", "OK" if all(votes) and verdict else "FAILED", flush=True)
 
 
 if __name__ == "__main__":
