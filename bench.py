@@ -353,7 +353,7 @@ def run_ours(args):
     if world == 1:
         m, v = model.like(), model.like()
     else:
-        exchange = dp.GradExchange(model, grads, LRS, mode=args.dp_mode, peer_ptrs=peer, ordering=args.dp_ordering)
+        exchange = dp.GradExchange(model, grads, LRS, mode=args.dp_mode, peer_ptrs=peer, ordering=args.dp_ordering, multicast=args.dp_multicast)
     rast = tr.Rasterizer(model, W, H, deg, isect_capacity=max(12 * n, 1 << 22))
     rast_t = tr.Rasterizer(held_out, W, H, deg, isect_capacity=max(12 * n, 1 << 22))
     lossfn = tr.PhotometricLoss(W, H, dev)
@@ -598,7 +598,7 @@ def run_ours(args):
         dist.all_gather(allc, chk)
         same_params = all(bool(torch.equal(allc[0], c)) for c in allc)
         exchange.raise_if_failed()      # no bounded wait of the timed steps ran out
-        small = dp_self_check(pkg, dev, rank, world, args.dp_mode, dp_split, dp_rank1, args.dp_ordering)
+        small = dp_self_check(pkg, dev, rank, world, args.dp_mode, dp_split, dp_rank1, args.dp_ordering, args.dp_multicast)
         dp_check = {"ok": bool(same_params and small["ok"]), "bench_parameters_identical_on_all_ranks": bool(same_params), **small}
     if rank == 0:
         # launches inside one call that are not individually bracketed: scan = 3 kernels, sort = 3 per pass
@@ -689,7 +689,7 @@ def run_ours(args):
                           "cameras_per_rank": cams_per_rank,
                           "optimizer_overlap": bool(overlap), "optimizer": ("inside lfs_render_backward_adam" if (rank1_sh and args.one_call_optimizer) else "separate call"),
                           "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else ("rank-1 factors over NVLink" if dp_rank1 else "materialised"),
-                          "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split and cams_per_rank == 1 else "") + (f"+{exchange.ordering}" if args.dp_mode == "fused_p2p" else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
+                          "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split and cams_per_rank == 1 else "") + (f"+{exchange.ordering}" + ("+multimem" if exchange.mc_params else "") if args.dp_mode == "fused_p2p" else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
                "clocks": clocks, "e2e": {"value": batch * 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": h2d,
                                          "d2h_bytes_per_step": d2h, "steps": n_e2e},
@@ -701,7 +701,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None):
+def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None, multicast=None):
     """Cross-rank correctness of the exchange the benchmark just timed, on a small scene: three data-parallel steps with
     the same mode flags must leave bit-identical parameters on every rank, equal (to gradient-summation rounding) to what
     ONE process gets by rendering every camera itself, accumulating the gradients and applying Adam to their mean."""
@@ -738,7 +738,7 @@ def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None):
     else:
         model, grads = tr.SplatData(n, K, dev, cap).load(P), tr.SplatData(n, K, dev, cap)
     rast = tr.Rasterizer(model, W, H, deg)
-    ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer, ordering=ordering)
+    ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer, ordering=ordering, multicast=multicast)
     side = torch.cuda.Stream(device=dev)
     for s in range(steps):
         if split:
@@ -984,6 +984,9 @@ def main():
     ap.add_argument("--dp-ordering", default="flags", choices=["flags", "nccl"],
                     help="N > 1, fused_p2p: how the ranks' kernels are ordered around the peer-memory exchange: flag words in peer "
                          "memory with bounded waits (lfs_dp_signal / lfs_dp_wait), or 4-byte NCCL all-reduces")
+    ap.add_argument("--dp-multicast", action=argparse.BooleanOptionalAction, default=None,
+                    help="N > 1, fused_p2p: broadcast the new parameters with multimem.st through the NVSwitch multicast mapping of "
+                         "the parameter buffer instead of one peer store per rank (default: environment LFS_DP_MULTICAST, else off)")
     ap.add_argument("--dp-mode", default="fused_p2p", choices=["allreduce", "sharded", "fused_p2p"],
                     help="gradient exchange for N > 1 (see lichtfeld-studio_b200/dp.py)")
     args = ap.parse_args()

@@ -163,9 +163,10 @@ int lfs_adam_step(float* param, float* exp_avg, float* exp_avg_sq, const float* 
  * stores the new coefficients into every rank's shN tensor. peer_factors[i] / peer_shN[i] (host arrays of `world` device
  * pointers) belong to rank (own_rank + i) % world, entry 0 is this rank's own. It moves 24 N / world bytes per peer in
  * instead of 12 (K-1) N / world; ordering against the other ranks as for lfs_dp_reduce_adam_broadcast. Rows >= N
- * (capacity padding) take a zero gradient. Plain peer loads / stores only; no multicast. */
-int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, float* const* peer_shN, int N, int sh_coeffs,
-                                   int sh_degree, int64_t lo, int64_t n, float* exp_avg, float* exp_avg_sq, float lr,
+ * (capacity padding) take a zero gradient. multicast_shN as multicast_params of lfs_dp_reduce_adam_broadcast (the address of
+ * the same tensor inside the multicast mapping), or NULL. */
+int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, float* const* peer_shN, float* multicast_shN,
+                                   int N, int sh_coeffs, int sh_degree, int64_t lo, int64_t n, float* exp_avg, float* exp_avg_sq, float lr,
                                    double beta1, double beta2, double eps, int64_t step_count, float grad_scale,
                                    int ctas_per_sm, void* stream);
 
@@ -370,7 +371,9 @@ int lfs_render_backward_adam(const lfs_render_config* cfg, const lfs_splats* par
  * rows on the fly from grads->sh0, params->means and the camera of the forward state in `workspace` (the one the backward
  * used). The other five groups are updated from their gradient tensors as in lfs_adam_step_splats. Saves the write and the
  * read of 12 (K-1) N gradient bytes per step; the result equals backward-with-shN + lfs_adam_step_splats up to one
- * rounding of the colour gradient. Not for gradients accumulated over several cameras (their sum is no outer product). */
+ * rounding of the colour gradient. Not for gradients accumulated over several cameras (their sum is no outer product), and
+ * only while params->means are the means the forward used: a caller that moves them between backward and this call (the
+ * MCMC noise, a relocation) must let the backward write grads->shN and use lfs_adam_step_splats. */
 int lfs_adam_step_splats_rank1_sh(const lfs_render_config* cfg, const lfs_splats* params, const lfs_splats* exp_avg,
                                   const lfs_splats* exp_avg_sq, const lfs_splats* grads, const float* lr /* host[6] */,
                                   double beta1, double beta2, double eps, int64_t step_count, int skip_shN,
@@ -412,8 +415,11 @@ int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segments /* h
  * ctas_per_sm: launch footprint, 0 = default (16 CTAs of 256 threads per SM); the kernel is NVLink-bound and keeps its
  * speed with 2 - 4, which leaves thread slots for kernels running next to it on other streams.
  * The caller must order it against the other ranks: every rank's backward finished before, nobody reads
- * parameters or rewrites gradients until all ranks finished after (e.g. a stream-ordered barrier). Plain
- * peer loads / stores only; no multicast. */
+ * parameters or rewrites gradients until all ranks finished after (lfs_dp_barrier, or a stream-ordered collective).
+ * multicast_params: NULL, or the address of the parameter buffer in an NVSwitch multicast mapping bound to the same memory
+ * on all `world` GPUs (cuMulticast* / torch symmetric memory's multicast_ptr): the new parameters then leave this GPU as ONE
+ * multimem.st per 16 bytes, which the switch replicates, instead of `world` peer stores (the broadcast's share of the NVLink
+ * egress drops by the number of peers). Gradients are always read with plain peer loads. */
 typedef struct lfs_dp_segment {
     int64_t offset;      /* first element of the segment in the flat buffers */
     int64_t n;           /* elements */
@@ -421,8 +427,8 @@ typedef struct lfs_dp_segment {
     float* exp_avg_sq;
     float lr;
 } lfs_dp_segment;
-int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,
-                                 const lfs_dp_segment* segments /* host */, double beta1, double beta2, double eps,
+int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, float* multicast_params,
+                                 int n_segments, const lfs_dp_segment* segments /* host */, double beta1, double beta2, double eps,
                                  int64_t step_count, float grad_scale, int ctas_per_sm, void* stream);
 
 /* ------------------------------------------------------------------------------------------ */

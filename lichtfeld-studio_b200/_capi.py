@@ -110,12 +110,12 @@ _SIGNATURES = {
                                       vp, sz, vp],
     "lfs_regularization": [i32, vp, vp, f32, f32, vp, vp, vp, vp],
     "lfs_adam_step_segments": [i32, C.POINTER(AdamSegment), C.c_double, C.c_double, C.c_double, i64, f32, i32, vp],
-    "lfs_dp_reduce_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, C.POINTER(DpSegment), C.c_double,
+    "lfs_dp_reduce_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), vp, i32, C.POINTER(DpSegment), C.c_double,
                                      C.c_double, C.c_double, i64, f32, i32, vp],
     "lfs_dp_signal": [i32, C.POINTER(C.c_void_p), i32, i32, i32, vp],
     "lfs_dp_wait": [i32, vp, i32, i32, C.c_uint64, vp, vp],
     "lfs_dp_barrier": [i32, C.POINTER(C.c_void_p), i32, i32, i32, C.c_uint64, vp, vp],
-    "lfs_dp_sh_rank1_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), i32, i32, i32, i64, i64, vp, vp, f32,
+    "lfs_dp_sh_rank1_adam_broadcast": [i32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), vp, i32, i32, i32, i64, i64, vp, vp, f32,
                                        C.c_double, C.c_double, C.c_double, i64, f32, i32, vp],
     "lfs_mcmc_classify": [i32, vp, vp, f32, vp, vp, vp, vp, vp, sz, vp],
     "lfs_mcmc_classify_noalloc": [i32, vp, vp, f32, vp, vp, vp, vp, vp],

@@ -518,8 +518,8 @@ int lfs_adam_step_segments(int n_segments, const lfs_adam_segment* segs, double 
     return launch_adam_segments(S, ctas_per_sm, S_(stream));
 }
 
-int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, int n_segments,
-                                 const lfs_dp_segment* segs, double beta1, double beta2, double eps, int64_t step_count,
+int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, float* const* peer_params, float* multicast_params,
+                                 int n_segments, const lfs_dp_segment* segs, double beta1, double beta2, double eps, int64_t step_count,
                                  float grad_scale, int ctas_per_sm, void* stream) {
     LFS_REQUIRE(world >= 1 && world <= kMaxPeers, "world must be in [1, 8]");
     LFS_REQUIRE(n_segments >= 0 && n_segments <= 6, "at most 6 segments");
@@ -537,6 +537,8 @@ int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, floa
         A.grads[r] = peer_grads[r];
         A.params[r] = peer_params[r];
     }
+    LFS_REQUIRE(aligned16(multicast_params), "the multicast address must be 16-byte aligned");
+    A.mc_params = multicast_params;
     A.prefix4[0] = 0;
     int ns = 0;
     for (int k = 0; k < n_segments; ++k) {
@@ -555,7 +557,8 @@ int lfs_dp_reduce_adam_broadcast(int world, const float* const* peer_grads, floa
     return launch_dp_reduce_adam_broadcast(A, ctas_per_sm, S_(stream));
 }
 
-int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, float* const* peer_shN, int N, int sh_coeffs,
+int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, float* const* peer_shN, float* multicast_shN, int N,
+                                   int sh_coeffs,
                                    int sh_degree, int64_t lo, int64_t n, float* exp_avg, float* exp_avg_sq, float lr,
                                    double beta1, double beta2, double eps, int64_t step_count, float grad_scale,
                                    int ctas_per_sm, void* stream) {
@@ -578,7 +581,8 @@ int lfs_dp_sh_rank1_adam_broadcast(int world, const float* const* peer_factors, 
         A.shN[r] = peer_shN[r];
         vec = vec && aligned16(peer_shN[r]);
     }
-    A.vec = vec;
+    A.vec = vec && aligned16(multicast_shN);
+    A.mc_shN = multicast_shN;
     A.adam = AdamRank1{nullptr, nullptr, nullptr, lr * (float)bc1, (float)beta1, (float)beta2, (float)eps, (float)bc2, grad_scale, 0};
     return launch_dp_sh_rank1(sh_coeffs, sh_degree, A, ctas_per_sm, S_(stream));
 }

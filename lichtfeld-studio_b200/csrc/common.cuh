@@ -114,4 +114,14 @@ int radix_sort_pairs(uint32_t* keys[2], uint32_t* vals[2], const int32_t* n_dev,
 int exclusive_scan_gather(const int32_t* src, const uint32_t* idx, int64_t n, int32_t* out, int32_t* total_dev,
                           const SortScratch& scratch, cudaStream_t st);
 
+// One 16-byte store to an NVSwitch multicast address: the switch writes it into the same offset of every GPU bound to the
+// multicast object (this GPU included), so a broadcast leaves this GPU's NVLink ports once instead of once per peer.
+__device__ __forceinline__ void multimem_st4(float* mc, const float4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void multimem_st1(float* mc, const float v) {
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+}
+
 }  // namespace lfs

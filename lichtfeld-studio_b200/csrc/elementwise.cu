@@ -87,7 +87,8 @@ __global__ void __launch_bounds__(256) adam_segments_kernel(AdamSegments S) {
 
 // Reduce-scatter + Adam + all-gather in one pass over this rank's shard. Each element is summed by its
 // owner only, in rank order, so every rank ends up with bit-identical parameters. Peer traffic is plain
-// 16-byte loads / stores over NVLink.
+// 16-byte loads over NVLink and, for the new parameters, either one plain 16-byte store per rank or one multimem.st
+// through the NVSwitch multicast address of the buffer.
 __global__ void __launch_bounds__(256) dp_reduce_adam_broadcast_kernel(DpArgs A) {
     const int64_t total4 = A.prefix4[A.n_segments];
     for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < total4; q += (int64_t)gridDim.x * blockDim.x) {
@@ -116,9 +117,13 @@ __global__ void __launch_bounds__(256) dp_reduce_adam_broadcast_kernel(DpArgs A)
         adam_update(p.w, m.w, v.w, g.w * A.grad_scale, A.beta1, A.beta2, A.eps, sg.step_size, A.bc2_sqrt_rcp);
         *reinterpret_cast<float4*>(sg.m + e) = m;
         *reinterpret_cast<float4*>(sg.v + e) = v;
+        if (A.mc_params) {
+            multimem_st4(A.mc_params + f, p);
+        } else {
 #pragma unroll
-        for (int r = 0; r < kMaxPeers; ++r)
-            if (r < A.world) *reinterpret_cast<float4*>(A.params[r] + f) = p;
+            for (int r = 0; r < kMaxPeers; ++r)
+                if (r < A.world) *reinterpret_cast<float4*>(A.params[r] + f) = p;
+        }
     }
 }
 

@@ -38,6 +38,7 @@ struct DpSegment {
 struct DpArgs {
     const float* grads[kMaxPeers];
     float* params[kMaxPeers];
+    float* mc_params;          // NVSwitch multicast address of the parameter buffer, or nullptr: plain peer stores
     DpSegment seg[6];
     int64_t prefix4[7];
     int world, n_segments;

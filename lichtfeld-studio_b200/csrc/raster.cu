@@ -645,9 +645,11 @@ __global__ void __launch_bounds__(256, 4) grad_epilogue_fused_kernel(
         for (int k = 0; k < 4; ++k) a_in[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (in_range) {
             rad = reinterpret_cast<const int2*>(radii)[g];
-            const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
+            if (rad.x > 0 && rad.y > 0) {   // culled Gaussians have no accumulator row: the projection zeroes visible rows only
+                const float4* a4 = reinterpret_cast<const float4*>(accum) + (size_t)g * 4;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) a_in[k] = a4[k];
+                for (int k = 0; k < 4; ++k) a_in[k] = a4[k];
+            }
 #pragma unroll
             for (int k = 0; k < 3; ++k) { m_in[k] = means[g * 3 + k]; s_in[k] = scaling_raw[g * 3 + k]; }
             o_in = opacity_raw[g];
@@ -862,12 +864,13 @@ __global__ void __launch_bounds__(256, 4) adam_sh_rank1_kernel(int N, int K_rt, 
 // that intersect them, the gradient row is the sum over ranks of (SH basis of that rank's view direction) x (that
 // rank's clamped colour gradient), both read from the rank's factor buffer [N,6] through its peer pointer (24 bytes per
 // row and rank instead of the 12 (K-1) bytes of a materialised row); then Adam with the shard-local moments and 16-byte
-// stores of the new coefficients into every rank's parameter buffer. Plain peer loads and stores; the caller orders the
-// launch against the other ranks.
+// stores of the new coefficients into every rank's parameter buffer (plain peer stores, or one multimem.st through the
+// NVSwitch multicast address of the tensor). Plain peer loads; the caller orders the launch against the other ranks.
 template <int KT>
 __global__ void __launch_bounds__(256) dp_sh_rank1_kernel(int K_rt, int sh_degree, DpRank1 A) {
     extern __shared__ __align__(16) float s_rows[];
     constexpr int U = 2;
+    constexpr int kPre = 4;
     const int K = KT ? KT : K_rt;
     const int rest = (K - 1) * 3;
     const int nb = (sh_degree + 1) * (sh_degree + 1);
@@ -881,27 +884,39 @@ __global__ void __launch_bounds__(256) dp_sh_rank1_kernel(int K_rt, int sh_degre
         const int64_t g = chunk * 32 + lane;
         for (int j = 0; j < rest; ++j) my[lane * rest + j] = 0.f;
         if (g < A.N) {
-            for (int r = 0; r < A.world; ++r) {
-                const float2* f = reinterpret_cast<const float2*>(A.factors[r]) + g * 3;
-                const float2 f0 = f[0], f1 = f[1], f2 = f[2];
-                const float vc[3] = {f0.x, f0.y, f1.x};
-                if (vc[0] == 0.f && vc[1] == 0.f && vc[2] == 0.f) continue;
-                float B[25];
+            // kPre ranks' factors are in flight at a time (a peer load takes microseconds)
+            for (int r0 = 0; r0 < A.world; r0 += kPre) {
+                float2 F[kPre][3];
 #pragma unroll
-                for (int k = 0; k < 25; ++k) B[k] = 0.f;
-                sh_basis(sh_degree, f1.y, f2.x, f2.y, B);
-                if (KT) {
-#pragma unroll
-                    for (int k = 1; k < (KT ? KT : 1); ++k) {
-                        const float w = k < nb ? B[k] : 0.f;
-#pragma unroll
-                        for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] += w * vc[c];
+                for (int q = 0; q < kPre; ++q) {
+                    if (r0 + q < A.world) {
+                        const float2* f = reinterpret_cast<const float2*>(A.factors[r0 + q]) + g * 3;
+                        F[q][0] = f[0]; F[q][1] = f[1]; F[q][2] = f[2];
+                    } else {
+                        F[q][0] = F[q][1] = F[q][2] = make_float2(0.f, 0.f);
                     }
-                } else {
-                    for (int k = 1; k < K; ++k) {
-                        const float w = k < nb ? B[k] : 0.f;
+                }
 #pragma unroll
-                        for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] += w * vc[c];
+                for (int q = 0; q < kPre; ++q) {
+                    const float vc[3] = {F[q][0].x, F[q][0].y, F[q][1].x};
+                    if (vc[0] == 0.f && vc[1] == 0.f && vc[2] == 0.f) continue;
+                    float B[25];
+#pragma unroll
+                    for (int k = 0; k < 25; ++k) B[k] = 0.f;
+                    sh_basis(sh_degree, F[q][1].y, F[q][2].x, F[q][2].y, B);
+                    if (KT) {
+#pragma unroll
+                        for (int k = 1; k < (KT ? KT : 1); ++k) {
+                            const float w = k < nb ? B[k] : 0.f;
+#pragma unroll
+                            for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] += w * vc[c];
+                        }
+                    } else {
+                        for (int k = 1; k < K; ++k) {
+                            const float w = k < nb ? B[k] : 0.f;
+#pragma unroll
+                            for (int c = 0; c < 3; ++c) my[lane * rest + (k - 1) * 3 + c] += w * vc[c];
+                        }
                     }
                 }
             }
@@ -938,7 +953,11 @@ __global__ void __launch_bounds__(256) dp_sh_rank1_kernel(int K_rt, int sh_degre
                         adam_rank1_update(p[u].z, m[u].z, v[u].z, gr.z * A.adam.grad_scale, A.adam);
                         adam_rank1_update(p[u].w, m[u].w, v[u].w, gr.w * A.adam.grad_scale, A.adam);
                         m4[i] = m[u]; v4[i] = v[u];
-                        for (int r = 0; r < A.world; ++r) reinterpret_cast<float4*>(A.shN[r] + e0)[i] = p[u];
+                        if (A.mc_shN) {
+                            multimem_st4(A.mc_shN + e0 + 4 * (int64_t)i, p[u]);
+                        } else {
+                            for (int r = 0; r < A.world; ++r) reinterpret_cast<float4*>(A.shN[r] + e0)[i] = p[u];
+                        }
                     }
                 }
             }
@@ -948,7 +967,11 @@ __global__ void __launch_bounds__(256) dp_sh_rank1_kernel(int K_rt, int sh_degre
             float p = pp[i], m = mm[i], v = vv[i];
             adam_rank1_update(p, m, v, grad[i] * A.adam.grad_scale, A.adam);
             mm[i] = m; vv[i] = v;
-            for (int r = 0; r < A.world; ++r) A.shN[r][e0 + i] = p;
+            if (A.mc_shN) {
+                multimem_st1(A.mc_shN + e0 + i, p);
+            } else {
+                for (int r = 0; r < A.world; ++r) A.shN[r][e0 + i] = p;
+            }
         }
         __syncwarp();
     }

@@ -66,6 +66,7 @@ constexpr int kRank1MaxPeers = 8;
 struct DpRank1 {
     const float* factors[kRank1MaxPeers];
     float* shN[kRank1MaxPeers];
+    float* mc_shN;             // NVSwitch multicast address of the shN tensor, or nullptr: plain peer stores
     int64_t lo, n;
     float* m; float* v;
     AdamRank1 adam;   // p / m / v unused here

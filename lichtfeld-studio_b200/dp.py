@@ -83,12 +83,15 @@ class GradExchange:
     SLOT_GRADS, SLOT_EXCHANGED, SLOT_COLOR = 0, 1, 2
 
     def __init__(self, model: SplatData, grads: SplatData, lrs, mode: str = "sharded", betas=(0.9, 0.999), eps=1e-15,
-                 group=None, peer_ptrs=None, ordering: str | None = None, wait_timeout_s: float = 20.0):
+                 group=None, peer_ptrs=None, ordering: str | None = None, wait_timeout_s: float = 20.0,
+                 multicast: bool | None = None):
         """ordering (fused_p2p only; default: environment LFS_DP_ORDERING, else "flags"): how the ranks' kernels are ordered
         around the peer-memory exchange. "flags": every rank stores its step number into a flag word of every peer
         (lfs_dp_signal) and waits, for at most `wait_timeout_s` (<= 60), until all its own words show the step
         (lfs_dp_wait); a wait that runs out sets a status word that raise_if_failed() reports, and the stream carries on.
-        "nccl": stream-ordered 4-byte all-reduces."""
+        "nccl": stream-ordered 4-byte all-reduces.
+        multicast (fused_p2p; default: environment LFS_DP_MULTICAST, else off): send the new parameters with multimem.st through
+        the NVSwitch multicast mapping of the parameter buffer (peer_ptrs[2], from symmetric_flat_buffers) when there is one."""
         self.model, self.grads, self.lrs, self.mode = model, grads, [float(x) for x in lrs], mode
         self.betas, self.eps, self.group = betas, eps, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -107,7 +110,9 @@ class GradExchange:
         if mode == "fused_p2p":
             if peer_ptrs is None:
                 raise RuntimeError("fused_p2p needs the peer-mapped addresses of every rank's parameter and gradient buffers")
-            self.peer_grads, self.peer_params = peer_ptrs
+            self.peer_grads, self.peer_params = peer_ptrs[0], peer_ptrs[1]
+            want_mc = (os.environ.get("LFS_DP_MULTICAST", "0") not in ("", "0")) if multicast is None else bool(multicast)
+            self.mc_params = int(peer_ptrs[2]) if (want_mc and len(peer_ptrs) > 2 and self.world > 1) else 0
         ordering = ordering or os.environ.get("LFS_DP_ORDERING", "flags")
         if ordering not in ("flags", "nccl"):
             raise ValueError(f"ordering {ordering!r}: expected 'flags' or 'nccl'")
@@ -121,7 +126,9 @@ class GradExchange:
         self._split = None   # lazily built state of step_split()
         self.timing = None   # set to a list to collect (name, start event, end event) of every rendezvous
         self.color_ctas_per_sm = int(os.environ.get("LFS_DP_COLOR_CTAS", "1"))   # launch footprint of the overlapped part
-        self.color_after_geometry = os.environ.get("LFS_DP_COLOR_AFTER_GEOMETRY", "0") not in ("", "0")
+        # when the colour exchange may start: 0 = with the geometry exchange (every rank's gradients are written), 1 = after this
+        # rank's geometry kernel, 2 = after every rank's geometry kernel (the exchange on the critical path then has NVLink to itself)
+        self.color_after_geometry = int(os.environ.get("LFS_DP_COLOR_AFTER_GEOMETRY", "2") or 0)
 
     # -- helpers --------------------------------------------------------------------------------
     def _stream(self):
@@ -236,8 +243,8 @@ class GradExchange:
             order = [(self.rank + i) % self.world for i in range(self.world)]
             pg = (C.c_void_p * self.world)(*[self.peer_grads[r] for r in order])
             pp = (C.c_void_p * self.world)(*[self.peer_params[r] for r in order])
-            capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
-                      self.step_count, float(gs), 0, self._stream())
+            capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, capi.vp(self.mc_params or None), len(segs), arr, self.betas[0],
+                      self.betas[1], self.eps, self.step_count, float(gs), 0, self._stream())
             # nobody may read parameters or overwrite gradients before every rank's kernel has finished
             self._rendezvous(token, self.group, "rendezvous_exchange_done", self.SLOT_EXCHANGED)
             return
@@ -265,8 +272,8 @@ class GradExchange:
         order = [(self.rank + i) % self.world for i in range(self.world)]
         pg = (C.c_void_p * self.world)(*[self.peer_grads[r] for r in order])
         pp = (C.c_void_p * self.world)(*[self.peer_params[r] for r in order])
-        capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, len(segs), arr, self.betas[0], self.betas[1], self.eps,
-                  self.step_count, float(gs), int(ctas_per_sm), self._stream())
+        capi.call("lfs_dp_reduce_adam_broadcast", self.world, pg, pp, capi.vp(self.mc_params or None), len(segs), arr, self.betas[0],
+                  self.betas[1], self.eps, self.step_count, float(gs), int(ctas_per_sm), self._stream())
 
     def _rank1_call(self, seg, m, v, gs, sh_degree, ctas_per_sm=0):
         """The shN part of this rank's colour shard from every rank's factor buffer (see Rasterizer.backward(sh_factors=True))."""
@@ -276,7 +283,8 @@ class GradExchange:
         order = [(self.rank + i) % self.world for i in range(self.world)]
         pf = (C.c_void_p * self.world)(*[self.peer_grads[r] + 4 * shn_off for r in order])
         ps = (C.c_void_p * self.world)(*[self.peer_params[r] + 4 * shn_off for r in order])
-        capi.call("lfs_dp_sh_rank1_adam_broadcast", self.world, pf, ps, self.model.size, self.model.K, int(sh_degree),
+        mc = capi.vp(self.mc_params + 4 * shn_off) if self.mc_params else capi.vp(None)
+        capi.call("lfs_dp_sh_rank1_adam_broadcast", self.world, pf, ps, mc, self.model.size, self.model.K, int(sh_degree),
                   off - shn_off, cnt, capi.vp(m.data_ptr() + 4 * rel), capi.vp(v.data_ptr() + 4 * rel), float(lr), self.betas[0],
                   self.betas[1], self.eps, self.step_count, float(gs), int(ctas_per_sm), self._stream())
 
@@ -304,12 +312,15 @@ class GradExchange:
         st["ev_grads"].record(main)
         segs, _ = class_segments(model.capacity, model.K, GEOMETRY_CLASS, self.world, self.rank, self.lrs)
         self._fused_call(segs, st["geo_m"], st["geo_v"], gs)
-        if self.color_after_geometry:
+        if self.color_after_geometry == 1:
             st["ev_geo"].record(main)
         self._rendezvous(st["token_a"], self.group, "rendezvous_geometry_done", self.SLOT_EXCHANGED)   # every rank's geometry kernel has finished
+        if self.color_after_geometry == 2:
+            st["ev_geo"].record(main)
+        st["pending"] = True
         with torch.cuda.stream(st["side"]):
             # the colour exchange starts once every rank's gradients are written; optionally only after this rank's geometry
-            # kernel, so that the exchange on the critical path has the NVLink ports to itself
+            # kernel or every rank's, so that the exchange on the critical path has the NVLink ports to itself
             st["side"].wait_event(st["ev_geo"] if self.color_after_geometry else st["ev_grads"])
             segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
             # small footprint: this kernel shares the SMs with the next step's projection and sorting
@@ -326,7 +337,6 @@ class GradExchange:
                 self._fused_call(segs, st["col_m"], st["col_v"], gs, ctas_per_sm=self.color_ctas_per_sm)
             self._rendezvous(st["token_b"], st["group_b"], "rendezvous_color_done_side", self.SLOT_COLOR)  # every rank's colour kernel has finished
             st["ev_color"].record(st["side"])
-        st["pending"] = True
 
     def wait_color(self):
         """Make the current stream wait for the colour part of the last step_split()."""
@@ -337,7 +347,7 @@ class GradExchange:
 def symmetric_flat_buffers(numel: int, device, group=None):
     """Two peer-mapped float32 buffers (parameters, gradients) of `numel` elements and the device addresses
     of every rank's copies, via torch's symmetric memory (CUDA VMM over NVLink). Returns
-    (param_flat, grad_flat, (peer_grad_ptrs, peer_param_ptrs))."""
+    (param_flat, grad_flat, (peer_grad_ptrs, peer_param_ptrs, multicast address of the parameter buffer or 0))."""
     import torch.distributed._symmetric_memory as symm_mem
     name = (group or dist.group.WORLD).group_name
     if hasattr(symm_mem, "enable_symm_mem_for_group"):
@@ -353,7 +363,8 @@ def symmetric_flat_buffers(numel: int, device, group=None):
     hp = symm_mem.rendezvous(p, name)
     hg = symm_mem.rendezvous(g, name)
     p.zero_(); g.zero_()
-    return p, g, ([int(x) for x in hg.buffer_ptrs], [int(x) for x in hp.buffer_ptrs])
+    mc = int(getattr(hp, "multicast_ptr", 0) or 0)     # 0 where the GPUs / the driver offer no NVSwitch multicast
+    return p, g, ([int(x) for x in hg.buffer_ptrs], [int(x) for x in hp.buffer_ptrs], mc)
 
 
 def symmetric_flags(device, group=None):

@@ -162,11 +162,20 @@ class MCMC(IStrategy):
             self.relocate_gs()
             self.add_new_gs()
         self.inject_noise()
+        self._means_moved_iter = iter     # the noise moved every mean; relocation rewrote rows
 
     def step(self, iter: int, grad_scale: float = 1.0, rasterizer=None):
         """mcmc.cpp:395-402. On an iteration whose post_backward appended or removed rows the optimizer does nothing and
         does not count the step (the gradients belong to the old rows); the scheduler still runs. The next backward
-        writes every gradient row again."""
+        writes every gradient row again.
+        rasterizer (FusedAdam.step): the rank-1 shN update rebuilds each gradient row from the CURRENT means and the camera
+        of the forward, so it is only equal to the materialised gradient while the means are those the forward saw. It is
+        refused after this iteration's post_backward (which moved them); leave rasterizer=None in the reference's order
+        backward -> post_backward -> step."""
+        if rasterizer is not None and getattr(self, "_means_moved_iter", None) == iter:
+            raise RuntimeError("MCMC.step(rasterizer=...): post_backward of this iteration moved the means; the rank-1 shN "
+                               "update would rebuild its gradient rows from other view directions than the forward's. "
+                               "Call step() without a rasterizer (backward must then write the shN gradient).")
         if iter < self._params.iterations:
             if self._grads_valid:
                 self._optimizer.step(iter, self.grads, grad_scale, rasterizer=rasterizer)

@@ -17,6 +17,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 LRS = [1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2]
+LAST_EXCHANGE = [None]
 
 
 def main():
@@ -58,7 +59,7 @@ def main():
             return model.flat.clone()
         if mode == "fused_p2p_split_rank1":
             # as fused_p2p_split, with the shN gradient crossing NVLink as its two rank-1 factors
-            ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
+            ex = LAST_EXCHANGE[0] = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
             side = torch.cuda.Stream(device=dev)
             for s in range(steps):
                 rast.forward_lists(cam(s * world + rank))
@@ -72,7 +73,7 @@ def main():
             return model.flat.clone()
         if mode == "fused_p2p_split":
             # geometry groups exchanged on the main stream, colour groups on a side stream under the next step's lists
-            ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
+            ex = LAST_EXCHANGE[0] = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer)
             side = torch.cuda.Stream(device=dev)
             for s in range(steps):
                 rast.forward_lists(cam(s * world + rank))
@@ -84,7 +85,7 @@ def main():
             ex.wait_color()
             torch.cuda.synchronize()
             return model.flat.clone()
-        ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer)
+        ex = LAST_EXCHANGE[0] = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer)
         for s in range(steps):
             out = rast.forward(cam(s * world + rank), bg)
             _, vr = lossfn(out.image, targets[s * world + rank])
@@ -120,6 +121,18 @@ def main():
         elif rank == 0:     # the backward sums with atomics, so two runs agree to rounding, not bit for bit
             print(f"orderings flags / nccl: |difference| / |update| = {float((first - res).norm() / (first - start).norm()):.2e}", flush=True)
     os.environ["LFS_DP_ORDERING"] = "flags"
+    os.environ["LFS_DP_MULTICAST"] = "1"        # parameters broadcast with multimem.st where the box has NVSwitch multicast
+    for mode in ("fused_p2p", "fused_p2p_split_rank1"):
+        out = run(mode)
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(gathered[0], g) for g in gathered)
+        rel = float((out - ref).norm() / (ref - start).norm())
+        if rank == 0:
+            print(f"{mode} + multimem.st: identical on all ranks = {same}; |update - local update| / |local update| = {rel:.2e}"
+                  f" (multicast address {'present' if LAST_EXCHANGE[0].mc_params else 'ABSENT: plain stores were used'})", flush=True)
+            print("DP MULTICAST CHECK", "OK" if same and rel < 2e-3 else "FAILED", flush=True)
+    os.environ["LFS_DP_MULTICAST"] = "0"
     failure_detection(dp, tr, dev, rank, world, n, K, P)
     dist.destroy_process_group()
 
@@ -127,13 +140,13 @@ def main():
 def failure_detection(dp, tr, dev, rank, world, n, K, P):
     """The last rank stops stepping after step 1, between steps, with nothing of its own in flight; it stays alive (its memory
     stays mapped) and waits on the host. The others run step 2: their bounded wait for its flag gives up, the status word
-    names it, raise_if_failed() raises, and their CUDA contexts stay usable."""
+    names it, raise_if_failed() raises, and their CUDA contexts stay usable. Plain peer loads and stores only (no multimem)."""
     cap = (n + 31) // 32 * 32
     numel = cap * tr.SplatData(1, K, "cpu").row_floats
     pf, gf, peer = dp.symmetric_flat_buffers(numel, dev)
     model, grads = tr.SplatData(n, K, dev, cap, flat=pf).load(P), tr.SplatData(n, K, dev, cap, flat=gf)
     grads.flat.fill_(1e-3)
-    ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer, wait_timeout_s=0.5)
+    ex = dp.GradExchange(model, grads, LRS, mode="fused_p2p", peer_ptrs=peer, wait_timeout_s=0.5, multicast=False)
     ex.step(2000)
     ex.raise_if_failed()                       # step 1: everybody took part
     torch.cuda.synchronize()

@@ -66,7 +66,7 @@ def test_emulated_ranks_equal_accumulated_gradients(pkg, synth, n, deg, world, a
     pf = (C.c_void_p * world)(*[facs[r].tensor("shN").data_ptr() for r in range(world)])
     ps = (C.c_void_p * world)(*[copies[r][0].tensor("shN").data_ptr() for r in range(world)])
     for lo, cnt in ((0, cut), (cut, total - cut)):
-        capi.call("lfs_dp_sh_rank1_adam_broadcast", world, pf, ps, n, K, active, lo, cnt,
+        capi.call("lfs_dp_sh_rank1_adam_broadcast", world, pf, ps, None, n, K, active, lo, cnt,
                   capi.vp(m_own.tensor("shN").data_ptr() + 4 * lo), capi.vp(v_own.tensor("shN").data_ptr() + 4 * lo),
                   LRS[2], 0.9, 0.999, 1e-15, 2, 1.0 / world, 0, stream)
     torch.cuda.synchronize()

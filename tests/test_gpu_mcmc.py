@@ -140,3 +140,18 @@ def test_strategy_schedule_and_step(pkg, synth):
     s.remove_gaussians(mask)
     assert s._splat_data.size == n - int(mask.sum()) and torch.equal(s._splat_data.tensor("means"), keep_rows)
     assert s._optimizer.exp_avg.size == s._splat_data.size
+
+
+def test_rank1_step_is_refused_after_post_backward(pkg, synth):
+    """The rank-1 shN update rebuilds its gradient rows from the current means: after post_backward (noise on every mean,
+    relocated rows) those are no longer the forward's, so the strategy refuses it; the reference's order with a
+    materialised shN gradient goes through."""
+    s, P, M, V = build(pkg, synth, 1500, 1, cap=3000)
+    s.grads.flat.normal_()
+    marker = object()
+    s.post_backward(1500)
+    with pytest.raises(RuntimeError, match="moved the means"):
+        s.step(1500, rasterizer=marker)
+    assert s._optimizer.step_count == 0
+    s.step(1500)                       # materialised gradients: fine
+    assert s._optimizer.step_count == 1
