@@ -146,12 +146,12 @@ def test_rank1_step_is_refused_after_post_backward(pkg, synth):
     """The rank-1 shN update rebuilds its gradient rows from the current means: after post_backward (noise on every mean,
     relocated rows) those are no longer the forward's, so the strategy refuses it; the reference's order with a
     materialised shN gradient goes through."""
-    s, P, M, V = build(pkg, synth, 1500, 1, cap=3000)
+    s, P, M, V = build(pkg, synth, 1501, 1, cap=3000)
     s.grads.flat.normal_()
     marker = object()
-    s.post_backward(1500)
+    s.post_backward(1501)              # no refinement on this iteration: noise only
     with pytest.raises(RuntimeError, match="moved the means"):
-        s.step(1500, rasterizer=marker)
+        s.step(1501, rasterizer=marker)
     assert s._optimizer.step_count == 0
-    s.step(1500)                       # materialised gradients: fine
+    s.step(1501)                       # materialised gradients: fine
     assert s._optimizer.step_count == 1
