@@ -507,10 +507,13 @@ int lfs_ewa_forward(const lfs_ewa_config* cfg, const lfs_splats* params, const f
  * the gradient of the FINAL image (the background term is folded in, pass the same background), grad_alpha
  * [1,H,W] or NULL. grads: the six raw-parameter gradients, overwritten (all N rows) or added to.
  * densification_info (device [2,N] or NULL): row 0 += 1 and row 1 += |d mean2d * (W/2, H/2)| for every Gaussian
- * that reached a tile (kernels_backward.cuh:228-232). The camera-pose gradient (grad_w2c) is not produced. */
+ * that reached a tile (kernels_backward.cuh:228-232). grad_w2c (device [4,4] row-major or NULL): the camera-pose
+ * gradient of kernels_backward.cuh:160-173, rows 0..2 = sum over those Gaussians of (gradient of the camera-space mean) x
+ * (mean, 1), row 3 zero; overwritten, or added to with `accumulate`. Like the reference's it carries the mean term only
+ * (not the pose's part in the covariance or the SH view direction). */
 int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const float* w2c, const float* cam_position,
                      const float* background, const float* alpha, const float* grad_image, const float* grad_alpha,
-                     const lfs_splats* grads, int accumulate, float* densification_info,
+                     const lfs_splats* grads, int accumulate, float* densification_info, float* grad_w2c,
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* FusedAdam::step after a ONE-camera lfs_ewa_backward whose grads->shN was NULL (that gradient is then not written):

@@ -88,7 +88,7 @@ _SIGNATURES = {
     "lfs_add_noise": [i32, vp, vp, vp, vp, vp, f32, vp],
     "lfs_quats_to_rotmats": [i32, vp, vp, vp],
     "lfs_ewa_forward": [C.POINTER(EwaConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, sz, vp],
-    "lfs_ewa_backward": [C.POINTER(EwaConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, C.POINTER(Splats), i32, vp, vp, sz, vp],
+    "lfs_ewa_backward": [C.POINTER(EwaConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, C.POINTER(Splats), i32, vp, vp, vp, sz, vp],
     "lfs_ewa_adam_step_rank1_sh": [C.POINTER(EwaConfig), C.POINTER(Splats), vp, C.POINTER(Splats), C.POINTER(Splats), C.POINTER(Splats),
                                    C.POINTER(C.c_float), C.c_double, C.c_double, C.c_double, i64, i32, f32, vp],
     "lfs_ewa_workspace_view": [C.POINTER(EwaConfig), vp, sz, C.POINTER(EwaView)],

@@ -682,7 +682,7 @@ int lfs_ewa_forward(const lfs_ewa_config* cfg, const lfs_splats* params, const f
 
 int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const float* w2c, const float* cam_position,
                      const float* background, const float* alpha, const float* grad_image, const float* grad_alpha,
-                     const lfs_splats* grads, int accumulate, float* densification_info, void* workspace,
+                     const lfs_splats* grads, int accumulate, float* densification_info, float* grad_w2c, void* workspace,
                      size_t workspace_bytes, void* stream) {
     int rc = check_ewa_cfg(cfg);
     if (rc != LFS_OK) return rc;
@@ -698,7 +698,7 @@ int lfs_ewa_backward(const lfs_ewa_config* cfg, const lfs_splats* params, const 
     rc = launch_ewa_blend_bwd(b, alpha, w.n_contrib, grad_image, grad_alpha, w.accum, st);
     if (rc != LFS_OK) return rc;
     return launch_ewa_epilogue(cfg->N, cfg->sh_coeffs, *params, cam, w.n_touched, w.records, w.accum, *grads, accumulate,
-                               densification_info, st);
+                               densification_info, grad_w2c, st);
 }
 
 int lfs_ewa_adam_step_rank1_sh(const lfs_ewa_config* cfg, const lfs_splats* params, const float* cam_position,

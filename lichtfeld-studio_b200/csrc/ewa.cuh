@@ -37,6 +37,6 @@ int launch_ewa_blend_bwd(const EwaBlendArgs& a, const float* alpha, const int32_
 // preprocess_backward_cu + SH backward; writes all N rows of the six gradient tensors (zeros for culled Gaussians)
 // or adds to them; densification_info [2,N] may be null.
 int launch_ewa_epilogue(int N, int K, const lfs_splats& p, const EwaCamera& cam, const int32_t* n_touched, const float4* records,
-                        const float* accum, const lfs_splats& g, int accumulate, float* densification_info, cudaStream_t st);
+                        const float* accum, const lfs_splats& g, int accumulate, float* densification_info, float* grad_w2c, cudaStream_t st);
 
 }  // namespace lfs

@@ -293,13 +293,22 @@ __global__ void __launch_bounds__(kBlock, 4) ewa_blend_bwd_kernel(
 // memory) are read as one coalesced run into shared memory, every lane then works on its own row in place
 // (coefficient in, gradient out), and the 32 gradient rows leave as one coalesced run.
 // capped at 64 registers (the compiler takes 114 unasked): this stage is latency bound and wants the fourth resident CTA
+// W2C: also the camera-pose gradient of kernels_backward.cuh:160-173, sum over the Gaussians that reached a tile of
+// (gradient of the camera-space mean) x (mean, 1), rows 0..2 of a [4,4] matrix: per warp a shuffle reduction, per CTA 12
+// shared sums, 12 atomics per CTA at the end. A separate instantiation, so the default one keeps its registers.
+template <bool W2C>
 __global__ void __launch_bounds__(256, 4) ewa_epilogue_kernel(
     int N, int K, const float* __restrict__ means, const float* __restrict__ shN, const float* __restrict__ scaling_raw,
     const float* __restrict__ rotation_raw, EwaCamera cam, const int32_t* __restrict__ n_touched, const float4* __restrict__ records,
     const float* __restrict__ accum, float* __restrict__ g_means, float* __restrict__ g_sh0, float* __restrict__ g_shN,
     float* __restrict__ g_scaling, float* __restrict__ g_rotation, float* __restrict__ g_opacity, int accumulate,
-    float* __restrict__ densification_info) {
+    float* __restrict__ densification_info, float* __restrict__ grad_w2c) {
     extern __shared__ float s_rows[];
+    __shared__ float s_pose[8][12];
+    if (W2C) {
+        if (threadIdx.x < 96) s_pose[threadIdx.x / 12][threadIdx.x % 12] = 0.f;
+        __syncthreads();
+    }
     float r1[4], r2[4], r3[4], campos[3];
 #pragma unroll
     for (int k = 0; k < 4; ++k) { r1[k] = cam.w2c[k]; r2[k] = cam.w2c[4 + k]; r3[k] = cam.w2c[8 + k]; }
@@ -339,6 +348,11 @@ __global__ void __launch_bounds__(256, 4) ewa_epilogue_kernel(
         __syncwarp();
         float* out_rest = my + lane * rest;   // this lane's row: coefficients now, gradients afterwards
         float gm[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, g0[3] = {0.f, 0.f, 0.f}, go = 0.f;
+        float pose[12];
+        if (W2C) {
+#pragma unroll
+            for (int k = 0; k < 12; ++k) pose[k] = 0.f;
+        }
         if (!visible) {
             for (int k = 0; k < rest; ++k) out_rest[k] = 0.f;
         } else {
@@ -461,6 +475,13 @@ __global__ void __launch_bounds__(256, 4) ewa_epilogue_kernel(
         const float dcz = -j11 * (x * m2x + (dj11 - 2.0f * tx * dj13) / depth) - j22 * (y * m2y + (dj22 - 2.0f * ty * dj23) / depth);
 #pragma unroll
         for (int k = 0; k < 3; ++k) gm[k] = (r1[k] * dcx + r2[k] * dcy + r3[k] * dcz) + dmc[k];
+        if (W2C) {
+            const float dc[3] = {dcx, dcy, dcz}, mh[4] = {m0, m1, m2, 1.0f};
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) pose[r * 4 + k] = dc[r] * mh[k];
+        }
         // variances (columns of R) and the log-scale chain
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
@@ -489,6 +510,15 @@ __global__ void __launch_bounds__(256, 4) ewa_epilogue_kernel(
         }
         }  // visible
         __syncwarp();
+        if (W2C) {
+#pragma unroll
+            for (int k = 0; k < 12; ++k) {
+                float v = pose[k];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) s_pose[warp][k] += v;
+            }
+        }
         if (!g_shN) {
             // the caller rebuilds these rows from the sh0 gradient (lfs_ewa_adam_step_rank1_sh)
         } else if (accumulate) {
@@ -510,6 +540,15 @@ __global__ void __launch_bounds__(256, 4) ewa_epilogue_kernel(
                 reinterpret_cast<float4*>(g_rotation)[i] = make_float4(gq[0], gq[1], gq[2], gq[3]);
                 g_opacity[i] = go;
             }
+        }
+    }
+    if (W2C) {
+        __syncthreads();
+        if (threadIdx.x < 12) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += s_pose[w][threadIdx.x];
+            if (v != 0.f) atomicAdd(grad_w2c + threadIdx.x, v);
         }
     }
 }
@@ -536,15 +575,23 @@ int launch_ewa_blend_bwd(const EwaBlendArgs& a, const float* alpha, const int32_
 }
 
 int launch_ewa_epilogue(int N, int K, const lfs_splats& p, const EwaCamera& cam, const int32_t* n_touched, const float4* records,
-                        const float* accum, const lfs_splats& g, int accumulate, float* densification_info, cudaStream_t st) {
+                        const float* accum, const lfs_splats& g, int accumulate, float* densification_info, float* grad_w2c,
+                        cudaStream_t st) {
+    if (grad_w2c && !accumulate) cudaMemsetAsync(grad_w2c, 0, 16 * sizeof(float), st);
     if (N == 0) return LFS_OK;
     LFS_TIMED("ewa_epilogue", st);
     const size_t smem = (size_t)8 * 32 * (K - 1) * 3 * sizeof(float);
     if (smem > 200 * 1024) { set_error("ewa_epilogue: too many SH coefficients"); return LFS_EINVAL; }
-    if (smem > 48 * 1024) cudaFuncSetAttribute(ewa_epilogue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ewa_epilogue_kernel<<<grid_for(N, 256), 256, smem, st>>>(N, K, p.means, p.shN, p.scaling_raw, p.rotation_raw, cam, n_touched, records,
-                                                          accum, g.means, g.sh0, g.shN, g.scaling_raw, g.rotation_raw, g.opacity_raw,
-                                                          accumulate, densification_info);
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(ewa_epilogue_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(ewa_epilogue_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+#define LFS_EWA_EPILOGUE(W2C)                                                                                                       \
+    ewa_epilogue_kernel<W2C><<<grid_for(N, 256), 256, smem, st>>>(N, K, p.means, p.shN, p.scaling_raw, p.rotation_raw, cam, n_touched, \
+                                                                 records, accum, g.means, g.sh0, g.shN, g.scaling_raw, g.rotation_raw, \
+                                                                 g.opacity_raw, accumulate, densification_info, grad_w2c)
+    if (grad_w2c) LFS_EWA_EPILOGUE(true); else LFS_EWA_EPILOGUE(false);
+#undef LFS_EWA_EPILOGUE
     return check_launch("ewa_epilogue");
 }
 

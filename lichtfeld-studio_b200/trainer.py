@@ -333,15 +333,18 @@ class FastRasterizer:
 
     def backward(self, grad_image: torch.Tensor, grads: SplatData, background: torch.Tensor | None = None,
                  grad_alpha: torch.Tensor | None = None, accumulate: bool = False, densification_info: torch.Tensor | None = None,
-                 write_shN: bool = True):
+                 write_shN: bool = True, grad_w2c: torch.Tensor | None = None):
         """grad_image [3,H,W] w.r.t. the final (background-blended) image; densification_info [2,N] is updated in place.
-        write_shN=False leaves grads' shN tensor untouched (one-camera steps that update shN with adam_step_rank1_sh)."""
+        write_shN=False leaves grads' shN tensor untouched (one-camera steps that update shN with adam_step_rank1_sh).
+        grad_w2c: float32 [4,4] on the device, receives the camera-pose gradient (kernels_backward.cuh:160-173)."""
+        if grad_w2c is not None and (grad_w2c.dtype != torch.float32 or grad_w2c.numel() != 16 or not grad_w2c.is_contiguous()):
+            raise ValueError("grad_w2c must be a contiguous float32 [4,4] tensor")
         cam = self._cam
         p, g = self.model.struct(), grads.struct()
         if not write_shN:
             g.shN = None
         call("lfs_ewa_backward", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam._campos), ptr(background), ptr(self.alpha),
-             ptr(grad_image), ptr(grad_alpha), C.byref(g), 1 if accumulate else 0, ptr(densification_info), ptr(self.ws),
+             ptr(grad_image), ptr(grad_alpha), C.byref(g), 1 if accumulate else 0, ptr(densification_info), ptr(grad_w2c), ptr(self.ws),
              self.ws.numel(), _stream())
 
     def adam_step_rank1_sh(self, exp_avg: SplatData, exp_avg_sq: SplatData, grads: SplatData, lrs, step_count: int,

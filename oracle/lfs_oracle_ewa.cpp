@@ -351,14 +351,15 @@ void orc_ewa_blend_bwd(int N, int W, int H, const int32_t* instance_ids, const i
     }
 }
 
-// preprocess_backward_cu (kernels_backward.cuh:19-233) without the camera-pose gradient. Only Gaussians with
+// preprocess_backward_cu (kernels_backward.cuh:19-233); g_mean_cam [N,3] (nullable) receives the gradient of every
+// camera-space mean, from which the caller sums the camera-pose gradient. Only Gaussians with
 // n_touched > 0 are written; the others keep what the buffers held (the reference zero-fills them beforehand).
 // densification_info [2,N] (nullable): row 0 += 1, row 1 += |grad_mean2d * (W/2, H/2)|.
 void orc_ewa_preprocess_bwd(int N, const float* means, const float* scales_raw, const float* rotations_raw, const float* shN,
                             const float* w2c, const float* cam_position, const int32_t* n_touched, const float* grad_mean2d,
                             const float* grad_conic, const float* grad_color, int active_sh_bases, int total_rest, int W, int H,
                             float fx, float fy, float cx, float cy, float* g_means, float* g_scales_raw, float* g_rotations_raw,
-                            float* g_sh0, float* g_shN, float* densification_info) {
+                            float* g_sh0, float* g_shN, float* densification_info, float* g_mean_cam) {
     const float* r1 = w2c;
     const float* r2 = w2c + 4;
     const float* r3 = w2c + 8;
@@ -431,6 +432,8 @@ void orc_ewa_preprocess_bwd(int N, const float* means, const float* scales_raw, 
                              -g.j11 * (g.x * m2x + hz1 / g.depth) - g.j22 * (g.y * m2y + hz2 / g.depth)};
         for (int k = 0; k < 3; ++k)
             g_means[(size_t)i * 3 + k] = (r1[k] * dc[0] + r2[k] * dc[1] + r3[k] * dc[2]) + dmean_color[k];
+        if (g_mean_cam)   // the summands of the camera-pose gradient (kernels_backward.cuh:160-173)
+            for (int k = 0; k < 3; ++k) g_mean_cam[(size_t)i * 3 + k] = dc[k];
         // variances: d/d(var_k) = r_k^T S r_k with r_k the k-th column of R
         const float* R = g.R;
         for (int k = 0; k < 3; ++k) {

@@ -481,12 +481,17 @@ def ewa_backward(params, fwd, grad_image, grad_alpha=None, densification_info=No
     shN = _f32(params["shN"])
     g_means, g_scales, g_rot = np.zeros((N, 3), np.float32), np.zeros((N, 3), np.float32), np.zeros((N, 4), np.float32)
     g_sh0, g_shN = np.zeros((N, 1, 3), np.float32), np.zeros_like(shN)
+    g_cam = np.zeros((N, 3), np.float32)
     f = lambda v: C.c_float(float(v))
     lib().orc_ewa_preprocess_bwd(i32(N), _p(means), _p(_f32(params["scaling_raw"])), _p(_f32(params["rotation_raw"])), _p(shN),
                                  _p(w2c), _p(cam_position), _p(fwd["n_touched"]), _p(gm2), _p(gcon), _p(gcol), i32(active),
                                  i32(total_rest), i32(W), i32(H), f(fx), f(fy), f(cx), f(cy), _p(g_means), _p(g_scales), _p(g_rot),
-                                 _p(g_sh0), _p(g_shN), _p(densification_info))
+                                 _p(g_sh0), _p(g_shN), _p(densification_info), _p(g_cam))
+    # camera-pose gradient (kernels_backward.cuh:160-173): sum of (camera-space mean gradient) x (mean, 1), rows 0..2
+    grad_w2c = np.zeros((4, 4), np.float64)
+    grad_w2c[:3, :3] = g_cam.astype(np.float64).T @ means.astype(np.float64)
+    grad_w2c[:3, 3] = g_cam.astype(np.float64).sum(0)
     vis = fwd["n_touched"] > 0
     gop = np.where(vis, gop, 0).astype(np.float32)
     return dict(means=g_means, sh0=g_sh0, shN=g_shN, scaling_raw=g_scales, rotation_raw=g_rot, opacity_raw=gop.reshape(N, 1),
-                grad_mean2d=gm2, grad_conic=gcon, grad_color=gcol)
+                grad_mean2d=gm2, grad_conic=gcon, grad_color=gcol, grad_w2c=grad_w2c.astype(np.float32))

@@ -64,7 +64,8 @@ def test_ewa_forward_backward_match_oracle(pkg, orc, synth, n, W, H, deg, active
     bwd = orc.ewa_backward(r["P"], fwd, gi, ga, dens_ref)
     grads = r["model"].like()
     dens = T(dens0)
-    r["rast"].backward(T(gi), grads, T(bg), T(ga[None]), densification_info=dens)
+    gw = torch.full((4, 4), 7.0, device=DEV)      # overwritten, not added to
+    r["rast"].backward(T(gi), grads, T(bg), T(ga[None]), densification_info=dens, grad_w2c=gw)
     for name in NAMES:
         a = grads.tensor(name).cpu().numpy()
         if a.size:
@@ -72,6 +73,14 @@ def test_ewa_forward_backward_match_oracle(pkg, orc, synth, n, W, H, deg, active
             assert (a[~vis] == 0).all(), name
     d = dens.cpu().numpy()
     assert np.array_equal(d[0], dens_ref[0]) and np.allclose(d[1], dens_ref[1], rtol=2e-3, atol=1e-6)
+    # camera-pose gradient (kernels_backward.cuh:160-173): rows 0..2, float32 sums of ~N terms against a float64 sum
+    gw = gw.cpu().numpy()
+    assert (gw[3] == 0).all() and rel_l2(gw[:3], bwd["grad_w2c"][:3]) < 1e-3, (gw, bwd["grad_w2c"])
+    # the gradients of the Gaussians do not depend on whether the pose gradient was asked for
+    grads2 = r["model"].like()
+    r["rast"].forward(r["cam"], T(bg))
+    r["rast"].backward(T(gi), grads2, T(bg), T(ga[None]))
+    assert rel_l2(grads2.flat.cpu().numpy(), grads.flat.cpu().numpy()) < 1e-5    # the blend backward sums with atomics
 
 
 def test_ewa_accumulate_and_overflow(pkg, orc, synth):
@@ -84,9 +93,15 @@ def test_ewa_accumulate_and_overflow(pkg, orc, synth):
     r["rast"].backward(gi, g1, T(bg))
     g2.flat.copy_(g1.flat)
     r["rast"].forward(r["cam"], T(bg))
-    r["rast"].backward(gi, g2, T(bg), accumulate=True)   # adds the same gradient once more
+    gw1, gw2 = torch.zeros(4, 4, device=DEV), torch.zeros(4, 4, device=DEV)
+    r["rast"].backward(gi, g2, T(bg), accumulate=True, grad_w2c=gw2)   # adds the same gradient once more
     for name in NAMES:
         assert rel_l2(g2.tensor(name).cpu().numpy(), 2.0 * g1.tensor(name).cpu().numpy()) < 1e-4, name
+    r["rast"].forward(r["cam"], T(bg))
+    r["rast"].backward(gi, g1.like(), T(bg), grad_w2c=gw1)
+    r["rast"].forward(r["cam"], T(bg))
+    r["rast"].backward(gi, g1.like(), T(bg), accumulate=True, grad_w2c=gw2)   # pose gradient: added to with `accumulate`
+    assert float(gw1.abs().max()) > 0 and rel_l2(gw2.cpu().numpy(), 2.0 * gw1.cpu().numpy()) < 1e-4
     # capacity too small: the overflow flag is raised, nothing is drawn, the backward leaves zeros
     n_inst = int(r["out"].status[1].item())
     small = tr.FastRasterizer(r["model"], 128, 96, 2, instance_capacity=n_inst // 2)

@@ -301,6 +301,29 @@ def test_ewa_step_against_reference(pkg, synth, R):
             assert rel_l2(a, r["grad_" + name]) < 1e-3, name
 
 
+def test_ewa_pose_gradient_against_reference(pkg, synth, R):
+    """grad_w2c of FastGSRasterize::backward (kernels_backward.cuh:160-173, returned when w2c requires a gradient) against
+    lfs_ewa_backward's: both sum ~N float32 terms with atomics in arbitrary order, hence the relative bound."""
+    tr = pkg.trainer
+    n, W, H, deg, seed = 20000, 250, 170, 3, 3
+    cfg, P, vm, K = make_scene(synth, n, W, H, deg, seed=seed)
+    bg = np.array([0.1, 0.2, 0.3], np.float32)
+    G = (torch.randn((3, H, W), generator=torch.Generator().manual_seed(4)) * 1e-3).to(DEV)
+    trn = R.make_trainer(P, [0.0] * 6, deg)
+    vm_t = T(vm[None]).clone().requires_grad_(True)
+    rr = trn.fast_rasterize(vm_t, float(K[0, 0]), float(K[1, 1]), float(K[0, 2]), float(K[1, 2]), W, H, T(bg))
+    (rr.image * G).sum().backward()
+    ref_gw = vm_t.grad[0].cpu().numpy()
+    assert np.abs(ref_gw[:3]).max() > 0 and (ref_gw[3] == 0).all()
+    model = tr.SplatData(n, (deg + 1) ** 2, DEV).load(P)
+    rast = tr.FastRasterizer(model, W, H, deg)
+    rast.forward(tr.Camera(T(vm), T(K), W, H), T(bg))
+    gw = torch.zeros(4, 4, device=DEV)
+    rast.backward(G, model.like(), T(bg), grad_w2c=gw)
+    gw = gw.cpu().numpy()
+    assert (gw[3] == 0).all() and rel_l2(gw[:3], ref_gw[:3]) < 1e-3, (gw, ref_gw)
+
+
 def test_equirectangular_camera_against_reference(pkg, synth, R, ref):
     """CameraModelType::EQUIRECTANGULAR (gsplat/Cameras.cuh:1003-1039): the whole sphere on a 2:1 image, no near-plane cull,
     Gaussians behind the camera carry a negative depth whose bit pattern sorts after every positive one
