@@ -401,6 +401,8 @@ def run_ours(args):
     # colours are evaluated once the side stream is done. Every kernel of every step is inside the timed region.
     side = torch.cuda.Stream(device=dev)
     ev_bwd, ev_color = torch.cuda.Event(), torch.cuda.Event()
+    ev_projected = torch.cuda.Event()
+    ev_projected.record()          # creates the handle that forward_lists(projected_event=...) records
     overlap = world == 1 and args.overlap
     state = {"color_pending": False}
 
@@ -432,13 +434,19 @@ def run_ours(args):
         if dp_split:
             # N > 1: the geometry groups are exchanged first; the colour groups (three quarters of the bytes) cross
             # NVLink on a side stream while this step's projection and tile lists are built
-            rast.forward_lists(cam)
+            if args.dp_color_after_projection:
+                # the colour exchange of the previous step starts when this projection kernel is done (event recorded inside
+                # forward_lists) and runs next to the sorting kernels
+                rast.forward_lists(cam, projected_event=ev_projected)
+                exchange.launch_color(after=ev_projected)
+            else:
+                rast.forward_lists(cam)
             exchange.wait_color()
             out = rast.forward_shade(bg)
             loss, v_render = lossfn(out.image, target)
             # one camera per rank: the shN gradient crosses NVLink as its two rank-1 factors (24 bytes per Gaussian)
             rast.backward(v_render, grads, bg, sh_factors=dp_rank1)
-            exchange.step_split(2000 + s + 1, side, rank1_sh=dp_rank1, sh_degree=deg)
+            exchange.step_split(2000 + s + 1, side, rank1_sh=dp_rank1, sh_degree=deg, defer_color=args.dp_color_after_projection)
             return loss
         if not overlap:
             out = rast.forward(cam, bg)
@@ -598,7 +606,7 @@ def run_ours(args):
         dist.all_gather(allc, chk)
         same_params = all(bool(torch.equal(allc[0], c)) for c in allc)
         exchange.raise_if_failed()      # no bounded wait of the timed steps ran out
-        small = dp_self_check(pkg, dev, rank, world, args.dp_mode, dp_split, dp_rank1, args.dp_ordering, args.dp_multicast)
+        small = dp_self_check(pkg, dev, rank, world, args.dp_mode, dp_split, dp_rank1, args.dp_ordering, args.dp_multicast, args.dp_color_after_projection)
         dp_check = {"ok": bool(same_params and small["ok"]), "bench_parameters_identical_on_all_ranks": bool(same_params), **small}
     if rank == 0:
         # launches inside one call that are not individually bracketed: scan = 3 kernels, sort = 3 per pass
@@ -689,7 +697,7 @@ def run_ours(args):
                           "cameras_per_rank": cams_per_rank,
                           "optimizer_overlap": bool(overlap), "optimizer": ("inside lfs_render_backward_adam" if (rank1_sh and args.one_call_optimizer) else "separate call"),
                           "shN_gradient": "rank-1, rebuilt inside Adam" if rank1_sh else ("rank-1 factors over NVLink" if dp_rank1 else "materialised"),
-                          "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split and cams_per_rank == 1 else "") + (f"+{exchange.ordering}" + ("+multimem" if exchange.mc_params else "") if args.dp_mode == "fused_p2p" else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
+                          "parallelism": (f"dp{world}:{args.dp_mode}" + ("+split" if dp_split and cams_per_rank == 1 else "") + (f"+{exchange.ordering}" + ("+multimem" if exchange.mc_params else "") + ("+colour-after-projection" if dp_split and args.dp_color_after_projection else "") if args.dp_mode == "fused_p2p" else "")) if world > 1 else "single", "l2": "inputs larger than L2 "
                           f"({model.flat.numel() * 4 * 4 / 1e6:.0f} MB of parameters, moments and gradients streamed per step)"},
                "clocks": clocks, "e2e": {"value": batch * 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": h2d,
                                          "d2h_bytes_per_step": d2h, "steps": n_e2e},
@@ -701,7 +709,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None, multicast=None):
+def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None, multicast=None, after_projection=False):
     """Cross-rank correctness of the exchange the benchmark just timed, on a small scene: three data-parallel steps with
     the same mode flags must leave bit-identical parameters on every rank, equal (to gradient-summation rounding) to what
     ONE process gets by rendering every camera itself, accumulating the gradients and applying Adam to their mean."""
@@ -740,9 +748,15 @@ def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None, mult
     rast = tr.Rasterizer(model, W, H, deg)
     ex = dp.GradExchange(model, grads, LRS, mode=mode, peer_ptrs=peer, ordering=ordering, multicast=multicast)
     side = torch.cuda.Stream(device=dev)
+    evp = torch.cuda.Event()
+    evp.record()
     for s in range(steps):
         if split:
-            rast.forward_lists(cam(s * world + rank))
+            if after_projection:
+                rast.forward_lists(cam(s * world + rank), projected_event=evp)
+                ex.launch_color(after=evp)
+            else:
+                rast.forward_lists(cam(s * world + rank))
             ex.wait_color()
             out = rast.forward_shade(bg)
         else:
@@ -750,7 +764,7 @@ def dp_self_check(pkg, dev, rank, world, mode, split, rank1, ordering=None, mult
         _, vr = lossfn(out.image, targets[s * world + rank])
         rast.backward(vr, grads, bg, sh_factors=bool(split and rank1))
         if split:
-            ex.step_split(2000 + s, side, rank1_sh=bool(rank1), sh_degree=deg)
+            ex.step_split(2000 + s, side, rank1_sh=bool(rank1), sh_degree=deg, defer_color=after_projection)
         else:
             ex.step(2000 + s)
     ex.wait_color()
@@ -984,6 +998,9 @@ def main():
     ap.add_argument("--dp-ordering", default="flags", choices=["flags", "nccl"],
                     help="N > 1, fused_p2p: how the ranks' kernels are ordered around the peer-memory exchange: flag words in peer "
                          "memory with bounded waits (lfs_dp_signal / lfs_dp_wait), or 4-byte NCCL all-reduces")
+    ap.add_argument("--dp-color-after-projection", action=argparse.BooleanOptionalAction, default=False,
+                    help="N > 1, split exchange: start the colour exchange of a step when the NEXT step's projection kernel has "
+                         "finished (event inside lfs_render_forward_lists_event), so that it runs next to the sorting kernels only")
     ap.add_argument("--dp-multicast", action=argparse.BooleanOptionalAction, default=None,
                     help="N > 1, fused_p2p: broadcast the new parameters with multimem.st through the NVSwitch multicast mapping of "
                          "the parameter buffer instead of one peer store per rank (default: environment LFS_DP_MULTICAST, else off)")

@@ -276,6 +276,13 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
  * that stream is done. lists + shade on one workspace = lfs_render_forward, bit for bit. */
 int lfs_render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat,
                              const float* K, void* workspace, size_t workspace_bytes, void* stream);
+/* lfs_render_forward_lists that also records `projected_event` (a cudaEvent_t of the caller, or NULL) on the stream right
+ * after the per-Gaussian projection kernel and before the sorting kernels: work on another stream that should not run
+ * next to the projection (the NVLink-bound colour exchange of a data-parallel step, whose queued peer stores slow it
+ * threefold) waits for this event and runs next to the sorts instead. */
+int lfs_render_forward_lists_event(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat,
+                                   const float* K, void* projected_event, void* workspace, size_t workspace_bytes,
+                                   void* stream);
 int lfs_render_forward_shade(const lfs_render_config* cfg, const lfs_splats* params, const float* background,
                              float* render, float* alpha, int32_t* status_dev,
                              void* workspace, size_t workspace_bytes, void* stream);

@@ -96,6 +96,7 @@ _SIGNATURES = {
     "lfs_ply_unpack_rows": [i32, i32, vp, C.POINTER(Splats), vp],
     "lfs_render_forward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, vp, vp, sz, vp],
     "lfs_render_forward_lists": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, sz, vp],
+    "lfs_render_forward_lists_event": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, sz, vp],
     "lfs_render_forward_shade": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, vp, sz, vp],
     "lfs_render_backward": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, C.POINTER(Splats), i32, vp, sz, vp],
     "lfs_render_backward_adam": [C.POINTER(RenderConfig), C.POINTER(Splats), vp, vp, vp, vp, C.POINTER(Splats), C.POINTER(Splats),

@@ -769,7 +769,7 @@ size_t lfs_render_workspace_bytes(const lfs_render_config* cfg) {
 
 // Shared body of the forward: per-Gaussian stage + tile lists (stage 1), shading + blending (stage 2).
 static int render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
-                                int with_colors, RenderWs& w, int* sel_out, cudaStream_t st) {
+                                int with_colors, RenderWs& w, int* sel_out, cudaStream_t st, cudaEvent_t projected = nullptr) {
     const int tw = (cfg->image_width + 15) / 16, th = (cfg->image_height + 15) / 16;
     int rc = launch_camera_setup(1, viewmat, cfg->viewmat_end, cfg_rs_type(*cfg), K, cfg->radial_coeffs, cfg->tangential_coeffs,
                                  cfg->thin_prism_coeffs, cfg->image_width, cfg->image_height, cfg->camera_model, w.cam, st);
@@ -784,6 +784,7 @@ static int render_forward_lists(const lfs_render_config* cfg, const lfs_splats* 
                              th, w.radii, w.means2d, w.depths, w.tiles, w.gkeys[0], w.gvals[0], w.records, w.bounds,
                              reinterpret_cast<float4*>(w.accum), w.counters + 2, st);
     if (rc != LFS_OK) return rc;
+    if (projected && cudaEventRecord(projected, st) != cudaSuccess) { set_error("cudaEventRecord failed"); return LFS_ECUDA; }
     TileListArgs a{};
     a.C = 1; a.N = cfg->N; a.tw = tw; a.th = th; a.tile_size = cfg->tile_size; a.sort = 1; a.keys_ready = 1;
     a.means2d = w.means2d; a.radii = w.radii; a.depths = w.depths; a.tiles = w.tiles;
@@ -826,8 +827,8 @@ int lfs_render_forward(const lfs_render_config* cfg, const lfs_splats* params, c
     return check_launch("lfs_render_forward");
 }
 
-int lfs_render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
-                             void* workspace, size_t workspace_bytes, void* stream) {
+int lfs_render_forward_lists_event(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
+                                   void* projected_event, void* workspace, size_t workspace_bytes, void* stream) {
     int rc = check_cfg(cfg);
     if (rc != LFS_OK) return rc;
     LFS_REQUIRE(params && viewmat && K && workspace, "null pointer");
@@ -835,9 +836,14 @@ int lfs_render_forward_lists(const lfs_render_config* cfg, const lfs_splats* par
     RenderWs w = carve_render(*cfg, workspace);
     if (workspace_bytes < w.bytes) { set_error("lfs_render_forward_lists: workspace too small"); return LFS_ECAPACITY; }
     int sel = 0;
-    rc = render_forward_lists(cfg, params, viewmat, K, 0, w, &sel, S(stream));
+    rc = render_forward_lists(cfg, params, viewmat, K, 0, w, &sel, S(stream), reinterpret_cast<cudaEvent_t>(projected_event));
     if (rc != LFS_OK) return rc;
     return check_launch("lfs_render_forward_lists");
+}
+
+int lfs_render_forward_lists(const lfs_render_config* cfg, const lfs_splats* params, const float* viewmat, const float* K,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    return lfs_render_forward_lists_event(cfg, params, viewmat, K, nullptr, workspace, workspace_bytes, stream);
 }
 
 int lfs_render_forward_shade(const lfs_render_config* cfg, const lfs_splats* params, const float* background, float* render,

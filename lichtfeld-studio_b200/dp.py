@@ -128,7 +128,10 @@ class GradExchange:
         self.color_ctas_per_sm = int(os.environ.get("LFS_DP_COLOR_CTAS", "1"))   # launch footprint of the overlapped part
         # when the colour exchange may start: 0 = with the geometry exchange (every rank's gradients are written), 1 = after this
         # rank's geometry kernel, 2 = after every rank's geometry kernel (the exchange on the critical path then has NVLink to itself)
-        self.color_after_geometry = int(os.environ.get("LFS_DP_COLOR_AFTER_GEOMETRY", "2") or 0)
+        # Measured on B200s (train_1m): with 8 ranks 2 is fastest (3.16 against 3.20 ms: the exchange on the critical path takes
+        # 0.15 instead of 0.5 ms), with 2 ranks 0 is (2.89 against 2.95 ms: there is little traffic to compete with).
+        default_after = "2" if self.world >= 8 else "0"
+        self.color_after_geometry = int(os.environ.get("LFS_DP_COLOR_AFTER_GEOMETRY", default_after) or 0)
 
     # -- helpers --------------------------------------------------------------------------------
     def _stream(self):
@@ -255,7 +258,7 @@ class GradExchange:
         if self._split is None:
             dev = self.model.flat.device
             st = {"side": side_stream, "group_b": dist.new_group() if self.world > 1 else None,
-                  "ev_grads": torch.cuda.Event(), "ev_geo": torch.cuda.Event(), "ev_color": torch.cuda.Event(), "pending": False}
+                  "ev_grads": torch.cuda.Event(), "ev_geo": torch.cuda.Event(), "ev_color": torch.cuda.Event(), "pending": False, "color_args": None}
             for cls, names in (("geo", GEOMETRY_CLASS), ("col", COLOR_CLASS)):
                 _, per = class_segments(self.model.capacity, self.model.K, names, self.world, self.rank, self.lrs)
                 st[cls + "_m"] = torch.zeros(max(per, 4), dtype=torch.float32, device=dev)
@@ -289,13 +292,16 @@ class GradExchange:
                   self.betas[1], self.eps, self.step_count, float(gs), int(ctas_per_sm), self._stream())
 
     def step_split(self, iteration: int, side_stream, grad_scale: float | None = None, rank1_sh: bool = False,
-                   sh_degree: int | None = None):
+                   sh_degree: int | None = None, defer_color: bool = False):
         """fused_p2p in two parts. On the current stream: rendezvous, reduce + Adam + broadcast of the geometry groups
         (means, scales, rotations, opacities), rendezvous. On `side_stream`: the same for the colour groups (sh0, shN:
         three quarters of the bytes), finishing with its own rendezvous on a second communicator. The caller may start
         the next step's projection and tile lists right away and must call wait_color() before anything reads the
-        colour groups or overwrites the gradients. rank1_sh: every rank rendered ONE camera and ran
-        backward(sh_factors=True); the shN gradient then crosses NVLink as 24 bytes per Gaussian and rank (sh_degree = the
+        colour groups or overwrites the gradients. defer_color: the colour kernels are not enqueued here but by
+        launch_color(after=event), which the caller invokes once the next step's forward_lists(projected_event=event) is
+        enqueued: the colour exchange then starts when the projection kernel has finished and runs next to the sorting
+        kernels (next to the projection, its queued peer stores slowed that kernel threefold). rank1_sh: every rank
+        rendered ONE camera and ran backward(sh_factors=True); the shN gradient then crosses NVLink as 24 bytes per Gaussian and rank (sh_degree = the
         degree the forward used)."""
         if self.mode != "fused_p2p":
             raise RuntimeError("step_split needs mode fused_p2p")
@@ -318,10 +324,25 @@ class GradExchange:
         if self.color_after_geometry == 2:
             st["ev_geo"].record(main)
         st["pending"] = True
+        st["color_args"] = (skip, rank1_sh, sh_degree, gs)
+        if not defer_color:
+            self.launch_color()
+
+    def launch_color(self, after: torch.cuda.Event | None = None):
+        """Enqueue the colour part of the last step_split() on the side stream; `after`: an event (already recorded on some
+        stream) that it additionally waits for. A no-op when it is already enqueued."""
+        st = self._split
+        if st is None or st.get("color_args") is None:
+            return
+        skip, rank1_sh, sh_degree, gs = st["color_args"]
+        st["color_args"] = None
+        model = self.model
         with torch.cuda.stream(st["side"]):
             # the colour exchange starts once every rank's gradients are written; optionally only after this rank's geometry
             # kernel or every rank's, so that the exchange on the critical path has the NVLink ports to itself
             st["side"].wait_event(st["ev_geo"] if self.color_after_geometry else st["ev_grads"])
+            if after is not None:
+                st["side"].wait_event(after)
             segs, _ = class_segments(model.capacity, model.K, COLOR_CLASS, self.world, self.rank, self.lrs, skip_shN=skip)
             # small footprint: this kernel shares the SMs with the next step's projection and sorting
             if rank1_sh:
@@ -341,6 +362,7 @@ class GradExchange:
     def wait_color(self):
         """Make the current stream wait for the colour part of the last step_split()."""
         if self._split is not None and self._split["pending"]:
+            self.launch_color()
             torch.cuda.current_stream().wait_event(self._split["ev_color"])
 
 

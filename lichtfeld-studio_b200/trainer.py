@@ -187,9 +187,11 @@ class Rasterizer:
         depth = None if self.channels == 3 else self.render[..., self.channels - 1:]
         return RenderOutput(image, self.alpha, self.W, self.H, self.status, depth, self.render)
 
-    def forward_lists(self, cam: Camera):
+    def forward_lists(self, cam: Camera, projected_event: torch.cuda.Event | None = None):
         """First half of forward(): per-Gaussian stage without colours and the tile lists. Needs only means, scales,
-        rotations and opacities, so it can run while the SH tensors are still being updated on another stream."""
+        rotations and opacities, so it can run while the SH tensors are still being updated on another stream.
+        projected_event: recorded on the current stream between the projection kernel and the sorting kernels (an event
+        that was recorded at least once before, so that its handle exists)."""
         if cam.width != self.W or cam.height != self.H:
             raise RuntimeError("camera size does not match the rasterizer")
         self.cfg.N = self.model.size
@@ -198,8 +200,13 @@ class Rasterizer:
         self.cfg.shutter = int(cam.shutter)
         self.cfg.viewmat_end = None if cam.viewmat_end is None else cam.viewmat_end.data_ptr()
         p = self.model.struct()
-        call("lfs_render_forward_lists", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), ptr(self.ws), self.ws.numel(),
-             _stream())
+        ev = None
+        if projected_event is not None:
+            ev = int(projected_event.cuda_event)
+            if not ev:
+                raise RuntimeError("projected_event has no handle yet: record it once before the first use")
+        call("lfs_render_forward_lists_event", C.byref(self.cfg), C.byref(p), ptr(cam.viewmat), ptr(cam.K), C.c_void_p(ev), ptr(self.ws),
+             self.ws.numel(), _stream())
 
     def forward_shade(self, background: torch.Tensor | None) -> RenderOutput:
         """Second half: SH colours of the visible Gaussians, then blending. forward_lists + forward_shade == forward."""
