@@ -155,23 +155,23 @@ def failure_detection(dp, tr, dev, rank, world, n, K, P):
     if rank == leaver:
         store.set("dp_failure/left", "1")      # what a heartbeat would stop saying
         store.wait([f"dp_failure/done{r}" for r in range(world - 1)], datetime.timedelta(seconds=60))
-        verdict = True
+        passed = True
     else:
         store.wait(["dp_failure/left"], datetime.timedelta(seconds=60))
         ex.step(2001)                          # the leaver's flag never arrives
         try:
             ex.raise_if_failed()
-            verdict = False
+            passed = False
         except RuntimeError as e:
-            verdict = f"ranks [{leaver}]" in str(e)
+            passed = f"ranks [{leaver}]" in str(e)
             if rank == 0:
                 print("detected:", e, flush=True)
         alive = float((torch.ones(1024, device=dev) * 2).sum())    # the context still works
-        verdict = verdict and alive == 2048.0
-        store.set(f"dp_failure/done{rank}", "1" if verdict else "0")
+        passed = passed and alive == 2048.0
+        store.set(f"dp_failure/done{rank}", "1" if passed else "0")
     votes = [store.get(f"dp_failure/done{r}") == b"1" for r in range(world - 1)]
     if rank == 0:
-        print("DP FAILURE DETECTION", "OK" if all(votes) and verdict else "FAILED", flush=True)
+        print("DP FAILURE DETECTION", "OK" if all(votes) and passed else "FAILED", flush=True)
 
 
 if __name__ == "__main__":

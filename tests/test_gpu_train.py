@@ -135,6 +135,21 @@ def test_split_forward_and_split_adam_equal_the_fused_calls(pkg, synth):
     sa, sb = a.state(), b.state()
     vis = (sa["radii"] > 0).all(-1)   # records of culled Gaussians are never written
     assert torch.equal(sa["radii"], sb["radii"]) and torch.equal(sa["records"][vis], sb["records"][vis])
+    # the same lists with an event recorded between the projection kernel and the sorting kernels: work of another stream
+    # that waits for it starts no earlier than the projection's end
+    c = tr.Rasterizer(model, W, H, deg)
+    ev = torch.cuda.Event()
+    with pytest.raises(RuntimeError, match="no handle"):
+        c.forward_lists(cam, projected_event=ev)
+    ev.record()
+    side = torch.cuda.Stream()
+    c.forward_lists(cam, projected_event=ev)
+    with torch.cuda.stream(side):
+        side.wait_event(ev)
+        radii_seen = c.state()["radii"].clone()           # written by the projection kernel
+    out_c = c.forward_shade(bg)
+    torch.cuda.synchronize()
+    assert ev.query() and torch.equal(out_a.image, out_c.image) and torch.equal(radii_seen, sa["radii"])
     rng = np.random.default_rng(0)
     v = T(rng.normal(size=(H, W, 3)).astype(np.float32))
     ga, gb = model.like(), model.like()
