@@ -129,8 +129,9 @@ class GradExchange:
         # when the colour exchange may start: 0 = with the geometry exchange (every rank's gradients are written), 1 = after this
         # rank's geometry kernel, 2 = after every rank's geometry kernel (the exchange on the critical path then has NVLink to itself)
         # Measured on B200s (train_1m): with 8 ranks 2 is fastest (3.16 against 3.20 ms: the exchange on the critical path takes
-        # 0.15 instead of 0.5 ms), with 2 ranks 0 is (2.89 against 2.95 ms: there is little traffic to compete with).
-        default_after = "2" if self.world >= 8 else "0"
+        # 0.15 instead of 0.5 ms), with 4 ranks 2 and 0 are level (3.045 / 3.054 ms), with 2 ranks 0 is fastest (2.89 against
+        # 2.95 ms: there is little traffic to compete with).
+        default_after = "2" if self.world >= 4 else "0"
         self.color_after_geometry = int(os.environ.get("LFS_DP_COLOR_AFTER_GEOMETRY", default_after) or 0)
 
     # -- helpers --------------------------------------------------------------------------------
