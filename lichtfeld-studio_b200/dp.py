@@ -161,11 +161,9 @@ class GradExchange:
         flag never arrived: they stopped stepping (crashed, hung on the host, or left the job)."""
         if self.status is None:
             return
-        st = self.status.tolist()
-        if st[0]:
-            missing = [r for r in range(self.world) if st[1] >> r & 1]
-            raise RuntimeError(f"data-parallel step: ranks {missing} did not reach step {st[3]} (flag slot {st[2]}) within "
-                               f"{self.wait_timeout_ns / 1e9:.1f} s; the parameters of this step are not valid")
+        msg = describe_wait_status(self.status.tolist(), self.world, self.wait_timeout_ns / 1e9)
+        if msg:
+            raise RuntimeError(msg)
 
     def collect_timing(self):
         """[(name, ms)] of the recorded rendezvous; synchronises."""
@@ -365,6 +363,17 @@ class GradExchange:
         if self._split is not None and self._split["pending"]:
             self.launch_color()
             torch.cuda.current_stream().wait_event(self._split["ev_color"])
+
+
+def describe_wait_status(status, world: int, timeout_s: float) -> str | None:
+    """The status word of lfs_dp_wait / lfs_dp_barrier ({failed, bit mask of the missing ranks, slot, step}) as a message,
+    or None when no wait ran out."""
+    failed, mask, slot, step = (int(x) for x in status[:4])
+    if not failed:
+        return None
+    missing = [r for r in range(world) if mask >> r & 1]
+    return (f"data-parallel step: ranks {missing} did not reach step {step} (flag slot {slot}) within {timeout_s:.1f} s; "
+            f"the parameters of this step are not valid")
 
 
 def symmetric_flat_buffers(numel: int, device, group=None):

@@ -108,3 +108,12 @@ def test_class_segments_partition_each_class_exactly_once(pkg):
                 size = capacity * w[name]
                 assert (cover[off:off + size] == (1 if name in names else 0)).all(), name
                 off += size
+
+
+def test_wait_status_names_the_missing_ranks(pkg):
+    """Host side of the bounded waits: the status word of lfs_dp_wait / lfs_dp_barrier as the error the step raises."""
+    dp = pkg.dp
+    assert dp.describe_wait_status([0, 0, 0, 0], 8, 20.0) is None
+    msg = dp.describe_wait_status([1, (1 << 7) | (1 << 2), 1, 41], 8, 0.5)
+    assert "ranks [2, 7]" in msg and "step 41" in msg and "slot 1" in msg and "0.5 s" in msg
+    assert "ranks [0]" in dp.describe_wait_status([1, 1, 0, 3], 2, 20.0)
