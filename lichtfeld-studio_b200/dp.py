@@ -256,7 +256,7 @@ class GradExchange:
     def _split_state(self, side_stream):
         if self._split is None:
             dev = self.model.flat.device
-            st = {"side": side_stream, "group_b": dist.new_group() if self.world > 1 else None,
+            st = {"side": side_stream, "group_b": dist.new_group() if (self.world > 1 and self.flags is None) else None,   # second communicator: NCCL ordering only
                   "ev_grads": torch.cuda.Event(), "ev_geo": torch.cuda.Event(), "ev_color": torch.cuda.Event(), "pending": False, "color_args": None}
             for cls, names in (("geo", GEOMETRY_CLASS), ("col", COLOR_CLASS)):
                 _, per = class_segments(self.model.capacity, self.model.K, names, self.world, self.rank, self.lrs)
