@@ -3,8 +3,11 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 tests/run_dp_check.py
 
 Every rank renders its own camera; the three exchanges (NCCL all-reduce, NCCL reduce-scatter + sharded Adam
-+ all-gather, fused peer-memory kernel) must leave the same parameters on every rank, equal to what one GPU
-gets by rendering all cameras itself and averaging the gradients. Not collected by pytest."""
++ all-gather, fused peer-memory kernel, also split over two streams and with the shN gradient as rank-1 factors) must
+leave the same parameters on every rank, equal to what one GPU gets by rendering all cameras itself and averaging the
+gradients. Then: the flag ordering against the NCCL ordering, the multimem.st broadcast (where the box has NVSwitch
+multicast), and failure detection: one rank stops stepping between steps (it stays alive, nothing of its own in flight)
+and the others' bounded waits report it. Run with NCCL_NVLS_ENABLE=0. Not collected by pytest."""
 import datetime
 import importlib
 import os
