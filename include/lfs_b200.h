@@ -55,8 +55,10 @@ const char* lfs_build_info(void);
 /* Opt-in per-kernel timing (the reference only has wall-clock ScopedTimer logging,
  * include/core/logger.hpp:382-401). While enabled, every kernel launch of this library is bracketed by
  * two CUDA events on its stream. lfs_profile_collect waits for the recorded events and returns up to
- * max_records (name, milliseconds) pairs in launch order; lfs_profile_enable(0 or 1) clears the list.
- * Not thread-safe; creates CUDA events, so leave it off in production and during graph capture. */
+ * max_records (name, milliseconds) pairs in launch order; every lfs_profile_enable call clears the list.
+ * `on` is a set of bits: 1 = CUDA events, 2 = an NVTX range (nvtx3, same names) around every launch for timeline
+ * tools (free unless a profiler is attached; records nothing for lfs_profile_collect). 0 switches both off.
+ * Not thread-safe; bit 1 creates CUDA events, so leave it off in production and during graph capture. */
 int lfs_profile_enable(int on);
 int lfs_profile_collect(int max_records, const char** names, float* ms);
 

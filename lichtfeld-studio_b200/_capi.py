@@ -162,8 +162,11 @@ def call(name: str, *args):
         raise LfsError(f"{name} failed ({rc}): {lib().lfs_last_error().decode()}")
 
 
-def profile_enable(on: bool):
-    lib().lfs_profile_enable(1 if on else 0)
+def profile_enable(on: bool, nvtx: bool = False):
+    """on: CUDA events around every launch (profile_collect); nvtx: an NVTX range of the same name around every launch."""
+    rc = lib().lfs_profile_enable((1 if on else 0) | (2 if nvtx else 0))
+    if rc != LFS_OK:
+        raise LfsError(f"lfs_profile_enable failed ({rc})")
 
 
 def profile_collect(max_records: int = 4096):

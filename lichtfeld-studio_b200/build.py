@@ -65,7 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     raise RuntimeError("nvcc failed:\n" + " ".join(res.args) + "\n" + res.stderr)
     objs = [str(OBJ / (s + ".o")) for s, _ in SOURCES]
     if force or jobs or _stale(OUT, objs):
-        subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", str(OUT)] + objs + ["-lcudart"])
+        subprocess.check_call([nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", str(OUT)] + objs + ["-lcudart", "-ldl"])
     return OUT
 
 

@@ -16,7 +16,7 @@
 
 namespace lfs {
 const char* last_error();
-void profile_enable(bool on);
+void profile_enable(bool events, bool nvtx);
 int profile_collect(int max_records, const char** names, float* ms);
 
 namespace {
@@ -191,7 +191,11 @@ using namespace lfs;
 extern "C" {
 
 const char* lfs_last_error(void) { return lfs::last_error(); }
-int lfs_profile_enable(int on) { lfs::profile_enable(on != 0); return LFS_OK; }
+int lfs_profile_enable(int on) {
+    if (on < 0 || on > 3) { lfs::set_error("lfs_profile_enable: flags must be 0..3"); return LFS_EINVAL; }
+    lfs::profile_enable((on & 1) != 0, (on & 2) != 0);
+    return LFS_OK;
+}
 int lfs_profile_collect(int max_records, const char** names, float* ms) { return lfs::profile_collect(max_records, names, ms); }
 const char* lfs_build_info(void) { return "lfs_b200 0.1 (sm_100a, CUDA " LFS_STR(CUDART_VERSION) ")"; }
 

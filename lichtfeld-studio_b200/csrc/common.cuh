@@ -15,8 +15,8 @@ void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 
 // Opt-in per-kernel timing (lfs_profile_enable): when on, a KernelTimer brackets a launch with two
-// CUDA events on the launching stream; lfs_profile_collect returns the elapsed times. Off by default
-// and free when off.
+// CUDA events on the launching stream; lfs_profile_collect returns the elapsed times. With the NVTX bit it opens an
+// NVTX range of the same name around the launch for timeline tools. Off by default and free when off.
 struct KernelTimer {
     KernelTimer(const char* name, cudaStream_t st);
     ~KernelTimer();
@@ -24,6 +24,7 @@ struct KernelTimer {
     cudaStream_t st_;
     void* a_;
     void* b_;
+    bool nvtx_;
 };
 #define LFS_TIMED(name, st) ::lfs::KernelTimer lfs_kernel_timer_(name, st)
 

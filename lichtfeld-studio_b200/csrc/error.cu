@@ -3,6 +3,8 @@
 #include <cstdio>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>   // header-only: ranges cost nothing unless a profiler attached its injection library
+
 #include "common.cuh"
 
 namespace lfs {
@@ -41,11 +43,13 @@ int num_sms() {
 
 namespace {
 struct ProfRec { const char* name; cudaEvent_t a, b; };
-bool g_prof = false;
+bool g_prof = false;   // bracket every launch with two CUDA events
+bool g_nvtx = false;   // open an NVTX range (the LFS_TIMED name) around every launch
 std::vector<ProfRec> g_recs;
 }  // namespace
 
-KernelTimer::KernelTimer(const char* name, cudaStream_t st) : name_(name), st_(st), a_(nullptr), b_(nullptr) {
+KernelTimer::KernelTimer(const char* name, cudaStream_t st) : name_(name), st_(st), a_(nullptr), b_(nullptr), nvtx_(g_nvtx) {
+    if (nvtx_) nvtxRangePushA(name);
     if (!g_prof) return;
     cudaEvent_t a, b;
     if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
@@ -53,15 +57,17 @@ KernelTimer::KernelTimer(const char* name, cudaStream_t st) : name_(name), st_(s
     a_ = a; b_ = b;
 }
 KernelTimer::~KernelTimer() {
+    if (nvtx_) nvtxRangePop();
     if (!a_) return;
     cudaEventRecord(reinterpret_cast<cudaEvent_t>(b_), st_);
     g_recs.push_back(ProfRec{name_, reinterpret_cast<cudaEvent_t>(a_), reinterpret_cast<cudaEvent_t>(b_)});
 }
 
-void profile_enable(bool on) {
+void profile_enable(bool events, bool nvtx) {
     for (auto& r : g_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
     g_recs.clear();
-    g_prof = on;
+    g_prof = events;
+    g_nvtx = nvtx;
 }
 int profile_collect(int max_records, const char** names, float* ms) {
     int n = 0;

@@ -111,3 +111,30 @@ def test_one_huge_gaussian_covers_every_tile(pkg, orc, synth):
         out = rast.forward(tr.Camera(T(vm), T(K), W, H), None)
         assert out.status.cpu().tolist()[:3] == [0, tiles, 1]
         assert float(out.alpha.min()) > 0.5
+
+
+def test_profiling_modes(pkg, synth):
+    """lfs_profile_enable: CUDA-event records per launch, NVTX ranges (no records; free without an attached profiler), both,
+    and a rejected flag value. The images do not depend on the mode."""
+    tr, capi = pkg.trainer, pkg._capi
+    W, H = 96, 64
+    cfg, P, vm, K = make_scene(synth, 3000, W, H, 1, seed=1)
+    model = tr.SplatData(3000, 4, DEV).load(P)
+    rast = tr.Rasterizer(model, W, H, 1)
+    cam, bg = tr.Camera(T(vm), T(K), W, H), torch.zeros(3, device=DEV)
+    base = rast.forward(cam, bg).image.clone()
+    try:
+        capi.profile_enable(True)
+        img = rast.forward(cam, bg).image.clone()
+        recs = capi.profile_collect()
+        assert torch.equal(img, base) and {"project_pack", "raster_fwd"} <= {n for n, _ in recs} and all(ms >= 0 for _, ms in recs)
+        capi.profile_enable(False, nvtx=True)
+        img = rast.forward(cam, bg).image.clone()
+        assert torch.equal(img, base) and capi.profile_collect() == []
+        capi.profile_enable(True, nvtx=True)
+        rast.forward(cam, bg)
+        assert len(capi.profile_collect()) == len(recs)
+        assert capi.lib().lfs_profile_enable(4) == capi.LFS_EINVAL
+    finally:
+        capi.profile_enable(False)
+    assert capi.profile_collect() == []
