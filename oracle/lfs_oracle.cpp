@@ -366,6 +366,16 @@ inline bool cam_point_to_image(const Camera& c, V3 p, float margin, V2& out) {
         out.y = (p.y / p.z) * c.fy + c.cy;
         return in_bounds_margin(out, c, margin);
     }
+    if (c.model == EQUIRECTANGULAR) {
+        // EquirectangularCameraModel::camera_ray_to_image_point (Cameras.cuh:1013-1026): azimuth / elevation of the point,
+        // the whole sphere on the image; the bounds check is computed and dropped, every point is valid
+        const float kPi = 3.14159265358979323846f;
+        const float azimuth = std::atan2(p.x, p.z);
+        const float elevation = std::asin(p.y / std::sqrt(p.x * p.x + p.y * p.y + p.z * p.z));
+        out.x = (azimuth / (2.0f * kPi) + 0.5f) * (float)c.W;
+        out.y = (elevation / kPi + 0.5f) * (float)c.H;
+        return true;
+    }
     if (c.model == FISHEYE) {
         if (p.z <= 0.f) return false;
         float n = numerically_stable_norm2(p.x, p.y);
@@ -386,6 +396,19 @@ inline bool cam_point_to_image(const Camera& c, V3 p, float margin, V2& out) {
 // image_point_to_camera_ray. Pinhole: Cameras.cuh:457-470. Fisheye: :961-1000 with
 // eval_poly_inverse_horner_newton<20> (:169-206).
 inline bool image_to_cam_ray(const Camera& c, float px, float py, V3& ray) {
+    if (c.model == EQUIRECTANGULAR) {
+        // image_point_to_camera_ray (Cameras.cuh:1028-1037): the literals 2.0 and 0.5 make the angles and the trigonometry
+        // double; the direction is rounded to float and normalised
+        const double kPi = (double)3.14159265358979323846f;
+        const double azimuth = 2.0 * kPi * (px / (float)c.W - 0.5);
+        const double elevation = kPi * (py / (float)c.H - 0.5);
+        const float dx = (float)(std::cos(elevation) * std::sin(azimuth));
+        const float dy = (float)std::sin(elevation);
+        const float dz = (float)(std::cos(azimuth) * std::cos(elevation));
+        const float len = std::sqrt(dx * dx + dy * dy + dz * dz);
+        ray = {dx / len, dy / len, dz / len};
+        return true;
+    }
     const float ux = (px - c.cx) / c.fx;
     const float uy = (py - c.cy) / c.fy;
     if (c.model == PINHOLE && c.distorted) {

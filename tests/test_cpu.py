@@ -571,3 +571,42 @@ def test_oracle_rolling_shutter_rows_equal_global_renders_at_the_row_pose(orc, s
     vmx = vm0.copy(); vmx[:3, 3] = (np.float32(1) - t) * vm0[:3, 3] + t * vm1[:3, 3]
     diff = np.abs(roll_x["render"][:, x] - orc.render_fwd(P, vmx, K, W, H, deg)["render"][:, x]).max(-1)
     assert np.quantile(diff, 0.9) < 2e-3
+
+
+def test_oracle_equirectangular_pixels_equal_pinhole_renders_along_the_pixel_ray(orc, synth):
+    """Pins the oracle's EQUIRECTANGULAR model (gsplat/Cameras.cuh:1003-1039) to its pinhole model, which the reference's
+    golden vectors pin: pixel (x, y) of an equirectangular render looks along (cos E sin A, sin E, cos A cos E) with
+    A = 2 pi ((x + 0.5) / W - 0.5), E = pi ((y + 0.5) / H - 0.5); a pinhole camera at the same position, rotated so that its
+    optical axis is that direction, sees the same colour at its principal point (the rasterizer evaluates the Gaussians
+    along the world-space ray; only culling and the depth order, which is by camera z in both, can differ)."""
+    n, W, H, deg = 3000, 129, 65, 2
+    P = synth.make_gaussians(n, 6, "cube", deg)
+    vm = np.eye(4, dtype=np.float32)
+    vm[:3, 3] = [0.0, 0.0, 4.0]
+    K = synth.intrinsics(40.0, 40.0, W / 2, H / 2)
+    bg = np.array([0.1, 0.2, 0.3], np.float32)
+    e = orc.render_fwd(P, vm, K, W, H, deg, background=bg, camera_model=orc.EQUIRECTANGULAR)
+    assert (e["radii"] > 0).all(-1).sum() > 0.8 * n          # no frustum: (nearly) everything is kept
+
+    def rot_y(a):
+        c, s = np.cos(a), np.sin(a)
+        return np.array([[c, 0, s, 0], [0, 1, 0, 0], [-s, 0, c, 0], [0, 0, 0, 1]], np.float64)
+
+    def rot_x(a):
+        c, s = np.cos(a), np.sin(a)
+        return np.array([[1, 0, 0, 0], [0, c, -s, 0], [0, s, c, 0], [0, 0, 0, 1]], np.float64)
+
+    errs, covered = [], 0
+    for x, y in [(64, 32), (60, 32), (70, 32), (64, 28), (64, 36), (58, 27), (72, 38), (62, 30), (67, 34)]:
+        A, E = 2 * np.pi * ((x + 0.5) / W - 0.5), np.pi * ((y + 0.5) / H - 0.5)
+        d = np.array([np.cos(E) * np.sin(A), np.sin(E), np.cos(A) * np.cos(E)])
+        Cm = rot_x(E) @ rot_y(-A)                      # camera rotation that takes d to the optical axis
+        assert np.allclose(Cm[:3, :3] @ d, [0, 0, 1], atol=1e-12)
+        p = orc.render_fwd(P, (Cm @ vm.astype(np.float64)).astype(np.float32), K, W, H, deg, background=bg, camera_model=orc.PINHOLE)
+        errs.append(float(np.abs(e["render"][y, x] - p["render"][H // 2, W // 2]).max()))
+        assert abs(float(e["alpha"][y, x, 0]) - float(p["alpha"][H // 2, W // 2, 0])) < 3e-2
+        covered += float(e["alpha"][y, x, 0]) > 0.05
+    assert covered >= 6                                       # the probes do look at the Gaussians
+    # a Gaussian that one model culls (sub-pixel radius, image margin) or a depth-order swap shows in a probe or two; the rest
+    # agree to rounding
+    assert max(errs) < 3e-2 and np.median(errs) < 1e-5 and sum(v < 1e-5 for v in errs) >= 6, errs

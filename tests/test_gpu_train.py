@@ -295,3 +295,40 @@ def test_state_with_reserved_capacity(pkg, orc, synth):
     assert np.array_equal(st["flatten_ids"].cpu().numpy(), fwd["flatten_ids"])
     assert np.array_equal(st["tile_offsets"].cpu().numpy()[:-1], fwd["tile_offsets"].reshape(-1))
     assert (st["last_ids"].cpu().numpy() != fwd["last_ids"]).sum() <= 2
+
+
+def test_equirectangular_fused_path_matches_oracle(pkg, orc, synth):
+    """CameraModelType::EQUIRECTANGULAR through the fused path against the CPU oracle (whose equirectangular model is pinned
+    to its pinhole model by a CPU test): camera inside the scene, so Gaussians behind the camera (negative depth) are drawn
+    too. atan2f / asinf of the device and of the host's libm differ in the last bit, so the per-Gaussian values are compared
+    with a bound instead of bit for bit and a few Gaussians may change tiles."""
+    tr = pkg.trainer
+    n, W, H, deg = 8000, 256, 128, 2
+    P = synth.make_gaussians(n, 6, "cube", deg)
+    P["scaling_raw"] = (P["scaling_raw"] + np.float32(0.7)).astype(np.float32)
+    vm = np.eye(4, dtype=np.float32)
+    vm[:3, 3] = [0.05, -0.02, 0.1]
+    K = synth.intrinsics(100.0, 100.0, W / 2, H / 2)
+    bg = np.array([0.2, 0.1, 0.3], np.float32)
+    fwd = orc.render_fwd(P, vm, K, W, H, deg, background=bg, camera_model=orc.EQUIRECTANGULAR)
+    assert (fwd["depths"][fwd["masks"]] < 0).sum() > 100           # the back hemisphere is populated
+    model = tr.SplatData(n, (deg + 1) ** 2, DEV).load(P)
+    rast = tr.Rasterizer(model, W, H, deg)
+    cam = tr.Camera(T(vm), T(K), W, H, camera_model=pkg._capi.EQUIRECTANGULAR)
+    out = rast.forward(cam, T(bg))
+    st = rast.state()
+    vis = fwd["masks"]
+    assert (st["radii"].cpu().numpy() != fwd["radii"]).any(-1).sum() <= n // 500
+    assert np.abs(st["means2d"].cpu().numpy()[vis] - fwd["means2d"][vis]).max() < 2e-2   # a few ulp of a coordinate near 256
+    assert abs(st["n_isects"] - fwd["flatten_ids"].size) <= fwd["flatten_ids"].size // 1000
+    diff = np.abs(out.image.cpu().numpy() - fwd["render"]).max(-1)
+    assert (diff > 1e-4).mean() < 2e-3 and np.quantile(diff, 0.99) < 1e-4, (diff.max(), (diff > 1e-4).mean())
+    rng = np.random.default_rng(3)
+    v = rng.normal(size=(H, W, 3)).astype(np.float32) * 1e-3
+    bwd = orc.render_bwd(P, fwd, vm, K, W, H, deg, v, background=bg, camera_model=orc.EQUIRECTANGULAR)
+    grads = model.like()
+    rast.backward(T(v), grads, T(bg))
+    for name in NAMES:
+        a = grads.tensor(name).cpu().numpy()
+        if a.size:
+            assert rel_l2(a, bwd[name]) < 2e-3, name
