@@ -1,6 +1,7 @@
 """Writes reference_step.npz: outputs of the REFERENCE'S OWN CUDA build (oracle/_ref/lfs_reference.so, the reference's
 unmodified kernels compiled by oracle/ref_build.py) for the inputs stored in tiny_step.npz (one small training step
-of 512 Gaussians at 64x48, SH degree 2), plus its relocation, Adam, SSIM and EWA results on seeded inputs. These are
+of 512 Gaussians at 64x48, SH degree 2), plus its relocation, Adam, SSIM and EWA results on seeded inputs and an
+equirectangular render of the same Gaussians from inside the scene. These are
 the vectors that pin the CPU oracle to the reference where no GPU is available (tests/test_cpu.py) and a second
 anchor for the CUDA library (tests/test_gpu_golden.py).
 
@@ -70,6 +71,16 @@ def build():
     moved = T(P["means"].copy())
     ref.add_noise(T(P["opacity_raw"]), T(P["scaling_raw"]), T(P["rotation_raw"]), T(noise), moved, 80.0)
     out.update(in_noise=noise, noise_means=moved.cpu().numpy(), rotmats=ref.quats_to_rotmats(T(P["rotation_raw"])).cpu().numpy())
+    # EQUIRECTANGULAR camera (gsplat/Cameras.cuh:1003-1039) with the camera INSIDE the cube of Gaussians, so that the back
+    # hemisphere (negative depths) is populated: the reference's rasterize() from the raw parameters, 64x32
+    eq_vm = np.eye(4, dtype=np.float32)
+    eq_vm[:3, 3] = [0.05, -0.02, 0.1]
+    We, He = 64, 32
+    t = R.make_trainer(P, [0.0] * 6, deg)
+    rr = t.render_no_grad(True, T(eq_vm[None]), Kt, We, He, T(bg), 3)
+    pe = ref.projection_ut_3dgs_fused(means, q, s, o, T(eq_vm[None]), None, Kt, We, He, 0.3, 0.01, 1e4, 0.0, False, 3, None, 4, None, None, None)
+    out.update(eq_viewmat=eq_vm, eq_size=np.array([We, He], np.int32), eq_image=rr.image.cpu().numpy(), eq_alpha=rr.alpha.cpu().numpy(),
+               eq_radii=pe[0][0].cpu().numpy(), eq_means2d=pe[1][0].cpu().numpy(), eq_depths=pe[2][0].cpu().numpy())
     torch.cuda.synchronize()
     return out
 

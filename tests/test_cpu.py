@@ -610,3 +610,25 @@ def test_oracle_equirectangular_pixels_equal_pinhole_renders_along_the_pixel_ray
     # a Gaussian that one model culls (sub-pixel radius, image margin) or a depth-order swap shows in a probe or two; the rest
     # agree to rounding
     assert max(errs) < 3e-2 and np.median(errs) < 1e-5 and sum(v < 1e-5 for v in errs) >= 6, errs
+
+
+def test_oracle_equirectangular_matches_reference_cuda_golden(orc):
+    """The oracle's EQUIRECTANGULAR model against the reference's own CUDA build (eq_* of tests/golden/reference_step.npz,
+    written on a B200 by tests/golden/make_reference_golden.py): rasterize() of the 512 Gaussians of tiny_step.npz from a camera
+    inside the scene, 64x32, so 224 of them lie behind the camera. atan2f / asinf differ in the last bit between the device
+    and the host's libm, hence bounds on means2d instead of bit equality; radii and depths are exact."""
+    gold = np.load(Path(__file__).parent / "golden" / "reference_step.npz")
+    g = np.load(Path(__file__).parent / "golden" / "tiny_step.npz")
+    names = ("means", "sh0", "shN", "scaling_raw", "rotation_raw", "opacity_raw")
+    P = {k: g[f"in_{k}"] for k in names}
+    W, H = (int(x) for x in gold["eq_size"])
+    deg = int(g["in_size"][2])
+    f = orc.render_fwd(P, gold["eq_viewmat"], g["in_K"], W, H, deg, background=g["in_bg"], camera_model=orc.EQUIRECTANGULAR)
+    vis = (gold["eq_radii"] > 0).all(-1)
+    assert np.array_equal(f["masks"], vis) and (gold["eq_depths"][vis] < 0).sum() > 100
+    assert np.array_equal(f["radii"][vis], gold["eq_radii"][vis])
+    assert np.array_equal(f["depths"][vis].view(np.uint32), gold["eq_depths"][vis].view(np.uint32))
+    assert np.abs(f["means2d"][vis] - gold["eq_means2d"][vis]).max() < 5e-3
+    img = np.clip(f["render"], 0, 1).transpose(2, 0, 1)
+    assert np.abs(img - gold["eq_image"]).max() < 1e-5
+    assert np.abs(f["alpha"].reshape(H, W) - gold["eq_alpha"].reshape(H, W)).max() < 1e-5
