@@ -632,3 +632,42 @@ def test_oracle_equirectangular_matches_reference_cuda_golden(orc):
     img = np.clip(f["render"], 0, 1).transpose(2, 0, 1)
     assert np.abs(img - gold["eq_image"]).max() < 1e-5
     assert np.abs(f["alpha"].reshape(H, W) - gold["eq_alpha"].reshape(H, W)).max() < 1e-5
+
+
+def test_oracle_camera_features_match_reference_cuda_golden(orc):
+    """The oracle against the reference's own CUDA build for what the training-step golden does not exercise
+    (tests/golden/reference_cameras.npz, written on a B200 by tests/golden/make_reference_camera_golden.py from the outputs of
+    gsplat::rasterize_from_world_with_sh_fwd): OpenCV distortion (radial + tangential + thin prism), fisheye with radial
+    coefficients, two rolling shutters, the render modes D / ED / RGB_D / RGB_ED, the antialiased compensation and the scaling
+    modifier, on the 512 Gaussians and the 64x48 camera of tiny_step.npz. The reference is built with fast-math, the oracle
+    is IEEE: colours within 1e-5, the depth channel within 1e-5 of its range, one radius of 512 may differ."""
+    import contextlib
+    import importlib.util
+    here = Path(__file__).parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_reference_camera_golden", here / "make_reference_camera_golden.py")
+    G = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(G)                          # the case table and the coefficient values of the generator
+    gold, g = np.load(here / "reference_cameras.npz"), np.load(here / "tiny_step.npz")
+    P = {k: g[f"in_{k}"] for k in G.NAMES}
+    W, H, deg = (int(x) for x in g["in_size"])
+    vm, K, vm1 = g["in_viewmat"], g["in_K"], gold["viewmat_end"]
+    assert np.array_equal(vm1, G.end_pose(vm)) and np.array_equal(gold["radial"], G.RADIAL)
+    for name, c in G.CASES.items():
+        radial = None
+        if c["dist"]:
+            radial = orc.pack_distortion(radial=G.RADIAL, tangential=G.TANGENTIAL, thin_prism=G.THIN_PRISM)
+        if c["fish"]:
+            radial = G.FISHEYE_RADIAL
+        with (orc.shutter(vm1, c["rs"]) if c["rs"] != 4 else contextlib.nullcontext()):
+            f = orc.render_fwd(P, vm, K, W, H, deg, background=G.background(c["mode"]), camera_model=c["model"], radial=radial,
+                               render_mode=c["mode"], calc_compensations=c["aa"], scaling_modifier=c["smod"])
+        ref_render, ref_alpha, ref_radii = gold[name + "_render"], gold[name + "_alpha"], gold[name + "_radii"]
+        assert f["render"].shape == ref_render.shape, name
+        scale = np.maximum(np.abs(ref_render).reshape(H * W, -1).max(0), 1.0)      # depth channels are a few units wide
+        assert (np.abs(f["render"] - ref_render).reshape(H * W, -1) / scale).max() < 1e-5, name
+        assert np.abs(f["alpha"] - ref_alpha).max() < 1e-5, name
+        assert (f["radii"] != ref_radii).any(-1).sum() <= 1 and (ref_radii > 0).all(-1).sum() > 400, name
+    # the features do change the picture: each case differs from the plain pinhole RGB render where it should
+    plain = orc.render_fwd(P, vm, K, W, H, deg, background=G.background(0))["render"]
+    for name in ("dist_full", "fisheye", "rolling_tb", "antialiased_smod"):
+        assert np.abs(gold[name + "_render"] - plain).max() > 1e-2, name
