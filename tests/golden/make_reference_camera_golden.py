@@ -3,7 +3,8 @@ oracle/ref_build.py from the reference's unmodified sources) for the camera feat
 gsplat::rasterize_from_world_with_sh_fwd (gsplat/Rasterization.cpp:279-468) that the training-step golden does not
 exercise: OpenCV distortion, fisheye with radial coefficients, rolling shutter, the depth render modes, the antialiased
 compensation and the scaling modifier. Inputs are the 512 Gaussians and the 64x48 camera of tiny_step.npz; every case
-stores the operator's first two outputs (render_colors, render_alphas) and radii. These vectors pin the CPU oracle to the
+stores the operator's first two outputs (render_colors, render_alphas) and radii, and for seven of them the gradients of
+rasterize_from_world_with_sh_bwd for seeded output gradients. These vectors pin the CPU oracle to the
 reference for those features where no GPU is available (tests/test_cpu.py).
 
 Needs a GPU and the built reference module:
@@ -47,7 +48,17 @@ CASES = {
     "mode_ed": dict(model=0, mode=2, aa=False, smod=1.0, rs=4, dist=False, fish=False),
     "mode_rgb_ed_aa": dict(model=0, mode=4, aa=True, smod=1.0, rs=4, dist=False, fish=False),
     "antialiased_smod": dict(model=0, mode=0, aa=True, smod=0.7, rs=4, dist=False, fish=False),
+    "antialiased": dict(model=0, mode=0, aa=True, smod=1.0, rs=4, dist=False, fish=False),
 }
+# cases whose backward (gsplat::rasterize_from_world_with_sh_bwd, gsplat/Rasterization.cpp:470-642) is stored too: the
+# operator's gradients w.r.t. means, quats, scales, opacities and SH coefficients for seeded output gradients
+BACKWARD_CASES = ("dist_full", "dist_rgbd", "fisheye", "rolling_tb", "rolling_lr_rgbd", "mode_d", "antialiased")
+
+
+def output_gradients(name, H, W, ch):
+    """Seeded v_render [H,W,ch] and v_alpha [H,W,1] of a case (the CPU test draws the same ones)."""
+    rng = np.random.default_rng(sum(name.encode()))
+    return (rng.normal(size=(H, W, ch)).astype(np.float32) * 1e-2), (rng.normal(size=(H, W, 1)).astype(np.float32) * 1e-3)
 
 
 def channels(mode):
@@ -84,6 +95,16 @@ def build():
         out[name + "_render"] = res[0][0].cpu().numpy()
         out[name + "_alpha"] = res[1][0].cpu().numpy()
         out[name + "_radii"] = res[2][0].cpu().numpy()
+        if name in BACKWARD_CASES:
+            render, alpha, radii, means2d, depths, colors, offsets, flat, last_ids, comps = res
+            v_r, v_a = output_gradients(name, H, W, channels(c["mode"]))
+            comps_t = comps if comps is not None else torch.empty(0, device=dev)
+            b = ref.rasterize_from_world_with_sh_bwd(
+                means, q, s, o, sh, deg, T(bg[None]), None, W, H, 16, T(vm[None]), T(vm1[None]) if c["rs"] != 4 else None, T(K[None]),
+                c["model"], 0.3, 0.01, 10000.0, 0.0, float(c["smod"]), bool(c["aa"]), int(c["mode"]), None, int(c["rs"]), T(radial), T(tang),
+                T(prism), alpha, last_ids, offsets, flat, colors, radii, means2d, depths, comps_t, T(v_r[None]), T(v_a[None]))
+            for key, t in zip(("v_means", "v_quats", "v_scales", "v_opacities", "v_sh_coeffs"), b):
+                out[f"{name}_{key}"] = t.cpu().numpy()
     torch.cuda.synchronize()
     return out
 

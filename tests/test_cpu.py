@@ -639,8 +639,9 @@ def test_oracle_camera_features_match_reference_cuda_golden(orc):
     (tests/golden/reference_cameras.npz, written on a B200 by tests/golden/make_reference_camera_golden.py from the outputs of
     gsplat::rasterize_from_world_with_sh_fwd): OpenCV distortion (radial + tangential + thin prism), fisheye with radial
     coefficients, two rolling shutters, the render modes D / ED / RGB_D / RGB_ED, the antialiased compensation and the scaling
-    modifier, on the 512 Gaussians and the 64x48 camera of tiny_step.npz. The reference is built with fast-math, the oracle
-    is IEEE: colours within 1e-5, the depth channel within 1e-5 of its range, one radius of 512 may differ."""
+    modifier, on the 512 Gaussians and the 64x48 camera of tiny_step.npz, and for seven of the cases the operator's backward.
+    The reference is built with fast-math, the oracle is IEEE: colours within 1e-5, the depth channel within 1e-5 of its
+    range, one radius of 512 may differ, gradients within 2e-4 relative L2."""
     import contextlib
     import importlib.util
     here = Path(__file__).parent / "golden"
@@ -667,6 +668,20 @@ def test_oracle_camera_features_match_reference_cuda_golden(orc):
         assert (np.abs(f["render"] - ref_render).reshape(H * W, -1) / scale).max() < 1e-5, name
         assert np.abs(f["alpha"] - ref_alpha).max() < 1e-5, name
         assert (f["radii"] != ref_radii).any(-1).sum() <= 1 and (ref_radii > 0).all(-1).sum() > 400, name
+        if name in G.BACKWARD_CASES:
+            # gsplat::rasterize_from_world_with_sh_bwd for seeded output gradients: gradients w.r.t. the ACTIVATED parameters
+            v_r, v_a = G.output_gradients(name, H, W, G.channels(c["mode"]))
+            with (orc.shutter(vm1, c["rs"]) if c["rs"] != 4 else contextlib.nullcontext()):
+                b = orc.render_bwd(P, f, vm, K, W, H, deg, v_r, v_a, background=G.background(c["mode"]), camera_model=c["model"],
+                                   radial=radial)
+            pairs = (("v_means", b["means"]), ("v_quats", b["v_quats"]), ("v_scales", b["v_scales"]),
+                     ("v_opacities", b["v_opacities"].reshape(-1)), ("v_sh_coeffs", np.concatenate([b["sh0"], b["shN"]], 1)))
+            for key, mine in pairs:
+                theirs = gold[f"{name}_{key}"].reshape(mine.shape)
+                if np.abs(theirs).max() > 0:
+                    assert rel_l2(mine, theirs) < 2e-4, (name, key)      # measured: at most 3.3e-5
+                else:
+                    assert np.abs(mine).max() == 0, (name, key)         # depth-only mode: no colour gradient
     # the features do change the picture: each case differs from the plain pinhole RGB render where it should
     plain = orc.render_fwd(P, vm, K, W, H, deg, background=G.background(0))["render"]
     for name in ("dist_full", "fisheye", "rolling_tb", "antialiased_smod"):
