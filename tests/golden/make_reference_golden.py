@@ -58,6 +58,12 @@ def build():
     out.update(ewa_image=e["image"], ewa_alpha=e["alpha"], ewa_loss=np.float32(e["loss"]))
     for k in NAMES:
         out[f"ewa_grad_{k}"] = e[f"grad_{k}"]
+    # camera-pose gradient of the EWA path (kernels_backward.cuh:160-173): the same loss with a pose that requires a gradient
+    t2 = R.make_trainer(P, [0.0] * 6, deg)
+    vm_t = T(vm[None]).clone().requires_grad_(True)
+    rr2 = t2.fast_rasterize(vm_t, float(K[0, 0]), float(K[1, 1]), float(K[0, 2]), float(K[1, 2]), W, H, T(bg))
+    ref.photometric_loss(rr2.image, T(target), 0.2).backward()
+    out.update(ewa_grad_w2c=vm_t.grad[0].cpu().numpy())
     # relocation and Adam on tiny_step's inputs
     from oracle import oracle as orc
     no, ns = ref.relocation(T(g["in_reloc_opacity"]), T(g["in_reloc_scale"]), T(g["in_reloc_ratios"]), T(orc.binoms_table(51)), 51)

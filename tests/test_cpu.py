@@ -452,6 +452,13 @@ def test_oracle_matches_reference_cuda_golden(orc):
     ef = orc.ewa_forward(P, vm, orc.campos(vm), W, H, K_[0, 0], K_[1, 1], K_[0, 2], K_[1, 2], (deg + 1) ** 2, background=bg)
     d = np.abs(ef["image"] - r["ewa_image"]).max(0)
     assert (d > 1e-4).sum() <= 4 and np.quantile(d, 0.998) < 1e-4, d.max()
+    # its loss, backward (FastGSRasterize::backward) and camera-pose gradient (kernels_backward.cuh:160-173)
+    eloss, egr, _, _ = orc.photometric_loss(np.ascontiguousarray(ef["image"].transpose(1, 2, 0)), g["in_target"], 0.2)
+    assert abs(eloss - float(r["ewa_loss"])) < 1e-6
+    eb = orc.ewa_backward(P, ef, np.ascontiguousarray(egr.transpose(2, 0, 1)))
+    for k in names:
+        assert rel_l2(eb[k], r[f"ewa_grad_{k}"]) < 1e-3, k          # measured: 6e-5 .. 1e-4
+    assert (r["ewa_grad_w2c"][3] == 0).all() and rel_l2(eb["grad_w2c"][:3], r["ewa_grad_w2c"][:3]) < 1e-3     # measured: 3.4e-5
     # relocation (the reference's pow is fast-math), Adam, noise, rotation matrices
     no, ns = orc.relocation(g["in_reloc_opacity"], g["in_reloc_scale"], g["in_reloc_ratios"], orc.binoms_table(51), 51)
     assert np.allclose(no, r["reloc_opacity"], rtol=1e-3) and np.allclose(ns, r["reloc_scale"], rtol=1e-3)
