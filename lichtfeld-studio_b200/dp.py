@@ -365,6 +365,72 @@ class GradExchange:
             torch.cuda.current_stream().wait_event(self._split["ev_color"])
 
 
+class PeerLeft(RuntimeError):
+    """A peer rank stopped stepping (it raised, exited, or did not reach the step in time)."""
+
+    def __init__(self, message: str, ranks):
+        super().__init__(message)
+        self.ranks = list(ranks)
+
+
+class PeerWatch:
+    """Host side of failure detection, over the job's key-value store (torch.distributed's TCPStore / FileStore): what the
+    ranks tell each other BEFORE they launch a step, so that nobody enqueues an exchange a peer will never join.
+
+    Every rank publishes the number of the step it is about to launch (ready) and, when it stops for good (an exception
+    leaves the `with` block, or leave() is called), a mark with the reason. ready(step) returns once every peer has
+    published that step or a later one; it raises PeerLeft naming the ranks that left, or that did not get there within
+    `timeout_s`. The device-side counterpart, for a rank that dies without saying so, are the bounded waits of
+    lfs_dp_barrier (GradExchange.raise_if_failed). A store round trip costs tens of microseconds per peer: call ready() every
+    `interval` steps (it returns at once on the others)."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 30.0, interval: int = 1, prefix: str = "lfs_dp_watch",
+                 poll_s: float = 0.002):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.timeout_s, self.interval, self.prefix, self.poll_s = float(timeout_s), max(1, int(interval)), prefix, float(poll_s)
+
+    def _key(self, kind: str, rank: int) -> str:
+        return f"{self.prefix}/{kind}/{rank}"
+
+    def leave(self, reason: str = "left"):
+        self.store.set(self._key("left", self.rank), reason or "left")
+
+    def left(self) -> dict:
+        """{rank: reason} of the peers that have left."""
+        out = {}
+        for r in range(self.world):
+            if r != self.rank and self.store.check([self._key("left", r)]):
+                out[r] = self.store.get(self._key("left", r)).decode()
+        return out
+
+    def ready(self, step: int):
+        if step % self.interval:
+            return
+        import time
+        self.store.set(self._key("step", self.rank), str(int(step)))
+        deadline = time.monotonic() + self.timeout_s
+        waiting = [r for r in range(self.world) if r != self.rank]
+        while True:
+            gone = self.left()
+            if gone:
+                raise PeerLeft(f"data-parallel step {step}: ranks {sorted(gone)} left the job ({gone})", sorted(gone))
+            waiting = [r for r in waiting
+                       if not (self.store.check([self._key("step", r)]) and int(self.store.get(self._key("step", r))) >= step)]
+            if not waiting:
+                return
+            if time.monotonic() > deadline:
+                raise PeerLeft(f"data-parallel step {step}: ranks {waiting} did not get there within {self.timeout_s:.1f} s", waiting)
+            time.sleep(self.poll_s)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if exc_type is not None and not issubclass(exc_type, PeerLeft):
+            self.leave(f"{exc_type.__name__}: {exc}")
+        return False
+
+
 def describe_wait_status(status, world: int, timeout_s: float) -> str | None:
     """The status word of lfs_dp_wait / lfs_dp_barrier ({failed, bit mask of the missing ranks, slot, step}) as a message,
     or None when no wait ran out."""

@@ -117,3 +117,56 @@ def test_wait_status_names_the_missing_ranks(pkg):
     msg = dp.describe_wait_status([1, (1 << 7) | (1 << 2), 1, 41], 8, 0.5)
     assert "ranks [2, 7]" in msg and "step 41" in msg and "slot 1" in msg and "0.5 s" in msg
     assert "ranks [0]" in dp.describe_wait_status([1, 1, 0, 3], 2, 20.0)
+
+
+def _watch_worker(rank, world, port, tmp, scenario):
+    sys.path.insert(0, str(ROOT))
+    import importlib
+    pkg = importlib.import_module("lichtfeld-studio_b200")
+    dp = pkg.dp
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    watch = dp.PeerWatch(store, rank, world, timeout_s=(1.0 if scenario == "silent" else 20.0))
+    x = torch.ones(4)
+    done, verdict = 0, "finished"
+    try:
+        with watch:
+            for step in range(1, 6):
+                if rank == world - 1 and step == 3:
+                    if scenario == "raises":
+                        raise ValueError("bad batch")          # the failure, made on the host, between steps
+                    if scenario == "silent":
+                        store.wait([f"silent_done/{r}" for r in range(world - 1)])   # stops stepping without a word
+                        break
+                watch.ready(step)                              # nobody enqueues a collective that a peer will not join
+                dist.all_reduce(x)
+                done = step
+    except dp.PeerLeft as e:
+        verdict = f"peer_left:{e.ranks}:{e}"
+    except ValueError as e:
+        verdict = f"raised:{e}"
+    with open(os.path.join(tmp, f"watch_{scenario}_{rank}.txt"), "w") as f:
+        f.write(f"{done}|{verdict}")
+    if scenario == "silent" and rank != world - 1:
+        store.set(f"silent_done/{rank}", "1")
+    # no destroy_process_group barrier games: every rank reaches this point on its own
+
+
+@pytest.mark.parametrize("scenario", ["raises", "silent", "healthy"])
+def test_peer_watch_reports_a_rank_that_stops_stepping(pkg, tmp_path, scenario):
+    """Failure detection on the host, as gloo ranks: a rank that raises between steps (its `with PeerWatch` block publishes the
+    reason), a rank that silently stops (the others' ready() gives up after its limit), and a healthy run. In both failures the
+    others stop BEFORE the collective of the step the failed rank never launches, with two completed steps."""
+    world = 3
+    port = 29850 + (os.getpid() % 100) + {"raises": 0, "silent": 1, "healthy": 2}[scenario]
+    mp.spawn(_watch_worker, args=(world, port, str(tmp_path), scenario), nprocs=world, join=True)
+    res = [open(tmp_path / f"watch_{scenario}_{r}.txt").read().split("|", 1) for r in range(world)]
+    if scenario == "healthy":
+        assert all(d == "5" and v == "finished" for d, v in res)
+        return
+    for r in range(world - 1):
+        done, verdict = res[r]
+        assert done == "2" and verdict.startswith(f"peer_left:[{world - 1}]"), res
+        assert ("ValueError: bad batch" in verdict) if scenario == "raises" else ("did not get there within" in verdict), verdict
+    assert res[world - 1][0] == "2" and res[world - 1][1] == ("raised:bad batch" if scenario == "raises" else "finished")
