@@ -107,6 +107,7 @@ class GradExchange:
             self.v = torch.zeros(self.per, dtype=torch.float32, device=dev)
             self.g_shard = torch.zeros(self.per, dtype=torch.float32, device=dev)
             self.padded = self.per * self.world
+        self.mc_params = 0
         if mode == "fused_p2p":
             if peer_ptrs is None:
                 raise RuntimeError("fused_p2p needs the peer-mapped addresses of every rank's parameter and gradient buffers")
